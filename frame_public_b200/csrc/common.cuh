@@ -1,0 +1,150 @@
+// Shared helpers of the sm_100a kernel set: status/error plumbing, storage <-> fp32
+// conversion with one round-to-nearest-even at the store, 128-bit vector access, and launch
+// geometry sized for the 148 SMs of a B200.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/frame_b200.h"
+
+namespace fb200 {
+
+// ---- error plumbing -------------------------------------------------------------------------
+int set_error(int code, const char* fmt, ...);
+int cuda_error(cudaError_t err, const char* what);
+extern std::atomic<int64_t> g_launch_count;
+
+inline cudaStream_t as_stream(fb200_stream s) { return reinterpret_cast<cudaStream_t>(s); }
+
+#define FB200_CUDA_OK(expr)                                                 \
+  do {                                                                      \
+    cudaError_t fb200_err__ = (expr);                                       \
+    if (fb200_err__ != cudaSuccess) return ::fb200::cuda_error(fb200_err__, #expr); \
+  } while (0)
+
+// Call after every kernel launch: counts the launch and turns a launch error into a status.
+inline int after_launch(const char* kernel) {
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return cuda_error(err, kernel);
+  return FB200_OK;
+}
+
+constexpr int kNumSMs = 148;
+
+inline int itemsize_of(int dtype) {
+  switch (dtype) {
+    case FB200_F32: return 4;
+    case FB200_F64: return 8;
+    case FB200_F16: return 2;
+    case FB200_BF16: return 2;
+    case FB200_I8: return 1;
+    case FB200_I16: return 2;
+    case FB200_I32: return 4;
+    case FB200_I64: return 8;
+    case FB200_U8: return 1;
+    case FB200_BOOL: return 1;
+    default: return 0;
+  }
+}
+
+inline bool is_float_dtype(int dtype) {
+  return dtype == FB200_F32 || dtype == FB200_BF16 || dtype == FB200_F16;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Grid for a grid-stride kernel: enough CTAs to fill every SM `per_sm` times, never more than
+// the work needs.
+inline int grid_for(int64_t work_items, int threads, int per_sm) {
+  int64_t need = (work_items + threads - 1) / threads;
+  int64_t cap = static_cast<int64_t>(kNumSMs) * per_sm;
+  if (need < 1) need = 1;
+  return static_cast<int>(need < cap ? need : cap);
+}
+
+// ---- storage <-> fp32 ------------------------------------------------------------------------
+// Storage tags: the tensor dtype as the kernels see it.
+struct F32Tag { using storage = float; static constexpr int kVec = 4; };
+struct BF16Tag { using storage = __nv_bfloat16; static constexpr int kVec = 8; };
+struct F16Tag { using storage = __half; static constexpr int kVec = 8; };
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_f32(__half v) { return __half2float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+// __float2bfloat16_rn: RTNE; NaN becomes the canonical quiet NaN 0x7FFF (the CPU reference keeps
+// the payload's top bits) — both are NaN, and NaN never compares equal in the parity helper.
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+
+// Value after a store to T and a load back: the rounding point between fused steps.
+template <typename T> __device__ __forceinline__ float round_through(float v) {
+  return to_f32(from_f32<T>(v));
+}
+template <> __device__ __forceinline__ float round_through<float>(float v) { return v; }
+
+// 16-byte vector of storage elements.
+template <typename T> struct alignas(16) Vec16 { T v[16 / sizeof(T)]; };
+
+template <typename T>
+__device__ __forceinline__ void load_vec(const T* p, float (&out)[16 / sizeof(T)]) {
+  Vec16<T> raw = *reinterpret_cast<const Vec16<T>*>(p);
+#pragma unroll
+  for (int i = 0; i < int(16 / sizeof(T)); ++i) out[i] = to_f32(raw.v[i]);
+}
+
+template <typename T>
+__device__ __forceinline__ void store_vec(T* p, const float (&in)[16 / sizeof(T)]) {
+  Vec16<T> raw;
+#pragma unroll
+  for (int i = 0; i < int(16 / sizeof(T)); ++i) raw.v[i] = from_f32<T>(in[i]);
+  *reinterpret_cast<Vec16<T>*>(p) = raw;
+}
+
+// ---- elementwise op semantics (fp32 math) ----------------------------------------------------
+// Same formulas, in the same association, as the CPU reference lambdas; these files are
+// compiled with -fmad=false so that a*b+c is a rounded multiply followed by a rounded add.
+__device__ __forceinline__ float ew_sigmoid(float x) {
+  if (x >= 0.0f) return 1.0f / (1.0f + expf(-x));
+  const float e = expf(x);
+  return e / (1.0f + e);
+}
+
+__device__ __forceinline__ float ew_unary(int op, float x) {
+  switch (op) {
+    case FB200_EW_RELU: return x < 0.0f ? 0.0f : x;  // std::max(x, 0.f): NaN and -0 pass through
+    case FB200_EW_SQUARE: return x * x;
+    case FB200_EW_SIGMOID: return ew_sigmoid(x);
+    case FB200_EW_TANH: return tanhf(x);
+    case FB200_EW_RSQRT: return 1.0f / sqrtf(x);
+    case FB200_EW_GELU: {
+      const float inner = 0.7978845608028654f * (x + 0.044715f * (x * x * x));
+      return 0.5f * x * (1.0f + tanhf(inner));
+    }
+    case FB200_EW_SILU: return x * ew_sigmoid(x);
+    case FB200_EW_SOFTPLUS: return x > 20.0f ? x : log1pf(expf(x));
+    case FB200_EW_EXP: return expf(x);
+    default: return x;
+  }
+}
+
+__device__ __forceinline__ float ew_binary(int op, float a, float b) {
+  return op == FB200_EW_ADD ? a + b : a * b;
+}
+
+inline bool ew_is_binary(int op) { return op == FB200_EW_ADD || op == FB200_EW_MUL; }
+inline bool ew_is_known(int op) { return op >= FB200_EW_ADD && op <= FB200_EW_EXP; }
+
+}  // namespace fb200

@@ -1,0 +1,306 @@
+// conv2d (strict-fp32 direct form), conv1d and max_pool2d.
+//
+// conv2d follows src/backends/cpu/kernels/conv.cpp:225-257 (NCHW cross-correlation, groups,
+// stride, zero padding by skipping taps, accumulation order ci -> kh -> kw in fp32, bias last)
+// and replaces cudnnConvolutionForward + cudnnAddTensor
+// (src/backends/cuda/kernels/conv.cpp:385-520).  This file holds the strict-fp32 direct kernel:
+// every output keeps the CPU reference's accumulation order (compiled with -fmad=false), so for
+// fp32 it is bit-identical to the CPU backend.  The tensor-core implicit-GEMM form used when
+// TF32 is allowed lives in conv_tcgen05.cu.
+//
+// conv1d follows conv.cpp:565-589; the reference CUDA backend has no conv1d kernel at all and
+// drops the whole graph to its eager fallback (src/ops/schemas/conv.cpp:1021-1032).
+// max_pool2d follows src/backends/cpu/kernels/pool.cpp:187-233 (valid taps only, first maximum
+// wins) and replaces cudnnPoolingForward (src/backends/cuda/kernels/pool.cpp:231).
+#include "common.cuh"
+#include "epilogue.cuh"
+
+namespace fb200 {
+
+struct Conv2dDev {
+  int64_t n, cin, h, w, cout, kh, kw, sh, sw, ph, pw, groups, oh, ow, cpg, copg;
+};
+
+// One thread: one output pixel x CO_T consecutive output channels of one group.
+template <typename T, int CO_T>
+__global__ void __launch_bounds__(128)
+conv2d_direct_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ bias,
+                     T* __restrict__ out, Conv2dDev p, EpilogueDev epi) {
+  const int64_t pix_per_img = p.oh * p.ow;
+  const int64_t co_tiles = (p.copg + CO_T - 1) / CO_T;
+  const int64_t total = p.n * p.groups * co_tiles * pix_per_img;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += stride) {
+    const int64_t pix = i % pix_per_img;
+    int64_t rem = i / pix_per_img;
+    const int64_t ct = rem % co_tiles;
+    rem /= co_tiles;
+    const int64_t g = rem % p.groups;
+    const int64_t n = rem / p.groups;
+    const int64_t oh = pix / p.ow;
+    const int64_t ow = pix - oh * p.ow;
+    const int64_t co0 = g * p.copg + ct * CO_T;
+    const int64_t co_end = (ct + 1) * CO_T < p.copg ? CO_T : p.copg - ct * CO_T;
+    float acc[CO_T];
+#pragma unroll
+    for (int c = 0; c < CO_T; ++c) acc[c] = 0.0f;
+    for (int64_t ci = 0; ci < p.cpg; ++ci) {
+      const T* xc = x + ((n * p.cin + g * p.cpg + ci) * p.h) * p.w;
+      for (int64_t kh = 0; kh < p.kh; ++kh) {
+        const int64_t ih = oh * p.sh - p.ph + kh;
+        if (ih < 0 || ih >= p.h) continue;
+        for (int64_t kw = 0; kw < p.kw; ++kw) {
+          const int64_t iw = ow * p.sw - p.pw + kw;
+          if (iw < 0 || iw >= p.w) continue;
+          const float xv = to_f32(xc[ih * p.w + iw]);
+#pragma unroll
+          for (int c = 0; c < CO_T; ++c) {
+            if (c < co_end) {
+              const float wv = to_f32(w[(((co0 + c) * p.cpg + ci) * p.kh + kh) * p.kw + kw]);
+              acc[c] += xv * wv;
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < CO_T; ++c) {
+      if (c < co_end) {
+        const int64_t co = co0 + c;
+        float v = acc[c];
+        if (bias != nullptr) v += to_f32(bias[co]);
+        const int64_t oidx = ((n * p.cout + co) * p.oh + oh) * p.ow + ow;
+        v = apply_epilogue<T>(epi, v, oidx, ow, co);
+        out[oidx] = from_f32<T>(v);
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+conv1d_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ bias,
+              T* __restrict__ out, int64_t n, int64_t cin, int64_t l, int64_t cout, int64_t k,
+              int64_t stride_, int64_t padding, int64_t groups, int64_t ol) {
+  const int64_t cpg = cin / groups;
+  const int64_t copg = cout / groups;
+  const int64_t total = n * cout * ol;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += stride) {
+    const int64_t o = i % ol;
+    const int64_t rem = i / ol;
+    const int64_t co = rem % cout;
+    const int64_t b = rem / cout;
+    const int64_t g = co / copg;
+    float acc = 0.0f;
+    for (int64_t ci = 0; ci < cpg; ++ci) {
+      const T* xc = x + (b * cin + g * cpg + ci) * l;
+      const T* wc = w + (co * cpg + ci) * k;
+      for (int64_t kk = 0; kk < k; ++kk) {
+        const int64_t il = o * stride_ - padding + kk;
+        if (il < 0 || il >= l) continue;
+        acc += to_f32(xc[il]) * to_f32(wc[kk]);
+      }
+    }
+    if (bias != nullptr) acc += to_f32(bias[co]);
+    out[i] = from_f32<T>(acc);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+max_pool2d_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t n, int64_t c, int64_t h,
+                  int64_t w, int64_t kh, int64_t kw, int64_t sh, int64_t sw, int64_t ph,
+                  int64_t pw, int64_t oh, int64_t ow) {
+  const int64_t total = n * c * oh * ow;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += stride) {
+    const int64_t q = i % ow;
+    int64_t rem = i / ow;
+    const int64_t o = rem % oh;
+    rem /= oh;  // rem = n*c index
+    const T* xc = x + rem * h * w;
+    bool found = false;
+    float best = 0.0f;
+    T best_raw = T{};
+    for (int64_t a = 0; a < kh; ++a) {
+      const int64_t ih = o * sh - ph + a;
+      if (ih < 0 || ih >= h) continue;
+      for (int64_t b = 0; b < kw; ++b) {
+        const int64_t iw = q * sw - pw + b;
+        if (iw < 0 || iw >= w) continue;
+        const T raw = xc[ih * w + iw];
+        const float v = to_f32(raw);
+        if (!found || v > best) {
+          found = true;
+          best = v;
+          best_raw = raw;
+        }
+      }
+    }
+    out[i] = best_raw;  // the selected element itself: bit-exact, payloads included
+  }
+}
+
+}  // namespace fb200
+
+using namespace fb200;
+
+// Implemented in conv_tcgen05.cu; returns FB200_UNIMPLEMENTED when the shape is outside what the
+// tensor-core kernel covers, in which case the direct kernel below runs.
+extern "C" int fb200_conv2d_tcgen05(const void* x, const void* w, const void* bias, void* out,
+                                    const fb200_conv2d_params* p, int dtype,
+                                    const fb200_epilogue* epilogue, fb200_stream stream);
+
+extern "C" int fb200_conv2d(const void* x, const void* w, const void* bias, void* out,
+                            const fb200_conv2d_params* pp, int dtype, int allow_tf32,
+                            const fb200_epilogue* epilogue, fb200_stream stream) {
+  if (pp == nullptr) return set_error(FB200_INVALID_ARGUMENT, "conv2d: null params");
+  const fb200_conv2d_params& q = *pp;
+  if (q.n < 0 || q.cin < 1 || q.h < 1 || q.w < 1 || q.cout < 1 || q.kh < 1 || q.kw < 1 ||
+      q.stride_h < 1 || q.stride_w < 1 || q.pad_h < 0 || q.pad_w < 0 || q.groups < 1) {
+    return set_error(FB200_INVALID_ARGUMENT, "conv2d: invalid geometry");
+  }
+  if (q.cin % q.groups != 0 || q.cout % q.groups != 0) {
+    return set_error(FB200_INVALID_ARGUMENT,
+                     "conv2d: groups %lld must divide Cin %lld and Cout %lld", (long long)q.groups,
+                     (long long)q.cin, (long long)q.cout);
+  }
+  Conv2dDev d{};
+  d.n = q.n; d.cin = q.cin; d.h = q.h; d.w = q.w; d.cout = q.cout; d.kh = q.kh; d.kw = q.kw;
+  d.sh = q.stride_h; d.sw = q.stride_w; d.ph = q.pad_h; d.pw = q.pad_w; d.groups = q.groups;
+  d.oh = (q.h + 2 * q.pad_h - q.kh) / q.stride_h + 1;
+  d.ow = (q.w + 2 * q.pad_w - q.kw) / q.stride_w + 1;
+  if (q.h + 2 * q.pad_h < q.kh || q.w + 2 * q.pad_w < q.kw || d.oh < 1 || d.ow < 1) {
+    return set_error(FB200_INVALID_ARGUMENT, "conv2d: non-positive output size");
+  }
+  d.cpg = q.cin / q.groups;
+  d.copg = q.cout / q.groups;
+  if (q.n == 0) return FB200_OK;
+  if (x == nullptr || w == nullptr || out == nullptr) {
+    return set_error(FB200_INVALID_ARGUMENT, "conv2d: null argument");
+  }
+  if (allow_tf32 && dtype == FB200_F32) {
+    const int rc = fb200_conv2d_tcgen05(x, w, bias, out, pp, dtype, epilogue, stream);
+    if (rc != FB200_UNIMPLEMENTED) return rc;
+  }
+  EpilogueDev epi{};
+  if (int rc = make_epilogue(epilogue, &epi, "conv2d")) return rc;
+  cudaStream_t s = as_stream(stream);
+  constexpr int CO_T = 8;
+  const int64_t co_tiles = (d.copg + CO_T - 1) / CO_T;
+  const int64_t total = d.n * d.groups * co_tiles * d.oh * d.ow;
+  const int grid = grid_for(total, 128, 16);
+  switch (dtype) {
+    case FB200_F32:
+      conv2d_direct_kernel<float, CO_T><<<grid, 128, 0, s>>>(
+          static_cast<const float*>(x), static_cast<const float*>(w),
+          static_cast<const float*>(bias), static_cast<float*>(out), d, epi);
+      break;
+    case FB200_BF16:
+      conv2d_direct_kernel<__nv_bfloat16, CO_T><<<grid, 128, 0, s>>>(
+          static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+          static_cast<const __nv_bfloat16*>(bias), static_cast<__nv_bfloat16*>(out), d, epi);
+      break;
+    case FB200_F16:
+      conv2d_direct_kernel<__half, CO_T><<<grid, 128, 0, s>>>(
+          static_cast<const __half*>(x), static_cast<const __half*>(w),
+          static_cast<const __half*>(bias), static_cast<__half*>(out), d, epi);
+      break;
+    default:
+      return set_error(FB200_INVALID_ARGUMENT,
+                       "conv2d: dtype code %d is not float32/float16/bfloat16", dtype);
+  }
+  return after_launch("conv2d_direct_kernel");
+}
+
+extern "C" int fb200_conv1d(const void* x, const void* w, const void* bias, void* out, int64_t n,
+                            int64_t cin, int64_t l, int64_t cout, int64_t k, int64_t stride,
+                            int64_t padding, int64_t groups, int dtype, fb200_stream stream) {
+  if (n < 0 || cin < 1 || l < 1 || cout < 1 || k < 1 || stride < 1 || padding < 0 || groups < 1) {
+    return set_error(FB200_INVALID_ARGUMENT, "conv1d: invalid geometry");
+  }
+  if (cin % groups != 0 || cout % groups != 0) {
+    return set_error(FB200_INVALID_ARGUMENT, "conv1d: groups must divide Cin and Cout");
+  }
+  if (l + 2 * padding < k) return set_error(FB200_INVALID_ARGUMENT, "conv1d: non-positive output size");
+  const int64_t ol = (l + 2 * padding - k) / stride + 1;
+  if (n == 0) return FB200_OK;
+  if (x == nullptr || w == nullptr || out == nullptr) {
+    return set_error(FB200_INVALID_ARGUMENT, "conv1d: null argument");
+  }
+  cudaStream_t s = as_stream(stream);
+  const int grid = grid_for(n * cout * ol, 256, 8);
+  switch (dtype) {
+    case FB200_F32:
+      conv1d_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(x),
+                                                static_cast<const float*>(w),
+                                                static_cast<const float*>(bias),
+                                                static_cast<float*>(out), n, cin, l, cout, k,
+                                                stride, padding, groups, ol);
+      break;
+    case FB200_BF16:
+      conv1d_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(
+          static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+          static_cast<const __nv_bfloat16*>(bias), static_cast<__nv_bfloat16*>(out), n, cin, l,
+          cout, k, stride, padding, groups, ol);
+      break;
+    case FB200_F16:
+      conv1d_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(x),
+                                                 static_cast<const __half*>(w),
+                                                 static_cast<const __half*>(bias),
+                                                 static_cast<__half*>(out), n, cin, l, cout, k,
+                                                 stride, padding, groups, ol);
+      break;
+    default:
+      return set_error(FB200_INVALID_ARGUMENT,
+                       "conv1d: dtype code %d is not float32/float16/bfloat16", dtype);
+  }
+  return after_launch("conv1d_kernel");
+}
+
+extern "C" int fb200_max_pool2d(const void* x, void* out, int64_t n, int64_t c, int64_t h,
+                                int64_t w, int64_t kh, int64_t kw, int64_t stride_h,
+                                int64_t stride_w, int64_t pad_h, int64_t pad_w, int dtype,
+                                fb200_stream stream) {
+  if (n < 0 || c < 0 || h < 1 || w < 1 || kh < 1 || kw < 1 || stride_h < 1 || stride_w < 1 ||
+      pad_h < 0 || pad_w < 0) {
+    return set_error(FB200_INVALID_ARGUMENT, "max_pool2d: invalid geometry");
+  }
+  if (2 * pad_h > kh || 2 * pad_w > kw) {
+    return set_error(FB200_INVALID_ARGUMENT, "max_pool2d: padding*2 must not exceed kernel");
+  }
+  if (h + 2 * pad_h < kh || w + 2 * pad_w < kw) {
+    return set_error(FB200_INVALID_ARGUMENT, "max_pool2d: non-positive output size");
+  }
+  const int64_t oh = (h + 2 * pad_h - kh) / stride_h + 1;
+  const int64_t ow = (w + 2 * pad_w - kw) / stride_w + 1;
+  if (n == 0 || c == 0) return FB200_OK;
+  if (x == nullptr || out == nullptr) return set_error(FB200_INVALID_ARGUMENT, "max_pool2d: null argument");
+  cudaStream_t s = as_stream(stream);
+  const int grid = grid_for(n * c * oh * ow, 256, 8);
+  switch (dtype) {
+    case FB200_F32:
+      max_pool2d_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(x),
+                                                    static_cast<float*>(out), n, c, h, w, kh, kw,
+                                                    stride_h, stride_w, pad_h, pad_w, oh, ow);
+      break;
+    case FB200_BF16:
+      max_pool2d_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(
+          static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), n, c, h, w, kh,
+          kw, stride_h, stride_w, pad_h, pad_w, oh, ow);
+      break;
+    case FB200_F16:
+      max_pool2d_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(x),
+                                                     static_cast<__half*>(out), n, c, h, w, kh, kw,
+                                                     stride_h, stride_w, pad_h, pad_w, oh, ow);
+      break;
+    default:
+      return set_error(FB200_INVALID_ARGUMENT,
+                       "max_pool2d: dtype code %d is not float32/float16/bfloat16", dtype);
+  }
+  return after_launch("max_pool2d_kernel");
+}

@@ -1,0 +1,108 @@
+// matmul, strict-fp32 form: C[m,n] = sum_p A[m,p]*B[p,n] with an fp32 accumulator that visits
+// p in increasing order, one rounding at the store — src/backends/cpu/kernels/matmul.cpp:92-131.
+//
+// This is the kernel fb200_matmul uses when reduced-precision math is not allowed for fp32
+// (CompileOptions::allow_tf32 == false, include/frame/hal/backend.h:51-63) and for shapes whose
+// row pitch is not a multiple of 16 bytes (TMA cannot address them).  Each thread owns a
+// register micro-tile and accumulates every output over p = 0..K-1 in order; compiled with
+// -fmad=false the multiply and the add round separately exactly as the CPU reference (built
+// with -ffp-contract=off) does, so fp32 and bf16 results are BIT-IDENTICAL to the CPU backend.
+// The tensor-core path lives in gemm_tcgen05.cu.
+#include "common.cuh"
+#include "epilogue.cuh"
+
+namespace fb200 {
+
+template <typename T, int BM, int BN, int BK, int TM, int TN>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN))
+gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C, int64_t M,
+                 int64_t N, int64_t K, EpilogueDev epi) {
+  constexpr int THREADS = (BM / TM) * (BN / TN);
+  __shared__ float As[BK][BM + 4];
+  __shared__ float Bs[BK][BN + 4];
+  const int tid = threadIdx.x;
+  const int tx = tid % (BN / TN);
+  const int ty = tid / (BN / TN);
+  const int64_t tiles_n = (N + BN - 1) / BN;
+  const int64_t tiles_m = (M + BM - 1) / BM;
+  for (int64_t tile = blockIdx.x; tile < tiles_m * tiles_n; tile += gridDim.x) {
+    const int64_t m0 = (tile / tiles_n) * BM;
+    const int64_t n0 = (tile % tiles_n) * BN;
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
+    for (int64_t k0 = 0; k0 < K; k0 += BK) {
+      // A tile: BM rows x BK, K-contiguous in global; stored k-major in shared memory.
+      for (int e = tid; e < BM * BK; e += THREADS) {
+        const int r = e / BK, kk = e % BK;
+        const int64_t gm = m0 + r, gk = k0 + kk;
+        As[kk][r] = (gm < M && gk < K) ? to_f32(A[gm * K + gk]) : 0.0f;
+      }
+      for (int e = tid; e < BK * BN; e += THREADS) {
+        const int kk = e / BN, c = e % BN;
+        const int64_t gk = k0 + kk, gn = n0 + c;
+        Bs[kk][c] = (gk < K && gn < N) ? to_f32(B[gk * N + gn]) : 0.0f;
+      }
+      __syncthreads();
+      const int klen = static_cast<int>(K - k0 < BK ? K - k0 : BK);
+      for (int kk = 0; kk < klen; ++kk) {
+        float a[TM], b[TN];
+#pragma unroll
+        for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
+#pragma unroll
+        for (int j = 0; j < TN; ++j) b[j] = Bs[kk][tx * TN + j];
+#pragma unroll
+        for (int i = 0; i < TM; ++i)
+#pragma unroll
+          for (int j = 0; j < TN; ++j) acc[i][j] += a[i] * b[j];
+      }
+      __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+      const int64_t gm = m0 + ty * TM + i;
+      if (gm >= M) continue;
+#pragma unroll
+      for (int j = 0; j < TN; ++j) {
+        const int64_t gn = n0 + tx * TN + j;
+        if (gn >= N) continue;
+        const int64_t idx = gm * N + gn;
+        C[idx] = from_f32<T>(apply_epilogue<T>(epi, acc[i][j], idx, gn, gm));
+      }
+    }
+  }
+}
+
+template <typename T>
+static int launch_simt(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
+                       const EpilogueDev& epi, cudaStream_t s) {
+  const T* ap = static_cast<const T*>(a);
+  const T* bp = static_cast<const T*>(b);
+  T* cp = static_cast<T*>(c);
+  const int64_t big_tiles = ((m + 127) / 128) * ((n + 127) / 128);
+  if (big_tiles >= kNumSMs) {
+    const int grid = static_cast<int>(big_tiles < int64_t(kNumSMs) * 4 ? big_tiles : int64_t(kNumSMs) * 4);
+    gemm_simt_kernel<T, 128, 128, 16, 8, 8><<<grid, 256, 0, s>>>(ap, bp, cp, m, n, k, epi);
+  } else {
+    const int64_t tiles = ((m + 31) / 32) * ((n + 63) / 64);
+    const int grid = static_cast<int>(tiles < int64_t(kNumSMs) * 8 ? tiles : int64_t(kNumSMs) * 8);
+    gemm_simt_kernel<T, 32, 64, 32, 2, 4><<<grid, 256, 0, s>>>(ap, bp, cp, m, n, k, epi);
+  }
+  return after_launch("gemm_simt_kernel");
+}
+
+int gemm_simt(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int dtype,
+              const EpilogueDev& epi, cudaStream_t s) {
+  switch (dtype) {
+    case FB200_F32: return launch_simt<float>(a, b, c, m, n, k, epi, s);
+    case FB200_BF16: return launch_simt<__nv_bfloat16>(a, b, c, m, n, k, epi, s);
+    case FB200_F16: return launch_simt<__half>(a, b, c, m, n, k, epi, s);
+    default:
+      return set_error(FB200_INVALID_ARGUMENT,
+                       "matmul: dtype code %d is not float32/float16/bfloat16", dtype);
+  }
+}
+
+}  // namespace fb200

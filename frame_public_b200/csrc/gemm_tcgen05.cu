@@ -1,0 +1,449 @@
+// matmul on the 5th-generation tensor cores: C[M,N] = A[M,K] * B[K,N] (+ fused epilogue), all
+// row-major, bf16/f16 operands through tcgen05.mma kind::f16 and fp32 operands through
+// kind::tf32, fp32 accumulation in TMEM, one rounding at the store.
+//
+// Semantics: src/backends/cpu/kernels/matmul.cpp:92-131 (fp32 accumulate, single rounding).
+// Replaces the cublasLtMatmul call of src/backends/cuda/kernels/matmul.cpp:90-276, which also
+// ran bias and activation as separate launches; here they are the epilogue of the same kernel.
+//
+// Design (one persistent CTA per SM, 192 threads, warp-specialised):
+//   warp 0   TMA producer.  A tile [128 x BLOCK_K] is K-contiguous ("K-major" operand);
+//            B tile [BLOCK_K x BLOCK_N] is N-contiguous ("MN-major" operand), loaded as
+//            BLOCK_N*elt/128 boxes of 128 bytes x BLOCK_K rows.  Both land in 128-byte-swizzled
+//            shared memory; a ring of STAGES slots is handed over with full/empty mbarriers.
+//            No host-side transposes: the row-major B is consumed as it lies in HBM.
+//   warp 1   allocates TMEM (2 accumulators of BLOCK_N fp32 columns) and, from one thread, issues
+//            4 tcgen05.mma (M=128, N=BLOCK_N, K=32 bytes) per stage; tcgen05.commit releases the
+//            stage and, after the last k-block, publishes the accumulator.
+//   warps 2-5 epilogue: tcgen05.ld 32 lanes x 32 columns, the epilogue chain in fp32 registers
+//            (operands fetched with 128-bit loads), 128-bit stores.  The second accumulator lets
+//            the epilogue of tile i overlap the MMAs of tile i+1.
+// Tiles are walked in groups of 8 M-blocks so that concurrently resident CTAs share A and B
+// panels in the 126 MB L2.  Edge tiles rely on TMA zero fill for loads and masked stores.
+// Bound: tensor pipe.  FLOPs per launch = 2*M*N*K.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "epilogue.cuh"
+#include "sm100_ptx.cuh"
+
+namespace fb200 {
+
+int gemm_simt(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int dtype,
+              const EpilogueDev& epi, cudaStream_t s);
+
+using namespace sm100;
+
+constexpr int kBlockM = 128;
+constexpr int kGemmThreads = 192;
+constexpr int kGroupM = 8;
+
+enum GemmFault : int {
+  kFaultProducerEmpty = 101,
+  kFaultMmaFull = 102,
+  kFaultMmaTmemEmpty = 103,
+  kFaultEpilogueTmemFull = 104,
+};
+
+template <int ELT, int BLOCK_N>
+struct GemmCfg {
+  static constexpr int kBlockK = 128 / ELT;          // one 128-byte swizzle span of K
+  static constexpr int kUmmaKBytes = 32;              // K extent of one tcgen05.mma
+  static constexpr int kStepsPerBlock = 4;
+  static constexpr int kAStageBytes = kBlockM * 128;  // 16 KiB
+  static constexpr int kBChunkCols = 128 / ELT;       // N columns per 128-byte span
+  static constexpr int kBChunks = BLOCK_N / kBChunkCols;
+  static constexpr int kBChunkBytes = kBlockK * 128;
+  static constexpr int kBStageBytes = kBChunks * kBChunkBytes;
+  static constexpr int kStageBytes = kAStageBytes + kBStageBytes;
+  static constexpr int kStages = (BLOCK_N == 256) ? 4 : (BLOCK_N == 128 ? 6 : 8);
+  static constexpr int kTmemCols = 2 * BLOCK_N;
+  // B operand, MN-major, 128-byte swizzle: 8-row K groups are 1024 bytes apart (SBO); the next
+  // 128-byte span along N is one chunk further (LBO).  One MMA covers 32 bytes of K:
+  // 16 rows (two groups) for 2-byte elements, 8 rows (one group) for 4-byte elements.
+  static constexpr int kBKStepBytes = (kUmmaKBytes / ELT / 8) * 1024;
+  static constexpr size_t kSmemBytes = size_t(kStages) * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64_t tiles_n,
+                                            int64_t* tm, int64_t* tn) {
+  const int64_t per_group = kGroupM * tiles_n;
+  const int64_t group = tile / per_group;
+  const int64_t first_m = group * kGroupM;
+  const int64_t group_rows = tiles_m - first_m < kGroupM ? tiles_m - first_m : kGroupM;
+  const int64_t in_group = tile - group * per_group;
+  *tm = first_m + in_group % group_rows;
+  *tn = in_group / group_rows;
+}
+
+template <typename T, int ELT, int BLOCK_N>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                    const __grid_constant__ CUtensorMap tmap_b, T* __restrict__ C, int64_t M,
+                    int64_t N, int64_t K, uint32_t idesc, EpilogueDev epi, int* status) {
+  using Cfg = GemmCfg<ELT, BLOCK_N>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
+  uint8_t* base_ptr = smem_raw + (base - raw_addr);
+  const uint32_t bars = base + Cfg::kStages * Cfg::kStageBytes;
+  // barrier layout (8 bytes each): full[S], empty[S], tmem_full[2], tmem_empty[2], then tmem ptr
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (Cfg::kStages + s); };
+  auto tmem_full_bar = [&](int a) { return bars + 8u * (2 * Cfg::kStages + a); };
+  auto tmem_empty_bar = [&](int a) { return bars + 8u * (2 * Cfg::kStages + 2 + a); };
+  const uint32_t tmem_slot = bars + 8u * (2 * Cfg::kStages + 4);
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(
+      base_ptr + Cfg::kStages * Cfg::kStageBytes + 8 * (2 * Cfg::kStages + 4));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int64_t tiles_m = (M + kBlockM - 1) / kBlockM;
+  const int64_t tiles_n = (N + BLOCK_N - 1) / BLOCK_N;
+  const int64_t n_tiles = tiles_m * tiles_n;
+  const int64_t k_blocks = (K + Cfg::kBlockK - 1) / Cfg::kBlockK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tmem_full_bar(a), 1);
+      mbar_init(tmem_empty_bar(a), 4);  // one arrival per epilogue warp
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        int64_t tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+        for (int64_t kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, status, kFaultProducerEmpty)) { ok = false; break; }
+          mbar_arrive_expect_tx(full_bar(stage), Cfg::kStageBytes);
+          const uint32_t a_dst = base + stage * Cfg::kStageBytes;
+          const uint32_t b_dst = a_dst + Cfg::kAStageBytes;
+          tma_load_2d(a_dst, &tmap_a, full_bar(stage), static_cast<int32_t>(kb * Cfg::kBlockK),
+                      static_cast<int32_t>(tm * kBlockM));
+#pragma unroll
+          for (int c = 0; c < Cfg::kBChunks; ++c) {
+            tma_load_2d(b_dst + c * Cfg::kBChunkBytes, &tmap_b, full_bar(stage),
+                        static_cast<int32_t>(tn * BLOCK_N + c * Cfg::kBChunkCols),
+                        static_cast<int32_t>(kb * Cfg::kBlockK));
+          }
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, status, kFaultMmaTmemEmpty)) { ok = false; break; }
+        tcgen05_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
+        for (int64_t kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, status, kFaultMmaFull)) { ok = false; break; }
+          tcgen05_fence_after_sync();
+          const uint32_t a_addr = base + stage * Cfg::kStageBytes;
+          const uint32_t b_addr = a_addr + Cfg::kAStageBytes;
+#pragma unroll
+          for (int ks = 0; ks < Cfg::kStepsPerBlock; ++ks) {
+            // A: K-major, rows of 128 bytes, 8-row groups 1024 bytes apart; a K step is 32 bytes
+            // further inside the swizzled row.
+            const uint64_t a_desc = make_smem_desc_sw128(a_addr + ks * Cfg::kUmmaKBytes, 16, 1024);
+            const uint64_t b_desc = make_smem_desc_sw128(b_addr + ks * Cfg::kBKStepBytes,
+                                                         Cfg::kBChunkBytes, 1024);
+            const uint32_t accumulate = (kb > 0 || ks > 0) ? 1u : 0u;
+            if (ELT == 2) mma_f16(d_tmem, a_desc, b_desc, idesc, accumulate);
+            else mma_tf32(d_tmem, a_desc, b_desc, idesc, accumulate);
+          }
+          mma_commit(empty_bar(stage));  // the slot is free once these MMAs have read it
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        mma_commit(tmem_full_bar(acc));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // Epilogue warps 2..5; a warp may only touch TMEM lanes 32*(warp%4) .. +31.
+    const int quarter = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    constexpr int W = 16 / sizeof(T);
+    const bool vec_n = (N % W == 0) && ((reinterpret_cast<uintptr_t>(C) & 15u) == 0);
+    bool ok = true;
+    for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      int64_t tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+      if (!mbar_wait(tmem_full_bar(acc), acc_phase, status, kFaultEpilogueTmemFull)) { ok = false; break; }
+      tcgen05_fence_after_sync();
+      const int64_t row = tm * kBlockM + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                             static_cast<uint32_t>(acc * BLOCK_N);
+#pragma unroll 1
+      for (int c = 0; c < BLOCK_N / 32; ++c) {
+        const int64_t col0 = tn * BLOCK_N + c * 32;
+        if (col0 >= N) break;  // warp-uniform
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(c * 32), r);
+        tmem_ld_wait();
+        if (row < M) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = round_through<T>(__uint_as_float(r[j]));
+          const bool full_chunk = vec_n && col0 + 32 <= N;
+          const int64_t idx0 = row * N + col0;
+#pragma unroll 1
+          for (int s = 0; s < epi.n_ops; ++s) {
+            {
+              const int op = epi.ops[s];
+              const T* opnd = static_cast<const T*>(epi.operands[s]);
+              if (opnd != nullptr) {
+                const int mode = epi.modes[s];
+                if (mode == FB200_OPERAND_ROW) {
+                  const float rhs = to_f32(opnd[row]);
+#pragma unroll
+                  for (int j = 0; j < 32; ++j) v[j] = round_through<T>(ew_binary(op, v[j], rhs));
+                } else {
+                  const T* src = mode == FB200_OPERAND_FULL ? opnd + idx0 : opnd + col0;
+                  if (full_chunk && (reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
+#pragma unroll
+                    for (int q = 0; q < 32 / W; ++q) {
+                      float rhs[W];
+                      load_vec<T>(src + q * W, rhs);
+#pragma unroll
+                      for (int e = 0; e < W; ++e) {
+                        v[q * W + e] = round_through<T>(ew_binary(op, v[q * W + e], rhs[e]));
+                      }
+                    }
+                  } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                      if (col0 + j < N) v[j] = round_through<T>(ew_binary(op, v[j], to_f32(src[j])));
+                    }
+                  }
+                }
+              } else {
+                ew_unary_vec<T, 32>(op, v);
+              }
+            }
+          }
+          T* dst = C + idx0;
+          if (full_chunk) {
+#pragma unroll
+            for (int q = 0; q < 32 / W; ++q) {
+              float o[W];
+#pragma unroll
+              for (int e = 0; e < W; ++e) o[e] = v[q * W + e];
+              store_vec<T>(dst + q * W, o);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (col0 + j < N) dst[j] = from_f32<T>(v[j]);
+            }
+          }
+        }
+      }
+      tcgen05_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // Common exit: every role arrives here, on success or after a bounded wait gave up.
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    (void)cudaGetLastError();
+  });
+  return fn;
+}
+
+// 2-D row-major tensor [rows, cols] of `elt`-byte elements; box = 128 bytes x box_rows,
+// 128-byte swizzle, zero fill outside the tensor.
+int make_tmap_2d(CUtensorMap* map, const void* ptr, int dtype, int64_t rows, int64_t cols,
+                 int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return set_error(FB200_DEVICE_ERROR, "cuTensorMapEncodeTiled is not available");
+  const int elt = itemsize_of(dtype);
+  CUtensorMapDataType dt = dtype == FB200_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                           : dtype == FB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  cuuint64_t gdim[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t gstride[1] = {static_cast<cuuint64_t>(cols) * elt};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / elt), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, dt, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    return set_error(FB200_INTERNAL, "cuTensorMapEncodeTiled failed with code %d (rows %lld cols %lld)",
+                     static_cast<int>(r), (long long)rows, (long long)cols);
+  }
+  return FB200_OK;
+}
+
+// Per-device status word the kernels write when a bounded wait gives up (host-mapped, so the
+// host can read it after a stream synchronise without a copy).
+struct StatusWord { int* host = nullptr; int* dev = nullptr; };
+static StatusWord g_status[16];
+static std::mutex g_status_mu;
+
+int device_status_word(int** dev_ptr) {
+  int device = 0;
+  FB200_CUDA_OK(cudaGetDevice(&device));
+  if (device < 0 || device >= 16) return set_error(FB200_INVALID_ARGUMENT, "device index %d", device);
+  std::lock_guard<std::mutex> lock(g_status_mu);
+  if (g_status[device].host == nullptr) {
+    int* h = nullptr;
+    FB200_CUDA_OK(cudaHostAlloc(&h, sizeof(int), cudaHostAllocMapped));
+    *h = 0;
+    int* d = nullptr;
+    FB200_CUDA_OK(cudaHostGetDevicePointer(&d, h, 0));
+    g_status[device].host = h;
+    g_status[device].dev = d;
+  }
+  *dev_ptr = g_status[device].dev;
+  return FB200_OK;
+}
+
+template <typename T, int ELT, int BLOCK_N>
+static int launch_tc(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
+                     int dtype, const EpilogueDev& epi, cudaStream_t s) {
+  using Cfg = GemmCfg<ELT, BLOCK_N>;
+  CUtensorMap ta, tb;
+  if (int rc = make_tmap_2d(&ta, a, dtype, m, k, kBlockM)) return rc;
+  if (int rc = make_tmap_2d(&tb, b, dtype, k, n, Cfg::kBlockK)) return rc;
+  int* status = nullptr;
+  if (int rc = device_status_word(&status)) return rc;
+  const uint32_t fmt = dtype == FB200_F32 ? kFmtTF32 : (dtype == FB200_BF16 ? kFmtBF16 : kFmtF16);
+  const uint32_t idesc = make_instr_desc(fmt, /*a MN-major*/ 0, /*b MN-major*/ 1, kBlockM, BLOCK_N);
+  auto kernel = gemm_tcgen05_kernel<T, ELT, BLOCK_N>;
+  FB200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(Cfg::kSmemBytes)));
+  const int64_t tiles = ((m + kBlockM - 1) / kBlockM) * ((n + BLOCK_N - 1) / BLOCK_N);
+  const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
+  kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, static_cast<T*>(c), m, n, k, idesc,
+                                                      epi, status);
+  return after_launch("gemm_tcgen05_kernel");
+}
+
+template <typename T, int ELT>
+static int launch_tc_n(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
+                       int dtype, const EpilogueDev& epi, cudaStream_t s) {
+  const int64_t tiles_m = (m + kBlockM - 1) / kBlockM;
+  auto tiles = [&](int bn) { return tiles_m * ((n + bn - 1) / bn); };
+  if (n > 128 && tiles(256) >= kNumSMs) return launch_tc<T, ELT, 256>(a, b, c, m, n, k, dtype, epi, s);
+  if (n > 64 && tiles(128) >= kNumSMs) return launch_tc<T, ELT, 128>(a, b, c, m, n, k, dtype, epi, s);
+  if (n > 128 && tiles(64) < kNumSMs / 2) return launch_tc<T, ELT, 128>(a, b, c, m, n, k, dtype, epi, s);
+  return launch_tc<T, ELT, 64>(a, b, c, m, n, k, dtype, epi, s);
+}
+
+static bool tensor_core_eligible(const void* a, const void* b, const void* c, int64_t m, int64_t n,
+                                 int64_t k, int dtype, int allow_tf32) {
+  (void)m;
+  const int elt = itemsize_of(dtype);
+  if (dtype == FB200_F32 && !allow_tf32) return false;
+  if (dtype != FB200_F32 && dtype != FB200_BF16 && dtype != FB200_F16) return false;
+  // TMA: 16-byte aligned base and row pitch; coordinates must fit int32.
+  if ((k * elt) % 16 != 0 || (n * elt) % 16 != 0) return false;
+  if (a != nullptr && !aligned16(a)) return false;
+  if (b != nullptr && !aligned16(b)) return false;
+  (void)c;
+  if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX) return false;
+  return true;
+}
+
+}  // namespace fb200
+
+using namespace fb200;
+
+extern "C" int fb200_matmul_uses_tensor_cores(int64_t m, int64_t n, int64_t k, int dtype,
+                                              int allow_tf32) {
+  return tensor_core_eligible(nullptr, nullptr, nullptr, m, n, k, dtype, allow_tf32) ? 1 : 0;
+}
+
+extern "C" int fb200_matmul(const void* a, const void* b, void* c, int64_t m, int64_t n,
+                            int64_t k, int dtype, int allow_tf32, const fb200_epilogue* epilogue,
+                            fb200_stream stream) {
+  if (m < 0 || n < 0 || k < 0) return set_error(FB200_INVALID_ARGUMENT, "matmul: negative dimension");
+  if (!is_float_dtype(dtype)) {
+    return set_error(FB200_INVALID_ARGUMENT,
+                     "matmul: dtype code %d is not float32/float16/bfloat16", dtype);
+  }
+  if (m == 0 || n == 0) return FB200_OK;
+  if (c == nullptr || (k > 0 && (a == nullptr || b == nullptr))) {
+    return set_error(FB200_INVALID_ARGUMENT, "matmul: null argument");
+  }
+  EpilogueDev epi{};
+  if (int rc = make_epilogue(epilogue, &epi, "matmul")) return rc;
+  cudaStream_t s = as_stream(stream);
+  if (k > 0 && tensor_core_eligible(a, b, c, m, n, k, dtype, allow_tf32)) {
+    switch (dtype) {
+      case FB200_F32: return launch_tc_n<float, 4>(a, b, c, m, n, k, dtype, epi, s);
+      case FB200_BF16: return launch_tc_n<__nv_bfloat16, 2>(a, b, c, m, n, k, dtype, epi, s);
+      default: return launch_tc_n<__half, 2>(a, b, c, m, n, k, dtype, epi, s);
+    }
+  }
+  return gemm_simt(a, b, c, m, n, k, dtype, epi, s);
+}
+
+// Reads and clears the per-device kernel status word: 0 = no bounded wait has given up.
+extern "C" int fb200_kernel_status(int device, int* code) {
+  if (code == nullptr) return set_error(FB200_INVALID_ARGUMENT, "fb200_kernel_status: null out");
+  *code = 0;
+  if (device < 0 || device >= 16) return set_error(FB200_INVALID_ARGUMENT, "device index %d", device);
+  std::lock_guard<std::mutex> lock(g_status_mu);
+  if (g_status[device].host != nullptr) {
+    *code = *reinterpret_cast<volatile int*>(g_status[device].host);
+    *g_status[device].host = 0;
+  }
+  return FB200_OK;
+}

@@ -1,0 +1,750 @@
+// Whole-plan executor: the stream executor and arena allocator behind hal::Executable::run.
+//
+// Input is the step list ops::build_executable_plan derives from the nine-pass pipeline's output
+// (include/frame/ops/executable_plan.h:42-71): per step the op name, attribute values, input and
+// output slot numbers, output types, and for every intermediate the byte offset the memory
+// planner assigned inside one arena (src/ir/memory_plan.cpp:37-133).  The reference executes it
+// in CudaExecutable::run (src/backends/cuda/cuda_executable.cpp:41-128) by allocating the arena
+// with cudaMalloc inside every run, allocating every graph output separately and copying it
+// into the caller's tensor afterwards, and re-decoding attributes in every kernel call.
+//
+// Here, once per plan: the arena is allocated (one cudaMalloc, 256-byte aligned, the planner's
+// offsets are used as they are); attributes are decoded into POD launch records; constants are
+// materialised; matmul/conv2d steps absorb the elementwise group that follows them as their
+// epilogue when that is provably safe under the planner's buffer reuse; reshape becomes an
+// alias when no later step can overwrite the aliased bytes.  Per run: one loop of launches on
+// the caller's stream, graph outputs written straight into the caller's buffers, no allocation,
+// no synchronisation.
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+namespace fb200 {
+
+enum class Kind {
+  kMatmul, kConv2d, kConv1d, kMaxPool, kChain, kBiasAdd, kSoftmax, kLayerNorm, kScan, kMambaScan,
+  kTranspose, kSlice, kConcat, kSum, kCopy, kAlias, kConstant, kSkip
+};
+
+struct SlotInfo {
+  int dtype = 0;
+  std::vector<int64_t> dims;
+  int64_t numel = 1;
+  int64_t arena_offset = -1;  // >= 0: lives in the arena
+  int input_index = -1;       // >= 0: graph input
+  int output_index = -1;      // >= 0: graph output (first occurrence)
+  int alias_of = -1;          // >= 0: same bytes as that slot
+  void* constant = nullptr;   // materialised constant
+  size_t bytes() const { return static_cast<size_t>(numel) * itemsize_of(dtype); }
+};
+
+struct Attr {
+  std::string name, kind, text;
+};
+
+struct Step {
+  std::string op;
+  Kind kind = Kind::kSkip;
+  std::vector<int> in, out;
+  std::vector<Attr> attrs;
+  // decoded
+  std::vector<int> chain_ops, chain_arity;   // kChain, or the absorbed epilogue of a contraction
+  std::vector<int> epi_operand_slot;         // per epilogue step: slot of the operand or -1
+  std::vector<int> epi_mode;
+  int write_slot = -1;                       // where the (possibly fused) result goes
+  std::vector<int64_t> iv;                   // op-specific integers
+  double eps = 0.0;
+};
+
+}  // namespace fb200
+
+using namespace fb200;
+
+struct fb200_plan {
+  int device = 0;
+  int allow_tf32 = 0;
+  int opt_level = 1;
+  std::vector<SlotInfo> slots;
+  std::vector<Step> steps;
+  std::vector<int> input_slots, output_slots;
+  size_t arena_bytes = 0;
+  void* arena = nullptr;
+  std::vector<void*> owned;           // constants
+  std::vector<void*> stage_in, stage_out;  // device staging for run_host
+  int launches = 0;
+  std::mutex mu;
+};
+
+namespace fb200 {
+
+static const Attr* find_attr(const Step& s, const char* name) {
+  for (const Attr& a : s.attrs) if (a.name == name) return &a;
+  return nullptr;
+}
+
+static std::vector<int64_t> parse_int_list(const std::string& text) {
+  std::vector<int64_t> out;
+  const char* p = text.c_str();
+  while (*p) {
+    if ((*p >= '0' && *p <= '9') || *p == '-') {
+      char* end = nullptr;
+      out.push_back(strtoll(p, &end, 10));
+      p = end;
+    } else {
+      ++p;
+    }
+  }
+  return out;
+}
+
+static std::vector<double> parse_double_list(const std::string& text) {
+  std::vector<double> out;
+  const char* p = text.c_str();
+  while (*p) {
+    if ((*p >= '0' && *p <= '9') || *p == '-' || *p == '+' || *p == '.' || *p == 'i' || *p == 'n') {
+      char* end = nullptr;
+      const double v = strtod(p, &end);
+      if (end == p) { ++p; continue; }
+      out.push_back(v);
+      p = end;
+    } else {
+      ++p;
+    }
+  }
+  return out;
+}
+
+static std::string unquote(const std::string& t) {
+  std::string out;
+  size_t i = 0;
+  while (i < t.size() && t[i] != '"') ++i;
+  for (++i; i < t.size() && t[i] != '"'; ++i) {
+    if (t[i] == '\\' && i + 1 < t.size()) { ++i; out += (t[i] == 'n') ? '\n' : t[i]; }
+    else out += t[i];
+  }
+  return out;
+}
+
+static int ew_code(const std::string& name) {
+  static const char* names[] = {"", "add", "mul", "relu", "square", "sigmoid", "tanh", "rsqrt",
+                                "gelu", "silu", "softplus", "exp"};
+  for (int i = 1; i <= 11; ++i) if (name == names[i]) return i;
+  return 0;
+}
+
+static int dtype_from_name(const std::string& text) {
+  static const char* names[] = {"float32", "float64", "float16", "bfloat16", "int8", "int16",
+                                "int32", "int64", "uint8", "bool"};
+  for (int i = 0; i < 10; ++i) if (text.find(names[i]) != std::string::npos) return i;
+  return -1;
+}
+
+// Resolves a slot to the slot whose bytes it shares.
+static int root_slot(const fb200_plan& p, int s) {
+  while (p.slots[s].alias_of >= 0) s = p.slots[s].alias_of;
+  return s;
+}
+
+static bool ranges_overlap(const fb200_plan& p, int a, int b) {
+  a = root_slot(p, a);
+  b = root_slot(p, b);
+  if (a == b) return true;
+  const SlotInfo& x = p.slots[a];
+  const SlotInfo& y = p.slots[b];
+  if (x.arena_offset < 0 || y.arena_offset < 0) return false;  // distinct non-arena buffers
+  const int64_t xe = x.arena_offset + static_cast<int64_t>(x.bytes());
+  const int64_t ye = y.arena_offset + static_cast<int64_t>(y.bytes());
+  return x.arena_offset < ye && y.arena_offset < xe;
+}
+
+static int parse_plan(const char* text, fb200_plan* p) {
+  std::istringstream is(text);
+  std::string line;
+  int slot_count = 0;
+  Step* cur = nullptr;
+  while (std::getline(is, line)) {
+    if (line.empty()) continue;
+    std::istringstream ls(line);
+    std::string tag;
+    ls >> tag;
+    if (tag == "plan") {
+      std::string a, b;
+      ls >> a >> b;
+      if (a.rfind("slots=", 0) != 0 || b.rfind("arena=", 0) != 0) {
+        return set_error(FB200_INVALID_ARGUMENT, "plan: malformed header '%s'", line.c_str());
+      }
+      slot_count = atoi(a.c_str() + 6);
+      p->arena_bytes = strtoull(b.c_str() + 6, nullptr, 10);
+      p->slots.assign(static_cast<size_t>(slot_count), SlotInfo{});
+    } else if (tag == "in") {
+      int idx, dtype, rank;
+      ls >> idx >> dtype >> rank;
+      if (idx < 0 || idx >= slot_count || rank < 0 || rank > 8) {
+        return set_error(FB200_INVALID_ARGUMENT, "plan: bad input line '%s'", line.c_str());
+      }
+      SlotInfo& s = p->slots[idx];
+      s.dtype = dtype;
+      s.dims.resize(rank);
+      s.numel = 1;
+      for (int i = 0; i < rank; ++i) { ls >> s.dims[i]; s.numel *= s.dims[i]; }
+      s.input_index = static_cast<int>(p->input_slots.size());
+      p->input_slots.push_back(idx);
+    } else if (tag == "step") {
+      p->steps.emplace_back();
+      cur = &p->steps.back();
+      std::string tok;
+      ls >> cur->op >> tok;
+      if (tok.rfind("nin=", 0) != 0) return set_error(FB200_INVALID_ARGUMENT, "plan: bad step line '%s'", line.c_str());
+      const int nin = atoi(tok.c_str() + 4);
+      for (int i = 0; i < nin; ++i) { int s; ls >> s; cur->in.push_back(s); }
+      ls >> tok;
+      if (tok.rfind("nout=", 0) != 0) return set_error(FB200_INVALID_ARGUMENT, "plan: bad step line '%s'", line.c_str());
+      const int nout = atoi(tok.c_str() + 5);
+      for (int i = 0; i < nout; ++i) {
+        int slot, dtype, rank;
+        long long off;
+        ls >> slot >> dtype >> off >> rank;
+        if (slot < 0 || slot >= slot_count || rank < 0 || rank > 8) {
+          return set_error(FB200_INVALID_ARGUMENT, "plan: bad step output in '%s'", line.c_str());
+        }
+        SlotInfo& s = p->slots[slot];
+        s.dtype = dtype;
+        s.arena_offset = off;
+        s.dims.resize(rank);
+        s.numel = 1;
+        for (int d = 0; d < rank; ++d) { ls >> s.dims[d]; s.numel *= s.dims[d]; }
+        cur->out.push_back(slot);
+      }
+      for (int s : cur->in) {
+        if (s < 0 || s >= slot_count) return set_error(FB200_INVALID_ARGUMENT, "plan: slot out of range in '%s'", line.c_str());
+      }
+    } else if (tag == "attr") {
+      if (cur == nullptr) return set_error(FB200_INVALID_ARGUMENT, "plan: attr before any step");
+      Attr a;
+      ls >> a.name >> a.kind;
+      std::getline(ls, a.text);
+      if (!a.text.empty() && a.text[0] == ' ') a.text.erase(0, 1);
+      cur->attrs.push_back(a);
+    } else if (tag == "out") {
+      int s;
+      ls >> s;
+      if (s < 0 || s >= slot_count) return set_error(FB200_INVALID_ARGUMENT, "plan: bad out line '%s'", line.c_str());
+      if (p->slots[s].output_index < 0) p->slots[s].output_index = static_cast<int>(p->output_slots.size());
+      p->output_slots.push_back(s);
+    } else {
+      return set_error(FB200_INVALID_ARGUMENT, "plan: unknown line '%s'", line.c_str());
+    }
+  }
+  if (p->slots.empty() && slot_count != 0) return set_error(FB200_INVALID_ARGUMENT, "plan: missing header");
+  return FB200_OK;
+}
+
+// Decodes one step's attributes into its launch record.  Unknown op -> UNIMPLEMENTED with the
+// op name (the contract of Backend::compile, include/frame/hal/backend.h:103-104).
+static int decode_step(fb200_plan* p, Step& s) {
+  const std::string& op = s.op;
+  auto need = [&](const char* name) -> const Attr* {
+    const Attr* a = find_attr(s, name);
+    if (a == nullptr) set_error(FB200_INVALID_ARGUMENT, "op '%s' is missing required attribute '%s'", op.c_str(), name);
+    return a;
+  };
+  if (!s.out.empty()) s.write_slot = s.out[0];
+  if (op == "matmul") {
+    s.kind = Kind::kMatmul;
+  } else if (op == "conv2d") {
+    s.kind = Kind::kConv2d;
+    const Attr *st = need("stride"), *pd = need("padding"), *g = need("groups");
+    if (!st || !pd || !g) return FB200_INVALID_ARGUMENT;
+    auto sv = parse_int_list(st->text), pv = parse_int_list(pd->text), gv = parse_int_list(g->text);
+    if (sv.size() != 2 || pv.size() != 2 || gv.size() != 1) return set_error(FB200_INVALID_ARGUMENT, "op 'conv2d': malformed attributes");
+    s.iv = {sv[0], sv[1], pv[0], pv[1], gv[0]};
+  } else if (op == "conv1d") {
+    s.kind = Kind::kConv1d;
+    const Attr *st = need("stride"), *pd = need("padding"), *g = need("groups");
+    if (!st || !pd || !g) return FB200_INVALID_ARGUMENT;
+    s.iv = {parse_int_list(st->text).at(0), parse_int_list(pd->text).at(0), parse_int_list(g->text).at(0)};
+  } else if (op == "max_pool2d") {
+    s.kind = Kind::kMaxPool;
+    const Attr *k = need("kernel"), *st = need("stride"), *pd = need("padding");
+    if (!k || !st || !pd) return FB200_INVALID_ARGUMENT;
+    auto kv = parse_int_list(k->text), sv = parse_int_list(st->text), pv = parse_int_list(pd->text);
+    if (kv.size() != 2 || sv.size() != 2 || pv.size() != 2) return set_error(FB200_INVALID_ARGUMENT, "op 'max_pool2d': malformed attributes");
+    s.iv = {kv[0], kv[1], sv[0], sv[1], pv[0], pv[1]};
+  } else if (op == "fused_elementwise_internal") {
+    s.kind = Kind::kChain;
+    const Attr *o = need("ops"), *a = need("arities");
+    if (!o || !a) return FB200_INVALID_ARGUMENT;
+    const std::string names = unquote(o->text);
+    size_t start = 0;
+    while (start <= names.size()) {
+      const size_t semi = names.find(';', start);
+      const std::string name = names.substr(start, semi == std::string::npos ? std::string::npos : semi - start);
+      const int code = ew_code(name);
+      if (code == 0) return set_error(FB200_UNIMPLEMENTED, "op 'fused_elementwise_internal': sub-op '%s' has no cuda kernel", name.c_str());
+      s.chain_ops.push_back(code);
+      if (semi == std::string::npos) break;
+      start = semi + 1;
+    }
+    for (int64_t v : parse_int_list(a->text)) s.chain_arity.push_back(static_cast<int>(v));
+    if (s.chain_arity.size() != s.chain_ops.size()) return set_error(FB200_INVALID_ARGUMENT, "op 'fused_elementwise_internal': ops/arities length mismatch");
+  } else if (ew_code(op) != 0) {
+    s.kind = Kind::kChain;
+    s.chain_ops = {ew_code(op)};
+    s.chain_arity = {ew_is_binary(ew_code(op)) ? 2 : 1};
+  } else if (op == "bias_add") {
+    s.kind = Kind::kBiasAdd;
+  } else if (op == "softmax") {
+    s.kind = Kind::kSoftmax;
+  } else if (op == "layer_norm") {
+    s.kind = Kind::kLayerNorm;
+    const Attr* e = need("eps");
+    if (!e) return FB200_INVALID_ARGUMENT;
+    s.eps = strtod(e->text.c_str(), nullptr);
+  } else if (op == "selective_scan") {
+    s.kind = Kind::kScan;
+  } else if (op == "mamba_scan") {
+    s.kind = Kind::kMambaScan;
+  } else if (op == "transpose") {
+    s.kind = Kind::kTranspose;
+    const Attr* pm = need("perm");
+    if (!pm) return FB200_INVALID_ARGUMENT;
+    s.iv = parse_int_list(pm->text);
+  } else if (op == "slice") {
+    s.kind = Kind::kSlice;
+    const Attr *ax = need("axis"), *st = need("start"), *sp = need("stop");
+    if (!ax || !st || !sp) return FB200_INVALID_ARGUMENT;
+    s.iv = {parse_int_list(ax->text).at(0), parse_int_list(st->text).at(0), parse_int_list(sp->text).at(0)};
+  } else if (op == "concat") {
+    s.kind = Kind::kConcat;
+    const Attr* ax = need("axis");
+    if (!ax) return FB200_INVALID_ARGUMENT;
+    s.iv = {parse_int_list(ax->text).at(0)};
+  } else if (op == "sum") {
+    s.kind = Kind::kSum;
+    const Attr* ax = need("axes");
+    if (!ax) return FB200_INVALID_ARGUMENT;
+    s.iv = parse_int_list(ax->text);
+  } else if (op == "reshape") {
+    s.kind = Kind::kCopy;  // may become kAlias below
+  } else if (op == "constant") {
+    s.kind = Kind::kConstant;
+  } else {
+    return set_error(FB200_UNIMPLEMENTED, "op '%s' has no kernel registered for backend 'cuda'", op.c_str());
+  }
+  (void)p;
+  return FB200_OK;
+}
+
+static int materialise_constant(fb200_plan* p, Step& s) {
+  const Attr* v = find_attr(s, "value");
+  if (v == nullptr) return set_error(FB200_INVALID_ARGUMENT, "op 'constant' is missing required attribute 'value'");
+  SlotInfo& slot = p->slots[s.out[0]];
+  std::vector<double> vals = parse_double_list(v->text);
+  const int64_t n = slot.numel;
+  if (static_cast<int64_t>(vals.size()) == 1 && n != 1) vals.assign(static_cast<size_t>(n), vals[0]);
+  if (static_cast<int64_t>(vals.size()) != n) {
+    return set_error(FB200_INVALID_ARGUMENT, "op 'constant': value has %zu elements, shape needs %lld", vals.size(), (long long)n);
+  }
+  if (n == 0) return FB200_OK;
+  std::vector<uint8_t> host(slot.bytes());
+  for (int64_t i = 0; i < n; ++i) {
+    const double d = vals[i];
+    switch (slot.dtype) {
+      case FB200_F32: reinterpret_cast<float*>(host.data())[i] = static_cast<float>(d); break;
+      case FB200_F64: reinterpret_cast<double*>(host.data())[i] = d; break;
+      case FB200_BF16: {
+        const float f = static_cast<float>(d);
+        uint32_t bits; memcpy(&bits, &f, 4);
+        uint16_t h;
+        if ((bits & 0x7fffffffu) > 0x7f800000u) h = static_cast<uint16_t>((bits >> 16) | 0x40u);
+        else h = static_cast<uint16_t>((bits + 0x7fffu + ((bits >> 16) & 1u)) >> 16);
+        reinterpret_cast<uint16_t*>(host.data())[i] = h;
+        break;
+      }
+      case FB200_F16: {
+        const __half h = __float2half_rn(static_cast<float>(d));
+        memcpy(host.data() + 2 * i, &h, 2);
+        break;
+      }
+      case FB200_I32: reinterpret_cast<int32_t*>(host.data())[i] = static_cast<int32_t>(d); break;
+      case FB200_I64: reinterpret_cast<int64_t*>(host.data())[i] = static_cast<int64_t>(d); break;
+      default: return set_error(FB200_UNIMPLEMENTED, "op 'constant': unsupported dtype code %d", slot.dtype);
+    }
+  }
+  // A constant that is also a graph output is copied into the caller's buffer at run time.
+  void* dev = nullptr;
+  if (int rc = fb200_malloc(p->device, host.size(), 256, &dev)) return rc;
+  p->owned.push_back(dev);
+  if (int rc = fb200_memcpy(p->device, dev, host.data(), host.size(), FB200_H2D, nullptr, 1)) return rc;
+  slot.constant = dev;
+  return FB200_OK;
+}
+
+// Last step index that reads `slot` (through aliases too); graph outputs live to the end.
+static int last_use(const fb200_plan& p, int slot) {
+  int last = -1;
+  const int root = root_slot(p, slot);
+  for (size_t i = 0; i < p.steps.size(); ++i) {
+    for (int in : p.steps[i].in) if (root_slot(p, in) == root) last = static_cast<int>(i);
+  }
+  for (int o : p.output_slots) if (root_slot(p, o) == root) last = static_cast<int>(p.steps.size());
+  return last;
+}
+
+static void optimise(fb200_plan* p) {
+  const int n = static_cast<int>(p->steps.size());
+  // reshape -> alias when the aliased bytes cannot be overwritten while the alias is live
+  for (int i = 0; i < n; ++i) {
+    Step& s = p->steps[i];
+    if (s.op != "reshape" || s.in.size() != 1 || s.out.size() != 1) continue;
+    const int src = s.in[0], dst = s.out[0];
+    if (p->slots[dst].output_index >= 0) continue;   // must land in the caller's buffer
+    if (p->slots[dst].numel == 0) { s.kind = Kind::kSkip; continue; }
+    const int end = last_use(*p, dst);
+    bool safe = true;
+    const int src_root = root_slot(*p, src);
+    if (p->slots[src_root].output_index >= 0) safe = true;  // output buffers are never reused
+    for (int j = i + 1; j <= end && j < n && safe; ++j) {
+      for (int w : p->steps[j].out) {
+        if (w != dst && p->slots[w].arena_offset >= 0 && p->slots[src_root].arena_offset >= 0 &&
+            ranges_overlap(*p, w, src_root)) safe = false;
+      }
+    }
+    if (safe) {
+      p->slots[dst].alias_of = src;
+      s.kind = Kind::kAlias;
+    }
+  }
+  if (p->opt_level < 1) return;
+  // matmul / conv2d absorb the elementwise group(s) that directly follow them
+  for (int i = 0; i < n; ++i) {
+    Step& s = p->steps[i];
+    if (s.kind != Kind::kMatmul && s.kind != Kind::kConv2d) continue;
+    int cur_out = s.out[0];
+    for (int j = i + 1; j < n; ++j) {
+      Step& t = p->steps[j];
+      if (t.kind != Kind::kChain && t.kind != Kind::kBiasAdd) break;
+      if (t.in.empty() || t.out.size() != 1) break;
+      // The contraction's result must be operand 0 of the group; add and mul commute exactly,
+      // so a leading binary step may also take it as operand 1.
+      size_t lhs_index = 0;
+      if (t.in[0] != cur_out) {
+        if (t.kind == Kind::kChain && t.chain_arity[0] == 2 && t.in.size() >= 2 && t.in[1] == cur_out) {
+          lhs_index = 1;
+        } else {
+          break;
+        }
+      }
+      std::vector<int> ext;
+      for (size_t a = 0; a < t.in.size(); ++a) if (a != lhs_index) ext.push_back(t.in[a]);
+      if (p->slots[cur_out].output_index >= 0) break;          // the intermediate is observable
+      if (p->slots[t.out[0]].dtype != p->slots[cur_out].dtype) break;
+      if (p->slots[t.out[0]].dtype == FB200_I32 || p->slots[t.out[0]].dtype == FB200_I64) break;
+      // single consumer: nobody else reads cur_out
+      bool single = true;
+      for (int q = 0; q < n && single; ++q) {
+        if (q == j) {
+          for (int e : ext) if (e == cur_out) single = false;
+          continue;
+        }
+        for (int in : p->steps[q].in) if (in == cur_out) single = false;
+      }
+      if (!single) break;
+      const int add_ops = t.kind == Kind::kBiasAdd ? 1 : static_cast<int>(t.chain_ops.size());
+      if (static_cast<int>(s.chain_ops.size()) + add_ops > FB200_MAX_CHAIN) break;
+      // the fused store goes to t's output: it must not overlap anything the contraction reads
+      bool overlap = false;
+      for (int in : s.in) if (ranges_overlap(*p, t.out[0], in)) overlap = true;
+      for (int os : s.epi_operand_slot) if (os >= 0 && ranges_overlap(*p, t.out[0], os)) overlap = true;
+      for (int e : ext) if (ranges_overlap(*p, t.out[0], e)) overlap = true;
+      if (overlap) break;
+      if (t.kind == Kind::kBiasAdd) {
+        if (s.kind != Kind::kMatmul || ext.size() != 1) break;
+        s.chain_ops.push_back(FB200_EW_ADD);
+        s.epi_operand_slot.push_back(ext[0]);
+        s.epi_mode.push_back(FB200_OPERAND_COL);
+      } else {
+        size_t next_ext = 0;
+        for (size_t c = 0; c < t.chain_ops.size(); ++c) {
+          s.chain_ops.push_back(t.chain_ops[c]);
+          if (t.chain_arity[c] == 2) {
+            s.epi_operand_slot.push_back(ext[next_ext++]);
+            s.epi_mode.push_back(FB200_OPERAND_FULL);
+          } else {
+            s.epi_operand_slot.push_back(-1);
+            s.epi_mode.push_back(FB200_OPERAND_FULL);
+          }
+        }
+      }
+      s.write_slot = t.out[0];
+      t.kind = Kind::kSkip;
+      cur_out = t.out[0];
+    }
+  }
+}
+
+static void* slot_ptr(fb200_plan* p, int slot, const void* const* inputs, void* const* outputs) {
+  const int r = root_slot(*p, slot);
+  const SlotInfo& s = p->slots[r];
+  if (s.input_index >= 0) return const_cast<void*>(inputs[s.input_index]);
+  if (s.output_index >= 0) return outputs[s.output_index];
+  if (s.constant != nullptr) return s.constant;
+  if (s.arena_offset >= 0) return static_cast<char*>(p->arena) + s.arena_offset;
+  return nullptr;
+}
+
+static int run_step(fb200_plan* p, Step& s, const void* const* inputs, void* const* outputs,
+                    fb200_stream stream) {
+  auto in_ptr = [&](size_t i) { return slot_ptr(p, s.in[i], inputs, outputs); };
+  auto in_slot = [&](size_t i) -> const SlotInfo& { return p->slots[s.in[i]]; };
+  void* out = s.write_slot >= 0 ? slot_ptr(p, s.write_slot, inputs, outputs) : nullptr;
+  const SlotInfo& os = p->slots[s.out.empty() ? 0 : s.out[0]];
+  fb200_epilogue epi{};
+  const fb200_epilogue* epi_ptr = nullptr;
+  if (!s.chain_ops.empty() && (s.kind == Kind::kMatmul || s.kind == Kind::kConv2d)) {
+    epi.n_ops = static_cast<int>(s.chain_ops.size());
+    for (int i = 0; i < epi.n_ops; ++i) {
+      epi.ops[i] = s.chain_ops[i];
+      epi.modes[i] = s.epi_mode[i];
+      epi.operands[i] = s.epi_operand_slot[i] >= 0 ? slot_ptr(p, s.epi_operand_slot[i], inputs, outputs) : nullptr;
+    }
+    epi_ptr = &epi;
+  }
+  switch (s.kind) {
+    case Kind::kSkip:
+    case Kind::kAlias:
+    case Kind::kConstant:
+      return FB200_OK;
+    case Kind::kMatmul: {
+      if (s.in.size() != 2 || in_slot(0).dims.size() != 2 || in_slot(1).dims.size() != 2) {
+        return set_error(FB200_INVALID_ARGUMENT, "op 'matmul' expects two rank-2 inputs");
+      }
+      const int64_t m = in_slot(0).dims[0], k = in_slot(0).dims[1], n = in_slot(1).dims[1];
+      if (in_slot(1).dims[0] != k) return set_error(FB200_INVALID_ARGUMENT, "op 'matmul': contraction dims differ");
+      return fb200_matmul(in_ptr(0), in_ptr(1), out, m, n, k, os.dtype, p->allow_tf32, epi_ptr, stream);
+    }
+    case Kind::kConv2d: {
+      if (s.in.size() < 2 || in_slot(0).dims.size() != 4 || in_slot(1).dims.size() != 4) {
+        return set_error(FB200_INVALID_ARGUMENT, "op 'conv2d' expects rank-4 x and w");
+      }
+      fb200_conv2d_params q{};
+      q.n = in_slot(0).dims[0]; q.cin = in_slot(0).dims[1]; q.h = in_slot(0).dims[2]; q.w = in_slot(0).dims[3];
+      q.cout = in_slot(1).dims[0]; q.kh = in_slot(1).dims[2]; q.kw = in_slot(1).dims[3];
+      q.stride_h = s.iv[0]; q.stride_w = s.iv[1]; q.pad_h = s.iv[2]; q.pad_w = s.iv[3]; q.groups = s.iv[4];
+      return fb200_conv2d(in_ptr(0), in_ptr(1), s.in.size() > 2 ? in_ptr(2) : nullptr, out, &q,
+                          os.dtype, p->allow_tf32, epi_ptr, stream);
+    }
+    case Kind::kConv1d: {
+      if (s.in.size() < 2 || in_slot(0).dims.size() != 3 || in_slot(1).dims.size() != 3) {
+        return set_error(FB200_INVALID_ARGUMENT, "op 'conv1d' expects rank-3 x and w");
+      }
+      return fb200_conv1d(in_ptr(0), in_ptr(1), s.in.size() > 2 ? in_ptr(2) : nullptr, out,
+                          in_slot(0).dims[0], in_slot(0).dims[1], in_slot(0).dims[2],
+                          in_slot(1).dims[0], in_slot(1).dims[2], s.iv[0], s.iv[1], s.iv[2],
+                          os.dtype, stream);
+    }
+    case Kind::kMaxPool: {
+      if (in_slot(0).dims.size() != 4) return set_error(FB200_INVALID_ARGUMENT, "op 'max_pool2d' expects rank-4 x");
+      return fb200_max_pool2d(in_ptr(0), out, in_slot(0).dims[0], in_slot(0).dims[1],
+                              in_slot(0).dims[2], in_slot(0).dims[3], s.iv[0], s.iv[1], s.iv[2],
+                              s.iv[3], s.iv[4], s.iv[5], os.dtype, stream);
+    }
+    case Kind::kChain: {
+      const void* ptrs[FB200_MAX_CHAIN_INPUTS];
+      if (s.in.size() > FB200_MAX_CHAIN_INPUTS) return set_error(FB200_UNIMPLEMENTED, "op '%s': more than %d external inputs", s.op.c_str(), FB200_MAX_CHAIN_INPUTS);
+      for (size_t i = 0; i < s.in.size(); ++i) ptrs[i] = in_ptr(i);
+      return fb200_fused_elementwise(ptrs, static_cast<int>(s.in.size()), out, os.numel, os.dtype,
+                                     s.chain_ops.data(), s.chain_arity.data(),
+                                     static_cast<int>(s.chain_ops.size()), stream);
+    }
+    case Kind::kBiasAdd: {
+      const int64_t cols = os.dims.empty() ? 1 : os.dims.back();
+      return fb200_bias_add(in_ptr(0), in_ptr(1), out, cols ? os.numel / cols : 0, cols, os.dtype, stream);
+    }
+    case Kind::kSoftmax:
+      if (os.dims.size() != 2) return set_error(FB200_INVALID_ARGUMENT, "op 'softmax' requires rank-2 x");
+      return fb200_softmax(in_ptr(0), out, os.dims[0], os.dims[1], os.dtype, stream);
+    case Kind::kLayerNorm:
+      if (os.dims.size() != 2 || s.in.size() != 3) return set_error(FB200_INVALID_ARGUMENT, "op 'layer_norm' requires rank-2 x, gamma, beta");
+      return fb200_layer_norm(in_ptr(0), in_ptr(1), in_ptr(2), out, os.dims[0], os.dims[1], s.eps, os.dtype, stream);
+    case Kind::kScan: {
+      if (s.in.size() != 5 || os.dims.empty()) return set_error(FB200_INVALID_ARGUMENT, "op 'selective_scan' expects 5 inputs of rank >= 1");
+      const int64_t steps = os.dims.back();
+      return fb200_selective_scan(in_ptr(0), in_ptr(1), in_ptr(2), in_ptr(3), in_ptr(4), out,
+                                  steps ? os.numel / steps : 0, steps, os.dtype, stream);
+    }
+    case Kind::kMambaScan: {
+      // inputs: u, delta, A, B, C, D [, z]; u: [batch, len, dm]; A: [dm, nstate]
+      if (s.in.size() < 6 || in_slot(0).dims.size() != 3 || in_slot(2).dims.size() != 2) {
+        return set_error(FB200_INVALID_ARGUMENT, "op 'mamba_scan' expects u[b,l,d], delta, A[d,n], B, C, D [, z]");
+      }
+      return fb200_mamba_scan(in_ptr(0), in_ptr(1), in_ptr(2), in_ptr(3), in_ptr(4), in_ptr(5),
+                              s.in.size() > 6 ? in_ptr(6) : nullptr, out, in_slot(0).dims[0],
+                              in_slot(0).dims[1], in_slot(0).dims[2], in_slot(2).dims[1], stream);
+    }
+    case Kind::kTranspose:
+      return fb200_transpose(in_ptr(0), out, static_cast<int>(in_slot(0).dims.size()),
+                             in_slot(0).dims.data(), s.iv.data(), itemsize_of(os.dtype), stream);
+    case Kind::kSlice:
+      return fb200_slice(in_ptr(0), out, static_cast<int>(in_slot(0).dims.size()),
+                         in_slot(0).dims.data(), s.iv[0], s.iv[1], s.iv[2], itemsize_of(os.dtype), stream);
+    case Kind::kConcat: {
+      std::vector<const void*> ptrs(s.in.size());
+      std::vector<int64_t> sizes(s.in.size());
+      const int64_t axis = s.iv[0];
+      for (size_t i = 0; i < s.in.size(); ++i) {
+        ptrs[i] = in_ptr(i);
+        sizes[i] = in_slot(i).dims[static_cast<size_t>(axis)];
+      }
+      return fb200_concat(ptrs.data(), static_cast<int>(ptrs.size()), sizes.data(), out,
+                          static_cast<int>(os.dims.size()), os.dims.data(), axis, itemsize_of(os.dtype), stream);
+    }
+    case Kind::kSum:
+      return fb200_sum_axes(in_ptr(0), out, static_cast<int>(in_slot(0).dims.size()),
+                            in_slot(0).dims.data(), s.iv.data(), static_cast<int>(s.iv.size()), os.dtype, stream);
+    case Kind::kCopy:
+      return fb200_memcpy(p->device, out, in_ptr(0), os.bytes(), FB200_D2D, stream, 0);
+  }
+  return FB200_OK;
+}
+
+}  // namespace fb200
+
+extern "C" int fb200_plan_create(const char* plan_text, int device, int allow_tf32, int opt_level,
+                                 fb200_plan** plan) {
+  if (plan_text == nullptr || plan == nullptr) return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_create: null argument");
+  *plan = nullptr;
+  fb200_plan* p = new fb200_plan();
+  p->device = device;
+  p->allow_tf32 = allow_tf32;
+  p->opt_level = opt_level;
+  int rc = parse_plan(plan_text, p);
+  for (size_t i = 0; rc == FB200_OK && i < p->steps.size(); ++i) rc = decode_step(p, p->steps[i]);
+  if (rc == FB200_OK) {
+    // arena bounds: every intermediate must fit inside what the planner announced
+    for (const SlotInfo& s : p->slots) {
+      if (s.arena_offset >= 0 && s.arena_offset + s.bytes() > p->arena_bytes && s.output_index < 0 && s.numel > 0) {
+        rc = set_error(FB200_INVALID_ARGUMENT, "plan: an intermediate at offset %lld (+%zu bytes) exceeds the arena of %zu bytes",
+                       (long long)s.arena_offset, s.bytes(), p->arena_bytes);
+        break;
+      }
+    }
+  }
+  if (rc == FB200_OK) {
+    // graph outputs are written in the caller's buffers, never in the arena
+    for (int o : p->output_slots) p->slots[o].arena_offset = -1;
+    if (p->arena_bytes > 0) rc = fb200_malloc(device, p->arena_bytes, 256, &p->arena);
+  }
+  for (size_t i = 0; rc == FB200_OK && i < p->steps.size(); ++i) {
+    if (p->steps[i].kind == Kind::kConstant) rc = materialise_constant(p, p->steps[i]);
+  }
+  if (rc != FB200_OK) {
+    fb200_plan_destroy(p);
+    return rc;
+  }
+  optimise(p);
+  p->launches = 0;
+  for (const Step& s : p->steps) {
+    if (s.kind != Kind::kSkip && s.kind != Kind::kAlias && s.kind != Kind::kConstant && s.kind != Kind::kCopy) ++p->launches;
+  }
+  *plan = p;
+  return FB200_OK;
+}
+
+extern "C" int fb200_plan_destroy(fb200_plan* p) {
+  if (p == nullptr) return FB200_OK;
+  if (p->arena) fb200_free(p->device, p->arena);
+  for (void* q : p->owned) fb200_free(p->device, q);
+  for (void* q : p->stage_in) fb200_free(p->device, q);
+  for (void* q : p->stage_out) fb200_free(p->device, q);
+  delete p;
+  return FB200_OK;
+}
+
+extern "C" int fb200_plan_num_inputs(const fb200_plan* p) { return p ? static_cast<int>(p->input_slots.size()) : 0; }
+extern "C" int fb200_plan_num_outputs(const fb200_plan* p) { return p ? static_cast<int>(p->output_slots.size()) : 0; }
+extern "C" size_t fb200_plan_arena_bytes(const fb200_plan* p) { return p ? p->arena_bytes : 0; }
+extern "C" int fb200_plan_launches_per_run(const fb200_plan* p) { return p ? p->launches : 0; }
+
+extern "C" int fb200_plan_io_spec(const fb200_plan* p, int is_output, int index, int* dtype,
+                                  int* rank, int64_t* dims) {
+  if (p == nullptr || dtype == nullptr || rank == nullptr || dims == nullptr) return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_io_spec: null argument");
+  const std::vector<int>& v = is_output ? p->output_slots : p->input_slots;
+  if (index < 0 || static_cast<size_t>(index) >= v.size()) return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_io_spec: index %d out of range", index);
+  const SlotInfo& s = p->slots[v[static_cast<size_t>(index)]];
+  *dtype = s.dtype;
+  *rank = static_cast<int>(s.dims.size());
+  for (size_t i = 0; i < s.dims.size(); ++i) dims[i] = s.dims[i];
+  return FB200_OK;
+}
+
+extern "C" int fb200_plan_run(fb200_plan* p, const void* const* inputs, void* const* outputs,
+                              fb200_stream stream) {
+  if (p == nullptr) return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_run: null plan");
+  if ((!p->input_slots.empty() && inputs == nullptr) || (!p->output_slots.empty() && outputs == nullptr)) {
+    return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_run: null input/output table");
+  }
+  for (size_t i = 0; i < p->input_slots.size(); ++i) {
+    if (inputs[i] == nullptr && p->slots[p->input_slots[i]].numel > 0) return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_run: input %zu is null", i);
+  }
+  for (size_t i = 0; i < p->output_slots.size(); ++i) {
+    if (outputs[i] == nullptr && p->slots[p->output_slots[i]].numel > 0) return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_run: output %zu is null", i);
+  }
+  FB200_CUDA_OK(cudaSetDevice(p->device));
+  std::lock_guard<std::mutex> lock(p->mu);  // runs share the arena
+  for (Step& s : p->steps) {
+    if (int rc = run_step(p, s, inputs, outputs, stream)) {
+      // keep the kernel's message, prefix the op like CudaExecutable::run does
+      std::string msg = fb200_last_error();
+      return set_error(rc, "plan run: op '%s' kernel failed: %s", s.op.c_str(), msg.c_str());
+    }
+  }
+  // Outputs that are not produced by a step writing into the caller's buffer: graph inputs
+  // passed through, constants, repeated outputs.
+  for (size_t i = 0; i < p->output_slots.size(); ++i) {
+    const int slot = p->output_slots[i];
+    const int r = root_slot(*p, slot);
+    const SlotInfo& s = p->slots[r];
+    const void* src = nullptr;
+    if (s.input_index >= 0) src = inputs[s.input_index];
+    else if (s.constant != nullptr) src = s.constant;
+    else if (s.output_index >= 0 && static_cast<size_t>(s.output_index) != i) src = outputs[s.output_index];
+    if (src != nullptr && src != outputs[i]) {
+      if (int rc = fb200_memcpy(p->device, outputs[i], src, p->slots[slot].bytes(), FB200_D2D, stream, 0)) return rc;
+    }
+  }
+  return FB200_OK;
+}
+
+extern "C" int fb200_plan_run_host(fb200_plan* p, const void* const* host_inputs,
+                                   void* const* host_outputs, fb200_stream stream) {
+  if (p == nullptr) return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_run_host: null plan");
+  {
+    std::lock_guard<std::mutex> lock(p->mu);
+    if (p->stage_in.empty() && p->stage_out.empty()) {
+      for (int slot : p->input_slots) {
+        void* d = nullptr;
+        if (p->slots[slot].bytes() > 0) { if (int rc = fb200_malloc(p->device, p->slots[slot].bytes(), 256, &d)) return rc; }
+        p->stage_in.push_back(d);
+      }
+      for (int slot : p->output_slots) {
+        void* d = nullptr;
+        if (p->slots[slot].bytes() > 0) { if (int rc = fb200_malloc(p->device, p->slots[slot].bytes(), 256, &d)) return rc; }
+        p->stage_out.push_back(d);
+      }
+    }
+  }
+  for (size_t i = 0; i < p->input_slots.size(); ++i) {
+    if (int rc = fb200_memcpy(p->device, p->stage_in[i], host_inputs[i], p->slots[p->input_slots[i]].bytes(), FB200_H2D, stream, 0)) return rc;
+  }
+  if (int rc = fb200_plan_run(p, p->stage_in.data(), p->stage_out.data(), stream)) return rc;
+  for (size_t i = 0; i < p->output_slots.size(); ++i) {
+    if (int rc = fb200_memcpy(p->device, host_outputs[i], p->stage_out[i], p->slots[p->output_slots[i]].bytes(), FB200_D2H, stream, 0)) return rc;
+  }
+  return fb200_stream_synchronize(p->device, stream);
+}

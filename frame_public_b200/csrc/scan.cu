@@ -1,0 +1,360 @@
+// selective_scan and the fused Mamba scan.
+//
+// selective_scan follows src/backends/cpu/kernels/sequence.cpp:95-106: for every row (all
+// leading axes flattened), time on the last axis, fp32 state starting at 0,
+//     state = a*state + b*x ;  out = c*state + d*x
+// and replaces the reference CUDA path, which launches three kernels PER ROW from a host loop
+// and then synchronises the stream (src/backends/cuda/kernels/sequence.cu:170-217).
+//
+// Two single-launch kernels, both HBM-bound (algorithmic bytes = 6 * rows * steps * itemsize):
+//  * rows_kernel — many rows.  A warp owns 32 rows; the five operands of a 32-step chunk are
+//    read with 128-bit loads (each row segment is contiguous), transposed through padded shared
+//    memory so that lane r then walks row r sequentially, conflict-free, in exactly the CPU's
+//    order and association (compiled with -fmad=false: bit-identical to the CPU reference for
+//    fp32), and the outputs go back through shared memory to 128-bit stores.
+//  * steps_kernel — few, long rows.  A warp owns one row; each lane takes one 128-bit vector of
+//    a chunk, folds it into an affine pair (A,B) with h_out = A*h_in + B, the pairs are combined
+//    with a warp-shuffle inclusive scan, the carry moves to the next chunk through a register.
+//    The association differs from the CPU's, so this kernel is tolerance-exact, not bit-exact.
+//
+// mamba_scan is a NEW op with no reference counterpart: the SSM recurrence with dt, A, B, C, D
+// un-materialised and the d_state-wide state held in registers.
+#include "common.cuh"
+
+namespace fb200 {
+
+constexpr int kScanWarps = 4;
+constexpr int kScanThreads = kScanWarps * 32;
+constexpr int kChunk = 32;        // steps per shared-memory tile
+constexpr int kTileStride = 33;   // padded row length: conflict-free both ways
+constexpr int kTileFloats = kChunk * kTileStride;
+
+// Loads tile[i][r] = src[(row0+r)*steps + t0 + i] for r < 32, i < kChunk.
+template <typename T>
+__device__ __forceinline__ void load_tile(float* tile, const T* __restrict__ src, int64_t row0,
+                                          int64_t rows, int64_t steps, int64_t t0, int lane,
+                                          bool vec_ok) {
+  constexpr int W = 16 / sizeof(T);
+  constexpr int VPR = kChunk / W;        // vectors per row segment
+  constexpr int RPI = 32 / VPR;          // rows covered by one warp-wide instruction
+  if (vec_ok && t0 + kChunk <= steps) {
+    const int v = lane % VPR;
+    const int rsub = lane / VPR;
+#pragma unroll
+    for (int it = 0; it < 32 / RPI; ++it) {
+      const int r = it * RPI + rsub;
+      const int64_t row = row0 + r;
+      float vals[W];
+      if (row < rows) {
+        load_vec<T>(src + row * steps + t0 + v * W, vals);
+      } else {
+#pragma unroll
+        for (int e = 0; e < W; ++e) vals[e] = 0.0f;
+      }
+#pragma unroll
+      for (int e = 0; e < W; ++e) tile[(v * W + e) * kTileStride + r] = vals[e];
+    }
+  } else {
+    for (int r = 0; r < 32; ++r) {
+      const int64_t row = row0 + r;
+      const int64_t t = t0 + lane;
+      float val = 0.0f;
+      if (row < rows && t < steps) val = to_f32(src[row * steps + t]);
+      tile[lane * kTileStride + r] = val;
+    }
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void store_tile(const float* tile, T* __restrict__ dst, int64_t row0,
+                                           int64_t rows, int64_t steps, int64_t t0, int lane,
+                                           bool vec_ok) {
+  constexpr int W = 16 / sizeof(T);
+  constexpr int VPR = kChunk / W;
+  constexpr int RPI = 32 / VPR;
+  if (vec_ok && t0 + kChunk <= steps) {
+    const int v = lane % VPR;
+    const int rsub = lane / VPR;
+#pragma unroll
+    for (int it = 0; it < 32 / RPI; ++it) {
+      const int r = it * RPI + rsub;
+      const int64_t row = row0 + r;
+      if (row < rows) {
+        float vals[W];
+#pragma unroll
+        for (int e = 0; e < W; ++e) vals[e] = tile[(v * W + e) * kTileStride + r];
+        store_vec<T>(dst + row * steps + t0 + v * W, vals);
+      }
+    }
+  } else {
+    for (int r = 0; r < 32; ++r) {
+      const int64_t row = row0 + r;
+      const int64_t t = t0 + lane;
+      if (row < rows && t < steps) dst[row * steps + t] = from_f32<T>(tile[lane * kTileStride + r]);
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kScanThreads)
+selective_scan_rows_kernel(const T* __restrict__ x, const T* __restrict__ a,
+                           const T* __restrict__ b, const T* __restrict__ c,
+                           const T* __restrict__ d, T* __restrict__ out, int64_t rows,
+                           int64_t steps, int vec_ok) {
+  extern __shared__ float smem[];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  float* tx = smem + warp * 6 * kTileFloats;
+  float* ta = tx + kTileFloats;
+  float* tb = ta + kTileFloats;
+  float* tc = tb + kTileFloats;
+  float* td = tc + kTileFloats;
+  float* to = td + kTileFloats;
+  const int64_t n_groups = (rows + 31) / 32;
+  const int64_t total_warps = static_cast<int64_t>(gridDim.x) * kScanWarps;
+  for (int64_t g = static_cast<int64_t>(blockIdx.x) * kScanWarps + warp; g < n_groups;
+       g += total_warps) {
+    const int64_t row0 = g * 32;
+    float state = 0.0f;
+    for (int64_t t0 = 0; t0 < steps; t0 += kChunk) {
+      load_tile<T>(tx, x, row0, rows, steps, t0, lane, vec_ok);
+      load_tile<T>(ta, a, row0, rows, steps, t0, lane, vec_ok);
+      load_tile<T>(tb, b, row0, rows, steps, t0, lane, vec_ok);
+      load_tile<T>(tc, c, row0, rows, steps, t0, lane, vec_ok);
+      load_tile<T>(td, d, row0, rows, steps, t0, lane, vec_ok);
+      __syncwarp();
+      const int len = static_cast<int>(steps - t0 < kChunk ? steps - t0 : kChunk);
+#pragma unroll 8
+      for (int i = 0; i < kChunk; ++i) {
+        if (i < len) {
+          const float xv = tx[i * kTileStride + lane];
+          state = ta[i * kTileStride + lane] * state + tb[i * kTileStride + lane] * xv;
+          to[i * kTileStride + lane] =
+              round_through<T>(tc[i * kTileStride + lane] * state + td[i * kTileStride + lane] * xv);
+        }
+      }
+      __syncwarp();
+      store_tile<T>(to, out, row0, rows, steps, t0, lane, vec_ok);
+      __syncwarp();
+    }
+  }
+}
+
+// Affine pair combine: apply (a1,b1) first, then (a2,b2): h -> a2*(a1*h+b1)+b2.
+struct Affine { float a, b; };
+__device__ __forceinline__ Affine combine(Affine first, Affine second) {
+  return Affine{second.a * first.a, second.a * first.b + second.b};
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kScanThreads)
+selective_scan_steps_kernel(const T* __restrict__ x, const T* __restrict__ a,
+                            const T* __restrict__ b, const T* __restrict__ c,
+                            const T* __restrict__ d, T* __restrict__ out, int64_t rows,
+                            int64_t steps) {
+  constexpr int W = 16 / sizeof(T);
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int64_t total_warps = static_cast<int64_t>(gridDim.x) * kScanWarps;
+  const int64_t chunk = 32 * W;
+  for (int64_t row = static_cast<int64_t>(blockIdx.x) * kScanWarps + warp; row < rows;
+       row += total_warps) {
+    const int64_t base = row * steps;
+    float carry = 0.0f;
+    for (int64_t t0 = 0; t0 < steps; t0 += chunk) {
+      const int64_t t = t0 + static_cast<int64_t>(lane) * W;
+      float xv[W], av[W], bv[W], cv[W], dv[W];
+      if (t + W <= steps) {
+        load_vec<T>(x + base + t, xv);
+        load_vec<T>(a + base + t, av);
+        load_vec<T>(b + base + t, bv);
+        load_vec<T>(c + base + t, cv);
+        load_vec<T>(d + base + t, dv);
+      } else {
+#pragma unroll
+        for (int e = 0; e < W; ++e) {  // identity steps past the end of the row
+          xv[e] = 0.0f; av[e] = 1.0f; bv[e] = 0.0f; cv[e] = 0.0f; dv[e] = 0.0f;
+        }
+      }
+      Affine seg{1.0f, 0.0f};
+#pragma unroll
+      for (int e = 0; e < W; ++e) seg = combine(seg, Affine{av[e], bv[e] * xv[e]});
+      // inclusive warp scan of the affine pairs
+      Affine inc = seg;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float pa = __shfl_up_sync(0xffffffffu, inc.a, o);
+        const float pb = __shfl_up_sync(0xffffffffu, inc.b, o);
+        if (lane >= o) inc = combine(Affine{pa, pb}, inc);
+      }
+      // state entering this lane's segment = exclusive prefix applied to the carry
+      float ea = __shfl_up_sync(0xffffffffu, inc.a, 1);
+      float eb = __shfl_up_sync(0xffffffffu, inc.b, 1);
+      if (lane == 0) { ea = 1.0f; eb = 0.0f; }
+      float state = ea * carry + eb;
+      float yv[W];
+#pragma unroll
+      for (int e = 0; e < W; ++e) {
+        state = av[e] * state + bv[e] * xv[e];
+        yv[e] = cv[e] * state + dv[e] * xv[e];
+      }
+      if (t + W <= steps) store_vec<T>(out + base + t, yv);
+      const float la = __shfl_sync(0xffffffffu, inc.a, 31);
+      const float lb = __shfl_sync(0xffffffffu, inc.b, 31);
+      carry = la * carry + lb;
+    }
+  }
+}
+
+// ---- fused Mamba scan (new op) ----------------------------------------------------------------
+// One thread per (batch, channel); threads of a warp are consecutive channels, so u/delta/z/y
+// accesses are coalesced in the time-major [batch, len, dm] layout the GEMMs produce; B_t and
+// C_t (nstate values each) are warp-uniform broadcast loads.
+constexpr int kMambaThreads = 128;
+constexpr int kMaxState = 16;
+
+template <int NS>
+__global__ void __launch_bounds__(kMambaThreads)
+mamba_scan_kernel(const float* __restrict__ u, const float* __restrict__ delta,
+                  const float* __restrict__ A, const float* __restrict__ B,
+                  const float* __restrict__ C, const float* __restrict__ D,
+                  const float* __restrict__ z, float* __restrict__ y, int64_t len, int64_t dm) {
+  const int64_t bidx = blockIdx.y;
+  const int64_t ch = static_cast<int64_t>(blockIdx.x) * kMambaThreads + threadIdx.x;
+  if (ch >= dm) return;
+  float h[NS], Ar[NS];
+#pragma unroll
+  for (int n = 0; n < NS; ++n) { h[n] = 0.0f; Ar[n] = A[ch * NS + n]; }
+  const float Dd = D[ch];
+  const float* up = u + bidx * len * dm + ch;
+  const float* dp = delta + bidx * len * dm + ch;
+  const float* zp = z != nullptr ? z + bidx * len * dm + ch : nullptr;
+  float* yp = y + bidx * len * dm + ch;
+  const float* Bp = B + bidx * len * NS;
+  const float* Cp = C + bidx * len * NS;
+  constexpr int U = 4;  // time steps whose loads are issued together
+  for (int64_t t0 = 0; t0 < len; t0 += U) {
+    float uu[U], dd[U], zz[U];
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+      const int64_t t = t0 + j;
+      const bool ok = t < len;
+      uu[j] = ok ? up[t * dm] : 0.0f;
+      dd[j] = ok ? dp[t * dm] : 0.0f;
+      zz[j] = (ok && zp != nullptr) ? zp[t * dm] : 0.0f;
+    }
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+      const int64_t t = t0 + j;
+      if (t < len) {
+        float acc = 0.0f;
+#pragma unroll
+        for (int n = 0; n < NS; ++n) {
+          const float da = expf(dd[j] * Ar[n]);
+          const float db = dd[j] * __ldg(Bp + t * NS + n);
+          h[n] = da * h[n] + db * uu[j];
+          acc = acc + __ldg(Cp + t * NS + n) * h[n];
+        }
+        float out = acc + Dd * uu[j];
+        if (zp != nullptr) out = out * (zz[j] * ew_sigmoid(zz[j]));
+        yp[t * dm] = out;
+      }
+    }
+  }
+}
+
+}  // namespace fb200
+
+using namespace fb200;
+
+template <typename T>
+static int launch_scan(const void* x, const void* a, const void* b, const void* c, const void* d,
+                       void* out, int64_t rows, int64_t steps, cudaStream_t s) {
+  constexpr int W = 16 / sizeof(T);
+  const T* xp = static_cast<const T*>(x);
+  const T* ap = static_cast<const T*>(a);
+  const T* bp = static_cast<const T*>(b);
+  const T* cp = static_cast<const T*>(c);
+  const T* dp = static_cast<const T*>(d);
+  T* op = static_cast<T*>(out);
+  const bool al = aligned16(x) && aligned16(a) && aligned16(b) && aligned16(c) && aligned16(d) &&
+                  aligned16(out) && steps % W == 0;
+  // Few long rows: parallelise along time.  Needs whole 128-bit vectors per row.
+  const int64_t row_groups = (rows + 31) / 32;
+  if (al && row_groups < 2 * kNumSMs && steps >= 8 * 32 * W) {
+    const int grid = grid_for(rows * 32, kScanThreads, 8);
+    selective_scan_steps_kernel<T><<<grid, kScanThreads, 0, s>>>(xp, ap, bp, cp, dp, op, rows, steps);
+    return after_launch("selective_scan_steps_kernel");
+  }
+  const size_t smem = static_cast<size_t>(kScanWarps) * 6 * kTileFloats * sizeof(float);
+  static bool attr_set = false;
+  if (!attr_set) {
+    FB200_CUDA_OK(cudaFuncSetAttribute(selective_scan_rows_kernel<T>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem)));
+    attr_set = true;
+  }
+  const int grid = grid_for(row_groups * 32, kScanThreads, 2);
+  selective_scan_rows_kernel<T><<<grid, kScanThreads, smem, s>>>(xp, ap, bp, cp, dp, op, rows,
+                                                                  steps, al ? 1 : 0);
+  return after_launch("selective_scan_rows_kernel");
+}
+
+extern "C" int fb200_selective_scan(const void* x, const void* a, const void* b, const void* c,
+                                    const void* d, void* out, int64_t rows, int64_t steps,
+                                    int dtype, fb200_stream stream) {
+  if (rows < 0) return set_error(FB200_INVALID_ARGUMENT, "selective_scan: negative rows");
+  if (steps < 1) {
+    return set_error(FB200_INVALID_ARGUMENT,
+                     "selective_scan: the last dimension (steps) must be >= 1, got %lld",
+                     static_cast<long long>(steps));
+  }
+  if (rows == 0) return FB200_OK;
+  if (!x || !a || !b || !c || !d || !out) {
+    return set_error(FB200_INVALID_ARGUMENT, "selective_scan: null argument");
+  }
+  cudaStream_t s = as_stream(stream);
+  switch (dtype) {
+    case FB200_F32: return launch_scan<float>(x, a, b, c, d, out, rows, steps, s);
+    case FB200_BF16: return launch_scan<__nv_bfloat16>(x, a, b, c, d, out, rows, steps, s);
+    case FB200_F16: return launch_scan<__half>(x, a, b, c, d, out, rows, steps, s);
+    default:
+      return set_error(FB200_INVALID_ARGUMENT,
+                       "selective_scan: dtype code %d is not float32/float16/bfloat16", dtype);
+  }
+}
+
+extern "C" int fb200_mamba_scan(const void* u, const void* delta, const void* A, const void* B,
+                                const void* C, const void* D, const void* z, void* y,
+                                int64_t batch, int64_t len, int64_t dm, int64_t nstate,
+                                fb200_stream stream) {
+  if (batch < 0 || len < 0 || dm < 0) return set_error(FB200_INVALID_ARGUMENT, "mamba_scan: negative shape");
+  if (nstate != 16 && nstate != 8 && nstate != 4) {
+    return set_error(FB200_UNIMPLEMENTED, "mamba_scan: nstate must be 4, 8 or 16, got %lld",
+                     static_cast<long long>(nstate));
+  }
+  if (batch == 0 || len == 0 || dm == 0) return FB200_OK;
+  if (!u || !delta || !A || !B || !C || !D || !y) {
+    return set_error(FB200_INVALID_ARGUMENT, "mamba_scan: null argument");
+  }
+  if (batch > 65535) return set_error(FB200_INVALID_ARGUMENT, "mamba_scan: batch > 65535");
+  cudaStream_t s = as_stream(stream);
+  dim3 grid(static_cast<unsigned>((dm + kMambaThreads - 1) / kMambaThreads),
+            static_cast<unsigned>(batch));
+  const float* up = static_cast<const float*>(u);
+  const float* dp = static_cast<const float*>(delta);
+  const float* Ap = static_cast<const float*>(A);
+  const float* Bp = static_cast<const float*>(B);
+  const float* Cp = static_cast<const float*>(C);
+  const float* Dp = static_cast<const float*>(D);
+  const float* zp = static_cast<const float*>(z);
+  float* yp = static_cast<float*>(y);
+  if (nstate == 16) {
+    mamba_scan_kernel<16><<<grid, kMambaThreads, 0, s>>>(up, dp, Ap, Bp, Cp, Dp, zp, yp, len, dm);
+  } else if (nstate == 8) {
+    mamba_scan_kernel<8><<<grid, kMambaThreads, 0, s>>>(up, dp, Ap, Bp, Cp, Dp, zp, yp, len, dm);
+  } else {
+    mamba_scan_kernel<4><<<grid, kMambaThreads, 0, s>>>(up, dp, Ap, Bp, Cp, Dp, zp, yp, len, dm);
+  }
+  return after_launch("mamba_scan_kernel");
+}

@@ -1,0 +1,273 @@
+/*
+ * frame_b200.h — C ABI of libframe_b200.so: hand-written sm_100a (B200) kernels and the CUDA
+ * HAL plumbing for the compiled-graph inference path of the Frame deep-learning framework.
+ *
+ * The library owns no Frame types.  Every entry point takes plain pointers, int64 sizes and a
+ * CUDA stream handle, allocates nothing unless its name says so, enqueues on the given stream
+ * and returns an fb200_status.  fb200_last_error() returns a thread-local English message for
+ * the last non-zero status.  There is no CPU fallback: on a machine without a usable B200 the
+ * compute entry points return FB200_DEVICE_ERROR.
+ *
+ * Each declaration cites the interface of the reference project it stands behind
+ * (file:line, paths inside the reference project).  The C++20 adapter that implements
+ * hal::Backend / Allocator / Stream / Event / Executable and registers one KernelFn per op
+ * with FRAME_REGISTER_KERNEL is the only intended caller inside a Frame process.
+ */
+#ifndef FRAME_B200_H_
+#define FRAME_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define FB200_API __attribute__((visibility("default")))
+#else
+#define FB200_API
+#endif
+
+/* Status codes: same numbering as frame::ErrorCode (include/frame/core/status.h:18-27). */
+typedef enum fb200_status {
+  FB200_OK = 0,
+  FB200_INVALID_ARGUMENT = 1,
+  FB200_NOT_FOUND = 2,
+  FB200_ALREADY_EXISTS = 3,
+  FB200_UNIMPLEMENTED = 4,
+  FB200_OUT_OF_MEMORY = 5,
+  FB200_INTERNAL = 6,
+  FB200_DEVICE_ERROR = 7
+} fb200_status;
+
+/* Element types: same numbering as frame::DTypeCode (include/frame/core/dtype.h:17-29).
+ * bf16/f16 are 16-bit storage PODs (dtype.h:38-43). */
+typedef enum fb200_dtype {
+  FB200_F32 = 0,
+  FB200_F64 = 1,
+  FB200_F16 = 2,
+  FB200_BF16 = 3,
+  FB200_I8 = 4,
+  FB200_I16 = 5,
+  FB200_I32 = 6,
+  FB200_I64 = 7,
+  FB200_U8 = 8,
+  FB200_BOOL = 9
+} fb200_dtype;
+
+/* A cudaStream_t passed as an opaque pointer (hal::Stream::native_handle,
+ * include/frame/hal/stream.h:22-28).  NULL = the default stream
+ * (ops::KernelContext::stream may be null, include/frame/ops/kernel_registry.h:30-43). */
+typedef void* fb200_stream;
+typedef void* fb200_event;
+
+/* ---- library ----------------------------------------------------------------------------- */
+FB200_API const char* fb200_last_error(void);
+FB200_API const char* fb200_version(void);
+/* Number of kernels this library has launched in the calling process (for harness accounting). */
+FB200_API int64_t fb200_launch_count(void);
+
+/* Reads and clears the per-device kernel status word.  Every wait inside the tensor-core
+ * kernels is bounded; a wait that gives up records a non-zero code here and the kernel exits
+ * cleanly (its results are then invalid).  0 = healthy.  Read after a stream synchronise. */
+FB200_API int fb200_kernel_status(int device, int* code);
+
+/* ---- HAL: devices, allocator, copies, streams, events -------------------------------------
+ * Behind hal::Backend::device_count / allocator / copy / create_stream / create_event
+ * (include/frame/hal/backend.h:77-109) and hal::Allocator (include/frame/hal/allocator.h:13-21);
+ * replaces src/backends/cuda/cuda_backend.cpp:68-312 and cuda_allocator.cpp:26-66. */
+FB200_API int fb200_device_count(int* count);
+/* bytes > 0, alignment a power of two <= 256 (cuda_allocator.cpp:26-41). */
+FB200_API int fb200_malloc(int device, size_t bytes, size_t alignment, void** ptr);
+FB200_API int fb200_free(int device, void* ptr);
+/* Pinned host staging memory for the harness-side end-to-end path. */
+FB200_API int fb200_host_alloc(size_t bytes, void** ptr);
+FB200_API int fb200_host_free(void* ptr);
+typedef enum fb200_copy_kind { FB200_H2D = 1, FB200_D2H = 2, FB200_D2D = 3 } fb200_copy_kind;
+/* stream == NULL with blocking != 0 is a synchronous copy (cuda_backend.cpp:194-203);
+ * bytes == 0 is a no-op; a null pointer with bytes > 0 is FB200_INVALID_ARGUMENT. */
+FB200_API int fb200_memcpy(int device, void* dst, const void* src, size_t bytes, int kind,
+                           fb200_stream stream, int blocking);
+FB200_API int fb200_memset(int device, void* dst, int value, size_t bytes, fb200_stream stream);
+FB200_API int fb200_stream_create(int device, fb200_stream* stream);
+FB200_API int fb200_stream_destroy(int device, fb200_stream stream);
+FB200_API int fb200_stream_synchronize(int device, fb200_stream stream);
+FB200_API int fb200_event_create(int device, int timing, fb200_event* event);
+FB200_API int fb200_event_destroy(int device, fb200_event event);
+FB200_API int fb200_event_record(int device, fb200_event event, fb200_stream stream);
+FB200_API int fb200_stream_wait_event(int device, fb200_stream stream, fb200_event event);
+/* *done = 1 when complete (include/frame/hal/event.h:16-24). */
+FB200_API int fb200_event_query(int device, fb200_event event, int* done);
+FB200_API int fb200_event_synchronize(int device, fb200_event event);
+FB200_API int fb200_event_elapsed_ms(fb200_event start, fb200_event stop, float* ms);
+
+/* ---- elementwise and fused groups ----------------------------------------------------------
+ * Sub-op codes of a fused elementwise chain.  add/mul/relu/square/sigmoid/tanh/rsqrt follow
+ * src/backends/cpu/kernels/elementwise.cpp:39-56,146-163,242-255,329-404; gelu (tanh form),
+ * silu, softplus, exp have no counterpart in the reference (new ops). */
+typedef enum fb200_ew_op {
+  FB200_EW_ADD = 1,
+  FB200_EW_MUL = 2,
+  FB200_EW_RELU = 3,
+  FB200_EW_SQUARE = 4,
+  FB200_EW_SIGMOID = 5,
+  FB200_EW_TANH = 6,
+  FB200_EW_RSQRT = 7,
+  FB200_EW_GELU = 8,
+  FB200_EW_SILU = 9,
+  FB200_EW_SOFTPLUS = 10,
+  FB200_EW_EXP = 11
+} fb200_ew_op;
+#define FB200_MAX_CHAIN 8
+#define FB200_MAX_CHAIN_INPUTS 9
+
+/* One launch for a whole fused group: op `fused_elementwise_internal` with attrs
+ * ops="add;mul;relu", arities=[2,2,1] (include/frame/ops/fused_elementwise_utils.h:28,44-59).
+ * Wiring as src/ops/fused_elementwise_utils.cpp:88-101,141-165: segment 0 reads its operands
+ * from `inputs`; segment i>0 takes the previous result as operand 0 and the next external
+ * inputs for the rest.  Every intermediate is rounded to `dtype` exactly as the unfused chain
+ * does.  A chain of one op is the standalone op (elementwise.cu:582-785 of the reference CUDA
+ * backend).  dtype: F32, BF16, F16; I32/I64 for a chain consisting of `add` only. */
+FB200_API int fb200_fused_elementwise(const void* const* inputs, int n_inputs, void* out,
+                                      int64_t numel, int dtype, const int* ops,
+                                      const int* arities, int n_ops, fb200_stream stream);
+/* NEW op: out[r, j] = x[r, j] + bias[j] (row-broadcast bias; no reference counterpart, the
+ * reference only has same-shape add, src/ops/schemas/elementwise.cpp:41-66). */
+FB200_API int fb200_bias_add(const void* x, const void* bias, void* out, int64_t rows,
+                             int64_t cols, int dtype, fb200_stream stream);
+
+/* ---- epilogue shared by matmul and conv2d --------------------------------------------------
+ * A short elementwise chain applied to the accumulator before the single store.  Binary steps
+ * read a second operand: same shape as the output (mode FULL, what reference graphs contain:
+ * a Linear bias is a full [batch,out] tensor, src/nn/layers.cpp:241-248), one value per output
+ * column (mode COL: matmul [N]; conv2d: unused) or one value per output row / channel
+ * (mode ROW: conv2d per-Cout). */
+typedef enum fb200_operand_mode { FB200_OPERAND_FULL = 0, FB200_OPERAND_COL = 1, FB200_OPERAND_ROW = 2 } fb200_operand_mode;
+typedef struct fb200_epilogue {
+  int n_ops;
+  int ops[FB200_MAX_CHAIN];
+  const void* operands[FB200_MAX_CHAIN]; /* NULL for unary steps */
+  int modes[FB200_MAX_CHAIN];
+} fb200_epilogue;
+
+/* ---- dense contractions --------------------------------------------------------------------
+ * matmul: C[m,n] = sum_p A[m,p]*B[p,n], rank-2 row-major operands of one dtype, fp32
+ * accumulation, one rounding at the store (src/backends/cpu/kernels/matmul.cpp:92-131;
+ * replaces the cublasLtMatmul call of src/backends/cuda/kernels/matmul.cpp:90-276).
+ * BF16/F16: tcgen05 kind::f16.  F32: allow_tf32 != 0 selects tcgen05 kind::tf32 (the
+ * CompileOptions::allow_tf32 switch, include/frame/hal/backend.h:51-63); allow_tf32 == 0 keeps
+ * strict fp32 arithmetic.  `epilogue` may be NULL. */
+FB200_API int fb200_matmul(const void* a, const void* b, void* c, int64_t m, int64_t n,
+                           int64_t k, int dtype, int allow_tf32, const fb200_epilogue* epilogue,
+                           fb200_stream stream);
+/* Which kernel family fb200_matmul would pick: 1 = tcgen05/TMEM/TMA, 0 = SIMT. */
+FB200_API int fb200_matmul_uses_tensor_cores(int64_t m, int64_t n, int64_t k, int dtype,
+                                             int allow_tf32);
+
+/* conv2d: NCHW cross-correlation with groups, stride, zero padding, optional [Cout] bias,
+ * accumulation in fp32 (src/backends/cpu/kernels/conv.cpp:225-257; schema
+ * src/ops/schemas/conv.cpp:979-989; replaces cudnnConvolutionForward,
+ * src/backends/cuda/kernels/conv.cpp:385-520). */
+typedef struct fb200_conv2d_params {
+  int64_t n, cin, h, w;
+  int64_t cout, kh, kw;
+  int64_t stride_h, stride_w, pad_h, pad_w, groups;
+} fb200_conv2d_params;
+FB200_API int fb200_conv2d(const void* x, const void* w, const void* bias, void* out,
+                           const fb200_conv2d_params* p, int dtype, int allow_tf32,
+                           const fb200_epilogue* epilogue, fb200_stream stream);
+/* conv1d: NCL, same conventions (src/backends/cpu/kernels/conv.cpp:565-589; the reference CUDA
+ * backend has no kernel for it and falls back, src/ops/schemas/conv.cpp:1021-1032). */
+FB200_API int fb200_conv1d(const void* x, const void* w, const void* bias, void* out, int64_t n,
+                           int64_t cin, int64_t l, int64_t cout, int64_t k, int64_t stride,
+                           int64_t padding, int64_t groups, int dtype, fb200_stream stream);
+/* max_pool2d: max over valid positions only, first maximum wins
+ * (src/backends/cpu/kernels/pool.cpp:187-233; replaces cudnnPoolingForward,
+ * src/backends/cuda/kernels/pool.cpp:231). */
+FB200_API int fb200_max_pool2d(const void* x, void* out, int64_t n, int64_t c, int64_t h,
+                               int64_t w, int64_t kh, int64_t kw, int64_t stride_h,
+                               int64_t stride_w, int64_t pad_h, int64_t pad_w, int dtype,
+                               fb200_stream stream);
+
+/* ---- row kernels ---------------------------------------------------------------------------
+ * softmax over the last axis of a rank-2 tensor (src/backends/cpu/kernels/sequence.cpp:114-174;
+ * replaces cudnnSoftmaxForward, src/backends/cuda/kernels/sequence.cpp:108-174). */
+FB200_API int fb200_softmax(const void* x, void* out, int64_t rows, int64_t cols, int dtype,
+                            fb200_stream stream);
+/* layer_norm over the last axis, gamma/beta of shape [cols], eps cast to float
+ * (src/backends/cpu/kernels/sequence.cpp:182-279; replaces
+ * src/backends/cuda/kernels/sequence.cu:104-155). */
+FB200_API int fb200_layer_norm(const void* x, const void* gamma, const void* beta, void* out,
+                               int64_t rows, int64_t cols, double eps, int dtype,
+                               fb200_stream stream);
+/* selective_scan: per row h_t = a_t*h_{t-1} + b_t*x_t, y_t = c_t*h_t + d_t*x_t, h_{-1} = 0,
+ * time on the last axis, fp32 state (src/backends/cpu/kernels/sequence.cpp:95-106; replaces the
+ * per-row CUB scans of src/backends/cuda/kernels/sequence.cu:170-217).  One launch. */
+FB200_API int fb200_selective_scan(const void* x, const void* a, const void* b, const void* c,
+                                   const void* d, void* out, int64_t rows, int64_t steps,
+                                   int dtype, fb200_stream stream);
+/* NEW op (no reference counterpart): the Mamba SSM scan with un-materialised operands, fp32.
+ * u, delta, z, y: [batch, len, dm]; A: [dm, nstate]; B, C: [batch, len, nstate]; D: [dm];
+ * z may be NULL.  h[n] = exp(delta*A[d,n])*h[n] + delta*B[n]*u; y = sum_n C[n]*h[n] + D[d]*u;
+ * y *= silu(z).  nstate <= 16. */
+FB200_API int fb200_mamba_scan(const void* u, const void* delta, const void* A, const void* B,
+                               const void* C, const void* D, const void* z, void* y,
+                               int64_t batch, int64_t len, int64_t dm, int64_t nstate,
+                               fb200_stream stream);
+
+/* ---- data movement -------------------------------------------------------------------------
+ * transpose: out.dims[i] = x.dims[perm[i]] (src/ops/schemas/shape.cpp:424-429;
+ * src/backends/cpu/kernels/shape.cpp:73; replaces src/backends/cuda/kernels/shape.cu:65-83). */
+FB200_API int fb200_transpose(const void* x, void* out, int rank, const int64_t* dims,
+                              const int64_t* perm, int itemsize, fb200_stream stream);
+/* slice: one half-open range on one axis (shape.cpp:276; replaces the per-segment
+ * cudaMemcpyAsync loop of src/backends/cuda/kernels/shape.cpp:342). */
+FB200_API int fb200_slice(const void* x, void* out, int rank, const int64_t* dims, int64_t axis,
+                          int64_t start, int64_t stop, int itemsize, fb200_stream stream);
+/* concat along one axis (shape.cpp:172; replaces src/backends/cuda/kernels/shape.cpp:207).
+ * `axis_sizes[i]` is input i's extent on `axis`; `out_dims` is the output shape. */
+FB200_API int fb200_concat(const void* const* inputs, int n_inputs, const int64_t* axis_sizes,
+                           void* out, int rank, const int64_t* out_dims, int64_t axis,
+                           int itemsize, fb200_stream stream);
+/* sum over an axis subset (src/backends/cpu/kernels/reduction.cpp:130; replaces
+ * src/backends/cuda/kernels/reduction.cu:90-130). */
+FB200_API int fb200_sum_axes(const void* x, void* out, int rank, const int64_t* dims,
+                             const int64_t* axes, int n_axes, int dtype, fb200_stream stream);
+
+/* ---- whole-plan executor -------------------------------------------------------------------
+ * Runs the step list that ops::build_executable_plan produces for the nine-pass pipeline's
+ * output (include/frame/ops/executable_plan.h:42-71), honouring the memory planner's arena
+ * offsets (src/ir/memory_plan.cpp:37-133).  Replaces CudaExecutable::run
+ * (src/backends/cuda/cuda_executable.cpp:41-128): the arena is allocated once per plan, graph
+ * outputs are written straight into the caller's buffers, constants are materialised once,
+ * reshape is a zero-copy alias, and matmul/conv2d steps absorb a following elementwise group
+ * as their epilogue when it is their only consumer.
+ *
+ * `plan_text` is the line-oriented form written by the reference-side shim
+ * (`plan slots= arena=`, `in`, `step`, `attr`, `out` lines). */
+typedef struct fb200_plan fb200_plan;
+FB200_API int fb200_plan_create(const char* plan_text, int device, int allow_tf32, int opt_level,
+                                fb200_plan** plan);
+FB200_API int fb200_plan_destroy(fb200_plan* plan);
+FB200_API int fb200_plan_num_inputs(const fb200_plan* plan);
+FB200_API int fb200_plan_num_outputs(const fb200_plan* plan);
+/* dtype, rank and dims (up to 8) of input/output `index`. */
+FB200_API int fb200_plan_io_spec(const fb200_plan* plan, int is_output, int index, int* dtype,
+                                 int* rank, int64_t* dims);
+FB200_API size_t fb200_plan_arena_bytes(const fb200_plan* plan);
+/* Number of kernel launches one run enqueues (after epilogue absorption and aliasing). */
+FB200_API int fb200_plan_launches_per_run(const fb200_plan* plan);
+/* Device pointers in, device pointers out; asynchronous on `stream`.  Runs of one plan are
+ * serialised by a per-plan mutex because they share its arena. */
+FB200_API int fb200_plan_run(fb200_plan* plan, const void* const* inputs, void* const* outputs,
+                             fb200_stream stream);
+/* Host buffers in and out: H2D of every input, the run, D2H of every output, one stream
+ * synchronise.  Staging buffers on the device are owned by the plan. */
+FB200_API int fb200_plan_run_host(fb200_plan* plan, const void* const* host_inputs,
+                                  void* const* host_outputs, fb200_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FRAME_B200_H_ */

@@ -1,0 +1,65 @@
+#!/usr/bin/env bash
+# TEST INFRASTRUCTURE — builds the reference's own CPU implementation of the
+# compiled-graph path from the reference's sources, where they lie, into
+# oracle/_ref/ (git-ignored).  Nothing is copied from the reference tree; only
+# object files and one shared library are produced.
+#
+#   usage: oracle/build_ref.sh [REFERENCE_ROOT]      (default /root/reference)
+#
+# Product of this script:
+#   oracle/_ref/libframe_ref.so   core + ir + ops + schemas + compiler + passes +
+#                                 runtime + nn + backends/cpu of the reference,
+#                                 object files linked directly so that the
+#                                 static op / kernel / backend registrars run at
+#                                 load time (the reference links its archives
+#                                 WHOLE for the same reason).
+#   oracle/_ref/libframe_ref_shim.so  the extern "C" shim of oracle/ref_shim.cpp.
+#
+# Flags: -O2 -ffp-contract=off, no -march=native, no -ffast-math, so that
+# `acc += a*b` is never contracted into an FMA and the numbers equal those of
+# the reference's own Debug/Release builds.
+# src/backends/cpu/kernels/fft.cpp is skipped: it needs pocketfft, which the
+# reference downloads at configure time; rfft/irfft are not on the path.
+set -euo pipefail
+REF="${1:-/root/reference}"
+HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
+OUT="$HERE/_ref"
+OBJ="$OUT/obj"
+mkdir -p "$OBJ"
+
+if [ ! -d "$REF/src" ]; then
+  echo "build_ref.sh: reference tree not found at $REF (prebuilt files in $OUT are used as they are)" >&2
+  exit 0
+fi
+
+CXX="${CXX:-g++}"
+CXXFLAGS="-std=c++20 -O2 -ffp-contract=off -fPIC -fvisibility=default -I$REF/include -I$REF/src"
+DIRS="core ir ops ops/schemas compiler compiler/passes runtime nn backends/cpu backends/cpu/kernels"
+
+list_sources() {
+  for d in $DIRS; do
+    for f in "$REF/src/$d"/*.cpp; do
+      [ -e "$f" ] || continue
+      case "$f" in */backends/cpu/kernels/fft.cpp) continue ;; esac
+      echo "$f"
+    done
+  done
+}
+
+compile_one() {
+  src="$1"
+  rel="${src#$REF/src/}"
+  obj="$OBJ/$(echo "${rel%.cpp}" | tr '/' '_').o"
+  if [ ! -e "$obj" ] || [ "$src" -nt "$obj" ]; then
+    $CXX $CXXFLAGS -c "$src" -o "$obj"
+  fi
+}
+export -f compile_one
+export REF OBJ CXX CXXFLAGS
+
+list_sources | xargs -P "$(nproc)" -I{} bash -c 'compile_one "$@"' _ {}
+
+$CXX -shared -o "$OUT/libframe_ref.so" "$OBJ"/*.o -lpthread
+$CXX $CXXFLAGS -shared -o "$OUT/libframe_ref_shim.so" "$HERE/ref_shim.cpp" \
+  -L"$OUT" -lframe_ref -Wl,-rpath,'$ORIGIN'
+echo "built $OUT/libframe_ref.so and libframe_ref_shim.so"

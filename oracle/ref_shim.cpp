@@ -1,0 +1,353 @@
+// TEST INFRASTRUCTURE — extern "C" shim over the reference framework's own
+// public C++ API, so that Python (ctypes) can drive the UNMODIFIED reference:
+// parse an IR text, run the nine-pass pipeline, compile on a named backend and
+// run with host buffers.  With backend "cpu" this is the parity oracle and the
+// timed CPU baseline; with backend "cuda" (the sm_100a backend of this
+// repository loaded into the same process) it is the end-to-end product path.
+// Nothing here computes anything itself.
+//
+// Reference API used (paths inside the reference project):
+//   ir::parse_text / dump_text            include/frame/ir/serialization.h:77-81
+//   runtime::compile                      src/runtime/compile.cpp:128-178
+//   compiler::standard_pipeline           src/compiler/pipeline.cpp:9-28
+//   ops::build_executable_plan            src/ops/executable_plan.cpp:16-121
+//   hal::Backend::{allocator,copy,create_stream}  include/frame/hal/backend.h:77-109
+//   runtime::FallbackStats                include/frame/runtime/fallback_stats.h:21-41
+#include <chrono>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <sstream>
+#include <string>
+#include <string_view>
+#include <variant>
+#include <vector>
+
+#include <frame/compiler/pipeline.h>
+#include <frame/core/tensor.h>
+#include <frame/hal/allocator.h>
+#include <frame/hal/backend.h>
+#include <frame/hal/executable.h>
+#include <frame/hal/stream.h>
+#include <frame/ir/graph.h>
+#include <frame/ir/serialization.h>
+#include <frame/ops/executable_plan.h>
+#include <frame/ops/kernel_registry.h>
+#include <frame/ops/op_registry.h>
+#include <frame/runtime/compile.h>
+#include <frame/runtime/fallback_stats.h>
+
+namespace {
+
+using frame::Device;
+using frame::Result;
+using frame::Status;
+using frame::Tensor;
+
+void set_err(char* err, int errlen, const std::string& msg) {
+  if (err == nullptr || errlen <= 0) return;
+  std::snprintf(err, static_cast<size_t>(errlen), "%s", msg.c_str());
+}
+
+std::string_view static_backend_name(std::string_view name) {
+  if (name == frame::kCpuBackendName) return frame::kCpuBackendName;
+  if (name == frame::kCudaBackendName) return frame::kCudaBackendName;
+  return {};
+}
+
+struct Handle {
+  std::shared_ptr<frame::hal::Executable> exe;
+  frame::hal::Backend* backend = nullptr;
+  Device device;
+  std::vector<frame::hal::IoSpec> in_sig;
+  std::vector<frame::hal::IoSpec> out_sig;
+  std::vector<Tensor> dev_in;
+  std::vector<Tensor> dev_out;
+  std::unique_ptr<frame::hal::Stream> stream;
+};
+
+Status ensure_buffers(Handle& h) {
+  if (!h.dev_in.empty() || !h.dev_out.empty()) return Status::ok();
+  frame::hal::Allocator* alloc = h.backend->allocator(h.device);
+  if (alloc == nullptr) {
+    return Status::make(frame::ErrorCode::kInternal, "shim: null allocator");
+  }
+  for (const auto& spec : h.in_sig) {
+    Result<Tensor> t = Tensor::empty(spec.shape, spec.dtype, h.device, *alloc);
+    if (!t.is_ok()) return t.status();
+    h.dev_in.push_back(t.value());
+  }
+  for (const auto& spec : h.out_sig) {
+    Result<Tensor> t = Tensor::empty(spec.shape, spec.dtype, h.device, *alloc);
+    if (!t.is_ok()) return t.status();
+    h.dev_out.push_back(t.value());
+  }
+  Result<std::unique_ptr<frame::hal::Stream>> s = h.backend->create_stream(h.device);
+  if (!s.is_ok()) return s.status();
+  h.stream = std::move(s.value());
+  return Status::ok();
+}
+
+size_t spec_bytes(const frame::hal::IoSpec& spec) {
+  return static_cast<size_t>(spec.shape.numel()) * spec.dtype.itemsize();
+}
+
+}  // namespace
+
+extern "C" {
+
+// Parses `ir_text`, compiles it for `backend` through runtime::compile (cache,
+// nine-pass pipeline, Backend::compile, fallback chain) and returns a handle.
+void* fref_compile(const char* ir_text, const char* backend, int device_index, int allow_tf32,
+                   char* err, int errlen) {
+  const std::string_view bname = static_backend_name(backend);
+  if (bname.empty()) {
+    set_err(err, errlen, "shim: backend must be cpu or cuda");
+    return nullptr;
+  }
+  Result<frame::ir::Graph> graph = frame::ir::parse_text(ir_text);
+  if (!graph.is_ok()) {
+    set_err(err, errlen, std::string(graph.status().message()));
+    return nullptr;
+  }
+  frame::hal::CompileOptions options;
+  options.allow_tf32 = allow_tf32 != 0;
+  Result<std::shared_ptr<frame::hal::Executable>> exe =
+      frame::runtime::compile(graph.value(), bname, options);
+  if (!exe.is_ok()) {
+    set_err(err, errlen, std::string(exe.status().message()));
+    return nullptr;
+  }
+  Result<frame::hal::Backend*> be = frame::hal::BackendRegistry::instance().get(bname);
+  if (!be.is_ok()) {
+    set_err(err, errlen, std::string(be.status().message()));
+    return nullptr;
+  }
+  auto* h = new Handle();
+  h->exe = exe.value();
+  h->backend = be.value();
+  h->device = Device{bname, device_index};
+  h->in_sig = h->exe->input_signature();
+  h->out_sig = h->exe->output_signature();
+  return h;
+}
+
+void fref_free(void* handle) { delete static_cast<Handle*>(handle); }
+
+int fref_num_io(void* handle, int is_output) {
+  auto* h = static_cast<Handle*>(handle);
+  return static_cast<int>(is_output ? h->out_sig.size() : h->in_sig.size());
+}
+
+// dtype code (reference DTypeCode numbering), rank and dims of one signature entry.
+int fref_io_spec(void* handle, int is_output, int index, int* dtype, int* rank, int64_t* dims,
+                 int dims_cap) {
+  auto* h = static_cast<Handle*>(handle);
+  const auto& sig = is_output ? h->out_sig : h->in_sig;
+  if (index < 0 || static_cast<size_t>(index) >= sig.size()) return -1;
+  const auto& spec = sig[static_cast<size_t>(index)];
+  *dtype = static_cast<int>(spec.dtype.code());
+  *rank = static_cast<int>(spec.shape.rank());
+  for (int i = 0; i < *rank && i < dims_cap; ++i) dims[i] = spec.shape.dims()[static_cast<size_t>(i)];
+  return 0;
+}
+
+// One run with HOST buffers: copy in through Backend::copy, Executable::run on a
+// persistent stream, synchronise, copy out.
+int fref_run(void* handle, const void* const* host_in, void* const* host_out, char* err,
+             int errlen) {
+  auto* h = static_cast<Handle*>(handle);
+  Status st = ensure_buffers(*h);
+  if (!st.is_ok()) {
+    set_err(err, errlen, std::string(st.message()));
+    return 1;
+  }
+  for (size_t i = 0; i < h->in_sig.size(); ++i) {
+    const size_t bytes = spec_bytes(h->in_sig[i]);
+    if (bytes == 0) continue;
+    st = h->backend->copy(h->dev_in[i].raw_data(), h->device, host_in[i], frame::cpu_device(),
+                          bytes, h->stream.get());
+    if (!st.is_ok()) {
+      set_err(err, errlen, std::string(st.message()));
+      return 2;
+    }
+  }
+  st = h->exe->run(h->dev_in, h->dev_out, *h->stream);
+  if (!st.is_ok()) {
+    set_err(err, errlen, std::string(st.message()));
+    return 3;
+  }
+  for (size_t i = 0; i < h->out_sig.size(); ++i) {
+    const size_t bytes = spec_bytes(h->out_sig[i]);
+    if (bytes == 0) continue;
+    st = h->backend->copy(host_out[i], frame::cpu_device(), h->dev_out[i].raw_data(), h->device,
+                          bytes, h->stream.get());
+    if (!st.is_ok()) {
+      set_err(err, errlen, std::string(st.message()));
+      return 4;
+    }
+  }
+  st = h->stream->synchronize();
+  if (!st.is_ok()) {
+    set_err(err, errlen, std::string(st.message()));
+    return 5;
+  }
+  return 0;
+}
+
+// Seconds per Executable::run (inputs already resident), averaged over `iters`
+// back-to-back runs followed by one stream synchronise; one untimed warm-up.
+double fref_time_run(void* handle, int iters, char* err, int errlen) {
+  auto* h = static_cast<Handle*>(handle);
+  Status st = ensure_buffers(*h);
+  if (!st.is_ok()) {
+    set_err(err, errlen, std::string(st.message()));
+    return -1.0;
+  }
+  st = h->exe->run(h->dev_in, h->dev_out, *h->stream);
+  if (st.is_ok()) st = h->stream->synchronize();
+  if (!st.is_ok()) {
+    set_err(err, errlen, std::string(st.message()));
+    return -1.0;
+  }
+  const auto t0 = std::chrono::steady_clock::now();
+  for (int i = 0; i < iters; ++i) {
+    st = h->exe->run(h->dev_in, h->dev_out, *h->stream);
+    if (!st.is_ok()) {
+      set_err(err, errlen, std::string(st.message()));
+      return -1.0;
+    }
+  }
+  st = h->stream->synchronize();
+  const auto t1 = std::chrono::steady_clock::now();
+  if (!st.is_ok()) {
+    set_err(err, errlen, std::string(st.message()));
+    return -1.0;
+  }
+  return std::chrono::duration<double>(t1 - t0).count() / (iters > 0 ? iters : 1);
+}
+
+// Device pointer of a resident input/output buffer (for harness-side timing).
+void* fref_device_buffer(void* handle, int is_output, int index) {
+  auto* h = static_cast<Handle*>(handle);
+  if (!ensure_buffers(*h).is_ok()) return nullptr;
+  auto& v = is_output ? h->dev_out : h->dev_in;
+  if (index < 0 || static_cast<size_t>(index) >= v.size()) return nullptr;
+  return v[static_cast<size_t>(index)].raw_data();
+}
+
+// IR text after the standard nine-pass pipeline for `backend` (what
+// Backend::compile receives).  Returns the number of bytes needed.
+int64_t fref_pipeline_text(const char* ir_text, const char* backend, char* out, int64_t cap,
+                           char* err, int errlen) {
+  const std::string_view bname = static_backend_name(backend);
+  Result<frame::ir::Graph> graph = frame::ir::parse_text(ir_text);
+  if (!graph.is_ok()) {
+    set_err(err, errlen, std::string(graph.status().message()));
+    return -1;
+  }
+  Result<frame::compiler::PassManager> pm = frame::compiler::standard_pipeline(bname);
+  if (!pm.is_ok()) {
+    set_err(err, errlen, std::string(pm.status().message()));
+    return -1;
+  }
+  const Status st = pm.value().run(graph.value());
+  if (!st.is_ok()) {
+    set_err(err, errlen, std::string(st.message()));
+    return -1;
+  }
+  const std::string text = frame::ir::dump_text(graph.value());
+  if (out != nullptr && cap > 0) {
+    std::snprintf(out, static_cast<size_t>(cap), "%s", text.c_str());
+  }
+  return static_cast<int64_t>(text.size()) + 1;
+}
+
+// The executable plan the reference builds for the pipeline's output (steps,
+// slots, arena offsets of the memory planner), as line-oriented text:
+//   plan slots=<n> arena=<bytes>
+//   in <slot> <dtype> <rank> <dims...>
+//   step <op> nin=<k> <slots...> nout=<m> (<slot> <dtype> <offset|-1> <rank> <dims...>)* attrs=<k>
+//   attr <name> <kind> <value text in the IR's own attribute format>
+//   out <slot>
+int64_t fref_plan_text(const char* ir_text, const char* backend, int run_pipeline, char* out,
+                       int64_t cap, char* err, int errlen) {
+  const std::string_view bname = static_backend_name(backend);
+  Result<frame::ir::Graph> graph = frame::ir::parse_text(ir_text);
+  if (!graph.is_ok()) {
+    set_err(err, errlen, std::string(graph.status().message()));
+    return -1;
+  }
+  if (run_pipeline != 0) {
+    Result<frame::compiler::PassManager> pm = frame::compiler::standard_pipeline(bname);
+    if (!pm.is_ok()) {
+      set_err(err, errlen, std::string(pm.status().message()));
+      return -1;
+    }
+    const Status st = pm.value().run(graph.value());
+    if (!st.is_ok()) {
+      set_err(err, errlen, std::string(st.message()));
+      return -1;
+    }
+  }
+  Result<frame::ops::ExecutablePlan> plan = frame::ops::build_executable_plan(graph.value(), bname);
+  if (!plan.is_ok()) {
+    set_err(err, errlen, std::string(plan.status().message()));
+    return -1;
+  }
+  const frame::ops::ExecutablePlan& p = plan.value();
+  std::ostringstream os;
+  os << "plan slots=" << p.slot_count << " arena=" << p.arena_total_bytes << "\n";
+  for (size_t i = 0; i < p.input_types.size(); ++i) {
+    const auto& t = p.input_types[i];
+    os << "in " << i << " " << static_cast<int>(t.dtype.code()) << " " << t.shape.rank();
+    for (const int64_t d : t.shape.dims()) os << " " << d;
+    os << "\n";
+  }
+  for (const auto& step : p.steps) {
+    os << "step " << step.op << " nin=" << step.input_slots.size();
+    for (const int32_t s : step.input_slots) os << " " << s;
+    os << " nout=" << step.output_slots.size();
+    for (size_t i = 0; i < step.output_slots.size(); ++i) {
+      const auto& t = step.output_types[i];
+      const long long off = step.output_arena_offsets[i].has_value()
+                                ? static_cast<long long>(*step.output_arena_offsets[i])
+                                : -1LL;
+      os << " " << step.output_slots[i] << " " << static_cast<int>(t.dtype.code()) << " " << off
+         << " " << t.shape.rank();
+      for (const int64_t d : t.shape.dims()) os << " " << d;
+    }
+    os << " attrs=" << step.attrs.size() << "\n";
+    std::vector<std::string> names;
+    for (const auto& kv : step.attrs) names.push_back(kv.first);
+    std::sort(names.begin(), names.end());
+    for (const auto& name : names) {
+      const auto& v = step.attrs.at(name);
+      os << "attr " << name << " " << frame::ir::attr_type_name(frame::ir::attr_type_of(v)) << " "
+         << frame::ir::format_attr_value(v) << "\n";
+    }
+  }
+  for (const int32_t s : p.output_slots) os << "out " << s << "\n";
+  const std::string text = os.str();
+  if (out != nullptr && cap > 0) {
+    std::snprintf(out, static_cast<size_t>(cap), "%s", text.c_str());
+  }
+  return static_cast<int64_t>(text.size()) + 1;
+}
+
+int64_t fref_fallback_count(const char* op, const char* backend) {
+  return frame::runtime::FallbackStats::instance().count(op, backend);
+}
+
+void fref_fallback_reset() { frame::runtime::FallbackStats::instance().reset(); }
+
+int fref_has_kernel(const char* op, const char* backend) {
+  return frame::ops::KernelRegistry::instance().find(op, backend).is_ok() ? 1 : 0;
+}
+
+int fref_has_backend(const char* backend) {
+  return frame::hal::BackendRegistry::instance().get(backend).is_ok() ? 1 : 0;
+}
+
+}  // extern "C"

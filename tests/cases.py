@@ -1,0 +1,205 @@
+"""Seeded single-op parity cases shared by the golden-vector generator, the oracle pin tests
+(CPU) and the C-ABI parity tests (GPU).  Shapes follow the reference's own CUDA-vs-CPU
+differential tests (tests/cpp/backends/test_cuda_backend.cpp:1174-2345 of the reference: the
+1023/1024 vectorisation boundary, odd shapes, zero-size tensors) and the BASELINE configs in
+miniature.  Every case names the reference op, its attributes and its inputs in storage form
+(uint16 bit patterns for bf16)."""
+from __future__ import annotations
+
+import os
+import sys
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from oracle import frame_oracle as fo  # noqa: E402
+from frame_public_b200 import irtext  # noqa: E402
+
+F32, BF16, I32, I64 = fo.DT_F32, fo.DT_BF16, fo.DT_I32, fo.DT_I64
+
+
+@dataclass
+class Case:
+    name: str
+    op: str
+    dtype: int
+    inputs: List[np.ndarray]
+    attrs: Dict[str, object] = field(default_factory=dict)
+    oracle: Callable[..., np.ndarray] = None
+    exact: bool = False       # integer/indexing work or fp32 without libm: bit-exact expected
+    new_op: bool = False      # not in the reference (parity unpinned by the reference)
+
+    def expected(self) -> np.ndarray:
+        return self.oracle(*self.inputs)
+
+    def ir_text(self, backend: str = "cpu") -> str:
+        g = irtext.IrGraph(backend)
+        dt = irtext.DTYPE_NAMES[self.dtype]
+        vals = [g.input(dt, a.shape) for a in self.inputs]
+        out_shape = self.expected().shape
+        attrs = dict(self.attrs)
+        if "target_shape" in attrs:
+            attrs["target_shape"] = irtext.Shape(tuple(attrs["target_shape"]))
+        out = g.node(self.op, vals, attrs, dt, out_shape)
+        g.output(out)
+        return g.text()
+
+
+def _store(x, dtype):
+    return fo.from_accum(np.asarray(x, dtype=np.float32), dtype) if dtype in (F32, BF16) else x
+
+
+def _rng(seed):
+    return np.random.default_rng(seed)
+
+
+def build_cases() -> List[Case]:
+    cases: List[Case] = []
+    seed = [1000]
+
+    def rnd(shape, dtype=F32, lo=None, scale=1.0):
+        seed[0] += 1
+        r = _rng(seed[0])
+        if lo is not None:
+            v = r.uniform(lo[0], lo[1], size=shape).astype(np.float32)
+        else:
+            v = (r.standard_normal(size=shape) * scale).astype(np.float32)
+        return _store(v, dtype)
+
+    # ---- matmul ----------------------------------------------------------------------------
+    for name, (m, k, n), dt in [("matmul_f32_5x7x3", (5, 7, 3), F32),
+                                ("matmul_f32_64x784x256", (64, 784, 256), F32),
+                                ("matmul_f32_33x17x9", (33, 17, 9), F32),
+                                ("matmul_f32_64x256x10", (64, 256, 10), F32),
+                                ("matmul_f32_130x70x200", (130, 70, 200), F32),
+                                ("matmul_bf16_64x64x64", (64, 64, 64), BF16),
+                                ("matmul_bf16_37x50x21", (37, 50, 21), BF16)]:
+        a, b = rnd((m, k), dt, lo=(-1, 1)), rnd((k, n), dt, lo=(-1, 1))
+        cases.append(Case(name, "matmul", dt, [a, b], {}, lambda a, b, dt=dt: fo.matmul(a, b, dt),
+                          exact=True))
+
+    # ---- elementwise and fused groups --------------------------------------------------------
+    for dt, tag in [(F32, "f32"), (BF16, "bf16")]:
+        for n in (1023, 1024, 5):
+            for op in ("add", "mul"):
+                cases.append(Case(f"{op}_{tag}_{n}", op, dt, [rnd((n,), dt), rnd((n,), dt)], {},
+                                  lambda a, b, op=op, dt=dt: fo.BINARY[op](a, b, dt), exact=True))
+            for op in ("relu", "square"):
+                cases.append(Case(f"{op}_{tag}_{n}", op, dt, [rnd((n,), dt)], {},
+                                  lambda a, op=op, dt=dt: fo.UNARY[op](a, dt), exact=True))
+            for op in ("sigmoid", "tanh"):
+                cases.append(Case(f"{op}_{tag}_{n}", op, dt, [rnd((n,), dt, scale=3.0)], {},
+                                  lambda a, op=op, dt=dt: fo.UNARY[op](a, dt)))
+            cases.append(Case(f"rsqrt_{tag}_{n}", "rsqrt", dt, [rnd((n,), dt, lo=(0.01, 9.0))], {},
+                              lambda a, dt=dt: fo.rsqrt(a, dt), exact=True))
+        for chain, ar in [("add;relu", [2, 1]), ("add;mul;relu", [2, 2, 1]),
+                          ("relu;add", [1, 2]), ("square;add;mul;relu", [1, 2, 2, 1])]:
+            n_in = sum(ar) - (len(ar) - 1)
+            ins = [rnd((6, 171), dt) for _ in range(n_in)]
+            cases.append(Case(f"fused_{chain.replace(';', '_')}_{tag}", "fused_elementwise_internal",
+                              dt, ins, {"ops": chain, "arities": ar},
+                              lambda *xs, chain=chain, ar=ar, dt=dt: fo.fused_elementwise(list(xs), chain, ar, dt),
+                              exact=True))
+    for dt, tag, npdt in [(I32, "i32", np.int32), (I64, "i64", np.int64)]:
+        r = _rng(77)
+        a = r.integers(-1000, 1000, size=(1023,)).astype(npdt)
+        b = r.integers(-1000, 1000, size=(1023,)).astype(npdt)
+        cases.append(Case(f"add_{tag}_1023", "add", dt, [a, b], {}, lambda a, b, dt=dt: fo.add(a, b, dt),
+                          exact=True))
+
+    # ---- row kernels -------------------------------------------------------------------------
+    for name, shape, dt in [("softmax_f32_64x10", (64, 10), F32), ("softmax_f32_5x33", (5, 33), F32),
+                            ("softmax_f32_9x512", (9, 512), F32), ("softmax_bf16_8x512", (8, 512), BF16),
+                            ("softmax_bf16_3x40", (3, 40), BF16), ("softmax_f32_2x4100", (2, 4100), F32)]:
+        cases.append(Case(name, "softmax", dt, [rnd(shape, dt, scale=2.0)], {},
+                          lambda x, dt=dt: fo.softmax(x, dt)))
+    for name, shape, dt in [("layer_norm_f32_4x100", (4, 100), F32), ("layer_norm_f32_7x1024", (7, 1024), F32),
+                            ("layer_norm_bf16_7x1024", (7, 1024), BF16), ("layer_norm_bf16_5x24", (5, 24), BF16)]:
+        g = _store(1.0 + 0.1 * _rng(5).standard_normal(shape[1]).astype(np.float32), dt)
+        b = _store(0.1 * _rng(6).standard_normal(shape[1]).astype(np.float32), dt)
+        cases.append(Case(name, "layer_norm", dt, [rnd(shape, dt), g, b], {"eps": 1e-5},
+                          lambda x, g, b, dt=dt: fo.layer_norm(x, g, b, 1e-5, dt)))
+
+    # ---- selective scan ----------------------------------------------------------------------
+    for name, shape, dt in [("scan_f32_3x5x37", (3, 5, 37), F32), ("scan_f32_70x64", (70, 64), F32),
+                            ("scan_f32_2x2048", (2, 2048), F32), ("scan_bf16_40x96", (40, 96), BF16),
+                            ("scan_f32_1", (1,), F32), ("scan_f32_0x3", (0, 3), F32)]:
+        x = rnd(shape, dt)
+        a = rnd(shape, dt, lo=(0.5, 0.99))
+        b, c, d = rnd(shape, dt), rnd(shape, dt), rnd(shape, dt)
+        exact = name != "scan_f32_2x2048"  # few long rows take the time-parallel kernel
+        cases.append(Case(name, "selective_scan", dt, [x, a, b, c, d], {},
+                          lambda x, a, b, c, d, dt=dt: fo.selective_scan(x, a, b, c, d, dt), exact=exact))
+
+    # ---- conv / pool ---------------------------------------------------------------------------
+    def conv_case(name, xs, ws, stride, padding, groups, bias, dt=F32):
+        x, w = rnd(xs, dt), rnd(ws, dt, scale=0.3)
+        ins = [x, w] + ([rnd((ws[0],), dt)] if bias else [])
+        cases.append(Case(name, "conv2d", dt, ins,
+                          {"stride": list(stride), "padding": list(padding), "groups": groups},
+                          lambda x, w, b=None, dt=dt: fo.conv2d(x, w, b, stride, padding, groups, dt),
+                          exact=True))
+
+    conv_case("conv2d_f32_3x3_s1_p1", (2, 3, 9, 9), (4, 3, 3, 3), (1, 1), (1, 1), 1, True)
+    conv_case("conv2d_f32_7x7_s2_p3", (1, 3, 20, 20), (8, 3, 7, 7), (2, 2), (3, 3), 1, True)
+    conv_case("conv2d_f32_groups2", (2, 4, 6, 7), (6, 2, 3, 2), (1, 2), (0, 1), 2, False)
+    conv_case("conv2d_f32_64ch_3x3", (2, 64, 10, 10), (64, 64, 3, 3), (1, 1), (1, 1), 1, True)
+    conv_case("conv2d_bf16_3x3", (1, 4, 8, 8), (5, 4, 3, 3), (1, 1), (1, 1), 1, True, BF16)
+    xs, ws = (2, 6, 20), (6, 1, 4)
+    cases.append(Case("conv1d_f32_depthwise_causal", "conv1d", F32,
+                      [rnd(xs), rnd(ws, scale=0.5), rnd((6,))], {"stride": 1, "padding": 3, "groups": 6},
+                      lambda x, w, b: fo.conv1d(x, w, b, 1, 3, 6, F32), exact=True))
+    cases.append(Case("conv1d_f32_dense_s2", "conv1d", F32, [rnd((2, 4, 15)), rnd((3, 4, 3), scale=0.5)],
+                      {"stride": 2, "padding": 1, "groups": 1},
+                      lambda x, w: fo.conv1d(x, w, None, 2, 1, 1, F32), exact=True))
+    tie = np.array([[[[5, 5, 1, 2], [5, 5, 2, 2], [1, 1, 3, 3], [0, 1, 3, 3]]]], dtype=np.float32)
+    cases.append(Case("max_pool2d_f32_ties", "max_pool2d", F32, [tie],
+                      {"kernel": [2, 2], "stride": [2, 2], "padding": [0, 0]},
+                      lambda x: fo.max_pool2d(x, (2, 2), (2, 2), (0, 0), F32), exact=True))
+    cases.append(Case("max_pool2d_f32_k3_s2_p1", "max_pool2d", F32, [rnd((2, 3, 9, 11))],
+                      {"kernel": [3, 3], "stride": [2, 2], "padding": [1, 1]},
+                      lambda x: fo.max_pool2d(x, (3, 3), (2, 2), (1, 1), F32), exact=True))
+    cases.append(Case("max_pool2d_bf16_k3_s2_p1", "max_pool2d", BF16, [rnd((1, 2, 8, 8), BF16)],
+                      {"kernel": [3, 3], "stride": [2, 2], "padding": [1, 1]},
+                      lambda x: fo.max_pool2d(x, (3, 3), (2, 2), (1, 1), BF16), exact=True))
+
+    # ---- data movement ---------------------------------------------------------------------------
+    for name, shape, perm, dt in [("transpose_f32_5x7", (5, 7), (1, 0), F32),
+                                  ("transpose_f32_2x33x65_021", (2, 33, 65), (0, 2, 1), F32),
+                                  ("transpose_bf16_3x40x24_021", (3, 40, 24), (0, 2, 1), BF16),
+                                  ("transpose_f32_2x3x4_201", (2, 3, 4), (2, 0, 1), F32),
+                                  ("transpose_f32_2x3x4x5_0213", (2, 3, 4, 5), (0, 2, 1, 3), F32)]:
+        cases.append(Case(name, "transpose", dt, [rnd(shape, dt)], {"perm": list(perm)},
+                          lambda x, perm=perm: fo.transpose(x, perm), exact=True))
+    cases.append(Case("slice_f32_cols", "slice", F32, [rnd((6, 30))], {"axis": 1, "start": 10, "stop": 20},
+                      lambda x: fo.slice_(x, 1, 10, 20), exact=True))
+    cases.append(Case("slice_bf16_odd", "slice", BF16, [rnd((3, 7, 5), BF16)], {"axis": 1, "start": 1, "stop": 4},
+                      lambda x: fo.slice_(x, 1, 1, 4), exact=True))
+    cases.append(Case("concat_f32_axis1", "concat", F32, [rnd((4, 3)), rnd((4, 5)), rnd((4, 8))], {"axis": 1},
+                      lambda *xs: fo.concat(xs, 1), exact=True))
+    cases.append(Case("concat_bf16_axis0", "concat", BF16, [rnd((2, 6), BF16), rnd((3, 6), BF16)], {"axis": 0},
+                      lambda *xs: fo.concat(xs, 0), exact=True))
+    cases.append(Case("reshape_f32", "reshape", F32, [rnd((4, 6))], {"target_shape": (2, 12)},
+                      lambda x: fo.reshape(x, (2, 12)), exact=True))
+    cases.append(Case("sum_f32_axis2of4", "sum", F32, [rnd((2, 5, 16, 24))], {"axes": [2]},
+                      lambda x: fo.sum_axes(x, [2], False, F32), exact=True))
+    cases.append(Case("sum_f32_last", "sum", F32, [rnd((7, 33))], {"axes": [1]},
+                      lambda x: fo.sum_axes(x, [1], False, F32), exact=True))
+
+    # ---- new ops (not in the reference) ------------------------------------------------------------
+    for dt, tag in [(F32, "f32"), (BF16, "bf16")]:
+        for op in ("gelu", "silu", "softplus", "exp"):
+            cases.append(Case(f"{op}_{tag}_1023", op, dt, [rnd((1023,), dt, scale=2.0)], {},
+                              lambda a, op=op, dt=dt: fo.UNARY[op](a, dt), new_op=True))
+        cases.append(Case(f"bias_add_{tag}", "bias_add", dt, [rnd((9, 40), dt), rnd((40,), dt)], {},
+                          lambda x, b, dt=dt: fo.bias_add(x, b, dt), exact=True, new_op=True))
+    return cases
+
+
+CASES = build_cases()
+CASES_BY_NAME = {c.name: c for c in CASES}

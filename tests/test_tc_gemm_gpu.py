@@ -1,0 +1,113 @@
+"""Tensor-core (tcgen05/TMEM/TMA) matmul parity against the CPU oracle.
+
+bf16: products of bf16 values are exact in fp32, so the only difference from the CPU reference
+is the order of the fp32 accumulation; tolerance = the reference's bf16 tier (rtol 2e-2,
+atol 2e-3).  fp32 with allow_tf32: operands are read as TF32 (10 explicit mantissa bits), so the
+error of a K-term dot product is about 2^-10 * sqrt(K) * rms(a) * rms(b); tolerance =
+rtol 1e-3 (the reference's TF32 tier, tests/cpp/common/tolerance.h:90-98) plus
+atol = 2e-3 * sqrt(K) * rms(a) * rms(b) for outputs that cancel to near zero."""
+import numpy as np
+import pytest
+
+from frame_public_b200 import capi
+from oracle import frame_oracle as fo
+
+pytestmark = pytest.mark.gpu
+
+
+def _gen(m, k, n, dt, seed):
+    rng = np.random.default_rng(seed)
+    a = fo.from_accum(rng.uniform(-1, 1, (m, k)).astype(np.float32), dt)
+    b = fo.from_accum(rng.uniform(-1, 1, (k, n)).astype(np.float32), dt)
+    return a, b
+
+
+def _run(a, b, dt, allow_tf32, steps=None, operands=None):
+    m, k = a.shape
+    n = b.shape[1]
+    da, db = capi.DeviceBuffer.from_numpy(a), capi.DeviceBuffer.from_numpy(b)
+    dc = capi.DeviceBuffer(m * n * capi.ITEMSIZE[dt])
+    keep = []
+    epi = None
+    if steps:
+        lst = []
+        for name, opnd, mode in steps:
+            if opnd is not None:
+                buf = capi.DeviceBuffer.from_numpy(opnd)
+                keep.append(buf)
+                lst.append((name, buf.ptr, mode))
+            else:
+                lst.append((name, None, 0))
+        epi = capi.make_epilogue(lst)
+    capi.matmul(da.ptr, db.ptr, dc.ptr, m, n, k, dt, allow_tf32, epi)
+    capi.synchronize()
+    assert capi.kernel_status(0) == 0
+    return dc.download(capi.NP_STORAGE[dt], (m, n))
+
+
+SHAPES = [(128, 64, 256), (256, 256, 256), (128, 512, 64), (300, 136, 520), (64, 784, 256),
+          (1024, 1024, 1024), (4096, 64, 512), (512, 512, 64), (130, 72, 80)]
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_bf16_matmul_tensor_cores(shape):
+    m, k, n = shape
+    assert capi.load().fb200_matmul_uses_tensor_cores(m, n, k, capi.BF16, 0) == 1
+    a, b = _gen(m, k, n, fo.DT_BF16, 11)
+    got = _run(a, b, fo.DT_BF16, False)
+    exp = fo.matmul(a, b, fo.DT_BF16)
+    assert fo.all_close(got, exp, fo.DT_BF16), fo.max_err(got, exp, fo.DT_BF16)
+
+
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_tf32_matmul_tensor_cores(shape):
+    m, k, n = shape
+    assert capi.load().fb200_matmul_uses_tensor_cores(m, n, k, capi.F32, 1) == 1
+    a, b = _gen(m, k, n, fo.DT_F32, 12)
+    got = _run(a, b, fo.DT_F32, True)
+    exp = fo.matmul(a, b, fo.DT_F32)
+    atol = 2e-3 * np.sqrt(k) * float(np.sqrt((a ** 2).mean()) * np.sqrt((b ** 2).mean()))
+    assert fo.all_close(got, exp, fo.DT_F32, rtol=1e-3, atol=atol), fo.max_err(got, exp)
+
+
+def test_strict_fp32_is_bit_identical_to_the_cpu_reference():
+    a, b = _gen(200, 300, 136, fo.DT_F32, 13)
+    got = _run(a, b, fo.DT_F32, False)
+    assert np.array_equal(got, fo.matmul(a, b, fo.DT_F32))
+
+
+@pytest.mark.parametrize("dt,tf32", [(fo.DT_BF16, False), (fo.DT_F32, True), (fo.DT_F32, False)],
+                         ids=["bf16", "tf32", "fp32_strict"])
+def test_fused_epilogue_bias_full_then_gelu_then_residual(dt, tf32):
+    m, k, n = 384, 256, 520
+    a, b = _gen(m, k, n, dt, 14)
+    rng = np.random.default_rng(15)
+    bias_full = fo.from_accum(np.tile(rng.normal(0, 0.1, (1, n)).astype(np.float32), (m, 1)), dt)
+    resid = fo.from_accum(rng.standard_normal((m, n)).astype(np.float32), dt)
+    got = _run(a, b, dt, tf32, steps=[("add", bias_full, capi.OPERAND_FULL), ("gelu", None, 0),
+                                      ("add", resid, capi.OPERAND_FULL)])
+    mm = fo.matmul(a, b, dt)
+    exp = fo.add(fo.gelu(fo.add(mm, bias_full, dt), dt), resid, dt)
+    if dt == fo.DT_F32 and not tf32:
+        assert fo.all_close(got, exp, dt), fo.max_err(got, exp, dt)
+    elif dt == fo.DT_F32:
+        atol = 2e-3 * np.sqrt(k) * float(np.sqrt((a ** 2).mean()) * np.sqrt((b ** 2).mean()))
+        assert fo.all_close(got, exp, dt, rtol=1e-3, atol=atol), fo.max_err(got, exp, dt)
+    else:
+        assert fo.all_close(got, exp, dt, rtol=2e-2, atol=2e-2), fo.max_err(got, exp, dt)
+
+
+def test_epilogue_column_and_row_operands():
+    m, k, n = 256, 128, 264
+    dt = fo.DT_BF16
+    a, b = _gen(m, k, n, dt, 16)
+    rng = np.random.default_rng(17)
+    col = fo.from_accum(rng.standard_normal(n).astype(np.float32), dt)
+    row = fo.from_accum(rng.uniform(0.5, 1.5, m).astype(np.float32), dt)
+    got = _run(a, b, dt, False, steps=[("add", col, capi.OPERAND_COL), ("relu", None, 0),
+                                       ("mul", row, capi.OPERAND_ROW)])
+    mm = fo.to_accum(fo.matmul(a, b, dt), dt)
+    e1 = fo.round_through(mm + fo.to_accum(col, dt)[None, :], dt)
+    e2 = np.where(e1 < 0, 0, e1).astype(np.float32)
+    exp = fo.from_accum(e2 * fo.to_accum(row, dt)[:, None], dt)
+    assert fo.all_close(got, exp, dt, rtol=2e-2, atol=2e-2), fo.max_err(got, exp, dt)
