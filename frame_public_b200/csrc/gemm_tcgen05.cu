@@ -174,8 +174,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
             // A: K-major, rows of 128 bytes, 8-row groups 1024 bytes apart; a K step is 32 bytes
             // further inside the swizzled row.
             const uint64_t a_desc = make_smem_desc_sw128(a_addr + ks * Cfg::kUmmaKBytes, 16, 1024);
-            const uint64_t b_desc = make_smem_desc_sw128(b_addr + ks * Cfg::kBKStepBytes,
-                                                         Cfg::kBChunkBytes, 1024);
+            // B: MN-major.  2-byte elements: 16-byte swizzle units, 8-row K groups 1024 bytes
+            // apart.  4-byte elements: 32-byte swizzle units, 4-row K groups 512 bytes apart.
+            const uint64_t b_desc =
+                ELT == 2 ? make_smem_desc(b_addr + ks * Cfg::kBKStepBytes, Cfg::kBChunkBytes, 1024,
+                                          kLayoutSw128)
+                         : make_smem_desc(b_addr + ks * Cfg::kBKStepBytes, Cfg::kBChunkBytes, 512,
+                                          kLayoutSw128Base32);
             const uint32_t accumulate = (kb > 0 || ks > 0) ? 1u : 0u;
             if (ELT == 2) mma_f16(d_tmem, a_desc, b_desc, idesc, accumulate);
             else mma_tf32(d_tmem, a_desc, b_desc, idesc, accumulate);
@@ -307,9 +312,10 @@ static EncodeTiledFn encode_tiled_fn() {
 }
 
 // 2-D row-major tensor [rows, cols] of `elt`-byte elements; box = 128 bytes x box_rows,
-// 128-byte swizzle, zero fill outside the tensor.
+// 128-byte swizzle (16-byte units, or 32-byte units for an MN-major 32-bit operand), zero fill
+// outside the tensor.
 int make_tmap_2d(CUtensorMap* map, const void* ptr, int dtype, int64_t rows, int64_t cols,
-                 int box_rows) {
+                 int box_rows, bool swizzle_32b_units) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return set_error(FB200_DEVICE_ERROR, "cuTensorMapEncodeTiled is not available");
   const int elt = itemsize_of(dtype);
@@ -321,7 +327,8 @@ int make_tmap_2d(CUtensorMap* map, const void* ptr, int dtype, int64_t rows, int
   cuuint32_t box[2] = {static_cast<cuuint32_t>(128 / elt), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, dt, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle_32b_units ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     return set_error(FB200_INTERNAL, "cuTensorMapEncodeTiled failed with code %d (rows %lld cols %lld)",
@@ -359,8 +366,8 @@ static int launch_tc(const void* a, const void* b, void* c, int64_t m, int64_t n
                      int dtype, const EpilogueDev& epi, cudaStream_t s) {
   using Cfg = GemmCfg<ELT, BLOCK_N>;
   CUtensorMap ta, tb;
-  if (int rc = make_tmap_2d(&ta, a, dtype, m, k, kBlockM)) return rc;
-  if (int rc = make_tmap_2d(&tb, b, dtype, k, n, Cfg::kBlockK)) return rc;
+  if (int rc = make_tmap_2d(&ta, a, dtype, m, k, kBlockM, false)) return rc;
+  if (int rc = make_tmap_2d(&tb, b, dtype, k, n, Cfg::kBlockK, ELT == 4)) return rc;
   int* status = nullptr;
   if (int rc = device_status_word(&status)) return rc;
   const uint32_t fmt = dtype == FB200_F32 ? kFmtTF32 : (dtype == FB200_BF16 ? kFmtBF16 : kFmtF16);

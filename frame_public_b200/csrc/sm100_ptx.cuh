@@ -167,12 +167,19 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
 // Shared-memory matrix descriptor (64-bit): start address >> 4 in bits [0,14), leading-dimension
 // byte offset >> 4 in [16,30), stride-dimension byte offset >> 4 in [32,46), descriptor version
 // 1 in [46,48), base offset 0, layout type in [61,64) (2 = 128-byte swizzle).
-__host__ __device__ constexpr uint64_t make_smem_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes,
-                                                            uint32_t sbo_bytes) {
+// Layout types: 2 = 128-byte swizzle of 16-byte units over 8 rows; 1 = 128-byte swizzle of
+// 32-byte units over 4 rows, the only form tcgen05 accepts for MN-major 32-bit (TF32) operands.
+enum : uint32_t { kLayoutSw128 = 2, kLayoutSw128Base32 = 1 };
+__host__ __device__ constexpr uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes,
+                                                      uint32_t sbo_bytes, uint32_t layout_type) {
   return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) |
          (static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16) |
          (static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32) |
-         (static_cast<uint64_t>(1) << 46) | (static_cast<uint64_t>(2) << 61);
+         (static_cast<uint64_t>(1) << 46) | (static_cast<uint64_t>(layout_type) << 61);
+}
+__host__ __device__ constexpr uint64_t make_smem_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes,
+                                                            uint32_t sbo_bytes) {
+  return make_smem_desc(smem_addr, lbo_bytes, sbo_bytes, kLayoutSw128);
 }
 
 // Instruction descriptor (32-bit) for kind::f16 / kind::tf32 with an fp32 accumulator:

@@ -155,3 +155,19 @@ def has_kernel(op: str, backend: str) -> bool:
 
 def has_backend(backend: str) -> bool:
     return bool(load().fref_has_backend(backend.encode()))
+
+
+_plugin = None
+
+
+def load_b200_backend():
+    """Loads this repository's Frame plugin (backend "cuda" + new-op registrations) into the
+    reference process.  The plugin's static registrars run at load time."""
+    global _plugin
+    if _plugin is None:
+        load()
+        path = os.path.join(os.path.dirname(HERE), "frame_public_b200", "lib", "libframe_b200_hal.so")
+        if not os.path.exists(path):
+            raise FileNotFoundError(f"{path} not built: run frame_public_b200/host/build_adapter.sh")
+        _plugin = ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
+    return _plugin

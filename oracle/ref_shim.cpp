@@ -13,12 +13,12 @@
 //   ops::build_executable_plan            src/ops/executable_plan.cpp:16-121
 //   hal::Backend::{allocator,copy,create_stream}  include/frame/hal/backend.h:77-109
 //   runtime::FallbackStats                include/frame/runtime/fallback_stats.h:21-41
+#include <algorithm>
 #include <chrono>
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
 #include <memory>
-#include <sstream>
 #include <string>
 #include <string_view>
 #include <variant>
@@ -297,39 +297,45 @@ int64_t fref_plan_text(const char* ir_text, const char* backend, int run_pipelin
     return -1;
   }
   const frame::ops::ExecutablePlan& p = plan.value();
-  std::ostringstream os;
-  os << "plan slots=" << p.slot_count << " arena=" << p.arena_total_bytes << "\n";
+  // Plain string appends: no iostreams in this translation unit.
+  std::string text;
+  auto num = [&](long long v) { text += ' '; text += std::to_string(v); };
+  text += "plan slots=" + std::to_string(p.slot_count) + " arena=" + std::to_string(p.arena_total_bytes) + "\n";
   for (size_t i = 0; i < p.input_types.size(); ++i) {
     const auto& t = p.input_types[i];
-    os << "in " << i << " " << static_cast<int>(t.dtype.code()) << " " << t.shape.rank();
-    for (const int64_t d : t.shape.dims()) os << " " << d;
-    os << "\n";
+    text += "in";
+    num(static_cast<long long>(i));
+    num(static_cast<int>(t.dtype.code()));
+    num(t.shape.rank());
+    for (const int64_t d : t.shape.dims()) num(d);
+    text += '\n';
   }
   for (const auto& step : p.steps) {
-    os << "step " << step.op << " nin=" << step.input_slots.size();
-    for (const int32_t s : step.input_slots) os << " " << s;
-    os << " nout=" << step.output_slots.size();
+    text += "step " + step.op + " nin=" + std::to_string(step.input_slots.size());
+    for (const int32_t s : step.input_slots) num(s);
+    text += " nout=" + std::to_string(step.output_slots.size());
     for (size_t i = 0; i < step.output_slots.size(); ++i) {
       const auto& t = step.output_types[i];
       const long long off = step.output_arena_offsets[i].has_value()
                                 ? static_cast<long long>(*step.output_arena_offsets[i])
                                 : -1LL;
-      os << " " << step.output_slots[i] << " " << static_cast<int>(t.dtype.code()) << " " << off
-         << " " << t.shape.rank();
-      for (const int64_t d : t.shape.dims()) os << " " << d;
+      num(step.output_slots[i]);
+      num(static_cast<int>(t.dtype.code()));
+      num(off);
+      num(t.shape.rank());
+      for (const int64_t d : t.shape.dims()) num(d);
     }
-    os << " attrs=" << step.attrs.size() << "\n";
+    text += " attrs=" + std::to_string(step.attrs.size()) + "\n";
     std::vector<std::string> names;
     for (const auto& kv : step.attrs) names.push_back(kv.first);
     std::sort(names.begin(), names.end());
     for (const auto& name : names) {
       const auto& v = step.attrs.at(name);
-      os << "attr " << name << " " << frame::ir::attr_type_name(frame::ir::attr_type_of(v)) << " "
-         << frame::ir::format_attr_value(v) << "\n";
+      text += "attr " + name + " " + std::string(frame::ir::attr_type_name(frame::ir::attr_type_of(v))) +
+              " " + frame::ir::format_attr_value(v) + "\n";
     }
   }
-  for (const int32_t s : p.output_slots) os << "out " << s << "\n";
-  const std::string text = os.str();
+  for (const int32_t s : p.output_slots) text += "out " + std::to_string(s) + "\n";
   if (out != nullptr && cap > 0) {
     std::snprintf(out, static_cast<size_t>(cap), "%s", text.c_str());
   }

@@ -1,0 +1,63 @@
+"""Compiled-graph parity on the GPU: the miniature workloads (MLP, GEMM+epilogue, conv stack,
+transformer block, Mamba block) run through the plan executor of the C ABI, fed with the plans the
+reference pipeline emitted (tests/golden/plans), against outputs of the unmodified reference CPU
+backend for the same seeded inputs (tests/golden/ref_cpu_workloads.npz)."""
+import os
+
+import numpy as np
+import pytest
+
+from frame_public_b200 import capi, configs, runtime
+from oracle import frame_oracle as fo
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+GOLD = os.path.join(HERE, "golden", "ref_cpu_workloads.npz")
+WORKLOADS = configs.small_workloads("cpu")
+
+
+def _plan_text(name):
+    with open(os.path.join(HERE, "golden", "plans", name + ".plan")) as f:
+        return f.read()
+
+
+def _tolerance(wl, tf32):
+    if wl.dtype == configs.BF16:
+        return dict(rtol=2e-2, atol=2e-2)   # bf16 tier, one notch looser for chains of bf16 ops
+    if tf32:
+        return dict(rtol=1e-3, atol=2e-3)   # TF32 tier (fp32 GEMM/conv on the tensor cores)
+    return dict(rtol=1e-5, atol=1e-6)       # strict fp32 tier
+
+
+@pytest.mark.parametrize("wl", WORKLOADS, ids=lambda w: w.name)
+@pytest.mark.parametrize("tf32", [False, True], ids=["strict", "allow_tf32"])
+@pytest.mark.parametrize("opt", [1, 0], ids=["fused", "unfused"])
+def test_workload_matches_reference_cpu(wl, tf32, opt):
+    gold = np.load(GOLD)[wl.name]
+    plan = runtime.CompiledPlan(_plan_text(wl.name), 0, allow_tf32=tf32, opt_level=opt)
+    (got,) = plan.run_host(wl.inputs)
+    (again,) = plan.run_host(wl.inputs)   # the arena is reused: a second run must agree bit for bit
+    assert capi.kernel_status(0) == 0
+    assert np.array_equal(got.view(np.uint8), again.view(np.uint8))
+    tol = _tolerance(wl, tf32)
+    assert fo.all_close(got, gold, wl.dtype, **tol), (wl.name, fo.max_err(got, gold, wl.dtype))
+    plan.close()
+
+
+def test_epilogue_absorption_reduces_launches():
+    wl = WORKLOADS[0]  # MLP: matmul, add;relu, matmul, add;relu, matmul, add, softmax
+    fused = runtime.CompiledPlan(_plan_text(wl.name), 0, opt_level=1)
+    plain = runtime.CompiledPlan(_plan_text(wl.name), 0, opt_level=0)
+    assert plain.launches_per_run == 7
+    assert fused.launches_per_run == 4
+    before = capi.launch_count()
+    fused.run_host(wl.inputs)
+    assert capi.launch_count() - before == 4
+
+
+def test_unknown_op_is_unimplemented_with_its_name():
+    lib = capi.load()
+    text = "plan slots=2 arena=0\nin 0 0 1 4\nstep frobnicate nin=1 0 nout=1 1 0 -1 1 4 attrs=0\nout 1\n"
+    p = capi.c_void_p()
+    rc = lib.fb200_plan_create(text.encode(), 0, 0, 1, capi.byref(p))
+    assert rc == 4 and b"frobnicate" in lib.fb200_last_error()
