@@ -64,7 +64,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
         objs = list(pool.map(lambda s: _compile(s, force, verbose), sources))
     if (force or not os.path.exists(LIB_PATH)
             or any(os.path.getmtime(o) > os.path.getmtime(LIB_PATH) for o in objs)):
-        cmd = [NVCC, *ARCH, "-shared", "-o", LIB_PATH, *objs, "-lpthread", "-ldl"]
+        cmd = [NVCC, *ARCH, "-shared", "-o", LIB_PATH, *objs, "-lpthread", "-ldl",
+               "-Xlinker", "--version-script=" + os.path.join(CSRC, "exports.map")]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")

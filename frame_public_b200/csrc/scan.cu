@@ -140,6 +140,106 @@ selective_scan_rows_kernel(const T* __restrict__ x, const T* __restrict__ a,
   }
 }
 
+// ---- many rows, aligned: double-buffered cp.async pipeline ----------------------------------------
+// A warp owns 32 rows.  One chunk is 64 bytes of every row and operand (16 fp32 / 32 bf16 steps);
+// the five operand tiles of chunk i+1 are in flight (cp.async, 16 bytes per request, 10 KiB per
+// warp) while lane r walks row r of chunk i.  Tiles keep the global row-major order with an 80-byte
+// pitch, which makes the per-lane 128-bit shared-memory reads conflict-free.  Same order and
+// association of operations as the CPU reference: bit-identical for fp32.
+constexpr int kSegBytes = 64;
+constexpr int kPitchBytes = 80;
+constexpr int kAsyncTileBytes = 32 * kPitchBytes;                 // one operand, one chunk
+constexpr int kAsyncWarpBytes = (2 * 5 + 1) * kAsyncTileBytes;    // double-buffered inputs + output
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kScanThreads)
+selective_scan_rows_async_kernel(const T* __restrict__ x, const T* __restrict__ a,
+                                 const T* __restrict__ b, const T* __restrict__ c,
+                                 const T* __restrict__ d, T* __restrict__ out, int64_t rows,
+                                 int64_t steps) {
+  constexpr int W = 16 / sizeof(T);           // elements per 16-byte vector
+  constexpr int CS = kSegBytes / sizeof(T);   // steps per chunk
+  extern __shared__ __align__(16) uint8_t smem_bytes[];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  uint8_t* wbase = smem_bytes + warp * kAsyncWarpBytes;
+  const uint32_t wbase_u32 = static_cast<uint32_t>(__cvta_generic_to_shared(wbase));
+  uint8_t* otile = wbase + 10 * kAsyncTileBytes;
+  const T* srcs[5] = {x, a, b, c, d};
+  const int64_t n_groups = (rows + 31) / 32;
+  const int64_t n_chunks = steps / CS;
+  const int64_t total_warps = static_cast<int64_t>(gridDim.x) * kScanWarps;
+  const int lrow = lane >> 2;   // 8 rows per warp-wide request
+  const int lvec = lane & 3;    // 4 vectors per 64-byte row segment
+
+  for (int64_t g = static_cast<int64_t>(blockIdx.x) * kScanWarps + warp; g < n_groups;
+       g += total_warps) {
+    const int64_t row0 = g * 32;
+    auto issue = [&](int64_t chunk, int buf) {
+#pragma unroll
+      for (int op = 0; op < 5; ++op) {
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const int r = it * 8 + lrow;
+          const int64_t row = row0 + r;
+          if (row < rows) {
+            const T* src = srcs[op] + row * steps + chunk * CS + lvec * W;
+            cp_async_16(wbase_u32 + (buf * 5 + op) * kAsyncTileBytes + r * kPitchBytes + lvec * 16, src);
+          }
+        }
+      }
+      cp_async_commit();
+    };
+    float state = 0.0f;
+    issue(0, 0);
+    for (int64_t ch = 0; ch < n_chunks; ++ch) {
+      const int buf = static_cast<int>(ch & 1);
+      if (ch + 1 < n_chunks) {
+        issue(ch + 1, buf ^ 1);
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
+      }
+      __syncwarp();
+      const uint8_t* tin = wbase + buf * 5 * kAsyncTileBytes + lane * kPitchBytes;
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        float xv[W], av[W], bv[W], cv[W], dv[W], yv[W];
+        load_vec<T>(reinterpret_cast<const T*>(tin + 0 * kAsyncTileBytes + v * 16), xv);
+        load_vec<T>(reinterpret_cast<const T*>(tin + 1 * kAsyncTileBytes + v * 16), av);
+        load_vec<T>(reinterpret_cast<const T*>(tin + 2 * kAsyncTileBytes + v * 16), bv);
+        load_vec<T>(reinterpret_cast<const T*>(tin + 3 * kAsyncTileBytes + v * 16), cv);
+        load_vec<T>(reinterpret_cast<const T*>(tin + 4 * kAsyncTileBytes + v * 16), dv);
+#pragma unroll
+        for (int e = 0; e < W; ++e) {
+          state = av[e] * state + bv[e] * xv[e];
+          yv[e] = cv[e] * state + dv[e] * xv[e];
+        }
+        store_vec<T>(reinterpret_cast<T*>(otile + lane * kPitchBytes + v * 16), yv);
+      }
+      __syncwarp();
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {
+        const int r = it * 8 + lrow;
+        const int64_t row = row0 + r;
+        if (row < rows) {
+          const uint4 val = *reinterpret_cast<const uint4*>(otile + r * kPitchBytes + lvec * 16);
+          *reinterpret_cast<uint4*>(out + row * steps + ch * CS + lvec * W) = val;
+        }
+      }
+      __syncwarp();
+    }
+  }
+}
+
 // Affine pair combine: apply (a1,b1) first, then (a2,b2): h -> a2*(a1*h+b1)+b2.
 struct Affine { float a, b; };
 __device__ __forceinline__ Affine combine(Affine first, Affine second) {
@@ -286,14 +386,20 @@ static int launch_scan(const void* x, const void* a, const void* b, const void* 
     selective_scan_steps_kernel<T><<<grid, kScanThreads, 0, s>>>(xp, ap, bp, cp, dp, op, rows, steps);
     return after_launch("selective_scan_steps_kernel");
   }
-  const size_t smem = static_cast<size_t>(kScanWarps) * 6 * kTileFloats * sizeof(float);
-  static bool attr_set = false;
-  if (!attr_set) {
-    FB200_CUDA_OK(cudaFuncSetAttribute(selective_scan_rows_kernel<T>,
+  if (al && steps % (kSegBytes / static_cast<int>(sizeof(T))) == 0) {
+    const size_t smem_async = static_cast<size_t>(kScanWarps) * kAsyncWarpBytes;
+    FB200_CUDA_OK(cudaFuncSetAttribute(selective_scan_rows_async_kernel<T>,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>(smem)));
-    attr_set = true;
+                                       static_cast<int>(smem_async)));
+    const int grid_async = grid_for(row_groups * 32, kScanThreads, 2);
+    selective_scan_rows_async_kernel<T><<<grid_async, kScanThreads, smem_async, s>>>(xp, ap, bp, cp, dp,
+                                                                                    op, rows, steps);
+    return after_launch("selective_scan_rows_async_kernel");
   }
+  const size_t smem = static_cast<size_t>(kScanWarps) * 6 * kTileFloats * sizeof(float);
+  FB200_CUDA_OK(cudaFuncSetAttribute(selective_scan_rows_kernel<T>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(smem)));
   const int grid = grid_for(row_groups * 32, kScanThreads, 2);
   selective_scan_rows_kernel<T><<<grid, kScanThreads, smem, s>>>(xp, ap, bp, cp, dp, op, rows,
                                                                   steps, al ? 1 : 0);

@@ -117,6 +117,60 @@ transpose_tile_kernel(const U* __restrict__ in, U* __restrict__ out, int64_t bat
   }
 }
 
+// Vectorised form for 2- and 4-byte elements whose extents allow 128-bit access on both sides:
+// a 64 x 64 tile, 16-byte global loads along C, a padded shared-memory tile, 16-byte global
+// stores along R.
+template <typename U>
+__global__ void __launch_bounds__(256)
+transpose_tile64_kernel(const U* __restrict__ in, U* __restrict__ out, int64_t batch, int64_t R,
+                        int64_t C) {
+  constexpr int V = 16 / sizeof(U);       // elements per 16-byte vector
+  constexpr int T = 64;                   // tile edge in elements
+  constexpr int VPR = T / V;              // vectors per tile row
+  constexpr int RPP = 256 / VPR;          // tile rows covered by one pass of the CTA
+  constexpr int PAD = 4 / sizeof(U);      // one 32-bit word of padding per row
+  __shared__ U tile[T][T + PAD];
+  const int64_t tiles_c = (C + T - 1) / T;
+  const int64_t tiles_r = (R + T - 1) / T;
+  const int64_t per_mat = tiles_c * tiles_r;
+  const int64_t total = per_mat * batch;
+  const int vec = threadIdx.x % VPR;
+  const int sub = threadIdx.x / VPR;
+  for (int64_t tix = blockIdx.x; tix < total; tix += gridDim.x) {
+    const int64_t b = tix / per_mat;
+    const int64_t rem = tix - b * per_mat;
+    const int64_t tr = rem / tiles_c;
+    const int64_t tc = rem - tr * tiles_c;
+    const U* src = in + b * R * C;
+    U* dst = out + b * R * C;
+#pragma unroll
+    for (int p = 0; p < T / RPP; ++p) {
+      const int lr = p * RPP + sub;
+      const int64_t r = tr * T + lr;
+      const int64_t c = tc * T + vec * V;
+      if (r < R && c < C) {   // C % V == 0: a vector is entirely inside or outside
+        const Vec16<U> v = *reinterpret_cast<const Vec16<U>*>(src + r * C + c);
+#pragma unroll
+        for (int e = 0; e < V; ++e) tile[lr][vec * V + e] = v.v[e];
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int p = 0; p < T / RPP; ++p) {
+      const int lc = p * RPP + sub;         // output row inside the tile = input column
+      const int64_t c = tc * T + lc;
+      const int64_t r = tr * T + vec * V;   // R % V == 0
+      if (c < C && r < R) {
+        Vec16<U> v;
+#pragma unroll
+        for (int e = 0; e < V; ++e) v.v[e] = tile[vec * V + e][lc];
+        *reinterpret_cast<Vec16<U>*>(dst + c * R + r) = v;
+      }
+    }
+    __syncthreads();
+  }
+}
+
 struct PermDesc {
   int rank;
   int64_t out_dims[8];
@@ -140,6 +194,25 @@ transpose_generic_kernel(const U* __restrict__ in, U* __restrict__ out, PermDesc
     }
     out[i] = in[off];
   }
+}
+
+// Launches the batched 2-D transpose out[b][c][r] = in[b][r][c].
+template <typename U>
+static int launch_tile_transpose(const U* ip, U* op, int64_t batch, int64_t R, int64_t C,
+                                 cudaStream_t s) {
+  constexpr int V = 16 / sizeof(U);
+  const bool vec_ok = (sizeof(U) == 2 || sizeof(U) == 4) && R % V == 0 && C % V == 0 &&
+                      aligned16(ip) && aligned16(op);
+  if (vec_ok) {
+    const int64_t tiles = batch * ((R + 63) / 64) * ((C + 63) / 64);
+    const int grid = static_cast<int>(tiles < int64_t(kNumSMs) * 8 ? tiles : int64_t(kNumSMs) * 8);
+    transpose_tile64_kernel<U><<<grid, 256, 0, s>>>(ip, op, batch, R, C);
+    return after_launch("transpose_tile64_kernel");
+  }
+  const int64_t tiles = batch * ((R + 31) / 32) * ((C + 31) / 32);
+  const int grid = static_cast<int>(tiles < int64_t(kNumSMs) * 16 ? tiles : int64_t(kNumSMs) * 16);
+  transpose_tile_kernel<U><<<grid, 256, 0, s>>>(ip, op, batch, R, C);
+  return after_launch("transpose_tile_kernel");
 }
 
 template <typename U>
@@ -176,16 +249,10 @@ static int launch_transpose(const void* x, void* out, int rank, const int64_t* d
   }
   // [R,C] -> [C,R]  or  [B,R,C] -> [B,C,R]
   if (n == 2 && os[0] == 1 && os[1] == od[0]) {
-    const int64_t tiles = ((od[0] + 31) / 32) * ((od[1] + 31) / 32);
-    const int grid = static_cast<int>(tiles < int64_t(kNumSMs) * 16 ? tiles : int64_t(kNumSMs) * 16);
-    transpose_tile_kernel<U><<<grid, 256, 0, s>>>(ip, op, 1, od[1], od[0]);
-    return after_launch("transpose_tile_kernel");
+    return launch_tile_transpose<U>(ip, op, 1, od[1], od[0], s);
   }
   if (n == 3 && os[1] == 1 && os[2] == od[1] && os[0] == od[1] * od[2]) {
-    const int64_t tiles = od[0] * ((od[1] + 31) / 32) * ((od[2] + 31) / 32);
-    const int grid = static_cast<int>(tiles < int64_t(kNumSMs) * 16 ? tiles : int64_t(kNumSMs) * 16);
-    transpose_tile_kernel<U><<<grid, 256, 0, s>>>(ip, op, od[0], od[2], od[1]);
-    return after_launch("transpose_tile_kernel");
+    return launch_tile_transpose<U>(ip, op, od[0], od[2], od[1], s);
   }
   PermDesc d{};
   d.rank = n;

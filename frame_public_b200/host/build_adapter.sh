@@ -20,5 +20,5 @@ ${CXX:-g++} -std=c++20 -O2 -ffp-contract=off -fPIC -shared \
   -I"$FRAME_ROOT/include" -I"$ROOT/include" -I"$HERE" \
   "$HERE/b200_backend.cpp" "$HERE/b200_kernels.cpp" "$HERE/new_ops.cpp" \
   -o "$PKG/lib/libframe_b200_hal.so" \
-  -L"$PKG/lib" -lframe_b200 -Wl,-rpath,'$ORIGIN'
+  -L"$PKG/lib" -lframe_b200 -Wl,-rpath,'$ORIGIN' -Wl,--version-script="$HERE/adapter_exports.map"
 echo "built $PKG/lib/libframe_b200_hal.so"

@@ -59,7 +59,7 @@ export REF OBJ CXX CXXFLAGS
 
 list_sources | xargs -P "$(nproc)" -I{} bash -c 'compile_one "$@"' _ {}
 
-$CXX -shared -o "$OUT/libframe_ref.so" "$OBJ"/*.o -lpthread
+$CXX -shared -o "$OUT/libframe_ref.so" "$OBJ"/*.o -lpthread -Wl,--version-script="$HERE/ref_exports.map"
 $CXX $CXXFLAGS -shared -o "$OUT/libframe_ref_shim.so" "$HERE/ref_shim.cpp" \
-  -L"$OUT" -lframe_ref -Wl,-rpath,'$ORIGIN'
+  -L"$OUT" -lframe_ref -Wl,-rpath,'$ORIGIN' -Wl,--version-script="$HERE/shim_exports.map"
 echo "built $OUT/libframe_ref.so and libframe_ref_shim.so"
