@@ -1,0 +1,97 @@
+"""Tensor-core implicit-GEMM conv2d (fp32 tensors, TF32 math, allow_tf32) against the CPU oracle.
+Tolerance: tcgen05 reads fp32 operands as TF32 (10 explicit mantissa bits, the low 13 bits are
+dropped), so each product errs by at most 2^-9 relative and an output by at most
+2^-9 * sum |x||w| over its window; the test bound is that elementwise figure plus the strict-fp32
+tier (rtol 1e-5, atol 1e-6) for the fp32 accumulation.  On these inputs that is tighter than the
+reference's TF32 tier (rtol 1e-3 / atol 1e-4 at K=512, tests/cpp/common/tolerance.h:90-98) scaled
+to the output magnitudes."""
+import numpy as np
+import pytest
+
+from frame_public_b200 import capi
+from oracle import frame_oracle as fo
+
+pytestmark = pytest.mark.gpu
+
+CASES = [
+    # (x shape, w shape, stride, padding, bias)
+    ((2, 3, 9, 9), (4, 3, 3, 3), (1, 1), (1, 1), True),
+    ((1, 3, 20, 20), (8, 3, 7, 7), (2, 2), (3, 3), True),
+    ((2, 64, 10, 10), (64, 64, 3, 3), (1, 1), (1, 1), True),
+    ((3, 16, 13, 17), (40, 16, 3, 3), (2, 1), (0, 1), False),
+    ((2, 3, 64, 64), (64, 3, 7, 7), (2, 2), (3, 3), True),
+    ((4, 64, 56, 56), (64, 64, 3, 3), (1, 1), (1, 1), True),
+    ((1, 8, 9, 9), (130, 8, 1, 1), (1, 1), (0, 0), True),
+]
+
+
+def _run(x, w, b, stride, padding, steps=None, extra=None):
+    n, cin, h, wd = x.shape
+    cout, _, kh, kw = w.shape
+    oh = (h + 2 * padding[0] - kh) // stride[0] + 1
+    ow = (wd + 2 * padding[1] - kw) // stride[1] + 1
+    dx, dw = capi.DeviceBuffer.from_numpy(x), capi.DeviceBuffer.from_numpy(w)
+    db = capi.DeviceBuffer.from_numpy(b) if b is not None else None
+    dout = capi.DeviceBuffer(n * cout * oh * ow * 4)
+    keep, epi = [], None
+    if steps:
+        lst = []
+        for name, opnd, mode in steps:
+            if opnd is not None:
+                buf = capi.DeviceBuffer.from_numpy(opnd)
+                keep.append(buf)
+                lst.append((name, buf.ptr, mode))
+            else:
+                lst.append((name, None, 0))
+        epi = capi.make_epilogue(lst)
+    p = capi.Conv2dParams(n, cin, h, wd, cout, kh, kw, stride[0], stride[1], padding[0], padding[1], 1)
+    capi.conv2d(dx.ptr, dw.ptr, db.ptr if db else None, dout.ptr, p, capi.F32, True, epi)
+    capi.synchronize()
+    assert capi.kernel_status(0) == 0
+    return dout.download(np.float32, (n, cout, oh, ow))
+
+
+def _within_tf32_bound(got, exp, x, w, stride, padding):
+    mag = fo.conv2d(np.abs(x), np.abs(w), None, stride, padding, 1, fo.DT_F32).astype(np.float64)
+    bound = mag * 2.0 ** -9 + 1e-5 * np.abs(exp) + 1e-6
+    err = np.abs(got.astype(np.float64) - exp.astype(np.float64))
+    return bool(np.all(err <= bound)), float((err / bound).max())
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: "x".join(map(str, c[0])) + "_w" + "x".join(map(str, c[1])))
+def test_conv2d_tensor_cores(case):
+    xs, ws, stride, padding, use_bias = case
+    rng = np.random.default_rng(21)
+    x = rng.standard_normal(xs).astype(np.float32)
+    w = (rng.standard_normal(ws) * 0.3).astype(np.float32)
+    b = rng.standard_normal(ws[0]).astype(np.float32) if use_bias else None
+    got = _run(x, w, b, stride, padding)
+    exp = fo.conv2d(x, w, b, stride, padding, 1, fo.DT_F32)
+    ok, worst = _within_tf32_bound(got, exp, x, w, stride, padding)
+    assert ok, (worst, fo.max_err(got, exp))
+
+
+def test_conv2d_tensor_cores_fused_relu_and_residual():
+    rng = np.random.default_rng(22)
+    x = rng.standard_normal((2, 64, 28, 28)).astype(np.float32)
+    w = (rng.standard_normal((64, 64, 3, 3)) * 0.05).astype(np.float32)
+    b = rng.standard_normal(64).astype(np.float32)
+    res = rng.standard_normal((2, 64, 28, 28)).astype(np.float32)
+    got = _run(x, w, b, (1, 1), (1, 1), steps=[("relu", None, 0), ("add", res, capi.OPERAND_FULL)])
+    exp = fo.add(fo.relu(fo.conv2d(x, w, b, (1, 1), (1, 1), 1)), res)
+    ok, worst = _within_tf32_bound(got, exp, x, w, (1, 1), (1, 1))
+    assert ok, (worst, fo.max_err(got, exp))
+
+
+def test_strict_conv2d_stays_bit_identical():
+    rng = np.random.default_rng(23)
+    x = rng.standard_normal((2, 8, 12, 12)).astype(np.float32)
+    w = rng.standard_normal((16, 8, 3, 3)).astype(np.float32)
+    n, cin, h, wd = x.shape
+    dx, dw = capi.DeviceBuffer.from_numpy(x), capi.DeviceBuffer.from_numpy(w)
+    dout = capi.DeviceBuffer(2 * 16 * 12 * 12 * 4)
+    p = capi.Conv2dParams(n, cin, h, wd, 16, 3, 3, 1, 1, 1, 1, 1)
+    capi.conv2d(dx.ptr, dw.ptr, None, dout.ptr, p, capi.F32, False)
+    capi.synchronize()
+    got = dout.download(np.float32, (2, 16, 12, 12))
+    assert np.array_equal(got, fo.conv2d(x, w, None, (1, 1), (1, 1), 1))
