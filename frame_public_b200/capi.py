@@ -103,6 +103,8 @@ SIGNATURES = {
     "fb200_plan_launches_per_run": (c_int, [_P]),
     "fb200_plan_run": (c_int, [_P, _PP, _PP, _P]),
     "fb200_plan_run_host": (c_int, [_P, _PP, _PP, _P]),
+    "fb200_plan_profile": (c_int, [_P, _PP, _PP, _P, POINTER(c_float), c_int, _IP]),
+    "fb200_plan_step_op": (c_char_p, [_P, c_int]),
 }
 
 _lib = None

@@ -78,6 +78,14 @@ struct fb200_plan {
   std::vector<void*> stage_in, stage_out;  // device staging for run_host
   int launches = 0;
   std::mutex mu;
+  // CUDA-graph replay of the step list: the first run with a given set of input/output pointers
+  // is eager (it also performs every lazy initialisation), the second captures the launches into
+  // a graph, later runs with the same pointers replay it with one cudaGraphLaunch.
+  bool graph_enabled = true;
+  int runs_with_key = 0;
+  std::vector<const void*> graph_key;
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t graph_exec = nullptr;
 };
 
 namespace fb200 {
@@ -648,6 +656,7 @@ extern "C" int fb200_plan_create(const char* plan_text, int device, int allow_tf
     return rc;
   }
   optimise(p);
+  if (const char* env = getenv("FRAME_B200_GRAPH")) p->graph_enabled = atoi(env) != 0;
   p->launches = 0;
   for (const Step& s : p->steps) {
     if (s.kind != Kind::kSkip && s.kind != Kind::kAlias && s.kind != Kind::kConstant && s.kind != Kind::kCopy) ++p->launches;
@@ -658,6 +667,8 @@ extern "C" int fb200_plan_create(const char* plan_text, int device, int allow_tf
 
 extern "C" int fb200_plan_destroy(fb200_plan* p) {
   if (p == nullptr) return FB200_OK;
+  if (p->graph_exec) cudaGraphExecDestroy(p->graph_exec);
+  if (p->graph) cudaGraphDestroy(p->graph);
   if (p->arena) fb200_free(p->device, p->arena);
   for (void* q : p->owned) fb200_free(p->device, q);
   for (void* q : p->stage_in) fb200_free(p->device, q);
@@ -697,12 +708,62 @@ extern "C" int fb200_plan_run(fb200_plan* p, const void* const* inputs, void* co
   }
   FB200_CUDA_OK(cudaSetDevice(p->device));
   std::lock_guard<std::mutex> lock(p->mu);  // runs share the arena
-  for (Step& s : p->steps) {
-    if (int rc = run_step(p, s, inputs, outputs, stream)) {
-      // keep the kernel's message, prefix the op like CudaExecutable::run does
-      std::string msg = fb200_last_error();
-      return set_error(rc, "plan run: op '%s' kernel failed: %s", s.op.c_str(), msg.c_str());
+  auto run_eager = [&]() -> int {
+    for (Step& s : p->steps) {
+      if (int rc = run_step(p, s, inputs, outputs, stream)) {
+        // keep the kernel's message, prefix the op like CudaExecutable::run does
+        std::string msg = fb200_last_error();
+        return set_error(rc, "plan run: op '%s' kernel failed: %s", s.op.c_str(), msg.c_str());
+      }
     }
+    return FB200_OK;
+  };
+  bool done = false;
+  if (p->graph_enabled && stream != nullptr && p->launches >= 2) {
+    std::vector<const void*> key;
+    for (size_t i = 0; i < p->input_slots.size(); ++i) key.push_back(inputs[i]);
+    for (size_t i = 0; i < p->output_slots.size(); ++i) key.push_back(outputs[i]);
+    key.push_back(stream);
+    if (key != p->graph_key) {
+      if (p->graph_exec) { cudaGraphExecDestroy(p->graph_exec); p->graph_exec = nullptr; }
+      if (p->graph) { cudaGraphDestroy(p->graph); p->graph = nullptr; }
+      p->graph_key = key;
+      p->runs_with_key = 0;
+    }
+    if (p->graph_exec != nullptr) {
+      FB200_CUDA_OK(cudaGraphLaunch(p->graph_exec, as_stream(stream)));
+      g_launch_count.fetch_add(p->launches, std::memory_order_relaxed);
+      done = true;
+    } else if (p->runs_with_key >= 1) {
+      const int64_t count_before = g_launch_count.load(std::memory_order_relaxed);
+      if (cudaStreamBeginCapture(as_stream(stream), cudaStreamCaptureModeRelaxed) == cudaSuccess) {
+        const int rc = run_eager();
+        cudaGraph_t captured = nullptr;
+        const cudaError_t end = cudaStreamEndCapture(as_stream(stream), &captured);
+        if (rc == FB200_OK && end == cudaSuccess && captured != nullptr &&
+            cudaGraphInstantiate(&p->graph_exec, captured, 0) == cudaSuccess) {
+          p->graph = captured;
+          g_launch_count.store(count_before, std::memory_order_relaxed);  // capture launched nothing
+          FB200_CUDA_OK(cudaGraphLaunch(p->graph_exec, as_stream(stream)));
+          g_launch_count.fetch_add(p->launches, std::memory_order_relaxed);
+          done = true;
+        } else {
+          if (captured) cudaGraphDestroy(captured);
+          p->graph_exec = nullptr;
+          p->graph_enabled = false;  // this plan stays on eager launches
+          (void)cudaGetLastError();
+          g_launch_count.store(count_before, std::memory_order_relaxed);
+          if (rc != FB200_OK) return rc;
+        }
+      } else {
+        (void)cudaGetLastError();
+        p->graph_enabled = false;
+      }
+    }
+    ++p->runs_with_key;
+  }
+  if (!done) {
+    if (int rc = run_eager()) return rc;
   }
   // Outputs that are not produced by a step writing into the caller's buffer: graph inputs
   // passed through, constants, repeated outputs.
@@ -747,4 +808,49 @@ extern "C" int fb200_plan_run_host(fb200_plan* p, const void* const* host_inputs
     if (int rc = fb200_memcpy(p->device, host_outputs[i], p->stage_out[i], p->slots[p->output_slots[i]].bytes(), FB200_D2H, stream, 0)) return rc;
   }
   return fb200_stream_synchronize(p->device, stream);
+}
+
+// Per-step device times of one eager run (CUDA events on `stream` around every step), for
+// harness-side roofline accounting.  Steps that launch nothing report 0.  Synchronises the stream.
+extern "C" int fb200_plan_profile(fb200_plan* p, const void* const* inputs, void* const* outputs,
+                                  fb200_stream stream, float* step_ms, int cap, int* n_steps) {
+  if (p == nullptr || step_ms == nullptr || n_steps == nullptr) {
+    return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_profile: null argument");
+  }
+  const int n = static_cast<int>(p->steps.size());
+  *n_steps = n;
+  if (cap < n) return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_profile: room for %d steps, plan has %d", cap, n);
+  FB200_CUDA_OK(cudaSetDevice(p->device));
+  std::lock_guard<std::mutex> lock(p->mu);
+  std::vector<cudaEvent_t> ev(static_cast<size_t>(n) + 1);
+  for (auto& e : ev) FB200_CUDA_OK(cudaEventCreate(&e));
+  int rc = FB200_OK;
+  FB200_CUDA_OK(cudaEventRecord(ev[0], as_stream(stream)));
+  for (int i = 0; i < n && rc == FB200_OK; ++i) {
+    rc = run_step(p, p->steps[i], inputs, outputs, stream);
+    FB200_CUDA_OK(cudaEventRecord(ev[i + 1], as_stream(stream)));
+  }
+  FB200_CUDA_OK(cudaStreamSynchronize(as_stream(stream)));
+  for (int i = 0; i < n && rc == FB200_OK; ++i) {
+    const Kind k = p->steps[i].kind;
+    step_ms[i] = 0.0f;
+    if (k != Kind::kSkip && k != Kind::kAlias && k != Kind::kConstant) {
+      FB200_CUDA_OK(cudaEventElapsedTime(&step_ms[i], ev[i], ev[i + 1]));
+    }
+  }
+  for (auto& e : ev) cudaEventDestroy(e);
+  return rc;
+}
+
+// Op name of step `index`; a contraction that absorbed a following group reports
+// "matmul+epilogue" / "conv2d+epilogue", a step folded away reports "(absorbed)" or "(alias)".
+extern "C" const char* fb200_plan_step_op(const fb200_plan* p, int index) {
+  static thread_local std::string name;
+  if (p == nullptr || index < 0 || static_cast<size_t>(index) >= p->steps.size()) return "";
+  const Step& s = p->steps[static_cast<size_t>(index)];
+  if (s.kind == Kind::kSkip) name = "(absorbed)";
+  else if (s.kind == Kind::kAlias) name = "(alias)";
+  else if ((s.kind == Kind::kMatmul || s.kind == Kind::kConv2d) && !s.chain_ops.empty()) name = s.op + "+epilogue";
+  else name = s.op;
+  return name.c_str();
 }

@@ -63,6 +63,16 @@ class CompiledPlan:
         self.run_host_ptrs([a.ctypes.data for a in ins], [o.ctypes.data for o in outs], stream)
         return outs
 
+    def profile(self, in_ptrs: Sequence, out_ptrs: Sequence, stream=None):
+        """[(op name, milliseconds)] per step of one eager run."""
+        from ctypes import c_float
+        a = (c_void_p * max(1, len(in_ptrs)))(*[p.value if isinstance(p, c_void_p) else p for p in in_ptrs])
+        b = (c_void_p * max(1, len(out_ptrs)))(*[p.value if isinstance(p, c_void_p) else p for p in out_ptrs])
+        ms = (c_float * 4096)()
+        n = c_int(0)
+        capi.check(self.lib.fb200_plan_profile(self._h, a, b, stream, ms, 4096, byref(n)))
+        return [(self.lib.fb200_plan_step_op(self._h, i).decode(), float(ms[i])) for i in range(n.value)]
+
     def close(self):
         if self._h:
             self.lib.fb200_plan_destroy(self._h)

@@ -267,6 +267,15 @@ FB200_API int fb200_plan_run(fb200_plan* plan, const void* const* inputs, void* 
 FB200_API int fb200_plan_run_host(fb200_plan* plan, const void* const* host_inputs,
                                   void* const* host_outputs, fb200_stream stream);
 
+/* Per-step device times (ms) of one eager run, measured with CUDA events on `stream`; steps that
+ * launch nothing report 0.  For harness-side accounting of which kernel dominates a graph; has no
+ * counterpart in the reference (it has no profiling hooks).  Synchronises the stream. */
+FB200_API int fb200_plan_profile(fb200_plan* plan, const void* const* inputs, void* const* outputs,
+                                 fb200_stream stream, float* step_ms, int cap, int* n_steps);
+/* Op name of step `index` ("matmul+epilogue" when a following group was absorbed, "(absorbed)" /
+ * "(alias)" for steps folded away).  The pointer is valid until the calling thread's next call. */
+FB200_API const char* fb200_plan_step_op(const fb200_plan* plan, int index);
+
 #ifdef __cplusplus
 }
 #endif
