@@ -81,6 +81,11 @@ SIGNATURES = {
     "fb200_bias_add": (c_int, [_P, _P, _P, c_int64, c_int64, c_int, _P]),
     "fb200_matmul": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int, c_int,
                              POINTER(Epilogue), _P]),
+    "fb200_matmul_colsplit": (c_int, [_P, _P, _PP, c_int, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                      c_int, c_int, POINTER(Epilogue), _P]),
+    "fb200_ipc_export": (c_int, [c_int, _P, _P]),
+    "fb200_ipc_import": (c_int, [c_int, _P, _PP]),
+    "fb200_ipc_close": (c_int, [c_int, _P]),
     "fb200_matmul_uses_tensor_cores": (c_int, [c_int64, c_int64, c_int64, c_int, c_int]),
     "fb200_conv2d": (c_int, [_P, _P, _P, _P, POINTER(Conv2dParams), c_int, c_int,
                              POINTER(Epilogue), _P]),

@@ -23,6 +23,7 @@
 // Bound: tensor pipe.  FLOPs per launch = 2*M*N*K.
 #include <cuda.h>
 
+#include <cstring>
 #include <mutex>
 
 #include "common.cuh"
@@ -39,6 +40,18 @@ using namespace sm100;
 constexpr int kBlockM = 128;
 constexpr int kGemmThreads = 192;
 constexpr int kGroupM = 8;
+
+// Where a tile of the result goes: one or several destination matrices of row pitch `ld`, at
+// column offset `col0`.  One destination with ld == N, col0 == 0 is the ordinary matmul; several
+// destinations are this GPU's and its peers' copies of a column-split result (the all-gather is
+// fused into the epilogue as plain peer stores over NVLink).
+constexpr int kMaxDest = 8;
+struct GemmDest {
+  void* ptr[kMaxDest];
+  int n;
+  int64_t ld;
+  int64_t col0;
+};
 
 enum GemmFault : int {
   kFaultProducerEmpty = 101,
@@ -81,7 +94,7 @@ __device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64
 template <typename T, int ELT, int BLOCK_N>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                    const __grid_constant__ CUtensorMap tmap_b, T* __restrict__ C, int64_t M,
+                    const __grid_constant__ CUtensorMap tmap_b, GemmDest dest, int64_t M,
                     int64_t N, int64_t K, uint32_t idesc, EpilogueDev epi, int* status) {
   using Cfg = GemmCfg<ELT, BLOCK_N>;
   extern __shared__ uint8_t smem_raw[];
@@ -199,7 +212,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int acc = 0;
     uint32_t acc_phase = 0;
     constexpr int W = 16 / sizeof(T);
-    const bool vec_n = (N % W == 0) && ((reinterpret_cast<uintptr_t>(C) & 15u) == 0);
+    bool vec_n = (N % W == 0) && (dest.ld % W == 0) && (dest.col0 % W == 0);
+    for (int d = 0; d < dest.n; ++d) vec_n = vec_n && ((reinterpret_cast<uintptr_t>(dest.ptr[d]) & 15u) == 0);
     bool ok = true;
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
       int64_t tm, tn;
@@ -257,19 +271,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
               }
             }
           }
-          T* dst = C + idx0;
-          if (full_chunk) {
+          for (int d = 0; d < dest.n; ++d) {
+            T* dst = static_cast<T*>(dest.ptr[d]) + row * dest.ld + dest.col0 + col0;
+            if (full_chunk) {
 #pragma unroll
-            for (int q = 0; q < 32 / W; ++q) {
-              float o[W];
+              for (int q = 0; q < 32 / W; ++q) {
+                float o[W];
 #pragma unroll
-              for (int e = 0; e < W; ++e) o[e] = v[q * W + e];
-              store_vec<T>(dst + q * W, o);
-            }
-          } else {
+                for (int e = 0; e < W; ++e) o[e] = v[q * W + e];
+                store_vec<T>(dst + q * W, o);
+              }
+            } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (col0 + j < N) dst[j] = from_f32<T>(v[j]);
+              for (int j = 0; j < 32; ++j) {
+                if (col0 + j < N) dst[j] = from_f32<T>(v[j]);
+              }
             }
           }
         }
@@ -362,7 +378,7 @@ int device_status_word(int** dev_ptr) {
 }
 
 template <typename T, int ELT, int BLOCK_N>
-static int launch_tc(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
+static int launch_tc(const void* a, const void* b, const GemmDest& c, int64_t m, int64_t n, int64_t k,
                      int dtype, const EpilogueDev& epi, cudaStream_t s) {
   using Cfg = GemmCfg<ELT, BLOCK_N>;
   CUtensorMap ta, tb;
@@ -377,13 +393,13 @@ static int launch_tc(const void* a, const void* b, void* c, int64_t m, int64_t n
                                      static_cast<int>(Cfg::kSmemBytes)));
   const int64_t tiles = ((m + kBlockM - 1) / kBlockM) * ((n + BLOCK_N - 1) / BLOCK_N);
   const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
-  kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, static_cast<T*>(c), m, n, k, idesc,
+  kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, c, m, n, k, idesc,
                                                       epi, status);
   return after_launch("gemm_tcgen05_kernel");
 }
 
 template <typename T, int ELT>
-static int launch_tc_n(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
+static int launch_tc_n(const void* a, const void* b, const GemmDest& c, int64_t m, int64_t n, int64_t k,
                        int dtype, const EpilogueDev& epi, cudaStream_t s) {
   const int64_t tiles_m = (m + kBlockM - 1) / kBlockM;
   auto tiles = [&](int bn) { return tiles_m * ((n + bn - 1) / bn); };
@@ -433,10 +449,15 @@ extern "C" int fb200_matmul(const void* a, const void* b, void* c, int64_t m, in
   if (int rc = make_epilogue(epilogue, &epi, "matmul")) return rc;
   cudaStream_t s = as_stream(stream);
   if (k > 0 && tensor_core_eligible(a, b, c, m, n, k, dtype, allow_tf32)) {
+    GemmDest dest{};
+    dest.ptr[0] = c;
+    dest.n = 1;
+    dest.ld = n;
+    dest.col0 = 0;
     switch (dtype) {
-      case FB200_F32: return launch_tc_n<float, 4>(a, b, c, m, n, k, dtype, epi, s);
-      case FB200_BF16: return launch_tc_n<__nv_bfloat16, 2>(a, b, c, m, n, k, dtype, epi, s);
-      default: return launch_tc_n<__half, 2>(a, b, c, m, n, k, dtype, epi, s);
+      case FB200_F32: return launch_tc_n<float, 4>(a, b, dest, m, n, k, dtype, epi, s);
+      case FB200_BF16: return launch_tc_n<__nv_bfloat16, 2>(a, b, dest, m, n, k, dtype, epi, s);
+      default: return launch_tc_n<__half, 2>(a, b, dest, m, n, k, dtype, epi, s);
     }
   }
   return gemm_simt(a, b, c, m, n, k, dtype, epi, s);
@@ -452,5 +473,70 @@ extern "C" int fb200_kernel_status(int device, int* code) {
     *code = *reinterpret_cast<volatile int*>(g_status[device].host);
     *g_status[device].host = 0;
   }
+  return FB200_OK;
+}
+
+// Column-split matmul with the all-gather of C fused into the epilogue.  This rank multiplies A
+// [m,k] by its own column block of B (`b_local`, [k, n_local], contiguous) and stores
+// epilogue(A.B_local) into columns [col0, col0+n_local) of every destination matrix in `c_dest`
+// (row pitch n_total): its own copy of C and its peers' copies, mapped into this process with
+// fb200_ipc_import.  Peer stores are ordinary global stores that travel over NVLink; when every
+// rank has finished (stream synchronise + a host-side barrier) each GPU holds the whole C.
+// Epilogue operands are indexed in the local [m, n_local] layout.  Tensor-core shapes only.
+extern "C" int fb200_matmul_colsplit(const void* a, const void* b_local, void* const* c_dest,
+                                     int n_dest, int64_t m, int64_t n_local, int64_t n_total,
+                                     int64_t col0, int64_t k, int dtype, int allow_tf32,
+                                     const fb200_epilogue* epilogue, fb200_stream stream) {
+  if (c_dest == nullptr || n_dest < 1 || n_dest > kMaxDest) {
+    return set_error(FB200_INVALID_ARGUMENT, "matmul_colsplit: between 1 and %d destinations", kMaxDest);
+  }
+  if (m < 1 || n_local < 1 || k < 1 || col0 < 0 || col0 + n_local > n_total) {
+    return set_error(FB200_INVALID_ARGUMENT, "matmul_colsplit: invalid geometry");
+  }
+  if (!tensor_core_eligible(a, b_local, nullptr, m, n_local, k, dtype, allow_tf32)) {
+    return set_error(FB200_UNIMPLEMENTED,
+                     "matmul_colsplit: shape/dtype outside the tensor-core kernel (16-byte row pitches, "
+                     "bf16/f16, or fp32 with allow_tf32)");
+  }
+  EpilogueDev epi{};
+  if (int rc = make_epilogue(epilogue, &epi, "matmul_colsplit")) return rc;
+  GemmDest dest{};
+  for (int d = 0; d < n_dest; ++d) {
+    if (c_dest[d] == nullptr) return set_error(FB200_INVALID_ARGUMENT, "matmul_colsplit: destination %d is null", d);
+    dest.ptr[d] = c_dest[d];
+  }
+  dest.n = n_dest;
+  dest.ld = n_total;
+  dest.col0 = col0;
+  cudaStream_t s = as_stream(stream);
+  switch (dtype) {
+    case FB200_F32: return launch_tc_n<float, 4>(a, b_local, dest, m, n_local, k, dtype, epi, s);
+    case FB200_BF16: return launch_tc_n<__nv_bfloat16, 2>(a, b_local, dest, m, n_local, k, dtype, epi, s);
+    default: return launch_tc_n<__half, 2>(a, b_local, dest, m, n_local, k, dtype, epi, s);
+  }
+}
+
+// ---- peer memory plumbing for the column-split variant ------------------------------------------------
+extern "C" int fb200_ipc_export(int device, void* ptr, void* handle64) {
+  if (ptr == nullptr || handle64 == nullptr) return set_error(FB200_INVALID_ARGUMENT, "fb200_ipc_export: null argument");
+  FB200_CUDA_OK(cudaSetDevice(device));
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  FB200_CUDA_OK(cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(handle64), ptr));
+  return FB200_OK;
+}
+
+extern "C" int fb200_ipc_import(int device, const void* handle64, void** ptr) {
+  if (ptr == nullptr || handle64 == nullptr) return set_error(FB200_INVALID_ARGUMENT, "fb200_ipc_import: null argument");
+  FB200_CUDA_OK(cudaSetDevice(device));
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  FB200_CUDA_OK(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return FB200_OK;
+}
+
+extern "C" int fb200_ipc_close(int device, void* ptr) {
+  if (ptr == nullptr) return FB200_OK;
+  FB200_CUDA_OK(cudaSetDevice(device));
+  FB200_CUDA_OK(cudaIpcCloseMemHandle(ptr));
   return FB200_OK;
 }

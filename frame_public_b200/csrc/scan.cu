@@ -307,11 +307,14 @@ selective_scan_steps_kernel(const T* __restrict__ x, const T* __restrict__ a,
 }
 
 // ---- fused Mamba scan (new op) ----------------------------------------------------------------
-// One thread per (batch, channel); threads of a warp are consecutive channels, so u/delta/z/y
-// accesses are coalesced in the time-major [batch, len, dm] layout the GEMMs produce; B_t and
-// C_t (nstate values each) are warp-uniform broadcast loads.
+// Four lanes share one (batch, channel): each holds a quarter of the d_state-wide state in
+// registers, so a warp covers 8 channels and the grid has 4x the threads of a thread-per-channel
+// mapping (the recurrence is latency-bound on exp, not on HBM, until enough warps are resident).
+// u/delta/z/y are time-major [batch, len, dm]; B_t / C_t are 16-byte broadcast loads; the state sum
+// is finished with two shuffles.
 constexpr int kMambaThreads = 128;
-constexpr int kMaxState = 16;
+constexpr int kMambaLanes = 4;
+constexpr int kMambaChannelsPerCta = kMambaThreads / kMambaLanes;
 
 template <int NS>
 __global__ void __launch_bounds__(kMambaThreads)
@@ -319,45 +322,55 @@ mamba_scan_kernel(const float* __restrict__ u, const float* __restrict__ delta,
                   const float* __restrict__ A, const float* __restrict__ B,
                   const float* __restrict__ C, const float* __restrict__ D,
                   const float* __restrict__ z, float* __restrict__ y, int64_t len, int64_t dm) {
+  constexpr int PER = NS / kMambaLanes;  // states per lane
   const int64_t bidx = blockIdx.y;
-  const int64_t ch = static_cast<int64_t>(blockIdx.x) * kMambaThreads + threadIdx.x;
-  if (ch >= dm) return;
-  float h[NS], Ar[NS];
+  const int sg = threadIdx.x & (kMambaLanes - 1);
+  const int64_t ch_raw = static_cast<int64_t>(blockIdx.x) * kMambaChannelsPerCta + (threadIdx.x >> 2);
+  const bool live = ch_raw < dm;
+  const int64_t ch = live ? ch_raw : dm - 1;  // dead lanes shadow a valid channel and never store
+  float h[PER], Ar[PER];
 #pragma unroll
-  for (int n = 0; n < NS; ++n) { h[n] = 0.0f; Ar[n] = A[ch * NS + n]; }
+  for (int n = 0; n < PER; ++n) { h[n] = 0.0f; Ar[n] = A[ch * NS + sg * PER + n]; }
   const float Dd = D[ch];
   const float* up = u + bidx * len * dm + ch;
   const float* dp = delta + bidx * len * dm + ch;
   const float* zp = z != nullptr ? z + bidx * len * dm + ch : nullptr;
   float* yp = y + bidx * len * dm + ch;
-  const float* Bp = B + bidx * len * NS;
-  const float* Cp = C + bidx * len * NS;
+  const float* Bp = B + bidx * len * NS + sg * PER;
+  const float* Cp = C + bidx * len * NS + sg * PER;
   constexpr int U = 4;  // time steps whose loads are issued together
   for (int64_t t0 = 0; t0 < len; t0 += U) {
-    float uu[U], dd[U], zz[U];
+    float uu[U], dd[U], zz[U], bb[U][PER], cc[U][PER];
 #pragma unroll
     for (int j = 0; j < U; ++j) {
-      const int64_t t = t0 + j;
-      const bool ok = t < len;
-      uu[j] = ok ? up[t * dm] : 0.0f;
-      dd[j] = ok ? dp[t * dm] : 0.0f;
-      zz[j] = (ok && zp != nullptr) ? zp[t * dm] : 0.0f;
+      const int64_t t = t0 + j < len ? t0 + j : len - 1;
+      uu[j] = __ldg(up + t * dm);
+      dd[j] = __ldg(dp + t * dm);
+      zz[j] = zp != nullptr ? __ldg(zp + t * dm) : 0.0f;
+#pragma unroll
+      for (int n = 0; n < PER; ++n) {
+        bb[j][n] = __ldg(Bp + t * NS + n);
+        cc[j][n] = __ldg(Cp + t * NS + n);
+      }
     }
 #pragma unroll
     for (int j = 0; j < U; ++j) {
-      const int64_t t = t0 + j;
-      if (t < len) {
+      if (t0 + j < len) {   // uniform across the CTA
         float acc = 0.0f;
 #pragma unroll
-        for (int n = 0; n < NS; ++n) {
+        for (int n = 0; n < PER; ++n) {
           const float da = expf(dd[j] * Ar[n]);
-          const float db = dd[j] * __ldg(Bp + t * NS + n);
+          const float db = dd[j] * bb[j][n];
           h[n] = da * h[n] + db * uu[j];
-          acc = acc + __ldg(Cp + t * NS + n) * h[n];
+          acc = acc + cc[j][n] * h[n];
         }
-        float out = acc + Dd * uu[j];
-        if (zp != nullptr) out = out * (zz[j] * ew_sigmoid(zz[j]));
-        yp[t * dm] = out;
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        if (sg == 0 && live) {
+          float out = acc + Dd * uu[j];
+          if (zp != nullptr) out = out * (zz[j] * ew_sigmoid(zz[j]));
+          yp[(t0 + j) * dm] = out;
+        }
       }
     }
   }
@@ -445,7 +458,7 @@ extern "C" int fb200_mamba_scan(const void* u, const void* delta, const void* A,
   }
   if (batch > 65535) return set_error(FB200_INVALID_ARGUMENT, "mamba_scan: batch > 65535");
   cudaStream_t s = as_stream(stream);
-  dim3 grid(static_cast<unsigned>((dm + kMambaThreads - 1) / kMambaThreads),
+  dim3 grid(static_cast<unsigned>((dm + kMambaChannelsPerCta - 1) / kMambaChannelsPerCta),
             static_cast<unsigned>(batch));
   const float* up = static_cast<const float*>(u);
   const float* dp = static_cast<const float*>(delta);

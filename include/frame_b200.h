@@ -165,6 +165,22 @@ FB200_API int fb200_matmul(const void* a, const void* b, void* c, int64_t m, int
 FB200_API int fb200_matmul_uses_tensor_cores(int64_t m, int64_t n, int64_t k, int dtype,
                                              int allow_tf32);
 
+/* Column-split matmul with the all-gather of C fused into the epilogue (the optional multi-GPU
+ * variant of the GEMM config; the reference has no multi-GPU code at all).  This rank computes
+ * epilogue(A . B_local) for its column block [col0, col0+n_local) and stores it into that block of
+ * every matrix in c_dest (row pitch n_total): its own C and its peers' copies, imported with
+ * fb200_ipc_import.  Peer stores are plain global stores over NVLink; after a stream synchronise
+ * and a host-side barrier every GPU holds the whole C.  Epilogue operands use the local
+ * [m, n_local] layout. */
+FB200_API int fb200_matmul_colsplit(const void* a, const void* b_local, void* const* c_dest,
+                                    int n_dest, int64_t m, int64_t n_local, int64_t n_total,
+                                    int64_t col0, int64_t k, int dtype, int allow_tf32,
+                                    const fb200_epilogue* epilogue, fb200_stream stream);
+/* CUDA IPC handles (64 bytes) for device allocations, to map a peer process's buffer. */
+FB200_API int fb200_ipc_export(int device, void* ptr, void* handle64);
+FB200_API int fb200_ipc_import(int device, const void* handle64, void** ptr);
+FB200_API int fb200_ipc_close(int device, void* ptr);
+
 /* conv2d: NCHW cross-correlation with groups, stride, zero padding, optional [Cout] bias,
  * accumulation in fp32 (src/backends/cpu/kernels/conv.cpp:225-257; schema
  * src/ops/schemas/conv.cpp:979-989; replaces cudnnConvolutionForward,
