@@ -109,6 +109,42 @@ conv1d_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restr
   }
 }
 
+// Depthwise, stride 1 (groups == Cin == Cout, one tap row per channel): the Mamba causal conv.
+// One CTA walks 1024 consecutive outputs of one (batch, channel) row: no index division per
+// element, taps in registers, x reads coalesced and overlapping reads served by L1.  Same order
+// of operations as the generic kernel (bit-identical to the CPU reference).
+template <typename T, int MAXK>
+__global__ void __launch_bounds__(256)
+conv1d_depthwise_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ bias,
+                        T* __restrict__ out, int64_t rows, int64_t channels, int64_t l, int k,
+                        int64_t padding, int64_t ol, int64_t chunks) {
+  for (int64_t blk = blockIdx.x; blk < rows * chunks; blk += gridDim.x) {
+    const int64_t row = blk / chunks;
+    const int64_t chunk = blk - row * chunks;
+    const int64_t co = row % channels;
+    float taps[MAXK];
+#pragma unroll
+    for (int kk = 0; kk < MAXK; ++kk) taps[kk] = kk < k ? to_f32(w[co * k + kk]) : 0.0f;
+    const float bv = bias != nullptr ? to_f32(bias[co]) : 0.0f;
+    const T* xr = x + row * l;
+    T* orow = out + row * ol;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t o = chunk * 1024 + j * 256 + threadIdx.x;
+      if (o < ol) {
+        float acc = 0.0f;
+#pragma unroll
+        for (int kk = 0; kk < MAXK; ++kk) {
+          const int64_t il = o - padding + kk;
+          if (kk < k && il >= 0 && il < l) acc += to_f32(xr[il]) * taps[kk];
+        }
+        if (bias != nullptr) acc += bv;
+        orow[o] = from_f32<T>(acc);
+      }
+    }
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 max_pool2d_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t n, int64_t c, int64_t h,
@@ -233,6 +269,27 @@ extern "C" int fb200_conv1d(const void* x, const void* w, const void* bias, void
     return set_error(FB200_INVALID_ARGUMENT, "conv1d: null argument");
   }
   cudaStream_t s = as_stream(stream);
+  if (groups == cin && cout == cin && stride == 1 && k <= 8) {
+    const int64_t rows = n * cout;
+    const int64_t chunks = (ol + 1023) / 1024;
+    const int64_t blocks = rows * chunks;
+    const int dgrid = static_cast<int>(blocks < int64_t(kNumSMs) * 16 ? blocks : int64_t(kNumSMs) * 16);
+    switch (dtype) {
+      case FB200_F32:
+        conv1d_depthwise_kernel<float, 8><<<dgrid, 256, 0, s>>>(
+            static_cast<const float*>(x), static_cast<const float*>(w), static_cast<const float*>(bias),
+            static_cast<float*>(out), rows, cout, l, static_cast<int>(k), padding, ol, chunks);
+        return after_launch("conv1d_depthwise_kernel");
+      case FB200_BF16:
+        conv1d_depthwise_kernel<__nv_bfloat16, 8><<<dgrid, 256, 0, s>>>(
+            static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+            static_cast<const __nv_bfloat16*>(bias), static_cast<__nv_bfloat16*>(out), rows, cout, l,
+            static_cast<int>(k), padding, ol, chunks);
+        return after_launch("conv1d_depthwise_kernel");
+      default:
+        break;  // f16 and anything else: generic kernel below
+    }
+  }
   const int grid = grid_for(n * cout * ol, 256, 8);
   switch (dtype) {
     case FB200_F32:
