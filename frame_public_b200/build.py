@@ -29,7 +29,7 @@ COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hi
 NO_FMA = {"elementwise.cu", "rowops.cu", "scan.cu", "conv_pool.cu", "gemm_simt.cu", "shape_ops.cu"}
 
 SOURCES = ["runtime.cu", "elementwise.cu", "rowops.cu", "scan.cu", "shape_ops.cu", "conv_pool.cu",
-           "gemm_simt.cu", "gemm_tcgen05.cu", "conv_tcgen05.cu", "plan.cu"]
+           "gemm_simt.cu", "gemm_tcgen05.cu", "conv_tcgen05.cu", "plan.cu", "mamba_scan.cu"]
 
 
 def _headers_mtime() -> float:

@@ -17,8 +17,7 @@
 //    with a warp-shuffle inclusive scan, the carry moves to the next chunk through a register.
 //    The association differs from the CPU's, so this kernel is tolerance-exact, not bit-exact.
 //
-// mamba_scan is a NEW op with no reference counterpart: the SSM recurrence with dt, A, B, C, D
-// un-materialised and the d_state-wide state held in registers.
+// (The fused Mamba scan, a new op without a reference counterpart, lives in mamba_scan.cu.)
 #include "common.cuh"
 
 namespace fb200 {
@@ -306,81 +305,6 @@ selective_scan_steps_kernel(const T* __restrict__ x, const T* __restrict__ a,
   }
 }
 
-// ---- fused Mamba scan (new op) ----------------------------------------------------------------
-// Four lanes share one (batch, channel): each holds a quarter of the d_state-wide state in
-// registers, so a warp covers 8 channels and the grid has 4x the threads of a thread-per-channel
-// mapping (the recurrence is latency-bound on exp, not on HBM, until enough warps are resident).
-// u/delta/z/y are time-major [batch, len, dm]; B_t / C_t are 16-byte broadcast loads; the state sum
-// is finished with two shuffles.
-constexpr int kMambaThreads = 128;
-constexpr int kMambaLanes = 4;
-constexpr int kMambaChannelsPerCta = kMambaThreads / kMambaLanes;
-
-template <int NS>
-__global__ void __launch_bounds__(kMambaThreads)
-mamba_scan_kernel(const float* __restrict__ u, const float* __restrict__ delta,
-                  const float* __restrict__ A, const float* __restrict__ B,
-                  const float* __restrict__ C, const float* __restrict__ D,
-                  const float* __restrict__ z, float* __restrict__ y, int64_t len, int64_t dm) {
-  constexpr int PER = NS / kMambaLanes;  // states per lane
-  const int64_t bidx = blockIdx.y;
-  const int sg = threadIdx.x & (kMambaLanes - 1);
-  const int64_t ch_raw = static_cast<int64_t>(blockIdx.x) * kMambaChannelsPerCta + (threadIdx.x >> 2);
-  const bool live = ch_raw < dm;
-  const int64_t ch = live ? ch_raw : dm - 1;  // dead lanes shadow a valid channel and never store
-  float h[PER], Ar[PER];
-#pragma unroll
-  for (int n = 0; n < PER; ++n) {
-    h[n] = 0.0f;
-    // exp(dt*A) is evaluated as exp2(dt * (A*log2(e))): one multiply and one ex2 per state and step
-    // instead of a full-range expf (2 ulp; the recurrence contracts, so the error does not grow).
-    Ar[n] = A[ch * NS + sg * PER + n] * 1.4426950408889634f;
-  }
-  const float Dd = D[ch];
-  const float* up = u + bidx * len * dm + ch;
-  const float* dp = delta + bidx * len * dm + ch;
-  const float* zp = z != nullptr ? z + bidx * len * dm + ch : nullptr;
-  float* yp = y + bidx * len * dm + ch;
-  const float* Bp = B + bidx * len * NS + sg * PER;
-  const float* Cp = C + bidx * len * NS + sg * PER;
-  constexpr int U = 4;  // time steps whose loads are issued together
-  for (int64_t t0 = 0; t0 < len; t0 += U) {
-    float uu[U], dd[U], zz[U], bb[U][PER], cc[U][PER];
-#pragma unroll
-    for (int j = 0; j < U; ++j) {
-      const int64_t t = t0 + j < len ? t0 + j : len - 1;
-      uu[j] = __ldg(up + t * dm);
-      dd[j] = __ldg(dp + t * dm);
-      zz[j] = zp != nullptr ? __ldg(zp + t * dm) : 0.0f;
-#pragma unroll
-      for (int n = 0; n < PER; ++n) {
-        bb[j][n] = __ldg(Bp + t * NS + n);
-        cc[j][n] = __ldg(Cp + t * NS + n);
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < U; ++j) {
-      if (t0 + j < len) {   // uniform across the CTA
-        float acc = 0.0f;
-#pragma unroll
-        for (int n = 0; n < PER; ++n) {
-          const float da = exp2f(dd[j] * Ar[n]);
-          const float db = dd[j] * bb[j][n];
-          h[n] = da * h[n] + db * uu[j];
-          acc = acc + cc[j][n] * h[n];
-        }
-        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-        if (sg == 0 && live) {
-          float out = acc + Dd * uu[j];
-          if (zp != nullptr) out = out * (zz[j] * ew_sigmoid(zz[j]));
-          yp[(t0 + j) * dm] = out;
-        }
-      }
-    }
-  }
-}
-
 }  // namespace fb200
 
 using namespace fb200;
@@ -448,37 +372,3 @@ extern "C" int fb200_selective_scan(const void* x, const void* a, const void* b,
   }
 }
 
-extern "C" int fb200_mamba_scan(const void* u, const void* delta, const void* A, const void* B,
-                                const void* C, const void* D, const void* z, void* y,
-                                int64_t batch, int64_t len, int64_t dm, int64_t nstate,
-                                fb200_stream stream) {
-  if (batch < 0 || len < 0 || dm < 0) return set_error(FB200_INVALID_ARGUMENT, "mamba_scan: negative shape");
-  if (nstate != 16 && nstate != 8 && nstate != 4) {
-    return set_error(FB200_UNIMPLEMENTED, "mamba_scan: nstate must be 4, 8 or 16, got %lld",
-                     static_cast<long long>(nstate));
-  }
-  if (batch == 0 || len == 0 || dm == 0) return FB200_OK;
-  if (!u || !delta || !A || !B || !C || !D || !y) {
-    return set_error(FB200_INVALID_ARGUMENT, "mamba_scan: null argument");
-  }
-  if (batch > 65535) return set_error(FB200_INVALID_ARGUMENT, "mamba_scan: batch > 65535");
-  cudaStream_t s = as_stream(stream);
-  dim3 grid(static_cast<unsigned>((dm + kMambaChannelsPerCta - 1) / kMambaChannelsPerCta),
-            static_cast<unsigned>(batch));
-  const float* up = static_cast<const float*>(u);
-  const float* dp = static_cast<const float*>(delta);
-  const float* Ap = static_cast<const float*>(A);
-  const float* Bp = static_cast<const float*>(B);
-  const float* Cp = static_cast<const float*>(C);
-  const float* Dp = static_cast<const float*>(D);
-  const float* zp = static_cast<const float*>(z);
-  float* yp = static_cast<float*>(y);
-  if (nstate == 16) {
-    mamba_scan_kernel<16><<<grid, kMambaThreads, 0, s>>>(up, dp, Ap, Bp, Cp, Dp, zp, yp, len, dm);
-  } else if (nstate == 8) {
-    mamba_scan_kernel<8><<<grid, kMambaThreads, 0, s>>>(up, dp, Ap, Bp, Cp, Dp, zp, yp, len, dm);
-  } else {
-    mamba_scan_kernel<4><<<grid, kMambaThreads, 0, s>>>(up, dp, Ap, Bp, Cp, Dp, zp, yp, len, dm);
-  }
-  return after_launch("mamba_scan_kernel");
-}
