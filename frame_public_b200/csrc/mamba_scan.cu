@@ -50,36 +50,43 @@ mamba_scan_kernel(const float* __restrict__ u, const float* __restrict__ delta,
   float* yp = y + bidx * len * dm + ch;
   const float* Bp = B + bidx * len * NS + sg * PER;
   const float* Cp = C + bidx * len * NS + sg * PER;
-  for (int64_t t0 = 0; t0 < len; t0 += U) {
-    float uu[U], dd[U], bb[U][PER], cc[U][PER], da[U][PER];
+  // Software pipeline: the operands of the next four steps are in flight while the current four are
+  // computed (two register sets, loop unrolled by two).
+  struct Batch {
+    float uu[U], dd[U], bb[U][PER], cc[U][PER], zmine;
+  };
+  auto load = [&](int64_t t0, Batch& b) {
 #pragma unroll
     for (int j = 0; j < U; ++j) {
       const int64_t t = t0 + j < len ? t0 + j : len - 1;
-      uu[j] = __ldg(up + t * dm);
-      dd[j] = __ldg(dp + t * dm);
+      b.uu[j] = __ldg(up + t * dm);
+      b.dd[j] = __ldg(dp + t * dm);
 #pragma unroll
       for (int n = 0; n < PER; ++n) {
-        bb[j][n] = __ldg(Bp + t * NS + n);
-        cc[j][n] = __ldg(Cp + t * NS + n);
+        b.bb[j][n] = __ldg(Bp + t * NS + n);
+        b.cc[j][n] = __ldg(Cp + t * NS + n);
       }
     }
-    // this lane finishes step t0 + sg: fetch its gate and skip operands now
+    // this lane finishes step t0 + sg: its gate operand
     const int64_t tmine = t0 + sg < len ? t0 + sg : len - 1;
-    const float zmine = zp != nullptr ? __ldg(zp + tmine * dm) : 0.0f;
+    b.zmine = zp != nullptr ? __ldg(zp + tmine * dm) : 0.0f;
+  };
+  auto compute = [&](int64_t t0, const Batch& b) {
+    float da[U][PER];
 #pragma unroll
     for (int j = 0; j < U; ++j) {
 #pragma unroll
-      for (int n = 0; n < PER; ++n) da[j][n] = exp2f(dd[j] * Ar[n]);
+      for (int n = 0; n < PER; ++n) da[j][n] = exp2f(b.dd[j] * Ar[n]);
     }
     float acc[U];
 #pragma unroll
     for (int j = 0; j < U; ++j) {
-      const float du = dd[j] * uu[j];
+      const float du = b.dd[j] * b.uu[j];
       float a = 0.0f;
 #pragma unroll
       for (int n = 0; n < PER; ++n) {
-        h[n] = da[j][n] * h[n] + du * bb[j][n];
-        a = a + cc[j][n] * h[n];
+        h[n] = da[j][n] * h[n] + du * b.bb[j][n];
+        a = a + b.cc[j][n] * h[n];
       }
       acc[j] = a;
     }
@@ -89,16 +96,24 @@ mamba_scan_kernel(const float* __restrict__ u, const float* __restrict__ delta,
       acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 2);
     }
     // every lane now holds all four sums; lane sg finishes step t0 + sg
-    float mine = acc[0], umine = uu[0];
+    float mine = acc[0], umine = b.uu[0];
 #pragma unroll
     for (int j = 1; j < U; ++j) {
-      if (sg == j) { mine = acc[j]; umine = uu[j]; }
+      if (sg == j) { mine = acc[j]; umine = b.uu[j]; }
     }
     if (live && t0 + sg < len) {
       float out = mine + Dd * umine;
-      if (zp != nullptr) out = out * (zmine * ew_sigmoid(zmine));
+      if (zp != nullptr) out = out * (b.zmine * ew_sigmoid(b.zmine));
       yp[(t0 + sg) * dm] = out;
     }
+  };
+  Batch b0, b1;
+  load(0, b0);
+  for (int64_t t0 = 0; t0 < len; t0 += 2 * U) {
+    load(t0 + U, b1);
+    compute(t0, b0);
+    load(t0 + 2 * U, b0);
+    if (t0 + U < len) compute(t0 + U, b1);   // uniform across the CTA
   }
 }
 
