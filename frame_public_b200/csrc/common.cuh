@@ -116,10 +116,12 @@ __device__ __forceinline__ void store_vec(T* p, const float (&in)[16 / sizeof(T)
 // ---- elementwise op semantics (fp32 math) ----------------------------------------------------
 // Same formulas, in the same association, as the CPU reference lambdas; these files are
 // compiled with -fmad=false so that a*b+c is a rounded multiply followed by a rounded add.
+// sigmoid in the reference's two-branch stable form (1/(1+e^-x) for x >= 0, e^x/(1+e^x) below),
+// evaluated branch-free with e = exp(-|x|) through ex2.approx and an approximate division: about
+// 5e-7 relative, inside the fp32 tolerance tier (libm results are not bit-reproducible anyway).
 __device__ __forceinline__ float ew_sigmoid(float x) {
-  if (x >= 0.0f) return 1.0f / (1.0f + expf(-x));
-  const float e = expf(x);
-  return e / (1.0f + e);
+  const float e = __expf(-fabsf(x));
+  return __fdividef(x >= 0.0f ? 1.0f : e, 1.0f + e);
 }
 
 __device__ __forceinline__ float ew_unary(int op, float x) {
@@ -130,8 +132,11 @@ __device__ __forceinline__ float ew_unary(int op, float x) {
     case FB200_EW_TANH: return tanhf(x);
     case FB200_EW_RSQRT: return 1.0f / sqrtf(x);
     case FB200_EW_GELU: {
+      // 0.5*x*(1+tanh(t)) == x * e^{2t}/(e^{2t}+1): no cancellation for negative t; t is clamped
+      // where tanh(t) == 1 in fp32 so that e^{2t} stays finite.
       const float inner = 0.7978845608028654f * (x + 0.044715f * (x * x * x));
-      return 0.5f * x * (1.0f + tanhf(inner));
+      const float e2 = __expf(2.0f * fminf(inner, 15.0f));
+      return x * __fdividef(e2, e2 + 1.0f);
     }
     case FB200_EW_SILU: return x * ew_sigmoid(x);
     case FB200_EW_SOFTPLUS: return x > 20.0f ? x : log1pf(expf(x));

@@ -145,28 +145,27 @@ conv1d_depthwise_kernel(const T* __restrict__ x, const T* __restrict__ w, const 
   }
 }
 
-template <typename T>
+// IDX = int for tensors below 2^31 elements (no 64-bit divisions on the hot path), else int64_t.
+template <typename T, typename IDX>
 __global__ void __launch_bounds__(256)
-max_pool2d_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t n, int64_t c, int64_t h,
-                  int64_t w, int64_t kh, int64_t kw, int64_t sh, int64_t sw, int64_t ph,
-                  int64_t pw, int64_t oh, int64_t ow) {
-  const int64_t total = n * c * oh * ow;
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
-       i += stride) {
-    const int64_t q = i % ow;
-    int64_t rem = i / ow;
-    const int64_t o = rem % oh;
-    rem /= oh;  // rem = n*c index
-    const T* xc = x + rem * h * w;
+max_pool2d_kernel(const T* __restrict__ x, T* __restrict__ out, IDX nc, IDX h, IDX w, IDX kh, IDX kw,
+                  IDX sh, IDX sw, IDX ph, IDX pw, IDX oh, IDX ow) {
+  const IDX total = nc * oh * ow;
+  const IDX stride = static_cast<IDX>(gridDim.x) * blockDim.x;
+  for (IDX i = static_cast<IDX>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const IDX q = i % ow;
+    IDX rem = i / ow;
+    const IDX o = rem % oh;
+    rem /= oh;  // (n, c) plane
+    const T* xc = x + static_cast<int64_t>(rem) * h * w;
     bool found = false;
     float best = 0.0f;
     T best_raw = T{};
-    for (int64_t a = 0; a < kh; ++a) {
-      const int64_t ih = o * sh - ph + a;
+    for (IDX a = 0; a < kh; ++a) {
+      const IDX ih = o * sh - ph + a;
       if (ih < 0 || ih >= h) continue;
-      for (int64_t b = 0; b < kw; ++b) {
-        const int64_t iw = q * sw - pw + b;
+      for (IDX b = 0; b < kw; ++b) {
+        const IDX iw = q * sw - pw + b;
         if (iw < 0 || iw >= w) continue;
         const T raw = xc[ih * w + iw];
         const float v = to_f32(raw);
@@ -339,22 +338,25 @@ extern "C" int fb200_max_pool2d(const void* x, void* out, int64_t n, int64_t c, 
   if (x == nullptr || out == nullptr) return set_error(FB200_INVALID_ARGUMENT, "max_pool2d: null argument");
   cudaStream_t s = as_stream(stream);
   const int grid = grid_for(n * c * oh * ow, 256, 8);
+  const bool small = n * c * h * w < (int64_t(1) << 31);
+  auto run = [&](auto tag) {
+    using T = decltype(tag);
+    if (small) {
+      max_pool2d_kernel<T, int><<<grid, 256, 0, s>>>(
+          static_cast<const T*>(x), static_cast<T*>(out), static_cast<int>(n * c), static_cast<int>(h),
+          static_cast<int>(w), static_cast<int>(kh), static_cast<int>(kw), static_cast<int>(stride_h),
+          static_cast<int>(stride_w), static_cast<int>(pad_h), static_cast<int>(pad_w),
+          static_cast<int>(oh), static_cast<int>(ow));
+    } else {
+      max_pool2d_kernel<T, int64_t><<<grid, 256, 0, s>>>(static_cast<const T*>(x), static_cast<T*>(out),
+                                                         n * c, h, w, kh, kw, stride_h, stride_w, pad_h,
+                                                         pad_w, oh, ow);
+    }
+  };
   switch (dtype) {
-    case FB200_F32:
-      max_pool2d_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(x),
-                                                    static_cast<float*>(out), n, c, h, w, kh, kw,
-                                                    stride_h, stride_w, pad_h, pad_w, oh, ow);
-      break;
-    case FB200_BF16:
-      max_pool2d_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(
-          static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(out), n, c, h, w, kh,
-          kw, stride_h, stride_w, pad_h, pad_w, oh, ow);
-      break;
-    case FB200_F16:
-      max_pool2d_kernel<__half><<<grid, 256, 0, s>>>(static_cast<const __half*>(x),
-                                                     static_cast<__half*>(out), n, c, h, w, kh, kw,
-                                                     stride_h, stride_w, pad_h, pad_w, oh, ow);
-      break;
+    case FB200_F32: run(float{}); break;
+    case FB200_BF16: run(__nv_bfloat16{}); break;
+    case FB200_F16: run(__half{}); break;
     default:
       return set_error(FB200_INVALID_ARGUMENT,
                        "max_pool2d: dtype code %d is not float32/float16/bfloat16", dtype);

@@ -307,6 +307,15 @@ selective_scan_steps_kernel(const T* __restrict__ x, const T* __restrict__ a,
 
 }  // namespace fb200
 
+namespace fb200 {
+// scan_chunked.cu
+int64_t scan_chunking(int64_t rows, int64_t steps, int elems_per_vec, int64_t* chunk_len);
+template <typename T>
+int scan_chunked_launch(const void* x, const void* a, const void* b, const void* c, const void* d,
+                        void* out, int64_t rows, int64_t steps, int64_t chunks, int64_t chunk_len,
+                        float2* scratch, cudaStream_t s);
+}  // namespace fb200
+
 using namespace fb200;
 
 template <typename T>
@@ -324,6 +333,18 @@ static int launch_scan(const void* x, const void* a, const void* b, const void* 
   // Few long rows: parallelise along time.  Needs whole 128-bit vectors per row.
   const int64_t row_groups = (rows + 31) / 32;
   if (al && row_groups < 2 * kNumSMs && steps >= 8 * 32 * W) {
+    // Fewer rows than the GPU has warps: cut the time axis into chunks (two passes and a scratch
+    // array of one affine pair per (row, chunk), taken from the stream-ordered allocator).
+    int64_t chunk_len = steps;
+    const int64_t chunks = rows < kNumSMs * 8 ? scan_chunking(rows, steps, W, &chunk_len) : 1;
+    if (chunks >= 2) {
+      float2* scratch = nullptr;
+      FB200_CUDA_OK(cudaMallocAsync(reinterpret_cast<void**>(&scratch),
+                                    static_cast<size_t>(rows * chunks) * sizeof(float2), s));
+      const int rc = scan_chunked_launch<T>(x, a, b, c, d, out, rows, steps, chunks, chunk_len, scratch, s);
+      FB200_CUDA_OK(cudaFreeAsync(scratch, s));
+      return rc;
+    }
     const int grid = grid_for(rows * 32, kScanThreads, 8);
     selective_scan_steps_kernel<T><<<grid, kScanThreads, 0, s>>>(xp, ap, bp, cp, dp, op, rows, steps);
     return after_launch("selective_scan_steps_kernel");
