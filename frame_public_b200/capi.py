@@ -94,6 +94,7 @@ SIGNATURES = {
     "fb200_softmax": (c_int, [_P, _P, c_int64, c_int64, c_int, _P]),
     "fb200_layer_norm": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_double, c_int, _P]),
     "fb200_selective_scan": (c_int, [_P] * 6 + [c_int64, c_int64, c_int, _P]),
+    "fb200_selective_scan_noalloc": (c_int, [_P] * 6 + [c_int64, c_int64, c_int, _P]),
     "fb200_mamba_scan": (c_int, [_P] * 8 + [c_int64] * 4 + [_P]),
     "fb200_transpose": (c_int, [_P, _P, c_int, _I64P, _I64P, c_int, _P]),
     "fb200_slice": (c_int, [_P, _P, c_int, _I64P, c_int64, c_int64, c_int64, c_int, _P]),

@@ -13,6 +13,8 @@
 // sequential order: results agree within the fp32 / bf16 tolerance tier, not bit for bit.
 // The scratch (8 bytes per (row, chunk)) is global memory beyond the op's inputs and outputs; the
 // regular entry point takes it from the stream-ordered allocator.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace fb200 {
@@ -181,3 +183,84 @@ template int scan_chunked_launch<__half>(const void*, const void*, const void*, 
                                          void*, int64_t, int64_t, int64_t, int64_t, float2*, cudaStream_t);
 
 }  // namespace fb200
+
+// ---- the same scan without any allocation ----------------------------------------------------------
+// Some callers may not allocate device memory when they run this op: a host that captures its work
+// into a CUDA graph, or one that sized every device buffer up front (Frame's memory planner does
+// exactly that for a compiled graph) and treats a run-time allocation as a bug.  For them the
+// scratch of the two-pass scan lives in this fixed array instead of coming from the stream-ordered
+// allocator.  It is part of the library image: every GPU that loads the library carries these
+// 512 KiB until the process exits.
+namespace fb200 {
+
+constexpr int64_t kStaticScanPairs = 65536;  // (row, chunk) pairs the fixed scratch can hold
+static __device__ __align__(256) float2 g_static_scan_scratch[kStaticScanPairs];
+
+// In host code the name above is only a handle for the symbol, not a device address; the address
+// each device gave the array is looked up once per device and kept here.
+static float2* g_static_scan_ptr[64] = {nullptr};
+static std::mutex g_static_scan_mu;
+
+static int static_scan_scratch(float2** ptr) {
+  int device = 0;
+  FB200_CUDA_OK(cudaGetDevice(&device));
+  if (device < 0 || device >= 64) return set_error(FB200_INVALID_ARGUMENT, "device index %d", device);
+  std::lock_guard<std::mutex> lock(g_static_scan_mu);
+  if (g_static_scan_ptr[device] == nullptr) {
+    float2* p = nullptr;
+    FB200_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_scan_scratch));
+    g_static_scan_ptr[device] = p;
+  }
+  *ptr = g_static_scan_ptr[device];
+  return FB200_OK;
+}
+
+}  // namespace fb200
+
+using namespace fb200;
+
+extern "C" int fb200_selective_scan_noalloc(const void* x, const void* a, const void* b,
+                                            const void* c, const void* d, void* out, int64_t rows,
+                                            int64_t steps, int dtype, fb200_stream stream) {
+  if (rows < 0) return set_error(FB200_INVALID_ARGUMENT, "selective_scan_noalloc: negative rows");
+  if (steps < 1) {
+    return set_error(FB200_INVALID_ARGUMENT,
+                     "selective_scan_noalloc: the last dimension (steps) must be >= 1, got %lld",
+                     static_cast<long long>(steps));
+  }
+  if (rows == 0) return FB200_OK;
+  if (!x || !a || !b || !c || !d || !out) {
+    return set_error(FB200_INVALID_ARGUMENT, "selective_scan_noalloc: null argument");
+  }
+  if (dtype != FB200_F32 && dtype != FB200_BF16 && dtype != FB200_F16) {
+    return set_error(FB200_INVALID_ARGUMENT,
+                     "selective_scan_noalloc: dtype code %d is not float32/float16/bfloat16", dtype);
+  }
+  const int w = 16 / itemsize_of(dtype);
+  if (steps % w != 0 || !aligned16(x) || !aligned16(a) || !aligned16(b) || !aligned16(c) ||
+      !aligned16(d) || !aligned16(out)) {
+    return set_error(FB200_INVALID_ARGUMENT,
+                     "selective_scan_noalloc: needs 16-byte aligned operands and steps a multiple of %d", w);
+  }
+  if (rows > kStaticScanPairs) {
+    return set_error(FB200_INVALID_ARGUMENT,
+                     "selective_scan_noalloc: %lld rows exceed the fixed scratch of %lld (row, chunk) "
+                     "pairs; use fb200_selective_scan",
+                     static_cast<long long>(rows), static_cast<long long>(kStaticScanPairs));
+  }
+  int64_t chunk_len = steps;
+  int64_t chunks = scan_chunking(rows, steps, w, &chunk_len);
+  const int64_t pass = 32 * static_cast<int64_t>(w);
+  while (rows * chunks > kStaticScanPairs) {   // fewer, longer chunks until the pairs fit
+    chunk_len = (chunk_len * 2 + pass - 1) / pass * pass;
+    chunks = (steps + chunk_len - 1) / chunk_len;
+  }
+  float2* scratch = nullptr;
+  if (int rc = static_scan_scratch(&scratch)) return rc;
+  cudaStream_t s = as_stream(stream);
+  switch (dtype) {
+    case FB200_F32: return scan_chunked_launch<float>(x, a, b, c, d, out, rows, steps, chunks, chunk_len, scratch, s);
+    case FB200_BF16: return scan_chunked_launch<__nv_bfloat16>(x, a, b, c, d, out, rows, steps, chunks, chunk_len, scratch, s);
+    default: return scan_chunked_launch<__half>(x, a, b, c, d, out, rows, steps, chunks, chunk_len, scratch, s);
+  }
+}

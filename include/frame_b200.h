@@ -223,6 +223,20 @@ FB200_API int fb200_layer_norm(const void* x, const void* gamma, const void* bet
 FB200_API int fb200_selective_scan(const void* x, const void* a, const void* b, const void* c,
                                    const void* d, void* out, int64_t rows, int64_t steps,
                                    int dtype, fb200_stream stream);
+/* selective_scan that allocates nothing (no counterpart in the reference: its CUDA path allocates
+ * scratch with cudaMalloc on every call, src/backends/cuda/kernels/sequence.cu:173-186).  For hosts
+ * that must not allocate device memory while the op runs — work being captured into a CUDA graph, or
+ * a process that planned all of its device memory up front.  Same results as fb200_selective_scan's
+ * chunked two-pass path; its scratch is a fixed 512 KiB array inside the library image (held by
+ * every GPU that loads the library until the process exits), good for rows <= 65536; more rows are
+ * rejected with FB200_INVALID_ARGUMENT.  Needs 16-byte aligned operands and steps a multiple of the
+ * 128-bit vector width.  The first call on a device looks up the array's address on that device
+ * (make that call before starting a stream capture, with the device current).  All calls share
+ * the one array (every entry is rewritten by a call before it is read, nothing needs clearing), so
+ * two calls that overlap on the GPU — different streams, or graphs replayed concurrently — race. */
+FB200_API int fb200_selective_scan_noalloc(const void* x, const void* a, const void* b,
+                                           const void* c, const void* d, void* out, int64_t rows,
+                                           int64_t steps, int dtype, fb200_stream stream);
 /* NEW op (no reference counterpart): the Mamba SSM scan with un-materialised operands, fp32.
  * u, delta, z, y: [batch, len, dm]; A: [dm, nstate]; B, C: [batch, len, nstate]; D: [dm];
  * z may be NULL.  h[n] = exp(delta*A[d,n])*h[n] + delta*B[n]*u; y = sum_n C[n]*h[n] + D[d]*u;
