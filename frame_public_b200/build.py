@@ -29,7 +29,8 @@ COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hi
 NO_FMA = {"elementwise.cu", "rowops.cu", "scan.cu", "scan_chunked.cu", "conv_pool.cu", "gemm_simt.cu", "shape_ops.cu"}
 
 SOURCES = ["runtime.cu", "elementwise.cu", "rowops.cu", "scan.cu", "shape_ops.cu", "conv_pool.cu",
-           "gemm_simt.cu", "gemm_tcgen05.cu", "conv_tcgen05.cu", "plan.cu", "mamba_scan.cu", "scan_chunked.cu"]
+           "gemm_simt.cu", "gemm_tcgen05.cu", "conv_tcgen05.cu", "plan.cu", "mamba_scan.cu", "scan_chunked.cu",
+           "attention_tcgen05.cu"]
 
 
 def _headers_mtime() -> float:

@@ -95,6 +95,9 @@ SIGNATURES = {
     "fb200_layer_norm": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_double, c_int, _P]),
     "fb200_selective_scan": (c_int, [_P] * 6 + [c_int64, c_int64, c_int, _P]),
     "fb200_selective_scan_noalloc": (c_int, [_P] * 6 + [c_int64, c_int64, c_int, _P]),
+    "fb200_attention_fan_supported": (c_int, [c_int64, c_int64, c_int64, c_int]),
+    "fb200_attention_fan": (c_int, [_P, c_int64, c_int64, _P, c_int64, c_int64, _P, c_int64, c_int64, _P,
+                                    c_int64, _P, c_int64, c_int64, c_int64, c_int64, c_int, _P]),
     "fb200_mamba_scan": (c_int, [_P] * 8 + [c_int64] * 4 + [_P]),
     "fb200_transpose": (c_int, [_P, _P, c_int, _I64P, _I64P, c_int, _P]),
     "fb200_slice": (c_int, [_P, _P, c_int, _I64P, c_int64, c_int64, c_int64, c_int, _P]),
@@ -262,6 +265,17 @@ def selective_scan(x, a, b, c, d, out, rows, steps, dtype, stream=None):
 
 def mamba_scan(u, delta, A, B, C, D, z, y, batch, length, dm, nstate, stream=None):
     check(load().fb200_mamba_scan(u, delta, A, B, C, D, z, y, batch, length, dm, nstate, stream))
+
+
+HEAD_DTYPE = np.dtype([("q_row", "<i4"), ("q_col", "<i4"), ("k_row", "<i4"), ("k_col", "<i4"),
+                       ("v_row", "<i4"), ("v_col", "<i4"), ("o_offset", "<i8")])
+
+
+def attention_fan(q, q_rows, q_ld, k, k_rows, k_ld, v, v_rows, v_ld, o, o_ld, heads_dev, n_heads,
+                  sq, sk, head_dim, dtype, stream=None):
+    """heads_dev: device pointer of an array of HEAD_DTYPE records (fb200_attention_head)."""
+    check(load().fb200_attention_fan(q, q_rows, q_ld, k, k_rows, k_ld, v, v_rows, v_ld, o, o_ld,
+                                     heads_dev, n_heads, sq, sk, head_dim, dtype, stream))
 
 
 def transpose(x, out, dims, perm, itemsize, stream=None):

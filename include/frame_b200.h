@@ -237,6 +237,28 @@ FB200_API int fb200_selective_scan(const void* x, const void* a, const void* b, 
 FB200_API int fb200_selective_scan_noalloc(const void* x, const void* a, const void* b,
                                            const void* c, const void* d, void* out, int64_t rows,
                                            int64_t steps, int dtype, fb200_stream stream);
+/* A fan of per-head attention chains in one launch.  Stands behind the per-(batch, head) node
+ * groups `matmul(q, transpose(k)) -> softmax -> matmul(p, v)` that the reference builds in
+ * nn::MultiHeadAttention (src/nn/layers.cpp:950-1170) and runs node by node
+ * (src/backends/cuda/cuda_executable.cpp:84-118); each of the three results is rounded to the
+ * storage dtype exactly where the separate operators would round it.  For head h:
+ *   Q_h = sq x 64 window of q_base (row-major, q_rows x q_ld) at (q_row, q_col); K_h, V_h likewise
+ *   with sk rows; O_h (sq x 64, row pitch o_ld) is written at element offset o_offset of o_base.
+ * Column coordinates must be multiples of 8 elements (a table entry that is not is refused by
+ * the kernel, which records status 305).  `heads_dev` is a DEVICE array owned by the caller.
+ * Supported: bfloat16 / float16, head_dim 64, 64 <= sk <= 512 in multiples of 64, any sq >= 1
+ * (fb200_attention_fan_supported tells); anything else returns FB200_UNIMPLEMENTED. */
+typedef struct fb200_attention_head {
+  int32_t q_row, q_col, k_row, k_col, v_row, v_col;
+  int64_t o_offset;
+} fb200_attention_head;
+FB200_API int fb200_attention_fan_supported(int64_t sq, int64_t sk, int64_t head_dim, int dtype);
+FB200_API int fb200_attention_fan(const void* q_base, int64_t q_rows, int64_t q_ld,
+                                  const void* k_base, int64_t k_rows, int64_t k_ld,
+                                  const void* v_base, int64_t v_rows, int64_t v_ld, void* o_base,
+                                  int64_t o_ld, const fb200_attention_head* heads_dev,
+                                  int64_t n_heads, int64_t sq, int64_t sk, int64_t head_dim,
+                                  int dtype, fb200_stream stream);
 /* NEW op (no reference counterpart): the Mamba SSM scan with un-materialised operands, fp32.
  * u, delta, z, y: [batch, len, dm]; A: [dm, nstate]; B, C: [batch, len, nstate]; D: [dm];
  * z may be NULL.  h[n] = exp(delta*A[d,n])*h[n] + delta*B[n]*u; y = sum_n C[n]*h[n] + D[d]*u;

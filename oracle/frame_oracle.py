@@ -489,6 +489,15 @@ TOL = {DT_F32: (1e-5, 1e-6), DT_F16: (1e-2, 1e-3), DT_BF16: (2e-2, 2e-3)}
 TOL_TF32 = (1e-3, 1e-4)
 
 
+def attention_fan(q, k, v, dtype: int = DT_BF16):
+    """One head of the attention fan as the three reference operators in a row, each rounding
+    its result to the storage dtype: matmul(q, k^T) (src/backends/cpu/kernels/matmul.cpp:92-131),
+    softmax over rows (src/backends/cpu/kernels/sequence.cpp:114-174), matmul(p, v).  q: [sq, d],
+    k, v: [sk, d], all in storage form."""
+    kt = np.ascontiguousarray(k.T)
+    return matmul(softmax(matmul(q, kt, dtype), dtype), v, dtype)
+
+
 def all_close(actual, expected, dtype: int = DT_F32, rtol=None, atol=None):
     """|a-e| <= atol + rtol*|e| elementwise; NaN/inf never compare equal unless bit-equal
     in class (the reference's helper rejects them; here inf==inf of the same sign passes)."""
