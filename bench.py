@@ -352,6 +352,8 @@ def run_ours(args):
     dom_index = max(range(len(prof)), key=lambda i: prof[i][1])
     dom_op, dom_ms = prof[dom_index]
     d_flops, d_bytes = plantext.step_work(ptext, dom_index)
+    if dom_op == "attention_fan":   # one launch standing for every per-head chain of the plan
+        d_flops, d_bytes = plantext.attention_fan_work(ptext)
     step_total = sum(ms for _, ms in prof)
     if d_flops > 0 and (wl.arith != "f32"):
         bound = "tensor"
@@ -374,7 +376,7 @@ def run_ours(args):
                 "kernel_share_of_step": round(dom_ms / step_total, 3) if step_total else None,
                 "peak_source": peak_note,
                 "steps_ms": {f"{i}:{op}": round(ms, 4) for i, (op, ms) in enumerate(prof) if ms > 0}
-                if len(prof) <= 40 else None}
+                if sum(1 for _, ms in prof if ms > 0) <= 40 else None}
 
     # ---- reference CPU backend on a bounded slab (rank 0, N=1 only) -------------------------------------
     cpu_baseline = None

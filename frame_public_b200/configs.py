@@ -257,5 +257,7 @@ def small_workloads(backend: str = "cpu") -> List[Workload]:
         gemm_epilogue(n=64, m=48, dtype=F32, broadcast_bias=True, backend=backend),
         conv_stack(batch=2, hw=32, backend=backend),
         transformer_block(batch=2, seq=32, d_model=64, heads=2, ffn=128, backend=backend),
+        # head_dim 64 and 128 keys: the shape the fused attention launch accepts
+        transformer_block(batch=2, seq=128, d_model=128, heads=2, ffn=256, backend=backend),
         mamba_block(batch=2, seq=24, d_model=16, d_state=16, dt_rank=4, backend=backend),
     ]

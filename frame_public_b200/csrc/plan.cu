@@ -15,6 +15,7 @@
 // alias when no later step can overwrite the aliased bytes.  Per run: one loop of launches on
 // the caller's stream, graph outputs written straight into the caller's buffers, no allocation,
 // no synchronisation.
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -28,7 +29,7 @@ namespace fb200 {
 
 enum class Kind {
   kMatmul, kConv2d, kConv1d, kMaxPool, kChain, kBiasAdd, kSoftmax, kLayerNorm, kScan, kMambaScan,
-  kTranspose, kSlice, kConcat, kSum, kCopy, kAlias, kConstant, kSkip
+  kTranspose, kSlice, kConcat, kSum, kCopy, kAlias, kConstant, kSkip, kAttentionFan
 };
 
 struct SlotInfo {
@@ -59,6 +60,11 @@ struct Step {
   int write_slot = -1;                       // where the (possibly fused) result goes
   std::vector<int64_t> iv;                   // op-specific integers
   double eps = 0.0;
+  // kAttentionFan: the matrices the heads' q/k/v windows lie in, where the results go, and the
+  // device table of per-head coordinates
+  int fan_q = -1, fan_k = -1, fan_v = -1, fan_dest = -1;
+  int64_t fan_heads = 0, fan_sq = 0, fan_sk = 0;
+  void* fan_table = nullptr;
 };
 
 }  // namespace fb200
@@ -496,6 +502,248 @@ static void optimise(fb200_plan* p) {
   }
 }
 
+
+// ---- attention-fan recognition ------------------------------------------------------------------
+// A window of a rank-2 matrix reached through a chain of `slice` steps.
+struct Window { int base; int64_t row, col; };
+
+static Window resolve_window(const fb200_plan& p, const std::vector<int>& producer, int slot) {
+  Window w{slot, 0, 0};
+  for (;;) {
+    const int j = producer[static_cast<size_t>(w.base)];
+    if (j < 0) break;
+    const Step& s = p.steps[static_cast<size_t>(j)];
+    if (s.kind != Kind::kSlice || s.in.size() != 1) break;
+    const SlotInfo& src = p.slots[static_cast<size_t>(s.in[0])];
+    if (src.dims.size() != 2 || s.iv[1] < 0) break;
+    if (s.iv[0] == 0) w.row += s.iv[1]; else w.col += s.iv[1];
+    w.base = s.in[0];
+  }
+  return w;
+}
+
+// Live steps that read `slot` (directly, through an alias, or as an epilogue operand).
+static std::vector<std::pair<int, int>> readers_of(const fb200_plan& p, int slot) {
+  std::vector<std::pair<int, int>> out;
+  const int root = root_slot(p, slot);
+  for (size_t j = 0; j < p.steps.size(); ++j) {
+    const Step& s = p.steps[j];
+    if (s.kind == Kind::kSkip) continue;
+    for (size_t i = 0; i < s.in.size(); ++i) {
+      if (root_slot(p, s.in[i]) == root) out.emplace_back(static_cast<int>(j), static_cast<int>(i));
+    }
+    for (int e : s.epi_operand_slot) if (e >= 0 && root_slot(p, e) == root) out.emplace_back(static_cast<int>(j), -1);
+  }
+  return out;
+}
+
+struct FanHead {
+  int transpose, scores, softmax, values;   // step indices
+  Window q, k, v;
+  int dest;                                 // slot the result finally lands in
+  int64_t dest_row, dest_col;
+  std::vector<std::pair<int, int>> path;    // (concat step, input index) from the head outwards
+};
+
+// Finds groups of `matmul(q, transpose(k)) -> softmax -> matmul(p, v)` chains whose operands are
+// windows of common matrices and whose results are concatenated into one matrix, and replaces each
+// group by ONE attention_fan launch at the position of its last step.  The windows are read in
+// place and the results are written straight into the concatenated matrix, so the slices,
+// transposes and concats of the group are not executed at all.  Because that moves reads and
+// writes in time relative to what the memory planner assumed, the group is only formed when
+//  (1) no step that still runs between the producer of a source matrix and the launch writes
+//      bytes overlapping that matrix,
+//  (2) no step that still runs between the launch and the (skipped) outermost concat touches bytes
+//      overlapping the destination, and every reader of the destination comes after the launch,
+//  (3) every concat on the way is fed only by heads of the group (or by such concats).
+// Anything else keeps the step-by-step path.
+static void fuse_attention_fans(fb200_plan* p) {
+  const int n = static_cast<int>(p->steps.size());
+  std::vector<int> producer(p->slots.size(), -1);
+  for (int i = 0; i < n; ++i) {
+    for (int o : p->steps[static_cast<size_t>(i)].out) producer[static_cast<size_t>(o)] = i;
+  }
+  auto sole_reader = [&](int slot, int* step, int* index) {
+    if (p->slots[static_cast<size_t>(slot)].output_index >= 0) return false;
+    const auto r = readers_of(*p, slot);
+    if (r.size() != 1 || r[0].second < 0) return false;
+    *step = r[0].first;
+    *index = r[0].second;
+    return true;
+  };
+  std::vector<FanHead> heads;
+  for (int i = 0; i < n; ++i) {
+    const Step& sm = p->steps[static_cast<size_t>(i)];
+    if (sm.kind != Kind::kSoftmax || sm.in.size() != 1 || sm.out.size() != 1) continue;
+    FanHead h{};
+    h.softmax = i;
+    h.scores = producer[static_cast<size_t>(sm.in[0])];
+    if (h.scores < 0) continue;
+    const Step& m1 = p->steps[static_cast<size_t>(h.scores)];
+    if (m1.kind != Kind::kMatmul || !m1.chain_ops.empty() || m1.write_slot != m1.out[0] || m1.in.size() != 2) continue;
+    int step = -1, index = -1;
+    if (!sole_reader(m1.out[0], &step, &index) || step != i) continue;
+    h.transpose = producer[static_cast<size_t>(m1.in[1])];
+    if (h.transpose < 0) continue;
+    const Step& tr = p->steps[static_cast<size_t>(h.transpose)];
+    if (tr.kind != Kind::kTranspose || tr.iv.size() != 2 || tr.iv[0] != 1 || tr.iv[1] != 0) continue;
+    if (!sole_reader(tr.out[0], &step, &index) || step != h.scores) continue;
+    if (!sole_reader(sm.out[0], &step, &index) || index != 0) continue;
+    h.values = step;
+    const Step& m2 = p->steps[static_cast<size_t>(h.values)];
+    if (m2.kind != Kind::kMatmul || !m2.chain_ops.empty() || m2.write_slot != m2.out[0] || m2.in.size() != 2) continue;
+    const SlotInfo& qs = p->slots[static_cast<size_t>(m1.in[0])];
+    const SlotInfo& ks = p->slots[static_cast<size_t>(tr.in[0])];
+    const SlotInfo& vs = p->slots[static_cast<size_t>(m2.in[1])];
+    if (qs.dims.size() != 2 || ks.dims.size() != 2 || vs.dims.size() != 2) continue;
+    if (qs.dims[1] != ks.dims[1] || vs.dims[0] != ks.dims[0] || vs.dims[1] != qs.dims[1]) continue;
+    if (ks.dtype != qs.dtype || vs.dtype != qs.dtype) continue;
+    if (!fb200_attention_fan_supported(qs.dims[0], ks.dims[0], qs.dims[1], qs.dtype)) continue;
+    h.q = resolve_window(*p, producer, m1.in[0]);
+    h.k = resolve_window(*p, producer, tr.in[0]);
+    h.v = resolve_window(*p, producer, m2.in[1]);
+    bool ok = true;
+    for (const Window* w : {&h.q, &h.k, &h.v}) {
+      const SlotInfo& b = p->slots[static_cast<size_t>(w->base)];
+      if (b.dims.size() != 2 || b.dims[1] % 8 != 0 || w->col % 8 != 0 || b.dims[0] > 0x7fffffff ||
+          b.dims[1] > 0x7fffffff) ok = false;
+    }
+    if (!ok) continue;
+    // where the result finally lands
+    int cur = m2.out[0];
+    h.dest_row = h.dest_col = 0;
+    while (sole_reader(cur, &step, &index)) {
+      const Step& c = p->steps[static_cast<size_t>(step)];
+      if (c.kind != Kind::kConcat || p->slots[static_cast<size_t>(c.out[0])].dims.size() != 2) break;
+      const int64_t axis = c.iv[0];
+      int64_t off = 0;
+      for (int a = 0; a < index; ++a) off += p->slots[static_cast<size_t>(c.in[static_cast<size_t>(a)])].dims[static_cast<size_t>(axis)];
+      if (axis == 0) h.dest_row += off; else h.dest_col += off;
+      h.path.emplace_back(step, index);
+      cur = c.out[0];
+    }
+    h.dest = cur;
+    const SlotInfo& d = p->slots[static_cast<size_t>(h.dest)];
+    if (d.dims.size() != 2 || d.dims[1] % 8 != 0 || h.dest_col % 8 != 0) continue;
+    heads.push_back(h);
+  }
+  std::vector<char> used(heads.size(), 0);
+  for (size_t g = 0; g < heads.size(); ++g) {
+    if (used[g]) continue;
+    // the group: every head with the same source matrices, destination and shape
+    std::vector<size_t> group;
+    const SlotInfo& q0 = p->slots[static_cast<size_t>(p->steps[static_cast<size_t>(heads[g].scores)].in[0])];
+    const SlotInfo& k0 = p->slots[static_cast<size_t>(p->steps[static_cast<size_t>(heads[g].transpose)].in[0])];
+    for (size_t o = g; o < heads.size(); ++o) {
+      if (used[o]) continue;
+      const SlotInfo& qo = p->slots[static_cast<size_t>(p->steps[static_cast<size_t>(heads[o].scores)].in[0])];
+      const SlotInfo& ko = p->slots[static_cast<size_t>(p->steps[static_cast<size_t>(heads[o].transpose)].in[0])];
+      if (heads[o].q.base == heads[g].q.base && heads[o].k.base == heads[g].k.base &&
+          heads[o].v.base == heads[g].v.base && heads[o].dest == heads[g].dest &&
+          qo.dims == q0.dims && ko.dims == k0.dims && qo.dtype == q0.dtype) {
+        group.push_back(o);
+        used[o] = 1;
+      }
+    }
+    // tentatively skip the group's steps, then check the three conditions
+    std::vector<Kind> saved(static_cast<size_t>(n));
+    for (int i = 0; i < n; ++i) saved[static_cast<size_t>(i)] = p->steps[static_cast<size_t>(i)].kind;
+    auto restore = [&]() { for (int i = 0; i < n; ++i) p->steps[static_cast<size_t>(i)].kind = saved[static_cast<size_t>(i)]; };
+    int pos = -1, outer_concat = -1;
+    std::vector<int> concats;
+    for (size_t o : group) {
+      const FanHead& h = heads[o];
+      pos = std::max(pos, h.values);
+      for (const auto& pc : h.path) {
+        if (std::find(concats.begin(), concats.end(), pc.first) == concats.end()) concats.push_back(pc.first);
+        outer_concat = std::max(outer_concat, pc.first);
+      }
+    }
+    // (3) every input of every concat on the way comes from the group
+    bool ok = true;
+    for (int c : concats) {
+      const Step& cs = p->steps[static_cast<size_t>(c)];
+      for (size_t a = 0; a < cs.in.size() && ok; ++a) {
+        bool fed = false;
+        for (size_t o : group) {
+          for (const auto& pc : heads[o].path) if (pc.first == c && pc.second == static_cast<int>(a)) fed = true;
+        }
+        if (!fed) ok = false;
+      }
+    }
+    if (!ok) continue;
+    for (size_t o : group) {
+      const FanHead& h = heads[o];
+      for (int j : {h.transpose, h.scores, h.softmax, h.values}) p->steps[static_cast<size_t>(j)].kind = Kind::kSkip;
+    }
+    for (int c : concats) p->steps[static_cast<size_t>(c)].kind = Kind::kSkip;
+    // slices nobody reads any more
+    for (bool changed = true; changed;) {
+      changed = false;
+      for (int i = 0; i < n; ++i) {
+        Step& s = p->steps[static_cast<size_t>(i)];
+        if (s.kind != Kind::kSlice || p->slots[static_cast<size_t>(s.out[0])].output_index >= 0) continue;
+        if (readers_of(*p, s.out[0]).empty()) { s.kind = Kind::kSkip; changed = true; }
+      }
+    }
+    const FanHead& first = heads[group[0]];
+    // (1) the source matrices stay intact until the launch
+    for (int base : {first.q.base, first.k.base, first.v.base}) {
+      const int from = producer[static_cast<size_t>(root_slot(*p, base))];
+      for (int j = from + 1; j < pos && ok; ++j) {
+        const Step& s = p->steps[static_cast<size_t>(j)];
+        if (s.kind == Kind::kSkip || s.kind == Kind::kAlias || s.kind == Kind::kConstant) continue;
+        for (int w : s.out) if (ranges_overlap(*p, w, base)) ok = false;
+        if (s.write_slot >= 0 && ranges_overlap(*p, s.write_slot, base)) ok = false;
+      }
+    }
+    // (2) the destination: readers come after the launch; nothing that still runs before the
+    // outermost concat's position touches its bytes
+    for (const auto& r : readers_of(*p, first.dest)) if (r.first <= pos) ok = false;
+    for (int j = pos + 1; j < outer_concat && ok; ++j) {
+      const Step& s = p->steps[static_cast<size_t>(j)];
+      if (s.kind == Kind::kSkip || s.kind == Kind::kAlias || s.kind == Kind::kConstant) continue;
+      for (int w : s.out) if (ranges_overlap(*p, w, first.dest)) ok = false;
+      for (int r : s.in) if (ranges_overlap(*p, r, first.dest)) ok = false;
+      for (int e : s.epi_operand_slot) if (e >= 0 && ranges_overlap(*p, e, first.dest)) ok = false;
+      if (s.write_slot >= 0 && ranges_overlap(*p, s.write_slot, first.dest)) ok = false;
+    }
+    // without a concat on the way the result stays where the planner put it, but is written later
+    // than planned: its bytes must not be in use by a step that still runs in between
+    if (concats.empty() && group.size() != 1) ok = false;
+    std::vector<fb200_attention_head> table;
+    const int64_t o_ld = p->slots[static_cast<size_t>(first.dest)].dims[1];
+    for (size_t o : group) {
+      const FanHead& h = heads[o];
+      fb200_attention_head e{};
+      const int64_t coords[6] = {h.q.row, h.q.col, h.k.row, h.k.col, h.v.row, h.v.col};
+      for (int64_t c : coords) if (c < 0 || c > 0x7fffffff) ok = false;
+      e.q_row = static_cast<int32_t>(h.q.row); e.q_col = static_cast<int32_t>(h.q.col);
+      e.k_row = static_cast<int32_t>(h.k.row); e.k_col = static_cast<int32_t>(h.k.col);
+      e.v_row = static_cast<int32_t>(h.v.row); e.v_col = static_cast<int32_t>(h.v.col);
+      e.o_offset = h.dest_row * o_ld + h.dest_col;
+      table.push_back(e);
+    }
+    void* dev_table = nullptr;
+    if (ok) {
+      const size_t bytes = table.size() * sizeof(fb200_attention_head);
+      ok = fb200_malloc(p->device, bytes, 256, &dev_table) == FB200_OK &&
+           fb200_memcpy(p->device, dev_table, table.data(), bytes, FB200_H2D, nullptr, 0) == FB200_OK;
+      if (!ok && dev_table) { fb200_free(p->device, dev_table); dev_table = nullptr; }
+    }
+    if (!ok) { restore(); continue; }
+    p->owned.push_back(dev_table);
+    Step& launch = p->steps[static_cast<size_t>(pos)];
+    launch.kind = Kind::kAttentionFan;
+    launch.fan_q = first.q.base; launch.fan_k = first.k.base; launch.fan_v = first.v.base;
+    launch.fan_dest = first.dest;
+    launch.fan_heads = static_cast<int64_t>(group.size());
+    launch.fan_sq = q0.dims[0];
+    launch.fan_sk = k0.dims[0];
+    launch.fan_table = dev_table;
+  }
+}
+
 static void* slot_ptr(fb200_plan* p, int slot, const void* const* inputs, void* const* outputs) {
   const int r = root_slot(*p, slot);
   const SlotInfo& s = p->slots[r];
@@ -617,6 +865,18 @@ static int run_step(fb200_plan* p, Step& s, const void* const* inputs, void* con
                             in_slot(0).dims.data(), s.iv.data(), static_cast<int>(s.iv.size()), os.dtype, stream);
     case Kind::kCopy:
       return fb200_memcpy(p->device, out, in_ptr(0), os.bytes(), FB200_D2D, stream, 0);
+    case Kind::kAttentionFan: {
+      const SlotInfo& qb = p->slots[static_cast<size_t>(s.fan_q)];
+      const SlotInfo& kb = p->slots[static_cast<size_t>(s.fan_k)];
+      const SlotInfo& vb = p->slots[static_cast<size_t>(s.fan_v)];
+      const SlotInfo& db = p->slots[static_cast<size_t>(s.fan_dest)];
+      return fb200_attention_fan(slot_ptr(p, s.fan_q, inputs, outputs), qb.dims[0], qb.dims[1],
+                                 slot_ptr(p, s.fan_k, inputs, outputs), kb.dims[0], kb.dims[1],
+                                 slot_ptr(p, s.fan_v, inputs, outputs), vb.dims[0], vb.dims[1],
+                                 slot_ptr(p, s.fan_dest, inputs, outputs), db.dims[1],
+                                 static_cast<const fb200_attention_head*>(s.fan_table), s.fan_heads,
+                                 s.fan_sq, s.fan_sk, 64, db.dtype, stream);
+    }
   }
   return FB200_OK;
 }
@@ -656,6 +916,7 @@ extern "C" int fb200_plan_create(const char* plan_text, int device, int allow_tf
     return rc;
   }
   optimise(p);
+  if (p->opt_level >= 1) fuse_attention_fans(p);
   if (const char* env = getenv("FRAME_B200_GRAPH")) p->graph_enabled = atoi(env) != 0;
   p->launches = 0;
   for (const Step& s : p->steps) {
@@ -849,6 +1110,7 @@ extern "C" const char* fb200_plan_step_op(const fb200_plan* p, int index) {
   if (p == nullptr || index < 0 || static_cast<size_t>(index) >= p->steps.size()) return "";
   const Step& s = p->steps[static_cast<size_t>(index)];
   if (s.kind == Kind::kSkip) name = "(absorbed)";
+  else if (s.kind == Kind::kAttentionFan) name = "attention_fan";
   else if (s.kind == Kind::kAlias) name = "(alias)";
   else if ((s.kind == Kind::kMatmul || s.kind == Kind::kConv2d) && !s.chain_ops.empty()) name = s.op + "+epilogue";
   else name = s.op;

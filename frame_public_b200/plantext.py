@@ -99,3 +99,24 @@ def step_work(plan: Plan, index: int) -> Tuple[float, float]:
         cout, cpg, k = ins[1].dims
         flops = 2.0 * outs[0].numel * cpg * k
     return flops, nbytes
+
+
+def attention_fan_work(plan: Plan) -> Tuple[float, float]:
+    """(FLOPs, bytes) of all `matmul -> softmax -> matmul` chains of the plan together: the work of
+    the single attention_fan launch that replaces them.  Bytes: each head's q, k, v read and its
+    result written once."""
+    producer = {o: i for i, s in enumerate(plan.steps) for o in s.outputs}
+    flops = nbytes = 0.0
+    for i, s in enumerate(plan.steps):
+        if s.op != "softmax":
+            continue
+        scores = producer.get(s.inputs[0])
+        values = next((j for j, t in enumerate(plan.steps) if t.op == "matmul" and t.inputs[0] == s.outputs[0]), None)
+        if scores is None or values is None or plan.steps[scores].op != "matmul":
+            continue
+        flops += step_work(plan, scores)[0] + step_work(plan, values)[0]
+        q, kt = (plan.slots[k] for k in plan.steps[scores].inputs)
+        v = plan.slots[plan.steps[values].inputs[1]]
+        o = plan.slots[plan.steps[values].outputs[0]]
+        nbytes += q.nbytes + kt.nbytes + v.nbytes + o.nbytes
+    return flops, nbytes

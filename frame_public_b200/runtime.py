@@ -73,6 +73,16 @@ class CompiledPlan:
         capi.check(self.lib.fb200_plan_profile(self._h, a, b, stream, ms, 4096, byref(n)))
         return [(self.lib.fb200_plan_step_op(self._h, i).decode(), float(ms[i])) for i in range(n.value)]
 
+    def step_names(self) -> List[str]:
+        """Op name of every step as the executor will run it ("(absorbed)" for a step folded into
+        another launch, "(alias)" for a reshape that became a view)."""
+        names = []
+        while True:
+            name = self.lib.fb200_plan_step_op(self._h, len(names)).decode()
+            if not name:
+                return names
+            names.append(name)
+
     def close(self):
         if self._h:
             self.lib.fb200_plan_destroy(self._h)

@@ -68,3 +68,20 @@ def test_unknown_op_is_unimplemented_with_its_name():
     p = capi.c_void_p()
     rc = lib.fb200_plan_create(text.encode(), 0, 0, 1, capi.byref(p))
     assert rc == 4 and b"frobnicate" in lib.fb200_last_error()
+
+
+def test_attention_heads_become_one_launch():
+    """2 batches x 2 heads of slice/transpose/matmul/softmax/matmul + two levels of concat: one
+    attention_fan launch at opt level 1, the step-by-step path at opt level 0, same numbers within
+    the bf16 tier."""
+    wl = next(w for w in WORKLOADS if w.name == "transformer_bf16_b2_s128_d128")
+    fused = runtime.CompiledPlan(_plan_text(wl.name), 0, opt_level=1)
+    plain = runtime.CompiledPlan(_plan_text(wl.name), 0, opt_level=0)
+    names = fused.step_names()
+    assert names.count("attention_fan") == 1
+    assert not any(n in ("softmax", "transpose", "concat", "slice") for n in names)
+    assert fused.launches_per_run <= 8 < plain.launches_per_run
+    (a,) = fused.run_host(wl.inputs)
+    (b,) = plain.run_host(wl.inputs)
+    assert capi.kernel_status(0) == 0
+    assert fo.all_close(a, b, wl.dtype, rtol=2e-2, atol=2e-2), fo.max_err(a, b, wl.dtype)
