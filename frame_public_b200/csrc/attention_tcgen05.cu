@@ -6,7 +6,7 @@
 // for 8 x 16 heads that is about 900 launches of tiny kernels.  This kernel computes, for every
 // head h of a table,
 //     S = Q_h K_h^T   (fp32 accumulate, rounded once to T: the first matmul's store)
-//     P = softmax(S)  (row max, exp(x - max), sum, e / sum in fp32; rounded once to T)
+//     P = softmax(S)  (row max, exp(x - max), sum, e * (1 / sum) in fp32; rounded once to T)
 //     O = P V_h       (fp32 accumulate, rounded once to T)
 // i.e. the same three operators with the same rounding points (matmul:
 // src/backends/cpu/kernels/matmul.cpp:92-131, softmax: src/backends/cpu/kernels/sequence.cpp:114-174);
@@ -17,12 +17,13 @@
 // materialised; O_h is written at an element offset of an output matrix with its own row pitch,
 // so a concat can be skipped too.
 //
-// One CTA (128 threads) per (head, block of 128 query rows):
+// One CTA (256 threads) per (head, block of 128 query rows):
 //   thread 0   TMA loads of Q (16 KiB), K and V (sk x 128 B each, 128-byte swizzle);
 //              tcgen05.mma S[128, sk] = Q K^T into TMEM (N <= 256 per instruction);
-//   all        thread r owns query row r = TMEM lane r: three passes over the row with
-//              tcgen05.ld (max; exp and sum, written back with tcgen05.st; normalise), P written
-//              to shared memory as the K-major, 128-byte-swizzled A operand (over K's bytes);
+//   all        two threads per query row (= TMEM lane), each on half of the keys: three sweeps
+//              with tcgen05.ld (max; exp and sum, written back with tcgen05.st; normalise), P
+//              written to shared memory as the K-major, 128-byte-swizzled A operand (over K's
+//              bytes);
 //   thread 0   tcgen05.mma O[128, 64] = P V (V is the MN-major B operand straight from TMA);
 //   all        tcgen05.ld O, convert, 128-byte row stores.
 // Shared memory: 16 KiB + sk*256 + sk*128 (208 KiB at sk = 512); TMEM: sk columns (power of two).
@@ -40,7 +41,7 @@ int device_status_word(int** dev_ptr);
 
 using namespace sm100;
 
-constexpr int kAttnThreads = 128;
+constexpr int kAttnThreads = 256;
 constexpr int kAttnBlockM = 128;
 constexpr int kAttnHeadDim = 64;
 constexpr int kAttnMaxKeys = 512;
@@ -71,6 +72,12 @@ __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
 template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -79,6 +86,16 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, f
 template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
   const __half2 v = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// Value of an fp32 score after the first matmul's store to T and the softmax's load of it.  The
+// conversion instructions run on the quarter-rate XU pipe, which exp2 already saturates, so the
+// bfloat16 round-to-nearest-even is done with integer arithmetic instead (finite inputs; a NaN
+// stays a NaN).
+template <typename T> __device__ __forceinline__ float stored_score(float v) { return round_through<T>(v); }
+template <> __device__ __forceinline__ float stored_score<__nv_bfloat16>(float v) {
+  const uint32_t b = __float_as_uint(v);
+  return __uint_as_float((b + 0x7FFFu + ((b >> 16) & 1u)) & 0xFFFF0000u);
 }
 
 template <typename T>
@@ -164,50 +181,79 @@ attention_fan_kernel(const __grid_constant__ CUtensorMap tmap_q,
   bool ok = head_ok && mbar_wait(bar_s, 0, status, kFaultAttnScores);
   ok = __all_sync(0xffffffffu, ok);
 
-  // thread r <-> query row r <-> TMEM lane r (warp w may touch lanes 32w .. 32w+31 only)
-  const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+  // Two threads per query row: warp w works on TMEM lanes 32*(w & 3) .. +31 (the only lanes it may
+  // touch) and on the key columns of half w >> 2; row maximum and row sum are exchanged through
+  // shared memory.  Each sweep keeps the next 32-column tcgen05.ld in flight while the current one
+  // is processed.
+  const int quad = warp & 3, half = warp >> 2;
+  const int row_in_tile = quad * 32 + (tid & 31);
+  const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+  const int c_begin = half * (sk / 2), c_end = c_begin + sk / 2;
+  float* red_max = reinterpret_cast<float*>(base_ptr + bar_off + 64);   // [2][128]
+  float* red_sum = red_max + 2 * kAttnBlockM;
+  auto sweep = [&](auto&& body) {
+    uint32_t ra[32], rb[32];
+    tmem_ld_32x32b_x32(lane_addr + static_cast<uint32_t>(c_begin), ra);
+    for (int c = c_begin; c < c_end; c += 64) {
+      tmem_ld_wait();
+      const bool two = c + 32 < c_end;
+      if (two) tmem_ld_32x32b_x32(lane_addr + static_cast<uint32_t>(c + 32), rb);
+      body(c, ra);
+      if (two) {
+        tmem_ld_wait();
+        if (c + 64 < c_end) tmem_ld_32x32b_x32(lane_addr + static_cast<uint32_t>(c + 64), ra);
+        body(c + 32, rb);
+      }
+    }
+  };
+  float mx = -INFINITY;
   if (ok) {
     tcgen05_fence_after_sync();
-    uint32_t r[32];
-    float mx = -INFINITY;
-    for (int c = 0; c < sk; c += 32) {
-      tmem_ld_32x32b_x32(lane_addr + static_cast<uint32_t>(c), r);
-      tmem_ld_wait();
+    sweep([&](int, uint32_t (&r)[32]) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, round_through<T>(__uint_as_float(r[i])));
-    }
-    float sum = 0.0f;
-    for (int c = 0; c < sk; c += 32) {
-      tmem_ld_32x32b_x32(lane_addr + static_cast<uint32_t>(c), r);
-      tmem_ld_wait();
+      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+    });
+    mx = stored_score<T>(mx);   // rounding is monotonic: max of the rounded = rounded max
+  }
+  red_max[half * kAttnBlockM + row_in_tile] = mx;
+  __syncthreads();
+  mx = fmaxf(red_max[row_in_tile], red_max[kAttnBlockM + row_in_tile]);
+  float sum = 0.0f;
+  if (ok) {
+    const float mx2 = mx * 1.4426950408889634f;
+    sweep([&](int c, uint32_t (&r)[32]) {
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        const float e = __expf(round_through<T>(__uint_as_float(r[i])) - mx);
+        const float e = ex2_approx(fmaf(stored_score<T>(__uint_as_float(r[i])), 1.4426950408889634f, -mx2));
         sum += e;
         r[i] = __float_as_uint(e);
       }
       tmem_st_32x32b_x32(lane_addr + static_cast<uint32_t>(c), r);
-    }
+    });
     tmem_st_wait();
+  }
+  red_sum[half * kAttnBlockM + row_in_tile] = sum;
+  __syncthreads();
+  sum = red_sum[row_in_tile] + red_sum[kAttnBlockM + row_in_tile];
+  if (ok) {
     // P in the A-operand layout: blocks of 64 keys (128 bytes per row, 16 KiB per block), the
     // 16-byte unit index XORed with (row & 7).
-    uint8_t* p_row = base_ptr + kp_off + static_cast<uint32_t>(tid) * 128u;
-    const uint32_t swz = static_cast<uint32_t>(tid & 7);
-    for (int c = 0; c < sk; c += 32) {
-      tmem_ld_32x32b_x32(lane_addr + static_cast<uint32_t>(c), r);
-      tmem_ld_wait();
+    uint8_t* p_row = base_ptr + kp_off + static_cast<uint32_t>(row_in_tile) * 128u;
+    const uint32_t swz = static_cast<uint32_t>(row_in_tile & 7);
+    const float inv = 1.0f / sum;
+    sweep([&](int c, uint32_t (&r)[32]) {
       uint8_t* blk = p_row + static_cast<uint32_t>(c >> 6) * 16384u;
       const uint32_t unit0 = static_cast<uint32_t>((c >> 3) & 7);   // 0 or 4
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         uint4 v;
-        v.x = pack2<T>(__fdividef(__uint_as_float(r[8 * u + 0]), sum), __fdividef(__uint_as_float(r[8 * u + 1]), sum));
-        v.y = pack2<T>(__fdividef(__uint_as_float(r[8 * u + 2]), sum), __fdividef(__uint_as_float(r[8 * u + 3]), sum));
-        v.z = pack2<T>(__fdividef(__uint_as_float(r[8 * u + 4]), sum), __fdividef(__uint_as_float(r[8 * u + 5]), sum));
-        v.w = pack2<T>(__fdividef(__uint_as_float(r[8 * u + 6]), sum), __fdividef(__uint_as_float(r[8 * u + 7]), sum));
+        v.x = pack2<T>(__uint_as_float(r[8 * u + 0]) * inv, __uint_as_float(r[8 * u + 1]) * inv);
+        v.y = pack2<T>(__uint_as_float(r[8 * u + 2]) * inv, __uint_as_float(r[8 * u + 3]) * inv);
+        v.z = pack2<T>(__uint_as_float(r[8 * u + 4]) * inv, __uint_as_float(r[8 * u + 5]) * inv);
+        v.w = pack2<T>(__uint_as_float(r[8 * u + 6]) * inv, __uint_as_float(r[8 * u + 7]) * inv);
         *reinterpret_cast<uint4*>(blk + (((unit0 + u) ^ swz) << 4)) = v;
       }
-    }
+    });
     fence_proxy_async_smem();   // P must be visible to the tensor core's reads
   }
   tcgen05_fence_before_sync();
@@ -234,23 +280,21 @@ attention_fan_kernel(const __grid_constant__ CUtensorMap tmap_q,
   ok = __all_sync(0xffffffffu, ok);
   if (ok) {
     tcgen05_fence_after_sync();
-    const int row = qb * kAttnBlockM + tid;
-    T* dst = o_base + h.o_offset + static_cast<int64_t>(row) * o_ld;
+    const int row = qb * kAttnBlockM + row_in_tile;
+    const int c = half * 32;   // each half of the warps stores 32 of the 64 columns
+    T* dst = o_base + h.o_offset + static_cast<int64_t>(row) * o_ld + c;
+    uint32_t r[32];
+    tmem_ld_32x32b_x32(lane_addr + static_cast<uint32_t>(c), r);
+    tmem_ld_wait();
+    if (row < sq) {
 #pragma unroll
-    for (int c = 0; c < kAttnHeadDim; c += 32) {
-      uint32_t r[32];
-      tmem_ld_32x32b_x32(lane_addr + static_cast<uint32_t>(c), r);
-      tmem_ld_wait();
-      if (row < sq) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          uint4 v;
-          v.x = pack2<T>(__uint_as_float(r[8 * u + 0]), __uint_as_float(r[8 * u + 1]));
-          v.y = pack2<T>(__uint_as_float(r[8 * u + 2]), __uint_as_float(r[8 * u + 3]));
-          v.z = pack2<T>(__uint_as_float(r[8 * u + 4]), __uint_as_float(r[8 * u + 5]));
-          v.w = pack2<T>(__uint_as_float(r[8 * u + 6]), __uint_as_float(r[8 * u + 7]));
-          *reinterpret_cast<uint4*>(dst + c + 8 * u) = v;
-        }
+      for (int u = 0; u < 4; ++u) {
+        uint4 v;
+        v.x = pack2<T>(__uint_as_float(r[8 * u + 0]), __uint_as_float(r[8 * u + 1]));
+        v.y = pack2<T>(__uint_as_float(r[8 * u + 2]), __uint_as_float(r[8 * u + 3]));
+        v.z = pack2<T>(__uint_as_float(r[8 * u + 4]), __uint_as_float(r[8 * u + 5]));
+        v.w = pack2<T>(__uint_as_float(r[8 * u + 6]), __uint_as_float(r[8 * u + 7]));
+        *reinterpret_cast<uint4*>(dst + 8 * u) = v;
       }
     }
   }
@@ -304,7 +348,8 @@ extern "C" int fb200_attention_fan(const void* q_base, int64_t q_rows, int64_t q
   if (int rc = device_status_word(&status)) return rc;
   uint32_t tmem_cols = 64;
   while (tmem_cols < static_cast<uint32_t>(sk)) tmem_cols *= 2;
-  const size_t smem = kAttnBlockM * 128 + static_cast<size_t>(sk) * 384 + 1024 + 64;
+  const size_t smem = kAttnBlockM * 128 + static_cast<size_t>(sk) * 384 + 1024 /*align*/ + 64 /*barriers*/ +
+                      4 * kAttnBlockM * sizeof(float) /*row max and sum exchange*/;
   const int grid = static_cast<int>(n_heads * q_blocks);
   cudaStream_t s = as_stream(stream);
   if (dtype == FB200_BF16) {

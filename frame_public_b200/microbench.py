@@ -7,7 +7,8 @@ measured peak (MEASURED_PEAKS.json at the repository root, when present).
     python -m frame_public_b200.microbench --op gemm --m 4096 --n 4096 --k 4096 --dtype bf16
 
 Ops: fused_add_relu, gelu, silu, softmax, layer_norm, scan_rows, mamba_scan, transpose, slice,
-max_pool, conv1d_depthwise, conv2d_tf32, gemm.  Inputs are seeded random data; between timed
+max_pool, conv1d_depthwise, conv2d_tf32, attention (--batch, --cols = sequence length, --m = model
+width), gemm.  Inputs are seeded random data; between timed
 launches nothing is flushed, so choose sizes larger than the 126 MB L2 for HBM figures.  This is
 also the command the ncu captures summarised under profiles/ were taken with.
 """
@@ -136,6 +137,23 @@ def main():
         fn = lambda: capi.conv2d(x.ptr, w.ptr, b.ptr, o.ptr, p, capi.F32, True)
         nbytes = (n * cin * h * h + n * cout * h * h) * 4
         flops = 2.0 * n * cout * h * h * cin * k * k
+    elif a.op == "attention":
+        # the transformer workload's layout: [batch*seq, 3*heads*64] projection, 64-wide heads
+        bt, seq, heads = a.batch, a.cols, a.m // 64
+        width = heads * 64
+        qkv = _rand((bt * seq, 3 * width), capi.BF16, rng)
+        o = capi.DeviceBuffer(bt * seq * width * 2)
+        table = np.zeros(bt * heads, dtype=capi.HEAD_DTYPE)
+        for b in range(bt):
+            for h in range(heads):
+                table[b * heads + h] = (b * seq, h * 64, b * seq, width + h * 64, b * seq,
+                                        2 * width + h * 64, b * seq * width + h * 64)
+        tab = capi.DeviceBuffer.from_numpy(table.view(np.uint8))
+        rows, ld = bt * seq, 3 * width
+        fn = lambda: capi.attention_fan(qkv.ptr, rows, ld, qkv.ptr, rows, ld, qkv.ptr, rows, ld, o.ptr, width,
+                                        tab.ptr, len(table), seq, seq, 64, capi.BF16)
+        nbytes = 4 * bt * seq * width * 2
+        flops = 4.0 * bt * heads * seq * seq * 64
     elif a.op == "gemm":
         m, n, k = a.m, a.n, a.k
         x, w, o = _rand((m, k), dt, rng), _rand((k, n), dt, rng), capi.DeviceBuffer(m * n * es)
