@@ -95,6 +95,8 @@ SIGNATURES = {
     "fb200_layer_norm": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_double, c_int, _P]),
     "fb200_selective_scan": (c_int, [_P] * 6 + [c_int64, c_int64, c_int, _P]),
     "fb200_selective_scan_noalloc": (c_int, [_P] * 6 + [c_int64, c_int64, c_int, _P]),
+    "fb200_dwconv1d_time_major": (c_int, [_P, c_int64, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                          c_int64, c_int64, POINTER(c_int), c_int, c_int, _P]),
     "fb200_attention_fan_supported": (c_int, [c_int64, c_int64, c_int64, c_int]),
     "fb200_attention_fan": (c_int, [_P, c_int64, c_int64, _P, c_int64, c_int64, _P, c_int64, c_int64, _P,
                                     c_int64, _P, c_int64, c_int64, c_int64, c_int64, c_int, _P]),
@@ -265,6 +267,13 @@ def selective_scan(x, a, b, c, d, out, rows, steps, dtype, stream=None):
 
 def mamba_scan(u, delta, A, B, C, D, z, y, batch, length, dm, nstate, stream=None):
     check(load().fb200_mamba_scan(u, delta, A, B, C, D, z, y, batch, length, dm, nstate, stream))
+
+
+def dwconv1d_time_major(x, x_ld, w, bias, out, out_ld, batch, length, out_len, channels, k, shift,
+                        op_names, dtype, stream=None):
+    ops = (c_int * max(1, len(op_names)))(*[EW[n] for n in op_names])
+    check(load().fb200_dwconv1d_time_major(x, x_ld, w, bias, out, out_ld, batch, length, out_len, channels,
+                                           k, shift, ops, len(op_names), dtype, stream))
 
 
 HEAD_DTYPE = np.dtype([("q_row", "<i4"), ("q_col", "<i4"), ("k_row", "<i4"), ("k_col", "<i4"),

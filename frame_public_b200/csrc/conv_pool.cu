@@ -363,3 +363,162 @@ extern "C" int fb200_max_pool2d(const void* x, void* out, int64_t n, int64_t c, 
   }
   return after_launch("max_pool2d_kernel");
 }
+
+// ---- depthwise conv1d along time, in the time-major layout -----------------------------------------
+// The reference's Mamba block computes its causal depthwise convolution as
+//   transpose [B,L,C] -> [B,C,L], conv1d(groups = C, padding = K-1), slice to L, activation,
+//   transpose back (src/nn/layers.cpp:1596-1602),
+// five full passes over the activation.  This kernel produces the same values straight from the
+// time-major tensor (row pitch x_ld, so a column window of a wider matrix works) into a time-major
+// result: out[b,t,c] = ops(bias[c] + sum_k w[c,k] * x[b, t+shift+k, c]), taps outside [0, len)
+// skipped, products accumulated for k increasing and the bias added last, the sum rounded to T
+// and each unary op rounded to T — the operations of conv1d_forward_compute
+// (src/backends/cpu/kernels/conv.cpp:565-589) and of the elementwise chain, in their order, so
+// fp32 results are bit-identical to the five-step form.
+// A thread owns one 16-byte vector of channels and walks kDwRun consecutive time steps with the
+// K most recent inputs in registers: every input is loaded once per run (plus K-1 halo rows);
+// the loads of four steps are issued together.
+namespace fb200 {
+
+constexpr int kDwRun = 64;     // time steps per thread (a multiple of kDwUnroll)
+constexpr int kDwUnroll = 4;  // outputs per group: that many loads in flight per thread
+constexpr int kDwMaxK = 8;
+
+struct DwOps { int n; int op[FB200_MAX_CHAIN]; };
+
+template <typename T, int K>
+__global__ void __launch_bounds__(128)
+dwconv1d_time_major_kernel(const T* __restrict__ x, int64_t x_ld, const T* __restrict__ w,
+                           const T* __restrict__ bias, T* __restrict__ out, int64_t out_ld,
+                           int64_t len, int64_t out_len, int64_t channels, int64_t shift,
+                           DwOps ops) {
+  constexpr int V = 16 / sizeof(T);
+  const int64_t c0 = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * V;
+  if (c0 >= channels) return;
+  const int64_t b = blockIdx.z;
+  const int64_t t_begin = static_cast<int64_t>(blockIdx.y) * kDwRun;
+  const int64_t t_end = t_begin + kDwRun < out_len ? t_begin + kDwRun : out_len;
+  float taps[K][V];
+#pragma unroll
+  for (int kk = 0; kk < K; ++kk) {
+#pragma unroll
+    for (int v = 0; v < V; ++v) taps[kk][v] = to_f32(w[(c0 + v) * K + kk]);
+  }
+  float bv[V];
+#pragma unroll
+  for (int v = 0; v < V; ++v) bv[v] = bias != nullptr ? to_f32(bias[c0 + v]) : 0.0f;
+  const T* xb = x + b * len * x_ld + c0;
+  T* ob = out + b * out_len * out_ld + c0;
+  // rows[j] = input row (t + shift + j) for the U outputs of one group: K-1 rows of history and U
+  // new ones, all U loads issued before the arithmetic; rows outside [0, len) are marked invalid
+  constexpr int U = kDwUnroll;
+  float rows[K - 1 + U][V];
+  bool valid[K - 1 + U];
+  auto fetch = [&](int64_t row, float (&dst)[V], bool& ok) {
+    ok = row >= 0 && row < len;
+    if (ok) {
+      load_vec<T>(xb + row * x_ld, dst);
+    } else {
+#pragma unroll
+      for (int v = 0; v < V; ++v) dst[v] = 0.0f;
+    }
+  };
+#pragma unroll
+  for (int j = 0; j < K - 1; ++j) fetch(t_begin + shift + j, rows[j], valid[j]);
+  for (int64_t t = t_begin; t < t_end; t += U) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) fetch(t + u + shift + K - 1, rows[K - 1 + u], valid[K - 1 + u]);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float acc[V];
+#pragma unroll
+      for (int v = 0; v < V; ++v) acc[v] = 0.0f;
+#pragma unroll
+      for (int kk = 0; kk < K; ++kk) {
+        if (valid[u + kk]) {
+#pragma unroll
+          for (int v = 0; v < V; ++v) acc[v] += rows[u + kk][v] * taps[kk][v];
+        }
+      }
+#pragma unroll
+      for (int v = 0; v < V; ++v) {
+        if (bias != nullptr) acc[v] += bv[v];
+        float r = round_through<T>(acc[v]);
+        for (int o = 0; o < ops.n; ++o) r = round_through<T>(ew_unary(ops.op[o], r));
+        acc[v] = r;
+      }
+      if (t + u < t_end) store_vec<T>(ob + (t + u) * out_ld, acc);
+    }
+#pragma unroll
+    for (int j = 0; j < K - 1; ++j) {   // the last K-1 rows become the next group's history
+#pragma unroll
+      for (int v = 0; v < V; ++v) rows[j][v] = rows[j + U][v];
+      valid[j] = valid[j + U];
+    }
+  }
+}
+
+template <typename T>
+static void launch_dwconv(dim3 grid, cudaStream_t s, const void* x, int64_t x_ld, const void* w,
+                          const void* bias, void* out, int64_t out_ld, int64_t len, int64_t out_len,
+                          int64_t channels, int k, int64_t shift, const DwOps& ops) {
+  const T* xp = static_cast<const T*>(x);
+  const T* wp = static_cast<const T*>(w);
+  const T* bp = static_cast<const T*>(bias);
+  T* op = static_cast<T*>(out);
+#define FB200_DW_CASE(KK)                                                                          \
+  case KK:                                                                                         \
+    dwconv1d_time_major_kernel<T, KK><<<grid, 128, 0, s>>>(xp, x_ld, wp, bp, op, out_ld, len, out_len, \
+                                                           channels, shift, ops);                  \
+    break;
+  switch (k) {
+    FB200_DW_CASE(1) FB200_DW_CASE(2) FB200_DW_CASE(3) FB200_DW_CASE(4)
+    FB200_DW_CASE(5) FB200_DW_CASE(6) FB200_DW_CASE(7) FB200_DW_CASE(8)
+    default: break;
+  }
+#undef FB200_DW_CASE
+}
+
+}  // namespace fb200
+
+extern "C" int fb200_dwconv1d_time_major(const void* x, int64_t x_ld, const void* w, const void* bias,
+                                         void* out, int64_t out_ld, int64_t batch, int64_t len,
+                                         int64_t out_len, int64_t channels, int64_t k, int64_t shift,
+                                         const int* unary_ops, int n_ops, int dtype,
+                                         fb200_stream stream) {
+  if (batch < 0 || len < 1 || out_len < 0 || channels < 1 || k < 1 || k > kDwMaxK) {
+    return set_error(FB200_INVALID_ARGUMENT, "dwconv1d_time_major: invalid geometry (1 <= k <= %d)", kDwMaxK);
+  }
+  if (n_ops < 0 || n_ops > FB200_MAX_CHAIN || (n_ops > 0 && unary_ops == nullptr)) {
+    return set_error(FB200_INVALID_ARGUMENT, "dwconv1d_time_major: bad op list");
+  }
+  DwOps ops{};
+  ops.n = n_ops;
+  for (int i = 0; i < n_ops; ++i) {
+    if (!ew_is_known(unary_ops[i]) || ew_is_binary(unary_ops[i])) {
+      return set_error(FB200_INVALID_ARGUMENT, "dwconv1d_time_major: op code %d is not a unary elementwise op", unary_ops[i]);
+    }
+    ops.op[i] = unary_ops[i];
+  }
+  if (dtype != FB200_F32 && dtype != FB200_BF16 && dtype != FB200_F16) {
+    return set_error(FB200_INVALID_ARGUMENT, "dwconv1d_time_major: dtype code %d is not float32/float16/bfloat16", dtype);
+  }
+  if (batch == 0 || out_len == 0) return FB200_OK;
+  if (x == nullptr || w == nullptr || out == nullptr) return set_error(FB200_INVALID_ARGUMENT, "dwconv1d_time_major: null argument");
+  const int v = 16 / itemsize_of(dtype);
+  if (channels % v || x_ld % v || out_ld % v || x_ld < channels || out_ld < channels || !aligned16(x) || !aligned16(out)) {
+    return set_error(FB200_INVALID_ARGUMENT,
+                     "dwconv1d_time_major: channels and row pitches must be multiples of %d elements and the "
+                     "tensors 16-byte aligned", v);
+  }
+  const int64_t runs = (out_len + kDwRun - 1) / kDwRun;
+  if (batch > 65535 || runs > 65535) return set_error(FB200_INVALID_ARGUMENT, "dwconv1d_time_major: batch or length too large");
+  const int64_t vecs = channels / v;
+  dim3 grid(static_cast<unsigned>((vecs + 127) / 128), static_cast<unsigned>(runs), static_cast<unsigned>(batch));
+  cudaStream_t s = as_stream(stream);
+  const int kk = static_cast<int>(k);
+  if (dtype == FB200_F32) launch_dwconv<float>(grid, s, x, x_ld, w, bias, out, out_ld, len, out_len, channels, kk, shift, ops);
+  else if (dtype == FB200_BF16) launch_dwconv<__nv_bfloat16>(grid, s, x, x_ld, w, bias, out, out_ld, len, out_len, channels, kk, shift, ops);
+  else launch_dwconv<__half>(grid, s, x, x_ld, w, bias, out, out_ld, len, out_len, channels, kk, shift, ops);
+  return after_launch("dwconv1d_time_major_kernel");
+}

@@ -6,7 +6,7 @@
 // Replaces the cublasLtMatmul call of src/backends/cuda/kernels/matmul.cpp:90-276, which also
 // ran bias and activation as separate launches; here they are the epilogue of the same kernel.
 //
-// Design (one persistent CTA per SM, 192 threads, warp-specialised):
+// Design (one persistent CTA per SM, 320 threads, warp-specialised):
 //   warp 0   TMA producer.  A tile [128 x BLOCK_K] is K-contiguous ("K-major" operand);
 //            B tile [BLOCK_K x BLOCK_N] is N-contiguous ("MN-major" operand), loaded as
 //            BLOCK_N*elt/128 boxes of 128 bytes x BLOCK_K rows.  Both land in 128-byte-swizzled
@@ -15,9 +15,11 @@
 //   warp 1   allocates TMEM (2 accumulators of BLOCK_N fp32 columns) and, from one thread, issues
 //            4 tcgen05.mma (M=128, N=BLOCK_N, K=32 bytes) per stage; tcgen05.commit releases the
 //            stage and, after the last k-block, publishes the accumulator.
-//   warps 2-5 epilogue: tcgen05.ld 32 lanes x 32 columns, the epilogue chain in fp32 registers
-//            (operands fetched with 128-bit loads), 128-bit stores.  The second accumulator lets
-//            the epilogue of tile i overlap the MMAs of tile i+1.
+//   warps 2-9 epilogue: tcgen05.ld 32 lanes x 32 columns, the epilogue chain in fp32 registers
+//            (operands fetched with 128-bit loads), 128-bit stores; two warps per TMEM lane
+//            quarter, each on half of the tile's columns (with four warps a transcendental
+//            epilogue behind a short K was bound by those 128 threads).  The second accumulator
+//            lets the epilogue of tile i overlap the MMAs of tile i+1.
 // Tiles are walked in groups of 8 M-blocks so that concurrently resident CTAs share A and B
 // panels in the 126 MB L2.  Edge tiles rely on TMA zero fill for loads and masked stores.
 // Bound: tensor pipe.  FLOPs per launch = 2*M*N*K.
@@ -38,7 +40,7 @@ int gemm_simt(const void* a, const void* b, void* c, int64_t m, int64_t n, int64
 using namespace sm100;
 
 constexpr int kBlockM = 128;
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 320;   // TMA warp, MMA warp, eight epilogue warps
 constexpr int kGroupM = 8;
 
 // Where a tile of the result goes: one or several destination matrices of row pitch `ld`, at
@@ -125,7 +127,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tmem_full_bar(a), 1);
-      mbar_init(tmem_empty_bar(a), 4);  // one arrival per epilogue warp
+      mbar_init(tmem_empty_bar(a), 8);  // one arrival per epilogue warp
     }
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
@@ -207,8 +209,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
     }
   } else {
-    // Epilogue warps 2..5; a warp may only touch TMEM lanes 32*(warp%4) .. +31.
+    // Epilogue warps 2..9; a warp may only touch TMEM lanes 32*(warp%4) .. +31, so two warps share
+    // each lane quarter and split the tile's columns between them.
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    constexpr int kChunksPerWarp = BLOCK_N / 64;
     int acc = 0;
     uint32_t acc_phase = 0;
     constexpr int W = 16 / sizeof(T);
@@ -224,7 +229,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(acc * BLOCK_N);
 #pragma unroll 1
-      for (int c = 0; c < BLOCK_N / 32; ++c) {
+      for (int c = half * kChunksPerWarp; c < (half + 1) * kChunksPerWarp; ++c) {
         const int64_t col0 = tn * BLOCK_N + c * 32;
         if (col0 >= N) break;  // warp-uniform
         uint32_t r[32];

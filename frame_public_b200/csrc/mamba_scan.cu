@@ -7,34 +7,48 @@
 // u / delta / z / y are time-major [batch, len, dm] (the layout the surrounding GEMMs produce);
 // A is [dm, nstate]; B, C are [batch, len, nstate]; D is [dm].
 //
-// Mapping: four lanes share one (batch, channel), each holding a quarter of the state, so a warp
-// covers 8 channels and there are 4x the threads of a thread-per-channel mapping — the recurrence is
-// latency-bound (exp + dependent multiply-adds), not HBM-bound, until enough warps are resident.
-// Four time steps are processed per iteration: all loads and all exp2 first, then the four short
-// recurrences, then the partial state sums are combined with two shuffles per step, after which
-// every lane holds all four sums and lane j finishes (D skip, gate, store) step j.
-// exp(delta*A) is evaluated as exp2(delta * (A*log2 e)): 2 ulp, and the recurrence contracts, so
-// the error does not grow.  Algorithmic bytes = (4*B*L*D + 2*B*L*N) * 4.
+// Mapping: LANES lanes share one (batch, channel), each holding NS/LANES states.  The recurrence is
+// bound by instruction issue and by the exp2 unit, not by HBM (0.8 GB per run at the Mamba
+// configuration), so what matters is instructions per channel-step: the per-lane overhead (loads of
+// u and delta, addressing, the cross-lane sum, the finishing of y) is paid LANES times, the state
+// arithmetic once.  Two lanes of eight states keep enough threads for one wave on 148 SMs and
+// cost a third of the instructions of four lanes of four.
+// Four time steps are processed per iteration: u, delta and z of the NEXT four steps are in flight
+// (two register sets) while the current four are computed; B and C rows, shared by all channels
+// of a batch and therefore L1/L2 hits, are fetched with 128-bit loads at the start of the
+// iteration.  The partial sums are combined with log2(LANES) shuffles per step, after which every
+// lane holds all four sums and lane s finishes (D skip, gate, store) the steps j with j % LANES == s.
+// exp(delta*A) is evaluated as ex2.approx(delta * (A*log2 e)): 2 ulp, and the recurrence contracts,
+// so the error does not grow.  Algorithmic bytes = (4*B*L*D + 2*B*L*N) * 4.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace fb200 {
 
 constexpr int kMambaThreads = 128;
-constexpr int kMambaLanes = 4;
-constexpr int kMambaChannelsPerCta = kMambaThreads / kMambaLanes;
-constexpr int kMambaSteps = 4;  // time steps per iteration == lanes per channel
+constexpr int kMambaSteps = 4;  // time steps per iteration
 
-template <int NS>
+__device__ __forceinline__ float mamba_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int NS, int LANES>
 __global__ void __launch_bounds__(kMambaThreads)
 mamba_scan_kernel(const float* __restrict__ u, const float* __restrict__ delta,
                   const float* __restrict__ A, const float* __restrict__ B,
                   const float* __restrict__ C, const float* __restrict__ D,
                   const float* __restrict__ z, float* __restrict__ y, int64_t len, int64_t dm) {
-  constexpr int PER = NS / kMambaLanes;  // states per lane
+  constexpr int PER = NS / LANES;  // states per lane
   constexpr int U = kMambaSteps;
+  constexpr int FIN = U / LANES;   // steps each lane finishes per iteration
+  constexpr int kChannelsPerCta = kMambaThreads / LANES;
+  static_assert(PER % 4 == 0 && U % LANES == 0, "states per lane must fill 128-bit loads");
   const int64_t bidx = blockIdx.y;
-  const int sg = threadIdx.x & (kMambaLanes - 1);
-  const int64_t ch_raw = static_cast<int64_t>(blockIdx.x) * kMambaChannelsPerCta + (threadIdx.x >> 2);
+  const int sg = threadIdx.x % LANES;
+  const int64_t ch_raw = static_cast<int64_t>(blockIdx.x) * kChannelsPerCta + threadIdx.x / LANES;
   const bool live = ch_raw < dm;
   const int64_t ch = live ? ch_raw : dm - 1;  // dead lanes shadow a valid channel and never store
   float h[PER], Ar[PER];
@@ -48,73 +62,238 @@ mamba_scan_kernel(const float* __restrict__ u, const float* __restrict__ delta,
   const float* dp = delta + bidx * len * dm + ch;
   const float* zp = z != nullptr ? z + bidx * len * dm + ch : nullptr;
   float* yp = y + bidx * len * dm + ch;
-  const float* Bp = B + bidx * len * NS + sg * PER;
-  const float* Cp = C + bidx * len * NS + sg * PER;
-  // Software pipeline: the operands of the next four steps are in flight while the current four are
-  // computed (two register sets, loop unrolled by two).
-  struct Batch {
-    float uu[U], dd[U], bb[U][PER], cc[U][PER], zmine;
+  const float4* Bp = reinterpret_cast<const float4*>(B + bidx * len * NS + sg * PER);
+  const float4* Cp = reinterpret_cast<const float4*>(C + bidx * len * NS + sg * PER);
+  struct Ahead {
+    float uu[U], dd[U], zz[FIN];
   };
-  auto load = [&](int64_t t0, Batch& b) {
+  auto load = [&](int64_t t0, Ahead& a) {
 #pragma unroll
     for (int j = 0; j < U; ++j) {
       const int64_t t = t0 + j < len ? t0 + j : len - 1;
-      b.uu[j] = __ldg(up + t * dm);
-      b.dd[j] = __ldg(dp + t * dm);
-#pragma unroll
-      for (int n = 0; n < PER; ++n) {
-        b.bb[j][n] = __ldg(Bp + t * NS + n);
-        b.cc[j][n] = __ldg(Cp + t * NS + n);
-      }
+      a.uu[j] = __ldg(up + t * dm);
+      a.dd[j] = __ldg(dp + t * dm);
     }
-    // this lane finishes step t0 + sg: its gate operand
-    const int64_t tmine = t0 + sg < len ? t0 + sg : len - 1;
-    b.zmine = zp != nullptr ? __ldg(zp + tmine * dm) : 0.0f;
+#pragma unroll
+    for (int f = 0; f < FIN; ++f) {   // gate operands of the steps this lane finishes
+      const int64_t tm = t0 + f * LANES + sg;
+      const int64_t t = tm < len ? tm : len - 1;
+      a.zz[f] = zp != nullptr ? __ldg(zp + t * dm) : 0.0f;
+    }
   };
-  auto compute = [&](int64_t t0, const Batch& b) {
-    float da[U][PER];
+  auto compute = [&](int64_t t0, const Ahead& a) {
+    float4 bb[U][PER / 4], cc[U][PER / 4];
 #pragma unroll
     for (int j = 0; j < U; ++j) {
+      const int64_t t = t0 + j < len ? t0 + j : len - 1;
 #pragma unroll
-      for (int n = 0; n < PER; ++n) da[j][n] = exp2f(b.dd[j] * Ar[n]);
+      for (int q = 0; q < PER / 4; ++q) {
+        bb[j][q] = __ldg(Bp + t * (NS / 4) + q);
+        cc[j][q] = __ldg(Cp + t * (NS / 4) + q);
+      }
     }
     float acc[U];
 #pragma unroll
     for (int j = 0; j < U; ++j) {
-      const float du = b.dd[j] * b.uu[j];
-      float a = 0.0f;
+      const float du = a.dd[j] * a.uu[j];
+      float s = 0.0f;
 #pragma unroll
-      for (int n = 0; n < PER; ++n) {
-        h[n] = da[j][n] * h[n] + du * b.bb[j][n];
-        a = a + b.cc[j][n] * h[n];
+      for (int q = 0; q < PER / 4; ++q) {
+        const float bq[4] = {bb[j][q].x, bb[j][q].y, bb[j][q].z, bb[j][q].w};
+        const float cq[4] = {cc[j][q].x, cc[j][q].y, cc[j][q].z, cc[j][q].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int n = q * 4 + e;
+          h[n] = mamba_ex2(a.dd[j] * Ar[n]) * h[n] + du * bq[e];
+          s = s + cq[e] * h[n];
+        }
       }
-      acc[j] = a;
+      acc[j] = s;
     }
 #pragma unroll
     for (int j = 0; j < U; ++j) {
-      acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 1);
-      acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 2);
-    }
-    // every lane now holds all four sums; lane sg finishes step t0 + sg
-    float mine = acc[0], umine = b.uu[0];
 #pragma unroll
-    for (int j = 1; j < U; ++j) {
-      if (sg == j) { mine = acc[j]; umine = b.uu[j]; }
+      for (int o = 1; o < LANES; o <<= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
     }
-    if (live && t0 + sg < len) {
-      float out = mine + Dd * umine;
-      if (zp != nullptr) out = out * (b.zmine * ew_sigmoid(b.zmine));
-      yp[(t0 + sg) * dm] = out;
+#pragma unroll
+    for (int f = 0; f < FIN; ++f) {
+      float mine = acc[f * LANES], umine = a.uu[f * LANES];
+#pragma unroll
+      for (int l = 1; l < LANES; ++l) {
+        if (sg == l) { mine = acc[f * LANES + l]; umine = a.uu[f * LANES + l]; }
+      }
+      const int64_t t = t0 + f * LANES + sg;
+      if (live && t < len) {
+        float out = mine + Dd * umine;
+        if (zp != nullptr) out = out * (a.zz[f] * ew_sigmoid(a.zz[f]));
+        yp[t * dm] = out;
+      }
     }
   };
-  Batch b0, b1;
-  load(0, b0);
+  Ahead a0, a1;
+  load(0, a0);
   for (int64_t t0 = 0; t0 < len; t0 += 2 * U) {
-    load(t0 + U, b1);
-    compute(t0, b0);
-    load(t0 + 2 * U, b0);
-    if (t0 + U < len) compute(t0 + U, b1);   // uniform across the CTA
+    load(t0 + U, a1);
+    compute(t0, a0);
+    load(t0 + 2 * U, a0);
+    if (t0 + U < len) compute(t0 + U, a1);   // uniform across the CTA
   }
+}
+
+// ---- the same recurrence behind a per-warp cp.async pipeline ---------------------------------------
+// The direct kernel above has every thread wait for its own global loads once per iteration: with
+// 2048 sequential steps per thread that latency, not throughput, set the run time.  Here each warp
+// streams its operands (u, delta, z for its 32/LANES channels, the B and C rows) for kPipeTile time
+// steps per stage into shared memory with 16-byte cp.async copies, kPipeStages - 1 stages ahead,
+// and computes from shared memory; warps are independent (no CTA-wide barrier).  Needs
+// dm % (32/LANES) == 0 and 16-byte aligned operands; other shapes take the direct kernel.
+constexpr int kPipeTile = 8;
+constexpr int kPipeStages = 4;
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <int NS, int LANES>
+__host__ __device__ constexpr int mamba_pipe_stage_floats() { return 3 * kPipeTile * (32 / LANES) + 2 * kPipeTile * NS; }
+
+template <int NS, int LANES>
+__global__ void __launch_bounds__(kMambaThreads)
+mamba_scan_pipe_kernel(const float* __restrict__ u, const float* __restrict__ delta,
+                       const float* __restrict__ A, const float* __restrict__ B,
+                       const float* __restrict__ C, const float* __restrict__ D,
+                       const float* __restrict__ z, float* __restrict__ y, int64_t len, int64_t dm) {
+  constexpr int PER = NS / LANES;
+  constexpr int CW = 32 / LANES;             // channels per warp
+  constexpr int TT = kPipeTile, ST = kPipeStages, U = kMambaSteps;
+  constexpr int FIN = U / LANES;
+  constexpr int kStageFloats = mamba_pipe_stage_floats<NS, LANES>();
+  static_assert(PER % 4 == 0 && U % LANES == 0 && TT % U == 0 && CW % 4 == 0, "tile geometry");
+  extern __shared__ float4 mamba_smem4[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* ws = reinterpret_cast<float*>(mamba_smem4) + warp * ST * kStageFloats;
+  const int64_t ch0 = (static_cast<int64_t>(blockIdx.x) * (kMambaThreads / 32) + warp) * CW;
+  if (ch0 >= dm) return;                     // whole warp; warps never wait on each other
+  const int64_t bidx = blockIdx.y;
+  const int sg = lane % LANES, c = lane / LANES;
+  const int64_t ch = ch0 + c;
+  float h[PER], Ar[PER];
+#pragma unroll
+  for (int n = 0; n < PER; ++n) {
+    h[n] = 0.0f;
+    Ar[n] = A[ch * NS + sg * PER + n] * 1.4426950408889634f;
+  }
+  const float Dd = D[ch];
+  const float* ub = u + bidx * len * dm + ch0;
+  const float* db = delta + bidx * len * dm + ch0;
+  const float* zb = z != nullptr ? z + bidx * len * dm + ch0 : nullptr;
+  const float* Bb = B + bidx * len * NS;
+  const float* Cb = C + bidx * len * NS;
+  float* yp = y + bidx * len * dm + ch;
+  const int64_t n_tiles = (len + TT - 1) / TT;
+  // stage layout (floats): u[TT][CW] | delta[TT][CW] | z[TT][CW] | B[TT][NS] | C[TT][NS]
+  auto issue = [&](int64_t tile) {
+    if (tile < n_tiles) {
+      float* st = ws + (tile % ST) * kStageFloats;
+      const int64_t t0 = tile * TT;
+      constexpr int kChunksX = TT * CW / 4, kChunksS = TT * NS / 4;
+      for (int i = lane; i < kChunksX; i += 32) {
+        const int r = i / (CW / 4), q = i % (CW / 4);
+        const int64_t t = t0 + r < len ? t0 + r : len - 1;
+        cp_async16(st + r * CW + q * 4, ub + t * dm + q * 4);
+        cp_async16(st + TT * CW + r * CW + q * 4, db + t * dm + q * 4);
+        if (zb != nullptr) cp_async16(st + 2 * TT * CW + r * CW + q * 4, zb + t * dm + q * 4);
+      }
+      for (int i = lane; i < kChunksS; i += 32) {
+        const int r = i / (NS / 4), q = i % (NS / 4);
+        const int64_t t = t0 + r < len ? t0 + r : len - 1;
+        cp_async16(st + 3 * TT * CW + r * NS + q * 4, Bb + t * NS + q * 4);
+        cp_async16(st + 3 * TT * CW + TT * NS + r * NS + q * 4, Cb + t * NS + q * 4);
+      }
+    }
+    cp_async_commit();   // an empty group keeps the group count uniform
+  };
+  for (int s = 0; s < ST - 1; ++s) issue(s);
+  for (int64_t tile = 0; tile < n_tiles; ++tile) {
+    issue(tile + ST - 1);
+    cp_async_wait<ST - 1>();
+    __syncwarp();
+    const float* st = ws + (tile % ST) * kStageFloats;
+    const float* su = st;
+    const float* sd = st + TT * CW;
+    const float* sz = st + 2 * TT * CW;
+    const float* sB = st + 3 * TT * CW + sg * PER;
+    const float* sC = sB + TT * NS;
+#pragma unroll
+    for (int g = 0; g < TT / U; ++g) {
+      float acc[U], uu[U];
+#pragma unroll
+      for (int j = 0; j < U; ++j) {
+        const int r = g * U + j;
+        const float dd = sd[r * CW + c];
+        uu[j] = su[r * CW + c];
+        const float du = dd * uu[j];
+        float sum = 0.0f;
+#pragma unroll
+        for (int q = 0; q < PER / 4; ++q) {
+          const float4 b4 = *reinterpret_cast<const float4*>(sB + r * NS + q * 4);
+          const float4 c4 = *reinterpret_cast<const float4*>(sC + r * NS + q * 4);
+          const float bq[4] = {b4.x, b4.y, b4.z, b4.w};
+          const float cq[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int n = q * 4 + e;
+            h[n] = mamba_ex2(dd * Ar[n]) * h[n] + du * bq[e];
+            sum = sum + cq[e] * h[n];
+          }
+        }
+        acc[j] = sum;
+      }
+#pragma unroll
+      for (int j = 0; j < U; ++j) {
+#pragma unroll
+        for (int o = 1; o < LANES; o <<= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+      }
+#pragma unroll
+      for (int f = 0; f < FIN; ++f) {
+        float mine = acc[f * LANES], umine = uu[f * LANES];
+#pragma unroll
+        for (int l = 1; l < LANES; ++l) {
+          if (sg == l) { mine = acc[f * LANES + l]; umine = uu[f * LANES + l]; }
+        }
+        const int r = g * U + f * LANES + sg;
+        const int64_t t = tile * TT + r;
+        if (t < len) {
+          float out = mine + Dd * umine;
+          if (zb != nullptr) {
+            const float zz = sz[r * CW + c];
+            out = out * (zz * ew_sigmoid(zz));
+          }
+          yp[t * dm] = out;
+        }
+      }
+    }
+    __syncwarp();   // every lane is done with this stage before the next issue overwrites it
+  }
+}
+
+// Lanes per channel for a state size; FRAME_B200_MAMBA_LANES (1, 2 or 4) overrides it for
+// measurements.
+static int mamba_lanes(int64_t nstate) {
+  static const int forced = [] {
+    const char* e = getenv("FRAME_B200_MAMBA_LANES");
+    return e != nullptr ? atoi(e) : 0;
+  }();
+  const int natural = nstate >= 16 ? 2 : (nstate >= 8 ? 2 : 1);
+  if (forced == 1 || forced == 2 || forced == 4) {
+    if (nstate / forced >= 4) return forced;
+  }
+  return natural;
 }
 
 }  // namespace fb200
@@ -136,8 +315,6 @@ extern "C" int fb200_mamba_scan(const void* u, const void* delta, const void* A,
   }
   if (batch > 65535) return set_error(FB200_INVALID_ARGUMENT, "mamba_scan: batch > 65535");
   cudaStream_t s = as_stream(stream);
-  dim3 grid(static_cast<unsigned>((dm + kMambaChannelsPerCta - 1) / kMambaChannelsPerCta),
-            static_cast<unsigned>(batch));
   const float* up = static_cast<const float*>(u);
   const float* dp = static_cast<const float*>(delta);
   const float* Ap = static_cast<const float*>(A);
@@ -146,12 +323,36 @@ extern "C" int fb200_mamba_scan(const void* u, const void* delta, const void* A,
   const float* Dp = static_cast<const float*>(D);
   const float* zp = static_cast<const float*>(z);
   float* yp = static_cast<float*>(y);
+  if (!aligned16(B) || !aligned16(C)) return set_error(FB200_INVALID_ARGUMENT, "mamba_scan: B and C must be 16-byte aligned");
+  const int lanes = mamba_lanes(nstate);
+  const int per_cta = kMambaThreads / lanes;
+  dim3 grid(static_cast<unsigned>((dm + per_cta - 1) / per_cta), static_cast<unsigned>(batch));
+  const int cw = 32 / lanes;
+  const bool piped = dm % cw == 0 && dm % 4 == 0 && aligned16(u) && aligned16(delta) &&
+                     (z == nullptr || aligned16(z)) && getenv("FRAME_B200_MAMBA_DIRECT") == nullptr;
+  if (piped) grid.x = static_cast<unsigned>((dm / cw + kMambaThreads / 32 - 1) / (kMambaThreads / 32));
+#define FB200_MAMBA_LAUNCH(NS, LN)                                                                   \
+  do {                                                                                               \
+    if (piped) {                                                                                     \
+      const size_t smem = size_t(kMambaThreads / 32) * kPipeStages * mamba_pipe_stage_floats<NS, LN>() * 4; \
+      auto kernel = mamba_scan_pipe_kernel<NS, LN>;                                                  \
+      FB200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
+                                         static_cast<int>(smem)));                                   \
+      kernel<<<grid, kMambaThreads, smem, s>>>(up, dp, Ap, Bp, Cp, Dp, zp, yp, len, dm);             \
+    } else {                                                                                         \
+      mamba_scan_kernel<NS, LN><<<grid, kMambaThreads, 0, s>>>(up, dp, Ap, Bp, Cp, Dp, zp, yp, len, dm); \
+    }                                                                                                \
+  } while (0)
   if (nstate == 16) {
-    mamba_scan_kernel<16><<<grid, kMambaThreads, 0, s>>>(up, dp, Ap, Bp, Cp, Dp, zp, yp, len, dm);
+    if (lanes == 4) { FB200_MAMBA_LAUNCH(16, 4); }
+    else if (lanes == 2) { FB200_MAMBA_LAUNCH(16, 2); }
+    else { FB200_MAMBA_LAUNCH(16, 1); }
   } else if (nstate == 8) {
-    mamba_scan_kernel<8><<<grid, kMambaThreads, 0, s>>>(up, dp, Ap, Bp, Cp, Dp, zp, yp, len, dm);
+    if (lanes == 2) { FB200_MAMBA_LAUNCH(8, 2); }
+    else { FB200_MAMBA_LAUNCH(8, 1); }
   } else {
-    mamba_scan_kernel<4><<<grid, kMambaThreads, 0, s>>>(up, dp, Ap, Bp, Cp, Dp, zp, yp, len, dm);
+    FB200_MAMBA_LAUNCH(4, 1);
   }
+#undef FB200_MAMBA_LAUNCH
   return after_launch("mamba_scan_kernel");
 }

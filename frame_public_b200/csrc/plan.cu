@@ -29,7 +29,7 @@ namespace fb200 {
 
 enum class Kind {
   kMatmul, kConv2d, kConv1d, kMaxPool, kChain, kBiasAdd, kSoftmax, kLayerNorm, kScan, kMambaScan,
-  kTranspose, kSlice, kConcat, kSum, kCopy, kAlias, kConstant, kSkip, kAttentionFan
+  kTranspose, kSlice, kConcat, kSum, kCopy, kAlias, kConstant, kSkip, kAttentionFan, kDwConvTimeMajor
 };
 
 struct SlotInfo {
@@ -65,6 +65,9 @@ struct Step {
   int fan_q = -1, fan_k = -1, fan_v = -1, fan_dest = -1;
   int64_t fan_heads = 0, fan_sq = 0, fan_sk = 0;
   void* fan_table = nullptr;
+  // kDwConvTimeMajor: input matrix slot and column window, weights, bias, geometry
+  int dw_x = -1, dw_w = -1, dw_bias = -1;
+  int64_t dw_col = 0, dw_ld = 0, dw_batch = 0, dw_len = 0, dw_out_len = 0, dw_channels = 0, dw_k = 0, dw_shift = 0;
 };
 
 }  // namespace fb200
@@ -528,7 +531,7 @@ static std::vector<std::pair<int, int>> readers_of(const fb200_plan& p, int slot
   const int root = root_slot(p, slot);
   for (size_t j = 0; j < p.steps.size(); ++j) {
     const Step& s = p.steps[j];
-    if (s.kind == Kind::kSkip) continue;
+    if (s.kind == Kind::kSkip || s.kind == Kind::kAlias) continue;
     for (size_t i = 0; i < s.in.size(); ++i) {
       if (root_slot(p, s.in[i]) == root) out.emplace_back(static_cast<int>(j), static_cast<int>(i));
     }
@@ -744,6 +747,179 @@ static void fuse_attention_fans(fb200_plan* p) {
   }
 }
 
+static bool step_runs(const Step& s) {
+  return s.kind != Kind::kSkip && s.kind != Kind::kAlias && s.kind != Kind::kConstant;
+}
+
+// Index of the step that writes the bytes of `slot` (through its own output or as the fused
+// result of a contraction), or -1.
+static int writer_of(const fb200_plan& p, int slot) {
+  const int root = root_slot(p, slot);
+  for (size_t j = 0; j < p.steps.size(); ++j) {
+    const Step& s = p.steps[j];
+    if (!step_runs(s) || s.write_slot < 0) continue;
+    if (root_slot(p, s.write_slot) == root) return static_cast<int>(j);
+  }
+  return -1;
+}
+
+// Does step `s` read or write bytes overlapping `slot`, other than through slots rooted at `own`?
+static bool step_touches(const fb200_plan& p, const Step& s, int slot, int own) {
+  auto hit = [&](int x) { return x >= 0 && root_slot(p, x) != own && ranges_overlap(p, x, slot); };
+  for (int x : s.in) if (hit(x)) return true;
+  for (int x : s.epi_operand_slot) if (hit(x)) return true;
+  if (hit(s.write_slot)) return true;
+  for (int x : {s.fan_q, s.fan_k, s.fan_v, s.fan_dest, s.dw_x, s.dw_w, s.dw_bias}) if (hit(x)) return true;
+  return false;
+}
+
+// reshape whose source could not become the view (the planner reuses the source's bytes while the
+// result is live): make the SOURCE a view of the result instead, i.e. let the source's producer
+// write where the planner put the reshape's output (an arena range, or the caller's output
+// buffer).  Safe when no step that runs between that producer and the reshape touches those
+// bytes, and the source is not read after the result's bytes may be reused.
+static void alias_reshape_sources(fb200_plan* p) {
+  const int n = static_cast<int>(p->steps.size());
+  // Last reshape first: in a chain a -> b -> c, b must already share c's bytes when a is considered,
+  // because b's own planned bytes may be what a's producer reads.
+  for (int i = n - 1; i >= 0; --i) {
+    Step& s = p->steps[static_cast<size_t>(i)];
+    if (s.op != "reshape" || s.kind != Kind::kCopy || s.in.size() != 1 || s.out.size() != 1) continue;
+    const int dst = s.out[0];
+    const int r = root_slot(*p, s.in[0]);
+    const int dr = root_slot(*p, dst);
+    const SlotInfo& rs = p->slots[static_cast<size_t>(r)];
+    const SlotInfo& ds = p->slots[static_cast<size_t>(dr)];
+    if (r == dr) continue;
+    if (rs.arena_offset < 0 || rs.input_index >= 0 || rs.output_index >= 0 || rs.constant != nullptr) continue;
+    if (ds.bytes() != rs.bytes() || ds.numel == 0 || ds.input_index >= 0 || ds.constant != nullptr) continue;
+    if (ds.arena_offset < 0 && ds.output_index < 0) continue;
+    const int d = writer_of(*p, r);
+    if (d < 0 || d >= i) continue;
+    const int src_last = last_use(*p, r), dst_last = std::max(i, last_use(*p, dst));
+    if (src_last > dst_last) continue;
+    bool safe = true;
+    for (int j = d; j < i && safe; ++j) {
+      const Step& t = p->steps[static_cast<size_t>(j)];
+      if (step_runs(t) && step_touches(*p, t, dst, r)) safe = false;
+    }
+    if (!safe) continue;
+    p->slots[static_cast<size_t>(r)].alias_of = dst;
+    s.kind = Kind::kAlias;
+  }
+}
+
+// transpose(0,2,1) -> conv1d(groups = channels, stride 1) [-> slice along time] [-> unary chain]
+// -> transpose(0,2,1)  becomes one time-major depthwise convolution at the position of the last
+// transpose.  The input may be a column window of a wider matrix (a `slice` along the columns
+// followed by a reshape that became a view): it is then read in place.  The result is written
+// where and when the planner expected the last transpose's output, so only the inputs move in
+// time: the group is formed when no step that still runs in between writes bytes overlapping the
+// input matrix, the weights or the bias, and the result does not overlap them either.
+static void fuse_time_major_convs(fb200_plan* p) {
+  const int n = static_cast<int>(p->steps.size());
+  std::vector<int> producer(p->slots.size(), -1);
+  for (int i = 0; i < n; ++i) for (int o : p->steps[static_cast<size_t>(i)].out) producer[static_cast<size_t>(o)] = i;
+  auto sole_reader = [&](int slot, int* step) {
+    if (p->slots[static_cast<size_t>(slot)].output_index >= 0) return false;
+    const auto r = readers_of(*p, slot);
+    if (r.size() != 1 || r[0].second < 0) return false;
+    *step = r[0].first;
+    return true;
+  };
+  auto is_time_swap = [](const Step& t) {
+    return t.kind == Kind::kTranspose && t.iv.size() == 3 && t.iv[0] == 0 && t.iv[1] == 2 && t.iv[2] == 1;
+  };
+  for (int ci = 0; ci < n; ++ci) {
+    Step& cv = p->steps[static_cast<size_t>(ci)];
+    if (cv.kind != Kind::kConv1d || cv.in.size() < 2) continue;
+    const SlotInfo& xs = p->slots[static_cast<size_t>(cv.in[0])];
+    const SlotInfo& ws = p->slots[static_cast<size_t>(cv.in[1])];
+    if (xs.dims.size() != 3 || ws.dims.size() != 3) continue;
+    const int64_t batch = xs.dims[0], chan = xs.dims[1], len = xs.dims[2], k = ws.dims[2];
+    const int64_t stride = cv.iv[0], padding = cv.iv[1], groups = cv.iv[2];
+    if (stride != 1 || groups != chan || ws.dims[0] != chan || ws.dims[1] != 1 || k < 1 || k > 8) continue;
+    const int vec = 16 / itemsize_of(xs.dtype);
+    if (!is_float_dtype(xs.dtype) || chan % vec != 0 || batch > 65535) continue;
+    const int t1 = producer[static_cast<size_t>(cv.in[0])];
+    if (t1 < 0 || !is_time_swap(p->steps[static_cast<size_t>(t1)])) continue;
+    int step = -1;
+    if (!sole_reader(cv.in[0], &step) || step != ci) continue;
+    std::vector<int> members = {t1, ci};
+    int cur = cv.out[0];
+    int64_t start = 0, out_len = len + 2 * padding - k + 1;
+    if (!sole_reader(cur, &step)) continue;
+    if (p->steps[static_cast<size_t>(step)].kind == Kind::kSlice && p->steps[static_cast<size_t>(step)].iv[0] == 2) {
+      const Step& sl = p->steps[static_cast<size_t>(step)];
+      if (sl.iv[1] < 0 || sl.iv[2] > out_len || sl.iv[2] < sl.iv[1]) continue;
+      start = sl.iv[1];
+      out_len = sl.iv[2] - sl.iv[1];
+      members.push_back(step);
+      cur = sl.out[0];
+      if (!sole_reader(cur, &step)) continue;
+    }
+    std::vector<int> ops;
+    if (p->steps[static_cast<size_t>(step)].kind == Kind::kChain) {
+      const Step& ch = p->steps[static_cast<size_t>(step)];
+      bool unary = ch.in.size() == 1;
+      for (int a : ch.chain_arity) if (a != 1) unary = false;
+      if (!unary || p->slots[static_cast<size_t>(ch.out[0])].dtype != xs.dtype) continue;
+      ops = ch.chain_ops;
+      members.push_back(step);
+      cur = ch.out[0];
+      if (!sole_reader(cur, &step)) continue;
+    }
+    if (!is_time_swap(p->steps[static_cast<size_t>(step)])) continue;
+    const int t2 = step;
+    Step& last = p->steps[static_cast<size_t>(t2)];
+    if (last.write_slot != last.out[0] || out_len > 65535 * 32) continue;
+    // the time-major input: a matrix of its own, or a column window of a wider rank-2 matrix
+    const int a_root = root_slot(*p, p->steps[static_cast<size_t>(t1)].in[0]);
+    int x_slot = a_root, slice_step = -1;
+    int64_t col = 0, ld = chan;
+    const int ap = writer_of(*p, a_root);
+    if (ap >= 0 && p->steps[static_cast<size_t>(ap)].kind == Kind::kSlice) {
+      const Step& sl = p->steps[static_cast<size_t>(ap)];
+      const SlotInfo& wide = p->slots[static_cast<size_t>(sl.in[0])];
+      if (wide.dims.size() == 2 && sl.iv[0] == 1 && sl.iv[1] >= 0 && sl.iv[2] - sl.iv[1] == chan &&
+          wide.dims[0] == batch * len && wide.dims[1] % vec == 0 && sl.iv[1] % vec == 0 &&
+          readers_of(*p, a_root).size() == 1) {
+        x_slot = sl.in[0];
+        col = sl.iv[1];
+        ld = wide.dims[1];
+        slice_step = ap;
+      }
+    }
+    // tentatively drop the group, then check that the inputs survive until the launch
+    std::vector<Kind> saved(static_cast<size_t>(n));
+    for (int i = 0; i < n; ++i) saved[static_cast<size_t>(i)] = p->steps[static_cast<size_t>(i)].kind;
+    for (int m : members) p->steps[static_cast<size_t>(m)].kind = Kind::kSkip;
+    if (slice_step >= 0) p->steps[static_cast<size_t>(slice_step)].kind = Kind::kSkip;
+    bool ok = true;
+    const int bias_slot = cv.in.size() > 2 ? cv.in[2] : -1;
+    for (int src : {x_slot, cv.in[1], bias_slot}) {
+      if (src < 0) continue;
+      if (ranges_overlap(*p, src, last.out[0])) ok = false;
+      const int from = std::max(writer_of(*p, src), producer[static_cast<size_t>(root_slot(*p, src))]);
+      for (int j = from + 1; j < t2 && ok; ++j) {
+        const Step& t = p->steps[static_cast<size_t>(j)];
+        if (!step_runs(t)) continue;
+        if (t.write_slot >= 0 && ranges_overlap(*p, t.write_slot, src)) ok = false;
+        if (t.kind == Kind::kAttentionFan && ranges_overlap(*p, t.fan_dest, src)) ok = false;
+      }
+    }
+    if (!ok) {
+      for (int i = 0; i < n; ++i) p->steps[static_cast<size_t>(i)].kind = saved[static_cast<size_t>(i)];
+      continue;
+    }
+    last.kind = Kind::kDwConvTimeMajor;
+    last.dw_x = x_slot; last.dw_w = cv.in[1]; last.dw_bias = bias_slot;
+    last.dw_col = col; last.dw_ld = ld; last.dw_batch = batch; last.dw_len = len;
+    last.dw_out_len = out_len; last.dw_channels = chan; last.dw_k = k; last.dw_shift = start - padding;
+    last.chain_ops = ops;
+  }
+}
+
 static void* slot_ptr(fb200_plan* p, int slot, const void* const* inputs, void* const* outputs) {
   const int r = root_slot(*p, slot);
   const SlotInfo& s = p->slots[r];
@@ -865,6 +1041,14 @@ static int run_step(fb200_plan* p, Step& s, const void* const* inputs, void* con
                             in_slot(0).dims.data(), s.iv.data(), static_cast<int>(s.iv.size()), os.dtype, stream);
     case Kind::kCopy:
       return fb200_memcpy(p->device, out, in_ptr(0), os.bytes(), FB200_D2D, stream, 0);
+    case Kind::kDwConvTimeMajor: {
+      const char* x = static_cast<const char*>(slot_ptr(p, s.dw_x, inputs, outputs)) + s.dw_col * itemsize_of(os.dtype);
+      return fb200_dwconv1d_time_major(x, s.dw_ld, slot_ptr(p, s.dw_w, inputs, outputs),
+                                       s.dw_bias >= 0 ? slot_ptr(p, s.dw_bias, inputs, outputs) : nullptr, out,
+                                       s.dw_channels, s.dw_batch, s.dw_len, s.dw_out_len, s.dw_channels, s.dw_k,
+                                       s.dw_shift, s.chain_ops.data(), static_cast<int>(s.chain_ops.size()),
+                                       os.dtype, stream);
+    }
     case Kind::kAttentionFan: {
       const SlotInfo& qb = p->slots[static_cast<size_t>(s.fan_q)];
       const SlotInfo& kb = p->slots[static_cast<size_t>(s.fan_k)];
@@ -916,7 +1100,11 @@ extern "C" int fb200_plan_create(const char* plan_text, int device, int allow_tf
     return rc;
   }
   optimise(p);
-  if (p->opt_level >= 1) fuse_attention_fans(p);
+  if (p->opt_level >= 1) {
+    alias_reshape_sources(p);
+    fuse_attention_fans(p);
+    fuse_time_major_convs(p);
+  }
   if (const char* env = getenv("FRAME_B200_GRAPH")) p->graph_enabled = atoi(env) != 0;
   p->launches = 0;
   for (const Step& s : p->steps) {
@@ -1111,6 +1299,7 @@ extern "C" const char* fb200_plan_step_op(const fb200_plan* p, int index) {
   const Step& s = p->steps[static_cast<size_t>(index)];
   if (s.kind == Kind::kSkip) name = "(absorbed)";
   else if (s.kind == Kind::kAttentionFan) name = "attention_fan";
+  else if (s.kind == Kind::kDwConvTimeMajor) name = "dwconv1d_time_major";
   else if (s.kind == Kind::kAlias) name = "(alias)";
   else if ((s.kind == Kind::kMatmul || s.kind == Kind::kConv2d) && !s.chain_ops.empty()) name = s.op + "+epilogue";
   else name = s.op;

@@ -198,6 +198,20 @@ FB200_API int fb200_conv2d(const void* x, const void* w, const void* bias, void*
 FB200_API int fb200_conv1d(const void* x, const void* w, const void* bias, void* out, int64_t n,
                            int64_t cin, int64_t l, int64_t cout, int64_t k, int64_t stride,
                            int64_t padding, int64_t groups, int dtype, fb200_stream stream);
+/* Depthwise conv1d along time in the TIME-MAJOR layout, with trailing unary elementwise ops.
+ * Stands behind the five-step group transpose [B,L,C]->[B,C,L], conv1d(groups = C), slice,
+ * activation, transpose back of the reference's Mamba block (src/nn/layers.cpp:1596-1602; conv1d:
+ * src/backends/cpu/kernels/conv.cpp:565-589), with the same operations in the same order:
+ *   out[b,t,c] = ops(bias[c] + sum_k w[c,k] * x[b, t+shift+k, c]),  taps outside [0, len) skipped,
+ * shift = slice_start - padding (-(k-1) for the causal form).  x: [batch, len] rows of pitch x_ld
+ * (a column window of a wider matrix works), out: [batch, out_len] rows of pitch out_ld, w: [C,1,k],
+ * bias: [C] or NULL.  channels and both pitches must be multiples of the 16-byte vector width;
+ * 1 <= k <= 8; unary_ops: FB200_EW_* codes applied in order, each rounded to the dtype. */
+FB200_API int fb200_dwconv1d_time_major(const void* x, int64_t x_ld, const void* w, const void* bias,
+                                        void* out, int64_t out_ld, int64_t batch, int64_t len,
+                                        int64_t out_len, int64_t channels, int64_t k, int64_t shift,
+                                        const int* unary_ops, int n_ops, int dtype,
+                                        fb200_stream stream);
 /* max_pool2d: max over valid positions only, first maximum wins
  * (src/backends/cpu/kernels/pool.cpp:187-233; replaces cudnnPoolingForward,
  * src/backends/cuda/kernels/pool.cpp:231). */

@@ -12,7 +12,8 @@ from oracle import frame_oracle as fo
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("shape", [(2, 9, 5, 4), (1, 33, 40, 16), (3, 64, 70, 16), (2, 17, 32, 8)],
+@pytest.mark.parametrize("shape", [(2, 9, 5, 4), (1, 33, 40, 16), (3, 64, 70, 16), (2, 17, 32, 8),
+                                   (2, 100, 48, 16), (1, 8, 64, 16), (1, 3, 32, 4)],  # cp.async pipeline
                          ids=lambda s: "x".join(map(str, s)))
 @pytest.mark.parametrize("gated", [True, False], ids=["gated", "ungated"])
 def test_mamba_scan_matches_oracle(shape, gated):

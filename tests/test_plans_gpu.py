@@ -85,3 +85,23 @@ def test_attention_heads_become_one_launch():
     (b,) = plain.run_host(wl.inputs)
     assert capi.kernel_status(0) == 0
     assert fo.all_close(a, b, wl.dtype, rtol=2e-2, atol=2e-2), fo.max_err(a, b, wl.dtype)
+
+
+def test_mamba_conv_group_becomes_one_time_major_launch():
+    """transpose, conv1d, slice, silu, transpose of the Mamba block run as one depthwise convolution
+    over the time-major tensor, reading the in_proj output in place.  Whether the group forms depends
+    on where the planner put the buffers (in the miniature plan the x_proj output overlaps the bytes
+    the result would need, so it stays step by step); the 2-sample plan of the benchmark shape does
+    form it, and must give the numbers of the step-by-step path (strict fp32: same operations)."""
+    wl = configs.mamba_block(batch=2)
+    text = runtime.load_plan_text(wl.name)
+    fused = runtime.CompiledPlan(text, 0, opt_level=1)
+    plain = runtime.CompiledPlan(text, 0, opt_level=0)
+    names = fused.step_names()
+    assert names.count("dwconv1d_time_major") == 1
+    assert "conv1d" not in names and "transpose" not in names
+    assert fused.launches_per_run < plain.launches_per_run
+    (a,) = fused.run_host(wl.inputs)
+    (b,) = plain.run_host(wl.inputs)
+    assert capi.kernel_status(0) == 0
+    assert fo.all_close(a, b, wl.dtype, rtol=1e-5, atol=1e-6), fo.max_err(a, b, wl.dtype)
