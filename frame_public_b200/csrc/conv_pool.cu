@@ -425,9 +425,23 @@ dwconv1d_time_major_kernel(const T* __restrict__ x, int64_t x_ld, const T* __res
   };
 #pragma unroll
   for (int j = 0; j < K - 1; ++j) fetch(t_begin + shift + j, rows[j], valid[j]);
+  // the U new rows of the next group are in flight while the current group is computed
+  float ahead[U][V];
+  bool ahead_valid[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) fetch(t_begin + u + shift + K - 1, ahead[u], ahead_valid[u]);
   for (int64_t t = t_begin; t < t_end; t += U) {
 #pragma unroll
-    for (int u = 0; u < U; ++u) fetch(t + u + shift + K - 1, rows[K - 1 + u], valid[K - 1 + u]);
+    for (int u = 0; u < U; ++u) {
+#pragma unroll
+      for (int v = 0; v < V; ++v) rows[K - 1 + u][v] = ahead[u][v];
+      valid[K - 1 + u] = ahead_valid[u];
+    }
+    if (t + U < t_end) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) fetch(t + U + u + shift + K - 1, ahead[u], ahead_valid[u]);
+    }
+    float res[U * V];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       float acc[V];
@@ -443,11 +457,19 @@ dwconv1d_time_major_kernel(const T* __restrict__ x, int64_t x_ld, const T* __res
 #pragma unroll
       for (int v = 0; v < V; ++v) {
         if (bias != nullptr) acc[v] += bv[v];
-        float r = round_through<T>(acc[v]);
-        for (int o = 0; o < ops.n; ++o) r = round_through<T>(ew_unary(ops.op[o], r));
-        acc[v] = r;
+        res[u * V + v] = round_through<T>(acc[v]);
       }
-      if (t + u < t_end) store_vec<T>(ob + (t + u) * out_ld, acc);
+    }
+#pragma unroll 1
+    for (int o = 0; o < ops.n; ++o) ew_unary_vec<T, U * V>(ops.op[o], res);   // one switch per group
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (t + u < t_end) {
+        float outv[V];
+#pragma unroll
+        for (int v = 0; v < V; ++v) outv[v] = res[u * V + v];
+        store_vec<T>(ob + (t + u) * out_ld, outv);
+      }
     }
 #pragma unroll
     for (int j = 0; j < K - 1; ++j) {   // the last K-1 rows become the next group's history

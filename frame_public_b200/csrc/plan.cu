@@ -781,7 +781,11 @@ static bool step_touches(const fb200_plan& p, const Step& s, int slot, int own) 
 static void alias_reshape_sources(fb200_plan* p) {
   const int n = static_cast<int>(p->steps.size());
   // Last reshape first: in a chain a -> b -> c, b must already share c's bytes when a is considered,
-  // because b's own planned bytes may be what a's producer reads.
+  // because b's own planned bytes may be what a's producer reads.  A reshape that became a view
+  // no longer reads or writes anything, which can make an earlier candidate safe: sweep until
+  // nothing changes.
+  for (int sweep = 0, changed = 1; changed && sweep < 8; ++sweep) {
+  changed = 0;
   for (int i = n - 1; i >= 0; --i) {
     Step& s = p->steps[static_cast<size_t>(i)];
     if (s.op != "reshape" || s.kind != Kind::kCopy || s.in.size() != 1 || s.out.size() != 1) continue;
@@ -806,6 +810,8 @@ static void alias_reshape_sources(fb200_plan* p) {
     if (!safe) continue;
     p->slots[static_cast<size_t>(r)].alias_of = dst;
     s.kind = Kind::kAlias;
+    changed = 1;
+  }
   }
 }
 

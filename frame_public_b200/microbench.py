@@ -7,7 +7,7 @@ measured peak (MEASURED_PEAKS.json at the repository root, when present).
     python -m frame_public_b200.microbench --op gemm --m 4096 --n 4096 --k 4096 --dtype bf16
 
 Ops: fused_add_relu, gelu, silu, softmax, layer_norm, scan_rows, mamba_scan, transpose, slice,
-max_pool, conv1d_depthwise, conv2d_tf32, attention (--batch, --cols = sequence length, --m = model
+max_pool, conv1d_depthwise, dwconv_time_major, conv2d_tf32, attention (--batch, --cols = sequence length, --m = model
 width), gemm.  Inputs are seeded random data; between timed
 launches nothing is flushed, so choose sizes larger than the 126 MB L2 for HBM figures.  This is
 also the command the ncu captures summarised under profiles/ were taken with.
@@ -129,6 +129,13 @@ def main():
         o = capi.DeviceBuffer(bt * ch * (L + 3) * es)
         fn = lambda: capi.conv1d(x.ptr, w.ptr, b.ptr, o.ptr, bt, ch, L, ch, 4, 1, 3, ch, dt)
         nbytes = (bt * ch * L + bt * ch * (L + 3)) * es
+    elif a.op == "dwconv_time_major":
+        # the Mamba block's causal conv: a 1536-wide window of the [batch*len, 3072] in_proj output
+        bt, L, ch = a.batch, a.cols, a.m
+        x, w, b = _rand((bt * L, 2 * ch), dt, rng), _rand((ch, 1, 4), dt, rng), _rand((ch,), dt, rng)
+        o = capi.DeviceBuffer(bt * L * ch * es)
+        fn = lambda: capi.dwconv1d_time_major(x.ptr, 2 * ch, w.ptr, b.ptr, o.ptr, ch, bt, L, L, ch, 4, -3, ["silu"], dt)
+        nbytes = 2 * bt * L * ch * es
     elif a.op == "conv2d_tf32":
         n, cin, h, cout, k = a.batch, 64, 56, 64, 3
         x, w, b = _rand((n, cin, h, h), capi.F32, rng), _rand((cout, cin, k, k), capi.F32, rng), _rand((cout,), capi.F32, rng)
