@@ -12,6 +12,8 @@
 // drops the whole graph to its eager fallback (src/ops/schemas/conv.cpp:1021-1032).
 // max_pool2d follows src/backends/cpu/kernels/pool.cpp:187-233 (valid taps only, first maximum
 // wins) and replaces cudnnPoolingForward (src/backends/cuda/kernels/pool.cpp:231).
+#include <cstdlib>
+
 #include "common.cuh"
 #include "epilogue.cuh"
 
@@ -180,6 +182,56 @@ max_pool2d_kernel(const T* __restrict__ x, T* __restrict__ out, IDX nc, IDX h, I
   }
 }
 
+// Small fixed windows (3x3, 2x2): every tap is loaded from a clamped, always valid address before
+// any comparison, so the loads of a window are all in flight together (with the bounds checks as
+// branches in front of each load, a thread waited for up to nine memory round trips in a row and
+// the kernel ran at a fifth of the copy bandwidth).  Selection order and result are unchanged.
+template <typename T, int KH, int KW>
+__global__ void __launch_bounds__(256)
+max_pool2d_window_kernel(const T* __restrict__ x, T* __restrict__ out, int nc, int h, int w, int sh,
+                         int sw, int ph, int pw, int oh, int ow) {
+  const int total = nc * oh * ow;
+  const int stride = static_cast<int>(gridDim.x) * blockDim.x;
+  for (int i = static_cast<int>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int q = i % ow;
+    int rem = i / ow;
+    const int o = rem % oh;
+    rem /= oh;  // (n, c) plane
+    const T* xc = x + static_cast<int64_t>(rem) * h * w;
+    T raw[KH][KW];
+    bool ok[KH][KW];
+#pragma unroll
+    for (int a = 0; a < KH; ++a) {
+      const int ih = o * sh - ph + a;
+      const bool okh = ih >= 0 && ih < h;
+      const int ihc = ih < 0 ? 0 : (ih >= h ? h - 1 : ih);
+#pragma unroll
+      for (int b = 0; b < KW; ++b) {
+        const int iw = q * sw - pw + b;
+        const int iwc = iw < 0 ? 0 : (iw >= w ? w - 1 : iw);
+        ok[a][b] = okh && iw >= 0 && iw < w;
+        raw[a][b] = xc[ihc * w + iwc];
+      }
+    }
+    bool found = false;
+    float best = 0.0f;
+    T best_raw = T{};
+#pragma unroll
+    for (int a = 0; a < KH; ++a) {
+#pragma unroll
+      for (int b = 0; b < KW; ++b) {
+        const float v = to_f32(raw[a][b]);
+        if (ok[a][b] && (!found || v > best)) {
+          found = true;
+          best = v;
+          best_raw = raw[a][b];
+        }
+      }
+    }
+    out[i] = best_raw;
+  }
+}
+
 }  // namespace fb200
 
 using namespace fb200;
@@ -189,6 +241,11 @@ using namespace fb200;
 extern "C" int fb200_conv2d_tcgen05(const void* x, const void* w, const void* bias, void* out,
                                     const fb200_conv2d_params* p, int dtype,
                                     const fb200_epilogue* epilogue, fb200_stream stream);
+
+// Implemented in conv_halo_tcgen05.cu: the halo-tile variant, tried first.
+extern "C" int fb200_conv2d_halo_tcgen05(const void* x, const void* w, const void* bias, void* out,
+                                         const fb200_conv2d_params* p, int dtype,
+                                         const fb200_epilogue* epilogue, fb200_stream stream);
 
 extern "C" int fb200_conv2d(const void* x, const void* w, const void* bias, void* out,
                             const fb200_conv2d_params* pp, int dtype, int allow_tf32,
@@ -219,6 +276,11 @@ extern "C" int fb200_conv2d(const void* x, const void* w, const void* bias, void
     return set_error(FB200_INVALID_ARGUMENT, "conv2d: null argument");
   }
   if (allow_tf32 && dtype == FB200_F32) {
+    static const bool no_halo = getenv("FRAME_B200_CONV_GATHER") != nullptr;   // measurement knob
+    if (!no_halo) {
+      const int rc = fb200_conv2d_halo_tcgen05(x, w, bias, out, pp, dtype, epilogue, stream);
+      if (rc != FB200_UNIMPLEMENTED) return rc;
+    }
     const int rc = fb200_conv2d_tcgen05(x, w, bias, out, pp, dtype, epilogue, stream);
     if (rc != FB200_UNIMPLEMENTED) return rc;
   }
@@ -341,7 +403,18 @@ extern "C" int fb200_max_pool2d(const void* x, void* out, int64_t n, int64_t c, 
   const bool small = n * c * h * w < (int64_t(1) << 31);
   auto run = [&](auto tag) {
     using T = decltype(tag);
-    if (small) {
+    if (small && ((kh == 3 && kw == 3) || (kh == 2 && kw == 2))) {
+      const T* xp = static_cast<const T*>(x);
+      T* op = static_cast<T*>(out);
+      const int a[9] = {static_cast<int>(n * c), static_cast<int>(h), static_cast<int>(w),
+                        static_cast<int>(stride_h), static_cast<int>(stride_w), static_cast<int>(pad_h),
+                        static_cast<int>(pad_w), static_cast<int>(oh), static_cast<int>(ow)};
+      if (kh == 3) {
+        max_pool2d_window_kernel<T, 3, 3><<<grid, 256, 0, s>>>(xp, op, a[0], a[1], a[2], a[3], a[4], a[5], a[6], a[7], a[8]);
+      } else {
+        max_pool2d_window_kernel<T, 2, 2><<<grid, 256, 0, s>>>(xp, op, a[0], a[1], a[2], a[3], a[4], a[5], a[6], a[7], a[8]);
+      }
+    } else if (small) {
       max_pool2d_kernel<T, int><<<grid, 256, 0, s>>>(
           static_cast<const T*>(x), static_cast<T*>(out), static_cast<int>(n * c), static_cast<int>(h),
           static_cast<int>(w), static_cast<int>(kh), static_cast<int>(kw), static_cast<int>(stride_h),

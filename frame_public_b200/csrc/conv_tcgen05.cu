@@ -83,7 +83,7 @@ conv2d_tcgen05_kernel(const float* __restrict__ x, const float* __restrict__ w,
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < g.stages; ++s) {
-      mbar_init(full_bar(s), kConvProducers);
+      mbar_init(full_bar(s), kConvProducers / 32);   // one arrival per producer warp
       mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -176,7 +176,8 @@ conv2d_tcgen05_kernel(const float* __restrict__ x, const float* __restrict__ w,
           asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(wv) : "memory");
         }
         fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor-core (async) proxy
-        mbar_arrive(full_bar(stage));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_bar(stage));   // 256 separate arrivals would serialise
         if (++stage == g.stages) { stage = 0; phase ^= 1u; }
       }
     }

@@ -358,6 +358,29 @@ int make_tmap_2d(CUtensorMap* map, const void* ptr, int dtype, int64_t rows, int
   return FB200_OK;
 }
 
+// Row-major fp32 tensor [n, c, h, w] with a box of [1, box_c, box_h, box_w] elements, no swizzle: the
+// halo tile of a convolution lands in shared memory as plain [box_c][box_h][box_w].  w must be a
+// multiple of 4 elements (strides are multiples of 16 bytes) and box_w too.
+int make_tmap_nchw_f32(CUtensorMap* map, const void* ptr, int64_t n, int64_t c, int64_t h, int64_t w,
+                       int box_c, int box_h, int box_w) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return set_error(FB200_DEVICE_ERROR, "cuTensorMapEncodeTiled is not available");
+  cuuint64_t gdim[4] = {static_cast<cuuint64_t>(w), static_cast<cuuint64_t>(h), static_cast<cuuint64_t>(c),
+                        static_cast<cuuint64_t>(n)};
+  cuuint64_t gstride[3] = {static_cast<cuuint64_t>(w) * 4, static_cast<cuuint64_t>(w * h) * 4,
+                           static_cast<cuuint64_t>(w * h * c) * 4};
+  cuuint32_t box[4] = {static_cast<cuuint32_t>(box_w), static_cast<cuuint32_t>(box_h),
+                       static_cast<cuuint32_t>(box_c), 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    return set_error(FB200_INTERNAL, "cuTensorMapEncodeTiled (nchw) failed with code %d", static_cast<int>(r));
+  }
+  return FB200_OK;
+}
+
 // Per-device status word the kernels write when a bounded wait gives up (host-mapped, so the
 // host can read it after a stream synchronise without a copy).
 struct StatusWord { int* host = nullptr; int* dev = nullptr; };

@@ -39,6 +39,21 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
+// Non-blocking probe of the phase (mbarrier.try_wait may park the warp for a while before it
+// reports a phase that completed in the meantime).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t done;
   asm volatile(
@@ -56,7 +71,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait.  `status` is a global status word shared by the whole grid: once any thread has
 // recorded a failure every other waiter gives up at its next check.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
+  // A short spin first: reading %globaltimer costs far more than a handoff between warps of one
+  // CTA normally takes, and most waits end within a few polls.
+#pragma unroll 1
+  for (int i = 0; i < 128; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+  }
   const unsigned long long t0 = globaltimer_ns();
   for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -91,6 +111,17 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void* tmap,
       " [%0], [%1, {%3, %4}], [%2];"
       :
       : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+// 4-D tiled load (x innermost).  x times the element size must again be a multiple of 16 bytes; the
+// other coordinates may be negative or past the end (those elements read as the fill value).
+__device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const void* tmap, uint32_t bar,
+                                            int32_t x, int32_t y, int32_t z, int32_t w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      :
+      : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
 }
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {

@@ -22,6 +22,13 @@ CASES = [
     ((2, 3, 64, 64), (64, 3, 7, 7), (2, 2), (3, 3), True),
     ((4, 64, 56, 56), (64, 64, 3, 3), (1, 1), (1, 1), True),
     ((1, 8, 9, 9), (130, 8, 1, 1), (1, 1), (0, 0), True),
+    # halo-tile kernel (image width a multiple of 4): two channel blocks and more tiles per CTA than
+    # TMEM accumulators (two rounds); a stride-2 7x7 stem with two rounds; ragged Cout with strides
+    # that differ; three channel blocks with one tile per image
+    ((44, 64, 56, 56), (64, 64, 3, 3), (1, 1), (1, 1), True),
+    ((12, 3, 224, 224), (64, 3, 7, 7), (2, 2), (3, 3), True),
+    ((3, 16, 12, 16), (40, 16, 3, 3), (2, 1), (0, 1), False),
+    ((2, 96, 8, 8), (32, 96, 3, 3), (1, 1), (1, 1), True),
 ]
 
 
