@@ -26,6 +26,11 @@
 // warp 8 issues tcgen05.mma kind::tf32 (M = 128, N = Cout padded to 32, K = 8 per instruction);
 // warps 9-12 run the epilogue (bias, chain, coalesced NCHW stores) of finished tiles.
 // Every wait is bounded; a wait that gives up records a status code and the CTA exits cleanly.
+// Measured with per-role cycle counters (Cout = 64): the single issuing thread spends about 130
+// cycles per tcgen05.mma although an M128 x N64 x K8 TF32 instruction is 32 cycles of tensor work,
+// i.e. with N = 64 the instruction rate, not the FLOP rate, bounds the mainloop, and TMEM reads of
+// the epilogue queue behind the MMAs.  (A transposed formulation, M = Cout, N = 256 pixels, would
+// halve the instruction count; not built.)
 // Bound: tensor pipe / shared-memory gather.  FLOPs per launch = 2 * N*OH*OW * Cout * Cin*KH*KW.
 #include <cuda.h>
 
@@ -50,6 +55,7 @@ constexpr int kHaloAStage = kHaloTileM * 128;   // 16 KiB: 128 pixels x one 32-w
 constexpr int kHaloSub = 2;                     // k-blocks per ring stage: one handshake per 64 k
 constexpr int kHaloStageBytes = kHaloSub * kHaloAStage;
 constexpr int kHaloMaxAcc = 8;
+constexpr int kHaloMaxBufs = 4;                 // halo tiles in flight
 
 enum HaloFault : int {
   kFaultHaloEmpty = 211,      // producers: A stage never freed
@@ -70,7 +76,7 @@ struct HaloGeom {
   int x0a, xoff;         // first column fetched (multiple of 4, <= -pw); -pw - x0a
   int kcb, kblocks;      // k extent of one channel block, its 32-wide blocks
   int npad, tmem_cols, acc_per_round, stages;
-  int halo_bytes, w_bytes;
+  int halo_bytes, w_bytes, n_halo;
 };
 
 // Flat walk over (round, channel block, tile) shared by all roles.
@@ -103,17 +109,17 @@ conv2d_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const flo
   uint8_t* base_ptr = smem_raw + (base - raw_addr);
   const uint32_t w_off = static_cast<uint32_t>(g.stages) * kHaloStageBytes;
   const uint32_t halo_off = w_off + static_cast<uint32_t>(g.w_bytes);
-  const uint32_t bar_off = halo_off + 2u * static_cast<uint32_t>(g.halo_bytes);
+  const uint32_t bar_off = halo_off + static_cast<uint32_t>(g.n_halo) * static_cast<uint32_t>(g.halo_bytes);
   const uint32_t bars = base + bar_off;
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (g.stages + s); };
   const uint32_t misc = bars + 8u * (2 * g.stages);
   auto halo_full = [&](int b) { return misc + 8u * b; };
-  auto halo_empty = [&](int b) { return misc + 8u * (2 + b); };
-  const uint32_t w_free = misc + 8u * 4;
-  auto tmem_full = [&](int a) { return misc + 8u * (5 + a); };
-  auto tmem_empty = [&](int a) { return misc + 8u * (5 + kHaloMaxAcc + a); };
-  const uint32_t slot_off = bar_off + 8u * (2 * g.stages + 5 + 2 * kHaloMaxAcc);
+  auto halo_empty = [&](int b) { return misc + 8u * (kHaloMaxBufs + b); };
+  const uint32_t w_free = misc + 8u * (2 * kHaloMaxBufs);
+  auto tmem_full = [&](int a) { return misc + 8u * (2 * kHaloMaxBufs + 1 + a); };
+  auto tmem_empty = [&](int a) { return misc + 8u * (2 * kHaloMaxBufs + 1 + kHaloMaxAcc + a); };
+  const uint32_t slot_off = bar_off + 8u * (2 * g.stages + 2 * kHaloMaxBufs + 1 + 2 * kHaloMaxAcc);
   const uint32_t tmem_slot = base + slot_off;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + slot_off);
   float* bias_s = reinterpret_cast<float*>(base_ptr + slot_off + 16);          // [256]
@@ -132,7 +138,7 @@ conv2d_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const flo
       mbar_init(full_bar(s), kHaloProducers / 32);   // one arrival per producer warp
       mbar_init(empty_bar(s), 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kHaloMaxBufs; ++b) {
       mbar_init(halo_full(b), 1);
       mbar_init(halo_empty(b), kHaloProducers / 32);
     }
@@ -198,16 +204,22 @@ conv2d_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const flo
     uint32_t phase = 0;
     int passes = 0;
     bool ok = true;
-    if (tid == 0 && total_items > 0) issue_halo(halo_decode(0, my_tiles, apr, g.n_cb), 0);
+    // halo tiles are fetched n_halo - 1 items ahead of the one being gathered
+    const int nb = g.n_halo;
+    if (tid == 0) {
+      for (int i = 0; i < nb - 1 && i < total_items; ++i) issue_halo(halo_decode(i, my_tiles, apr, g.n_cb), i);
+    }
     for (int idx = 0; idx < total_items && ok; ++idx) {
       const HaloItem it = halo_decode(idx, my_tiles, apr, g.n_cb);
-      const int buf = idx & 1;
-      if (tid == 0 && idx + 1 < total_items) {
-        // the other buffer was last used by item idx-1: every producer must have left it
-        if (idx >= 1 && !mbar_wait(halo_empty(buf ^ 1), ((idx - 1) >> 1) & 1, status, kFaultHaloReuse)) {
+      const int buf = idx % nb;
+      if (tid == 0 && idx + nb - 1 < total_items) {
+        // the buffer of item idx + nb - 1 was last used by item idx - 1: every producer must have
+        // left it
+        const int nbuf = (idx + nb - 1) % nb;
+        if (idx >= 1 && !mbar_wait(halo_empty(nbuf), ((idx - 1) / nb) & 1, status, kFaultHaloReuse)) {
           ok = false;
         } else {
-          issue_halo(halo_decode(idx + 1, my_tiles, apr, g.n_cb), buf ^ 1);
+          issue_halo(halo_decode(idx + nb - 1, my_tiles, apr, g.n_cb), nbuf);
         }
       }
       if (it.first_of_pass && (g.n_cb > 1 || idx == 0)) {
@@ -271,7 +283,7 @@ conv2d_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const flo
       }
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      if (!mbar_wait(halo_full(buf), (idx >> 1) & 1, status, kFaultHaloLoad)) { ok = false; break; }
+      if (!mbar_wait(halo_full(buf), (idx / nb) & 1, status, kFaultHaloLoad)) { ok = false; break; }
       const float* halo = reinterpret_cast<const float*>(base_ptr + halo_off + buf * g.halo_bytes) + pbase;
       for (int sb = 0; sb < n_stage_blocks; ++sb) {
         if (!mbar_wait(empty_bar(stage), phase ^ 1u, status, kFaultHaloEmpty)) { ok = false; break; }
@@ -469,19 +481,24 @@ extern "C" int fb200_conv2d_halo_tcgen05(const void* x, const void* w, const voi
   while (g.tmem_cols < g.acc_per_round * g.npad) g.tmem_cols *= 2;
   g.halo_bytes = (g.cb * g.ih_t * g.iwp * 4 + 1023) / 1024 * 1024;
   g.w_bytes = g.kblocks * g.npad * 128;
-  const int64_t fixed = static_cast<int64_t>(g.w_bytes) + 2 * g.halo_bytes + 1024 /*align*/ + 512 /*barriers*/ +
-                        1024 /*bias*/ + static_cast<int64_t>(g.kblocks) * kHaloBlockK * 4;
-  const int64_t room = 227 * 1024 - fixed;
-  g.stages = static_cast<int>(room / kHaloStageBytes);
-  if (g.stages > 4) g.stages = 4;
-  if (g.stages < 2) return FB200_UNIMPLEMENTED;
+  // shared memory: weights, two ring stages (the ring is not latency-bound: each handshake costs
+  // about as much as the MMAs it covers), and as many halo buffers as fit, up to four, because the
+  // strided 4-D copy of a halo tile takes longer than gathering one
+  const int64_t fixed = static_cast<int64_t>(g.w_bytes) + 1024 /*align*/ + 512 /*barriers*/ + 1024 /*bias*/ +
+                        static_cast<int64_t>(g.kblocks) * kHaloBlockK * 4;
+  g.stages = 2;
+  const int64_t room = 227 * 1024 - fixed - static_cast<int64_t>(g.stages) * kHaloStageBytes;
+  g.n_halo = static_cast<int>(room / g.halo_bytes);
+  if (g.n_halo > kHaloMaxBufs) g.n_halo = kHaloMaxBufs;
+  if (g.n_halo < 2) return FB200_UNIMPLEMENTED;
   EpilogueDev epi{};
   if (int rc = make_epilogue(epilogue, &epi, "conv2d")) return rc;
   CUtensorMap tx;
   if (int rc = make_tmap_nchw_f32(&tx, x, g.n, g.cin, g.h, g.w, g.cb, g.ih_t, g.iwp)) return rc;
   int* status = nullptr;
   if (int rc = device_status_word(&status)) return rc;
-  const size_t smem = static_cast<size_t>(g.stages) * kHaloStageBytes + static_cast<size_t>(fixed);
+  const size_t smem = static_cast<size_t>(g.stages) * kHaloStageBytes + static_cast<size_t>(fixed) +
+                      static_cast<size_t>(g.n_halo) * g.halo_bytes;
   FB200_CUDA_OK(cudaFuncSetAttribute(conv2d_halo_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(smem)));
   const uint32_t idesc = make_instr_desc(kFmtTF32, /*a MN-major*/ 1, /*b MN-major*/ 0, kHaloTileM,
@@ -492,3 +509,4 @@ extern "C" int fb200_conv2d_halo_tcgen05(const void* x, const void* w, const voi
       epi, status);
   return after_launch("conv2d_halo_tcgen05_kernel");
 }
+

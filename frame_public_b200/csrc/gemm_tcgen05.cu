@@ -175,6 +175,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      const uint64_t a_desc0 = make_smem_desc_sw128(base, 16, 1024);
+      const uint64_t b_desc0 = ELT == 2 ? make_smem_desc(base + Cfg::kAStageBytes, Cfg::kBChunkBytes, 1024, kLayoutSw128)
+                                        : make_smem_desc(base + Cfg::kAStageBytes, Cfg::kBChunkBytes, 512, kLayoutSw128Base32);
       for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
         if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, status, kFaultMmaTmemEmpty)) { ok = false; break; }
         tcgen05_fence_after_sync();
@@ -182,20 +185,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         for (int64_t kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, status, kFaultMmaFull)) { ok = false; break; }
           tcgen05_fence_after_sync();
-          const uint32_t a_addr = base + stage * Cfg::kStageBytes;
-          const uint32_t b_addr = a_addr + Cfg::kAStageBytes;
+          // A: K-major, rows of 128 bytes, 8-row groups 1024 bytes apart; a K step is 32 bytes
+          // further inside the swizzled row.  B: MN-major; 2-byte elements: 16-byte swizzle units,
+          // 8-row K groups 1024 bytes apart; 4-byte elements: 32-byte swizzle units, 4-row K groups
+          // 512 bytes apart.  Only the address field (bytes >> 4) changes between instructions, so
+          // the descriptors are built once per kernel and advanced by additions: this loop runs on
+          // one thread, where every instruction between two tcgen05.mma is exposed latency.
+          const uint32_t stage_units = static_cast<uint32_t>(stage * Cfg::kStageBytes) >> 4;
 #pragma unroll
           for (int ks = 0; ks < Cfg::kStepsPerBlock; ++ks) {
-            // A: K-major, rows of 128 bytes, 8-row groups 1024 bytes apart; a K step is 32 bytes
-            // further inside the swizzled row.
-            const uint64_t a_desc = make_smem_desc_sw128(a_addr + ks * Cfg::kUmmaKBytes, 16, 1024);
-            // B: MN-major.  2-byte elements: 16-byte swizzle units, 8-row K groups 1024 bytes
-            // apart.  4-byte elements: 32-byte swizzle units, 4-row K groups 512 bytes apart.
-            const uint64_t b_desc =
-                ELT == 2 ? make_smem_desc(b_addr + ks * Cfg::kBKStepBytes, Cfg::kBChunkBytes, 1024,
-                                          kLayoutSw128)
-                         : make_smem_desc(b_addr + ks * Cfg::kBKStepBytes, Cfg::kBChunkBytes, 512,
-                                          kLayoutSw128Base32);
+            const uint64_t a_desc = a_desc0 + (stage_units + static_cast<uint32_t>(ks * Cfg::kUmmaKBytes) / 16u);
+            const uint64_t b_desc = b_desc0 + (stage_units + static_cast<uint32_t>(ks * Cfg::kBKStepBytes) / 16u);
             const uint32_t accumulate = (kb > 0 || ks > 0) ? 1u : 0u;
             if (ELT == 2) mma_f16(d_tmem, a_desc, b_desc, idesc, accumulate);
             else mma_tf32(d_tmem, a_desc, b_desc, idesc, accumulate);
