@@ -81,9 +81,6 @@ class GemmWorkload:
         bias = rng.normal(0, 0.1, (n,)).astype(np.float32)
         return [a, b, conv(np.tile(bias[None, :], (n, 1)))]
 
-    def dominant_kernel(self):
-        return {"kernel": "gemm_tcgen05_kernel", "work": self.flops, "unit": "TFLOP/s", "launches_per_step": 1}
-
     # the reference CPU backend on a slab of `rows` rows of A (rows are independent)
     def cpu_slab(self, rows):
         from frame_public_b200 import irtext
@@ -467,8 +464,8 @@ def run_reference(args):
     cores = os.cpu_count() or 1
     procs = max(1, min(cores, 64))
     rows = 1   # one row of A per process per step: 2*N^2 FLOP, about a second of the reference's naive matmul
-    warm = min(args.warmup, 1)
-    steps = max(1, min(args.steps, 5))
+    warm = max(0, args.warmup)
+    steps = max(1, args.steps)   # about 0.7 s per step: the default K and W finish in seconds
     ctx = mp.get_context("spawn")
     with ctx.Pool(procs) as pool:
         res = pool.map(_ref_worker, [(wl.name, rows, steps, warm, 100 + i) for i in range(procs)])

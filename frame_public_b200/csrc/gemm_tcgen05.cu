@@ -20,11 +20,13 @@
 //            quarter, each on half of the tile's columns (with four warps a transcendental
 //            epilogue behind a short K was bound by those 128 threads).  The second accumulator
 //            lets the epilogue of tile i overlap the MMAs of tile i+1.
-// Tiles are walked in groups of 8 M-blocks so that concurrently resident CTAs share A and B
-// panels in the 126 MB L2.  Edge tiles rely on TMA zero fill for loads and masked stores.
+// Tiles are walked in groups of 16 M-blocks so that concurrently resident CTAs share A and B
+// panels in the 126 MB L2 (B is then streamed from HBM tiles_m/16 times: 1.0 GB of DRAM reads per
+// 8192^3 launch with groups of 8 measured by ncu, against 384 MB of distinct operands).  Edge tiles rely on TMA zero fill for loads and masked stores.
 // Bound: tensor pipe.  FLOPs per launch = 2*M*N*K.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -41,7 +43,15 @@ using namespace sm100;
 
 constexpr int kBlockM = 128;
 constexpr int kGemmThreads = 320;   // TMA warp, MMA warp, eight epilogue warps
-constexpr int kGroupM = 8;
+// M-blocks per group of the tile walk; FRAME_B200_GEMM_GROUP_M overrides it for measurements.
+static int gemm_group_m() {
+  static const int v = [] {
+    const char* e = getenv("FRAME_B200_GEMM_GROUP_M");
+    const int g = e != nullptr ? atoi(e) : 0;
+    return g >= 1 && g <= 1024 ? g : 16;   // 8: 1345, 16: 1362, 32: 1335, 64: 1278 TFLOP/s at 8192^3 bf16
+  }();
+  return v;
+}
 
 // Where a tile of the result goes: one or several destination matrices of row pitch `ld`, at
 // column offset `col0`.  One destination with ld == N, col0 == 0 is the ordinary matmul; several
@@ -51,6 +61,7 @@ constexpr int kMaxDest = 8;
 struct GemmDest {
   void* ptr[kMaxDest];
   int n;
+  int group_m;   // M-blocks per group of the tile walk
   int64_t ld;
   int64_t col0;
 };
@@ -82,7 +93,7 @@ struct GemmCfg {
   static constexpr size_t kSmemBytes = size_t(kStages) * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
 
-__device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64_t tiles_n,
+__device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64_t tiles_n, int kGroupM,
                                             int64_t* tm, int64_t* tn) {
   const int64_t per_group = kGroupM * tiles_n;
   const int64_t group = tile / per_group;
@@ -150,7 +161,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       bool ok = true;
       for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
         int64_t tm, tn;
-        tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+        tile_coords(tile, tiles_m, tiles_n, dest.group_m, &tm, &tn);
         for (int64_t kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, status, kFaultProducerEmpty)) { ok = false; break; }
           mbar_arrive_expect_tx(full_bar(stage), Cfg::kStageBytes);
@@ -222,7 +233,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     bool ok = true;
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
       int64_t tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, &tm, &tn);
+      tile_coords(tile, tiles_m, tiles_n, dest.group_m, &tm, &tn);
       if (!mbar_wait(tmem_full_bar(acc), acc_phase, status, kFaultEpilogueTmemFull)) { ok = false; break; }
       tcgen05_fence_after_sync();
       const int64_t row = tm * kBlockM + quarter * 32 + lane;
@@ -478,6 +489,7 @@ extern "C" int fb200_matmul(const void* a, const void* b, void* c, int64_t m, in
   cudaStream_t s = as_stream(stream);
   if (k > 0 && tensor_core_eligible(a, b, c, m, n, k, dtype, allow_tf32)) {
     GemmDest dest{};
+  dest.group_m = gemm_group_m();
     dest.ptr[0] = c;
     dest.n = 1;
     dest.ld = n;
@@ -529,6 +541,7 @@ extern "C" int fb200_matmul_colsplit(const void* a, const void* b_local, void* c
   EpilogueDev epi{};
   if (int rc = make_epilogue(epilogue, &epi, "matmul_colsplit")) return rc;
   GemmDest dest{};
+  dest.group_m = gemm_group_m();
   for (int d = 0; d < n_dest; ++d) {
     if (c_dest[d] == nullptr) return set_error(FB200_INVALID_ARGUMENT, "matmul_colsplit: destination %d is null", d);
     dest.ptr[d] = c_dest[d];
