@@ -99,7 +99,7 @@ SIGNATURES = {
                                           c_int64, c_int64, POINTER(c_int), c_int, c_int, _P]),
     "fb200_attention_fan_supported": (c_int, [c_int64, c_int64, c_int64, c_int]),
     "fb200_attention_fan": (c_int, [_P, c_int64, c_int64, _P, c_int64, c_int64, _P, c_int64, c_int64, _P,
-                                    c_int64, _P, c_int64, c_int64, c_int64, c_int64, c_int, _P]),
+                                    c_int64, _P, c_int64, c_int64, c_int64, c_int64, c_float, c_int, _P]),
     "fb200_mamba_scan": (c_int, [_P] * 8 + [c_int64] * 4 + [_P]),
     "fb200_transpose": (c_int, [_P, _P, c_int, _I64P, _I64P, c_int, _P]),
     "fb200_slice": (c_int, [_P, _P, c_int, _I64P, c_int64, c_int64, c_int64, c_int, _P]),
@@ -116,6 +116,7 @@ SIGNATURES = {
     "fb200_plan_run_host": (c_int, [_P, _PP, _PP, _P]),
     "fb200_plan_profile": (c_int, [_P, _PP, _PP, _P, POINTER(c_float), c_int, _IP]),
     "fb200_plan_step_op": (c_char_p, [_P, c_int]),
+    "fb200_plan_describe": (c_int, [c_char_p, c_int, _PP]),
 }
 
 _lib = None
@@ -281,10 +282,10 @@ HEAD_DTYPE = np.dtype([("q_row", "<i4"), ("q_col", "<i4"), ("k_row", "<i4"), ("k
 
 
 def attention_fan(q, q_rows, q_ld, k, k_rows, k_ld, v, v_rows, v_ld, o, o_ld, heads_dev, n_heads,
-                  sq, sk, head_dim, dtype, stream=None):
+                  sq, sk, head_dim, dtype, stream=None, scale=1.0):
     """heads_dev: device pointer of an array of HEAD_DTYPE records (fb200_attention_head)."""
     check(load().fb200_attention_fan(q, q_rows, q_ld, k, k_rows, k_ld, v, v_rows, v_ld, o, o_ld,
-                                     heads_dev, n_heads, sq, sk, head_dim, dtype, stream))
+                                     heads_dev, n_heads, sq, sk, head_dim, scale, dtype, stream))
 
 
 def transpose(x, out, dims, perm, itemsize, stream=None):

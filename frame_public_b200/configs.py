@@ -249,6 +249,28 @@ def mamba_block(batch: int = 16, seq: int = 2048, d_model: int = 768, expand: in
 
 
 # Miniatures of the five graphs for the parity tests (same structure, seconds on the CPU oracle).
+# The reference's OWN nn:: modules (include/frame/nn/layers.h:157-234), graphs emitted by its builder
+# where the reference is present (tests/golden/make_workload_golden.py): (golden name, module kind,
+# builder arguments, DTypeCode).  transformer: batch, seq, embed, heads, ffn, with_bias; mamba: batch,
+# steps, channels, kernel.
+NN_GRAPHS = [
+    ("nn_transformer_bf16_b2_s128_e128_h2", "transformer", (2, 128, 128, 2, 256, True), BF16),
+    ("nn_transformer_f32_b2_s16_e32_h2", "transformer", (2, 16, 32, 2, 64, True), F32),
+    ("nn_mamba_f32_b2_c16_s24_k4", "mamba", (2, 24, 16, 4, 0, True), F32),
+]
+
+
+def nn_inputs(shapes, dtype: int, seed: int = 11) -> List[np.ndarray]:
+    """Seeded inputs for a graph given the shapes of its inputs: the activation first, then the
+    parameters; N(0, 1) for the activation, N(0, 0.1) for everything else, in storage form."""
+    rng = np.random.default_rng(seed)
+    out = []
+    for i, shape in enumerate(shapes):
+        x = rng.standard_normal(shape).astype(np.float32) * np.float32(1.0 if i == 0 else 0.1)
+        out.append(_bf16(x) if dtype == BF16 else x)
+    return out
+
+
 def small_workloads(backend: str = "cpu") -> List[Workload]:
     return [
         mlp(batch=8, d_in=40, hidden=32, d_out=10, backend=backend),

@@ -5,7 +5,9 @@
 // its executable runs each node as its own kernel (src/backends/cuda/cuda_executable.cpp:84-118):
 // for 8 x 16 heads that is about 900 launches of tiny kernels.  This kernel computes, for every
 // head h of a table,
-//     S = Q_h K_h^T   (fp32 accumulate, rounded once to T: the first matmul's store)
+//     S = Q_h K_h^T   (fp32 accumulate, rounded once to T: the first matmul's store; then, when a
+//                     scale other than 1 is given, multiplied by it and rounded to T again: the
+//                     `mul` by a constant of the reference's own attention)
 //     P = softmax(S)  (row max, exp(x - max), sum, e * (1 / sum) in fp32; rounded once to T)
 //     O = P V_h       (fp32 accumulate, rounded once to T)
 // i.e. the same three operators with the same rounding points (matmul:
@@ -105,7 +107,7 @@ attention_fan_kernel(const __grid_constant__ CUtensorMap tmap_q,
                      const __grid_constant__ CUtensorMap tmap_v,
                      const fb200_attention_head* __restrict__ heads, T* __restrict__ o_base,
                      int64_t o_ld, int sq, int sk, int q_blocks, uint32_t tmem_cols, uint32_t fmt,
-                     int* status) {
+                     float scale, int* status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
@@ -206,6 +208,7 @@ attention_fan_kernel(const __grid_constant__ CUtensorMap tmap_q,
       }
     }
   };
+  const bool scaled = scale != 1.0f;
   float mx = -INFINITY;
   if (ok) {
     tcgen05_fence_after_sync();
@@ -214,6 +217,9 @@ attention_fan_kernel(const __grid_constant__ CUtensorMap tmap_q,
       for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
     });
     mx = stored_score<T>(mx);   // rounding is monotonic: max of the rounded = rounded max
+    // an optional `mul` by a constant between the matmul and the softmax (the reference's own
+    // attention scales there): its result is rounded to T again; a positive scale keeps the maximum
+    if (scaled) mx = stored_score<T>(mx * scale);
   }
   red_max[half * kAttnBlockM + row_in_tile] = mx;
   __syncthreads();
@@ -224,7 +230,9 @@ attention_fan_kernel(const __grid_constant__ CUtensorMap tmap_q,
     sweep([&](int c, uint32_t (&r)[32]) {
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        const float e = ex2_approx(fmaf(stored_score<T>(__uint_as_float(r[i])), 1.4426950408889634f, -mx2));
+        float sc = stored_score<T>(__uint_as_float(r[i]));
+        if (scaled) sc = stored_score<T>(sc * scale);
+        const float e = ex2_approx(fmaf(sc, 1.4426950408889634f, -mx2));
         sum += e;
         r[i] = __float_as_uint(e);
       }
@@ -321,7 +329,7 @@ extern "C" int fb200_attention_fan(const void* q_base, int64_t q_rows, int64_t q
                                    const void* v_base, int64_t v_rows, int64_t v_ld, void* o_base,
                                    int64_t o_ld, const fb200_attention_head* heads_dev,
                                    int64_t n_heads, int64_t sq, int64_t sk, int64_t head_dim,
-                                   int dtype, fb200_stream stream) {
+                                   float scale, int dtype, fb200_stream stream) {
   if (n_heads < 0 || sq < 0) return set_error(FB200_INVALID_ARGUMENT, "attention_fan: negative size");
   if (!fb200_attention_fan_supported(sq > 0 ? sq : 1, sk, head_dim, dtype)) {
     return set_error(FB200_UNIMPLEMENTED,
@@ -329,6 +337,7 @@ extern "C" int fb200_attention_fan(const void* q_base, int64_t q_rows, int64_t q
                      "multiples of 64 (got dtype %d, head_dim %lld, keys %lld)",
                      dtype, static_cast<long long>(head_dim), static_cast<long long>(sk));
   }
+  if (!(scale > 0.0f)) return set_error(FB200_INVALID_ARGUMENT, "attention_fan: the score scale must be positive");
   if (n_heads == 0 || sq == 0) return FB200_OK;
   if (!q_base || !k_base || !v_base || !o_base || !heads_dev) {
     return set_error(FB200_INVALID_ARGUMENT, "attention_fan: null argument");
@@ -357,13 +366,13 @@ extern "C" int fb200_attention_fan(const void* q_base, int64_t q_rows, int64_t q
     FB200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     kernel<<<grid, kAttnThreads, smem, s>>>(tq, tk, tv, heads_dev, static_cast<__nv_bfloat16*>(o_base), o_ld,
                                             static_cast<int>(sq), static_cast<int>(sk),
-                                            static_cast<int>(q_blocks), tmem_cols, kFmtBF16, status);
+                                            static_cast<int>(q_blocks), tmem_cols, kFmtBF16, scale, status);
   } else {
     auto kernel = attention_fan_kernel<__half>;
     FB200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     kernel<<<grid, kAttnThreads, smem, s>>>(tq, tk, tv, heads_dev, static_cast<__half*>(o_base), o_ld,
                                             static_cast<int>(sq), static_cast<int>(sk),
-                                            static_cast<int>(q_blocks), tmem_cols, kFmtF16, status);
+                                            static_cast<int>(q_blocks), tmem_cols, kFmtF16, scale, status);
   }
   return after_launch("attention_fan_kernel");
 }

@@ -16,6 +16,7 @@
 // the caller's stream, graph outputs written straight into the caller's buffers, no allocation,
 // no synchronisation.
 #include <algorithm>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -41,6 +42,9 @@ struct SlotInfo {
   int output_index = -1;      // >= 0: graph output (first occurrence)
   int alias_of = -1;          // >= 0: same bytes as that slot
   void* constant = nullptr;   // materialised constant
+  bool is_constant = false;   // produced by a `constant` step
+  bool splat = false;         // constant whose elements are all equal ...
+  float splat_value = 0.0f;   // ... to this value (as stored in the slot's dtype)
   size_t bytes() const { return static_cast<size_t>(numel) * itemsize_of(dtype); }
 };
 
@@ -64,6 +68,7 @@ struct Step {
   // device table of per-head coordinates
   int fan_q = -1, fan_k = -1, fan_v = -1, fan_dest = -1;
   int64_t fan_heads = 0, fan_sq = 0, fan_sk = 0;
+  float fan_scale = 1.0f;   // scores are multiplied by this (and rounded again) before the softmax
   void* fan_table = nullptr;
   // kDwConvTimeMajor: input matrix slot and column window, weights, bias, geometry
   int dw_x = -1, dw_w = -1, dw_bias = -1;
@@ -75,6 +80,7 @@ struct Step {
 using namespace fb200;
 
 struct fb200_plan {
+  bool dry = false;   // parsed and rewritten for description only: owns no device memory, cannot run
   int device = 0;
   int allow_tf32 = 0;
   int opt_level = 1;
@@ -98,6 +104,13 @@ struct fb200_plan {
 };
 
 namespace fb200 {
+
+// FRAME_B200_PLAN_DEBUG=1 prints to stderr why a group rewrite was not applied.
+static bool plan_debug() {
+  static const bool on = getenv("FRAME_B200_PLAN_DEBUG") != nullptr;
+  return on;
+}
+#define PLAN_TRACE(...) do { if (plan_debug()) { fprintf(stderr, "[fb200 plan] " __VA_ARGS__); fputc('\n', stderr); } } while (0)
 
 static const Attr* find_attr(const Step& s, const char* name) {
   for (const Attr& a : s.attrs) if (a.name == name) return &a;
@@ -368,6 +381,8 @@ static int materialise_constant(fb200_plan* p, Step& s) {
     return set_error(FB200_INVALID_ARGUMENT, "op 'constant': value has %zu elements, shape needs %lld", vals.size(), (long long)n);
   }
   if (n == 0) return FB200_OK;
+  bool all_equal = true;
+  for (int64_t i = 1; i < n && all_equal; ++i) all_equal = vals[static_cast<size_t>(i)] == vals[0];
   std::vector<uint8_t> host(slot.bytes());
   for (int64_t i = 0; i < n; ++i) {
     const double d = vals[i];
@@ -394,11 +409,27 @@ static int materialise_constant(fb200_plan* p, Step& s) {
     }
   }
   // A constant that is also a graph output is copied into the caller's buffer at run time.
-  void* dev = nullptr;
-  if (int rc = fb200_malloc(p->device, host.size(), 256, &dev)) return rc;
-  p->owned.push_back(dev);
-  if (int rc = fb200_memcpy(p->device, dev, host.data(), host.size(), FB200_H2D, nullptr, 1)) return rc;
-  slot.constant = dev;
+  slot.is_constant = true;
+  if (!p->dry) {
+    void* dev = nullptr;
+    if (int rc = fb200_malloc(p->device, host.size(), 256, &dev)) return rc;
+    p->owned.push_back(dev);
+    if (int rc = fb200_memcpy(p->device, dev, host.data(), host.size(), FB200_H2D, nullptr, 1)) return rc;
+    slot.constant = dev;
+  }
+  if (all_equal) {   // the value as the kernels will read it back from the slot's dtype
+    float stored = static_cast<float>(vals[0]);
+    if (slot.dtype == FB200_BF16) {
+      uint32_t bits = static_cast<uint32_t>(reinterpret_cast<uint16_t*>(host.data())[0]) << 16;
+      memcpy(&stored, &bits, 4);
+    } else if (slot.dtype == FB200_F16) {
+      __half h;
+      memcpy(&h, host.data(), 2);
+      stored = __half2float(h);
+    }
+    slot.splat = slot.dtype == FB200_F32 || slot.dtype == FB200_BF16 || slot.dtype == FB200_F16;
+    slot.splat_value = stored;
+  }
   return FB200_OK;
 }
 
@@ -506,6 +537,32 @@ static void optimise(fb200_plan* p) {
 }
 
 
+static bool step_runs(const Step& s) {
+  return s.kind != Kind::kSkip && s.kind != Kind::kAlias && s.kind != Kind::kConstant;
+}
+
+// Index of the step that writes the bytes of `slot` (through its own output or as the fused
+// result of a contraction), or -1.
+static int writer_of(const fb200_plan& p, int slot) {
+  const int root = root_slot(p, slot);
+  for (size_t j = 0; j < p.steps.size(); ++j) {
+    const Step& s = p.steps[j];
+    if (!step_runs(s) || s.write_slot < 0) continue;
+    if (root_slot(p, s.write_slot) == root) return static_cast<int>(j);
+  }
+  return -1;
+}
+
+// Does step `s` read or write bytes overlapping `slot`, other than through slots rooted at `own`?
+static bool step_touches(const fb200_plan& p, const Step& s, int slot, int own) {
+  auto hit = [&](int x) { return x >= 0 && root_slot(p, x) != own && ranges_overlap(p, x, slot); };
+  for (int x : s.in) if (hit(x)) return true;
+  for (int x : s.epi_operand_slot) if (hit(x)) return true;
+  if (hit(s.write_slot)) return true;
+  for (int x : {s.fan_q, s.fan_k, s.fan_v, s.fan_dest, s.dw_x, s.dw_w, s.dw_bias}) if (hit(x)) return true;
+  return false;
+}
+
 // ---- attention-fan recognition ------------------------------------------------------------------
 // A window of a rank-2 matrix reached through a chain of `slice` steps.
 struct Window { int base; int64_t row, col; };
@@ -542,6 +599,8 @@ static std::vector<std::pair<int, int>> readers_of(const fb200_plan& p, int slot
 
 struct FanHead {
   int transpose, scores, softmax, values;   // step indices
+  float scale;                              // 1, or the splat constant the scores are multiplied by
+  int scale_step;                           // the mul step when it is a step of its own, else -1
   Window q, k, v;
   int dest;                                 // slot the result finally lands in
   int64_t dest_row, dest_col;
@@ -580,28 +639,74 @@ static void fuse_attention_fans(fb200_plan* p) {
     if (sm.kind != Kind::kSoftmax || sm.in.size() != 1 || sm.out.size() != 1) continue;
     FanHead h{};
     h.softmax = i;
-    h.scores = producer[static_cast<size_t>(sm.in[0])];
-    if (h.scores < 0) continue;
+    // The scores: a matmul, possibly followed by a `mul` with a constant filled with one value (the
+    // reference's own attention scales by 1/sqrt(d) there, src/nn/layers.cpp:1062-1071).  That mul
+    // is either still a step of its own or has been absorbed as the matmul's epilogue.
+    h.scale = 1.0f;
+    h.scale_step = -1;
+    int scores_slot = sm.in[0];
+    int w0 = writer_of(*p, scores_slot);
+    if (w0 < 0) { PLAN_TRACE("softmax step %d: no producer for its input", i); continue; }
+    auto splat_of = [&](int slot, float* value) {
+      const SlotInfo& c = p->slots[static_cast<size_t>(root_slot(*p, slot))];
+      if (!c.is_constant || !c.splat) return false;
+      *value = c.splat_value;
+      return true;
+    };
+    if (p->steps[static_cast<size_t>(w0)].kind == Kind::kChain) {
+      const Step& mu = p->steps[static_cast<size_t>(w0)];
+      int sole = -1, sole_index = -1;
+      if (mu.chain_ops.size() != 1 || mu.chain_ops[0] != FB200_EW_MUL || mu.in.size() != 2 ||
+          !sole_reader(mu.out[0], &sole, &sole_index) || sole != i) {
+        PLAN_TRACE("softmax step %d: input written by step %d (%s), not a matmul or a mul", i, w0, mu.op.c_str());
+        continue;
+      }
+      float value = 1.0f;
+      int x = -1;
+      if (splat_of(mu.in[1], &value)) x = mu.in[0];
+      else if (splat_of(mu.in[0], &value)) x = mu.in[1];
+      if (x < 0) { PLAN_TRACE("softmax step %d: scores are multiplied by a tensor that is not a constant splat", i); continue; }
+      h.scale = value;
+      h.scale_step = w0;
+      scores_slot = x;
+      w0 = writer_of(*p, scores_slot);
+      if (w0 < 0) continue;
+    }
+    h.scores = w0;
     const Step& m1 = p->steps[static_cast<size_t>(h.scores)];
-    if (m1.kind != Kind::kMatmul || !m1.chain_ops.empty() || m1.write_slot != m1.out[0] || m1.in.size() != 2) continue;
+    if (m1.kind != Kind::kMatmul || m1.in.size() != 2 || m1.write_slot != scores_slot) {
+      PLAN_TRACE("softmax step %d: scores written by step %d (%s), not a matmul", i, h.scores, m1.op.c_str());
+      continue;
+    }
+    if (!m1.chain_ops.empty()) {
+      float value = 1.0f;
+      if (h.scale_step >= 0 || m1.chain_ops.size() != 1 || m1.chain_ops[0] != FB200_EW_MUL ||
+          m1.epi_operand_slot[0] < 0 || m1.epi_mode[0] != FB200_OPERAND_FULL ||
+          !splat_of(m1.epi_operand_slot[0], &value)) {
+        PLAN_TRACE("softmax step %d: scores have an epilogue other than one mul by a constant splat", i);
+        continue;
+      }
+      h.scale = value;
+    }
+    if (!(h.scale > 0.0f)) { PLAN_TRACE("softmax step %d: non-positive score scale", i); continue; }
     int step = -1, index = -1;
-    if (!sole_reader(m1.out[0], &step, &index) || step != i) continue;
+    if (!sole_reader(m1.write_slot, &step, &index) || step != (h.scale_step >= 0 ? h.scale_step : i)) { PLAN_TRACE("softmax step %d: scores have other readers", i); continue; }
     h.transpose = producer[static_cast<size_t>(m1.in[1])];
-    if (h.transpose < 0) continue;
+    if (h.transpose < 0) { PLAN_TRACE("softmax step %d: k operand has no producer", i); continue; }
     const Step& tr = p->steps[static_cast<size_t>(h.transpose)];
-    if (tr.kind != Kind::kTranspose || tr.iv.size() != 2 || tr.iv[0] != 1 || tr.iv[1] != 0) continue;
-    if (!sole_reader(tr.out[0], &step, &index) || step != h.scores) continue;
-    if (!sole_reader(sm.out[0], &step, &index) || index != 0) continue;
+    if (tr.kind != Kind::kTranspose || tr.iv.size() != 2 || tr.iv[0] != 1 || tr.iv[1] != 0) { PLAN_TRACE("softmax step %d: k operand is not a [1,0] transpose", i); continue; }
+    if (!sole_reader(tr.out[0], &step, &index) || step != h.scores) { PLAN_TRACE("softmax step %d: transposed k has other readers", i); continue; }
+    if (!sole_reader(sm.out[0], &step, &index) || index != 0) { PLAN_TRACE("softmax step %d: probabilities are not the lhs of exactly one step", i); continue; }
     h.values = step;
     const Step& m2 = p->steps[static_cast<size_t>(h.values)];
-    if (m2.kind != Kind::kMatmul || !m2.chain_ops.empty() || m2.write_slot != m2.out[0] || m2.in.size() != 2) continue;
+    if (m2.kind != Kind::kMatmul || !m2.chain_ops.empty() || m2.write_slot != m2.out[0] || m2.in.size() != 2) { PLAN_TRACE("softmax step %d: consumer is not a plain matmul", i); continue; }
     const SlotInfo& qs = p->slots[static_cast<size_t>(m1.in[0])];
     const SlotInfo& ks = p->slots[static_cast<size_t>(tr.in[0])];
     const SlotInfo& vs = p->slots[static_cast<size_t>(m2.in[1])];
     if (qs.dims.size() != 2 || ks.dims.size() != 2 || vs.dims.size() != 2) continue;
     if (qs.dims[1] != ks.dims[1] || vs.dims[0] != ks.dims[0] || vs.dims[1] != qs.dims[1]) continue;
     if (ks.dtype != qs.dtype || vs.dtype != qs.dtype) continue;
-    if (!fb200_attention_fan_supported(qs.dims[0], ks.dims[0], qs.dims[1], qs.dtype)) continue;
+    if (!fb200_attention_fan_supported(qs.dims[0], ks.dims[0], qs.dims[1], qs.dtype)) { PLAN_TRACE("softmax step %d: shape/dtype outside the fused kernel (sq %lld sk %lld d %lld dtype %d)", i, (long long)qs.dims[0], (long long)ks.dims[0], (long long)qs.dims[1], qs.dtype); continue; }
     h.q = resolve_window(*p, producer, m1.in[0]);
     h.k = resolve_window(*p, producer, tr.in[0]);
     h.v = resolve_window(*p, producer, m2.in[1]);
@@ -611,7 +716,7 @@ static void fuse_attention_fans(fb200_plan* p) {
       if (b.dims.size() != 2 || b.dims[1] % 8 != 0 || w->col % 8 != 0 || b.dims[0] > 0x7fffffff ||
           b.dims[1] > 0x7fffffff) ok = false;
     }
-    if (!ok) continue;
+    if (!ok) { PLAN_TRACE("softmax step %d: operand windows are not 16-byte addressable", i); continue; }
     // where the result finally lands
     int cur = m2.out[0];
     h.dest_row = h.dest_col = 0;
@@ -627,7 +732,7 @@ static void fuse_attention_fans(fb200_plan* p) {
     }
     h.dest = cur;
     const SlotInfo& d = p->slots[static_cast<size_t>(h.dest)];
-    if (d.dims.size() != 2 || d.dims[1] % 8 != 0 || h.dest_col % 8 != 0) continue;
+    if (d.dims.size() != 2 || d.dims[1] % 8 != 0 || h.dest_col % 8 != 0) { PLAN_TRACE("softmax step %d: destination not addressable", i); continue; }
     heads.push_back(h);
   }
   std::vector<char> used(heads.size(), 0);
@@ -643,7 +748,8 @@ static void fuse_attention_fans(fb200_plan* p) {
       const SlotInfo& ko = p->slots[static_cast<size_t>(p->steps[static_cast<size_t>(heads[o].transpose)].in[0])];
       if (heads[o].q.base == heads[g].q.base && heads[o].k.base == heads[g].k.base &&
           heads[o].v.base == heads[g].v.base && heads[o].dest == heads[g].dest &&
-          qo.dims == q0.dims && ko.dims == k0.dims && qo.dtype == q0.dtype) {
+          qo.dims == q0.dims && ko.dims == k0.dims && qo.dtype == q0.dtype &&
+          heads[o].scale == heads[g].scale) {
         group.push_back(o);
         used[o] = 1;
       }
@@ -674,10 +780,11 @@ static void fuse_attention_fans(fb200_plan* p) {
         if (!fed) ok = false;
       }
     }
-    if (!ok) continue;
+    if (!ok) { PLAN_TRACE("fan of %zu heads: a concat on the way has inputs from outside the fan", group.size()); continue; }
     for (size_t o : group) {
       const FanHead& h = heads[o];
       for (int j : {h.transpose, h.scores, h.softmax, h.values}) p->steps[static_cast<size_t>(j)].kind = Kind::kSkip;
+      if (h.scale_step >= 0) p->steps[static_cast<size_t>(h.scale_step)].kind = Kind::kSkip;
     }
     for (int c : concats) p->steps[static_cast<size_t>(c)].kind = Kind::kSkip;
     // slices nobody reads any more
@@ -728,14 +835,15 @@ static void fuse_attention_fans(fb200_plan* p) {
       table.push_back(e);
     }
     void* dev_table = nullptr;
-    if (ok) {
+    if (ok && !p->dry) {
       const size_t bytes = table.size() * sizeof(fb200_attention_head);
       ok = fb200_malloc(p->device, bytes, 256, &dev_table) == FB200_OK &&
            fb200_memcpy(p->device, dev_table, table.data(), bytes, FB200_H2D, nullptr, 0) == FB200_OK;
       if (!ok && dev_table) { fb200_free(p->device, dev_table); dev_table = nullptr; }
     }
-    if (!ok) { restore(); continue; }
-    p->owned.push_back(dev_table);
+    if (!ok) { PLAN_TRACE("fan of %zu heads ending at step %d: rejected by the byte-range checks", group.size(), pos); restore(); continue; }
+    PLAN_TRACE("fan of %zu heads -> one attention_fan launch at step %d (scale %g)", group.size(), pos, first.scale);
+    if (dev_table != nullptr) p->owned.push_back(dev_table);
     Step& launch = p->steps[static_cast<size_t>(pos)];
     launch.kind = Kind::kAttentionFan;
     launch.fan_q = first.q.base; launch.fan_k = first.k.base; launch.fan_v = first.v.base;
@@ -744,33 +852,8 @@ static void fuse_attention_fans(fb200_plan* p) {
     launch.fan_sq = q0.dims[0];
     launch.fan_sk = k0.dims[0];
     launch.fan_table = dev_table;
+    launch.fan_scale = first.scale;
   }
-}
-
-static bool step_runs(const Step& s) {
-  return s.kind != Kind::kSkip && s.kind != Kind::kAlias && s.kind != Kind::kConstant;
-}
-
-// Index of the step that writes the bytes of `slot` (through its own output or as the fused
-// result of a contraction), or -1.
-static int writer_of(const fb200_plan& p, int slot) {
-  const int root = root_slot(p, slot);
-  for (size_t j = 0; j < p.steps.size(); ++j) {
-    const Step& s = p.steps[j];
-    if (!step_runs(s) || s.write_slot < 0) continue;
-    if (root_slot(p, s.write_slot) == root) return static_cast<int>(j);
-  }
-  return -1;
-}
-
-// Does step `s` read or write bytes overlapping `slot`, other than through slots rooted at `own`?
-static bool step_touches(const fb200_plan& p, const Step& s, int slot, int own) {
-  auto hit = [&](int x) { return x >= 0 && root_slot(p, x) != own && ranges_overlap(p, x, slot); };
-  for (int x : s.in) if (hit(x)) return true;
-  for (int x : s.epi_operand_slot) if (hit(x)) return true;
-  if (hit(s.write_slot)) return true;
-  for (int x : {s.fan_q, s.fan_k, s.fan_v, s.fan_dest, s.dw_x, s.dw_w, s.dw_bias}) if (hit(x)) return true;
-  return false;
 }
 
 // reshape whose source could not become the view (the planner reuses the source's bytes while the
@@ -1065,7 +1148,7 @@ static int run_step(fb200_plan* p, Step& s, const void* const* inputs, void* con
                                  slot_ptr(p, s.fan_v, inputs, outputs), vb.dims[0], vb.dims[1],
                                  slot_ptr(p, s.fan_dest, inputs, outputs), db.dims[1],
                                  static_cast<const fb200_attention_head*>(s.fan_table), s.fan_heads,
-                                 s.fan_sq, s.fan_sk, 64, db.dtype, stream);
+                                 s.fan_sq, s.fan_sk, 64, s.fan_scale, db.dtype, stream);
     }
   }
   return FB200_OK;
@@ -1073,11 +1156,12 @@ static int run_step(fb200_plan* p, Step& s, const void* const* inputs, void* con
 
 }  // namespace fb200
 
-extern "C" int fb200_plan_create(const char* plan_text, int device, int allow_tf32, int opt_level,
-                                 fb200_plan** plan) {
+static int plan_create_impl(const char* plan_text, int device, int allow_tf32, int opt_level, bool dry,
+                            fb200_plan** plan) {
   if (plan_text == nullptr || plan == nullptr) return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_create: null argument");
   *plan = nullptr;
   fb200_plan* p = new fb200_plan();
+  p->dry = dry;
   p->device = device;
   p->allow_tf32 = allow_tf32;
   p->opt_level = opt_level;
@@ -1096,7 +1180,7 @@ extern "C" int fb200_plan_create(const char* plan_text, int device, int allow_tf
   if (rc == FB200_OK) {
     // graph outputs are written in the caller's buffers, never in the arena
     for (int o : p->output_slots) p->slots[o].arena_offset = -1;
-    if (p->arena_bytes > 0) rc = fb200_malloc(device, p->arena_bytes, 256, &p->arena);
+    if (p->arena_bytes > 0 && !dry) rc = fb200_malloc(device, p->arena_bytes, 256, &p->arena);
   }
   for (size_t i = 0; rc == FB200_OK && i < p->steps.size(); ++i) {
     if (p->steps[i].kind == Kind::kConstant) rc = materialise_constant(p, p->steps[i]);
@@ -1118,6 +1202,15 @@ extern "C" int fb200_plan_create(const char* plan_text, int device, int allow_tf
   }
   *plan = p;
   return FB200_OK;
+}
+
+extern "C" int fb200_plan_create(const char* plan_text, int device, int allow_tf32, int opt_level,
+                                 fb200_plan** plan) {
+  return plan_create_impl(plan_text, device, allow_tf32, opt_level, false, plan);
+}
+
+extern "C" int fb200_plan_describe(const char* plan_text, int opt_level, fb200_plan** plan) {
+  return plan_create_impl(plan_text, 0, 0, opt_level, true, plan);
 }
 
 extern "C" int fb200_plan_destroy(fb200_plan* p) {
@@ -1152,6 +1245,7 @@ extern "C" int fb200_plan_io_spec(const fb200_plan* p, int is_output, int index,
 extern "C" int fb200_plan_run(fb200_plan* p, const void* const* inputs, void* const* outputs,
                               fb200_stream stream) {
   if (p == nullptr) return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_run: null plan");
+  if (p->dry) return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_run: this plan was made by fb200_plan_describe and cannot run");
   if ((!p->input_slots.empty() && inputs == nullptr) || (!p->output_slots.empty() && outputs == nullptr)) {
     return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_run: null input/output table");
   }
@@ -1240,6 +1334,7 @@ extern "C" int fb200_plan_run(fb200_plan* p, const void* const* inputs, void* co
 extern "C" int fb200_plan_run_host(fb200_plan* p, const void* const* host_inputs,
                                    void* const* host_outputs, fb200_stream stream) {
   if (p == nullptr) return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_run_host: null plan");
+  if (p->dry) return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_run_host: this plan was made by fb200_plan_describe and cannot run");
   {
     std::lock_guard<std::mutex> lock(p->mu);
     if (p->stage_in.empty() && p->stage_out.empty()) {
@@ -1272,6 +1367,7 @@ extern "C" int fb200_plan_profile(fb200_plan* p, const void* const* inputs, void
   if (p == nullptr || step_ms == nullptr || n_steps == nullptr) {
     return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_profile: null argument");
   }
+  if (p->dry) return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_profile: this plan was made by fb200_plan_describe and cannot run");
   const int n = static_cast<int>(p->steps.size());
   *n_steps = n;
   if (cap < n) return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_profile: room for %d steps, plan has %d", cap, n);

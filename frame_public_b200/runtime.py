@@ -20,6 +20,24 @@ def load_plan_text(name: str) -> str:
         return f.read()
 
 
+def describe_plan(plan_text: str, opt_level: int = 1):
+    """(step names, launches per run) of a plan after the executor's rewrites, without touching a
+    GPU (fb200_plan_describe): what would run, not a runnable plan."""
+    lib = capi.load()
+    h = c_void_p()
+    capi.check(lib.fb200_plan_describe(plan_text.encode(), opt_level, byref(h)))
+    try:
+        names = []
+        while True:
+            name = lib.fb200_plan_step_op(h, len(names)).decode()
+            if not name:
+                break
+            names.append(name)
+        return names, int(lib.fb200_plan_launches_per_run(h))
+    finally:
+        lib.fb200_plan_destroy(h)
+
+
 class CompiledPlan:
     def __init__(self, plan_text: str, device: int = 0, allow_tf32: bool = False, opt_level: int = 1):
         self.lib = capi.load()

@@ -258,6 +258,9 @@ FB200_API int fb200_selective_scan_noalloc(const void* x, const void* a, const v
  * storage dtype exactly where the separate operators would round it.  For head h:
  *   Q_h = sq x 64 window of q_base (row-major, q_rows x q_ld) at (q_row, q_col); K_h, V_h likewise
  *   with sk rows; O_h (sq x 64, row pitch o_ld) is written at element offset o_offset of o_base.
+ * `scale` (> 0; 1 = none) stands for the elementwise `mul` by a constant that the reference's
+ * attention puts between the first matmul and the softmax (src/nn/layers.cpp:1062-1071): the
+ * rounded scores are multiplied by it and rounded to the storage dtype again.
  * Column coordinates must be multiples of 8 elements (a table entry that is not is refused by
  * the kernel, which records status 305).  `heads_dev` is a DEVICE array owned by the caller.
  * Supported: bfloat16 / float16, head_dim 64, 64 <= sk <= 512 in multiples of 64, any sq >= 1
@@ -272,7 +275,7 @@ FB200_API int fb200_attention_fan(const void* q_base, int64_t q_rows, int64_t q_
                                   const void* v_base, int64_t v_rows, int64_t v_ld, void* o_base,
                                   int64_t o_ld, const fb200_attention_head* heads_dev,
                                   int64_t n_heads, int64_t sq, int64_t sk, int64_t head_dim,
-                                  int dtype, fb200_stream stream);
+                                  float scale, int dtype, fb200_stream stream);
 /* NEW op (no reference counterpart): the Mamba SSM scan with un-materialised operands, fp32.
  * u, delta, z, y: [batch, len, dm]; A: [dm, nstate]; B, C: [batch, len, nstate]; D: [dm];
  * z may be NULL.  h[n] = exp(delta*A[d,n])*h[n] + delta*B[n]*u; y = sum_n C[n]*h[n] + D[d]*u;
@@ -315,6 +318,11 @@ FB200_API int fb200_sum_axes(const void* x, void* out, int rank, const int64_t* 
 typedef struct fb200_plan fb200_plan;
 FB200_API int fb200_plan_create(const char* plan_text, int device, int allow_tf32, int opt_level,
                                 fb200_plan** plan);
+/* The same parsing and rewriting without a device: allocates nothing on the GPU (and needs none),
+ * so the result only answers fb200_plan_launches_per_run / fb200_plan_step_op / io_spec /
+ * arena_bytes; every run entry point refuses it.  For tooling and for tests of the rewrite rules on
+ * machines without a GPU.  Free it with fb200_plan_destroy. */
+FB200_API int fb200_plan_describe(const char* plan_text, int opt_level, fb200_plan** plan);
 FB200_API int fb200_plan_destroy(fb200_plan* plan);
 FB200_API int fb200_plan_num_inputs(const fb200_plan* plan);
 FB200_API int fb200_plan_num_outputs(const fb200_plan* plan);

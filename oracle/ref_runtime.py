@@ -54,6 +54,9 @@ def load():
         s.fref_device_buffer.argtypes = [c_void_p, c_int, c_int]
         s.fref_pipeline_text.restype = c_int64
         s.fref_pipeline_text.argtypes = [c_char_p, c_char_p, c_char_p, c_int64, c_char_p, c_int]
+        s.fref_nn_graph_text.restype = c_int64
+        s.fref_nn_graph_text.argtypes = [c_char_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int, c_int,
+                                         c_char_p, c_int, c_char_p, c_int64, c_char_p, c_int]
         s.fref_plan_text.restype = c_int64
         s.fref_plan_text.argtypes = [c_char_p, c_char_p, c_int, c_char_p, c_int64, c_char_p, c_int]
         s.fref_fallback_count.restype = c_int64
@@ -128,6 +131,22 @@ def pipeline_text(ir_text: str, backend: str = "cpu") -> str:
         raise RuntimeError(f"pipeline failed: {err.value.decode('utf-8', 'replace')}")
     buf = create_string_buffer(int(n))
     s.fref_pipeline_text(ir_text.encode(), backend.encode(), buf, n, err, len(err))
+    return buf.value.decode()
+
+
+def nn_graph_text(kind: str, batch: int, p1: int, p2: int, p3: int, p4: int = 0, with_bias: bool = True,
+                  dtype_code: int = 0, backend: str = "cpu", device: int = 0) -> str:
+    """IR text of one of the reference's own nn:: modules (include/frame/nn/layers.h:157-234) as its
+    builder emits it: "transformer" (batch, seq, embed, heads, ffn), "mha" (batch, seq, embed, heads),
+    "mamba" (batch, steps, channels, kernel).  Input 0 is the activation, the parameters follow."""
+    s = load()
+    err = create_string_buffer(2048)
+    args = (kind.encode(), batch, p1, p2, p3, p4, int(with_bias), dtype_code, backend.encode(), device)
+    n = s.fref_nn_graph_text(*args, None, 0, err, len(err))
+    if n < 0:
+        raise RuntimeError(f"nn graph failed: {err.value.decode('utf-8', 'replace')}")
+    buf = create_string_buffer(int(n))
+    s.fref_nn_graph_text(*args, buf, n, err, len(err))
     return buf.value.decode()
 
 

@@ -32,6 +32,8 @@
 #include <frame/hal/stream.h>
 #include <frame/ir/graph.h>
 #include <frame/ir/serialization.h>
+#include <frame/nn/layers.h>
+#include <frame/nn/module.h>
 #include <frame/ops/executable_plan.h>
 #include <frame/ops/kernel_registry.h>
 #include <frame/ops/op_registry.h>
@@ -235,6 +237,75 @@ void* fref_device_buffer(void* handle, int is_output, int index) {
   auto& v = is_output ? h->dev_out : h->dev_in;
   if (index < 0 || static_cast<size_t>(index) >= v.size()) return nullptr;
   return v[static_cast<size_t>(index)].raw_data();
+}
+
+// IR text of one of the reference's own nn:: modules, built by the reference's builder
+// (include/frame/nn/layers.h:157-234, src/nn/layers.cpp): graph input 0 is the activation, the
+// module's parameters follow in Module::parameters() order.  kind: "transformer" =
+// nn::TransformerEncoderBlock(batch, seq, embed, heads, ffn, with_bias), x: [batch*seq, embed];
+// "mha" = nn::MultiheadAttention(batch, seq, embed, heads, with_bias); "mamba" =
+// nn::Mamba(batch, channels = p2, steps = p1, kernel = p3), x: [batch, channels, steps].
+// Returns the number of bytes needed, -1 on error.
+int64_t fref_nn_graph_text(const char* kind, int64_t batch, int64_t p1, int64_t p2, int64_t p3,
+                           int64_t p4, int with_bias, int dtype_code, const char* backend,
+                           int device_index, char* out, int64_t cap, char* err, int errlen) {
+  const std::string_view bname = static_backend_name(backend);
+  if (bname.empty()) {
+    set_err(err, errlen, "unknown backend");
+    return -1;
+  }
+  const frame::DType dtype(static_cast<frame::DTypeCode>(dtype_code));
+  const Device device{bname, device_index};
+  const std::string k(kind);
+  frame::nn::Module module;
+  frame::Shape x_shape;
+  if (k == "transformer") {
+    module = frame::nn::TransformerEncoderBlock("block", batch, p1, p2, p3, p4, with_bias != 0, dtype);
+    x_shape = frame::Shape({batch * p1, p2});
+  } else if (k == "mha") {
+    module = frame::nn::MultiheadAttention("mha", batch, p1, p2, p3, with_bias != 0, dtype);
+    x_shape = frame::Shape({batch * p1, p2});
+  } else if (k == "mamba") {
+    module = frame::nn::Mamba("mamba", batch, p2, p1, p3, dtype);
+    x_shape = frame::Shape({batch, p2, p1});
+  } else {
+    set_err(err, errlen, "unknown module kind");
+    return -1;
+  }
+  frame::ir::Graph graph("nn_" + k);
+  frame::ir::TensorType xt;
+  xt.dtype = dtype;
+  xt.shape = x_shape;
+  xt.layout = frame::ir::Layout::kRowMajor;
+  xt.device = device;
+  Result<frame::ir::Value*> x = graph.add_graph_input(xt);
+  if (!x.is_ok()) {
+    set_err(err, errlen, std::string(x.status().message()));
+    return -1;
+  }
+  std::vector<frame::nn::ParamSpec> specs = module.parameters();
+  for (auto& spec : specs) spec.type.device = device;
+  Result<std::vector<frame::ir::Value*>> params = frame::nn::add_parameter_inputs(graph, specs);
+  if (!params.is_ok()) {
+    set_err(err, errlen, std::string(params.status().message()));
+    return -1;
+  }
+  Result<std::vector<frame::ir::Value*>> outs =
+      module.build(graph, std::vector<frame::ir::Value*>{x.value()}, params.value());
+  if (!outs.is_ok()) {
+    set_err(err, errlen, std::string(outs.status().message()));
+    return -1;
+  }
+  for (frame::ir::Value* v : outs.value()) {
+    const Status st = graph.mark_output(v);
+    if (!st.is_ok()) {
+      set_err(err, errlen, std::string(st.message()));
+      return -1;
+    }
+  }
+  const std::string text = frame::ir::dump_text(graph);
+  if (out != nullptr && cap > 0) std::snprintf(out, static_cast<size_t>(cap), "%s", text.c_str());
+  return static_cast<int64_t>(text.size()) + 1;
 }
 
 // IR text after the standard nine-pass pipeline for `backend` (what

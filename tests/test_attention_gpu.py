@@ -59,6 +59,29 @@ def test_fan_over_a_fused_qkv_projection(batch, heads, seq, dt):
         assert fo.all_close(got, exp, dt, **TOL), fo.max_err(got, exp, dt)
 
 
+@pytest.mark.parametrize("scale", [0.125, 0.3])
+def test_scores_scaled_by_a_constant_before_the_softmax(scale):
+    """The reference's own attention multiplies the scores by a constant tensor filled with
+    1/sqrt(head_dim) (an elementwise mul, rounded to the storage dtype) before the softmax."""
+    dt = fo.DT_BF16
+    rng = np.random.default_rng(5)
+    q, k, v = (_store(rng.uniform(-1, 1, (128, 64)), dt) for _ in range(3))
+    const = _store(np.full((128, 128), scale, dtype=np.float32), dt)
+    s = fo.mul(fo.matmul(q, np.ascontiguousarray(k.T), dt), const, dt)
+    exp = fo.matmul(fo.softmax(s, dt), v, dt)
+    table = np.zeros(1, dtype=capi.HEAD_DTYPE)
+    bufs = [capi.DeviceBuffer.from_numpy(t) for t in (q, k, v)]
+    out = capi.DeviceBuffer(128 * 64 * 2)
+    d_tab = capi.DeviceBuffer.from_numpy(table.view(np.uint8))
+    stored_scale = float(fo.to_accum(const, dt)[0, 0])
+    capi.attention_fan(bufs[0].ptr, 128, 64, bufs[1].ptr, 128, 64, bufs[2].ptr, 128, 64, out.ptr, 64,
+                       d_tab.ptr, 1, 128, 128, 64, dt, scale=stored_scale)
+    capi.synchronize()
+    assert capi.kernel_status(0) == 0
+    got = out.download(np.uint16, (128, 64))
+    assert fo.all_close(got, exp, dt, **TOL), fo.max_err(got, exp, dt)
+
+
 def test_ragged_queries_separate_operands_and_untouched_neighbours():
     """sq = 200 (two query blocks, the second partly empty), sk = 192, q / k / v in separate
     matrices with different pitches, the output inside a wider matrix whose other bytes stay."""
@@ -94,6 +117,6 @@ def test_unsupported_shapes_are_unimplemented_not_wrong():
                           (128, 128, 64, capi.F32)]:
         assert lib.fb200_attention_fan_supported(sq, sk, d, dt) == 0
         rc = lib.fb200_attention_fan(buf.ptr, 128, 64, buf.ptr, 128, 64, buf.ptr, 128, 64, buf.ptr, 64,
-                                     buf.ptr, 1, sq, sk, d, dt, None)
+                                     buf.ptr, 1, sq, sk, d, 1.0, dt, None)
         assert rc == 4 and b"attention_fan" in lib.fb200_last_error()
     assert lib.fb200_attention_fan_supported(512, 512, 64, capi.BF16) == 1

@@ -1,0 +1,80 @@
+"""The plan executor's rewrite rules, checked without a GPU through fb200_plan_describe: the same
+parsing, aliasing, epilogue absorption and group recognition as fb200_plan_create, minus every
+device allocation.  Plans are the ones the reference pipeline and memory planner emitted for backend
+"cuda" (tests/golden/plans/, frame_public_b200/plans/)."""
+import os
+
+import pytest
+
+from frame_public_b200 import capi, runtime
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _golden(name):
+    with open(os.path.join(HERE, "golden", "plans", name + ".plan")) as f:
+        return f.read()
+
+
+def _live(names):
+    return [n for n in names if not n.startswith("(") and n != "constant"]
+
+
+def test_transformer_block_becomes_eight_launches():
+    text = runtime.load_plan_text("transformer_bf16_b8_s512_d1024")
+    names, launches = runtime.describe_plan(text, opt_level=1)
+    assert len(names) == 922
+    assert launches == 8
+    assert _live(names) == ["layer_norm", "matmul", "attention_fan", "matmul", "add", "layer_norm",
+                            "matmul+epilogue", "matmul+epilogue"]
+    plain, plain_launches = runtime.describe_plan(text, opt_level=0)
+    assert plain.count("softmax") == 128 and plain.count("attention_fan") == 0
+    assert plain_launches > 900
+
+
+def test_reference_nn_attention_with_its_scale_mul_is_recognised():
+    names, _ = runtime.describe_plan(_golden("nn_transformer_bf16_b2_s128_e128_h2"))
+    live = _live(names)
+    assert live.count("attention_fan") == 1
+    assert not any(n in ("softmax", "transpose", "concat", "slice", "mul") for n in live)
+    # the fp32 block is outside the fused kernel (16-bit dtypes only): it stays step by step
+    f32, _ = runtime.describe_plan(_golden("nn_transformer_f32_b2_s16_e32_h2"))
+    assert f32.count("attention_fan") == 0 and f32.count("softmax") == 4
+
+
+def test_mamba_conv_group_and_reshape_views():
+    names, launches = runtime.describe_plan(runtime.load_plan_text("mamba_f32_b16_s2048_d768"))
+    live = _live(names)
+    assert live.count("dwconv1d_time_major") == 1 and live.count("mamba_scan") == 1
+    assert "conv1d" not in live and "transpose" not in live and "silu" not in live
+    assert live.count("reshape") == 1           # the gate's reshape: its source is still being read
+    assert launches == 10
+    # miniature plan: the planner put the x_proj output on the bytes the fused result would need
+    small, _ = runtime.describe_plan(_golden("mamba_f32_b2_s24_d16"))
+    assert small.count("dwconv1d_time_major") == 0 and small.count("conv1d") == 1
+
+
+def test_mlp_absorbs_what_the_planner_allows():
+    names, launches = runtime.describe_plan(_golden("mlp_f32_b8"))
+    assert launches == 5
+    assert _live(names) == ["matmul+epilogue", "matmul", "fused_elementwise_internal", "matmul+epilogue",
+                            "softmax"]
+    _, plain = runtime.describe_plan(_golden("mlp_f32_b8"), opt_level=0)
+    assert plain == 7
+
+
+def test_a_described_plan_cannot_run():
+    lib = capi.load()
+    h = capi.c_void_p()
+    capi.check(lib.fb200_plan_describe(_golden("mlp_f32_b8").encode(), 1, capi.byref(h)))
+    rc = lib.fb200_plan_run(h, None, None, None)
+    assert rc == 1 and b"cannot run" in lib.fb200_last_error()
+    lib.fb200_plan_destroy(h)
+
+
+def test_unknown_op_is_unimplemented_with_its_name_without_a_gpu():
+    lib = capi.load()
+    text = "plan slots=2 arena=0\nin 0 0 1 4\nstep frobnicate nin=1 0 nout=1 1 0 -1 1 4 attrs=0\nout 1\n"
+    h = capi.c_void_p()
+    rc = lib.fb200_plan_describe(text.encode(), 1, capi.byref(h))
+    assert rc == 4 and b"frobnicate" in lib.fb200_last_error()
