@@ -119,7 +119,6 @@ def conv2d(x, w, bias=None, stride=(1, 1), padding=(0, 0), groups: int = 1, dtyp
             cif = g * cpg + ci
             for i in range(kh):
                 # valid output rows: 0 <= o*sh - ph + i < h
-                o_lo = max(0, -((i - ph) // sh)) if (i - ph) < 0 else 0
                 o_lo = 0
                 while o_lo < oh and o_lo * sh - ph + i < 0:
                     o_lo += 1
