@@ -401,9 +401,11 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised under
-# profiles/ (null until a capture of that workload exists)
-TRAFFIC = {}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, in bytes, from the
+# ncu captures summarised under profiles/ (null where no capture of that workload exists)
+TRAFFIC = {
+    "gemm_bias_gelu_bf16_8192": 1.31e9,   # profiles/gemm_tcgen05_bf16_dram_traffic_8192.md
+}
 
 
 def cpu_slab_baseline(wl, host_inputs, target_seconds):
