@@ -54,3 +54,22 @@ def test_selective_scan_through_reference_api_matches_known_answer():
     ins = [np.array(v, np.float32) for v in ([1, 2, -1], [0.5, 0.25, -0.5], [2, 1, 3], [1, 2, 0.5], [0.1, -1, 2])]
     (out,) = comp.run(ins)
     assert fo.all_close(out, np.array([2.1, 3.0, -4.125], np.float32))
+
+
+@pytest.mark.parametrize("spec", configs.NN_GRAPHS, ids=lambda s: s[0])
+def test_reference_nn_module_runs_on_cuda_without_fallback(spec):
+    """The reference's own nn:: builders (nn::TransformerEncoderBlock, nn::Mamba) emit the graph; the
+    reference's runtime::compile sends it to backend "cuda" (this plugin) and to its CPU backend; both
+    run the same seeded parameters.  Nothing may fall back to the eager chain."""
+    name, kind, args, dtype = spec
+    text_cpu = ref_runtime.nn_graph_text(kind, *args, dtype_code=dtype, backend="cpu")
+    text_gpu = ref_runtime.nn_graph_text(kind, *args, dtype_code=dtype, backend="cuda")
+    cpu = ref_runtime.Compiled(text_cpu, "cpu")
+    ins = configs.nn_inputs([shape for _, shape in cpu.inputs], dtype)
+    (exp,) = cpu.run(ins)
+    gpu = ref_runtime.Compiled(text_gpu, "cuda")
+    (got,) = gpu.run(ins)
+    tol = dict(rtol=2e-2, atol=2e-2) if dtype == configs.BF16 else dict(rtol=1e-5, atol=2e-6)
+    assert fo.all_close(got, exp, dtype, **tol), (name, fo.max_err(got, exp, dtype))
+    for op in OPS + ["sigmoid", "tanh", "constant"]:
+        assert ref_runtime.fallback_count(op, "cuda") == 0, f"op {op} fell back to the eager chain"
