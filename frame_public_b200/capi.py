@@ -24,7 +24,7 @@ NP_STORAGE = {F32: np.float32, F64: np.float64, F16: np.uint16, BF16: np.uint16,
               I16: np.int16, I32: np.int32, I64: np.int64, U8: np.uint8, BOOL: np.uint8}
 
 EW = {"add": 1, "mul": 2, "relu": 3, "square": 4, "sigmoid": 5, "tanh": 6, "rsqrt": 7,
-      "gelu": 8, "silu": 9, "softplus": 10, "exp": 11}
+      "gelu": 8, "silu": 9, "softplus": 10, "exp": 11, "heaviside_surrogate": 12}
 EW_ARITY = {"add": 2, "mul": 2}
 OPERAND_FULL, OPERAND_COL, OPERAND_ROW = 0, 1, 2
 H2D, D2H, D2D = 1, 2, 3
@@ -91,6 +91,9 @@ SIGNATURES = {
                              POINTER(Epilogue), _P]),
     "fb200_conv1d": (c_int, [_P, _P, _P, _P] + [c_int64] * 8 + [c_int, _P]),
     "fb200_max_pool2d": (c_int, [_P, _P] + [c_int64] * 10 + [c_int, _P]),
+    "fb200_avg_pool2d": (c_int, [_P, _P] + [c_int64] * 10 + [c_int, _P]),
+    "fb200_gather": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int, c_int, _P]),
+    "fb200_scatter_add": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int, c_int, _P]),
     "fb200_softmax": (c_int, [_P, _P, c_int64, c_int64, c_int, _P]),
     "fb200_layer_norm": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_double, c_int, _P]),
     "fb200_selective_scan": (c_int, [_P] * 6 + [c_int64, c_int64, c_int, _P]),
@@ -252,6 +255,18 @@ def conv1d(x, w, bias, out, n, cin, l, cout, k, stride, padding, groups, dtype, 
 
 def max_pool2d(x, out, n, c, h, w, kh, kw, sh, sw, ph, pw, dtype, stream=None):
     check(load().fb200_max_pool2d(x, out, n, c, h, w, kh, kw, sh, sw, ph, pw, dtype, stream))
+
+
+def avg_pool2d(x, out, n, c, h, w, kh, kw, sh, sw, ph, pw, dtype, stream=None):
+    check(load().fb200_avg_pool2d(x, out, n, c, h, w, kh, kw, sh, sw, ph, pw, dtype, stream))
+
+
+def gather(x, indices, out, n, f, k, dtype, index_dtype, stream=None):
+    check(load().fb200_gather(x, indices, out, n, f, k, dtype, index_dtype, stream))
+
+
+def scatter_add(updates, indices, out, k, f, v, dtype, index_dtype, stream=None):
+    check(load().fb200_scatter_add(updates, indices, out, k, f, v, dtype, index_dtype, stream))
 
 
 def softmax(x, out, rows, cols, dtype, stream=None):

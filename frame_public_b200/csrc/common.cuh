@@ -151,6 +151,7 @@ __device__ __forceinline__ float ew_unary(int op, float x) {
       return __logf(1.0f + e);
     }
     case FB200_EW_EXP: return expf(x);
+    case FB200_EW_HEAVISIDE: return x >= 0.0f ? 1.0f : 0.0f;
     default: return x;
   }
 }
@@ -160,6 +161,6 @@ __device__ __forceinline__ float ew_binary(int op, float a, float b) {
 }
 
 inline bool ew_is_binary(int op) { return op == FB200_EW_ADD || op == FB200_EW_MUL; }
-inline bool ew_is_known(int op) { return op >= FB200_EW_ADD && op <= FB200_EW_EXP; }
+inline bool ew_is_known(int op) { return op >= FB200_EW_ADD && op <= FB200_EW_HEAVISIDE; }
 
 }  // namespace fb200

@@ -437,6 +437,80 @@ extern "C" int fb200_max_pool2d(const void* x, void* out, int64_t n, int64_t c, 
   return after_launch("max_pool2d_kernel");
 }
 
+// ---- avg_pool2d ------------------------------------------------------------------------------------
+// Sum of the valid positions of the window in (kh, kw) order, divided by KH*KW whatever the padding
+// (src/backends/cpu/kernels/pool.cpp:280-303): the same fp32 additions in the same order and one
+// fp32 division, so results are bit-identical to the CPU reference.  As in the max-pool window
+// kernel every tap is loaded from a clamped address before it is used, so the loads of a window are
+// in flight together; an invalid tap contributes nothing (it is skipped, not added as zero, which
+// matters for -0 and NaN only in theory but keeps the operation count identical).
+namespace fb200 {
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+avg_pool2d_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t nc, int64_t h, int64_t w, int kh,
+                  int kw, int sh, int sw, int ph, int pw, int64_t oh, int64_t ow) {
+  const int64_t total = nc * oh * ow;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const float denom = static_cast<float>(kh * kw);
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int64_t q = i % ow;
+    int64_t rem = i / ow;
+    const int64_t o = rem % oh;
+    rem /= oh;
+    const T* xc = x + rem * h * w;
+    float acc = 0.0f;
+    for (int a = 0; a < kh; ++a) {
+      const int64_t ih = o * sh - ph + a;
+      if (ih < 0 || ih >= h) continue;
+      for (int b = 0; b < kw; ++b) {
+        const int64_t iw = q * sw - pw + b;
+        if (iw < 0 || iw >= w) continue;
+        acc += to_f32(xc[ih * w + iw]);
+      }
+    }
+    out[i] = from_f32<T>(acc / denom);
+  }
+}
+
+}  // namespace fb200
+
+extern "C" int fb200_avg_pool2d(const void* x, void* out, int64_t n, int64_t c, int64_t h, int64_t w,
+                                int64_t kh, int64_t kw, int64_t stride_h, int64_t stride_w,
+                                int64_t pad_h, int64_t pad_w, int dtype, fb200_stream stream) {
+  if (n < 0 || c < 0 || h < 1 || w < 1 || kh < 1 || kw < 1 || stride_h < 1 || stride_w < 1 ||
+      pad_h < 0 || pad_w < 0) {
+    return set_error(FB200_INVALID_ARGUMENT, "avg_pool2d: invalid geometry");
+  }
+  if (2 * pad_h > kh || 2 * pad_w > kw) {
+    return set_error(FB200_INVALID_ARGUMENT, "avg_pool2d: padding*2 must not exceed kernel");
+  }
+  if (h + 2 * pad_h < kh || w + 2 * pad_w < kw) {
+    return set_error(FB200_INVALID_ARGUMENT, "avg_pool2d: non-positive output size");
+  }
+  const int64_t oh = (h + 2 * pad_h - kh) / stride_h + 1;
+  const int64_t ow = (w + 2 * pad_w - kw) / stride_w + 1;
+  if (n == 0 || c == 0) return FB200_OK;
+  if (x == nullptr || out == nullptr) return set_error(FB200_INVALID_ARGUMENT, "avg_pool2d: null argument");
+  cudaStream_t s = as_stream(stream);
+  const int grid = grid_for(n * c * oh * ow, 256, 8);
+  auto run = [&](auto tag) {
+    using T = decltype(tag);
+    avg_pool2d_kernel<T><<<grid, 256, 0, s>>>(static_cast<const T*>(x), static_cast<T*>(out), n * c, h, w,
+                                              static_cast<int>(kh), static_cast<int>(kw),
+                                              static_cast<int>(stride_h), static_cast<int>(stride_w),
+                                              static_cast<int>(pad_h), static_cast<int>(pad_w), oh, ow);
+  };
+  switch (dtype) {
+    case FB200_F32: run(float{}); break;
+    case FB200_BF16: run(__nv_bfloat16{}); break;
+    case FB200_F16: run(__half{}); break;
+    default:
+      return set_error(FB200_INVALID_ARGUMENT, "avg_pool2d: dtype code %d is not float32/float16/bfloat16", dtype);
+  }
+  return after_launch("avg_pool2d_kernel");
+}
+
 // ---- depthwise conv1d along time, in the time-major layout -----------------------------------------
 // The reference's Mamba block computes its causal depthwise convolution as
 //   transpose [B,L,C] -> [B,C,L], conv1d(groups = C, padding = K-1), slice to L, activation,

@@ -64,6 +64,7 @@ __device__ __forceinline__ void ew_unary_vec(int op, float (&v)[NV]) {
     FB200_UNARY_CASE(FB200_EW_SILU)
     FB200_UNARY_CASE(FB200_EW_SOFTPLUS)
     FB200_UNARY_CASE(FB200_EW_EXP)
+    FB200_UNARY_CASE(FB200_EW_HEAVISIDE)
 #undef FB200_UNARY_CASE
     default: break;
   }

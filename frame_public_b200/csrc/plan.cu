@@ -30,7 +30,7 @@ namespace fb200 {
 
 enum class Kind {
   kMatmul, kConv2d, kConv1d, kMaxPool, kChain, kBiasAdd, kSoftmax, kLayerNorm, kScan, kMambaScan,
-  kTranspose, kSlice, kConcat, kSum, kCopy, kAlias, kConstant, kSkip, kAttentionFan, kDwConvTimeMajor
+  kTranspose, kSlice, kConcat, kSum, kCopy, kAlias, kConstant, kSkip, kAttentionFan, kDwConvTimeMajor, kAvgPool, kGather, kScatterAdd
 };
 
 struct SlotInfo {
@@ -162,8 +162,8 @@ static std::string unquote(const std::string& t) {
 
 static int ew_code(const std::string& name) {
   static const char* names[] = {"", "add", "mul", "relu", "square", "sigmoid", "tanh", "rsqrt",
-                                "gelu", "silu", "softplus", "exp"};
-  for (int i = 1; i <= 11; ++i) if (name == names[i]) return i;
+                                "gelu", "silu", "softplus", "exp", "heaviside_surrogate"};
+  for (int i = 1; i <= 12; ++i) if (name == names[i]) return i;
   return 0;
 }
 
@@ -305,6 +305,29 @@ static int decode_step(fb200_plan* p, Step& s) {
     auto kv = parse_int_list(k->text), sv = parse_int_list(st->text), pv = parse_int_list(pd->text);
     if (kv.size() != 2 || sv.size() != 2 || pv.size() != 2) return set_error(FB200_INVALID_ARGUMENT, "op 'max_pool2d': malformed attributes");
     s.iv = {kv[0], kv[1], sv[0], sv[1], pv[0], pv[1]};
+  } else if (op == "avg_pool2d") {
+    s.kind = Kind::kAvgPool;
+    const Attr *k = need("kernel"), *st = need("stride"), *pd = need("padding");
+    if (!k || !st || !pd) return FB200_INVALID_ARGUMENT;
+    auto kv = parse_int_list(k->text), sv = parse_int_list(st->text), pv = parse_int_list(pd->text);
+    if (kv.size() != 2 || sv.size() != 2 || pv.size() != 2) return set_error(FB200_INVALID_ARGUMENT, "op 'avg_pool2d': malformed attributes");
+    s.iv = {kv[0], kv[1], sv[0], sv[1], pv[0], pv[1]};
+  } else if (op == "gather") {
+    s.kind = Kind::kGather;
+    p->graph_enabled = false;   // the index check synchronises the stream
+  } else if (op == "scatter_add" || op == "gather_grad_internal") {
+    s.kind = Kind::kScatterAdd;
+    p->graph_enabled = false;
+  } else if (op == "heaviside_surrogate") {
+    const Attr* a = need("alpha");
+    if (!a) return FB200_INVALID_ARGUMENT;
+    const double alpha = strtod(a->text.c_str(), nullptr);
+    if (!(alpha > 0.0) || alpha != alpha || alpha > 1.7e308) {
+      return set_error(FB200_INVALID_ARGUMENT, "op 'heaviside_surrogate': attribute 'alpha' must be finite and positive, got %g", alpha);
+    }
+    s.kind = Kind::kChain;
+    s.chain_ops = {FB200_EW_HEAVISIDE};
+    s.chain_arity = {1};
   } else if (op == "fused_elementwise_internal") {
     s.kind = Kind::kChain;
     const Attr *o = need("ops"), *a = need("arities");
@@ -1075,6 +1098,26 @@ static int run_step(fb200_plan* p, Step& s, const void* const* inputs, void* con
                               in_slot(0).dims[2], in_slot(0).dims[3], s.iv[0], s.iv[1], s.iv[2],
                               s.iv[3], s.iv[4], s.iv[5], os.dtype, stream);
     }
+    case Kind::kAvgPool: {
+      if (in_slot(0).dims.size() != 4) return set_error(FB200_INVALID_ARGUMENT, "op 'avg_pool2d' expects rank-4 x");
+      return fb200_avg_pool2d(in_ptr(0), out, in_slot(0).dims[0], in_slot(0).dims[1], in_slot(0).dims[2],
+                              in_slot(0).dims[3], s.iv[0], s.iv[1], s.iv[2], s.iv[3], s.iv[4], s.iv[5],
+                              os.dtype, stream);
+    }
+    case Kind::kGather: {
+      if (s.in.size() != 2 || in_slot(0).dims.size() != 2 || in_slot(1).dims.size() != 1) {
+        return set_error(FB200_INVALID_ARGUMENT, "op 'gather' expects x [N, F] and indices [K]");
+      }
+      return fb200_gather(in_ptr(0), in_ptr(1), out, in_slot(0).dims[0], in_slot(0).dims[1],
+                          in_slot(1).dims[0], os.dtype, in_slot(1).dtype, stream);
+    }
+    case Kind::kScatterAdd: {
+      if (s.in.size() != 2 || in_slot(0).dims.size() != 2 || in_slot(1).dims.size() != 1 || os.dims.size() != 2) {
+        return set_error(FB200_INVALID_ARGUMENT, "op '%s' expects updates [K, F], indices [K] and a rank-2 result", s.op.c_str());
+      }
+      return fb200_scatter_add(in_ptr(0), in_ptr(1), out, in_slot(0).dims[0], in_slot(0).dims[1],
+                               os.dims[0], os.dtype, in_slot(1).dtype, stream);
+    }
     case Kind::kChain: {
       const void* ptrs[FB200_MAX_CHAIN_INPUTS];
       if (s.in.size() > FB200_MAX_CHAIN_INPUTS) return set_error(FB200_UNIMPLEMENTED, "op '%s': more than %d external inputs", s.op.c_str(), FB200_MAX_CHAIN_INPUTS);
@@ -1195,7 +1238,7 @@ static int plan_create_impl(const char* plan_text, int device, int allow_tf32, i
     fuse_attention_fans(p);
     fuse_time_major_convs(p);
   }
-  if (const char* env = getenv("FRAME_B200_GRAPH")) p->graph_enabled = atoi(env) != 0;
+  if (const char* env = getenv("FRAME_B200_GRAPH")) p->graph_enabled = p->graph_enabled && atoi(env) != 0;
   p->launches = 0;
   for (const Step& s : p->steps) {
     if (s.kind != Kind::kSkip && s.kind != Kind::kAlias && s.kind != Kind::kConstant && s.kind != Kind::kCopy) ++p->launches;

@@ -5,6 +5,7 @@
 // kernel or the whole graph drops to the eager fallback).  Each function only unpacks the
 // borrowed KernelContext and calls the C ABI; dtype dispatch happens inside the library.
 // They replace src/backends/cuda/kernels/*.cpp|*.cu of the reference.
+#include <cmath>
 #include <string>
 #include <variant>
 #include <vector>
@@ -90,8 +91,8 @@ Status elementwise(KernelContext& ctx, const char* op) {
 
 int code_of(std::string_view name) {
   static const char* names[] = {"", "add", "mul", "relu", "square", "sigmoid", "tanh", "rsqrt",
-                                "gelu", "silu", "softplus", "exp"};
-  for (int i = 1; i <= 11; ++i) if (name == names[i]) return i;
+                                "gelu", "silu", "softplus", "exp", "heaviside_surrogate"};
+  for (int i = 1; i <= 12; ++i) if (name == names[i]) return i;
   return 0;
 }
 
@@ -229,6 +230,70 @@ Status max_pool2d(KernelContext& ctx) {
                        (*stride)[1], (*padding)[0], (*padding)[1], dtype_of(x), stream_of(ctx)),
       "max_pool2d");
 }
+
+Status avg_pool2d(KernelContext& ctx) {
+  FRAME_RETURN_IF_ERROR(arity(ctx, "avg_pool2d", 1, 1));
+  const auto* kernel = attr<std::vector<int64_t>>(ctx, "kernel");
+  const auto* stride = attr<std::vector<int64_t>>(ctx, "stride");
+  const auto* padding = attr<std::vector<int64_t>>(ctx, "padding");
+  if (kernel == nullptr || kernel->size() != 2) return missing("avg_pool2d", "kernel");
+  if (stride == nullptr || stride->size() != 2) return missing("avg_pool2d", "stride");
+  if (padding == nullptr || padding->size() != 2) return missing("avg_pool2d", "padding");
+  const Tensor& x = ctx.inputs[0];
+  if (x.shape().rank() != 4) {
+    return Status::make(ErrorCode::kInvalidArgument, "op 'avg_pool2d' cuda kernel requires rank-4 x");
+  }
+  return frame_b200::to_status(
+      fb200_avg_pool2d(x.raw_data(), ctx.outputs[0].raw_data(), x.shape().dim(0), x.shape().dim(1),
+                       x.shape().dim(2), x.shape().dim(3), (*kernel)[0], (*kernel)[1], (*stride)[0],
+                       (*stride)[1], (*padding)[0], (*padding)[1], dtype_of(x), stream_of(ctx)),
+      "avg_pool2d");
+}
+
+// heaviside_surrogate: alpha only shapes the backward graph, but a bad alpha is an error here too
+// (src/backends/cpu/kernels/elementwise.cpp, read_heaviside_alpha).
+Status heaviside_surrogate(KernelContext& ctx) {
+  const double* alpha = attr<double>(ctx, "alpha");
+  if (alpha == nullptr) return missing("heaviside_surrogate", "alpha");
+  if (!std::isfinite(*alpha) || !(*alpha > 0.0)) {
+    return Status::make(ErrorCode::kInvalidArgument,
+                        "op 'heaviside_surrogate' cuda kernel attribute 'alpha' must be finite and positive, got " +
+                            std::to_string(*alpha));
+  }
+  return elementwise<FB200_EW_HEAVISIDE, 1>(ctx, "heaviside_surrogate");
+}
+
+// gather along axis 0 and scatter_add / gather_grad_internal (src/ops/schemas/gather.cpp:86-216).
+Status gather(KernelContext& ctx) {
+  FRAME_RETURN_IF_ERROR(arity(ctx, "gather", 2, 1));
+  const Tensor& x = ctx.inputs[0];
+  const Tensor& idx = ctx.inputs[1];
+  if (x.shape().rank() != 2 || idx.shape().rank() != 1) {
+    return Status::make(ErrorCode::kInvalidArgument, "op 'gather' cuda kernel requires x [N, F] and indices [K]");
+  }
+  return frame_b200::to_status(
+      fb200_gather(x.raw_data(), idx.raw_data(), ctx.outputs[0].raw_data(), x.shape().dim(0), x.shape().dim(1),
+                   idx.shape().dim(0), dtype_of(x), dtype_of(idx), stream_of(ctx)),
+      "gather");
+}
+
+Status scatter_add_like(KernelContext& ctx, const char* op) {
+  FRAME_RETURN_IF_ERROR(arity(ctx, op, 2, 1));
+  const Tensor& u = ctx.inputs[0];
+  const Tensor& idx = ctx.inputs[1];
+  const Tensor& out = ctx.outputs[0];
+  if (u.shape().rank() != 2 || idx.shape().rank() != 1 || out.shape().rank() != 2 ||
+      idx.shape().dim(0) != u.shape().dim(0) || out.shape().dim(1) != u.shape().dim(1)) {
+    return Status::make(ErrorCode::kInvalidArgument,
+                        std::string("op '") + op + "' cuda kernel requires updates [K, F], indices [K], out [V, F]");
+  }
+  return frame_b200::to_status(
+      fb200_scatter_add(u.raw_data(), idx.raw_data(), ctx.outputs[0].raw_data(), u.shape().dim(0), u.shape().dim(1),
+                        out.shape().dim(0), dtype_of(u), dtype_of(idx), stream_of(ctx)),
+      op);
+}
+Status scatter_add(KernelContext& ctx) { return scatter_add_like(ctx, "scatter_add"); }
+Status gather_grad_internal(KernelContext& ctx) { return scatter_add_like(ctx, "gather_grad_internal"); }
 
 // ---- row kernels -----------------------------------------------------------------------------------
 Status softmax(KernelContext& ctx) {
@@ -433,6 +498,11 @@ FRAME_REGISTER_KERNEL("matmul", "cuda", &matmul);
 FRAME_REGISTER_KERNEL("conv2d", "cuda", &conv2d);
 FRAME_REGISTER_KERNEL("conv1d", "cuda", &conv1d);
 FRAME_REGISTER_KERNEL("max_pool2d", "cuda", &max_pool2d);
+FRAME_REGISTER_KERNEL("avg_pool2d", "cuda", &avg_pool2d);
+FRAME_REGISTER_KERNEL("heaviside_surrogate", "cuda", &heaviside_surrogate);
+FRAME_REGISTER_KERNEL("gather", "cuda", &gather);
+FRAME_REGISTER_KERNEL("scatter_add", "cuda", &scatter_add);
+FRAME_REGISTER_KERNEL("gather_grad_internal", "cuda", &gather_grad_internal);
 FRAME_REGISTER_KERNEL("softmax", "cuda", &softmax);
 FRAME_REGISTER_KERNEL("layer_norm", "cuda", &layer_norm);
 FRAME_REGISTER_KERNEL("selective_scan", "cuda", &selective_scan);

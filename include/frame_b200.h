@@ -117,7 +117,8 @@ typedef enum fb200_ew_op {
   FB200_EW_GELU = 8,
   FB200_EW_SILU = 9,
   FB200_EW_SOFTPLUS = 10,
-  FB200_EW_EXP = 11
+  FB200_EW_EXP = 11,
+  FB200_EW_HEAVISIDE = 12   /* heaviside_surrogate forward: x >= 0 ? 1 : 0 (src/backends/cpu/kernels/elementwise.cpp, heaviside_surrogate_cpu_kernel) */
 } fb200_ew_op;
 #define FB200_MAX_CHAIN 8
 #define FB200_MAX_CHAIN_INPUTS 9
@@ -212,6 +213,25 @@ FB200_API int fb200_dwconv1d_time_major(const void* x, int64_t x_ld, const void*
                                         int64_t out_len, int64_t channels, int64_t k, int64_t shift,
                                         const int* unary_ops, int n_ops, int dtype,
                                         fb200_stream stream);
+/* avg_pool2d: sum over the valid positions of the window in (kh, kw) order divided by KH*KW
+ * (padding counts in the denominator), src/backends/cpu/kernels/pool.cpp:280-303; replaces
+ * cudnnPoolingForward of src/backends/cuda/kernels/pool.cpp.  Same geometry rules as max_pool2d. */
+FB200_API int fb200_avg_pool2d(const void* x, void* out, int64_t n, int64_t c, int64_t h,
+                               int64_t w, int64_t kh, int64_t kw, int64_t stride_h,
+                               int64_t stride_w, int64_t pad_h, int64_t pad_w, int dtype,
+                               fb200_stream stream);
+/* gather along axis 0: out[k, :] = x[indices[k], :], x [n, f], indices [k] of int32 / int64
+ * (src/ops/schemas/gather.cpp:86-118; replaces src/backends/cuda/kernels/gather.cu).  An index
+ * outside [0, n) is an error that names the value, found like the reference does by looking at the
+ * indices before the copy: this entry point synchronises the stream once for that.
+ * scatter_add / gather_grad_internal: out [v, f] = 0, then out[indices[k], :] += updates[k, :]
+ * (repeated indices accumulate; fp32 atomics, so the order of additions is not fixed and results
+ * agree with the CPU reference within the tolerance tier, not bit for bit). */
+FB200_API int fb200_gather(const void* x, const void* indices, void* out, int64_t n, int64_t f,
+                           int64_t k, int dtype, int index_dtype, fb200_stream stream);
+FB200_API int fb200_scatter_add(const void* updates, const void* indices, void* out, int64_t k,
+                                int64_t f, int64_t v, int dtype, int index_dtype,
+                                fb200_stream stream);
 /* max_pool2d: max over valid positions only, first maximum wins
  * (src/backends/cpu/kernels/pool.cpp:187-233; replaces cudnnPoolingForward,
  * src/backends/cuda/kernels/pool.cpp:231). */

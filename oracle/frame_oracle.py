@@ -212,6 +212,58 @@ def max_pool2d(x, kernel=(2, 2), stride=(2, 2), padding=(0, 0), dtype: int = DT_
     return from_accum(best, dtype)
 
 
+def avg_pool2d(x, kernel=(2, 2), stride=(2, 2), padding=(0, 0), dtype: int = DT_F32):
+    """Sum over the valid positions in (kh, kw) order, divided by KH*KW whatever the padding
+    (src/backends/cpu/kernels/pool.cpp:280-303); fp32 accumulate, one rounding."""
+    xv = to_accum(x, dtype)
+    n, c, h, wd = xv.shape
+    kh, kw = kernel
+    sh, sw = stride
+    ph, pw = padding
+    oh = conv_out_size(h, kh, sh, ph)
+    ow = conv_out_size(wd, kw, sw, pw)
+    acc = np.zeros((n, c, oh, ow), dtype=F32)
+    for i in range(kh):
+        for j in range(kw):
+            ohs = np.arange(oh) * sh - ph + i
+            ows = np.arange(ow) * sw - pw + j
+            oi = np.nonzero((ohs >= 0) & (ohs < h))[0]
+            qi = np.nonzero((ows >= 0) & (ows < wd))[0]
+            if oi.size == 0 or qi.size == 0:
+                continue
+            vals = xv[:, :, ohs[oi]][:, :, :, ows[qi]]
+            acc[:, :, oi[:, None], qi[None, :]] = (acc[:, :, oi[:, None], qi[None, :]] + vals).astype(F32)
+    return from_accum((acc / F32(kh * kw)).astype(F32), dtype)
+
+
+def gather(x, indices):
+    """out[k, :] = x[indices[k], :] along axis 0 (src/ops/schemas/gather.cpp:86-118); an index
+    outside [0, N) is an error."""
+    idx = np.asarray(indices).astype(np.int64)
+    if idx.size and (idx.min() < 0 or idx.max() >= x.shape[0]):
+        raise IndexError(f"gather: index out of range [0, {x.shape[0]})")
+    return np.ascontiguousarray(np.asarray(x)[idx])
+
+
+def scatter_add(updates, indices, output_shape, dtype: int = DT_F32):
+    """out [V, F] = 0; out[indices[k], :] += updates[k, :] in increasing k, accumulated in fp32 and
+    rounded once (scatter_add / gather_grad_internal of src/backends/cpu/kernels/gather.cpp)."""
+    idx = np.asarray(indices).astype(np.int64)
+    v, f = output_shape
+    if idx.size and (idx.min() < 0 or idx.max() >= v):
+        raise IndexError(f"scatter_add: index out of range [0, {v})")
+    acc = np.zeros((v, f), dtype=F32)
+    u = to_accum(updates, dtype)
+    for k in range(idx.shape[0]):
+        acc[idx[k]] = (acc[idx[k]] + u[k]).astype(F32)
+    return from_accum(acc, dtype)
+
+
+def heaviside_surrogate(x, dtype: int = DT_F32):
+    """Forward of the surrogate step: x >= 0 ? 1 : 0 (alpha only shapes the backward graph)."""
+    return _unary(lambda v: np.where(v >= 0, F32(1), F32(0)).astype(F32), x, dtype)
+
+
 # --------------------------------------------------------------------------------------
 # elementwise.  src/backends/cpu/kernels/elementwise.cpp:39-56,146-163,242-255,329-404
 # --------------------------------------------------------------------------------------

@@ -33,6 +33,7 @@ class Case:
     oracle: Callable[..., np.ndarray] = None
     exact: bool = False       # integer/indexing work or fp32 without libm: bit-exact expected
     new_op: bool = False      # not in the reference (parity unpinned by the reference)
+    in_dtypes: List[int] = None   # dtype code per input when they differ from `dtype` (indices)
 
     def expected(self) -> np.ndarray:
         return self.oracle(*self.inputs)
@@ -40,11 +41,13 @@ class Case:
     def ir_text(self, backend: str = "cpu") -> str:
         g = irtext.IrGraph(backend)
         dt = irtext.DTYPE_NAMES[self.dtype]
-        vals = [g.input(dt, a.shape) for a in self.inputs]
+        in_dts = self.in_dtypes or [self.dtype] * len(self.inputs)
+        vals = [g.input(irtext.DTYPE_NAMES[d], a.shape) for d, a in zip(in_dts, self.inputs)]
         out_shape = self.expected().shape
         attrs = dict(self.attrs)
-        if "target_shape" in attrs:
-            attrs["target_shape"] = irtext.Shape(tuple(attrs["target_shape"]))
+        for key in ("target_shape", "output_shape", "input_shape"):
+            if key in attrs:
+                attrs[key] = irtext.Shape(tuple(attrs[key]))
         out = g.node(self.op, vals, attrs, dt, out_shape)
         g.output(out)
         return g.text()
@@ -198,6 +201,39 @@ def build_cases() -> List[Case]:
                               lambda a, op=op, dt=dt: fo.UNARY[op](a, dt), new_op=True))
         cases.append(Case(f"bias_add_{tag}", "bias_add", dt, [rnd((9, 40), dt), rnd((40,), dt)], {},
                           lambda x, b, dt=dt: fo.bias_add(x, b, dt), exact=True, new_op=True))
+    # ---- ops added after the first golden set (kept last so that earlier seeded draws do not move) --
+    cases.append(Case("avg_pool2d_f32_k3_s2_p1", "avg_pool2d", F32, [rnd((2, 3, 9, 11))],
+                      {"kernel": [3, 3], "stride": [2, 2], "padding": [1, 1]},
+                      lambda x: fo.avg_pool2d(x, (3, 3), (2, 2), (1, 1), F32), exact=True))
+    cases.append(Case("avg_pool2d_f32_k2_s2", "avg_pool2d", F32, [rnd((1, 4, 8, 6))],
+                      {"kernel": [2, 2], "stride": [2, 2], "padding": [0, 0]},
+                      lambda x: fo.avg_pool2d(x, (2, 2), (2, 2), (0, 0), F32), exact=True))
+    cases.append(Case("avg_pool2d_bf16_k3_s1_p1", "avg_pool2d", BF16, [rnd((1, 2, 7, 7), BF16)],
+                      {"kernel": [3, 3], "stride": [1, 1], "padding": [1, 1]},
+                      lambda x: fo.avg_pool2d(x, (3, 3), (1, 1), (1, 1), BF16), exact=True))
+    cases.append(Case("heaviside_f32_1023", "heaviside_surrogate", F32,
+                      [np.concatenate([rnd((1021,)), np.array([0.0, -0.0], np.float32)])], {"alpha": 2.0},
+                      lambda x: fo.heaviside_surrogate(x, F32), exact=True))
+    cases.append(Case("heaviside_bf16_40x9", "heaviside_surrogate", BF16, [rnd((40, 9), BF16)], {"alpha": 1.0},
+                      lambda x: fo.heaviside_surrogate(x, BF16), exact=True))
+
+    # ---- gather / scatter_add (indices int32 or int64, repeated indices accumulate) -----------------
+    idx_a = _rng(41).integers(0, 13, size=(29,))
+    for tag, idt, npdt in (("i32", I32, np.int32), ("i64", I64, np.int64)):
+        cases.append(Case(f"gather_f32_13x20_{tag}", "gather", F32, [rnd((13, 20)), idx_a.astype(npdt)], {},
+                          lambda x, i: fo.gather(x, i), exact=True, in_dtypes=[F32, idt]))
+        cases.append(Case(f"scatter_add_f32_29x20_{tag}", "scatter_add", F32, [rnd((29, 20)), idx_a.astype(npdt)],
+                          {"output_shape": [13, 20]},
+                          lambda u, i: fo.scatter_add(u, i, (13, 20), F32), in_dtypes=[F32, idt]))
+    cases.append(Case("gather_bf16_13x7_i64", "gather", BF16, [rnd((13, 7), BF16), idx_a.astype(np.int64)], {},
+                      lambda x, i: fo.gather(x, i), exact=True, in_dtypes=[BF16, I64]))
+    cases.append(Case("scatter_add_bf16_29x8_i32", "scatter_add", BF16, [rnd((29, 8), BF16), idx_a.astype(np.int32)],
+                      {"output_shape": [13, 8]},
+                      lambda u, i: fo.scatter_add(u, i, (13, 8), BF16), in_dtypes=[BF16, I32]))
+    cases.append(Case("gather_grad_f32_29x5_i64", "gather_grad_internal", F32, [rnd((29, 5)), idx_a.astype(np.int64)],
+                      {"input_shape": [13, 5]},
+                      lambda u, i: fo.scatter_add(u, i, (13, 5), F32), in_dtypes=[F32, I64]))
+
     return cases
 
 

@@ -47,6 +47,18 @@ def run_case(case, allow_tf32=False):
         x = ins[0]
         capi.max_pool2d(ptr[0], out.ptr, *x.shape, at["kernel"][0], at["kernel"][1], at["stride"][0],
                         at["stride"][1], at["padding"][0], at["padding"][1], dt)
+    elif op == "avg_pool2d":
+        x = ins[0]
+        capi.avg_pool2d(ptr[0], out.ptr, *x.shape, at["kernel"][0], at["kernel"][1], at["stride"][0],
+                        at["stride"][1], at["padding"][0], at["padding"][1], dt)
+    elif op == "heaviside_surrogate":
+        capi.fused_elementwise(ptr, out.ptr, numel, dt, [op])
+    elif op == "gather":
+        capi.gather(ptr[0], ptr[1], out.ptr, ins[0].shape[0], ins[0].shape[1], ins[1].shape[0], dt,
+                    capi.I32 if ins[1].dtype == np.int32 else capi.I64)
+    elif op in ("scatter_add", "gather_grad_internal"):
+        capi.scatter_add(ptr[0], ptr[1], out.ptr, ins[0].shape[0], ins[0].shape[1], exp_shape[0], dt,
+                         capi.I32 if ins[1].dtype == np.int32 else capi.I64)
     elif op == "transpose":
         capi.transpose(ptr[0], out.ptr, ins[0].shape, at["perm"], capi.ITEMSIZE[dt])
     elif op == "slice":

@@ -73,3 +73,22 @@ def test_reference_nn_module_runs_on_cuda_without_fallback(spec):
     assert fo.all_close(got, exp, dtype, **tol), (name, fo.max_err(got, exp, dtype))
     for op in OPS + ["sigmoid", "tanh", "constant"]:
         assert ref_runtime.fallback_count(op, "cuda") == 0, f"op {op} fell back to the eager chain"
+
+
+NEW_OP_CASES = [c for c in __import__("cases").CASES
+                if c.op in ("avg_pool2d", "heaviside_surrogate", "gather", "scatter_add", "gather_grad_internal")]
+
+
+@pytest.mark.parametrize("case", NEW_OP_CASES, ids=lambda c: c.name)
+def test_pool_step_and_index_ops_through_the_reference_api(case):
+    """avg_pool2d, heaviside_surrogate, gather, scatter_add and gather_grad_internal compiled by the
+    reference's runtime::compile for backend "cuda": no fallback, same numbers as its CPU backend."""
+    cpu = ref_runtime.Compiled(case.ir_text("cpu"), "cpu")
+    (exp,) = cpu.run(case.inputs)
+    gpu = ref_runtime.Compiled(case.ir_text("cuda"), "cuda")
+    (got,) = gpu.run(case.inputs)
+    if case.exact:
+        assert np.array_equal(np.asarray(got).view(np.uint8), np.asarray(exp).view(np.uint8)), case.name
+    else:
+        assert fo.all_close(got, exp, case.dtype), (case.name, fo.max_err(got, exp, case.dtype))
+    assert ref_runtime.fallback_count(case.op, "cuda") == 0

@@ -89,3 +89,15 @@ def test_hal_allocator_and_copies_round_trip():
     capi.check(lib.fb200_stream_synchronize(0, st))
     capi.check(lib.fb200_event_destroy(0, ev))
     capi.check(lib.fb200_stream_destroy(0, st))
+
+
+def test_gather_names_an_out_of_range_index():
+    lib = capi.load()
+    x = capi.DeviceBuffer.from_numpy(np.zeros((5, 4), np.float32))
+    out = capi.DeviceBuffer(3 * 4 * 4)
+    for bad, npdt, code in ((7, np.int32, capi.I32), (-2, np.int64, capi.I64)):
+        idx = capi.DeviceBuffer.from_numpy(np.array([0, bad, 4], dtype=npdt))
+        rc = lib.fb200_gather(x.ptr, idx.ptr, out.ptr, 5, 4, 3, capi.F32, code, None)
+        assert rc == 1 and f"index {bad} is out of range [0, 5)".encode() in lib.fb200_last_error()
+        rc = lib.fb200_scatter_add(out.ptr, idx.ptr, x.ptr, 3, 4, 5, capi.F32, code, None)
+        assert rc == 1 and f"index {bad} is out of range".encode() in lib.fb200_last_error()

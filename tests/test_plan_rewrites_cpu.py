@@ -78,3 +78,16 @@ def test_unknown_op_is_unimplemented_with_its_name_without_a_gpu():
     h = capi.c_void_p()
     rc = lib.fb200_plan_describe(text.encode(), 1, capi.byref(h))
     assert rc == 4 and b"frobnicate" in lib.fb200_last_error()
+
+
+def test_pool_and_index_ops_decode_and_opt_out_of_graph_replay_checks():
+    text = ("plan slots=4 arena=1024\nin 0 0 2 5 4\nin 1 6 1 3\n"
+            "step gather nin=2 0 1 nout=1 2 0 0 2 3 4 attrs=0\n"
+            "step heaviside_surrogate nin=1 2 nout=1 3 0 -1 2 3 4 attrs=1\nattr alpha double 2.0\nout 3\n")
+    names, launches = runtime.describe_plan(text)
+    assert names == ["gather", "heaviside_surrogate"] and launches == 2
+    bad = text.replace("attr alpha double 2.0", "attr alpha double -1.0")
+    lib = capi.load()
+    h = capi.c_void_p()
+    rc = lib.fb200_plan_describe(bad.encode(), 1, capi.byref(h))
+    assert rc == 1 and b"alpha" in lib.fb200_last_error()
