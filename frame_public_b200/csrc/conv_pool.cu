@@ -232,6 +232,65 @@ max_pool2d_window_kernel(const T* __restrict__ x, T* __restrict__ out, int nc, i
   }
 }
 
+// 3x3 window, stride 2, padding 1 on rows whose length is a multiple of 4 (the stem pool of a ResNet):
+// a thread produces four neighbouring outputs of one row.  They need input columns 2*ow-1 .. 2*ow+7 of
+// three rows: two aligned 128-bit loads and one scalar per row, nine loads for four outputs where the
+// one-output kernel issues thirty-six, and consecutive threads read consecutive 32-byte spans.
+// Selection order (kh, then kw, strict >, first valid tap seeds) and result are unchanged.
+template <typename T>
+__global__ void __launch_bounds__(256)
+max_pool2d_k3s2p1_quad_kernel(const T* __restrict__ x, T* __restrict__ out, int nc, int h, int w, int oh,
+                              int ow) {
+  static_assert(sizeof(T) == 4, "32-bit elements");
+  const int quads = ow / 4;
+  const int total = nc * oh * quads;
+  const int stride = static_cast<int>(gridDim.x) * blockDim.x;
+  for (int i = static_cast<int>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int qd = i % quads;
+    int rem = i / quads;
+    const int o = rem % oh;
+    rem /= oh;
+    const T* xc = x + static_cast<int64_t>(rem) * h * w;
+    const int c0 = qd * 8;   // first input column covered by the aligned loads (= 2 * first ow)
+    T tap[3][9];             // columns c0-1 .. c0+7
+    bool row_ok[3];
+#pragma unroll
+    for (int a = 0; a < 3; ++a) {
+      const int ih = o * 2 - 1 + a;
+      row_ok[a] = ih >= 0 && ih < h;
+      const int ihc = ih < 0 ? 0 : (ih >= h ? h - 1 : ih);
+      const T* row = xc + static_cast<int64_t>(ihc) * w;
+      const float4 lo = *reinterpret_cast<const float4*>(row + c0);
+      const float4 hi = *reinterpret_cast<const float4*>(row + c0 + 4);
+      tap[a][0] = row[c0 > 0 ? c0 - 1 : 0];
+      tap[a][1] = lo.x; tap[a][2] = lo.y; tap[a][3] = lo.z; tap[a][4] = lo.w;
+      tap[a][5] = hi.x; tap[a][6] = hi.y; tap[a][7] = hi.z; tap[a][8] = hi.w;
+    }
+    float4 res;
+    float* resv = reinterpret_cast<float*>(&res);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      bool found = false;
+      float best = 0.0f;
+#pragma unroll
+      for (int a = 0; a < 3; ++a) {
+#pragma unroll
+        for (int b = 0; b < 3; ++b) {
+          const int col = c0 + 2 * j - 1 + b;          // input column of this tap
+          const bool ok = row_ok[a] && col >= 0 && col < w;
+          const float v = tap[a][2 * j + b];
+          if (ok && (!found || v > best)) {
+            found = true;
+            best = v;
+          }
+        }
+      }
+      resv[j] = best;
+    }
+    *reinterpret_cast<float4*>(out + (static_cast<int64_t>(rem) * oh + o) * ow + qd * 4) = res;
+  }
+}
+
 }  // namespace fb200
 
 using namespace fb200;
@@ -403,7 +462,15 @@ extern "C" int fb200_max_pool2d(const void* x, void* out, int64_t n, int64_t c, 
   const bool small = n * c * h * w < (int64_t(1) << 31);
   auto run = [&](auto tag) {
     using T = decltype(tag);
-    if (small && ((kh == 3 && kw == 3) || (kh == 2 && kw == 2))) {
+    if (small && sizeof(T) == 4 && kh == 3 && kw == 3 && stride_h == 2 && stride_w == 2 && pad_h == 1 &&
+        pad_w == 1 && w % 4 == 0 && ow % 4 == 0 && ow * 2 == w && aligned16(x) && aligned16(out)) {
+      if constexpr (sizeof(T) == 4) {
+        const int qgrid = grid_for(n * c * oh * (ow / 4), 256, 8);
+        max_pool2d_k3s2p1_quad_kernel<T><<<qgrid, 256, 0, s>>>(
+            static_cast<const T*>(x), static_cast<T*>(out), static_cast<int>(n * c), static_cast<int>(h),
+            static_cast<int>(w), static_cast<int>(oh), static_cast<int>(ow));
+      }
+    } else if (small && ((kh == 3 && kw == 3) || (kh == 2 && kw == 2))) {
       const T* xp = static_cast<const T*>(x);
       T* op = static_cast<T*>(out);
       const int a[9] = {static_cast<int>(n * c), static_cast<int>(h), static_cast<int>(w),

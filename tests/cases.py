@@ -234,6 +234,9 @@ def build_cases() -> List[Case]:
                       {"input_shape": [13, 5]},
                       lambda u, i: fo.scatter_add(u, i, (13, 5), F32), in_dtypes=[F32, I64]))
 
+    cases.append(Case("max_pool2d_f32_k3_s2_p1_w16", "max_pool2d", F32, [rnd((2, 3, 10, 16))],
+                      {"kernel": [3, 3], "stride": [2, 2], "padding": [1, 1]},
+                      lambda x: fo.max_pool2d(x, (3, 3), (2, 2), (1, 1), F32), exact=True))
     return cases
 
 
