@@ -119,6 +119,8 @@ SIGNATURES = {
     "fb200_plan_run_host": (c_int, [_P, _PP, _PP, _P]),
     "fb200_plan_profile": (c_int, [_P, _PP, _PP, _P, POINTER(c_float), c_int, _IP]),
     "fb200_plan_step_op": (c_char_p, [_P, c_int]),
+    "fb200_plan_run_host_async": (c_int, [_P, _PP, _PP, _P]),
+    "fb200_plan_host_sync": (c_int, [_P]),
     "fb200_plan_describe": (c_int, [c_char_p, c_int, _PP]),
 }
 

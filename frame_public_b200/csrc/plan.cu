@@ -97,10 +97,21 @@ struct fb200_plan {
   // is eager (it also performs every lazy initialisation), the second captures the launches into
   // a graph, later runs with the same pointers replay it with one cudaGraphLaunch.
   bool graph_enabled = true;
-  int runs_with_key = 0;
-  std::vector<const void*> graph_key;
-  cudaGraph_t graph = nullptr;
-  cudaGraphExec_t graph_exec = nullptr;
+  struct GraphEntry {
+    std::vector<const void*> key;   // input pointers, output pointers, stream
+    int runs = 0;
+    uint64_t last_used = 0;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+  };
+  std::vector<GraphEntry> graphs;   // a few pointer sets (the pipelined host path alternates two)
+  uint64_t graph_clock = 0;
+  // pipelined host runs: two sets of staging buffers, a copy-in and a copy-out stream, and events
+  // that order H2D(k) -> run(k) -> D2H(k) and keep a staging set from being reused too early
+  std::vector<void*> stage_in2, stage_out2;
+  cudaStream_t s_h2d = nullptr, s_d2h = nullptr;
+  cudaEvent_t ev_in[2] = {nullptr, nullptr}, ev_run[2] = {nullptr, nullptr}, ev_out[2] = {nullptr, nullptr};
+  uint64_t host_runs = 0;
 };
 
 namespace fb200 {
@@ -1258,8 +1269,19 @@ extern "C" int fb200_plan_describe(const char* plan_text, int opt_level, fb200_p
 
 extern "C" int fb200_plan_destroy(fb200_plan* p) {
   if (p == nullptr) return FB200_OK;
-  if (p->graph_exec) cudaGraphExecDestroy(p->graph_exec);
-  if (p->graph) cudaGraphDestroy(p->graph);
+  for (auto& e : p->graphs) {
+    if (e.exec) cudaGraphExecDestroy(e.exec);
+    if (e.graph) cudaGraphDestroy(e.graph);
+  }
+  for (int b = 0; b < 2; ++b) {
+    if (p->ev_in[b]) cudaEventDestroy(p->ev_in[b]);
+    if (p->ev_run[b]) cudaEventDestroy(p->ev_run[b]);
+    if (p->ev_out[b]) cudaEventDestroy(p->ev_out[b]);
+  }
+  if (p->s_h2d) cudaStreamDestroy(p->s_h2d);
+  if (p->s_d2h) cudaStreamDestroy(p->s_d2h);
+  for (void* q : p->stage_in2) fb200_free(p->device, q);
+  for (void* q : p->stage_out2) fb200_free(p->device, q);
   if (p->arena) fb200_free(p->device, p->arena);
   for (void* q : p->owned) fb200_free(p->device, q);
   for (void* q : p->stage_in) fb200_free(p->device, q);
@@ -1316,32 +1338,42 @@ extern "C" int fb200_plan_run(fb200_plan* p, const void* const* inputs, void* co
     for (size_t i = 0; i < p->input_slots.size(); ++i) key.push_back(inputs[i]);
     for (size_t i = 0; i < p->output_slots.size(); ++i) key.push_back(outputs[i]);
     key.push_back(stream);
-    if (key != p->graph_key) {
-      if (p->graph_exec) { cudaGraphExecDestroy(p->graph_exec); p->graph_exec = nullptr; }
-      if (p->graph) { cudaGraphDestroy(p->graph); p->graph = nullptr; }
-      p->graph_key = key;
-      p->runs_with_key = 0;
+    fb200_plan::GraphEntry* ge = nullptr;
+    for (auto& e : p->graphs) if (e.key == key) ge = &e;
+    if (ge == nullptr) {
+      if (p->graphs.size() < 4) {
+        p->graphs.emplace_back();
+        ge = &p->graphs.back();
+      } else {   // replace the entry used longest ago
+        ge = &p->graphs[0];
+        for (auto& e : p->graphs) if (e.last_used < ge->last_used) ge = &e;
+        if (ge->exec) cudaGraphExecDestroy(ge->exec);
+        if (ge->graph) cudaGraphDestroy(ge->graph);
+        *ge = fb200_plan::GraphEntry();
+      }
+      ge->key = key;
     }
-    if (p->graph_exec != nullptr) {
-      FB200_CUDA_OK(cudaGraphLaunch(p->graph_exec, as_stream(stream)));
+    ge->last_used = ++p->graph_clock;
+    if (ge->exec != nullptr) {
+      FB200_CUDA_OK(cudaGraphLaunch(ge->exec, as_stream(stream)));
       g_launch_count.fetch_add(p->launches, std::memory_order_relaxed);
       done = true;
-    } else if (p->runs_with_key >= 1) {
+    } else if (ge->runs >= 1) {
       const int64_t count_before = g_launch_count.load(std::memory_order_relaxed);
       if (cudaStreamBeginCapture(as_stream(stream), cudaStreamCaptureModeRelaxed) == cudaSuccess) {
         const int rc = run_eager();
         cudaGraph_t captured = nullptr;
         const cudaError_t end = cudaStreamEndCapture(as_stream(stream), &captured);
         if (rc == FB200_OK && end == cudaSuccess && captured != nullptr &&
-            cudaGraphInstantiate(&p->graph_exec, captured, 0) == cudaSuccess) {
-          p->graph = captured;
+            cudaGraphInstantiate(&ge->exec, captured, 0) == cudaSuccess) {
+          ge->graph = captured;
           g_launch_count.store(count_before, std::memory_order_relaxed);  // capture launched nothing
-          FB200_CUDA_OK(cudaGraphLaunch(p->graph_exec, as_stream(stream)));
+          FB200_CUDA_OK(cudaGraphLaunch(ge->exec, as_stream(stream)));
           g_launch_count.fetch_add(p->launches, std::memory_order_relaxed);
           done = true;
         } else {
           if (captured) cudaGraphDestroy(captured);
-          p->graph_exec = nullptr;
+          ge->exec = nullptr;
           p->graph_enabled = false;  // this plan stays on eager launches
           (void)cudaGetLastError();
           g_launch_count.store(count_before, std::memory_order_relaxed);
@@ -1352,7 +1384,7 @@ extern "C" int fb200_plan_run(fb200_plan* p, const void* const* inputs, void* co
         p->graph_enabled = false;
       }
     }
-    ++p->runs_with_key;
+    ++ge->runs;
   }
   if (!done) {
     if (int rc = run_eager()) return rc;
@@ -1434,6 +1466,80 @@ extern "C" int fb200_plan_profile(fb200_plan* p, const void* const* inputs, void
   }
   for (auto& e : ev) cudaEventDestroy(e);
   return rc;
+}
+
+// Pipelined variant of fb200_plan_run_host: the call returns once its work is queued.  Run k copies
+// its inputs on a copy-in stream, runs on `stream`, and copies its outputs on a copy-out stream, so
+// H2D(k+1), run(k) and D2H(k-1) overlap; two sets of staging buffers alternate.  The host input
+// buffers of run k may be rewritten, and its host outputs read, after fb200_plan_host_sync (or once
+// two further runs have been queued, which wait for the staging set to drain).  Pinned host memory
+// makes the copies asynchronous; pageable memory still works but serialises.
+extern "C" int fb200_plan_run_host_async(fb200_plan* p, const void* const* host_inputs,
+                                         void* const* host_outputs, fb200_stream stream) {
+  if (p == nullptr) return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_run_host_async: null plan");
+  if (p->dry) return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_run_host_async: this plan was made by fb200_plan_describe and cannot run");
+  FB200_CUDA_OK(cudaSetDevice(p->device));
+  int b = 0;
+  uint64_t k = 0;
+  {
+    std::lock_guard<std::mutex> lock(p->mu);
+    if (p->s_h2d == nullptr) {
+      FB200_CUDA_OK(cudaStreamCreateWithFlags(&p->s_h2d, cudaStreamNonBlocking));
+      FB200_CUDA_OK(cudaStreamCreateWithFlags(&p->s_d2h, cudaStreamNonBlocking));
+      for (int i = 0; i < 2; ++i) {
+        FB200_CUDA_OK(cudaEventCreateWithFlags(&p->ev_in[i], cudaEventDisableTiming));
+        FB200_CUDA_OK(cudaEventCreateWithFlags(&p->ev_run[i], cudaEventDisableTiming));
+        FB200_CUDA_OK(cudaEventCreateWithFlags(&p->ev_out[i], cudaEventDisableTiming));
+      }
+      auto fill = [&](std::vector<void*>& v, const std::vector<int>& slots) -> int {
+        for (int slot : slots) {
+          void* d = nullptr;
+          if (p->slots[slot].bytes() > 0) { if (int rc = fb200_malloc(p->device, p->slots[slot].bytes(), 256, &d)) return rc; }
+          v.push_back(d);
+        }
+        return FB200_OK;
+      };
+      if (p->stage_in.empty() && p->stage_out.empty()) {
+        if (int rc = fill(p->stage_in, p->input_slots)) return rc;
+        if (int rc = fill(p->stage_out, p->output_slots)) return rc;
+      }
+      if (int rc = fill(p->stage_in2, p->input_slots)) return rc;
+      if (int rc = fill(p->stage_out2, p->output_slots)) return rc;
+    }
+    k = p->host_runs++;
+    b = static_cast<int>(k & 1);
+  }
+  std::vector<void*>& in = b == 0 ? p->stage_in : p->stage_in2;
+  std::vector<void*>& out = b == 0 ? p->stage_out : p->stage_out2;
+  cudaStream_t cs = as_stream(stream);
+  // the staging inputs of this set were last read by run k-2
+  if (k >= 2) FB200_CUDA_OK(cudaStreamWaitEvent(p->s_h2d, p->ev_run[b], 0));
+  for (size_t i = 0; i < p->input_slots.size(); ++i) {
+    const size_t bytes = p->slots[p->input_slots[i]].bytes();
+    if (bytes > 0) FB200_CUDA_OK(cudaMemcpyAsync(in[i], host_inputs[i], bytes, cudaMemcpyHostToDevice, p->s_h2d));
+  }
+  FB200_CUDA_OK(cudaEventRecord(p->ev_in[b], p->s_h2d));
+  FB200_CUDA_OK(cudaStreamWaitEvent(cs, p->ev_in[b], 0));
+  // the staging outputs of this set were last copied out by run k-2
+  if (k >= 2) FB200_CUDA_OK(cudaStreamWaitEvent(cs, p->ev_out[b], 0));
+  if (int rc = fb200_plan_run(p, in.data(), out.data(), stream)) return rc;
+  FB200_CUDA_OK(cudaEventRecord(p->ev_run[b], cs));
+  FB200_CUDA_OK(cudaStreamWaitEvent(p->s_d2h, p->ev_run[b], 0));
+  for (size_t i = 0; i < p->output_slots.size(); ++i) {
+    const size_t bytes = p->slots[p->output_slots[i]].bytes();
+    if (bytes > 0) FB200_CUDA_OK(cudaMemcpyAsync(host_outputs[i], out[i], bytes, cudaMemcpyDeviceToHost, p->s_d2h));
+  }
+  FB200_CUDA_OK(cudaEventRecord(p->ev_out[b], p->s_d2h));
+  return FB200_OK;
+}
+
+// Waits until every pipelined run queued so far has delivered its outputs to the host.
+extern "C" int fb200_plan_host_sync(fb200_plan* p) {
+  if (p == nullptr) return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_host_sync: null plan");
+  if (p->s_d2h == nullptr) return FB200_OK;
+  FB200_CUDA_OK(cudaSetDevice(p->device));
+  FB200_CUDA_OK(cudaStreamSynchronize(p->s_d2h));
+  return FB200_OK;
 }
 
 // Op name of step `index`; a contraction that absorbed a following group reports

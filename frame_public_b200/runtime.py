@@ -72,6 +72,16 @@ class CompiledPlan:
         b = (c_void_p * max(1, len(out_ptrs)))(*out_ptrs)
         capi.check(self.lib.fb200_plan_run_host(self._h, a, b, stream))
 
+    def run_host_async_ptrs(self, in_ptrs: Sequence[int], out_ptrs: Sequence[int], stream=None) -> None:
+        """Queues one pipelined run (copy-in, run, copy-out on three streams, two staging sets); the
+        host outputs are valid after host_sync()."""
+        a = (c_void_p * max(1, len(in_ptrs)))(*in_ptrs)
+        b = (c_void_p * max(1, len(out_ptrs)))(*out_ptrs)
+        capi.check(self.lib.fb200_plan_run_host_async(self._h, a, b, stream))
+
+    def host_sync(self) -> None:
+        capi.check(self.lib.fb200_plan_host_sync(self._h))
+
     def run_host(self, arrays: Sequence[np.ndarray], stream=None) -> List[np.ndarray]:
         ins = [np.ascontiguousarray(a) for a in arrays]
         assert len(ins) == len(self.inputs)

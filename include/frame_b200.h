@@ -360,6 +360,15 @@ FB200_API int fb200_plan_run(fb200_plan* plan, const void* const* inputs, void* 
  * synchronise.  Staging buffers on the device are owned by the plan. */
 FB200_API int fb200_plan_run_host(fb200_plan* plan, const void* const* host_inputs,
                                   void* const* host_outputs, fb200_stream stream);
+/* The same, pipelined: returns when the work of this run is queued.  Inputs are copied on a copy-in
+ * stream, the plan runs on `stream` (must not be NULL), outputs are copied on a copy-out stream; two
+ * staging sets alternate, so H2D of run k+1, run k and D2H of run k-1 overlap.  Host outputs of a run
+ * are valid after fb200_plan_host_sync; its host inputs must stay unchanged until then.  Use pinned
+ * host memory (fb200_host_alloc).  No counterpart in the reference, whose Executable::run takes device
+ * tensors and leaves the copies to the caller (include/frame/hal/executable.h:33). */
+FB200_API int fb200_plan_run_host_async(fb200_plan* plan, const void* const* host_inputs,
+                                        void* const* host_outputs, fb200_stream stream);
+FB200_API int fb200_plan_host_sync(fb200_plan* plan);
 
 /* Per-step device times (ms) of one eager run, measured with CUDA events on `stream`; steps that
  * launch nothing report 0.  For harness-side accounting of which kernel dominates a graph; has no

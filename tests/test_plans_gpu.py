@@ -105,3 +105,28 @@ def test_mamba_conv_group_becomes_one_time_major_launch():
     (b,) = plain.run_host(wl.inputs)
     assert capi.kernel_status(0) == 0
     assert fo.all_close(a, b, wl.dtype, rtol=1e-5, atol=1e-6), fo.max_err(a, b, wl.dtype)
+
+
+def test_pipelined_host_runs_deliver_each_runs_own_result():
+    """fb200_plan_run_host_async: three runs in flight over two staging sets, each with its own host
+    buffers, must give what the synchronous entry point gives for the same inputs."""
+    wl = WORKLOADS[0]
+    plan = runtime.CompiledPlan(_plan_text(wl.name), 0)
+    rng = np.random.default_rng(9)
+    variants = []
+    for _ in range(3):
+        ins = [np.ascontiguousarray(a.copy()) for a in wl.inputs]
+        ins[0] = rng.standard_normal(ins[0].shape).astype(ins[0].dtype)
+        variants.append(ins)
+    expected = [plan.run_host(ins)[0] for ins in variants]
+    stream = capi.c_void_p()
+    capi.check(capi.load().fb200_stream_create(0, capi.byref(stream)))
+    for round_ in range(2):   # the second round replays the captured graphs of both staging sets
+        outs = [np.zeros_like(expected[0]) for _ in variants]
+        for ins, out in zip(variants, outs):
+            plan.run_host_async_ptrs([a.ctypes.data for a in ins], [out.ctypes.data], stream)
+        plan.host_sync()
+        assert capi.kernel_status(0) == 0
+        for got, exp in zip(outs, expected):
+            assert np.array_equal(got.view(np.uint8), exp.view(np.uint8)), round_
+    plan.close()
