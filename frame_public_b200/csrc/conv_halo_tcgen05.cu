@@ -77,6 +77,7 @@ struct HaloGeom {
   int kcb, kblocks;      // k extent of one channel block, its 32-wide blocks
   int npad, tmem_cols, acc_per_round, stages;
   int halo_bytes, w_bytes, n_halo;
+  int out_stage_bytes;   // > 0: results leave through a shared-memory tile and a TMA store
 };
 
 // Flat walk over (round, channel block, tile) shared by all roles.
@@ -100,7 +101,8 @@ __device__ __forceinline__ HaloItem halo_decode(int idx, int my_tiles, int apr, 
 }
 
 __global__ void __launch_bounds__(kHaloThreads, 1)
-conv2d_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const float* __restrict__ w,
+conv2d_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                           const __grid_constant__ CUtensorMap tmap_out, const float* __restrict__ w,
                            const float* __restrict__ bias, float* __restrict__ out, HaloGeom g,
                            uint32_t idesc, EpilogueDev epi, int* status) {
   extern __shared__ uint8_t smem_raw[];
@@ -124,6 +126,9 @@ conv2d_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const flo
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + slot_off);
   float* bias_s = reinterpret_cast<float*>(base_ptr + slot_off + 16);          // [256]
   int* ktab = reinterpret_cast<int*>(base_ptr + slot_off + 16 + 1024);
+  // staging tile of the TMA store: [cout][rows][ow] floats, 128-byte aligned, after the k-table
+  const uint32_t ostage_off = (slot_off + 16 + 1024 + static_cast<uint32_t>(g.kblocks) * kHaloBlockK * 4 + 127u) & ~127u;
+  float* ostage = reinterpret_cast<float*>(base_ptr + ostage_off);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -365,6 +370,8 @@ conv2d_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const flo
     const int pr = pix_ok ? m / g.ow : 0;
     const int px = pix_ok ? m - pr * g.ow : 0;
     const int64_t ohow = static_cast<int64_t>(g.oh) * g.ow;
+    const bool use_tma_store = g.out_stage_bytes > 0;
+    const int tile_px = g.rows * g.ow;
     bool ok = true;
     for (int ti = 0; ti < my_tiles && ok; ++ti) {
       const int acc = ti % apr, round = ti / apr;
@@ -418,17 +425,38 @@ conv2d_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x, const flo
               ew_unary_vec<float, 32>(op, v);
             }
           }
-          float* dst = out + obase;
+          if (use_tma_store) {
+            float* dst = ostage + static_cast<size_t>(c0) * tile_px + m;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (j < nch) dst[j * ohow] = v[j];
+            for (int j = 0; j < 32; ++j) {
+              if (j < nch) dst[j * tile_px] = v[j];
+            }
+          } else {
+            float* dst = out + obase;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (j < nch) dst[j * ohow] = v[j];
+            }
           }
         }
       }
       tcgen05_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty(acc));
+      if (use_tma_store) {
+        // the tile is complete in shared memory: one thread hands it to the TMA, which writes the
+        // cout x rows runs of ow floats (rows past the image are clipped by the tensor map)
+        fence_proxy_async_smem();
+        asm volatile("bar.sync 2, 128;" ::: "memory");   // the four epilogue warps
+        if (warp == kHaloMmaWarp + 1 && lane == 0) {
+          tma_store_4d(&tmap_out, base + ostage_off, 0, oy0, 0, img);
+          tma_store_commit();
+          tma_store_wait_read<0>();   // the staging tile may be overwritten by the next tile
+        }
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+      }
     }
+    if (use_tma_store && warp == kHaloMmaWarp + 1 && lane == 0) tma_store_wait_all();
   }
 
   tcgen05_fence_before_sync();
@@ -488,24 +516,38 @@ extern "C" int fb200_conv2d_halo_tcgen05(const void* x, const void* w, const voi
                         static_cast<int64_t>(g.kblocks) * kHaloBlockK * 4;
   g.stages = 2;
   const int64_t room = 227 * 1024 - fixed - static_cast<int64_t>(g.stages) * kHaloStageBytes;
-  g.n_halo = static_cast<int>(room / g.halo_bytes);
+  // results through a shared-memory tile and one TMA store per tile when there is room for the tile
+  // next to two halo buffers (scattered per-channel warp stores were the longest part of the
+  // epilogue); needs 16-byte aligned rows
+  int64_t room_left = room;
+  g.out_stage_bytes = 0;
+  const int64_t stage_need = (static_cast<int64_t>(g.cout) * g.rows * g.ow * 4 + 127) / 128 * 128 + 128;
+  if (g.ow % 4 == 0 && aligned16(out) && room - stage_need >= 2 * static_cast<int64_t>(g.halo_bytes)) {
+    g.out_stage_bytes = static_cast<int>(stage_need);
+    room_left = room - stage_need;
+  }
+  g.n_halo = static_cast<int>(room_left / g.halo_bytes);
   if (g.n_halo > kHaloMaxBufs) g.n_halo = kHaloMaxBufs;
   if (g.n_halo < 2) return FB200_UNIMPLEMENTED;
   EpilogueDev epi{};
   if (int rc = make_epilogue(epilogue, &epi, "conv2d")) return rc;
   CUtensorMap tx;
   if (int rc = make_tmap_nchw_f32(&tx, x, g.n, g.cin, g.h, g.w, g.cb, g.ih_t, g.iwp)) return rc;
+  CUtensorMap tout = tx;   // placeholder when the direct-store epilogue is used
+  if (g.out_stage_bytes > 0) {
+    if (int rc = make_tmap_nchw_f32(&tout, out, g.n, g.cout, g.oh, g.ow, g.cout, g.rows, g.ow)) return rc;
+  }
   int* status = nullptr;
   if (int rc = device_status_word(&status)) return rc;
   const size_t smem = static_cast<size_t>(g.stages) * kHaloStageBytes + static_cast<size_t>(fixed) +
-                      static_cast<size_t>(g.n_halo) * g.halo_bytes;
+                      static_cast<size_t>(g.n_halo) * g.halo_bytes + static_cast<size_t>(g.out_stage_bytes);
   FB200_CUDA_OK(cudaFuncSetAttribute(conv2d_halo_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(smem)));
   const uint32_t idesc = make_instr_desc(kFmtTF32, /*a MN-major*/ 1, /*b MN-major*/ 0, kHaloTileM,
                                          static_cast<uint32_t>(g.npad));
   const int grid = static_cast<int>(g.n_tiles < kNumSMs ? g.n_tiles : kNumSMs);
   conv2d_halo_tcgen05_kernel<<<grid, kHaloThreads, smem, as_stream(stream)>>>(
-      tx, static_cast<const float*>(w), static_cast<const float*>(bias), static_cast<float*>(out), g, idesc,
+      tx, tout, static_cast<const float*>(w), static_cast<const float*>(bias), static_cast<float*>(out), g, idesc,
       epi, status);
   return after_launch("conv2d_halo_tcgen05_kernel");
 }

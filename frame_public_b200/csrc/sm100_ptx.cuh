@@ -109,6 +109,28 @@ __device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const void* tmap,
       : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
 }
+// 4-D tiled STORE of a shared-memory tile (bulk async-group completion).  Elements that fall outside
+// the tensor are not written; the start coordinates must not be negative and x must again be a
+// multiple of 16 bytes.  tma_store_commit closes a group, tma_store_wait_read<N> returns once all but
+// the N most recent groups have finished READING shared memory (the staging buffer may be reused),
+// tma_store_wait_all once their global writes are done as well.
+__device__ __forceinline__ void tma_store_4d(const void* tmap, uint32_t smem_src, int32_t x, int32_t y,
+                                             int32_t z, int32_t w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+      :
+      : "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_src), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int N> __device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
 }

@@ -29,6 +29,8 @@ CASES = [
     ((12, 3, 224, 224), (64, 3, 7, 7), (2, 2), (3, 3), True),
     ((3, 16, 12, 16), (40, 16, 3, 3), (2, 1), (0, 1), False),
     ((2, 96, 8, 8), (32, 96, 3, 3), (1, 1), (1, 1), True),
+    # results through the TMA-store tile, last tile of each image only partly inside it (22 rows, 10 per tile)
+    ((2, 8, 22, 12), (24, 8, 3, 3), (1, 1), (1, 1), True),
 ]
 
 
