@@ -319,45 +319,47 @@ conv2d_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x,
       if (lane == 0) mbar_arrive(halo_empty(buf));
     }
   } else if (warp == kHaloMmaWarp) {
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      // A: MN-major, 32-pixel spans 4096 bytes apart (LBO), 4-row k groups 512 bytes apart (SBO);
-      // one MMA (K = 8) covers two groups = 1024 bytes.  B: K-major, 8-row groups 1024 bytes apart;
-      // a K step is 32 bytes inside the row.  The descriptors differ only in their address field
-      // (bytes >> 4), so they are built once and advanced by additions: this loop runs on ONE
-      // thread, where every instruction is latency rather than throughput.
-      const uint64_t a_desc0 = make_smem_desc(base, kHaloBlockK * 128, 512, kLayoutSw128Base32);
-      const uint64_t b_desc0 = make_smem_desc(base + w_off, 16, 1024, kLayoutSw128);
-      for (int idx = 0; idx < total_items && ok; ++idx) {
-        const HaloItem it = halo_decode(idx, my_tiles, apr, g.n_cb);
-        if (it.cb == 0) {
-          if (!mbar_wait(tmem_empty(it.acc), (static_cast<uint32_t>(it.round) & 1u) ^ 1u, status, kFaultHaloMmaTmem)) { ok = false; break; }
-          tcgen05_fence_after_sync();
-        }
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(it.acc * g.npad);
-        for (int sb = 0; sb < n_stage_blocks; ++sb) {
-          if (!mbar_wait(full_bar(stage), phase, status, kFaultHaloMmaFull)) { ok = false; break; }
-          tcgen05_fence_after_sync();
-          const int nsub = g.kblocks - sb * kHaloSub < kHaloSub ? g.kblocks - sb * kHaloSub : kHaloSub;
-          for (int sub = 0; sub < nsub; ++sub) {
-            const int kb = sb * kHaloSub + sub;
-            const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((stage * kHaloStageBytes + sub * kHaloAStage) >> 4);
-            const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((kb * g.npad * 128) >> 4);
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-              mma_tf32(d_tmem, a_desc + static_cast<uint64_t>(ks * 64), b_desc + static_cast<uint64_t>(ks * 2), idesc,
-                       (it.cb > 0 || kb > 0 || ks > 0) ? 1u : 0u);
-            }
-          }
-          mma_commit(empty_bar(stage));
-          if (++stage == g.stages) { stage = 0; phase ^= 1u; }
-        }
+    // The whole warp runs this loop and one elected lane issues (warp-uniform code keeps the
+    // descriptors in uniform registers: the single-lane branch this replaces fed the tensor pipe
+    // about a third slower).
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    // A: MN-major, 32-pixel spans 4096 bytes apart (LBO), 4-row k groups 512 bytes apart (SBO);
+    // one MMA (K = 8) covers two groups = 1024 bytes.  B: K-major, 8-row groups 1024 bytes apart;
+    // a K step is 32 bytes inside the row.  The descriptors differ only in their address field
+    // (bytes >> 4), so they are built once and advanced by additions.
+    const uint64_t a_desc0 = make_smem_desc(base, kHaloBlockK * 128, 512, kLayoutSw128Base32);
+    const uint64_t b_desc0 = make_smem_desc(base + w_off, 16, 1024, kLayoutSw128);
+    for (int idx = 0; idx < total_items && ok; ++idx) {
+      const HaloItem it = halo_decode(idx, my_tiles, apr, g.n_cb);
+      if (it.cb == 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(tmem_empty(it.acc), (static_cast<uint32_t>(it.round) & 1u) ^ 1u, status, kFaultHaloMmaTmem));
         if (!ok) break;
-        if (it.last_of_pass) mma_commit(w_free);
-        if (it.cb == g.n_cb - 1) mma_commit(tmem_full(it.acc));
+        tcgen05_fence_after_sync();
       }
+      const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(it.acc * g.npad);
+      for (int sb = 0; sb < n_stage_blocks; ++sb) {
+        ok = __all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, status, kFaultHaloMmaFull));
+        if (!ok) break;
+        tcgen05_fence_after_sync();
+        const int nsub = g.kblocks - sb * kHaloSub < kHaloSub ? g.kblocks - sb * kHaloSub : kHaloSub;
+        for (int sub = 0; sub < nsub; ++sub) {
+          const int kb = sb * kHaloSub + sub;
+          const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((stage * kHaloStageBytes + sub * kHaloAStage) >> 4);
+          const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((kb * g.npad * 128) >> 4);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            mma_tf32_elect(d_tmem, a_desc + static_cast<uint64_t>(ks * 64), b_desc + static_cast<uint64_t>(ks * 2), idesc,
+                           (it.cb > 0 || kb > 0 || ks > 0) ? 1u : 0u);
+          }
+        }
+        mma_commit_elect(empty_bar(stage));
+        if (++stage == g.stages) { stage = 0; phase ^= 1u; }
+      }
+      if (!ok) break;
+      if (it.last_of_pass) mma_commit_elect(w_free);
+      if (it.cb == g.n_cb - 1) mma_commit_elect(tmem_full(it.acc));
     }
   } else {
     // ---- epilogue warps 9..12: TMEM lane = pixel of the tile ------------------------------------

@@ -155,69 +155,72 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t tmem_base = *tmem_slot_ptr;
 
   if (warp == 0) {
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        int64_t tm, tn;
-        tile_coords(tile, tiles_m, tiles_n, dest.group_m, &tm, &tn);
-        for (int64_t kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u, status, kFaultProducerEmpty)) { ok = false; break; }
-          mbar_arrive_expect_tx(full_bar(stage), Cfg::kStageBytes);
-          const uint32_t a_dst = base + stage * Cfg::kStageBytes;
-          const uint32_t b_dst = a_dst + Cfg::kAStageBytes;
-          tma_load_2d(a_dst, &tmap_a, full_bar(stage), static_cast<int32_t>(kb * Cfg::kBlockK),
-                      static_cast<int32_t>(tm * kBlockM));
+    // Producer: the whole warp runs the loop, one elected lane issues the copies (warp-uniform code
+    // keeps the tensor-map address, the coordinates and the barrier address in uniform registers).
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      int64_t tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, dest.group_m, &tm, &tn);
+      const int32_t a_row = static_cast<int32_t>(tm * kBlockM);
+      const int32_t b_col = static_cast<int32_t>(tn * BLOCK_N);
+      for (int64_t kb = 0; kb < k_blocks; ++kb) {
+        ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1u, status, kFaultProducerEmpty));
+        if (!ok) break;
+        mbar_arrive_expect_tx_elect(full_bar(stage), Cfg::kStageBytes);
+        const uint32_t a_dst = base + stage * Cfg::kStageBytes;
+        const uint32_t b_dst = a_dst + Cfg::kAStageBytes;
+        const int32_t k0 = static_cast<int32_t>(kb * Cfg::kBlockK);
+        tma_load_2d_elect(a_dst, &tmap_a, full_bar(stage), k0, a_row);
 #pragma unroll
-          for (int c = 0; c < Cfg::kBChunks; ++c) {
-            tma_load_2d(b_dst + c * Cfg::kBChunkBytes, &tmap_b, full_bar(stage),
-                        static_cast<int32_t>(tn * BLOCK_N + c * Cfg::kBChunkCols),
-                        static_cast<int32_t>(kb * Cfg::kBlockK));
-          }
-          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+        for (int c = 0; c < Cfg::kBChunks; ++c) {
+          tma_load_2d_elect(b_dst + c * Cfg::kBChunkBytes, &tmap_b, full_bar(stage), b_col + c * Cfg::kBChunkCols, k0);
         }
+        if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      int acc = 0;
-      uint32_t acc_phase = 0;
-      bool ok = true;
-      const uint64_t a_desc0 = make_smem_desc_sw128(base, 16, 1024);
-      const uint64_t b_desc0 = ELT == 2 ? make_smem_desc(base + Cfg::kAStageBytes, Cfg::kBChunkBytes, 1024, kLayoutSw128)
-                                        : make_smem_desc(base + Cfg::kAStageBytes, Cfg::kBChunkBytes, 512, kLayoutSw128Base32);
-      for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, status, kFaultMmaTmemEmpty)) { ok = false; break; }
-        tcgen05_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
-        for (int64_t kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, status, kFaultMmaFull)) { ok = false; break; }
-          tcgen05_fence_after_sync();
-          // A: K-major, rows of 128 bytes, 8-row groups 1024 bytes apart; a K step is 32 bytes
-          // further inside the swizzled row.  B: MN-major; 2-byte elements: 16-byte swizzle units,
-          // 8-row K groups 1024 bytes apart; 4-byte elements: 32-byte swizzle units, 4-row K groups
-          // 512 bytes apart.  Only the address field (bytes >> 4) changes between instructions, so
-          // the descriptors are built once per kernel and advanced by additions: this loop runs on
-          // one thread, where every instruction between two tcgen05.mma is exposed latency.
-          const uint32_t stage_units = static_cast<uint32_t>(stage * Cfg::kStageBytes) >> 4;
-#pragma unroll
-          for (int ks = 0; ks < Cfg::kStepsPerBlock; ++ks) {
-            const uint64_t a_desc = a_desc0 + (stage_units + static_cast<uint32_t>(ks * Cfg::kUmmaKBytes) / 16u);
-            const uint64_t b_desc = b_desc0 + (stage_units + static_cast<uint32_t>(ks * Cfg::kBKStepBytes) / 16u);
-            const uint32_t accumulate = (kb > 0 || ks > 0) ? 1u : 0u;
-            if (ELT == 2) mma_f16(d_tmem, a_desc, b_desc, idesc, accumulate);
-            else mma_tf32(d_tmem, a_desc, b_desc, idesc, accumulate);
-          }
-          mma_commit(empty_bar(stage));  // the slot is free once these MMAs have read it
-          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
-        }
+    // The whole warp runs the loop and one elected lane issues: in warp-uniform code the
+    // descriptors live in uniform registers, and the tensor pipe gets an instruction every 128
+    // cycles (M128 x N256 x K16) instead of every 166 from a single-lane branch.
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    const uint64_t a_desc0 = make_smem_desc_sw128(base, 16, 1024);
+    const uint64_t b_desc0 = ELT == 2 ? make_smem_desc(base + Cfg::kAStageBytes, Cfg::kBChunkBytes, 1024, kLayoutSw128)
+                                      : make_smem_desc(base + Cfg::kAStageBytes, Cfg::kBChunkBytes, 512, kLayoutSw128Base32);
+    for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      ok = __all_sync(0xffffffffu, mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, status, kFaultMmaTmemEmpty));
+      if (!ok) break;
+      tcgen05_fence_after_sync();
+      const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
+      for (int64_t kb = 0; kb < k_blocks; ++kb) {
+        ok = __all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, status, kFaultMmaFull));
         if (!ok) break;
-        mma_commit(tmem_full_bar(acc));
-        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+        tcgen05_fence_after_sync();
+        // A: K-major, rows of 128 bytes, 8-row groups 1024 bytes apart; a K step is 32 bytes
+        // further inside the swizzled row.  B: MN-major; 2-byte elements: 16-byte swizzle units,
+        // 8-row K groups 1024 bytes apart; 4-byte elements: 32-byte swizzle units, 4-row K groups
+        // 512 bytes apart.  Only the address field (bytes >> 4) changes between instructions, so
+        // the descriptors are built once per kernel and advanced by additions.
+        const uint32_t stage_units = static_cast<uint32_t>(stage * Cfg::kStageBytes) >> 4;
+#pragma unroll
+        for (int ks = 0; ks < Cfg::kStepsPerBlock; ++ks) {
+          const uint64_t a_desc = a_desc0 + (stage_units + static_cast<uint32_t>(ks * Cfg::kUmmaKBytes) / 16u);
+          const uint64_t b_desc = b_desc0 + (stage_units + static_cast<uint32_t>(ks * Cfg::kBKStepBytes) / 16u);
+          const uint32_t accumulate = (kb > 0 || ks > 0) ? 1u : 0u;
+          if (ELT == 2) mma_f16_elect(d_tmem, a_desc, b_desc, idesc, accumulate);
+          else mma_tf32_elect(d_tmem, a_desc, b_desc, idesc, accumulate);
+        }
+        mma_commit_elect(empty_bar(stage));  // the slot is free once these MMAs have read it
+        if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
       }
+      if (!ok) break;
+      mma_commit_elect(tmem_full_bar(acc));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
   } else {
     // Epilogue warps 2..9; a warp may only touch TMEM lanes 32*(warp%4) .. +31, so two warps share
