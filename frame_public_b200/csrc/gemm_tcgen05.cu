@@ -53,6 +53,27 @@ static int gemm_group_m() {
   return v;
 }
 
+// FRAME_B200_GEMM_MH=1 keeps every GEMM on 128-row tiles (for measurements).
+static int gemm_m_halves() {
+  static const int v = [] {
+    const char* e = getenv("FRAME_B200_GEMM_MH");
+    return (e != nullptr && atoi(e) == 1) ? 1 : 2;
+  }();
+  return v;
+}
+
+// An epilogue of binary ops, ReLU, square and the step function: a few instructions per element.
+static bool light_epilogue(const EpilogueDev& epi) {
+  for (int i = 0; i < epi.n_ops; ++i) {
+    const int op = epi.ops[i];
+    if (op != FB200_EW_ADD && op != FB200_EW_MUL && op != FB200_EW_RELU && op != FB200_EW_SQUARE &&
+        op != FB200_EW_HEAVISIDE) {
+      return false;
+    }
+  }
+  return true;
+}
+
 // Where a tile of the result goes: one or several destination matrices of row pitch `ld`, at
 // column offset `col0`.  One destination with ld == N, col0 == 0 is the ordinary matmul; several
 // destinations are this GPU's and its peers' copies of a column-split result (the all-gather is
@@ -73,18 +94,19 @@ enum GemmFault : int {
   kFaultEpilogueTmemFull = 104,
 };
 
-template <int ELT, int BLOCK_N>
+template <int ELT, int BLOCK_N, int MH = 1>
 struct GemmCfg {
+  static constexpr int kTileM = kBlockM * MH;          // MH = 2: two M = 128 instructions share each B stage
   static constexpr int kBlockK = 128 / ELT;          // one 128-byte swizzle span of K
   static constexpr int kUmmaKBytes = 32;              // K extent of one tcgen05.mma
   static constexpr int kStepsPerBlock = 4;
-  static constexpr int kAStageBytes = kBlockM * 128;  // 16 KiB
+  static constexpr int kAStageBytes = kTileM * 128;   // 16 KiB per 128 rows
   static constexpr int kBChunkCols = 128 / ELT;       // N columns per 128-byte span
   static constexpr int kBChunks = BLOCK_N / kBChunkCols;
   static constexpr int kBChunkBytes = kBlockK * 128;
   static constexpr int kBStageBytes = kBChunks * kBChunkBytes;
   static constexpr int kStageBytes = kAStageBytes + kBStageBytes;
-  static constexpr int kStages = (BLOCK_N == 256) ? 4 : (BLOCK_N == 128 ? 6 : 8);
+  static constexpr int kStages = MH == 2 ? 3 : ((BLOCK_N == 256) ? 4 : (BLOCK_N == 128 ? 6 : 8));
   static constexpr int kTmemCols = 2 * BLOCK_N;
   // B operand, MN-major, 128-byte swizzle: 8-row K groups are 1024 bytes apart (SBO); the next
   // 128-byte span along N is one chunk further (LBO).  One MMA covers 32 bytes of K:
@@ -104,12 +126,13 @@ __device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64
   *tn = in_group / group_rows;
 }
 
-template <typename T, int ELT, int BLOCK_N>
+template <typename T, int ELT, int BLOCK_N, int MH>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                    const __grid_constant__ CUtensorMap tmap_b, GemmDest dest, int64_t M,
+                    const __grid_constant__ CUtensorMap tmap_b, int b_spans_map, GemmDest dest, int64_t M,
                     int64_t N, int64_t K, uint32_t idesc, EpilogueDev epi, int* status) {
-  using Cfg = GemmCfg<ELT, BLOCK_N>;
+  using Cfg = GemmCfg<ELT, BLOCK_N, MH>;
+  static_assert(MH == 1 || (MH == 2 && BLOCK_N == 256), "two M halves fill TMEM with one 256 x 256 tile");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
@@ -126,9 +149,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int64_t tiles_m = (M + kBlockM - 1) / kBlockM;
+  const int64_t tiles_m = (M + Cfg::kTileM - 1) / Cfg::kTileM;
   const int64_t tiles_n = (N + BLOCK_N - 1) / BLOCK_N;
   const int64_t n_tiles = tiles_m * tiles_n;
+  const int group_m = dest.group_m / MH > 0 ? dest.group_m / MH : 1;
   const int64_t k_blocks = (K + Cfg::kBlockK - 1) / Cfg::kBlockK;
 
   if (threadIdx.x == 0) {
@@ -138,7 +162,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tmem_full_bar(a), 1);
-      mbar_init(tmem_empty_bar(a), 8);  // one arrival per epilogue warp
+      mbar_init(tmem_empty_bar(a), 8 / MH);  // one arrival per epilogue warp that drains it
     }
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
@@ -162,8 +186,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     bool ok = true;
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
       int64_t tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, dest.group_m, &tm, &tn);
-      const int32_t a_row = static_cast<int32_t>(tm * kBlockM);
+      tile_coords(tile, tiles_m, tiles_n, group_m, &tm, &tn);
+      const int32_t a_row = static_cast<int32_t>(tm * Cfg::kTileM);
       const int32_t b_col = static_cast<int32_t>(tn * BLOCK_N);
       for (int64_t kb = 0; kb < k_blocks; ++kb) {
         ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1u, status, kFaultProducerEmpty));
@@ -173,9 +197,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t b_dst = a_dst + Cfg::kAStageBytes;
         const int32_t k0 = static_cast<int32_t>(kb * Cfg::kBlockK);
         tma_load_2d_elect(a_dst, &tmap_a, full_bar(stage), k0, a_row);
+        if (b_spans_map) {
+          // B seen as [N / span][K][span columns]: the whole B stage is one copy
+          tma_load_3d_elect(b_dst, &tmap_b, full_bar(stage), 0, k0, b_col / Cfg::kBChunkCols);
+        } else {
 #pragma unroll
-        for (int c = 0; c < Cfg::kBChunks; ++c) {
-          tma_load_2d_elect(b_dst + c * Cfg::kBChunkBytes, &tmap_b, full_bar(stage), b_col + c * Cfg::kBChunkCols, k0);
+          for (int c = 0; c < Cfg::kBChunks; ++c) {
+            tma_load_2d_elect(b_dst + c * Cfg::kBChunkBytes, &tmap_b, full_bar(stage), b_col + c * Cfg::kBChunkCols, k0);
+          }
         }
         if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
       }
@@ -193,10 +222,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint64_t b_desc0 = ELT == 2 ? make_smem_desc(base + Cfg::kAStageBytes, Cfg::kBChunkBytes, 1024, kLayoutSw128)
                                       : make_smem_desc(base + Cfg::kAStageBytes, Cfg::kBChunkBytes, 512, kLayoutSw128Base32);
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-      ok = __all_sync(0xffffffffu, mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, status, kFaultMmaTmemEmpty));
+      // MH = 1: the tile's accumulator alternates between the two TMEM halves; MH = 2: the tile
+      // uses both (rows 0-127 and 128-255), so nothing of the next tile overlaps this epilogue.
+      ok = __all_sync(0xffffffffu, mbar_wait(tmem_empty_bar(MH == 2 ? 0 : acc), acc_phase ^ 1u, status, kFaultMmaTmemEmpty));
+      if (MH == 2 && ok) ok = __all_sync(0xffffffffu, mbar_wait(tmem_empty_bar(1), acc_phase ^ 1u, status, kFaultMmaTmemEmpty));
       if (!ok) break;
       tcgen05_fence_after_sync();
-      const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BLOCK_N);
+      const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(MH == 2 ? 0 : acc * BLOCK_N);
       for (int64_t kb = 0; kb < k_blocks; ++kb) {
         ok = __all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, status, kFaultMmaFull));
         if (!ok) break;
@@ -209,26 +241,38 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const uint32_t stage_units = static_cast<uint32_t>(stage * Cfg::kStageBytes) >> 4;
 #pragma unroll
         for (int ks = 0; ks < Cfg::kStepsPerBlock; ++ks) {
-          const uint64_t a_desc = a_desc0 + (stage_units + static_cast<uint32_t>(ks * Cfg::kUmmaKBytes) / 16u);
           const uint64_t b_desc = b_desc0 + (stage_units + static_cast<uint32_t>(ks * Cfg::kBKStepBytes) / 16u);
           const uint32_t accumulate = (kb > 0 || ks > 0) ? 1u : 0u;
-          if (ELT == 2) mma_f16_elect(d_tmem, a_desc, b_desc, idesc, accumulate);
-          else mma_tf32_elect(d_tmem, a_desc, b_desc, idesc, accumulate);
+#pragma unroll
+          for (int h = 0; h < MH; ++h) {
+            const uint64_t a_desc = a_desc0 + (stage_units + static_cast<uint32_t>(h * kBlockM * 128 + ks * Cfg::kUmmaKBytes) / 16u);
+            const uint32_t d = d_tmem + static_cast<uint32_t>(h * BLOCK_N);
+            if (ELT == 2) mma_f16_elect(d, a_desc, b_desc, idesc, accumulate);
+            else mma_tf32_elect(d, a_desc, b_desc, idesc, accumulate);
+          }
         }
         mma_commit_elect(empty_bar(stage));  // the slot is free once these MMAs have read it
         if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
       }
       if (!ok) break;
-      mma_commit_elect(tmem_full_bar(acc));
-      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      if (MH == 2) {
+        mma_commit_elect(tmem_full_bar(0));
+        mma_commit_elect(tmem_full_bar(1));
+        acc_phase ^= 1u;
+      } else {
+        mma_commit_elect(tmem_full_bar(acc));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
     }
   } else {
     // Epilogue warps 2..9; a warp may only touch TMEM lanes 32*(warp%4) .. +31, so two warps share
     // each lane quarter and split the tile's columns between them.
     const int quarter = warp & 3;
     const int half = (warp - 2) >> 2;
-    constexpr int kChunksPerWarp = BLOCK_N / 64;
-    int acc = 0;
+    // MH = 1: the two warps of a lane quarter split the tile's columns; MH = 2: each drains one of
+    // the two accumulators (rows 0-127 / 128-255 of the tile) over all its columns.
+    constexpr int kChunksPerWarp = MH == 2 ? BLOCK_N / 32 : BLOCK_N / 64;
+    int acc = MH == 2 ? half : 0;
     uint32_t acc_phase = 0;
     constexpr int W = 16 / sizeof(T);
     bool vec_n = (N % W == 0) && (dest.ld % W == 0) && (dest.col0 % W == 0);
@@ -236,14 +280,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     bool ok = true;
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
       int64_t tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, dest.group_m, &tm, &tn);
+      tile_coords(tile, tiles_m, tiles_n, group_m, &tm, &tn);
       if (!mbar_wait(tmem_full_bar(acc), acc_phase, status, kFaultEpilogueTmemFull)) { ok = false; break; }
       tcgen05_fence_after_sync();
-      const int64_t row = tm * kBlockM + quarter * 32 + lane;
+      const int64_t row = tm * Cfg::kTileM + (MH == 2 ? half * kBlockM : 0) + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(acc * BLOCK_N);
 #pragma unroll 1
-      for (int c = half * kChunksPerWarp; c < (half + 1) * kChunksPerWarp; ++c) {
+      for (int c = (MH == 2 ? 0 : half * kChunksPerWarp); c < (MH == 2 ? kChunksPerWarp : (half + 1) * kChunksPerWarp); ++c) {
         const int64_t col0 = tn * BLOCK_N + c * 32;
         if (col0 >= N) break;  // warp-uniform
         uint32_t r[32];
@@ -312,7 +356,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tcgen05_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
-      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      if (MH == 2) {
+        acc_phase ^= 1u;
+      } else if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
     }
   }
 
@@ -372,6 +421,34 @@ int make_tmap_2d(CUtensorMap* map, const void* ptr, int dtype, int64_t rows, int
   return FB200_OK;
 }
 
+// The B operand [k, n] (row-major, n a multiple of the 128-byte span) seen as
+// [n / span][k][span columns]: one box of `spans` x box_k x span elements is a whole B stage, written
+// to shared memory span after span, i.e. what `spans` 2-D copies of 128-byte-wide boxes would write.
+int make_tmap_b_spans(CUtensorMap* map, const void* ptr, int dtype, int64_t k, int64_t n, int box_k,
+                      int spans, bool swizzle_32b_units) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return set_error(FB200_DEVICE_ERROR, "cuTensorMapEncodeTiled is not available");
+  const int elt = itemsize_of(dtype);
+  const int span = 128 / elt;
+  CUtensorMapDataType dt = dtype == FB200_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                           : dtype == FB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  cuuint64_t gdim[3] = {static_cast<cuuint64_t>(span), static_cast<cuuint64_t>(k),
+                        static_cast<cuuint64_t>(n / span)};
+  cuuint64_t gstride[2] = {static_cast<cuuint64_t>(n) * elt, static_cast<cuuint64_t>(span) * elt};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(span), static_cast<cuuint32_t>(box_k), static_cast<cuuint32_t>(spans)};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, dt, 3, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle_32b_units ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    return set_error(FB200_INTERNAL, "cuTensorMapEncodeTiled (B spans) failed with code %d (k %lld n %lld)",
+                     static_cast<int>(r), (long long)k, (long long)n);
+  }
+  return FB200_OK;
+}
+
 // Row-major fp32 tensor [n, c, h, w] with a box of [1, box_c, box_h, box_w] elements, no swizzle: the
 // halo tile of a convolution lands in shared memory as plain [box_c][box_h][box_w].  w must be a
 // multiple of 4 elements (strides are multiples of 16 bytes) and box_w too.
@@ -419,23 +496,30 @@ int device_status_word(int** dev_ptr) {
   return FB200_OK;
 }
 
-template <typename T, int ELT, int BLOCK_N>
+template <typename T, int ELT, int BLOCK_N, int MH = 1>
 static int launch_tc(const void* a, const void* b, const GemmDest& c, int64_t m, int64_t n, int64_t k,
                      int dtype, const EpilogueDev& epi, cudaStream_t s) {
-  using Cfg = GemmCfg<ELT, BLOCK_N>;
+  using Cfg = GemmCfg<ELT, BLOCK_N, MH>;
   CUtensorMap ta, tb;
-  if (int rc = make_tmap_2d(&ta, a, dtype, m, k, kBlockM, false)) return rc;
-  if (int rc = make_tmap_2d(&tb, b, dtype, k, n, Cfg::kBlockK, ELT == 4)) return rc;
+  if (int rc = make_tmap_2d(&ta, a, dtype, m, k, Cfg::kTileM, false)) return rc;
+  // one copy per B stage when n is a whole number of 128-byte spans (else the last span would run
+  // into the next row), `kBChunks` copies of one span otherwise
+  const int b_spans_map = (n % Cfg::kBChunkCols == 0 && Cfg::kBChunks > 1) ? 1 : 0;
+  if (b_spans_map) {
+    if (int rc = make_tmap_b_spans(&tb, b, dtype, k, n, Cfg::kBlockK, Cfg::kBChunks, ELT == 4)) return rc;
+  } else {
+    if (int rc = make_tmap_2d(&tb, b, dtype, k, n, Cfg::kBlockK, ELT == 4)) return rc;
+  }
   int* status = nullptr;
   if (int rc = device_status_word(&status)) return rc;
   const uint32_t fmt = dtype == FB200_F32 ? kFmtTF32 : (dtype == FB200_BF16 ? kFmtBF16 : kFmtF16);
   const uint32_t idesc = make_instr_desc(fmt, /*a MN-major*/ 0, /*b MN-major*/ 1, kBlockM, BLOCK_N);
-  auto kernel = gemm_tcgen05_kernel<T, ELT, BLOCK_N>;
+  auto kernel = gemm_tcgen05_kernel<T, ELT, BLOCK_N, MH>;
   FB200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(Cfg::kSmemBytes)));
-  const int64_t tiles = ((m + kBlockM - 1) / kBlockM) * ((n + BLOCK_N - 1) / BLOCK_N);
+  const int64_t tiles = ((m + Cfg::kTileM - 1) / Cfg::kTileM) * ((n + BLOCK_N - 1) / BLOCK_N);
   const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
-  kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, c, m, n, k, idesc,
+  kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, b_spans_map, c, m, n, k, idesc,
                                                       epi, status);
   return after_launch("gemm_tcgen05_kernel");
 }
@@ -445,7 +529,20 @@ static int launch_tc_n(const void* a, const void* b, const GemmDest& c, int64_t 
                        int dtype, const EpilogueDev& epi, cudaStream_t s) {
   const int64_t tiles_m = (m + kBlockM - 1) / kBlockM;
   auto tiles = [&](int bn) { return tiles_m * ((n + bn - 1) / bn); };
-  if (n > 128 && tiles(256) >= kNumSMs) return launch_tc<T, ELT, 256>(a, b, c, m, n, k, dtype, epi, s);
+  if (n > 128 && tiles(256) >= kNumSMs) {
+    // 256 x 256 tiles (two M halves per B stage) need a third less operand traffic from L2 per FLOP
+    // (8192^3 bf16: 1418 -> 1509 TFLOP/s, TF32 4096^3: 622 -> 690), but the tile fills TMEM, so its
+    // epilogue no longer overlaps the next mainloop: a transcendental epilogue (GELU over 64 Ki
+    // elements is about 18 K issue cycles per tile) costs more than the traffic saves.  They are
+    // taken for chains of adds, multiplies and ReLU, when the waves of tiles do not get longer by
+    // more than an eighth.
+    const int64_t t2 = ((m + 255) / 256) * ((n + 255) / 256);
+    const int64_t waves1 = (tiles(256) + kNumSMs - 1) / kNumSMs, waves2 = (t2 + kNumSMs - 1) / kNumSMs;
+    if (gemm_m_halves() == 2 && light_epilogue(epi) && m > 128 && t2 >= kNumSMs && 16 * waves2 <= 9 * waves1) {
+      return launch_tc<T, ELT, 256, 2>(a, b, c, m, n, k, dtype, epi, s);
+    }
+    return launch_tc<T, ELT, 256>(a, b, c, m, n, k, dtype, epi, s);
+  }
   if (n > 64 && tiles(128) >= kNumSMs) return launch_tc<T, ELT, 128>(a, b, c, m, n, k, dtype, epi, s);
   if (n > 128 && tiles(64) < kNumSMs / 2) return launch_tc<T, ELT, 128>(a, b, c, m, n, k, dtype, epi, s);
   return launch_tc<T, ELT, 64>(a, b, c, m, n, k, dtype, epi, s);

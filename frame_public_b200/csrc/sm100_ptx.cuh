@@ -75,6 +75,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
   }
 }
 
+// The same wait for a converged warp: lane 0 polls, the result is broadcast.  The other lanes are
+// ordered after lane 0's acquire by the shuffle's warp synchronisation.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, int* status, int code) {
+  int ok = 1;
+  if ((threadIdx.x & 31u) == 0u) ok = mbar_wait(bar, parity, status, code) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
 // ---- proxies and fences -----------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -119,6 +127,19 @@ __device__ __forceinline__ void tma_load_2d_elect(uint32_t smem_dst, const void*
       "}\n"
       :
       : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_elect(uint32_t smem_dst, const void* tmap, uint32_t bar,
+                                                  int32_t x, int32_t y, int32_t z) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "@q cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];\n\t"
+      "}\n"
+      :
+      : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
 // 4-D tiled load (x innermost).  x times the element size must again be a multiple of 16 bytes; the
