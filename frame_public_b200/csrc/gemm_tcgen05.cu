@@ -42,7 +42,8 @@ int gemm_simt(const void* a, const void* b, void* c, int64_t m, int64_t n, int64
 using namespace sm100;
 
 constexpr int kBlockM = 128;
-constexpr int kGemmThreads = 320;   // TMA warp, MMA warp, eight epilogue warps
+constexpr int kGemmThreads = 352;   // A-producer warp, MMA warp, eight epilogue warps, B-producer warp
+constexpr int kGemmBProducerWarp = 10;
 // M-blocks per group of the tile walk; FRAME_B200_GEMM_GROUP_M overrides it for measurements.
 static int gemm_group_m() {
   static const int v = [] {
@@ -94,25 +95,33 @@ enum GemmFault : int {
   kFaultEpilogueTmemFull = 104,
 };
 
-template <int ELT, int BLOCK_N, int MH = 1>
+template <int ELT, int BLOCK_N, int MH = 1, int KB = 128>
 struct GemmCfg {
+  // KB: bytes of K per A row in a ring stage (128, or 64 with the 64-byte swizzle).  What bounds the
+  // mainloop is the ring's turnaround (per-role cycle counters, 8192^3 bf16: about 2400 cycles from
+  // the first MMA of a slot to its refill having landed: 512 of MMAs, 450 until the producer sees the
+  // commit, the copy's issue, 1300 of L2 latency and transfer; four 48 KiB slots give one k-block
+  // per 600 cycles against 512 of tensor work).  Half-size slots (KB = 64, twice as many) would turn
+  // around faster, but the producers then cannot issue fast enough: measured 0.955 ms against
+  // 0.764 ms for 8192^3 on 128 x 256 tiles, 0.728 against 0.711 on 256 x 256.  Only KB = 128 is
+  // instantiated.
   static constexpr int kTileM = kBlockM * MH;          // MH = 2: two M = 128 instructions share each B stage
-  static constexpr int kBlockK = 128 / ELT;          // one 128-byte swizzle span of K
+  static constexpr int kBlockK = KB / ELT;           // K elements per stage: one swizzle span of the A rows
   static constexpr int kUmmaKBytes = 32;              // K extent of one tcgen05.mma
-  static constexpr int kStepsPerBlock = 4;
-  static constexpr int kAStageBytes = kTileM * 128;   // 16 KiB per 128 rows
+  static constexpr int kStepsPerBlock = KB / 32;
+  static constexpr int kAStageBytes = kTileM * KB;    // 16 KiB per 128 rows of 128 bytes
   static constexpr int kBChunkCols = 128 / ELT;       // N columns per 128-byte span
   static constexpr int kBChunks = BLOCK_N / kBChunkCols;
   static constexpr int kBChunkBytes = kBlockK * 128;
   static constexpr int kBStageBytes = kBChunks * kBChunkBytes;
   static constexpr int kStageBytes = kAStageBytes + kBStageBytes;
-  static constexpr int kStages = MH == 2 ? 3 : ((BLOCK_N == 256) ? 4 : (BLOCK_N == 128 ? 6 : 8));
+  static constexpr int kStages = (192 * 1024) / kStageBytes > 12 ? 12 : (192 * 1024) / kStageBytes;
   static constexpr int kTmemCols = 2 * BLOCK_N;
   // B operand, MN-major, 128-byte swizzle: 8-row K groups are 1024 bytes apart (SBO); the next
   // 128-byte span along N is one chunk further (LBO).  One MMA covers 32 bytes of K:
   // 16 rows (two groups) for 2-byte elements, 8 rows (one group) for 4-byte elements.
   static constexpr int kBKStepBytes = (kUmmaKBytes / ELT / 8) * 1024;
-  static constexpr size_t kSmemBytes = size_t(kStages) * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr size_t kSmemBytes = size_t(kStages) * kStageBytes + 1024 /*align*/ + 512 /*barriers*/;
 };
 
 __device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64_t tiles_n, int kGroupM,
@@ -126,12 +135,12 @@ __device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64
   *tn = in_group / group_rows;
 }
 
-template <typename T, int ELT, int BLOCK_N, int MH>
+template <typename T, int ELT, int BLOCK_N, int MH, int KB>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b, int b_spans_map, GemmDest dest, int64_t M,
                     int64_t N, int64_t K, uint32_t idesc, EpilogueDev epi, int* status) {
-  using Cfg = GemmCfg<ELT, BLOCK_N, MH>;
+  using Cfg = GemmCfg<ELT, BLOCK_N, MH, KB>;
   static_assert(MH == 1 || (MH == 2 && BLOCK_N == 256), "two M halves fill TMEM with one 256 x 256 tile");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -157,7 +166,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {
-      mbar_init(full_bar(s), 1);
+      mbar_init(full_bar(s), 2);   // the A producer's and the B producer's expect_tx arrivals
       mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -178,9 +187,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
 
-  if (warp == 0) {
-    // Producer: the whole warp runs the loop, one elected lane issues the copies (warp-uniform code
-    // keeps the tensor-map address, the coordinates and the barrier address in uniform registers).
+  if (warp == 0 || warp == kGemmBProducerWarp) {
+    // Producers: warp 0 loads the A tiles, warp 10 the B tiles, each with its own expect_tx arrival
+    // on the stage's full barrier (two short issue paths instead of one long one: the reaction to
+    // a freed slot is part of the ring's turnaround).  The whole warp runs the loop, one elected
+    // lane issues the copies (warp-uniform code keeps the tensor-map address, the coordinates and
+    // the barrier address in uniform registers).
+    const bool loads_b = warp != 0;
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -192,18 +205,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int64_t kb = 0; kb < k_blocks; ++kb) {
         ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1u, status, kFaultProducerEmpty));
         if (!ok) break;
-        mbar_arrive_expect_tx_elect(full_bar(stage), Cfg::kStageBytes);
         const uint32_t a_dst = base + stage * Cfg::kStageBytes;
         const uint32_t b_dst = a_dst + Cfg::kAStageBytes;
         const int32_t k0 = static_cast<int32_t>(kb * Cfg::kBlockK);
-        tma_load_2d_elect(a_dst, &tmap_a, full_bar(stage), k0, a_row);
-        if (b_spans_map) {
-          // B seen as [N / span][K][span columns]: the whole B stage is one copy
-          tma_load_3d_elect(b_dst, &tmap_b, full_bar(stage), 0, k0, b_col / Cfg::kBChunkCols);
+        if (!loads_b) {
+          mbar_arrive_expect_tx_elect(full_bar(stage), Cfg::kAStageBytes);
+          tma_load_2d_elect(a_dst, &tmap_a, full_bar(stage), k0, a_row);
         } else {
+          mbar_arrive_expect_tx_elect(full_bar(stage), Cfg::kBStageBytes);
+          if (b_spans_map) {
+            // B seen as [N / span][K][span columns]: the whole B stage is one copy
+            tma_load_3d_elect(b_dst, &tmap_b, full_bar(stage), 0, k0, b_col / Cfg::kBChunkCols);
+          } else {
 #pragma unroll
-          for (int c = 0; c < Cfg::kBChunks; ++c) {
-            tma_load_2d_elect(b_dst + c * Cfg::kBChunkBytes, &tmap_b, full_bar(stage), b_col + c * Cfg::kBChunkCols, k0);
+            for (int c = 0; c < Cfg::kBChunks; ++c) {
+              tma_load_2d_elect(b_dst + c * Cfg::kBChunkBytes, &tmap_b, full_bar(stage), b_col + c * Cfg::kBChunkCols, k0);
+            }
           }
         }
         if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
@@ -218,7 +235,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
-    const uint64_t a_desc0 = make_smem_desc_sw128(base, 16, 1024);
+    // A rows are KB bytes long: 128-byte swizzle with 8-row groups 1024 bytes apart, or 64-byte
+    // swizzle with 8-row groups 512 bytes apart.
+    const uint64_t a_desc0 = make_smem_desc(base, 16, 8 * KB, KB == 64 ? kLayoutSw64 : kLayoutSw128);
     const uint64_t b_desc0 = ELT == 2 ? make_smem_desc(base + Cfg::kAStageBytes, Cfg::kBChunkBytes, 1024, kLayoutSw128)
                                       : make_smem_desc(base + Cfg::kAStageBytes, Cfg::kBChunkBytes, 512, kLayoutSw128Base32);
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
@@ -245,7 +264,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           const uint32_t accumulate = (kb > 0 || ks > 0) ? 1u : 0u;
 #pragma unroll
           for (int h = 0; h < MH; ++h) {
-            const uint64_t a_desc = a_desc0 + (stage_units + static_cast<uint32_t>(h * kBlockM * 128 + ks * Cfg::kUmmaKBytes) / 16u);
+            const uint64_t a_desc = a_desc0 + (stage_units + static_cast<uint32_t>(h * kBlockM * KB + ks * Cfg::kUmmaKBytes) / 16u);
             const uint32_t d = d_tmem + static_cast<uint32_t>(h * BLOCK_N);
             if (ELT == 2) mma_f16_elect(d, a_desc, b_desc, idesc, accumulate);
             else mma_tf32_elect(d, a_desc, b_desc, idesc, accumulate);
@@ -264,7 +283,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       }
     }
-  } else {
+  } else if (warp < kGemmBProducerWarp) {
     // Epilogue warps 2..9; a warp may only touch TMEM lanes 32*(warp%4) .. +31, so two warps share
     // each lane quarter and split the tile's columns between them.
     const int quarter = warp & 3;
@@ -421,6 +440,30 @@ int make_tmap_2d(CUtensorMap* map, const void* ptr, int dtype, int64_t rows, int
   return FB200_OK;
 }
 
+// 2-D row-major tensor [rows, cols]; box = row_bytes (128 or 64) x box_rows with the swizzle of that
+// width (16-byte units): the K-major A operand.
+int make_tmap_rows(CUtensorMap* map, const void* ptr, int dtype, int64_t rows, int64_t cols, int box_rows,
+                   int row_bytes) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return set_error(FB200_DEVICE_ERROR, "cuTensorMapEncodeTiled is not available");
+  const int elt = itemsize_of(dtype);
+  CUtensorMapDataType dt = dtype == FB200_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                           : dtype == FB200_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  cuuint64_t gdim[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t gstride[1] = {static_cast<cuuint64_t>(cols) * elt};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(row_bytes / elt), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, dt, 2, const_cast<void*>(ptr), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    return set_error(FB200_INTERNAL, "cuTensorMapEncodeTiled failed with code %d (rows %lld cols %lld)",
+                     static_cast<int>(r), (long long)rows, (long long)cols);
+  }
+  return FB200_OK;
+}
+
 // The B operand [k, n] (row-major, n a multiple of the 128-byte span) seen as
 // [n / span][k][span columns]: one box of `spans` x box_k x span elements is a whole B stage, written
 // to shared memory span after span, i.e. what `spans` 2-D copies of 128-byte-wide boxes would write.
@@ -496,12 +539,12 @@ int device_status_word(int** dev_ptr) {
   return FB200_OK;
 }
 
-template <typename T, int ELT, int BLOCK_N, int MH = 1>
+template <typename T, int ELT, int BLOCK_N, int MH = 1, int KB = 128>
 static int launch_tc(const void* a, const void* b, const GemmDest& c, int64_t m, int64_t n, int64_t k,
                      int dtype, const EpilogueDev& epi, cudaStream_t s) {
-  using Cfg = GemmCfg<ELT, BLOCK_N, MH>;
+  using Cfg = GemmCfg<ELT, BLOCK_N, MH, KB>;
   CUtensorMap ta, tb;
-  if (int rc = make_tmap_2d(&ta, a, dtype, m, k, Cfg::kTileM, false)) return rc;
+  if (int rc = make_tmap_rows(&ta, a, dtype, m, k, Cfg::kTileM, KB)) return rc;
   // one copy per B stage when n is a whole number of 128-byte spans (else the last span would run
   // into the next row), `kBChunks` copies of one span otherwise
   const int b_spans_map = (n % Cfg::kBChunkCols == 0 && Cfg::kBChunks > 1) ? 1 : 0;
@@ -514,7 +557,7 @@ static int launch_tc(const void* a, const void* b, const GemmDest& c, int64_t m,
   if (int rc = device_status_word(&status)) return rc;
   const uint32_t fmt = dtype == FB200_F32 ? kFmtTF32 : (dtype == FB200_BF16 ? kFmtBF16 : kFmtF16);
   const uint32_t idesc = make_instr_desc(fmt, /*a MN-major*/ 0, /*b MN-major*/ 1, kBlockM, BLOCK_N);
-  auto kernel = gemm_tcgen05_kernel<T, ELT, BLOCK_N, MH>;
+  auto kernel = gemm_tcgen05_kernel<T, ELT, BLOCK_N, MH, KB>;
   FB200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(Cfg::kSmemBytes)));
   const int64_t tiles = ((m + Cfg::kTileM - 1) / Cfg::kTileM) * ((n + BLOCK_N - 1) / BLOCK_N);

@@ -291,7 +291,7 @@ __device__ __forceinline__ void mma_commit(uint32_t bar) {
 // 1 in [46,48), base offset 0, layout type in [61,64) (2 = 128-byte swizzle).
 // Layout types: 2 = 128-byte swizzle of 16-byte units over 8 rows; 1 = 128-byte swizzle of
 // 32-byte units over 4 rows, the only form tcgen05 accepts for MN-major 32-bit (TF32) operands.
-enum : uint32_t { kLayoutSw128 = 2, kLayoutSw128Base32 = 1 };
+enum : uint32_t { kLayoutSw128 = 2, kLayoutSw128Base32 = 1, kLayoutSw64 = 4 };   // 4: 64-byte swizzle of 16-byte units over 4 rows
 __host__ __device__ constexpr uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes,
                                                       uint32_t sbo_bytes, uint32_t layout_type) {
   return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) |
