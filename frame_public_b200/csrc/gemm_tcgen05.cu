@@ -6,20 +6,27 @@
 // Replaces the cublasLtMatmul call of src/backends/cuda/kernels/matmul.cpp:90-276, which also
 // ran bias and activation as separate launches; here they are the epilogue of the same kernel.
 //
-// Design (one persistent CTA per SM, 320 threads, warp-specialised):
-//   warp 0   TMA producer.  A tile [128 x BLOCK_K] is K-contiguous ("K-major" operand);
-//            B tile [BLOCK_K x BLOCK_N] is N-contiguous ("MN-major" operand), loaded as
-//            BLOCK_N*elt/128 boxes of 128 bytes x BLOCK_K rows.  Both land in 128-byte-swizzled
-//            shared memory; a ring of STAGES slots is handed over with full/empty mbarriers.
-//            No host-side transposes: the row-major B is consumed as it lies in HBM.
-//   warp 1   allocates TMEM (2 accumulators of BLOCK_N fp32 columns) and, from one thread, issues
-//            4 tcgen05.mma (M=128, N=BLOCK_N, K=32 bytes) per stage; tcgen05.commit releases the
-//            stage and, after the last k-block, publishes the accumulator.
+// Design (one persistent CTA per SM, 352 threads, warp-specialised):
+//   warps 0, 10  TMA producers: warp 0 loads the A tile [128*MH x BLOCK_K] (K-contiguous, "K-major"
+//            operand), warp 10 the B tile [BLOCK_K x BLOCK_N] (N-contiguous, "MN-major" operand)
+//            with one copy through a 3-D view [N/span][K][span] of the row-major matrix (or one copy
+//            per 128-byte span when N is not a whole number of spans).  Both land in
+//            128-byte-swizzled shared memory; a ring of STAGES slots is handed over with full/empty
+//            mbarriers.  No host-side transposes: the row-major B is consumed as it lies in HBM.
+//   warp 1   allocates TMEM (2 accumulators of BLOCK_N fp32 columns) and issues 4*MH tcgen05.mma
+//            (M=128, N=BLOCK_N, K=32 bytes) per stage; tcgen05.commit releases the stage and, after
+//            the last k-block, publishes the accumulator.
 //   warps 2-9 epilogue: tcgen05.ld 32 lanes x 32 columns, the epilogue chain in fp32 registers
 //            (operands fetched with 128-bit loads), 128-bit stores; two warps per TMEM lane
 //            quarter, each on half of the tile's columns (with four warps a transcendental
 //            epilogue behind a short K was bound by those 128 threads).  The second accumulator
-//            lets the epilogue of tile i overlap the MMAs of tile i+1.
+//            lets the epilogue of tile i overlap the MMAs of tile i+1 (MH = 1; with MH = 2 the
+//            256 x 256 tile takes both accumulators and each warp group drains one of them).
+// Producer and MMA loops are run by the whole warp, one elected lane issuing each instruction
+// (elect.sync + predicate): inside an `if (lane == 0)` branch the same loops fed the tensor pipe a
+// quarter slower (166 instead of 128 cycles per M128 x N256 x K16 instruction with resident
+// operands), because descriptors and coordinates then live in per-thread instead of uniform
+// registers.
 // Tiles are walked in groups of 16 M-blocks so that concurrently resident CTAs share A and B
 // panels in the 126 MB L2 (B is then streamed from HBM tiles_m/16 times: 1.0 GB of DRAM reads per
 // 8192^3 launch with groups of 8 measured by ncu, against 384 MB of distinct operands).  Edge tiles rely on TMA zero fill for loads and masked stores.
