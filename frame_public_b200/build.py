@@ -26,11 +26,11 @@ COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hi
 
 # Kernels whose arithmetic must round exactly like the CPU reference (built with
 # -ffp-contract=off): no fused multiply-add.
-NO_FMA = {"elementwise.cu", "rowops.cu", "scan.cu", "scan_chunked.cu", "conv_pool.cu", "gemm_simt.cu", "shape_ops.cu"}
+NO_FMA = {"elementwise.cu", "rowops.cu", "scan.cu", "scan_chunked.cu", "conv_pool.cu", "gemm_simt.cu", "shape_ops.cu", "grad_ops.cu"}
 
 SOURCES = ["runtime.cu", "elementwise.cu", "rowops.cu", "scan.cu", "shape_ops.cu", "conv_pool.cu",
            "gemm_simt.cu", "gemm_tcgen05.cu", "conv_tcgen05.cu", "plan.cu", "mamba_scan.cu", "scan_chunked.cu",
-           "attention_tcgen05.cu", "conv_halo_tcgen05.cu", "index_ops.cu"]
+           "attention_tcgen05.cu", "conv_halo_tcgen05.cu", "index_ops.cu", "grad_ops.cu"]
 
 
 def _headers_mtime() -> float:

@@ -92,6 +92,11 @@ SIGNATURES = {
     "fb200_conv1d": (c_int, [_P, _P, _P, _P] + [c_int64] * 8 + [c_int, _P]),
     "fb200_max_pool2d": (c_int, [_P, _P] + [c_int64] * 10 + [c_int, _P]),
     "fb200_avg_pool2d": (c_int, [_P, _P] + [c_int64] * 10 + [c_int, _P]),
+    "fb200_max_pool2d_select": (c_int, [_P, _P, _P] + [c_int64] * 10 + [c_int, _P]),
+    "fb200_max_pool2d_grad": (c_int, [_P, _P, _P] + [c_int64] * 10 + [c_int, _P]),
+    "fb200_avg_pool2d_grad": (c_int, [_P, _P] + [c_int64] * 10 + [c_int, _P]),
+    "fb200_conv2d_grad_input": (c_int, [_P, _P, _P, POINTER(Conv2dParams), c_int, _P]),
+    "fb200_conv2d_grad_filter": (c_int, [_P, _P, _P, POINTER(Conv2dParams), c_int, _P]),
     "fb200_gather": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int, c_int, _P]),
     "fb200_scatter_add": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int, c_int, _P]),
     "fb200_softmax": (c_int, [_P, _P, c_int64, c_int64, c_int, _P]),
@@ -261,6 +266,26 @@ def max_pool2d(x, out, n, c, h, w, kh, kw, sh, sw, ph, pw, dtype, stream=None):
 
 def avg_pool2d(x, out, n, c, h, w, kh, kw, sh, sw, ph, pw, dtype, stream=None):
     check(load().fb200_avg_pool2d(x, out, n, c, h, w, kh, kw, sh, sw, ph, pw, dtype, stream))
+
+
+def max_pool2d_select(g, x, out, n, c, h, w, kh, kw, sh, sw, ph, pw, dtype, stream=None):
+    check(load().fb200_max_pool2d_select(g, x, out, n, c, h, w, kh, kw, sh, sw, ph, pw, dtype, stream))
+
+
+def max_pool2d_grad(dy, x, dx, n, c, h, w, kh, kw, sh, sw, ph, pw, dtype, stream=None):
+    check(load().fb200_max_pool2d_grad(dy, x, dx, n, c, h, w, kh, kw, sh, sw, ph, pw, dtype, stream))
+
+
+def avg_pool2d_grad(dy, dx, n, c, h, w, kh, kw, sh, sw, ph, pw, dtype, stream=None):
+    check(load().fb200_avg_pool2d_grad(dy, dx, n, c, h, w, kh, kw, sh, sw, ph, pw, dtype, stream))
+
+
+def conv2d_grad_input(dy, w, dx, params: Conv2dParams, dtype, stream=None):
+    check(load().fb200_conv2d_grad_input(dy, w, dx, byref(params), dtype, stream))
+
+
+def conv2d_grad_filter(x, dy, dw, params: Conv2dParams, dtype, stream=None):
+    check(load().fb200_conv2d_grad_filter(x, dy, dw, byref(params), dtype, stream))
 
 
 def gather(x, indices, out, n, f, k, dtype, index_dtype, stream=None):

@@ -30,7 +30,8 @@ namespace fb200 {
 
 enum class Kind {
   kMatmul, kConv2d, kConv1d, kMaxPool, kChain, kBiasAdd, kSoftmax, kLayerNorm, kScan, kMambaScan,
-  kTranspose, kSlice, kConcat, kSum, kCopy, kAlias, kConstant, kSkip, kAttentionFan, kDwConvTimeMajor, kAvgPool, kGather, kScatterAdd
+  kTranspose, kSlice, kConcat, kSum, kCopy, kAlias, kConstant, kSkip, kAttentionFan, kDwConvTimeMajor, kAvgPool, kGather, kScatterAdd,
+  kPoolSelect, kMaxPoolGrad, kAvgPoolGrad, kConvGradInput, kConvGradFilter
 };
 
 struct SlotInfo {
@@ -323,6 +324,25 @@ static int decode_step(fb200_plan* p, Step& s) {
     auto kv = parse_int_list(k->text), sv = parse_int_list(st->text), pv = parse_int_list(pd->text);
     if (kv.size() != 2 || sv.size() != 2 || pv.size() != 2) return set_error(FB200_INVALID_ARGUMENT, "op 'avg_pool2d': malformed attributes");
     s.iv = {kv[0], kv[1], sv[0], sv[1], pv[0], pv[1]};
+  } else if (op == "max_pool2d_select_internal" || op == "max_pool2d_grad_internal" || op == "avg_pool2d_grad_internal") {
+    s.kind = op == "max_pool2d_select_internal" ? Kind::kPoolSelect
+             : op == "max_pool2d_grad_internal" ? Kind::kMaxPoolGrad : Kind::kAvgPoolGrad;
+    const Attr *k = need("kernel"), *st = need("stride"), *pd = need("padding");
+    if (!k || !st || !pd) return FB200_INVALID_ARGUMENT;
+    auto kv = parse_int_list(k->text), sv = parse_int_list(st->text), pv = parse_int_list(pd->text);
+    if (kv.size() != 2 || sv.size() != 2 || pv.size() != 2) {
+      return set_error(FB200_INVALID_ARGUMENT, "op '%s': malformed attributes", op.c_str());
+    }
+    s.iv = {kv[0], kv[1], sv[0], sv[1], pv[0], pv[1]};
+  } else if (op == "conv2d_grad_input_internal" || op == "conv2d_grad_filter_internal") {
+    s.kind = op == "conv2d_grad_input_internal" ? Kind::kConvGradInput : Kind::kConvGradFilter;
+    const Attr *st = need("stride"), *pd = need("padding"), *g = need("groups");
+    if (!st || !pd || !g) return FB200_INVALID_ARGUMENT;
+    auto sv = parse_int_list(st->text), pv = parse_int_list(pd->text), gv = parse_int_list(g->text);
+    if (sv.size() != 2 || pv.size() != 2 || gv.size() != 1) {
+      return set_error(FB200_INVALID_ARGUMENT, "op '%s': malformed attributes", op.c_str());
+    }
+    s.iv = {sv[0], sv[1], pv[0], pv[1], gv[0]};
   } else if (op == "gather") {
     s.kind = Kind::kGather;
     p->graph_enabled = false;   // the index check synchronises the stream
@@ -1114,6 +1134,35 @@ static int run_step(fb200_plan* p, Step& s, const void* const* inputs, void* con
       return fb200_avg_pool2d(in_ptr(0), out, in_slot(0).dims[0], in_slot(0).dims[1], in_slot(0).dims[2],
                               in_slot(0).dims[3], s.iv[0], s.iv[1], s.iv[2], s.iv[3], s.iv[4], s.iv[5],
                               os.dtype, stream);
+    }
+    case Kind::kPoolSelect:
+    case Kind::kMaxPoolGrad: {
+      // the forward op's input is operand 1 (x); operand 0 is g resp. dy
+      if (s.in.size() != 2 || in_slot(1).dims.size() != 4) {
+        return set_error(FB200_INVALID_ARGUMENT, "op '%s' expects two operands and a rank-4 x", s.op.c_str());
+      }
+      const auto& xd = in_slot(1).dims;
+      auto fn = s.kind == Kind::kPoolSelect ? fb200_max_pool2d_select : fb200_max_pool2d_grad;
+      return fn(in_ptr(0), in_ptr(1), out, xd[0], xd[1], xd[2], xd[3], s.iv[0], s.iv[1], s.iv[2], s.iv[3],
+                s.iv[4], s.iv[5], os.dtype, stream);
+    }
+    case Kind::kAvgPoolGrad: {
+      if (os.dims.size() != 4) return set_error(FB200_INVALID_ARGUMENT, "op 'avg_pool2d_grad_internal' expects a rank-4 result");
+      return fb200_avg_pool2d_grad(in_ptr(0), out, os.dims[0], os.dims[1], os.dims[2], os.dims[3], s.iv[0],
+                                   s.iv[1], s.iv[2], s.iv[3], s.iv[4], s.iv[5], os.dtype, stream);
+    }
+    case Kind::kConvGradInput:
+    case Kind::kConvGradFilter: {
+      // conv2d_grad_input_internal(dy, w) -> dx;  conv2d_grad_filter_internal(x, dy) -> dw
+      const bool wrt_input = s.kind == Kind::kConvGradInput;
+      if (s.in.size() != 2 || os.dims.size() != 4 || in_slot(wrt_input ? 1 : 0).dims.size() != 4) {
+        return set_error(FB200_INVALID_ARGUMENT, "op '%s' expects rank-4 operands", s.op.c_str());
+      }
+      const auto& xd = wrt_input ? os.dims : in_slot(0).dims;
+      const auto& wd = wrt_input ? in_slot(1).dims : os.dims;
+      fb200_conv2d_params cp{xd[0], xd[1], xd[2], xd[3], wd[0], wd[2], wd[3], s.iv[0], s.iv[1], s.iv[2], s.iv[3], s.iv[4]};
+      return wrt_input ? fb200_conv2d_grad_input(in_ptr(0), in_ptr(1), out, &cp, os.dtype, stream)
+                       : fb200_conv2d_grad_filter(in_ptr(0), in_ptr(1), out, &cp, os.dtype, stream);
     }
     case Kind::kGather: {
       if (s.in.size() != 2 || in_slot(0).dims.size() != 2 || in_slot(1).dims.size() != 1) {

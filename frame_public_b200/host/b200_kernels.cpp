@@ -250,6 +250,93 @@ Status avg_pool2d(KernelContext& ctx) {
       "avg_pool2d");
 }
 
+// Gradient-side internals of pooling and convolution (gathers in the CPU reference's order).  The
+// geometry comes from the tensors themselves: the forward op's input is operand 1 of the max-pool
+// ops, the result of avg_pool2d_grad_internal / conv2d_grad_input_internal, operand 0 of
+// conv2d_grad_filter_internal; the filter is operand 1 resp. the result.
+struct PoolAttrs3 {
+  const std::vector<int64_t>* kernel;
+  const std::vector<int64_t>* stride;
+  const std::vector<int64_t>* padding;
+};
+Status pool_attrs(KernelContext& ctx, const char* op, PoolAttrs3* a) {
+  a->kernel = attr<std::vector<int64_t>>(ctx, "kernel");
+  a->stride = attr<std::vector<int64_t>>(ctx, "stride");
+  a->padding = attr<std::vector<int64_t>>(ctx, "padding");
+  if (a->kernel == nullptr || a->kernel->size() != 2) return missing(op, "kernel");
+  if (a->stride == nullptr || a->stride->size() != 2) return missing(op, "stride");
+  if (a->padding == nullptr || a->padding->size() != 2) return missing(op, "padding");
+  return Status::ok();
+}
+
+Status max_pool2d_select_or_grad(KernelContext& ctx, const char* op, bool select) {
+  FRAME_RETURN_IF_ERROR(arity(ctx, op, 2, 2));
+  PoolAttrs3 a{};
+  FRAME_RETURN_IF_ERROR(pool_attrs(ctx, op, &a));
+  const Tensor& x = ctx.inputs[1];
+  if (x.shape().rank() != 4) {
+    return Status::make(ErrorCode::kInvalidArgument, std::string("op '") + op + "' cuda kernel requires rank-4 x");
+  }
+  auto fn = select ? fb200_max_pool2d_select : fb200_max_pool2d_grad;
+  return frame_b200::to_status(
+      fn(ctx.inputs[0].raw_data(), x.raw_data(), ctx.outputs[0].raw_data(), x.shape().dim(0), x.shape().dim(1),
+         x.shape().dim(2), x.shape().dim(3), (*a.kernel)[0], (*a.kernel)[1], (*a.stride)[0], (*a.stride)[1],
+         (*a.padding)[0], (*a.padding)[1], dtype_of(x), stream_of(ctx)),
+      op);
+}
+Status max_pool2d_select_internal(KernelContext& ctx) {
+  return max_pool2d_select_or_grad(ctx, "max_pool2d_select_internal", true);
+}
+Status max_pool2d_grad_internal(KernelContext& ctx) {
+  return max_pool2d_select_or_grad(ctx, "max_pool2d_grad_internal", false);
+}
+
+Status avg_pool2d_grad_internal(KernelContext& ctx) {
+  FRAME_RETURN_IF_ERROR(arity(ctx, "avg_pool2d_grad_internal", 1, 1));
+  PoolAttrs3 a{};
+  FRAME_RETURN_IF_ERROR(pool_attrs(ctx, "avg_pool2d_grad_internal", &a));
+  const Tensor& dx = ctx.outputs[0];
+  if (dx.shape().rank() != 4) {
+    return Status::make(ErrorCode::kInvalidArgument, "op 'avg_pool2d_grad_internal' cuda kernel requires a rank-4 result");
+  }
+  return frame_b200::to_status(
+      fb200_avg_pool2d_grad(ctx.inputs[0].raw_data(), ctx.outputs[0].raw_data(), dx.shape().dim(0), dx.shape().dim(1),
+                            dx.shape().dim(2), dx.shape().dim(3), (*a.kernel)[0], (*a.kernel)[1], (*a.stride)[0],
+                            (*a.stride)[1], (*a.padding)[0], (*a.padding)[1], dtype_of(dx), stream_of(ctx)),
+      "avg_pool2d_grad_internal");
+}
+
+Status conv2d_grad(KernelContext& ctx, const char* op, bool wrt_input) {
+  FRAME_RETURN_IF_ERROR(arity(ctx, op, 2, 2));
+  const auto* stride = attr<std::vector<int64_t>>(ctx, "stride");
+  const auto* padding = attr<std::vector<int64_t>>(ctx, "padding");
+  const auto* groups = attr<int64_t>(ctx, "groups");
+  if (stride == nullptr || stride->size() != 2) return missing(op, "stride");
+  if (padding == nullptr || padding->size() != 2) return missing(op, "padding");
+  if (groups == nullptr) return missing(op, "groups");
+  const Tensor& xt = wrt_input ? ctx.outputs[0] : ctx.inputs[0];
+  const Tensor& wt = wrt_input ? ctx.inputs[1] : ctx.outputs[0];
+  if (xt.shape().rank() != 4 || wt.shape().rank() != 4) {
+    return Status::make(ErrorCode::kInvalidArgument, std::string("op '") + op + "' cuda kernel requires rank-4 tensors");
+  }
+  fb200_conv2d_params p{};
+  p.n = xt.shape().dim(0); p.cin = xt.shape().dim(1); p.h = xt.shape().dim(2); p.w = xt.shape().dim(3);
+  p.cout = wt.shape().dim(0); p.kh = wt.shape().dim(2); p.kw = wt.shape().dim(3);
+  p.stride_h = (*stride)[0]; p.stride_w = (*stride)[1];
+  p.pad_h = (*padding)[0]; p.pad_w = (*padding)[1];
+  p.groups = *groups;
+  if (wt.shape().dim(1) * p.groups != p.cin) {
+    return Status::make(ErrorCode::kInvalidArgument, std::string("op '") + op + "' cuda kernel: w.dim(1)*groups != Cin");
+  }
+  const int rc = wrt_input ? fb200_conv2d_grad_input(ctx.inputs[0].raw_data(), ctx.inputs[1].raw_data(),
+                                                     ctx.outputs[0].raw_data(), &p, dtype_of(ctx.outputs[0]), stream_of(ctx))
+                           : fb200_conv2d_grad_filter(ctx.inputs[0].raw_data(), ctx.inputs[1].raw_data(),
+                                                      ctx.outputs[0].raw_data(), &p, dtype_of(ctx.outputs[0]), stream_of(ctx));
+  return frame_b200::to_status(rc, op);
+}
+Status conv2d_grad_input_internal(KernelContext& ctx) { return conv2d_grad(ctx, "conv2d_grad_input_internal", true); }
+Status conv2d_grad_filter_internal(KernelContext& ctx) { return conv2d_grad(ctx, "conv2d_grad_filter_internal", false); }
+
 // heaviside_surrogate: alpha only shapes the backward graph, but a bad alpha is an error here too
 // (src/backends/cpu/kernels/elementwise.cpp, read_heaviside_alpha).
 Status heaviside_surrogate(KernelContext& ctx) {
@@ -499,6 +586,11 @@ FRAME_REGISTER_KERNEL("conv2d", "cuda", &conv2d);
 FRAME_REGISTER_KERNEL("conv1d", "cuda", &conv1d);
 FRAME_REGISTER_KERNEL("max_pool2d", "cuda", &max_pool2d);
 FRAME_REGISTER_KERNEL("avg_pool2d", "cuda", &avg_pool2d);
+FRAME_REGISTER_KERNEL("max_pool2d_select_internal", "cuda", &max_pool2d_select_internal);
+FRAME_REGISTER_KERNEL("max_pool2d_grad_internal", "cuda", &max_pool2d_grad_internal);
+FRAME_REGISTER_KERNEL("avg_pool2d_grad_internal", "cuda", &avg_pool2d_grad_internal);
+FRAME_REGISTER_KERNEL("conv2d_grad_input_internal", "cuda", &conv2d_grad_input_internal);
+FRAME_REGISTER_KERNEL("conv2d_grad_filter_internal", "cuda", &conv2d_grad_filter_internal);
 FRAME_REGISTER_KERNEL("heaviside_surrogate", "cuda", &heaviside_surrogate);
 FRAME_REGISTER_KERNEL("gather", "cuda", &gather);
 FRAME_REGISTER_KERNEL("scatter_add", "cuda", &scatter_add);

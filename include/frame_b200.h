@@ -220,6 +220,36 @@ FB200_API int fb200_avg_pool2d(const void* x, void* out, int64_t n, int64_t c, i
                                int64_t w, int64_t kh, int64_t kw, int64_t stride_h,
                                int64_t stride_w, int64_t pad_h, int64_t pad_w, int dtype,
                                fb200_stream stream);
+/* Gradient-side internals of pooling and convolution (n, c, h, w and the params describe the FORWARD
+ * op's input x; out_h = (h + 2*pad_h - kh) / stride_h + 1, likewise out_w).  All are computed as
+ * gathers over their output, in the CPU reference's operation order: fp32 results are bit-identical.
+ *  max_pool2d_select_internal: out[n,c,oh,ow] = g[n,c, argmax of x over the window] (first maximum,
+ *    strict >), g and x [n,c,h,w]; src/backends/cpu/kernels/pool.cpp:459-483.
+ *  max_pool2d_grad_internal: dx [n,c,h,w] = dy [n,c,oh,ow] added into each window's argmax of x,
+ *    windows in (oh, ow) order; pool.cpp:356-389 (replaces cudnnPoolingBackward).
+ *  avg_pool2d_grad_internal: dx[n,c,ih,iw] = (sum of dy over the windows that cover it) / (KH*KW);
+ *    pool.cpp:542-568.
+ *  conv2d_grad_input_internal: dx [n,cin,h,w] from dy [n,cout,oh,ow] and w [cout,cin/groups,kh,kw],
+ *    terms in (co, kh, kw) order; src/backends/cpu/kernels/conv.cpp:321-353 (replaces
+ *    cudnnConvolutionBackwardData).
+ *  conv2d_grad_filter_internal: dw [cout,cin/groups,kh,kw] from x and dy, terms in (n, oh, ow) order;
+ *    conv.cpp:424-453 (replaces cudnnConvolutionBackwardFilter). */
+FB200_API int fb200_max_pool2d_select(const void* g, const void* x, void* out, int64_t n, int64_t c,
+                                      int64_t h, int64_t w, int64_t kh, int64_t kw, int64_t stride_h,
+                                      int64_t stride_w, int64_t pad_h, int64_t pad_w, int dtype,
+                                      fb200_stream stream);
+FB200_API int fb200_max_pool2d_grad(const void* dy, const void* x, void* dx, int64_t n, int64_t c,
+                                    int64_t h, int64_t w, int64_t kh, int64_t kw, int64_t stride_h,
+                                    int64_t stride_w, int64_t pad_h, int64_t pad_w, int dtype,
+                                    fb200_stream stream);
+FB200_API int fb200_avg_pool2d_grad(const void* dy, void* dx, int64_t n, int64_t c, int64_t h,
+                                    int64_t w, int64_t kh, int64_t kw, int64_t stride_h,
+                                    int64_t stride_w, int64_t pad_h, int64_t pad_w, int dtype,
+                                    fb200_stream stream);
+FB200_API int fb200_conv2d_grad_input(const void* dy, const void* w, void* dx,
+                                      const fb200_conv2d_params* p, int dtype, fb200_stream stream);
+FB200_API int fb200_conv2d_grad_filter(const void* x, const void* dy, void* dw,
+                                       const fb200_conv2d_params* p, int dtype, fb200_stream stream);
 /* gather along axis 0: out[k, :] = x[indices[k], :], x [n, f], indices [k] of int32 / int64
  * (src/ops/schemas/gather.cpp:86-118; replaces src/backends/cuda/kernels/gather.cu).  An index
  * outside [0, n) is an error that names the value, found like the reference does by looking at the

@@ -236,6 +236,157 @@ def avg_pool2d(x, kernel=(2, 2), stride=(2, 2), padding=(0, 0), dtype: int = DT_
     return from_accum((acc / F32(kh * kw)).astype(F32), dtype)
 
 
+def _pool_argmax(xv, kernel, stride, padding):
+    """Flat index ih*W+iw of each window's first maximum (strict >), shape [n, c, oh, ow]
+    (find_window_argmax, src/backends/cpu/kernels/pool.cpp:185-208)."""
+    n, c, h, wd = xv.shape
+    kh, kw = kernel
+    sh, sw = stride
+    ph, pw = padding
+    oh = conv_out_size(h, kh, sh, ph)
+    ow = conv_out_size(wd, kw, sw, pw)
+    best = np.zeros((n, c, oh, ow), dtype=F32)
+    arg = np.full((n, c, oh, ow), -1, dtype=np.int64)
+    for i in range(kh):
+        for j in range(kw):
+            ohs = np.arange(oh) * sh - ph + i
+            ows = np.arange(ow) * sw - pw + j
+            oi = np.nonzero((ohs >= 0) & (ohs < h))[0]
+            qi = np.nonzero((ows >= 0) & (ows < wd))[0]
+            if oi.size == 0 or qi.size == 0:
+                continue
+            vals = xv[:, :, ohs[oi]][:, :, :, ows[qi]]
+            cur = best[:, :, oi[:, None], qi[None, :]]
+            cur_arg = arg[:, :, oi[:, None], qi[None, :]]
+            take = (cur_arg < 0) | (vals > cur)
+            flat = (ohs[oi][:, None] * wd + ows[qi][None, :])[None, None]
+            best[:, :, oi[:, None], qi[None, :]] = np.where(take, vals, cur)
+            arg[:, :, oi[:, None], qi[None, :]] = np.where(take, flat, cur_arg)
+    assert (arg >= 0).all(), "max_pool2d window without a valid position"
+    return arg
+
+
+def max_pool2d_select(g, x, kernel, stride, padding, dtype: int = DT_F32):
+    """out = g at each window's argmax of x (pool.cpp:459-483); pure data movement."""
+    arg = _pool_argmax(to_accum(x, dtype), kernel, stride, padding)
+    n, c, oh, ow = arg.shape
+    flat = np.asarray(g).reshape(n * c, -1)
+    return np.take_along_axis(flat, arg.reshape(n * c, -1), axis=1).reshape(n, c, oh, ow)
+
+
+def max_pool2d_grad(dy, x, kernel, stride, padding, dtype: int = DT_F32):
+    """dy added into each window's argmax of x, windows in (oh, ow) order, fp32 buffer rounded once
+    (pool.cpp:356-389)."""
+    xv = to_accum(x, dtype)
+    dyv = to_accum(dy, dtype)
+    n, c, h, wd = xv.shape
+    arg = _pool_argmax(xv, kernel, stride, padding)
+    oh, ow = arg.shape[2:]
+    acc = np.zeros((n * c, h * wd), dtype=F32)
+    rows = np.arange(n * c)
+    arg2 = arg.reshape(n * c, oh, ow)
+    dy2 = dyv.reshape(n * c, oh, ow)
+    for o in range(oh):
+        for q in range(ow):
+            cols = arg2[:, o, q]
+            acc[rows, cols] = (acc[rows, cols] + dy2[:, o, q]).astype(F32)
+    return from_accum(acc.reshape(n, c, h, wd), dtype)
+
+
+def _covering(size_in, k, s, p, size_out, tap):
+    """Input positions i whose window through kernel tap `tap` is a valid output position o:
+    i + p - tap == o * s, 0 <= o < size_out.  Returns (i, o) index arrays."""
+    i = np.arange(size_in)
+    num = i + p - tap
+    ok = (num >= 0) & (num % s == 0) & (num // s < size_out)
+    return i[ok], (num // s)[ok]
+
+
+def avg_pool2d_grad(dy, input_shape, kernel, stride, padding, dtype: int = DT_F32):
+    """dx = (sum of dy over the covering windows, kh then kw ascending) / (KH*KW) (pool.cpp:542-568)."""
+    dyv = to_accum(dy, dtype)
+    n, c, h, wd = input_shape
+    kh, kw = kernel
+    sh, sw = stride
+    ph, pw = padding
+    oh, ow = dyv.shape[2:]
+    acc = np.zeros((n, c, h, wd), dtype=F32)
+    for a in range(kh):
+        ih, o = _covering(h, kh, sh, ph, oh, a)
+        if ih.size == 0:
+            continue
+        for b in range(kw):
+            iw, q = _covering(wd, kw, sw, pw, ow, b)
+            if iw.size == 0:
+                continue
+            acc[:, :, ih[:, None], iw[None, :]] = (
+                acc[:, :, ih[:, None], iw[None, :]] + dyv[:, :, o[:, None], q[None, :]]).astype(F32)
+    return from_accum((acc / F32(kh * kw)).astype(F32), dtype)
+
+
+def conv2d_grad_input(dy, w, input_shape, stride, padding, groups: int = 1, dtype: int = DT_F32):
+    """BackwardData as a gather over dx, terms in (co, kh, kw) order, rounded products added in fp32
+    (src/backends/cpu/kernels/conv.cpp:321-353)."""
+    dyv = to_accum(dy, dtype)
+    wv = to_accum(w, dtype)
+    n, cin, h, wd = input_shape
+    cout, cpg, kh, kw = wv.shape
+    sh, sw = stride
+    ph, pw = padding
+    oh, ow = dyv.shape[2:]
+    copg = cout // groups
+    acc = np.zeros((n, cin, h, wd), dtype=F32)
+    for g in range(groups):
+        cis = slice(g * cpg, (g + 1) * cpg)
+        for co in range(g * copg, (g + 1) * copg):
+            for a in range(kh):
+                ih, o = _covering(h, kh, sh, ph, oh, a)
+                if ih.size == 0:
+                    continue
+                for b in range(kw):
+                    iw, q = _covering(wd, kw, sw, pw, ow, b)
+                    if iw.size == 0:
+                        continue
+                    d = dyv[:, co][:, o[:, None], q[None, :]]                      # [n, |ih|, |iw|]
+                    prod = (d[:, None] * wv[co, :, a, b][None, :, None, None]).astype(F32)
+                    sub = acc[:, cis][:, :, ih[:, None], iw[None, :]]
+                    acc[:, cis, ih[:, None], iw[None, :]] = (sub + prod).astype(F32)
+    return from_accum(acc, dtype)
+
+
+def conv2d_grad_filter(x, dy, filter_shape, stride, padding, groups: int = 1, dtype: int = DT_F32):
+    """BackwardFilter: one dot product per filter element, terms in (n, oh, ow) order
+    (src/backends/cpu/kernels/conv.cpp:424-453)."""
+    xv = to_accum(x, dtype)
+    dyv = to_accum(dy, dtype)
+    cout, cpg, kh, kw = filter_shape
+    n, cin, h, wd = xv.shape
+    sh, sw = stride
+    ph, pw = padding
+    oh, ow = dyv.shape[2:]
+    copg = cout // groups
+    acc = np.zeros((cout, cpg, kh, kw), dtype=F32)
+    for g in range(groups):
+        cos = slice(g * copg, (g + 1) * copg)
+        cis = slice(g * cpg, (g + 1) * cpg)
+        for b in range(n):
+            for o in range(oh):
+                ihs = o * sh - ph + np.arange(kh)
+                av = np.nonzero((ihs >= 0) & (ihs < h))[0]
+                if av.size == 0:
+                    continue
+                for q in range(ow):
+                    iws = q * sw - pw + np.arange(kw)
+                    bv = np.nonzero((iws >= 0) & (iws < wd))[0]
+                    if bv.size == 0:
+                        continue
+                    xs = xv[b, cis][:, ihs[av][:, None], iws[bv][None, :]]          # [cpg, |a|, |b|]
+                    prod = (xs[None] * dyv[b, cos, o, q][:, None, None, None]).astype(F32)
+                    sub = acc[cos][:, :, av[:, None], bv[None, :]]
+                    acc[cos, :, av[:, None], bv[None, :]] = (sub + prod).astype(F32)
+    return from_accum(acc, dtype)
+
+
 def gather(x, indices):
     """out[k, :] = x[indices[k], :] along axis 0 (src/ops/schemas/gather.cpp:86-118); an index
     outside [0, N) is an error."""

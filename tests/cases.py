@@ -45,7 +45,7 @@ class Case:
         vals = [g.input(irtext.DTYPE_NAMES[d], a.shape) for d, a in zip(in_dts, self.inputs)]
         out_shape = self.expected().shape
         attrs = dict(self.attrs)
-        for key in ("target_shape", "output_shape", "input_shape"):
+        for key in ("target_shape", "output_shape", "input_shape", "filter_shape"):
             if key in attrs:
                 attrs[key] = irtext.Shape(tuple(attrs[key]))
         out = g.node(self.op, vals, attrs, dt, out_shape)
@@ -237,8 +237,51 @@ def build_cases() -> List[Case]:
     cases.append(Case("max_pool2d_f32_k3_s2_p1_w16", "max_pool2d", F32, [rnd((2, 3, 10, 16))],
                       {"kernel": [3, 3], "stride": [2, 2], "padding": [1, 1]},
                       lambda x: fo.max_pool2d(x, (3, 3), (2, 2), (1, 1), F32), exact=True))
+
+    # ---- gradient-side internals of pooling and convolution (bit-exact: gathers in the CPU's order) --
+    pool_geoms = [("k3_s2_p1", (2, 3, 9, 11), (3, 3), (2, 2), (1, 1)), ("k2_s2", (1, 4, 8, 6), (2, 2), (2, 2), (0, 0)),
+                  ("k3_s1_p1", (1, 2, 7, 7), (3, 3), (1, 1), (1, 1)), ("k3x2_s2x1_p1x0", (2, 2, 10, 5), (3, 2), (2, 1), (1, 0))]
+    for tag, xs, k, st, pd in pool_geoms:
+        oshape = (xs[0], xs[1], fo.conv_out_size(xs[2], k[0], st[0], pd[0]), fo.conv_out_size(xs[3], k[1], st[1], pd[1]))
+        pat = {"kernel": list(k), "stride": list(st), "padding": list(pd)}
+        for dt, dtag in ((F32, "f32"), (BF16, "bf16")):
+            if dt == BF16 and tag != "k3_s2_p1":
+                continue
+            cases.append(Case(f"max_pool2d_select_{dtag}_{tag}", "max_pool2d_select_internal", dt,
+                              [rnd(xs, dt), rnd(xs, dt)], dict(pat),
+                              lambda g, x, k=k, st=st, pd=pd, dt=dt: fo.max_pool2d_select(g, x, k, st, pd, dt), exact=True))
+            cases.append(Case(f"max_pool2d_grad_{dtag}_{tag}", "max_pool2d_grad_internal", dt,
+                              [rnd(oshape, dt), rnd(xs, dt)], dict(pat, input_shape=list(xs)),
+                              lambda dy, x, k=k, st=st, pd=pd, dt=dt: fo.max_pool2d_grad(dy, x, k, st, pd, dt), exact=True))
+            cases.append(Case(f"avg_pool2d_grad_{dtag}_{tag}", "avg_pool2d_grad_internal", dt,
+                              [rnd(oshape, dt)], dict(pat, input_shape=list(xs)),
+                              lambda dy, xs=xs, k=k, st=st, pd=pd, dt=dt: fo.avg_pool2d_grad(dy, xs, k, st, pd, dt), exact=True))
+    tie_x = np.array([[[[5, 5, 1, 2], [5, 5, 2, 2], [1, 1, 3, 3], [0, 1, 3, 3]]]], dtype=np.float32)
+    cases.append(Case("max_pool2d_grad_f32_ties_overlap", "max_pool2d_grad_internal", F32,
+                      [rnd((1, 1, 3, 3)), tie_x], {"kernel": [2, 2], "stride": [1, 1], "padding": [0, 0], "input_shape": [1, 1, 4, 4]},
+                      lambda dy, x: fo.max_pool2d_grad(dy, x, (2, 2), (1, 1), (0, 0), F32), exact=True))
+    conv_geoms = [("3x3_s1_p1", (2, 3, 9, 9), (4, 3, 3, 3), (1, 1), (1, 1), 1, F32),
+                  ("7x7_s2_p3", (1, 3, 20, 20), (8, 3, 7, 7), (2, 2), (3, 3), 1, F32),
+                  ("groups2", (2, 4, 6, 7), (6, 2, 3, 2), (1, 2), (0, 1), 2, F32),
+                  ("bf16_3x3", (1, 4, 8, 8), (5, 4, 3, 3), (1, 1), (1, 1), 1, BF16)]
+    for tag, xs, ws, st, pd, groups, dt in conv_geoms:
+        oshape = (xs[0], ws[0], fo.conv_out_size(xs[2], ws[2], st[0], pd[0]), fo.conv_out_size(xs[3], ws[3], st[1], pd[1]))
+        cat = {"stride": list(st), "padding": list(pd), "groups": groups}
+        cases.append(Case(f"conv2d_grad_input_{tag}", "conv2d_grad_input_internal", dt,
+                          [rnd(oshape, dt), rnd(ws, dt, scale=0.3)], dict(cat, input_shape=list(xs)),
+                          lambda dy, w, xs=xs, st=st, pd=pd, groups=groups, dt=dt: fo.conv2d_grad_input(dy, w, xs, st, pd, groups, dt),
+                          exact=True))
+        cases.append(Case(f"conv2d_grad_filter_{tag}", "conv2d_grad_filter_internal", dt,
+                          [rnd(xs, dt), rnd(oshape, dt, scale=0.3)], dict(cat, filter_shape=list(ws)),
+                          lambda x, dy, ws=ws, st=st, pd=pd, groups=groups, dt=dt: fo.conv2d_grad_filter(x, dy, ws, st, pd, groups, dt),
+                          exact=True))
     return cases
 
 
 CASES = build_cases()
 CASES_BY_NAME = {c.name: c for c in CASES}
+# Cases whose executable plan (as the reference derives it for backend "cuda") is committed under
+# tests/golden/plans/case_<name>.plan and run through the plan executor.
+PLAN_CASES = ["max_pool2d_select_f32_k3_s2_p1", "max_pool2d_grad_f32_k3_s2_p1", "max_pool2d_grad_bf16_k3_s2_p1",
+              "avg_pool2d_grad_f32_k3x2_s2x1_p1x0", "conv2d_grad_input_groups2", "conv2d_grad_input_3x3_s1_p1",
+              "conv2d_grad_filter_7x7_s2_p3", "conv2d_grad_filter_bf16_3x3"]

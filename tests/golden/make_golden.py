@@ -1,7 +1,7 @@
 """Generates tests/golden/ref_cpu_cases.npz: outputs of the UNMODIFIED reference CPU backend
 (oracle/_ref, built by oracle/build_ref.sh from the reference's own sources) for every
 reference-native case of tests/cases.py, plus a checksum of each case's inputs so that a drift
-of the seeded generator is detected.  Run where the reference is present:
+of the seeded generator is detected; and tests/golden/plans/case_<name>.plan for cases.PLAN_CASES.  Run where the reference is present:
 
     python tests/golden/make_golden.py
 """
@@ -42,6 +42,14 @@ def main():
     path = os.path.join(ROOT, "tests", "golden", "ref_cpu_cases.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes")
+    # executable plans of a few single-op graphs, derived by the reference for backend "cuda" with
+    # this repository's plugin loaded (backend_lowering must find the kernel registrations)
+    ref_runtime.load_b200_backend()
+    for name in cases.PLAN_CASES:
+        text = ref_runtime.plan_text(cases.CASES_BY_NAME[name].ir_text("cuda"), "cuda")
+        with open(os.path.join(ROOT, "tests", "golden", "plans", "case_" + name + ".plan"), "w") as f:
+            f.write(text)
+        print("plan", name)
 
 
 if __name__ == "__main__":

@@ -51,6 +51,21 @@ def run_case(case, allow_tf32=False):
         x = ins[0]
         capi.avg_pool2d(ptr[0], out.ptr, *x.shape, at["kernel"][0], at["kernel"][1], at["stride"][0],
                         at["stride"][1], at["padding"][0], at["padding"][1], dt)
+    elif op in ("max_pool2d_select_internal", "max_pool2d_grad_internal"):
+        xs = ins[1].shape
+        fn = capi.max_pool2d_select if op == "max_pool2d_select_internal" else capi.max_pool2d_grad
+        fn(ptr[0], ptr[1], out.ptr, *xs, at["kernel"][0], at["kernel"][1], at["stride"][0], at["stride"][1],
+           at["padding"][0], at["padding"][1], dt)
+    elif op == "avg_pool2d_grad_internal":
+        capi.avg_pool2d_grad(ptr[0], out.ptr, *at["input_shape"], at["kernel"][0], at["kernel"][1], at["stride"][0],
+                             at["stride"][1], at["padding"][0], at["padding"][1], dt)
+    elif op in ("conv2d_grad_input_internal", "conv2d_grad_filter_internal"):
+        xs = at["input_shape"] if op == "conv2d_grad_input_internal" else ins[0].shape
+        ws = ins[1].shape if op == "conv2d_grad_input_internal" else at["filter_shape"]
+        p = capi.Conv2dParams(xs[0], xs[1], xs[2], xs[3], ws[0], ws[2], ws[3], at["stride"][0], at["stride"][1],
+                              at["padding"][0], at["padding"][1], at["groups"])
+        fn = capi.conv2d_grad_input if op == "conv2d_grad_input_internal" else capi.conv2d_grad_filter
+        fn(ptr[0], ptr[1], out.ptr, p, dt)
     elif op == "heaviside_surrogate":
         capi.fused_elementwise(ptr, out.ptr, numel, dt, [op])
     elif op == "gather":

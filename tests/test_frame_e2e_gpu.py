@@ -76,12 +76,15 @@ def test_reference_nn_module_runs_on_cuda_without_fallback(spec):
 
 
 NEW_OP_CASES = [c for c in __import__("cases").CASES
-                if c.op in ("avg_pool2d", "heaviside_surrogate", "gather", "scatter_add", "gather_grad_internal")]
+                if c.op in ("avg_pool2d", "heaviside_surrogate", "gather", "scatter_add", "gather_grad_internal",
+                            "max_pool2d_select_internal", "max_pool2d_grad_internal", "avg_pool2d_grad_internal",
+                            "conv2d_grad_input_internal", "conv2d_grad_filter_internal")]
 
 
 @pytest.mark.parametrize("case", NEW_OP_CASES, ids=lambda c: c.name)
 def test_pool_step_and_index_ops_through_the_reference_api(case):
-    """avg_pool2d, heaviside_surrogate, gather, scatter_add and gather_grad_internal compiled by the
+    """avg_pool2d, heaviside_surrogate, gather, scatter_add, gather_grad_internal and the pooling /
+    convolution gradient internals compiled by the
     reference's runtime::compile for backend "cuda": no fallback, same numbers as its CPU backend."""
     cpu = ref_runtime.Compiled(case.ir_text("cpu"), "cpu")
     (exp,) = cpu.run(case.inputs)

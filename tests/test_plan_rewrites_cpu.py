@@ -91,3 +91,18 @@ def test_pool_and_index_ops_decode_and_opt_out_of_graph_replay_checks():
     h = capi.c_void_p()
     rc = lib.fb200_plan_describe(bad.encode(), 1, capi.byref(h))
     assert rc == 1 and b"alpha" in lib.fb200_last_error()
+
+
+def test_gradient_internals_decode_as_single_steps():
+    import sys
+    sys.path.insert(0, HERE)
+    import cases
+    for name in cases.PLAN_CASES:
+        names, launches = runtime.describe_plan(_golden("case_" + name))
+        assert names == [cases.CASES_BY_NAME[name].op] and launches == 1, name
+    # a malformed attribute list is rejected with the op's name
+    text = _golden("case_conv2d_grad_input_groups2").replace("attr stride int64_array [1, 2]", "attr stride int64_array [1]")
+    lib = capi.load()
+    h = capi.c_void_p()
+    rc = lib.fb200_plan_describe(text.encode(), 1, capi.byref(h))
+    assert rc == 1 and b"conv2d_grad_input_internal" in lib.fb200_last_error()

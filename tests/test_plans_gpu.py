@@ -130,3 +130,19 @@ def test_pipelined_host_runs_deliver_each_runs_own_result():
         for got, exp in zip(outs, expected):
             assert np.array_equal(got.view(np.uint8), exp.view(np.uint8)), round_
     plan.close()
+
+
+import cases as _cases  # noqa: E402
+
+
+@pytest.mark.parametrize("name", _cases.PLAN_CASES)
+def test_gradient_internals_through_the_plan_executor(name):
+    """Pooling / convolution gradient internals as one-step plans (the plans the reference derives for
+    backend "cuda"): bit-identical to the reference CPU backend's golden output."""
+    case = _cases.CASES_BY_NAME[name]
+    gold = np.load(os.path.join(HERE, "golden", "ref_cpu_cases.npz"))[name]
+    plan = runtime.CompiledPlan(_plan_text("case_" + name), 0)
+    (got,) = plan.run_host(case.inputs)
+    assert capi.kernel_status(0) == 0
+    assert np.array_equal(np.asarray(got).view(np.uint8), np.asarray(gold).view(np.uint8)), name
+    plan.close()
