@@ -97,6 +97,8 @@ SIGNATURES = {
     "fb200_avg_pool2d_grad": (c_int, [_P, _P] + [c_int64] * 10 + [c_int, _P]),
     "fb200_conv2d_grad_input": (c_int, [_P, _P, _P, POINTER(Conv2dParams), c_int, _P]),
     "fb200_conv2d_grad_filter": (c_int, [_P, _P, _P, POINTER(Conv2dParams), c_int, _P]),
+    "fb200_rfft": (c_int, [_P, _P, c_int64, c_int64, c_int, _P]),
+    "fb200_irfft": (c_int, [_P, _P, c_int64, c_int64, c_int, _P]),
     "fb200_gather": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int, c_int, _P]),
     "fb200_scatter_add": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int, c_int, _P]),
     "fb200_softmax": (c_int, [_P, _P, c_int64, c_int64, c_int, _P]),
@@ -286,6 +288,14 @@ def conv2d_grad_input(dy, w, dx, params: Conv2dParams, dtype, stream=None):
 
 def conv2d_grad_filter(x, dy, dw, params: Conv2dParams, dtype, stream=None):
     check(load().fb200_conv2d_grad_filter(x, dy, dw, byref(params), dtype, stream))
+
+
+def rfft(x, out, rows, n, dtype, stream=None):
+    check(load().fb200_rfft(x, out, rows, n, dtype, stream))
+
+
+def irfft(z, out, rows, n, dtype, stream=None):
+    check(load().fb200_irfft(z, out, rows, n, dtype, stream))
 
 
 def gather(x, indices, out, n, f, k, dtype, index_dtype, stream=None):

@@ -31,7 +31,7 @@ namespace fb200 {
 enum class Kind {
   kMatmul, kConv2d, kConv1d, kMaxPool, kChain, kBiasAdd, kSoftmax, kLayerNorm, kScan, kMambaScan,
   kTranspose, kSlice, kConcat, kSum, kCopy, kAlias, kConstant, kSkip, kAttentionFan, kDwConvTimeMajor, kAvgPool, kGather, kScatterAdd,
-  kPoolSelect, kMaxPoolGrad, kAvgPoolGrad, kConvGradInput, kConvGradFilter
+  kPoolSelect, kMaxPoolGrad, kAvgPoolGrad, kConvGradInput, kConvGradFilter, kRfft, kIrfft
 };
 
 struct SlotInfo {
@@ -343,6 +343,13 @@ static int decode_step(fb200_plan* p, Step& s) {
       return set_error(FB200_INVALID_ARGUMENT, "op '%s': malformed attributes", op.c_str());
     }
     s.iv = {sv[0], sv[1], pv[0], pv[1], gv[0]};
+  } else if (op == "rfft") {
+    s.kind = Kind::kRfft;
+  } else if (op == "irfft") {
+    s.kind = Kind::kIrfft;
+    const Attr* n = need("n");
+    if (!n) return FB200_INVALID_ARGUMENT;
+    s.iv = {parse_int_list(n->text).at(0)};
   } else if (op == "gather") {
     s.kind = Kind::kGather;
     p->graph_enabled = false;   // the index check synchronises the stream
@@ -1163,6 +1170,23 @@ static int run_step(fb200_plan* p, Step& s, const void* const* inputs, void* con
       fb200_conv2d_params cp{xd[0], xd[1], xd[2], xd[3], wd[0], wd[2], wd[3], s.iv[0], s.iv[1], s.iv[2], s.iv[3], s.iv[4]};
       return wrt_input ? fb200_conv2d_grad_input(in_ptr(0), in_ptr(1), out, &cp, os.dtype, stream)
                        : fb200_conv2d_grad_filter(in_ptr(0), in_ptr(1), out, &cp, os.dtype, stream);
+    }
+    case Kind::kRfft: {
+      const auto& xd = in_slot(0).dims;
+      if (xd.empty() || xd.back() < 2) return set_error(FB200_INVALID_ARGUMENT, "op 'rfft' requires the last dimension (n) to be >= 2");
+      int64_t rows = 1;
+      for (size_t d = 0; d + 1 < xd.size(); ++d) rows *= xd[d];
+      return fb200_rfft(in_ptr(0), out, rows, xd.back(), os.dtype, stream);
+    }
+    case Kind::kIrfft: {
+      const auto& zd = in_slot(0).dims;
+      const int64_t n = s.iv[0];
+      if (zd.size() < 2 || zd.back() != 2 || zd[zd.size() - 2] != n / 2 + 1) {
+        return set_error(FB200_INVALID_ARGUMENT, "op 'irfft' requires z [..., n/2+1, 2] for attribute n=%lld", (long long)n);
+      }
+      int64_t rows = 1;
+      for (size_t d = 0; d + 2 < zd.size(); ++d) rows *= zd[d];
+      return fb200_irfft(in_ptr(0), out, rows, n, os.dtype, stream);
     }
     case Kind::kGather: {
       if (s.in.size() != 2 || in_slot(0).dims.size() != 2 || in_slot(1).dims.size() != 1) {

@@ -337,6 +337,36 @@ Status conv2d_grad(KernelContext& ctx, const char* op, bool wrt_input) {
 Status conv2d_grad_input_internal(KernelContext& ctx) { return conv2d_grad(ctx, "conv2d_grad_input_internal", true); }
 Status conv2d_grad_filter_internal(KernelContext& ctx) { return conv2d_grad(ctx, "conv2d_grad_filter_internal", false); }
 
+// rfft / irfft along the last axis, float32 only as in the reference (src/ops/schemas/fft.cpp).
+Status rfft(KernelContext& ctx) {
+  FRAME_RETURN_IF_ERROR(arity(ctx, "rfft", 1, 1));
+  const Tensor& x = ctx.inputs[0];
+  const size_t rank = x.shape().rank();
+  if (rank < 1 || x.shape().dim(rank - 1) < 2) {
+    return Status::make(ErrorCode::kInvalidArgument, "op 'rfft' cuda kernel requires rank >= 1 and n >= 2");
+  }
+  const int64_t n = x.shape().dim(rank - 1);
+  const int64_t rows = n > 0 ? x.numel() / n : 0;
+  return frame_b200::to_status(
+      fb200_rfft(x.raw_data(), ctx.outputs[0].raw_data(), rows, n, dtype_of(x), stream_of(ctx)), "rfft");
+}
+
+Status irfft(KernelContext& ctx) {
+  FRAME_RETURN_IF_ERROR(arity(ctx, "irfft", 1, 1));
+  const auto* n = attr<int64_t>(ctx, "n");
+  if (n == nullptr) return missing("irfft", "n");
+  const Tensor& z = ctx.inputs[0];
+  const size_t rank = z.shape().rank();
+  if (rank < 2 || z.shape().dim(rank - 1) != 2 || z.shape().dim(rank - 2) != *n / 2 + 1) {
+    return Status::make(ErrorCode::kInvalidArgument,
+                        "op 'irfft' cuda kernel requires z [..., n/2+1, 2] for attribute n=" + std::to_string(*n));
+  }
+  const int64_t per_row = z.shape().dim(rank - 2) * 2;
+  const int64_t rows = z.numel() / per_row;
+  return frame_b200::to_status(
+      fb200_irfft(z.raw_data(), ctx.outputs[0].raw_data(), rows, *n, dtype_of(z), stream_of(ctx)), "irfft");
+}
+
 // heaviside_surrogate: alpha only shapes the backward graph, but a bad alpha is an error here too
 // (src/backends/cpu/kernels/elementwise.cpp, read_heaviside_alpha).
 Status heaviside_surrogate(KernelContext& ctx) {
@@ -586,6 +616,8 @@ FRAME_REGISTER_KERNEL("conv2d", "cuda", &conv2d);
 FRAME_REGISTER_KERNEL("conv1d", "cuda", &conv1d);
 FRAME_REGISTER_KERNEL("max_pool2d", "cuda", &max_pool2d);
 FRAME_REGISTER_KERNEL("avg_pool2d", "cuda", &avg_pool2d);
+FRAME_REGISTER_KERNEL("rfft", "cuda", &rfft);
+FRAME_REGISTER_KERNEL("irfft", "cuda", &irfft);
 FRAME_REGISTER_KERNEL("max_pool2d_select_internal", "cuda", &max_pool2d_select_internal);
 FRAME_REGISTER_KERNEL("max_pool2d_grad_internal", "cuda", &max_pool2d_grad_internal);
 FRAME_REGISTER_KERNEL("avg_pool2d_grad_internal", "cuda", &avg_pool2d_grad_internal);

@@ -250,6 +250,15 @@ FB200_API int fb200_conv2d_grad_input(const void* dy, const void* w, void* dx,
                                       const fb200_conv2d_params* p, int dtype, fb200_stream stream);
 FB200_API int fb200_conv2d_grad_filter(const void* x, const void* dy, void* dw,
                                        const fb200_conv2d_params* p, int dtype, fb200_stream stream);
+/* rfft / irfft along the last axis, float32 only (src/ops/schemas/fft.cpp:8-9; replace the cuFFT
+ * R2C / C2R plans of src/backends/cuda/kernels/fft.cpp).  rfft: x [rows, n] -> out [rows, n/2+1, 2]
+ * (interleaved re/im, forward sign, unscaled).  irfft: z [rows, n/2+1, 2] -> out [rows, n], scaled by
+ * 1/n; the imaginary parts of the DC and (even n) Nyquist terms are ignored.  Direct O(n^2)
+ * transforms accumulated in double precision and rounded once. */
+FB200_API int fb200_rfft(const void* x, void* out, int64_t rows, int64_t n, int dtype,
+                         fb200_stream stream);
+FB200_API int fb200_irfft(const void* z, void* out, int64_t rows, int64_t n, int dtype,
+                          fb200_stream stream);
 /* gather along axis 0: out[k, :] = x[indices[k], :], x [n, f], indices [k] of int32 / int64
  * (src/ops/schemas/gather.cpp:86-118; replaces src/backends/cuda/kernels/gather.cu).  An index
  * outside [0, n) is an error that names the value, found like the reference does by looking at the

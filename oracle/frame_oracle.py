@@ -387,6 +387,42 @@ def conv2d_grad_filter(x, dy, filter_shape, stride, padding, groups: int = 1, dt
     return from_accum(acc, dtype)
 
 
+def rfft(x):
+    """x[..., n] (float32) -> [..., n//2+1, 2], forward sign, unscaled (src/ops/schemas/fft.cpp:8).
+    The reference CPU kernel calls pocketfft r2c in float32; this restatement evaluates the DFT sum
+    itself in float64 and rounds once, pinned by the reference's known-answer tests
+    (tests/cpp/ops/test_op_fft.cpp:287-395)."""
+    xv = np.asarray(x, dtype=np.float64)
+    n = xv.shape[-1]
+    k = n // 2 + 1
+    idx = (np.arange(n)[:, None] * np.arange(k)[None, :]) % n
+    ang = -2.0 * np.pi * idx / n
+    re = xv @ np.cos(ang)
+    im = xv @ np.sin(ang)
+    return np.stack([re, im], axis=-1).astype(F32)
+
+
+def irfft(z, n: int):
+    """z[..., n//2+1, 2] -> [..., n], scaled by 1/n; imaginary parts of the DC and (even n) Nyquist
+    bins are ignored, as a c2r transform does (src/ops/schemas/fft.cpp:9; known answers
+    tests/cpp/ops/test_op_fft.cpp:477-570)."""
+    zv = np.asarray(z, dtype=np.float64)
+    k = n // 2 + 1
+    assert zv.shape[-1] == 2 and zv.shape[-2] == k
+    re, im = zv[..., 0], zv[..., 1]
+    weight = np.full(k, 2.0)
+    weight[0] = 1.0
+    im = im.copy()
+    im[..., 0] = 0.0
+    if n % 2 == 0:
+        weight[k - 1] = 1.0
+        im[..., k - 1] = 0.0
+    idx = (np.arange(k)[:, None] * np.arange(n)[None, :]) % n
+    ang = 2.0 * np.pi * idx / n
+    out = (re * weight) @ np.cos(ang) - (im * weight) @ np.sin(ang)
+    return (out / n).astype(F32)
+
+
 def gather(x, indices):
     """out[k, :] = x[indices[k], :] along axis 0 (src/ops/schemas/gather.cpp:86-118); an index
     outside [0, N) is an error."""

@@ -32,7 +32,8 @@ class Case:
     attrs: Dict[str, object] = field(default_factory=dict)
     oracle: Callable[..., np.ndarray] = None
     exact: bool = False       # integer/indexing work or fp32 without libm: bit-exact expected
-    new_op: bool = False      # not in the reference (parity unpinned by the reference)
+    new_op: bool = False      # no golden from the reference CPU backend: an op that is not in the reference, or
+                              # one whose CPU kernel needs a library that is absent here (rfft / irfft: pocketfft)
     in_dtypes: List[int] = None   # dtype code per input when they differ from `dtype` (indices)
 
     def expected(self) -> np.ndarray:
@@ -275,6 +276,16 @@ def build_cases() -> List[Case]:
                           [rnd(xs, dt), rnd(oshape, dt, scale=0.3)], dict(cat, filter_shape=list(ws)),
                           lambda x, dy, ws=ws, st=st, pd=pd, groups=groups, dt=dt: fo.conv2d_grad_filter(x, dy, ws, st, pd, groups, dt),
                           exact=True))
+
+    # ---- rfft / irfft (float32; the reference CPU kernel needs pocketfft, which is not in its tree:
+    #      pinned by the reference's known-answer tests instead, tests/test_fft_cpu.py) ----------------
+    for tag, shape in (("n4", (4,)), ("n5", (5,)), ("2x6", (2, 6)), ("3x64", (3, 64)), ("2x5x243", (2, 5, 243)),
+                       ("7x1000", (7, 1000))):
+        n = shape[-1]
+        cases.append(Case(f"rfft_f32_{tag}", "rfft", F32, [rnd(shape)], {}, lambda x: fo.rfft(x), new_op=True))
+        zshape = shape[:-1] + (n // 2 + 1, 2)
+        cases.append(Case(f"irfft_f32_{tag}", "irfft", F32, [rnd(zshape)], {"n": n},
+                          lambda z, n=n: fo.irfft(z, n), new_op=True))
     return cases
 
 

@@ -66,6 +66,12 @@ def run_case(case, allow_tf32=False):
                               at["padding"][0], at["padding"][1], at["groups"])
         fn = capi.conv2d_grad_input if op == "conv2d_grad_input_internal" else capi.conv2d_grad_filter
         fn(ptr[0], ptr[1], out.ptr, p, dt)
+    elif op == "rfft":
+        n = ins[0].shape[-1]
+        capi.rfft(ptr[0], out.ptr, ins[0].size // n, n, dt)
+    elif op == "irfft":
+        n = at["n"]
+        capi.irfft(ptr[0], out.ptr, ins[0].size // (2 * (n // 2 + 1)), n, dt)
     elif op == "heaviside_surrogate":
         capi.fused_elementwise(ptr, out.ptr, numel, dt, [op])
     elif op == "gather":

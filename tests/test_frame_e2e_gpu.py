@@ -95,3 +95,18 @@ def test_pool_step_and_index_ops_through_the_reference_api(case):
     else:
         assert fo.all_close(got, exp, case.dtype), (case.name, fo.max_err(got, exp, case.dtype))
     assert ref_runtime.fallback_count(case.op, "cuda") == 0
+
+
+FFT_CASES = [c for c in __import__("cases").CASES if c.op in ("rfft", "irfft")]
+
+
+@pytest.mark.parametrize("case", FFT_CASES, ids=lambda c: c.name)
+def test_rfft_irfft_through_the_reference_api(case):
+    """rfft / irfft compiled by the reference's runtime::compile for backend "cuda" (its shape
+    inference and attribute checks, this repository's kernels): no fallback; compared with the oracle,
+    because the reference's CPU kernel needs pocketfft, which its tree does not contain."""
+    gpu = ref_runtime.Compiled(case.ir_text("cuda"), "cuda")
+    (got,) = gpu.run(case.inputs)
+    exp = case.expected()
+    assert fo.all_close(got, exp, case.dtype, rtol=1e-5, atol=1e-5), (case.name, fo.max_err(got, exp, case.dtype))
+    assert ref_runtime.fallback_count(case.op, "cuda") == 0
