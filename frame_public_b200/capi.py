@@ -24,7 +24,8 @@ NP_STORAGE = {F32: np.float32, F64: np.float64, F16: np.uint16, BF16: np.uint16,
               I16: np.int16, I32: np.int32, I64: np.int64, U8: np.uint8, BOOL: np.uint8}
 
 EW = {"add": 1, "mul": 2, "relu": 3, "square": 4, "sigmoid": 5, "tanh": 6, "rsqrt": 7,
-      "gelu": 8, "silu": 9, "softplus": 10, "exp": 11, "heaviside_surrogate": 12}
+      "gelu": 8, "silu": 9, "softplus": 10, "exp": 11, "heaviside_surrogate": 12,
+      "relu_grad_internal": 13}
 EW_ARITY = {"add": 2, "mul": 2}
 OPERAND_FULL, OPERAND_COL, OPERAND_ROW = 0, 1, 2
 H2D, D2H, D2D = 1, 2, 3
@@ -97,6 +98,10 @@ SIGNATURES = {
     "fb200_avg_pool2d_grad": (c_int, [_P, _P] + [c_int64] * 10 + [c_int, _P]),
     "fb200_conv2d_grad_input": (c_int, [_P, _P, _P, POINTER(Conv2dParams), c_int, _P]),
     "fb200_conv2d_grad_filter": (c_int, [_P, _P, _P, POINTER(Conv2dParams), c_int, _P]),
+    "fb200_matmul_grad_lhs": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int, c_int, _P]),
+    "fb200_matmul_grad_rhs": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int, c_int, _P]),
+    "fb200_mse_loss": (c_int, [_P, _P, _P, c_int64, c_int, _P]),
+    "fb200_mse_loss_grad": (c_int, [_P, _P, _P, _P, c_int64, c_int, _P]),
     "fb200_rfft": (c_int, [_P, _P, c_int64, c_int64, c_int, _P]),
     "fb200_irfft": (c_int, [_P, _P, c_int64, c_int64, c_int, _P]),
     "fb200_gather": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int, c_int, _P]),
@@ -288,6 +293,22 @@ def conv2d_grad_input(dy, w, dx, params: Conv2dParams, dtype, stream=None):
 
 def conv2d_grad_filter(x, dy, dw, params: Conv2dParams, dtype, stream=None):
     check(load().fb200_conv2d_grad_filter(x, dy, dw, byref(params), dtype, stream))
+
+
+def matmul_grad_lhs(gy, b, ga, m, n, k, dtype, allow_tf32=False, stream=None):
+    check(load().fb200_matmul_grad_lhs(gy, b, ga, m, n, k, dtype, 1 if allow_tf32 else 0, stream))
+
+
+def matmul_grad_rhs(a, gy, gb, m, n, k, dtype, allow_tf32=False, stream=None):
+    check(load().fb200_matmul_grad_rhs(a, gy, gb, m, n, k, dtype, 1 if allow_tf32 else 0, stream))
+
+
+def mse_loss(pred, target, out, numel, dtype, stream=None):
+    check(load().fb200_mse_loss(pred, target, out, numel, dtype, stream))
+
+
+def mse_loss_grad(pred, target, gy, gpred, numel, dtype, stream=None):
+    check(load().fb200_mse_loss_grad(pred, target, gy, gpred, numel, dtype, stream))
 
 
 def rfft(x, out, rows, n, dtype, stream=None):

@@ -253,6 +253,34 @@ def mamba_block(batch: int = 16, seq: int = 2048, d_model: int = 768, expand: in
 # where the reference is present (tests/golden/make_workload_golden.py): (golden name, module kind,
 # builder arguments, DTypeCode).  transformer: batch, seq, embed, heads, ffn, with_bias; mamba: batch,
 # steps, channels, kernel.
+def train_mlp_forward(batch: int = 16, d_in: int = 32, hidden: int = 24, d_out: int = 8, dtype: int = F32,
+                      backend: str = "cpu"):
+    """Forward graph of a two-layer MLP with an MSE loss, as IR text, and its seeded inputs
+    (x, w1, b1 as a full-shape tensor, w2, target).  The reference's compiler::build_backward_graph
+    turns it into the training graph [loss, grad w1, grad b1, grad w2]: mse_loss_grad_internal,
+    matmul_grad_lhs/rhs_internal and relu_grad_internal beside the forward ops."""
+    name = irtext.DTYPE_NAMES[dtype]
+    g = irtext.IrGraph(backend)
+    x = g.input(name, (batch, d_in))
+    w1 = g.input(name, (d_in, hidden))
+    b1 = g.input(name, (batch, hidden))
+    w2 = g.input(name, (hidden, d_out))
+    t = g.input(name, (batch, d_out))
+    h = g.node("matmul", [x, w1], {}, name, (batch, hidden))
+    h = g.node("add", [h, b1], {}, name, (batch, hidden))
+    h = g.node("relu", [h], {}, name, (batch, hidden))
+    y = g.node("matmul", [h, w2], {}, name, (batch, d_out))
+    g.output(g.node("mse_loss", [y, t], {}, name, ()))
+    rng = np.random.default_rng(23)
+    ins = [_store(rng.standard_normal(s).astype(np.float32) * sc, dtype)
+           for s, sc in (((batch, d_in), 1.0), ((d_in, hidden), 0.3), ((batch, hidden), 0.1), ((hidden, d_out), 0.3),
+                         ((batch, d_out), 1.0))]
+    return g.text(), ins
+
+
+TRAIN_WRT = [1, 2, 3]   # gradients w.r.t. w1, b1, w2
+
+
 NN_GRAPHS = [
     ("nn_transformer_bf16_b2_s128_e128_h2", "transformer", (2, 128, 128, 2, 256, True), BF16),
     ("nn_transformer_f32_b2_s16_e32_h2", "transformer", (2, 16, 32, 2, 64, True), F32),

@@ -157,10 +157,11 @@ __device__ __forceinline__ float ew_unary(int op, float x) {
 }
 
 __device__ __forceinline__ float ew_binary(int op, float a, float b) {
-  return op == FB200_EW_ADD ? a + b : a * b;
+  return op == FB200_EW_ADD ? a + b : (op == FB200_EW_MUL ? a * b : (a > 0.0f ? b : 0.0f));
 }
 
-inline bool ew_is_binary(int op) { return op == FB200_EW_ADD || op == FB200_EW_MUL; }
-inline bool ew_is_known(int op) { return op >= FB200_EW_ADD && op <= FB200_EW_HEAVISIDE; }
+inline bool ew_is_binary(int op) { return op == FB200_EW_ADD || op == FB200_EW_MUL || op == FB200_EW_RELU_GRAD; }
+inline bool ew_commutes(int op) { return op == FB200_EW_ADD || op == FB200_EW_MUL; }
+inline bool ew_is_known(int op) { return op >= FB200_EW_ADD && op <= FB200_EW_RELU_GRAD; }
 
 }  // namespace fb200

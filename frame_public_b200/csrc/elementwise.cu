@@ -59,9 +59,12 @@ fused_chain_kernel(ChainDesc d, T* __restrict__ out, int64_t n_vec, int64_t nume
         if (op == FB200_EW_ADD) {
 #pragma unroll
           for (int e = 0; e < W; ++e) cur[e] = round_through<T>(cur[e] + rhs[e]);
-        } else {
+        } else if (op == FB200_EW_MUL) {
 #pragma unroll
           for (int e = 0; e < W; ++e) cur[e] = round_through<T>(cur[e] * rhs[e]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < W; ++e) cur[e] = round_through<T>(ew_binary(op, cur[e], rhs[e]));
         }
       } else {
         ew_unary_vec<T, W>(op, cur);

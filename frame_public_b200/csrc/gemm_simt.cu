@@ -13,10 +13,15 @@
 
 namespace fb200 {
 
+// Element strides of the two operands: A[i, p] = A[i*a_row + p*a_k], B[p, j] = B[p*b_k + j*b_col].
+// The plain product has (K, 1, N, 1); the gradient forms read one operand transposed in place
+// (src/backends/cpu/kernels/matmul.cpp:187-232, :289-330) with the same p-increasing accumulation.
+struct GemmStrides { int64_t a_row, a_k, b_k, b_col; };
+
 template <typename T, int BM, int BN, int BK, int TM, int TN>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN))
 gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict__ C, int64_t M,
-                 int64_t N, int64_t K, EpilogueDev epi) {
+                 int64_t N, int64_t K, GemmStrides st, EpilogueDev epi) {
   constexpr int THREADS = (BM / TM) * (BN / TN);
   __shared__ float As[BK][BM + 4];
   __shared__ float Bs[BK][BN + 4];
@@ -38,12 +43,12 @@ gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict
       for (int e = tid; e < BM * BK; e += THREADS) {
         const int r = e / BK, kk = e % BK;
         const int64_t gm = m0 + r, gk = k0 + kk;
-        As[kk][r] = (gm < M && gk < K) ? to_f32(A[gm * K + gk]) : 0.0f;
+        As[kk][r] = (gm < M && gk < K) ? to_f32(A[gm * st.a_row + gk * st.a_k]) : 0.0f;
       }
       for (int e = tid; e < BK * BN; e += THREADS) {
         const int kk = e / BN, c = e % BN;
         const int64_t gk = k0 + kk, gn = n0 + c;
-        Bs[kk][c] = (gk < K && gn < N) ? to_f32(B[gk * N + gn]) : 0.0f;
+        Bs[kk][c] = (gk < K && gn < N) ? to_f32(B[gk * st.b_k + gn * st.b_col]) : 0.0f;
       }
       __syncthreads();
       const int klen = static_cast<int>(K - k0 < BK ? K - k0 : BK);
@@ -77,32 +82,40 @@ gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict
 
 template <typename T>
 static int launch_simt(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
-                       const EpilogueDev& epi, cudaStream_t s) {
+                       const GemmStrides& st, const EpilogueDev& epi, cudaStream_t s) {
   const T* ap = static_cast<const T*>(a);
   const T* bp = static_cast<const T*>(b);
   T* cp = static_cast<T*>(c);
   const int64_t big_tiles = ((m + 127) / 128) * ((n + 127) / 128);
   if (big_tiles >= kNumSMs) {
     const int grid = static_cast<int>(big_tiles < int64_t(kNumSMs) * 4 ? big_tiles : int64_t(kNumSMs) * 4);
-    gemm_simt_kernel<T, 128, 128, 16, 8, 8><<<grid, 256, 0, s>>>(ap, bp, cp, m, n, k, epi);
+    gemm_simt_kernel<T, 128, 128, 16, 8, 8><<<grid, 256, 0, s>>>(ap, bp, cp, m, n, k, st, epi);
   } else {
     const int64_t tiles = ((m + 31) / 32) * ((n + 63) / 64);
     const int grid = static_cast<int>(tiles < int64_t(kNumSMs) * 8 ? tiles : int64_t(kNumSMs) * 8);
-    gemm_simt_kernel<T, 32, 64, 32, 2, 4><<<grid, 256, 0, s>>>(ap, bp, cp, m, n, k, epi);
+    gemm_simt_kernel<T, 32, 64, 32, 2, 4><<<grid, 256, 0, s>>>(ap, bp, cp, m, n, k, st, epi);
   }
   return after_launch("gemm_simt_kernel");
 }
 
-int gemm_simt(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int dtype,
-              const EpilogueDev& epi, cudaStream_t s) {
+// C[m, n] = sum_p A[i, p] * B[p, j] with explicit operand strides (see GemmStrides).
+int gemm_simt_strided(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
+                      int64_t a_row, int64_t a_k, int64_t b_k, int64_t b_col, int dtype,
+                      const EpilogueDev& epi, cudaStream_t s) {
+  const GemmStrides st{a_row, a_k, b_k, b_col};
   switch (dtype) {
-    case FB200_F32: return launch_simt<float>(a, b, c, m, n, k, epi, s);
-    case FB200_BF16: return launch_simt<__nv_bfloat16>(a, b, c, m, n, k, epi, s);
-    case FB200_F16: return launch_simt<__half>(a, b, c, m, n, k, epi, s);
+    case FB200_F32: return launch_simt<float>(a, b, c, m, n, k, st, epi, s);
+    case FB200_BF16: return launch_simt<__nv_bfloat16>(a, b, c, m, n, k, st, epi, s);
+    case FB200_F16: return launch_simt<__half>(a, b, c, m, n, k, st, epi, s);
     default:
       return set_error(FB200_INVALID_ARGUMENT,
                        "matmul: dtype code %d is not float32/float16/bfloat16", dtype);
   }
+}
+
+int gemm_simt(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int dtype,
+              const EpilogueDev& epi, cudaStream_t s) {
+  return gemm_simt_strided(a, b, c, m, n, k, k, 1, n, 1, dtype, epi, s);
 }
 
 }  // namespace fb200

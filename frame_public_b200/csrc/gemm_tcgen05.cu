@@ -731,3 +731,72 @@ extern "C" int fb200_ipc_close(int device, void* ptr) {
   FB200_CUDA_OK(cudaIpcCloseMemHandle(ptr));
   return FB200_OK;
 }
+
+// ---- gradients of matmul ------------------------------------------------------------------------
+// matmul_grad_lhs_internal: ga[m, k] = gy[m, n] * b[k, n]^T; matmul_grad_rhs_internal:
+// gb[k, n] = a[m, k]^T * gy[m, n] (src/backends/cpu/kernels/matmul.cpp:187-232, :289-330: fp32
+// accumulation over the contracted index in increasing order, one rounding).  Strict fp32 and
+// shapes TMA cannot address run the SIMT kernel with the transposed operand read in place, in the
+// CPU's order (bit-identical).  Where reduced-precision tensor-core math is allowed (bf16 / f16,
+// fp32 with allow_tf32) the transposed operand is materialised once in a stream-ordered scratch by
+// the tiled transpose kernel (an HBM-bound pass, small beside the product) and the product runs on
+// the tcgen05 GEMM above.
+namespace fb200 {
+int gemm_simt_strided(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
+                      int64_t a_row, int64_t a_k, int64_t b_k, int64_t b_col, int dtype,
+                      const EpilogueDev& epi, cudaStream_t s);
+}
+
+static int matmul_grad_check(const char* op, const void* x, const void* y, const void* out, int64_t m,
+                             int64_t n, int64_t k, int dtype, int64_t out_elems, int64_t contracted) {
+  if (m < 0 || n < 0 || k < 0) return set_error(FB200_INVALID_ARGUMENT, "%s: negative dimension", op);
+  if (!is_float_dtype(dtype)) {
+    return set_error(FB200_INVALID_ARGUMENT, "%s: dtype code %d is not float32/float16/bfloat16", op, dtype);
+  }
+  if (out_elems > 0 && (out == nullptr || (contracted > 0 && (x == nullptr || y == nullptr)))) {
+    return set_error(FB200_INVALID_ARGUMENT, "%s: null argument", op);
+  }
+  return FB200_OK;
+}
+
+extern "C" int fb200_matmul_grad_lhs(const void* gy, const void* b, void* ga, int64_t m, int64_t n,
+                                     int64_t k, int dtype, int allow_tf32, fb200_stream stream) {
+  if (int rc = matmul_grad_check("matmul_grad_lhs_internal", gy, b, ga, m, n, k, dtype, m * k, n)) return rc;
+  if (m == 0 || k == 0) return FB200_OK;
+  cudaStream_t s = as_stream(stream);
+  EpilogueDev epi{};
+  // as a plain product: [m, n] x [n, k]
+  if (n > 0 && m * k >= 128 * 128 && tensor_core_eligible(gy, b, ga, m, k, n, dtype, allow_tf32) &&
+      (k * itemsize_of(dtype)) % 16 == 0) {
+    void* bt = nullptr;
+    FB200_CUDA_OK(cudaMallocAsync(&bt, static_cast<size_t>(n) * k * itemsize_of(dtype), s));
+    const int64_t dims[2] = {k, n}, perm[2] = {1, 0};
+    int rc = fb200_transpose(b, bt, 2, dims, perm, itemsize_of(dtype), stream);
+    if (rc == FB200_OK) rc = fb200_matmul(gy, bt, ga, m, k, n, dtype, allow_tf32, nullptr, stream);
+    cudaFreeAsync(bt, s);
+    return rc;
+  }
+  // ga[i, p] = sum_j gy[i*n + j] * b[p*n + j]
+  return gemm_simt_strided(gy, b, ga, m, k, n, n, 1, 1, n, dtype, epi, s);
+}
+
+extern "C" int fb200_matmul_grad_rhs(const void* a, const void* gy, void* gb, int64_t m, int64_t n,
+                                     int64_t k, int dtype, int allow_tf32, fb200_stream stream) {
+  if (int rc = matmul_grad_check("matmul_grad_rhs_internal", a, gy, gb, m, n, k, dtype, k * n, m)) return rc;
+  if (k == 0 || n == 0) return FB200_OK;
+  cudaStream_t s = as_stream(stream);
+  EpilogueDev epi{};
+  // as a plain product: [k, m] x [m, n]
+  if (m > 0 && k * n >= 128 * 128 && tensor_core_eligible(a, gy, gb, k, n, m, dtype, allow_tf32) &&
+      (k * itemsize_of(dtype)) % 16 == 0) {
+    void* at = nullptr;
+    FB200_CUDA_OK(cudaMallocAsync(&at, static_cast<size_t>(m) * k * itemsize_of(dtype), s));
+    const int64_t dims[2] = {m, k}, perm[2] = {1, 0};
+    int rc = fb200_transpose(a, at, 2, dims, perm, itemsize_of(dtype), stream);
+    if (rc == FB200_OK) rc = fb200_matmul(at, gy, gb, k, n, m, dtype, allow_tf32, nullptr, stream);
+    cudaFreeAsync(at, s);
+    return rc;
+  }
+  // gb[p, j] = sum_i a[i*k + p] * gy[i*n + j]
+  return gemm_simt_strided(a, gy, gb, k, n, m, 1, k, n, 1, dtype, epi, s);
+}

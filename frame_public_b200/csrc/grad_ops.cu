@@ -356,3 +356,104 @@ extern "C" int fb200_conv2d_grad_filter(const void* x, const void* dy, void* dw,
   FB200_FLOAT_DISPATCH("conv2d_grad_filter_internal", dtype, run)
   return after_launch("conv2d_grad_filter_kernel");
 }
+
+// ---- mse_loss / mse_loss_grad_internal -----------------------------------------------------------
+// mse_loss(pred, target) = mean((pred - target)^2), a scalar: the CPU reference adds the squares
+// one after the other in fp32 and divides by the element count
+// (src/backends/cpu/kernels/loss.cpp:108-150).  Up to kMseSerialMax elements one thread repeats exactly
+// that (bit-identical; a third of a millisecond at the limit); larger tensors are reduced by one
+// block in double precision (the correctly rounded mean, which the serial fp32 sum itself only
+// approximates), compared with the reference within the tolerance tier.
+// mse_loss_grad_internal(pred, target, gy) = (2*gy/numel) * (pred - target), the coefficient formed
+// first as in the reference (loss.cpp:225-255): elementwise, bit-identical.
+namespace fb200 {
+
+constexpr int64_t kMseSerialMax = 65536;
+
+template <typename T>
+__global__ void mse_loss_serial_kernel(const T* __restrict__ pred, const T* __restrict__ target, T* __restrict__ out,
+                                       int64_t numel) {
+  if (blockIdx.x != 0 || threadIdx.x != 0) return;
+  float acc = 0.0f;
+  for (int64_t i = 0; i < numel; ++i) {
+    const float diff = to_f32(pred[i]) - to_f32(target[i]);
+    acc += diff * diff;
+  }
+  out[0] = from_f32<T>(acc / static_cast<float>(numel));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(1024)
+mse_loss_block_kernel(const T* __restrict__ pred, const T* __restrict__ target, T* __restrict__ out, int64_t numel) {
+  __shared__ double part[32];
+  double acc = 0.0;
+  for (int64_t i = threadIdx.x; i < numel; i += blockDim.x) {
+    const float diff = to_f32(pred[i]) - to_f32(target[i]);
+    acc += static_cast<double>(diff * diff);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    double v = threadIdx.x < (blockDim.x >> 5) ? part[threadIdx.x] : 0.0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (threadIdx.x == 0) out[0] = from_f32<T>(static_cast<float>(v / static_cast<double>(numel)));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+mse_loss_grad_kernel(const T* __restrict__ pred, const T* __restrict__ target, const T* __restrict__ gy,
+                     T* __restrict__ gpred, int64_t numel) {
+  const float coefficient = 2.0f * to_f32(gy[0]) / static_cast<float>(numel);
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < numel; i += stride) {
+    gpred[i] = from_f32<T>(coefficient * (to_f32(pred[i]) - to_f32(target[i])));
+  }
+}
+
+}  // namespace fb200
+
+extern "C" int fb200_mse_loss(const void* pred, const void* target, void* out, int64_t numel, int dtype,
+                              fb200_stream stream) {
+  if (numel < 1) {
+    return set_error(FB200_INVALID_ARGUMENT, "mse_loss: pred/target must have at least 1 element, got numel %lld",
+                     (long long)numel);
+  }
+  if (pred == nullptr || target == nullptr || out == nullptr) return set_error(FB200_INVALID_ARGUMENT, "mse_loss: null argument");
+  cudaStream_t s = as_stream(stream);
+  auto run = [&](auto tag) {
+    using T = decltype(tag);
+    if (numel <= kMseSerialMax) {
+      mse_loss_serial_kernel<T><<<1, 32, 0, s>>>(static_cast<const T*>(pred), static_cast<const T*>(target),
+                                                 static_cast<T*>(out), numel);
+    } else {
+      mse_loss_block_kernel<T><<<1, 1024, 0, s>>>(static_cast<const T*>(pred), static_cast<const T*>(target),
+                                                  static_cast<T*>(out), numel);
+    }
+  };
+  FB200_FLOAT_DISPATCH("mse_loss", dtype, run)
+  return after_launch("mse_loss_kernel");
+}
+
+extern "C" int fb200_mse_loss_grad(const void* pred, const void* target, const void* gy, void* gpred,
+                                   int64_t numel, int dtype, fb200_stream stream) {
+  if (numel < 1) {
+    return set_error(FB200_INVALID_ARGUMENT,
+                     "mse_loss_grad_internal: pred/target must have at least 1 element, got numel %lld", (long long)numel);
+  }
+  if (pred == nullptr || target == nullptr || gy == nullptr || gpred == nullptr) {
+    return set_error(FB200_INVALID_ARGUMENT, "mse_loss_grad_internal: null argument");
+  }
+  cudaStream_t s = as_stream(stream);
+  const int grid = grid_for(numel, 256, 8);
+  auto run = [&](auto tag) {
+    using T = decltype(tag);
+    mse_loss_grad_kernel<T><<<grid, 256, 0, s>>>(static_cast<const T*>(pred), static_cast<const T*>(target),
+                                                 static_cast<const T*>(gy), static_cast<T*>(gpred), numel);
+  };
+  FB200_FLOAT_DISPATCH("mse_loss_grad_internal", dtype, run)
+  return after_launch("mse_loss_grad_kernel");
+}

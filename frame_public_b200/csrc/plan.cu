@@ -31,7 +31,8 @@ namespace fb200 {
 enum class Kind {
   kMatmul, kConv2d, kConv1d, kMaxPool, kChain, kBiasAdd, kSoftmax, kLayerNorm, kScan, kMambaScan,
   kTranspose, kSlice, kConcat, kSum, kCopy, kAlias, kConstant, kSkip, kAttentionFan, kDwConvTimeMajor, kAvgPool, kGather, kScatterAdd,
-  kPoolSelect, kMaxPoolGrad, kAvgPoolGrad, kConvGradInput, kConvGradFilter, kRfft, kIrfft
+  kPoolSelect, kMaxPoolGrad, kAvgPoolGrad, kConvGradInput, kConvGradFilter, kRfft, kIrfft,
+  kMatmulGradLhs, kMatmulGradRhs, kMseLoss, kMseLossGrad
 };
 
 struct SlotInfo {
@@ -174,8 +175,8 @@ static std::string unquote(const std::string& t) {
 
 static int ew_code(const std::string& name) {
   static const char* names[] = {"", "add", "mul", "relu", "square", "sigmoid", "tanh", "rsqrt",
-                                "gelu", "silu", "softplus", "exp", "heaviside_surrogate"};
-  for (int i = 1; i <= 12; ++i) if (name == names[i]) return i;
+                                "gelu", "silu", "softplus", "exp", "heaviside_surrogate", "relu_grad_internal"};
+  for (int i = 1; i <= 13; ++i) if (name == names[i]) return i;
   return 0;
 }
 
@@ -343,6 +344,14 @@ static int decode_step(fb200_plan* p, Step& s) {
       return set_error(FB200_INVALID_ARGUMENT, "op '%s': malformed attributes", op.c_str());
     }
     s.iv = {sv[0], sv[1], pv[0], pv[1], gv[0]};
+  } else if (op == "matmul_grad_lhs_internal") {
+    s.kind = Kind::kMatmulGradLhs;
+  } else if (op == "matmul_grad_rhs_internal") {
+    s.kind = Kind::kMatmulGradRhs;
+  } else if (op == "mse_loss") {
+    s.kind = Kind::kMseLoss;
+  } else if (op == "mse_loss_grad_internal") {
+    s.kind = Kind::kMseLossGrad;
   } else if (op == "rfft") {
     s.kind = Kind::kRfft;
   } else if (op == "irfft") {
@@ -543,7 +552,8 @@ static void optimise(fb200_plan* p) {
       // so a leading binary step may also take it as operand 1.
       size_t lhs_index = 0;
       if (t.in[0] != cur_out) {
-        if (t.kind == Kind::kChain && t.chain_arity[0] == 2 && t.in.size() >= 2 && t.in[1] == cur_out) {
+        if (t.kind == Kind::kChain && t.chain_arity[0] == 2 && ew_commutes(t.chain_ops[0]) && t.in.size() >= 2 &&
+            t.in[1] == cur_out) {
           lhs_index = 1;
         } else {
           break;
@@ -1170,6 +1180,36 @@ static int run_step(fb200_plan* p, Step& s, const void* const* inputs, void* con
       fb200_conv2d_params cp{xd[0], xd[1], xd[2], xd[3], wd[0], wd[2], wd[3], s.iv[0], s.iv[1], s.iv[2], s.iv[3], s.iv[4]};
       return wrt_input ? fb200_conv2d_grad_input(in_ptr(0), in_ptr(1), out, &cp, os.dtype, stream)
                        : fb200_conv2d_grad_filter(in_ptr(0), in_ptr(1), out, &cp, os.dtype, stream);
+    }
+    case Kind::kMatmulGradLhs: {
+      // (gy [m, n], b [k, n]) -> ga [m, k]
+      if (s.in.size() != 2 || in_slot(0).dims.size() != 2 || in_slot(1).dims.size() != 2 ||
+          in_slot(0).dims[1] != in_slot(1).dims[1]) {
+        return set_error(FB200_INVALID_ARGUMENT, "op 'matmul_grad_lhs_internal' expects gy [m, n] and b [k, n]");
+      }
+      return fb200_matmul_grad_lhs(in_ptr(0), in_ptr(1), out, in_slot(0).dims[0], in_slot(0).dims[1],
+                                   in_slot(1).dims[0], os.dtype, p->allow_tf32, stream);
+    }
+    case Kind::kMatmulGradRhs: {
+      // (a [m, k], gy [m, n]) -> gb [k, n]
+      if (s.in.size() != 2 || in_slot(0).dims.size() != 2 || in_slot(1).dims.size() != 2 ||
+          in_slot(0).dims[0] != in_slot(1).dims[0]) {
+        return set_error(FB200_INVALID_ARGUMENT, "op 'matmul_grad_rhs_internal' expects a [m, k] and gy [m, n]");
+      }
+      return fb200_matmul_grad_rhs(in_ptr(0), in_ptr(1), out, in_slot(0).dims[0], in_slot(1).dims[1],
+                                   in_slot(0).dims[1], os.dtype, p->allow_tf32, stream);
+    }
+    case Kind::kMseLoss:
+    case Kind::kMseLossGrad: {
+      const size_t want = s.kind == Kind::kMseLoss ? 2 : 3;
+      if (s.in.size() != want || in_slot(0).dims != in_slot(1).dims) {
+        return set_error(FB200_INVALID_ARGUMENT, "op '%s' requires pred and target of the same shape", s.op.c_str());
+      }
+      int64_t numel = 1;
+      for (int64_t d : in_slot(0).dims) numel *= d;
+      return s.kind == Kind::kMseLoss
+                 ? fb200_mse_loss(in_ptr(0), in_ptr(1), out, numel, os.dtype, stream)
+                 : fb200_mse_loss_grad(in_ptr(0), in_ptr(1), in_ptr(2), out, numel, os.dtype, stream);
     }
     case Kind::kRfft: {
       const auto& xd = in_slot(0).dims;

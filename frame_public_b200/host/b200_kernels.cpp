@@ -91,8 +91,8 @@ Status elementwise(KernelContext& ctx, const char* op) {
 
 int code_of(std::string_view name) {
   static const char* names[] = {"", "add", "mul", "relu", "square", "sigmoid", "tanh", "rsqrt",
-                                "gelu", "silu", "softplus", "exp", "heaviside_surrogate"};
-  for (int i = 1; i <= 12; ++i) if (name == names[i]) return i;
+                                "gelu", "silu", "softplus", "exp", "heaviside_surrogate", "relu_grad_internal"};
+  for (int i = 1; i <= 13; ++i) if (name == names[i]) return i;
   return 0;
 }
 
@@ -336,6 +336,66 @@ Status conv2d_grad(KernelContext& ctx, const char* op, bool wrt_input) {
 }
 Status conv2d_grad_input_internal(KernelContext& ctx) { return conv2d_grad(ctx, "conv2d_grad_input_internal", true); }
 Status conv2d_grad_filter_internal(KernelContext& ctx) { return conv2d_grad(ctx, "conv2d_grad_filter_internal", false); }
+
+// Gradients of matmul and the MSE loss pair: ops the reference's own CUDA table lacks (a graph built by
+// build_backward_graph would otherwise take the fallback chain).
+Status matmul_grad_lhs_internal(KernelContext& ctx) {
+  FRAME_RETURN_IF_ERROR(arity(ctx, "matmul_grad_lhs_internal", 2, 2));
+  const Tensor& gy = ctx.inputs[0];
+  const Tensor& b = ctx.inputs[1];
+  if (gy.shape().rank() != 2 || b.shape().rank() != 2 || gy.shape().dim(1) != b.shape().dim(1)) {
+    return Status::make(ErrorCode::kInvalidArgument,
+                        "op 'matmul_grad_lhs_internal' cuda kernel requires gy [m, n] and b [k, n], got " +
+                            gy.shape().to_string() + " and " + b.shape().to_string());
+  }
+  return frame_b200::to_status(
+      fb200_matmul_grad_lhs(gy.raw_data(), b.raw_data(), ctx.outputs[0].raw_data(), gy.shape().dim(0),
+                            gy.shape().dim(1), b.shape().dim(0), dtype_of(gy), allow_tf32(ctx), stream_of(ctx)),
+      "matmul_grad_lhs_internal");
+}
+
+Status matmul_grad_rhs_internal(KernelContext& ctx) {
+  FRAME_RETURN_IF_ERROR(arity(ctx, "matmul_grad_rhs_internal", 2, 2));
+  const Tensor& a = ctx.inputs[0];
+  const Tensor& gy = ctx.inputs[1];
+  if (a.shape().rank() != 2 || gy.shape().rank() != 2 || a.shape().dim(0) != gy.shape().dim(0)) {
+    return Status::make(ErrorCode::kInvalidArgument,
+                        "op 'matmul_grad_rhs_internal' cuda kernel requires a [m, k] and gy [m, n], got " +
+                            a.shape().to_string() + " and " + gy.shape().to_string());
+  }
+  return frame_b200::to_status(
+      fb200_matmul_grad_rhs(a.raw_data(), gy.raw_data(), ctx.outputs[0].raw_data(), a.shape().dim(0),
+                            gy.shape().dim(1), a.shape().dim(1), dtype_of(a), allow_tf32(ctx), stream_of(ctx)),
+      "matmul_grad_rhs_internal");
+}
+
+Status mse_loss(KernelContext& ctx) {
+  FRAME_RETURN_IF_ERROR(arity(ctx, "mse_loss", 2, 2));
+  const Tensor& pred = ctx.inputs[0];
+  if (!(pred.shape() == ctx.inputs[1].shape())) {
+    return Status::make(ErrorCode::kInvalidArgument,
+                        "op 'mse_loss' cuda kernel requires pred and target of the same shape, got " +
+                            pred.shape().to_string() + ", " + ctx.inputs[1].shape().to_string());
+  }
+  return frame_b200::to_status(
+      fb200_mse_loss(pred.raw_data(), ctx.inputs[1].raw_data(), ctx.outputs[0].raw_data(), pred.numel(),
+                     dtype_of(pred), stream_of(ctx)),
+      "mse_loss");
+}
+
+Status mse_loss_grad_internal(KernelContext& ctx) {
+  FRAME_RETURN_IF_ERROR(arity(ctx, "mse_loss_grad_internal", 3, 3));
+  const Tensor& pred = ctx.inputs[0];
+  if (!(pred.shape() == ctx.inputs[1].shape()) || ctx.inputs[2].numel() != 1) {
+    return Status::make(ErrorCode::kInvalidArgument,
+                        "op 'mse_loss_grad_internal' cuda kernel requires pred and target of the same shape "
+                        "and a scalar gy");
+  }
+  return frame_b200::to_status(
+      fb200_mse_loss_grad(pred.raw_data(), ctx.inputs[1].raw_data(), ctx.inputs[2].raw_data(),
+                          ctx.outputs[0].raw_data(), pred.numel(), dtype_of(pred), stream_of(ctx)),
+      "mse_loss_grad_internal");
+}
 
 // rfft / irfft along the last axis, float32 only as in the reference (src/ops/schemas/fft.cpp).
 Status rfft(KernelContext& ctx) {
@@ -601,6 +661,7 @@ Status constant(KernelContext& ctx) {
 
 B200_ELEMENTWISE("add", FB200_EW_ADD, 2);
 B200_ELEMENTWISE("mul", FB200_EW_MUL, 2);
+B200_ELEMENTWISE("relu_grad_internal", FB200_EW_RELU_GRAD, 2);
 B200_ELEMENTWISE("relu", FB200_EW_RELU, 1);
 B200_ELEMENTWISE("square", FB200_EW_SQUARE, 1);
 B200_ELEMENTWISE("sigmoid", FB200_EW_SIGMOID, 1);
@@ -616,6 +677,10 @@ FRAME_REGISTER_KERNEL("conv2d", "cuda", &conv2d);
 FRAME_REGISTER_KERNEL("conv1d", "cuda", &conv1d);
 FRAME_REGISTER_KERNEL("max_pool2d", "cuda", &max_pool2d);
 FRAME_REGISTER_KERNEL("avg_pool2d", "cuda", &avg_pool2d);
+FRAME_REGISTER_KERNEL("matmul_grad_lhs_internal", "cuda", &matmul_grad_lhs_internal);
+FRAME_REGISTER_KERNEL("matmul_grad_rhs_internal", "cuda", &matmul_grad_rhs_internal);
+FRAME_REGISTER_KERNEL("mse_loss", "cuda", &mse_loss);
+FRAME_REGISTER_KERNEL("mse_loss_grad_internal", "cuda", &mse_loss_grad_internal);
 FRAME_REGISTER_KERNEL("rfft", "cuda", &rfft);
 FRAME_REGISTER_KERNEL("irfft", "cuda", &irfft);
 FRAME_REGISTER_KERNEL("max_pool2d_select_internal", "cuda", &max_pool2d_select_internal);

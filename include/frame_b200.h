@@ -118,7 +118,8 @@ typedef enum fb200_ew_op {
   FB200_EW_SILU = 9,
   FB200_EW_SOFTPLUS = 10,
   FB200_EW_EXP = 11,
-  FB200_EW_HEAVISIDE = 12   /* heaviside_surrogate forward: x >= 0 ? 1 : 0 (src/backends/cpu/kernels/elementwise.cpp, heaviside_surrogate_cpu_kernel) */
+  FB200_EW_HEAVISIDE = 12,  /* heaviside_surrogate forward: x >= 0 ? 1 : 0 (src/backends/cpu/kernels/elementwise.cpp, heaviside_surrogate_cpu_kernel) */
+  FB200_EW_RELU_GRAD = 13   /* relu_grad_internal(x, gy): x > 0 ? gy : 0, binary and NOT commutative: the running value is x, the operand gy (elementwise.cpp:411-414) */
 } fb200_ew_op;
 #define FB200_MAX_CHAIN 8
 #define FB200_MAX_CHAIN_INPUTS 9
@@ -250,6 +251,23 @@ FB200_API int fb200_conv2d_grad_input(const void* dy, const void* w, void* dx,
                                       const fb200_conv2d_params* p, int dtype, fb200_stream stream);
 FB200_API int fb200_conv2d_grad_filter(const void* x, const void* dy, void* dw,
                                        const fb200_conv2d_params* p, int dtype, fb200_stream stream);
+/* Gradients of matmul (src/backends/cpu/kernels/matmul.cpp:187-232, :289-330; the reference CUDA
+ * backend has no kernel for them): ga[m,k] = gy[m,n] * b[k,n]^T and gb[k,n] = a[m,k]^T * gy[m,n],
+ * fp32 accumulation over the contracted index in increasing order, one rounding.  Strict fp32 reads
+ * the transposed operand in place (bit-identical to the CPU reference); bf16 / f16 and fp32 with
+ * allow_tf32 transpose it once into a stream-ordered scratch and run the tensor-core GEMM. */
+FB200_API int fb200_matmul_grad_lhs(const void* gy, const void* b, void* ga, int64_t m, int64_t n,
+                                    int64_t k, int dtype, int allow_tf32, fb200_stream stream);
+FB200_API int fb200_matmul_grad_rhs(const void* a, const void* gy, void* gb, int64_t m, int64_t n,
+                                    int64_t k, int dtype, int allow_tf32, fb200_stream stream);
+/* mse_loss(pred, target) = mean((pred - target)^2) -> one element; mse_loss_grad_internal =
+ * (2*gy/numel) * (pred - target) with gy one element (src/backends/cpu/kernels/loss.cpp:108-150,
+ * :225-255).  The loss is bit-identical to the serial fp32 sum of the reference up to 65536
+ * elements and a double-precision block reduction above; the gradient is bit-identical. */
+FB200_API int fb200_mse_loss(const void* pred, const void* target, void* out, int64_t numel,
+                             int dtype, fb200_stream stream);
+FB200_API int fb200_mse_loss_grad(const void* pred, const void* target, const void* gy, void* gpred,
+                                  int64_t numel, int dtype, fb200_stream stream);
 /* rfft / irfft along the last axis, float32 only (src/ops/schemas/fft.cpp:8-9; replace the cuFFT
  * R2C / C2R plans of src/backends/cuda/kernels/fft.cpp).  rfft: x [rows, n] -> out [rows, n/2+1, 2]
  * (interleaved re/im, forward sign, unscaled).  irfft: z [rows, n/2+1, 2] -> out [rows, n], scaled by

@@ -387,6 +387,42 @@ def conv2d_grad_filter(x, dy, filter_shape, stride, padding, groups: int = 1, dt
     return from_accum(acc, dtype)
 
 
+def matmul_grad_lhs(gy, b, dtype: int = DT_F32):
+    """ga[i,p] = sum_j gy[i,j]*b[p,j], j increasing (src/backends/cpu/kernels/matmul.cpp:187-232)."""
+    return matmul(gy, np.ascontiguousarray(np.asarray(b).T), dtype)
+
+
+def matmul_grad_rhs(a, gy, dtype: int = DT_F32):
+    """gb[p,j] = sum_i a[i,p]*gy[i,j], i increasing (matmul.cpp:289-330)."""
+    return matmul(np.ascontiguousarray(np.asarray(a).T), gy, dtype)
+
+
+def relu_grad(x, gy, dtype: int = DT_F32):
+    """x > 0 ? gy : 0 (src/backends/cpu/kernels/elementwise.cpp:411-414)."""
+    xv, gv = to_accum(x, dtype), to_accum(gy, dtype)
+    return from_accum(np.where(xv > 0, gv, F32(0)).astype(F32), dtype)
+
+
+def mse_loss(pred, target, dtype: int = DT_F32):
+    """mean((pred-target)^2): squares added one after the other in fp32, then one division
+    (src/backends/cpu/kernels/loss.cpp:108-150).  Result shape ()."""
+    p, t = to_accum(pred, dtype).reshape(-1), to_accum(target, dtype).reshape(-1)
+    diff = (p - t).astype(F32)
+    sq = (diff * diff).astype(F32)
+    acc = F32(0)
+    for v in sq:
+        acc = F32(acc + v)
+    return np.asarray(from_accum(np.asarray(F32(acc / F32(p.size)), dtype=F32), dtype)).reshape(())
+
+
+def mse_loss_grad(pred, target, gy, dtype: int = DT_F32):
+    """(2*gy/numel) * (pred - target), the coefficient formed first (loss.cpp:225-255)."""
+    p, t = to_accum(pred, dtype), to_accum(target, dtype)
+    g = F32(to_accum(np.asarray(gy), dtype).reshape(-1)[0])
+    coefficient = F32(F32(F32(2.0) * g) / F32(p.size))
+    return from_accum((coefficient * (p - t).astype(F32)).astype(F32), dtype)
+
+
 def rfft(x):
     """x[..., n] (float32) -> [..., n//2+1, 2], forward sign, unscaled (src/ops/schemas/fft.cpp:8).
     The reference CPU kernel calls pocketfft r2c in float32; this restatement evaluates the DFT sum

@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import POINTER, byref, c_char_p, c_double, c_int, c_int64, c_void_p, create_string_buffer
+from ctypes import POINTER, byref, c_char_p, c_double, c_int, c_int32, c_int64, c_void_p, create_string_buffer
 
 import numpy as np
 
@@ -52,6 +52,8 @@ def load():
         s.fref_time_run.argtypes = [c_void_p, c_int, c_char_p, c_int]
         s.fref_device_buffer.restype = c_void_p
         s.fref_device_buffer.argtypes = [c_void_p, c_int, c_int]
+        s.fref_backward_text.restype = c_int64
+        s.fref_backward_text.argtypes = [c_char_p, c_int32, POINTER(c_int32), c_int32, c_char_p, c_int64, c_char_p, c_int]
         s.fref_pipeline_text.restype = c_int64
         s.fref_pipeline_text.argtypes = [c_char_p, c_char_p, c_char_p, c_int64, c_char_p, c_int]
         s.fref_nn_graph_text.restype = c_int64
@@ -120,6 +122,20 @@ class Compiled:
             self.close()
         except Exception:
             pass
+
+
+def backward_text(ir_text: str, loss_output_index: int, wrt_input_indices) -> str:
+    """IR text of the training graph the reference's build_backward_graph derives: the forward
+    outputs followed by the gradients w.r.t. the listed graph inputs."""
+    s = load()
+    err = create_string_buffer(2048)
+    wrt = (c_int32 * len(wrt_input_indices))(*wrt_input_indices)
+    n = s.fref_backward_text(ir_text.encode(), loss_output_index, wrt, len(wrt_input_indices), None, 0, err, len(err))
+    if n < 0:
+        raise RuntimeError(f"build_backward_graph failed: {err.value.decode('utf-8', 'replace')}")
+    buf = create_string_buffer(int(n))
+    s.fref_backward_text(ir_text.encode(), loss_output_index, wrt, len(wrt_input_indices), buf, n, err, len(err))
+    return buf.value.decode()
 
 
 def pipeline_text(ir_text: str, backend: str = "cpu") -> str:

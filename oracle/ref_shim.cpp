@@ -19,11 +19,13 @@
 #include <cstdio>
 #include <cstring>
 #include <memory>
+#include <span>
 #include <string>
 #include <string_view>
 #include <variant>
 #include <vector>
 
+#include <frame/compiler/autograd.h>
 #include <frame/compiler/pipeline.h>
 #include <frame/core/tensor.h>
 #include <frame/hal/allocator.h>
@@ -304,6 +306,27 @@ int64_t fref_nn_graph_text(const char* kind, int64_t batch, int64_t p1, int64_t 
     }
   }
   const std::string text = frame::ir::dump_text(graph);
+  if (out != nullptr && cap > 0) std::snprintf(out, static_cast<size_t>(cap), "%s", text.c_str());
+  return static_cast<int64_t>(text.size()) + 1;
+}
+
+// IR text of the training graph compiler::build_backward_graph derives from `ir_text`: the forward
+// outputs followed by the gradients w.r.t. the listed graph inputs
+// (include/frame/compiler/autograd.h:44).  Returns the number of bytes needed.
+int64_t fref_backward_text(const char* ir_text, int32_t loss_output_index, const int32_t* wrt,
+                           int32_t n_wrt, char* out, int64_t cap, char* err, int errlen) {
+  Result<frame::ir::Graph> graph = frame::ir::parse_text(ir_text);
+  if (!graph.is_ok()) {
+    set_err(err, errlen, std::string(graph.status().message()));
+    return -1;
+  }
+  Result<frame::ir::Graph> train = frame::compiler::build_backward_graph(
+      graph.value(), loss_output_index, std::span<const int32_t>(wrt, static_cast<size_t>(n_wrt)));
+  if (!train.is_ok()) {
+    set_err(err, errlen, std::string(train.status().message()));
+    return -1;
+  }
+  const std::string text = frame::ir::dump_text(train.value());
   if (out != nullptr && cap > 0) std::snprintf(out, static_cast<size_t>(cap), "%s", text.c_str());
   return static_cast<int64_t>(text.size()) + 1;
 }

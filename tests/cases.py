@@ -277,6 +277,26 @@ def build_cases() -> List[Case]:
                           lambda x, dy, ws=ws, st=st, pd=pd, groups=groups, dt=dt: fo.conv2d_grad_filter(x, dy, ws, st, pd, groups, dt),
                           exact=True))
 
+    # ---- training-side ops: gradients of matmul and relu, the MSE loss pair, a full reduction ---------
+    for tag, (m, k, n), dt in [("f32_5x7x3", (5, 7, 3), F32), ("f32_64x96x40", (64, 96, 40), F32),
+                               ("bf16_33x17x9", (33, 17, 9), BF16)]:
+        cases.append(Case(f"matmul_grad_lhs_{tag}", "matmul_grad_lhs_internal", dt, [rnd((m, n), dt), rnd((k, n), dt)], {},
+                          lambda gy, b, dt=dt: fo.matmul_grad_lhs(gy, b, dt), exact=True))
+        cases.append(Case(f"matmul_grad_rhs_{tag}", "matmul_grad_rhs_internal", dt, [rnd((m, k), dt), rnd((m, n), dt)], {},
+                          lambda a, gy, dt=dt: fo.matmul_grad_rhs(a, gy, dt), exact=True))
+    for dt, tag in ((F32, "f32"), (BF16, "bf16")):
+        xz = rnd((1023,), dt)
+        xz[:3] = _store(np.array([0.0, -0.0, 1e-30], np.float32), dt)
+        cases.append(Case(f"relu_grad_{tag}_1023", "relu_grad_internal", dt, [xz, rnd((1023,), dt)], {},
+                          lambda x, gy, dt=dt: fo.relu_grad(x, gy, dt), exact=True))
+        cases.append(Case(f"mse_loss_{tag}_37x29", "mse_loss", dt, [rnd((37, 29), dt), rnd((37, 29), dt)], {},
+                          lambda p, t, dt=dt: fo.mse_loss(p, t, dt), exact=True))
+        cases.append(Case(f"mse_loss_grad_{tag}_37x29", "mse_loss_grad_internal", dt,
+                          [rnd((37, 29), dt), rnd((37, 29), dt), np.asarray(rnd((), dt)).reshape(())], {},
+                          lambda p, t, g, dt=dt: fo.mse_loss_grad(p, t, g, dt), exact=True))
+    cases.append(Case("sum_f32_all_axes", "sum", F32, [rnd((7, 33))], {"axes": [0, 1]},
+                      lambda x: fo.sum_axes(x, [0, 1], False, F32), exact=True))
+
     # ---- rfft / irfft (float32; the reference CPU kernel needs pocketfft, which is not in its tree:
     #      pinned by the reference's known-answer tests instead, tests/test_fft_cpu.py) ----------------
     for tag, shape in (("n4", (4,)), ("n5", (5,)), ("2x6", (2, 6)), ("3x64", (3, 64)), ("2x5x243", (2, 5, 243)),

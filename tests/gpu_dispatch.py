@@ -66,6 +66,16 @@ def run_case(case, allow_tf32=False):
                               at["padding"][0], at["padding"][1], at["groups"])
         fn = capi.conv2d_grad_input if op == "conv2d_grad_input_internal" else capi.conv2d_grad_filter
         fn(ptr[0], ptr[1], out.ptr, p, dt)
+    elif op == "matmul_grad_lhs_internal":
+        (m, n), k = ins[0].shape, ins[1].shape[0]
+        capi.matmul_grad_lhs(ptr[0], ptr[1], out.ptr, m, n, k, dt, allow_tf32)
+    elif op == "matmul_grad_rhs_internal":
+        (m, k), n = ins[0].shape, ins[1].shape[1]
+        capi.matmul_grad_rhs(ptr[0], ptr[1], out.ptr, m, n, k, dt, allow_tf32)
+    elif op == "mse_loss":
+        capi.mse_loss(ptr[0], ptr[1], out.ptr, ins[0].size, dt)
+    elif op == "mse_loss_grad_internal":
+        capi.mse_loss_grad(ptr[0], ptr[1], ptr[2], out.ptr, ins[0].size, dt)
     elif op == "rfft":
         n = ins[0].shape[-1]
         capi.rfft(ptr[0], out.ptr, ins[0].size // n, n, dt)
@@ -104,7 +114,7 @@ def assert_parity(case, got, exact):
     exp = case.expected()
     assert got.shape == exp.shape
     if exact:
-        same = np.array_equal(np.asarray(got).view(np.uint8), np.asarray(exp).view(np.uint8))
+        same = np.array_equal(np.asarray(got).reshape(-1).view(np.uint8), np.asarray(exp).reshape(-1).view(np.uint8))
         assert same, (case.name, fo.max_err(got, exp, case.dtype))
     else:
         assert fo.all_close(got, exp, case.dtype), (case.name, fo.max_err(got, exp, case.dtype))

@@ -78,7 +78,9 @@ def test_reference_nn_module_runs_on_cuda_without_fallback(spec):
 NEW_OP_CASES = [c for c in __import__("cases").CASES
                 if c.op in ("avg_pool2d", "heaviside_surrogate", "gather", "scatter_add", "gather_grad_internal",
                             "max_pool2d_select_internal", "max_pool2d_grad_internal", "avg_pool2d_grad_internal",
-                            "conv2d_grad_input_internal", "conv2d_grad_filter_internal")]
+                            "conv2d_grad_input_internal", "conv2d_grad_filter_internal", "matmul_grad_lhs_internal",
+                            "matmul_grad_rhs_internal", "relu_grad_internal", "mse_loss", "mse_loss_grad_internal")
+                or c.name == "sum_f32_all_axes"]
 
 
 @pytest.mark.parametrize("case", NEW_OP_CASES, ids=lambda c: c.name)
@@ -91,7 +93,7 @@ def test_pool_step_and_index_ops_through_the_reference_api(case):
     gpu = ref_runtime.Compiled(case.ir_text("cuda"), "cuda")
     (got,) = gpu.run(case.inputs)
     if case.exact:
-        assert np.array_equal(np.asarray(got).view(np.uint8), np.asarray(exp).view(np.uint8)), case.name
+        assert np.array_equal(np.asarray(got).reshape(-1).view(np.uint8), np.asarray(exp).reshape(-1).view(np.uint8)), case.name
     else:
         assert fo.all_close(got, exp, case.dtype), (case.name, fo.max_err(got, exp, case.dtype))
     assert ref_runtime.fallback_count(case.op, "cuda") == 0
@@ -110,3 +112,21 @@ def test_rfft_irfft_through_the_reference_api(case):
     exp = case.expected()
     assert fo.all_close(got, exp, case.dtype, rtol=1e-5, atol=1e-5), (case.name, fo.max_err(got, exp, case.dtype))
     assert ref_runtime.fallback_count(case.op, "cuda") == 0
+
+
+def test_training_graph_through_the_reference_api_without_fallback():
+    """compiler::build_backward_graph of a two-layer MLP with an MSE loss, compiled by the reference's
+    runtime::compile for backend "cuda": [loss, grad w1, grad b1, grad w2] bit-identical to its CPU
+    backend (strict fp32) and no op of the training graph takes the fallback chain."""
+    fwd_cpu, ins = configs.train_mlp_forward(backend="cpu")
+    fwd_cuda, _ = configs.train_mlp_forward(backend="cuda")
+    cpu = ref_runtime.Compiled(ref_runtime.backward_text(fwd_cpu, 0, configs.TRAIN_WRT), "cpu")
+    exp = cpu.run(ins)
+    gpu = ref_runtime.Compiled(ref_runtime.backward_text(fwd_cuda, 0, configs.TRAIN_WRT), "cuda")
+    got = gpu.run(ins)
+    assert len(got) == len(exp) == 4
+    for g, e in zip(got, exp):
+        assert np.array_equal(np.asarray(g).reshape(-1).view(np.uint8), np.asarray(e).reshape(-1).view(np.uint8))
+    for op in ("matmul", "add", "relu", "mse_loss", "mse_loss_grad_internal", "matmul_grad_lhs_internal",
+               "matmul_grad_rhs_internal", "relu_grad_internal", "constant"):
+        assert ref_runtime.fallback_count(op, "cuda") == 0, f"op {op} fell back to the eager chain"

@@ -56,7 +56,7 @@ def test_oracle_matches_committed_reference_outputs(case):
     got = case.expected()
     assert got.shape == ref.shape
     if case.exact:
-        assert np.array_equal(np.asarray(got).view(np.uint8), np.asarray(ref).view(np.uint8)), case.name
+        assert np.array_equal(np.asarray(got).reshape(-1).view(np.uint8), np.asarray(ref).reshape(-1).view(np.uint8)), case.name
     else:
         assert fo.all_close(got, ref, case.dtype), fo.max_err(got, ref, case.dtype)
 
@@ -69,7 +69,7 @@ def test_oracle_matches_live_reference(case):
     comp.close()
     got = case.expected()
     if case.exact:
-        assert np.array_equal(np.asarray(got).view(np.uint8), np.asarray(ref).view(np.uint8))
+        assert np.array_equal(np.asarray(got).reshape(-1).view(np.uint8), np.asarray(ref).reshape(-1).view(np.uint8))
     else:
         assert fo.all_close(got, ref, case.dtype)
 

@@ -106,3 +106,11 @@ def test_gradient_internals_decode_as_single_steps():
     h = capi.c_void_p()
     rc = lib.fb200_plan_describe(text.encode(), 1, capi.byref(h))
     assert rc == 1 and b"conv2d_grad_input_internal" in lib.fb200_last_error()
+
+
+def test_training_graph_decodes_with_the_bias_add_absorbed():
+    names, launches = runtime.describe_plan(_golden("train_mlp_f32"))
+    assert _live(names) == ["matmul+epilogue", "relu", "matmul", "mse_loss", "mse_loss_grad_internal",
+                            "matmul_grad_lhs_internal", "matmul_grad_rhs_internal", "relu_grad_internal",
+                            "matmul_grad_rhs_internal"]
+    assert launches == 9

@@ -146,3 +146,21 @@ def test_gradient_internals_through_the_plan_executor(name):
     assert capi.kernel_status(0) == 0
     assert np.array_equal(np.asarray(got).view(np.uint8), np.asarray(gold).view(np.uint8)), name
     plan.close()
+
+
+def test_training_graph_of_the_reference_autograd_runs_bit_identically():
+    """The training graph compiler::build_backward_graph derives from a two-layer MLP with an MSE loss
+    ([loss, grad w1, grad b1, grad w2]; mse_loss_grad_internal, matmul_grad_lhs/rhs_internal,
+    relu_grad_internal beside the forward ops), planned by the reference for backend "cuda".  Strict
+    fp32: every output is bit-identical to the reference CPU backend, also on CUDA-graph replays."""
+    _, ins = configs.train_mlp_forward()
+    gold = np.load(GOLD)
+    plan = runtime.CompiledPlan(_plan_text("train_mlp_f32"), 0, allow_tf32=False)
+    for _ in range(3):
+        outs = plan.run_host(ins)
+        assert capi.kernel_status(0) == 0
+        assert len(outs) == 4
+        for i, got in enumerate(outs):
+            exp = gold[f"train_mlp_f32__{i}"]
+            assert np.array_equal(np.asarray(got).reshape(-1).view(np.uint8), np.asarray(exp).reshape(-1).view(np.uint8)), i
+    plan.close()

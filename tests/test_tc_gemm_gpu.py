@@ -132,3 +132,33 @@ def test_large_gemm_on_256x256_tiles_with_a_light_epilogue(dt, tf32):
         assert fo.all_close(got, exp, dt, rtol=1e-3, atol=atol), fo.max_err(got, exp, dt)
     else:
         assert fo.all_close(got, exp, dt, rtol=2e-2, atol=2e-2), fo.max_err(got, exp, dt)
+
+
+@pytest.mark.parametrize("dt,tf32", [(fo.DT_BF16, False), (fo.DT_F32, True), (fo.DT_F32, False)],
+                         ids=["bf16", "tf32", "fp32_strict"])
+def test_matmul_gradients_on_the_tensor_cores_and_strict(dt, tf32):
+    """ga = gy * b^T and gb = a^T * gy (src/backends/cpu/kernels/matmul.cpp:187-232, :289-330): the
+    transposed operand goes through a scratch transpose and the tcgen05 GEMM when reduced-precision
+    math is allowed, and is read in place by the strict kernel otherwise (bit-identical)."""
+    m, n, k = 520, 392, 264
+    rng = np.random.default_rng(31)
+    gy = fo.from_accum(rng.uniform(-1, 1, (m, n)).astype(np.float32), dt)
+    a = fo.from_accum(rng.uniform(-1, 1, (m, k)).astype(np.float32), dt)
+    b = fo.from_accum(rng.uniform(-1, 1, (k, n)).astype(np.float32), dt)
+    d_gy, d_a, d_b = (capi.DeviceBuffer.from_numpy(t) for t in (gy, a, b))
+    d_ga = capi.DeviceBuffer(m * k * capi.ITEMSIZE[dt])
+    d_gb = capi.DeviceBuffer(k * n * capi.ITEMSIZE[dt])
+    capi.matmul_grad_lhs(d_gy.ptr, d_b.ptr, d_ga.ptr, m, n, k, dt, tf32)
+    capi.matmul_grad_rhs(d_a.ptr, d_gy.ptr, d_gb.ptr, m, n, k, dt, tf32)
+    capi.synchronize()
+    assert capi.kernel_status(0) == 0
+    ga = d_ga.download(capi.NP_STORAGE[dt], (m, k))
+    gb = d_gb.download(capi.NP_STORAGE[dt], (k, n))
+    exp_a, exp_b = fo.matmul_grad_lhs(gy, b, dt), fo.matmul_grad_rhs(a, gy, dt)
+    if dt == fo.DT_F32 and not tf32:
+        assert np.array_equal(ga, exp_a) and np.array_equal(gb, exp_b)
+    elif dt == fo.DT_F32:
+        for got, exp, red in ((ga, exp_a, n), (gb, exp_b, m)):
+            assert fo.all_close(got, exp, dt, rtol=1e-3, atol=2e-3 * np.sqrt(red) / 3), fo.max_err(got, exp, dt)
+    else:
+        assert fo.all_close(ga, exp_a, dt, rtol=2e-2, atol=2e-2) and fo.all_close(gb, exp_b, dt, rtol=2e-2, atol=2e-2)
