@@ -26,7 +26,7 @@ NP_STORAGE = {F32: np.float32, F64: np.float64, F16: np.uint16, BF16: np.uint16,
 EW = {"add": 1, "mul": 2, "relu": 3, "square": 4, "sigmoid": 5, "tanh": 6, "rsqrt": 7,
       "gelu": 8, "silu": 9, "softplus": 10, "exp": 11, "heaviside_surrogate": 12,
       "relu_grad_internal": 13}
-EW_ARITY = {"add": 2, "mul": 2}
+EW_ARITY = {"add": 2, "mul": 2, "relu_grad_internal": 2}
 OPERAND_FULL, OPERAND_COL, OPERAND_ROW = 0, 1, 2
 H2D, D2H, D2D = 1, 2, 3
 MAX_CHAIN = 8
