@@ -70,16 +70,6 @@ static int gemm_m_halves() {
   return v;
 }
 
-// k-blocks by which an L2 prefetch runs ahead of the loads (0 = none); FRAME_B200_GEMM_L2_AHEAD.
-static int gemm_l2_ahead() {
-  static const int v = [] {
-    const char* e = getenv("FRAME_B200_GEMM_L2_AHEAD");
-    const int g = e != nullptr ? atoi(e) : 0;
-    return g >= 0 && g <= 64 ? g : 0;
-  }();
-  return v;
-}
-
 // An epilogue of binary ops, ReLU, square and the step function: a few instructions per element.
 static bool light_epilogue(const EpilogueDev& epi) {
   for (int i = 0; i < epi.n_ops; ++i) {
@@ -155,7 +145,7 @@ __device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64
 template <typename T, int ELT, int BLOCK_N, int MH, int KB>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                    const __grid_constant__ CUtensorMap tmap_b, int b_spans_map, int l2_ahead, GemmDest dest, int64_t M,
+                    const __grid_constant__ CUtensorMap tmap_b, int b_spans_map, GemmDest dest, int64_t M,
                     int64_t N, int64_t K, uint32_t idesc, EpilogueDev epi, int* status) {
   using Cfg = GemmCfg<ELT, BLOCK_N, MH, KB>;
   static_assert(MH == 1 || (MH == 2 && BLOCK_N == 256), "two M halves fill TMEM with one 256 x 256 tile");
@@ -228,17 +218,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (!loads_b) {
           mbar_arrive_expect_tx_elect(full_bar(stage), Cfg::kAStageBytes);
           tma_load_2d_elect(a_dst, &tmap_a, full_bar(stage), k0, a_row);
-          if (l2_ahead > 0 && kb + l2_ahead < k_blocks) {
-            tma_prefetch_l2_2d_elect(&tmap_a, k0 + l2_ahead * Cfg::kBlockK, a_row);
-          }
         } else {
           mbar_arrive_expect_tx_elect(full_bar(stage), Cfg::kBStageBytes);
           if (b_spans_map) {
             // B seen as [N / span][K][span columns]: the whole B stage is one copy
             tma_load_3d_elect(b_dst, &tmap_b, full_bar(stage), 0, k0, b_col / Cfg::kBChunkCols);
-            if (l2_ahead > 0 && kb + l2_ahead < k_blocks) {
-              tma_prefetch_l2_3d_elect(&tmap_b, 0, k0 + l2_ahead * Cfg::kBlockK, b_col / Cfg::kBChunkCols);
-            }
           } else {
 #pragma unroll
             for (int c = 0; c < Cfg::kBChunks; ++c) {
@@ -585,7 +569,7 @@ static int launch_tc(const void* a, const void* b, const GemmDest& c, int64_t m,
                                      static_cast<int>(Cfg::kSmemBytes)));
   const int64_t tiles = ((m + Cfg::kTileM - 1) / Cfg::kTileM) * ((n + BLOCK_N - 1) / BLOCK_N);
   const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
-  kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, b_spans_map, gemm_l2_ahead(), c, m, n, k, idesc,
+  kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, b_spans_map, c, m, n, k, idesc,
                                                       epi, status);
   return after_launch("gemm_tcgen05_kernel");
 }

@@ -142,29 +142,6 @@ __device__ __forceinline__ void tma_load_3d_elect(uint32_t smem_dst, const void*
       : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
-// L2 prefetch of a tile that a later load will fetch (no shared-memory destination, no barrier).
-__device__ __forceinline__ void tma_prefetch_l2_2d_elect(const void* tmap, int32_t x, int32_t y) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred q;\n\t"
-      "elect.sync _|q, 0xffffffff;\n\t"
-      "@q cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];\n\t"
-      "}\n"
-      :
-      : "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ void tma_prefetch_l2_3d_elect(const void* tmap, int32_t x, int32_t y, int32_t z) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred q;\n\t"
-      "elect.sync _|q, 0xffffffff;\n\t"
-      "@q cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];\n\t"
-      "}\n"
-      :
-      : "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(z)
-      : "memory");
-}
 // 4-D tiled load (x innermost).  x times the element size must again be a multiple of 16 bytes; the
 // other coordinates may be negative or past the end (those elements read as the fill value).
 __device__ __forceinline__ void tma_load_4d(uint32_t smem_dst, const void* tmap, uint32_t bar,
