@@ -38,19 +38,43 @@ gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ B, T* __restrict
     for (int i = 0; i < TM; ++i)
 #pragma unroll
       for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
-    for (int64_t k0 = 0; k0 < K; k0 += BK) {
-      // A tile: BM rows x BK, K-contiguous in global; stored k-major in shared memory.
-      for (int e = tid; e < BM * BK; e += THREADS) {
+    // The next k-block is fetched into registers while the current one is multiplied out of shared
+    // memory: with a handful of CTAs (a [64, 256] x [256, 10] product is two tiles) every global
+    // round trip would otherwise be exposed once per k-block.
+    constexpr int A_PER = (BM * BK + THREADS - 1) / THREADS;
+    constexpr int B_PER = (BK * BN + THREADS - 1) / THREADS;
+    float a_reg[A_PER], b_reg[B_PER];
+    auto fetch = [&](int64_t k0) {
+#pragma unroll
+      for (int q = 0; q < A_PER; ++q) {
+        const int e = tid + q * THREADS;
         const int r = e / BK, kk = e % BK;
         const int64_t gm = m0 + r, gk = k0 + kk;
-        As[kk][r] = (gm < M && gk < K) ? to_f32(A[gm * st.a_row + gk * st.a_k]) : 0.0f;
+        a_reg[q] = (e < BM * BK && gm < M && gk < K) ? to_f32(A[gm * st.a_row + gk * st.a_k]) : 0.0f;
       }
-      for (int e = tid; e < BK * BN; e += THREADS) {
+#pragma unroll
+      for (int q = 0; q < B_PER; ++q) {
+        const int e = tid + q * THREADS;
         const int kk = e / BN, c = e % BN;
         const int64_t gk = k0 + kk, gn = n0 + c;
-        Bs[kk][c] = (gk < K && gn < N) ? to_f32(B[gk * st.b_k + gn * st.b_col]) : 0.0f;
+        b_reg[q] = (e < BK * BN && gk < K && gn < N) ? to_f32(B[gk * st.b_k + gn * st.b_col]) : 0.0f;
+      }
+    };
+    fetch(0);
+    for (int64_t k0 = 0; k0 < K; k0 += BK) {
+      // A tile: BM rows x BK, stored k-major in shared memory; B tile: BK x BN.
+#pragma unroll
+      for (int q = 0; q < A_PER; ++q) {
+        const int e = tid + q * THREADS;
+        if (e < BM * BK) As[e % BK][e / BK] = a_reg[q];
+      }
+#pragma unroll
+      for (int q = 0; q < B_PER; ++q) {
+        const int e = tid + q * THREADS;
+        if (e < BK * BN) Bs[e / BN][e % BN] = b_reg[q];
       }
       __syncthreads();
+      if (k0 + BK < K) fetch(k0 + BK);
       const int klen = static_cast<int>(K - k0 < BK ? K - k0 : BK);
       for (int kk = 0; kk < klen; ++kk) {
         float a[TM], b[TN];
@@ -90,6 +114,12 @@ static int launch_simt(const void* a, const void* b, void* c, int64_t m, int64_t
   if (big_tiles >= kNumSMs) {
     const int grid = static_cast<int>(big_tiles < int64_t(kNumSMs) * 4 ? big_tiles : int64_t(kNumSMs) * 4);
     gemm_simt_kernel<T, 128, 128, 16, 8, 8><<<grid, 256, 0, s>>>(ap, bp, cp, m, n, k, st, epi);
+  } else if (((m + 31) / 32) * ((n + 63) / 64) < 16) {
+    // a handful of outputs (the [64, 10] head of an MLP): one output per thread, 16 x 16 tiles, so
+    // that more than one or two SMs take part
+    const int64_t tiles = ((m + 15) / 16) * ((n + 15) / 16);
+    const int grid = static_cast<int>(tiles < int64_t(kNumSMs) * 8 ? tiles : int64_t(kNumSMs) * 8);
+    gemm_simt_kernel<T, 16, 16, 64, 1, 1><<<grid, 256, 0, s>>>(ap, bp, cp, m, n, k, st, epi);
   } else {
     const int64_t tiles = ((m + 31) / 32) * ((n + 63) / 64);
     const int grid = static_cast<int>(tiles < int64_t(kNumSMs) * 8 ? tiles : int64_t(kNumSMs) * 8);
