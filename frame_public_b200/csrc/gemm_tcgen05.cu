@@ -584,11 +584,14 @@ static int launch_tc_n(const void* a, const void* b, const GemmDest& c, int64_t 
     // (8192^3 bf16: 1418 -> 1509 TFLOP/s, TF32 4096^3: 622 -> 690), but the tile fills TMEM, so its
     // epilogue no longer overlaps the next mainloop: a transcendental epilogue (GELU over 64 Ki
     // elements is about 18 K issue cycles per tile) costs more than the traffic saves.  They are
-    // taken for chains of adds, multiplies and ReLU, when the waves of tiles do not get longer by
-    // more than an eighth.
+    // taken for chains of adds, multiplies and ReLU over a long K, when the waves of tiles do not get
+    // longer by more than an eighth.
     const int64_t t2 = ((m + 255) / 256) * ((n + 255) / 256);
     const int64_t waves1 = (tiles(256) + kNumSMs - 1) / kNumSMs, waves2 = (t2 + kNumSMs - 1) / kNumSMs;
-    if (gemm_m_halves() == 2 && light_epilogue(epi) && m > 128 && t2 >= kNumSMs && 16 * waves2 <= 9 * waves1) {
+    // The exposed epilogue costs about 8-10 K cycles per tile against a gain of 6-11 % of the mainloop:
+    // only worth it from 128 k-blocks per tile on (measured slower at K = 768 and 1536 TF32).
+    if (gemm_m_halves() == 2 && light_epilogue(epi) && m > 128 && k * ELT >= 128 * 128 && t2 >= kNumSMs &&
+        16 * waves2 <= 9 * waves1) {
       return launch_tc<T, ELT, 256, 2>(a, b, c, m, n, k, dtype, epi, s);
     }
     return launch_tc<T, ELT, 256>(a, b, c, m, n, k, dtype, epi, s);
