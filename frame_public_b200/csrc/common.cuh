@@ -156,9 +156,17 @@ __device__ __forceinline__ float ew_unary(int op, float x) {
   }
 }
 
+// add / mul only: the form the contraction epilogues use (a third case here cost the softplus
+// epilogue of a short-K GEMM a third of its speed).
 __device__ __forceinline__ float ew_binary(int op, float a, float b) {
-  return op == FB200_EW_ADD ? a + b : (op == FB200_EW_MUL ? a * b : (a > 0.0f ? b : 0.0f));
+  return op == FB200_EW_ADD ? a + b : a * b;
 }
+// every binary code, for the elementwise chains
+__device__ __forceinline__ float ew_binary_any(int op, float a, float b) {
+  return op == FB200_EW_RELU_GRAD ? (a > 0.0f ? b : 0.0f) : ew_binary(op, a, b);
+}
+// codes a matmul / conv2d epilogue may carry
+inline bool ew_epilogue_ok(int op) { return op != FB200_EW_RELU_GRAD; }
 
 inline bool ew_is_binary(int op) { return op == FB200_EW_ADD || op == FB200_EW_MUL || op == FB200_EW_RELU_GRAD; }
 inline bool ew_commutes(int op) { return op == FB200_EW_ADD || op == FB200_EW_MUL; }

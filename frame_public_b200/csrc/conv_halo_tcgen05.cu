@@ -419,12 +419,9 @@ conv2d_halo_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x,
               if (op == FB200_EW_ADD) {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) v[j] = v[j] + rhs[j];
-              } else if (op == FB200_EW_MUL) {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = v[j] * rhs[j];
               } else {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] = ew_binary(op, v[j], rhs[j]);
+                for (int j = 0; j < 32; ++j) v[j] = v[j] * rhs[j];
               }
             } else {
               ew_unary_vec<float, 32>(op, v);

@@ -64,7 +64,7 @@ fused_chain_kernel(ChainDesc d, T* __restrict__ out, int64_t n_vec, int64_t nume
           for (int e = 0; e < W; ++e) cur[e] = round_through<T>(cur[e] * rhs[e]);
         } else {
 #pragma unroll
-          for (int e = 0; e < W; ++e) cur[e] = round_through<T>(ew_binary(op, cur[e], rhs[e]));
+          for (int e = 0; e < W; ++e) cur[e] = round_through<T>(ew_binary_any(op, cur[e], rhs[e]));
         }
       } else {
         ew_unary_vec<T, W>(op, cur);
@@ -80,7 +80,7 @@ fused_chain_kernel(ChainDesc d, T* __restrict__ out, int64_t n_vec, int64_t nume
         const int op = d.ops[s];
         if (d.ext[s] >= 0) {
           const float rhs = to_f32(static_cast<const T*>(d.in[d.ext[s]])[i]);
-          cur = round_through<T>(ew_binary(op, cur, rhs));
+          cur = round_through<T>(ew_binary_any(op, cur, rhs));
         } else {
           cur = round_through<T>(ew_unary(op, cur));
         }

@@ -26,8 +26,8 @@ inline int make_epilogue(const fb200_epilogue* e, EpilogueDev* out, const char* 
                      e->n_ops, FB200_MAX_CHAIN);
   }
   for (int i = 0; i < e->n_ops; ++i) {
-    if (!ew_is_known(e->ops[i])) {
-      return set_error(FB200_UNIMPLEMENTED, "%s: unknown epilogue op code %d", who, e->ops[i]);
+    if (!ew_is_known(e->ops[i]) || !ew_epilogue_ok(e->ops[i])) {
+      return set_error(FB200_UNIMPLEMENTED, "%s: op code %d cannot be an epilogue step", who, e->ops[i]);
     }
     if (ew_is_binary(e->ops[i])) {
       if (e->operands[i] == nullptr) {

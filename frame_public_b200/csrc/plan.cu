@@ -548,6 +548,9 @@ static void optimise(fb200_plan* p) {
       Step& t = p->steps[j];
       if (t.kind != Kind::kChain && t.kind != Kind::kBiasAdd) break;
       if (t.in.empty() || t.out.size() != 1) break;
+      bool epilogue_ok = true;   // relu_grad_internal stays a chain of its own
+      for (int c : t.chain_ops) epilogue_ok = epilogue_ok && ew_epilogue_ok(c);
+      if (!epilogue_ok) break;
       // The contraction's result must be operand 0 of the group; add and mul commute exactly,
       // so a leading binary step may also take it as operand 1.
       size_t lhs_index = 0;

@@ -119,7 +119,7 @@ typedef enum fb200_ew_op {
   FB200_EW_SOFTPLUS = 10,
   FB200_EW_EXP = 11,
   FB200_EW_HEAVISIDE = 12,  /* heaviside_surrogate forward: x >= 0 ? 1 : 0 (src/backends/cpu/kernels/elementwise.cpp, heaviside_surrogate_cpu_kernel) */
-  FB200_EW_RELU_GRAD = 13   /* relu_grad_internal(x, gy): x > 0 ? gy : 0, binary and NOT commutative: the running value is x, the operand gy (elementwise.cpp:411-414) */
+  FB200_EW_RELU_GRAD = 13   /* relu_grad_internal(x, gy): x > 0 ? gy : 0, binary and NOT commutative: the running value is x, the operand gy (elementwise.cpp:411-414); elementwise chains only, not a matmul / conv2d epilogue step */
 } fb200_ew_op;
 #define FB200_MAX_CHAIN 8
 #define FB200_MAX_CHAIN_INPUTS 9
