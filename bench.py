@@ -166,8 +166,23 @@ class ClockSampler:
         self.device = device
         self.proc = None
         self.lines = []
+        self.nvml = None        # (module, handle) when NVML can be polled in-process
+        self.samples = []       # (time, sm MHz, max sm MHz, reasons bitmask)
+        self._stop = False
 
     def start(self):
+        # NVML polled every 2 ms from a thread (read-only queries): a 20-step timed region lasts
+        # tens of milliseconds, which a 100 ms nvidia-smi loop samples once or not at all.
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            handle = pynvml.nvmlDeviceGetHandleByIndex(self.device)
+            pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)
+            self.nvml = (pynvml, handle)
+            threading.Thread(target=self._poll, daemon=True).start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
@@ -176,11 +191,41 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def _poll(self):
+        pynvml, handle = self.nvml
+        try:
+            mx = pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            mx = None
+        while not self._stop:
+            try:
+                sm = pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)
+                try:
+                    why = pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle)
+                except Exception:
+                    why = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle)
+                self.samples.append((time.time(), float(sm), float(mx) if mx else None, int(why)))
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def _stop_nvml(self, t0, t1):
+        self._stop = True
+        names = ((0x8, "hw_slowdown"), (0x40, "hw_thermal_slowdown"), (0x20, "sw_thermal_slowdown"), (0x4, "sw_power_cap"))
+        inside = [x for x in self.samples if t0 <= x[0] <= t1] or self.samples[-3:]
+        sm = [x[1] for x in inside]
+        mx = [x[2] for x in inside if x[2] is not None]
+        reasons = sorted({name for x in inside for bit, name in names if x[3] & bit})
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm), "source": "nvml, 2 ms poll"}
+
     def _read(self):
         for line in self.proc.stdout:
             self.lines.append((time.time(), line.strip()))
 
     def stop(self, t0, t1):
+        if self.nvml is not None:
+            return self._stop_nvml(t0, t1)
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         time.sleep(0.15)
