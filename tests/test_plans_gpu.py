@@ -164,3 +164,26 @@ def test_training_graph_of_the_reference_autograd_runs_bit_identically():
             exp = gold[f"train_mlp_f32__{i}"]
             assert np.array_equal(np.asarray(got).reshape(-1).view(np.uint8), np.asarray(exp).reshape(-1).view(np.uint8)), i
     plan.close()
+
+
+def test_tensor_core_matmul_gradient_inside_a_replayed_plan():
+    """matmul_grad_lhs_internal on the tensor-core route (bf16: scratch transpose from the
+    stream-ordered allocator + tcgen05 GEMM) as a plan step: the allocation and the free are part of
+    the captured CUDA graph, so the replays must keep producing the same result."""
+    m, n, k = 512, 384, 256
+    text = (f"plan slots=3 arena=0\nin 0 3 2 {m} {n}\nin 1 3 2 {k} {n}\n"
+            f"step matmul_grad_lhs_internal nin=2 0 1 nout=1 2 3 -1 2 {m} {k} attrs=0\nout 2\n")
+    rng = np.random.default_rng(41)
+    gy = fo.from_accum(rng.uniform(-1, 1, (m, n)).astype(np.float32), fo.DT_BF16)
+    b = fo.from_accum(rng.uniform(-1, 1, (k, n)).astype(np.float32), fo.DT_BF16)
+    exp = fo.matmul_grad_lhs(gy, b, fo.DT_BF16)
+    plan = runtime.CompiledPlan(text, 0)
+    first = None
+    for _ in range(4):
+        (got,) = plan.run_host([gy, b])
+        assert capi.kernel_status(0) == 0
+        assert fo.all_close(got, exp, fo.DT_BF16, rtol=2e-2, atol=2e-2), fo.max_err(got, exp, fo.DT_BF16)
+        if first is None:
+            first = got.copy()
+        assert np.array_equal(got, first)
+    plan.close()
