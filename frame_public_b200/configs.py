@@ -311,3 +311,87 @@ def small_workloads(backend: str = "cpu") -> List[Workload]:
         transformer_block(batch=2, seq=128, d_model=128, heads=2, ffn=256, backend=backend),
         mamba_block(batch=2, seq=24, d_model=16, d_state=16, dt_rank=4, backend=backend),
     ]
+
+
+# ---- slabs of the full-size workloads -------------------------------------------------------------
+# Every op on the path is row / sample independent, so the first sample (or the first rows of A)
+# of a full-size run depends only on its own inputs: the CPU backend can compute that slab in
+# seconds to a minute, and the full-size GPU result must agree with it on those rows.
+FULL_BUILDERS = {
+    "mlp": (mlp, dict()),
+    "gemm_bf16": (gemm_epilogue, dict(n=8192, dtype=BF16)),
+    "gemm_f32": (gemm_epilogue, dict(n=8192, dtype=F32)),
+    "conv_stack": (conv_stack, dict()),
+    "transformer": (transformer_block, dict()),
+    "mamba": (mamba_block, dict()),
+}
+GEMM_SLAB_ROWS = 16
+
+
+def slab_graph(key: str, backend: str = "cpu") -> str:
+    """IR text of the slab graph of a full-size workload: the same graph at batch 1 (GEMM: the first
+    GEMM_SLAB_ROWS rows of A; MLP: the whole batch)."""
+    builder, kw = FULL_BUILDERS[key]
+    if key == "mlp":
+        return builder(backend=backend, **kw).ir_text
+    if key.startswith("gemm"):
+        dt = irtext.DTYPE_NAMES[kw["dtype"]]
+        n = kw["n"]
+        g = irtext.IrGraph(backend)
+        va, vb, vbias = g.input(dt, (GEMM_SLAB_ROWS, n)), g.input(dt, (n, n)), g.input(dt, (GEMM_SLAB_ROWS, n))
+        g.output(g.unary("gelu", g.add(g.matmul(va, vb), vbias)))
+        return g.text()
+    small = dict(kw)
+    small["batch"] = 1
+    return _graph_text_only(builder, backend=backend, **small)
+
+
+def _graph_text_only(builder, **kw) -> str:
+    """The graph text of a builder without paying for its random inputs."""
+    class Zero:
+        def standard_normal(self, shape):
+            return np.zeros(shape, np.float32)
+
+        def normal(self, a, b, shape):
+            return np.zeros(shape, np.float32)
+
+        def uniform(self, a, b, shape):
+            return np.full(shape, 0.5 * (a + b), np.float64)
+
+    real = np.random.default_rng
+    np.random.default_rng = lambda seed=None: Zero()
+    try:
+        return builder(**kw).ir_text
+    finally:
+        np.random.default_rng = real
+
+
+def slab_inputs(key: str, full_inputs: List[np.ndarray]) -> List[np.ndarray]:
+    """The slab's inputs cut out of the full-size inputs (graph-input order is unchanged)."""
+    ins = list(full_inputs)
+    if key == "mlp":
+        return ins
+    if key.startswith("gemm"):
+        return [ins[0][:GEMM_SLAB_ROWS], ins[1], ins[2][:GEMM_SLAB_ROWS]]
+    builder, kw = FULL_BUILDERS[key]
+    if key == "conv_stack":
+        ins[0] = ins[0][:1]
+    else:   # transformer, mamba: activations are [batch * seq, d_model]
+        import inspect
+        seq = inspect.signature(builder).parameters["seq"].default
+        ins[0] = ins[0][:seq]
+    return [np.ascontiguousarray(a) for a in ins]
+
+
+def slab_of_output(key: str, full_output: np.ndarray) -> np.ndarray:
+    """The rows of a full-size result that the slab graph computes."""
+    if key == "mlp":
+        return full_output
+    if key.startswith("gemm"):
+        return full_output[:GEMM_SLAB_ROWS]
+    builder, _ = FULL_BUILDERS[key]
+    if key == "conv_stack":
+        return full_output[:1]
+    import inspect
+    seq = inspect.signature(builder).parameters["seq"].default
+    return full_output[:seq]
