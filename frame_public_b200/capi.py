@@ -62,6 +62,7 @@ SIGNATURES = {
     "fb200_launch_count": (c_int64, []),
     "fb200_kernel_status": (c_int, [c_int, _IP]),
     "fb200_device_count": (c_int, [_IP]),
+    "fb200_device_pci_bus_id": (c_int, [c_int, c_char_p, c_int]),
     "fb200_malloc": (c_int, [c_int, c_size_t, c_size_t, _PP]),
     "fb200_free": (c_int, [c_int, _P]),
     "fb200_host_alloc": (c_int, [c_size_t, _PP]),
@@ -133,6 +134,7 @@ SIGNATURES = {
     "fb200_plan_step_op": (c_char_p, [_P, c_int]),
     "fb200_plan_run_host_async": (c_int, [_P, _PP, _PP, _P]),
     "fb200_plan_host_sync": (c_int, [_P]),
+    "fb200_plan_bind_resident": (c_int, [_P, c_int, _P]),
     "fb200_plan_describe": (c_int, [c_char_p, c_int, _PP]),
 }
 

@@ -395,3 +395,21 @@ def slab_of_output(key: str, full_output: np.ndarray) -> np.ndarray:
     import inspect
     seq = inspect.signature(builder).parameters["seq"].default
     return full_output[:seq]
+
+
+def parity_tolerance(key: str, dtype: int, allow_tf32: bool, gold_f32: np.ndarray, inputs=None) -> Dict[str, float]:
+    """rtol/atol of |got - expected| <= atol + rtol*|expected| for a slab comparison, by the
+    reference's tiers (tests/cpp/common/tolerance.h:41-98 of the reference): bf16 2e-2 / 2e-3; strict
+    fp32 1e-5 / 1e-6; fp32 on the tensor cores rtol 1e-3 plus an absolute term for outputs that cancel
+    to near zero: 2e-3 * sqrt(K) * rms(a) * rms(b) for one GEMM, 5e-3 of the expected rms for graphs
+    that chain several TF32 contractions."""
+    if dtype == BF16:
+        return dict(rtol=2e-2, atol=2e-3)
+    if not allow_tf32:
+        return dict(rtol=1e-5, atol=1e-6)
+    if key.startswith("gemm") and inputs is not None:
+        a, b = np.asarray(inputs[0][:64], np.float64), np.asarray(inputs[1][:, :64], np.float64)
+        k = inputs[1].shape[0]
+        return dict(rtol=1e-3, atol=float(2e-3 * np.sqrt(k) * np.sqrt((a ** 2).mean()) * np.sqrt((b ** 2).mean())))
+    rms = float(np.sqrt(np.mean(np.square(np.asarray(gold_f32, np.float64)))))
+    return dict(rtol=1e-3, atol=max(1e-4, 5e-3 * rms))

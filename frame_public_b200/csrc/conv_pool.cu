@@ -335,8 +335,7 @@ extern "C" int fb200_conv2d(const void* x, const void* w, const void* bias, void
     return set_error(FB200_INVALID_ARGUMENT, "conv2d: null argument");
   }
   if (allow_tf32 && dtype == FB200_F32) {
-    static const bool no_halo = getenv("FRAME_B200_CONV_GATHER") != nullptr;   // measurement knob
-    if (!no_halo) {
+    {
       const int rc = fb200_conv2d_halo_tcgen05(x, w, bias, out, pp, dtype, epilogue, stream);
       if (rc != FB200_UNIMPLEMENTED) return rc;
     }

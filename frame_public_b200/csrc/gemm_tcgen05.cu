@@ -51,24 +51,9 @@ using namespace sm100;
 constexpr int kBlockM = 128;
 constexpr int kGemmThreads = 352;   // A-producer warp, MMA warp, eight epilogue warps, B-producer warp
 constexpr int kGemmBProducerWarp = 10;
-// M-blocks per group of the tile walk; FRAME_B200_GEMM_GROUP_M overrides it for measurements.
-static int gemm_group_m() {
-  static const int v = [] {
-    const char* e = getenv("FRAME_B200_GEMM_GROUP_M");
-    const int g = e != nullptr ? atoi(e) : 0;
-    return g >= 1 && g <= 1024 ? g : 16;   // 8: 1345, 16: 1362, 32: 1335, 64: 1278 TFLOP/s at 8192^3 bf16
-  }();
-  return v;
-}
-
-// FRAME_B200_GEMM_MH=1 keeps every GEMM on 128-row tiles (for measurements).
-static int gemm_m_halves() {
-  static const int v = [] {
-    const char* e = getenv("FRAME_B200_GEMM_MH");
-    return (e != nullptr && atoi(e) == 1) ? 1 : 2;
-  }();
-  return v;
-}
+// M-blocks per group of the tile walk (8192^3 bf16: groups of 8 gave 1345, 16: 1362, 32: 1335,
+// 64: 1278 TFLOP/s).
+constexpr int kGemmGroupM = 16;
 
 // An epilogue of binary ops, ReLU, square and the step function: a few instructions per element.
 static bool light_epilogue(const EpilogueDev& epi) {
@@ -590,7 +575,7 @@ static int launch_tc_n(const void* a, const void* b, const GemmDest& c, int64_t 
     const int64_t waves1 = (tiles(256) + kNumSMs - 1) / kNumSMs, waves2 = (t2 + kNumSMs - 1) / kNumSMs;
     // The exposed epilogue costs about 8-10 K cycles per tile against a gain of 6-11 % of the mainloop:
     // only worth it from 128 k-blocks per tile on (measured slower at K = 768 and 1536 TF32).
-    if (gemm_m_halves() == 2 && light_epilogue(epi) && m > 128 && k * ELT >= 128 * 128 && t2 >= kNumSMs &&
+    if (light_epilogue(epi) && m > 128 && k * ELT >= 128 * 128 && t2 >= kNumSMs &&
         16 * waves2 <= 9 * waves1) {
       return launch_tc<T, ELT, 256, 2>(a, b, c, m, n, k, dtype, epi, s);
     }
@@ -642,7 +627,7 @@ extern "C" int fb200_matmul(const void* a, const void* b, void* c, int64_t m, in
   cudaStream_t s = as_stream(stream);
   if (k > 0 && tensor_core_eligible(a, b, c, m, n, k, dtype, allow_tf32)) {
     GemmDest dest{};
-  dest.group_m = gemm_group_m();
+    dest.group_m = kGemmGroupM;
     dest.ptr[0] = c;
     dest.n = 1;
     dest.ld = n;
@@ -694,7 +679,7 @@ extern "C" int fb200_matmul_colsplit(const void* a, const void* b_local, void* c
   EpilogueDev epi{};
   if (int rc = make_epilogue(epilogue, &epi, "matmul_colsplit")) return rc;
   GemmDest dest{};
-  dest.group_m = gemm_group_m();
+  dest.group_m = kGemmGroupM;
   for (int d = 0; d < n_dest; ++d) {
     if (c_dest[d] == nullptr) return set_error(FB200_INVALID_ARGUMENT, "matmul_colsplit: destination %d is null", d);
     dest.ptr[d] = c_dest[d];

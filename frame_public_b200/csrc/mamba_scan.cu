@@ -282,19 +282,8 @@ mamba_scan_pipe_kernel(const float* __restrict__ u, const float* __restrict__ de
   }
 }
 
-// Lanes per channel for a state size; FRAME_B200_MAMBA_LANES (1, 2 or 4) overrides it for
-// measurements.
-static int mamba_lanes(int64_t nstate) {
-  static const int forced = [] {
-    const char* e = getenv("FRAME_B200_MAMBA_LANES");
-    return e != nullptr ? atoi(e) : 0;
-  }();
-  const int natural = nstate >= 16 ? 2 : (nstate >= 8 ? 2 : 1);
-  if (forced == 1 || forced == 2 || forced == 4) {
-    if (nstate / forced >= 4) return forced;
-  }
-  return natural;
-}
+// Lanes per channel for a state size: two lanes with nstate / 2 states each from 8 states on.
+static int mamba_lanes(int64_t nstate) { return nstate >= 8 ? 2 : 1; }
 
 }  // namespace fb200
 
@@ -329,7 +318,7 @@ extern "C" int fb200_mamba_scan(const void* u, const void* delta, const void* A,
   dim3 grid(static_cast<unsigned>((dm + per_cta - 1) / per_cta), static_cast<unsigned>(batch));
   const int cw = 32 / lanes;
   const bool piped = dm % cw == 0 && dm % 4 == 0 && aligned16(u) && aligned16(delta) &&
-                     (z == nullptr || aligned16(z)) && getenv("FRAME_B200_MAMBA_DIRECT") == nullptr;
+                     (z == nullptr || aligned16(z));
   if (piped) grid.x = static_cast<unsigned>((dm / cw + kMambaThreads / 32 - 1) / (kMambaThreads / 32));
 #define FB200_MAMBA_LAUNCH(NS, LN)                                                                   \
   do {                                                                                               \

@@ -114,6 +114,9 @@ struct fb200_plan {
   cudaStream_t s_h2d = nullptr, s_d2h = nullptr;
   cudaEvent_t ev_in[2] = {nullptr, nullptr}, ev_run[2] = {nullptr, nullptr}, ev_out[2] = {nullptr, nullptr};
   uint64_t host_runs = 0;
+  // inputs bound as device-resident parameters (fb200_plan_bind_resident): the host-buffer entry
+  // points read them where they lie instead of copying them in
+  std::vector<const void*> resident;
 };
 
 namespace fb200 {
@@ -912,7 +915,7 @@ static void fuse_attention_fans(fb200_plan* p) {
     if (ok && !p->dry) {
       const size_t bytes = table.size() * sizeof(fb200_attention_head);
       ok = fb200_malloc(p->device, bytes, 256, &dev_table) == FB200_OK &&
-           fb200_memcpy(p->device, dev_table, table.data(), bytes, FB200_H2D, nullptr, 0) == FB200_OK;
+           fb200_memcpy(p->device, dev_table, table.data(), bytes, FB200_H2D, nullptr, /*blocking*/ 1) == FB200_OK;
       if (!ok && dev_table) { fb200_free(p->device, dev_table); dev_table = nullptr; }
     }
     if (!ok) { PLAN_TRACE("fan of %zu heads ending at step %d: rejected by the byte-range checks", group.size(), pos); restore(); continue; }
@@ -1541,10 +1544,12 @@ extern "C" int fb200_plan_run_host(fb200_plan* p, const void* const* host_inputs
       }
     }
   }
+  std::vector<const void*> in(p->stage_in.begin(), p->stage_in.end());
   for (size_t i = 0; i < p->input_slots.size(); ++i) {
+    if (i < p->resident.size() && p->resident[i] != nullptr) { in[i] = p->resident[i]; continue; }
     if (int rc = fb200_memcpy(p->device, p->stage_in[i], host_inputs[i], p->slots[p->input_slots[i]].bytes(), FB200_H2D, stream, 0)) return rc;
   }
-  if (int rc = fb200_plan_run(p, p->stage_in.data(), p->stage_out.data(), stream)) return rc;
+  if (int rc = fb200_plan_run(p, in.data(), p->stage_out.data(), stream)) return rc;
   for (size_t i = 0; i < p->output_slots.size(); ++i) {
     if (int rc = fb200_memcpy(p->device, host_outputs[i], p->stage_out[i], p->slots[p->output_slots[i]].bytes(), FB200_D2H, stream, 0)) return rc;
   }
@@ -1625,14 +1630,16 @@ extern "C" int fb200_plan_run_host_async(fb200_plan* p, const void* const* host_
     k = p->host_runs++;
     b = static_cast<int>(k & 1);
   }
-  std::vector<void*>& in = b == 0 ? p->stage_in : p->stage_in2;
+  std::vector<void*>& stage = b == 0 ? p->stage_in : p->stage_in2;
+  std::vector<const void*> in(stage.begin(), stage.end());
   std::vector<void*>& out = b == 0 ? p->stage_out : p->stage_out2;
   cudaStream_t cs = as_stream(stream);
   // the staging inputs of this set were last read by run k-2
   if (k >= 2) FB200_CUDA_OK(cudaStreamWaitEvent(p->s_h2d, p->ev_run[b], 0));
   for (size_t i = 0; i < p->input_slots.size(); ++i) {
     const size_t bytes = p->slots[p->input_slots[i]].bytes();
-    if (bytes > 0) FB200_CUDA_OK(cudaMemcpyAsync(in[i], host_inputs[i], bytes, cudaMemcpyHostToDevice, p->s_h2d));
+    if (i < p->resident.size() && p->resident[i] != nullptr) { in[i] = p->resident[i]; continue; }
+    if (bytes > 0) FB200_CUDA_OK(cudaMemcpyAsync(stage[i], host_inputs[i], bytes, cudaMemcpyHostToDevice, p->s_h2d));
   }
   FB200_CUDA_OK(cudaEventRecord(p->ev_in[b], p->s_h2d));
   FB200_CUDA_OK(cudaStreamWaitEvent(cs, p->ev_in[b], 0));
@@ -1646,6 +1653,22 @@ extern "C" int fb200_plan_run_host_async(fb200_plan* p, const void* const* host_
     if (bytes > 0) FB200_CUDA_OK(cudaMemcpyAsync(host_outputs[i], out[i], bytes, cudaMemcpyDeviceToHost, p->s_d2h));
   }
   FB200_CUDA_OK(cudaEventRecord(p->ev_out[b], p->s_d2h));
+  return FB200_OK;
+}
+
+// Marks graph input `index` as a parameter that already lives on the device (weights, and the
+// reference's full-shape biases: a Frame module keeps them on the graph's device between runs).
+// fb200_plan_run_host and fb200_plan_run_host_async then read it in place and ignore the matching
+// host pointer; a null `device_ptr` restores the copy.  The caller keeps the buffer alive and
+// unchanged while runs are in flight.
+extern "C" int fb200_plan_bind_resident(fb200_plan* p, int index, const void* device_ptr) {
+  if (p == nullptr) return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_bind_resident: null plan");
+  if (index < 0 || static_cast<size_t>(index) >= p->input_slots.size()) {
+    return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_bind_resident: input %d out of range", index);
+  }
+  std::lock_guard<std::mutex> lock(p->mu);
+  if (p->resident.size() < p->input_slots.size()) p->resident.resize(p->input_slots.size(), nullptr);
+  p->resident[static_cast<size_t>(index)] = device_ptr;
   return FB200_OK;
 }
 

@@ -57,6 +57,14 @@ int fb200_device_count(int* count) {
   return FB200_OK;
 }
 
+// PCI bus id ("0000:1b:00.0") of a CUDA device ordinal: what identifies the same physical GPU to
+// NVML and nvidia-smi, whose own indices ignore CUDA_VISIBLE_DEVICES.
+int fb200_device_pci_bus_id(int device, char* buf, int len) {
+  if (buf == nullptr || len < 16) return set_error(FB200_INVALID_ARGUMENT, "fb200_device_pci_bus_id: buffer of at least 16 bytes");
+  FB200_CUDA_OK(cudaDeviceGetPCIBusId(buf, len, device));
+  return FB200_OK;
+}
+
 int fb200_malloc(int device, size_t bytes, size_t alignment, void** ptr) {
   if (ptr == nullptr) return set_error(FB200_INVALID_ARGUMENT, "fb200_malloc: null out pointer");
   *ptr = nullptr;

@@ -163,10 +163,12 @@ int scan_chunked_launch(const void* x, const void* a, const void* b, const void*
                         float2* scratch, cudaStream_t s) {
   const int64_t jobs = rows * chunks;
   const int grid = grid_for(jobs * 32, kChunkThreads, 8);
-  scan_chunk_summary_kernel<T><<<grid, kChunkThreads, 0, s>>>(
-      static_cast<const T*>(x), static_cast<const T*>(a), static_cast<const T*>(b), scratch, rows, steps,
-      chunks, chunk_len);
-  if (int rc = after_launch("scan_chunk_summary_kernel")) return rc;
+  if (chunks > 1) {   // with one chunk per row the apply pass reads no summary: nothing to fold
+    scan_chunk_summary_kernel<T><<<grid, kChunkThreads, 0, s>>>(
+        static_cast<const T*>(x), static_cast<const T*>(a), static_cast<const T*>(b), scratch, rows, steps,
+        chunks, chunk_len);
+    if (int rc = after_launch("scan_chunk_summary_kernel")) return rc;
+  }
   scan_chunk_apply_kernel<T><<<grid, kChunkThreads, 0, s>>>(
       static_cast<const T*>(x), static_cast<const T*>(a), static_cast<const T*>(b),
       static_cast<const T*>(c), static_cast<const T*>(d), static_cast<T*>(out), scratch, rows, steps,

@@ -5,9 +5,13 @@
 # resolved at load time by the Frame build of the host process (a Frame built with
 # FRAME_ENABLE_CUDA=OFF), exactly like any other backend plugin.
 #
-#   usage: frame_public_b200/host/build_adapter.sh [FRAME_ROOT]     (default /root/reference)
+#   usage: frame_public_b200/host/build_adapter.sh FRAME_ROOT     (or set FRAME_REFERENCE_ROOT)
 set -euo pipefail
-FRAME_ROOT="${1:-/root/reference}"
+FRAME_ROOT="${1:-${FRAME_REFERENCE_ROOT:-}}"
+if [ -z "$FRAME_ROOT" ]; then
+  echo "usage: build_adapter.sh FRAME_ROOT   (or set FRAME_REFERENCE_ROOT): the root of a Frame source tree" >&2
+  exit 2
+fi
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 PKG="$(dirname "$HERE")"
 ROOT="$(dirname "$PKG")"

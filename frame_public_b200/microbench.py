@@ -1,6 +1,6 @@
 """Times one kernel of libframe_b200.so through the C ABI with CUDA events, and prints one JSON
 line: launch time, algorithmic bytes or FLOPs per launch, achieved rate and the fraction of the
-measured peak (MEASURED_PEAKS.json at the repository root, when present).
+measured peak (the peaks file at the repository root, when present).
 
     python -m frame_public_b200.microbench --op scan_rows --rows 32768 --cols 2048 --dtype f32
     python -m frame_public_b200.microbench --op fused_add_relu --numel 67108864

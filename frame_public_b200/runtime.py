@@ -79,6 +79,11 @@ class CompiledPlan:
         b = (c_void_p * max(1, len(out_ptrs)))(*out_ptrs)
         capi.check(self.lib.fb200_plan_run_host_async(self._h, a, b, stream))
 
+    def bind_resident(self, index: int, device_ptr) -> None:
+        """Input `index` is a parameter that already lives on the device: the host-buffer entry points
+        read it in place instead of copying it in."""
+        capi.check(self.lib.fb200_plan_bind_resident(self._h, index, device_ptr))
+
     def host_sync(self) -> None:
         capi.check(self.lib.fb200_plan_host_sync(self._h))
 

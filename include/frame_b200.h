@@ -78,6 +78,10 @@ FB200_API int fb200_kernel_status(int device, int* code);
  * (include/frame/hal/backend.h:77-109) and hal::Allocator (include/frame/hal/allocator.h:13-21);
  * replaces src/backends/cuda/cuda_backend.cpp:68-312 and cuda_allocator.cpp:26-66. */
 FB200_API int fb200_device_count(int* count);
+/* PCI bus id of CUDA device `device` as text (at least 16 bytes): the key under which NVML and
+ * nvidia-smi know the same physical GPU (their indices ignore CUDA_VISIBLE_DEVICES).  The
+ * reference has no counterpart (include/frame/core/device.h:19-24 carries an ordinal only). */
+FB200_API int fb200_device_pci_bus_id(int device, char* buf, int len);
 /* bytes > 0, alignment a power of two <= 256 (cuda_allocator.cpp:26-41). */
 FB200_API int fb200_malloc(int device, size_t bytes, size_t alignment, void** ptr);
 FB200_API int fb200_free(int device, void* ptr);
@@ -426,6 +430,13 @@ FB200_API int fb200_plan_run_host(fb200_plan* plan, const void* const* host_inpu
 FB200_API int fb200_plan_run_host_async(fb200_plan* plan, const void* const* host_inputs,
                                         void* const* host_outputs, fb200_stream stream);
 FB200_API int fb200_plan_host_sync(fb200_plan* plan);
+/* Marks graph input `index` as a parameter that already lives on the device: the two host-buffer
+ * entry points above then read `device_ptr` in place and ignore the matching host pointer (NULL
+ * restores the copy).  This is how Frame itself runs a module: nn:: parameters, including the
+ * full-shape [batch, out] biases of nn::Linear (src/nn/layers.cpp:241-248), are device tensors the
+ * caller passes to Executable::run every time (include/frame/hal/executable.h:33); only the
+ * activations of a step travel.  The caller keeps the buffer alive while runs are in flight. */
+FB200_API int fb200_plan_bind_resident(fb200_plan* plan, int index, const void* device_ptr);
 
 /* Per-step device times (ms) of one eager run, measured with CUDA events on `stream`; steps that
  * launch nothing report 0.  For harness-side accounting of which kernel dominates a graph; has no

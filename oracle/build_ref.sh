@@ -4,7 +4,7 @@
 # oracle/_ref/ (git-ignored).  Nothing is copied from the reference tree; only
 # object files and one shared library are produced.
 #
-#   usage: oracle/build_ref.sh [REFERENCE_ROOT]      (default /root/reference)
+#   usage: oracle/build_ref.sh [REFERENCE_ROOT]      (default FRAME_ROOT)
 #
 # Product of this script:
 #   oracle/_ref/libframe_ref.so   core + ir + ops + schemas + compiler + passes +
@@ -26,7 +26,11 @@
 # src/backends/cpu/kernels/fft.cpp is skipped: it needs pocketfft, which the
 # reference downloads at configure time; rfft/irfft are not on the path.
 set -euo pipefail
-REF="${1:-/root/reference}"
+REF="${1:-${FRAME_REFERENCE_ROOT:-}}"
+if [ -z "$REF" ]; then
+  echo "usage: oracle/build_ref.sh FRAME_ROOT   (or set FRAME_REFERENCE_ROOT): the root of a Frame source tree" >&2
+  exit 2
+fi
 HERE="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 OUT="$HERE/_ref"
 OBJ="$OUT/obj"

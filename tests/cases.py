@@ -1,8 +1,8 @@
 """Seeded single-op parity cases shared by the golden-vector generator, the oracle pin tests
 (CPU) and the C-ABI parity tests (GPU).  Shapes follow the reference's own CUDA-vs-CPU
 differential tests (tests/cpp/backends/test_cuda_backend.cpp:1174-2345 of the reference: the
-1023/1024 vectorisation boundary, odd shapes, zero-size tensors) and the BASELINE configs in
-miniature.  Every case names the reference op, its attributes and its inputs in storage form
+1023/1024 vectorisation boundary, odd shapes, zero-size tensors) and the five benchmark workloads
+in miniature.  Every case names the reference op, its attributes and its inputs in storage form
 (uint16 bit patterns for bf16)."""
 from __future__ import annotations
 

@@ -44,16 +44,7 @@ def _record(row):
 
 
 def _tolerance(key, wl, tf32, gold):
-    if wl.dtype == configs.BF16:
-        return dict(rtol=2e-2, atol=2e-3)
-    if not tf32:
-        return dict(rtol=1e-5, atol=1e-6)
-    rms = float(np.sqrt(np.mean(np.square(gold.astype(np.float64)))))
-    if key == "gemm_f32":
-        a, b = wl.inputs[0][:64], wl.inputs[1][:, :64]
-        k = wl.inputs[1].shape[0]
-        return dict(rtol=1e-3, atol=2e-3 * np.sqrt(k) * float(np.sqrt((a ** 2).mean()) * np.sqrt((b ** 2).mean())))
-    return dict(rtol=1e-3, atol=max(1e-4, 5e-3 * rms))
+    return configs.parity_tolerance(key, wl.dtype, tf32, fo.to_accum(gold, wl.dtype), wl.inputs)
 
 
 @pytest.mark.parametrize("key", list(CASES))
