@@ -155,9 +155,10 @@ static int launch_chain(const ChainDesc& d, void* out, int64_t numel, bool vec_o
 
 using namespace fb200;
 
-extern "C" int fb200_fused_elementwise(const void* const* inputs, int n_inputs, void* out,
-                                       int64_t numel, int dtype, const int* ops,
-                                       const int* arities, int n_ops, fb200_stream stream) {
+// One launch: a chain of at most FB200_MAX_CHAIN steps.
+static int fused_chain_segment(const void* const* inputs, int n_inputs, void* out, int64_t numel,
+                               int dtype, const int* ops, const int* arities, int n_ops,
+                               fb200_stream stream) {
   if (n_ops < 1 || n_ops > FB200_MAX_CHAIN) {
     return set_error(FB200_INVALID_ARGUMENT,
                      "fused_elementwise: chain length %d outside [1, %d]", n_ops, FB200_MAX_CHAIN);
@@ -231,6 +232,46 @@ extern "C" int fb200_fused_elementwise(const void* const* inputs, int n_inputs, 
       return set_error(FB200_INVALID_ARGUMENT,
                        "fused_elementwise: dtype code %d is not float32/float16/bfloat16", dtype);
   }
+}
+
+// The reference's fusion pass builds chains of any length (src/compiler/passes/operator_fusion.cpp:
+// 140-157) and its executor runs them one sub-kernel at a time.  Here a group of up to
+// FB200_MAX_CHAIN steps is one launch; a longer group runs as successive launches of at most that
+// many steps, each continuing from `out` as its first operand (in place: every element is read and
+// written by the same thread), with the same rounding point at every step as the unfused ops.
+extern "C" int fb200_fused_elementwise(const void* const* inputs, int n_inputs, void* out,
+                                       int64_t numel, int dtype, const int* ops,
+                                       const int* arities, int n_ops, fb200_stream stream) {
+  if (n_ops < 1) return set_error(FB200_INVALID_ARGUMENT, "fused_elementwise: empty chain");
+  if (inputs == nullptr || ops == nullptr || arities == nullptr) {
+    return set_error(FB200_INVALID_ARGUMENT, "fused_elementwise: null argument");
+  }
+  if (n_ops <= FB200_MAX_CHAIN) {
+    return fused_chain_segment(inputs, n_inputs, out, numel, dtype, ops, arities, n_ops, stream);
+  }
+  int total = 0;
+  for (int s = 0; s < n_ops; ++s) {
+    if (arities[s] != 1 && arities[s] != 2) {
+      return set_error(FB200_INVALID_ARGUMENT, "fused_elementwise: sub-op %d has arity %d", s, arities[s]);
+    }
+    total += s == 0 ? arities[s] : arities[s] - 1;
+  }
+  if (total != n_inputs) {
+    return set_error(FB200_INVALID_ARGUMENT, "fused_elementwise: chain needs %d external inputs, got %d", total, n_inputs);
+  }
+  int next_input = 0;
+  for (int s0 = 0; s0 < n_ops; s0 += FB200_MAX_CHAIN) {
+    const int count = n_ops - s0 < FB200_MAX_CHAIN ? n_ops - s0 : FB200_MAX_CHAIN;
+    const void* seg[FB200_MAX_CHAIN_INPUTS];
+    int n_seg = 0;
+    if (s0 > 0) seg[n_seg++] = out;   // the running value
+    for (int s = s0; s < s0 + count; ++s) {
+      const int take = s == 0 ? arities[s] : arities[s] - 1;
+      for (int t = 0; t < take; ++t) seg[n_seg++] = inputs[next_input++];
+    }
+    if (int rc = fused_chain_segment(seg, n_seg, out, numel, dtype, ops + s0, arities + s0, count, stream)) return rc;
+  }
+  return FB200_OK;
 }
 
 extern "C" int fb200_bias_add(const void* x, const void* bias, void* out, int64_t rows,

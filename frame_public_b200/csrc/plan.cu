@@ -1249,10 +1249,9 @@ static int run_step(fb200_plan* p, Step& s, const void* const* inputs, void* con
                                os.dims[0], os.dtype, in_slot(1).dtype, stream);
     }
     case Kind::kChain: {
-      const void* ptrs[FB200_MAX_CHAIN_INPUTS];
-      if (s.in.size() > FB200_MAX_CHAIN_INPUTS) return set_error(FB200_UNIMPLEMENTED, "op '%s': more than %d external inputs", s.op.c_str(), FB200_MAX_CHAIN_INPUTS);
+      std::vector<const void*> ptrs(s.in.size());   // groups longer than one launch's limit are split inside
       for (size_t i = 0; i < s.in.size(); ++i) ptrs[i] = in_ptr(i);
-      return fb200_fused_elementwise(ptrs, static_cast<int>(s.in.size()), out, os.numel, os.dtype,
+      return fb200_fused_elementwise(ptrs.data(), static_cast<int>(s.in.size()), out, os.numel, os.dtype,
                                      s.chain_ops.data(), s.chain_arity.data(),
                                      static_cast<int>(s.chain_ops.size()), stream);
     }
@@ -1372,6 +1371,10 @@ static int plan_create_impl(const char* plan_text, int device, int allow_tf32, i
   p->launches = 0;
   for (const Step& s : p->steps) {
     if (s.kind != Kind::kSkip && s.kind != Kind::kAlias && s.kind != Kind::kConstant && s.kind != Kind::kCopy) ++p->launches;
+    // a fused group longer than one launch's limit runs as successive launches
+    if (s.kind == Kind::kChain && s.chain_ops.size() > FB200_MAX_CHAIN) {
+      p->launches += static_cast<int>((s.chain_ops.size() - 1) / FB200_MAX_CHAIN);
+    }
   }
   *plan = p;
   return FB200_OK;

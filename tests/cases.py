@@ -306,6 +306,15 @@ def build_cases() -> List[Case]:
         zshape = shape[:-1] + (n // 2 + 1, 2)
         cases.append(Case(f"irfft_f32_{tag}", "irfft", F32, [rnd(zshape)], {"n": n},
                           lambda z, n=n: fo.irfft(z, n), new_op=True))
+    # a fused group longer than one launch holds (the reference's fusion pass builds chains of any
+    # length, src/compiler/passes/operator_fusion.cpp:140-157): 12 steps, 8 external inputs
+    long_chain = "add;relu;mul;square;add;relu;mul;add;relu;add;mul;relu"
+    long_ar = [2, 1, 2, 1, 2, 1, 2, 2, 1, 2, 2, 1]
+    for dt, tag in [(F32, "f32"), (BF16, "bf16")]:
+        ins = [rnd((9, 1023), dt, scale=0.8) for _ in range(sum(long_ar) - (len(long_ar) - 1))]
+        cases.append(Case(f"fused_long_chain_12_{tag}", "fused_elementwise_internal", dt, ins,
+                          {"ops": long_chain, "arities": long_ar},
+                          lambda *xs, dt=dt: fo.fused_elementwise(list(xs), long_chain, long_ar, dt), exact=True))
     return cases
 
 

@@ -130,3 +130,30 @@ def test_training_graph_through_the_reference_api_without_fallback():
     for op in ("matmul", "add", "relu", "mse_loss", "mse_loss_grad_internal", "matmul_grad_lhs_internal",
                "matmul_grad_rhs_internal", "relu_grad_internal", "constant"):
         assert ref_runtime.fallback_count(op, "cuda") == 0, f"op {op} fell back to the eager chain"
+
+
+def test_twelve_elementwise_ops_fuse_into_one_group_and_run():
+    """Twelve consecutive fusable ops: the reference's fusion pass makes ONE fused_elementwise_internal
+    node of them (it has no length limit), longer than a single launch of the plugin's chain kernel
+    holds; the plugin runs it as successive launches.  fp32 elementwise without libm: bit-identical to
+    the CPU backend, which runs the same group one sub-kernel at a time."""
+    from frame_public_b200 import irtext
+
+    def build(backend):
+        g = irtext.IrGraph(backend)
+        xs = [g.input("float32", (9, 1023)) for _ in range(8)]
+        v = g.unary("relu", g.add(xs[0], xs[1]))
+        v = g.unary("square", g.mul(v, xs[2]))
+        v = g.unary("relu", g.add(v, xs[3]))
+        v = g.unary("relu", g.add(g.mul(v, xs[4]), xs[5]))
+        v = g.unary("relu", g.mul(g.add(v, xs[6]), xs[7]))
+        g.output(v)
+        return g.text()
+
+    assert ref_runtime.pipeline_text(build("cpu"), "cpu").count("fused_elementwise_internal") == 1
+    rng = np.random.default_rng(77)
+    ins = [(rng.standard_normal((9, 1023)) * 0.8).astype(np.float32) for _ in range(8)]
+    (exp,) = ref_runtime.Compiled(build("cpu"), "cpu").run(ins)
+    (got,) = ref_runtime.Compiled(build("cuda"), "cuda").run(ins)
+    assert np.array_equal(got.view(np.uint8), exp.view(np.uint8))
+    assert ref_runtime.fallback_count("fused_elementwise_internal", "cuda") == 0

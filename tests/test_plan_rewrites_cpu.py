@@ -114,3 +114,18 @@ def test_training_graph_decodes_with_the_bias_add_absorbed():
                             "matmul_grad_lhs_internal", "matmul_grad_rhs_internal", "relu_grad_internal",
                             "matmul_grad_rhs_internal"]
     assert launches == 9
+
+
+def test_a_fused_group_longer_than_one_launch_is_split_not_rejected():
+    """12 elementwise steps in one fused group (the reference's fusion pass has no length limit):
+    the executor keeps it as one step that runs as two successive launches."""
+    ops = "add;relu;mul;square;add;relu;mul;add;relu;add;mul;relu"
+    ar = [2, 1, 2, 1, 2, 1, 2, 2, 1, 2, 2, 1]
+    n_in = sum(ar) - (len(ar) - 1)
+    lines = [f"plan slots={n_in + 1} arena=0"]
+    lines += [f"in {i} 0 2 9 1023" for i in range(n_in)]
+    lines += [f"step fused_elementwise_internal nin={n_in} " + " ".join(str(i) for i in range(n_in))
+              + f" nout=1 {n_in} 0 -1 2 9 1023 attrs=2",
+              "attr arities int64_array [" + ", ".join(map(str, ar)) + "]", f'attr ops string "{ops}"', f"out {n_in}"]
+    names, launches = runtime.describe_plan("\n".join(lines) + "\n")
+    assert names == ["fused_elementwise_internal"] and launches == 2
