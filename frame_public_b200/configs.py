@@ -252,7 +252,7 @@ def mamba_block(batch: int = 16, seq: int = 2048, d_model: int = 768, expand: in
 # The reference's OWN nn:: modules (include/frame/nn/layers.h:157-234), graphs emitted by its builder
 # where the reference is present (tests/golden/make_workload_golden.py): (golden name, module kind,
 # builder arguments, DTypeCode).  transformer: batch, seq, embed, heads, ffn, with_bias; mamba: batch,
-# steps, channels, kernel.
+# steps, channels, kernel; cnn: batch, input channels, image size, conv channels, classes.
 def train_mlp_forward(batch: int = 16, d_in: int = 32, hidden: int = 24, d_out: int = 8, dtype: int = F32,
                       backend: str = "cpu"):
     """Forward graph of a two-layer MLP with an MSE loss, as IR text, and its seeded inputs
@@ -285,6 +285,10 @@ NN_GRAPHS = [
     ("nn_transformer_bf16_b2_s128_e128_h2", "transformer", (2, 128, 128, 2, 256, True), BF16),
     ("nn_transformer_f32_b2_s16_e32_h2", "transformer", (2, 16, 32, 2, 64, True), F32),
     ("nn_mamba_f32_b2_c16_s24_k4", "mamba", (2, 24, 16, 4, 0, True), F32),
+    # nn::Sequential CNN (conv2d + bias, relu, max_pool2d, flatten = reshape, linear): the reference's
+    # own golden shape, and a wider one that the tensor-core conv takes under allow_tf32
+    ("nn_cnn_f32_b8_c1_hw8_o4", "cnn", (8, 1, 8, 4, 1, True), F32),
+    ("nn_cnn_f32_b4_c16_hw32_o32", "cnn", (4, 16, 32, 32, 10, True), F32),
 ]
 
 

@@ -65,6 +65,7 @@ def load():
         s.fref_fallback_count.argtypes = [c_char_p, c_char_p]
         s.fref_has_kernel.argtypes = [c_char_p, c_char_p]
         s.fref_has_backend.argtypes = [c_char_p]
+        s.fref_hal_conformance.argtypes = [c_char_p, c_char_p, c_int]
         _shim = s
     return _shim
 
@@ -190,6 +191,13 @@ def has_kernel(op: str, backend: str) -> bool:
 
 def has_backend(backend: str) -> bool:
     return bool(load().fref_has_backend(backend.encode()))
+
+
+def hal_conformance(backend: str):
+    """(failed cases, report lines) of the HAL contract check on the backend's C++ classes."""
+    buf = create_string_buffer(4096)
+    failed = int(load().fref_hal_conformance(backend.encode(), buf, len(buf)))
+    return failed, buf.value.decode().splitlines()
 
 
 _plugin = None

@@ -30,6 +30,7 @@
 #include <frame/core/tensor.h>
 #include <frame/hal/allocator.h>
 #include <frame/hal/backend.h>
+#include <frame/hal/event.h>
 #include <frame/hal/executable.h>
 #include <frame/hal/stream.h>
 #include <frame/ir/graph.h>
@@ -97,7 +98,19 @@ size_t spec_bytes(const frame::hal::IoSpec& spec) {
   return static_cast<size_t>(spec.shape.numel()) * spec.dtype.itemsize();
 }
 
+// An op with a schema and no kernel on any backend: what Backend::compile must reject by name.
+constexpr std::string_view kOrphanOp = "fref_shim_op_without_kernel";
+
+Result<std::vector<frame::Shape>> infer_orphan(const frame::ops::NodeContext& ctx) {
+  if (ctx.input_types.size() != 1) {
+    return Status::make(frame::ErrorCode::kInvalidArgument, "op 'fref_shim_op_without_kernel' expects 1 input");
+  }
+  return std::vector<frame::Shape>{ctx.input_types[0].shape};
+}
+
 }  // namespace
+
+FRAME_REGISTER_OP(kOrphanOp).input("x", "input").output("out", "never given a kernel").shape_infer(&infer_orphan);
 
 extern "C" {
 
@@ -246,7 +259,8 @@ void* fref_device_buffer(void* handle, int is_output, int index) {
 // module's parameters follow in Module::parameters() order.  kind: "transformer" =
 // nn::TransformerEncoderBlock(batch, seq, embed, heads, ffn, with_bias), x: [batch*seq, embed];
 // "mha" = nn::MultiheadAttention(batch, seq, embed, heads, with_bias); "mamba" =
-// nn::Mamba(batch, channels = p2, steps = p1, kernel = p3), x: [batch, channels, steps].
+// nn::Mamba(batch, channels = p2, steps = p1, kernel = p3), x: [batch, channels, steps]; "cnn" =
+// nn::Sequential of Conv2d, Relu, MaxPool2d, Flatten, Linear, x: [batch, p1, p2, p2].
 // Returns the number of bytes needed, -1 on error.
 int64_t fref_nn_graph_text(const char* kind, int64_t batch, int64_t p1, int64_t p2, int64_t p3,
                            int64_t p4, int with_bias, int dtype_code, const char* backend,
@@ -270,6 +284,16 @@ int64_t fref_nn_graph_text(const char* kind, int64_t batch, int64_t p1, int64_t 
   } else if (k == "mamba") {
     module = frame::nn::Mamba("mamba", batch, p2, p1, p3, dtype);
     x_shape = frame::Shape({batch, p2, p1});
+  } else if (k == "cnn") {
+    // nn::Sequential{Conv2d 3x3 s1 p1 + bias, Relu, MaxPool2d 2x2 s2, Flatten, Linear}: the reference's
+    // own CNN (tests/cpp/nn/test_cnn_convergence.cpp:83-100; golden cnn_forward_expected.txt).
+    // p1 = input channels, p2 = image height = width, p3 = conv output channels, p4 = classes
+    const int64_t flat = p3 * (p2 / 2) * (p2 / 2);
+    module = frame::nn::Sequential(
+        "cnn", {frame::nn::Conv2d("conv", p1, p3, {3, 3}, {1, 1}, {1, 1}, 1, true, dtype), frame::nn::Relu("relu"),
+                frame::nn::MaxPool2d("pool", {2, 2}, {2, 2}, {0, 0}), frame::nn::Flatten("flatten"),
+                frame::nn::Linear("linear", batch, flat, p4, with_bias != 0, dtype)});
+    x_shape = frame::Shape({batch, p1, p2, p2});
   } else {
     set_err(err, errlen, "unknown module kind");
     return -1;
@@ -444,6 +468,116 @@ void fref_fallback_reset() { frame::runtime::FallbackStats::instance().reset(); 
 
 int fref_has_kernel(const char* op, const char* backend) {
   return frame::ops::KernelRegistry::instance().find(op, backend).is_ok() ? 1 : 0;
+}
+
+// The contract every registered hal::Backend must meet, checked on the C++ classes behind
+// BackendRegistry::get(backend): the eight cases of the reference's parameterised conformance suite
+// (tests/cpp/hal_conformance/test_hal_conformance.cpp:96-269), restated here because that suite needs
+// GoogleTest.  Returns the number of failed cases; `report` receives one "ok <case>" or
+// "FAIL <case>: <why>" line per case.
+int fref_hal_conformance(const char* backend, char* report, int cap) {
+  std::string text;
+  int failed = 0;
+  auto note = [&](const char* name, bool ok, const std::string& why = "") {
+    text += (ok ? std::string("ok ") : std::string("FAIL ")) + name + (ok || why.empty() ? "" : ": " + why) + "\n";
+    if (!ok) ++failed;
+  };
+  Result<frame::hal::Backend*> got = frame::hal::BackendRegistry::instance().get(backend);
+  note("get_returns_backend_with_matching_name", got.is_ok() && got.value()->name() == std::string_view(backend));
+  if (!got.is_ok()) {
+    if (report != nullptr && cap > 0) std::snprintf(report, static_cast<size_t>(cap), "%s", text.c_str());
+    return failed + 7;
+  }
+  frame::hal::Backend* b = got.value();
+  const Device dev{b->name(), 0};
+  {
+    Result<int32_t> n = b->device_count();
+    note("device_count_is_at_least_one", n.is_ok() && n.value() >= 1);
+  }
+  {
+    auto s = b->create_stream(dev);
+    note("create_stream_succeeds", s.is_ok(), s.is_ok() ? "" : std::string(s.status().message()));
+  }
+  {
+    auto e = b->create_event(dev);
+    const bool ok = e.is_ok() && e.value()->query() && e.value()->synchronize().is_ok();
+    note("unrecorded_event_reports_complete", ok);
+  }
+  {
+    auto s = b->create_stream(dev);
+    auto e = b->create_event(dev);
+    const bool ok = s.is_ok() && e.is_ok() && s.value()->record(*e.value()).is_ok() &&
+                    s.value()->wait(*e.value()).is_ok() && s.value()->synchronize().is_ok();
+    note("record_wait_synchronize_succeed", ok);
+  }
+  frame::hal::Allocator* alloc = b->allocator(dev);
+  {
+    bool ok = alloc != nullptr;
+    std::string why = ok ? "" : "null allocator";
+    if (ok) {
+      constexpr size_t kBytes = 256;
+      Result<void*> p = alloc->allocate(kBytes, 64);
+      ok = p.is_ok() && p.value() != nullptr && reinterpret_cast<std::uintptr_t>(p.value()) % 64 == 0;
+      if (ok) {
+        auto s = b->create_stream(dev);
+        std::vector<unsigned char> pattern(kBytes), back(kBytes, 0);
+        for (size_t i = 0; i < kBytes; ++i) pattern[i] = static_cast<unsigned char>(i * 13 + 0x21);
+        ok = s.is_ok() && b->copy(p.value(), dev, pattern.data(), frame::cpu_device(), kBytes, s.value().get()).is_ok() &&
+             b->copy(back.data(), frame::cpu_device(), p.value(), dev, kBytes, s.value().get()).is_ok() &&
+             s.value()->synchronize().is_ok() && std::memcmp(back.data(), pattern.data(), kBytes) == 0;
+        if (!ok) why = "bytes did not survive host -> device -> host";
+        alloc->deallocate(p.value());
+      } else {
+        why = "allocation failed or is not 64-byte aligned";
+      }
+    }
+    note("allocator_round_trip_at_alignment_64", ok, why);
+  }
+  {
+    bool ok = alloc != nullptr;
+    if (ok) {
+      constexpr size_t kBytes = 128;
+      Result<void*> a = alloc->allocate(kBytes, 64), c = alloc->allocate(kBytes, 64), d = alloc->allocate(kBytes, 64);
+      ok = a.is_ok() && c.is_ok() && d.is_ok();
+      if (ok) {
+        auto s = b->create_stream(dev);
+        std::vector<unsigned char> pattern(kBytes), back(kBytes, 0);
+        for (size_t i = 0; i < kBytes; ++i) pattern[i] = static_cast<unsigned char>(i * 5 + 9);
+        ok = s.is_ok() && b->copy(a.value(), dev, pattern.data(), frame::cpu_device(), kBytes, s.value().get()).is_ok() &&
+             b->copy(c.value(), dev, a.value(), dev, kBytes, s.value().get()).is_ok() &&
+             b->copy(d.value(), dev, c.value(), dev, kBytes, s.value().get()).is_ok() &&
+             b->copy(back.data(), frame::cpu_device(), d.value(), dev, kBytes, s.value().get()).is_ok() &&
+             s.value()->synchronize().is_ok() && std::memcmp(back.data(), pattern.data(), kBytes) == 0;
+      }
+      if (a.is_ok()) alloc->deallocate(a.value());
+      if (c.is_ok()) alloc->deallocate(c.value());
+      if (d.is_ok()) alloc->deallocate(d.value());
+    }
+    note("device_to_device_copies_preserve_bytes", ok);
+  }
+  {
+    frame::ir::Graph graph;
+    frame::ir::TensorType type;
+    type.dtype = frame::DType::of<float>();
+    type.shape = frame::Shape({4});
+    type.layout = frame::ir::Layout::kRowMajor;
+    type.device = dev;
+    bool ok = false;
+    std::string why = "graph construction failed";
+    auto in = graph.add_graph_input(type);
+    if (in.is_ok()) {
+      auto node = graph.create_node(std::string(kOrphanOp), {in.value()}, {type});
+      if (node.is_ok() && graph.mark_output(node.value(), 0).is_ok()) {
+        auto compiled = b->compile(graph, frame::hal::CompileOptions{});
+        ok = !compiled.is_ok() && compiled.status().code() == frame::ErrorCode::kUnimplemented &&
+             std::string(compiled.status().message()).find(std::string(kOrphanOp)) != std::string::npos;
+        why = compiled.is_ok() ? "compile accepted an op without a kernel" : std::string(compiled.status().message());
+      }
+    }
+    note("compile_rejects_unsupported_op_as_unimplemented_with_its_name", ok, why);
+  }
+  if (report != nullptr && cap > 0) std::snprintf(report, static_cast<size_t>(cap), "%s", text.c_str());
+  return failed;
 }
 
 int fref_has_backend(const char* backend) {
