@@ -408,6 +408,14 @@ def parity_tolerance(key: str, dtype: int, allow_tf32: bool, gold_f32: np.ndarra
     to near zero: 2e-3 * sqrt(K) * rms(a) * rms(b) for one GEMM, 5e-3 of the expected rms for graphs
     that chain several TF32 contractions."""
     if dtype == BF16:
+        if key == "transformer":
+            # A chain of bf16 nodes ending in residual adds: the reference's table has no tier beyond
+            # bf16 ("handled case by case by the caller", tolerance.h:63-80).  Every node stores bf16, so
+            # a different fp32 accumulation order inside a matmul can flip one rounding of an addend,
+            # and the sum then differs by one bf16 ulp OF THE ADDEND however small the sum is.  The
+            # absolute term is therefore one bf16 ulp at the largest magnitude of the residual stream.
+            top = float(np.max(np.abs(np.asarray(gold_f32, np.float64))))
+            return dict(rtol=2e-2, atol=float(2.0 ** (np.floor(np.log2(max(top, 1e-30))) - 7)))
         return dict(rtol=2e-2, atol=2e-3)
     if not allow_tf32:
         return dict(rtol=1e-5, atol=1e-6)

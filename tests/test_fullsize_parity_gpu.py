@@ -10,7 +10,9 @@ rtol 2e-2 / atol 2e-3; strict fp32 1e-5 / 1e-6; fp32 on the tensor cores (allow_
 an absolute term for outputs that cancel to near zero: 2e-3 * sqrt(K) * rms(a) * rms(b) for a single
 GEMM (= 2e-3 of the output's rms), and 5e-3 of the golden's rms for graphs that chain three or four
 TF32 contractions (operand errors of 2^-11 relative add up over the chain; the worst element of
-10^5..10^6 sits 4-5 standard deviations out).  Setting FRAME_B200_ERROR_TABLE=<file> appends the
+10^5..10^6 sits 4-5 standard deviations out).  The bf16 transformer block is a chain of bf16 nodes
+ending in residual adds: its absolute term is one bf16 ulp of the largest residual value (a flipped
+rounding of an addend), and at most 2 % of its elements may fall outside the single-op bf16 tier.  Setting FRAME_B200_ERROR_TABLE=<file> appends the
 measured errors of every case as JSON lines."""
 import json
 import os
@@ -65,8 +67,16 @@ def test_full_size_plan_matches_the_reference_cpu_slab(key):
             rows = rows[gold_file["mamba_rows"]]
         tol = _tolerance(key, wl, tf32, gold)
         max_abs, max_rel = fo.max_err(rows, gold, wl.dtype)
+        g64 = fo.to_accum(gold, wl.dtype).astype(np.float64)
+        err = np.abs(fo.to_accum(rows, wl.dtype).astype(np.float64) - g64)
+        base = dict(rtol=2e-2, atol=2e-3) if wl.dtype == configs.BF16 else tol
+        outside_base = float(np.mean(err > base["atol"] + base["rtol"] * np.abs(g64)))
         rms = float(np.sqrt(np.mean(np.square(fo.to_accum(gold, wl.dtype).astype(np.float64)))))
         _record({"case": key, "plan": plan_name, "allow_tf32": bool(tf32), "rows": int(rows.shape[0]),
-                 "max_abs": max_abs, "max_rel": max_rel, "gold_rms": rms, "rtol": tol["rtol"], "atol": float(tol["atol"])})
+                 "max_abs": max_abs, "max_rel": max_rel, "gold_rms": rms, "rtol": tol["rtol"], "atol": float(tol["atol"]),
+                 "fraction_outside_single_op_tier": outside_base})
         assert fo.all_close(rows, gold, wl.dtype, **tol), (key, tf32, max_abs, max_rel, rms, tol)
+        # the chain tolerance of the bf16 transformer block covers single flipped roundings only: all
+        # but a small share of the elements must still meet the single-op bf16 tier
+        assert outside_base <= 0.02, (key, outside_base)
         plan.close()

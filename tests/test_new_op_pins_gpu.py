@@ -5,7 +5,8 @@ the argument scaling, so the bound grows with |x|:
 
     |got - ref| <= (ulps + slope * |x|) * ulp32(ref) + cancel * 2^-24 * |x|
 
-fp32 `exp` itself goes through the accurate expf.  Every bound stays inside the fp32 tolerance tier
+softplus adds lg2.approx, whose absolute error of about 2^-22 is up to 20 ulps where the result is
+near 0.1.  fp32 `exp` itself goes through the accurate expf.  Every bound stays inside the fp32 tolerance tier
 (rtol 1e-5, atol 1e-6) the parity tests use; that tier is asserted as well."""
 import json
 import os
@@ -19,7 +20,7 @@ from frame_public_b200 import capi
 pytestmark = pytest.mark.gpu
 
 # (ulps, cancellation factor, ulps per unit of |x|)
-BOUNDS = {"gelu": (8, 6, 2.0), "silu": (8, 4, 2.0), "softplus": (12, 0, 2.0), "exp": (3, 0, 0.0)}
+BOUNDS = {"gelu": (8, 6, 2.0), "silu": (8, 4, 2.0), "softplus": (32, 0, 2.0), "exp": (3, 0, 0.0)}
 
 
 def _run(op, x):
