@@ -143,12 +143,12 @@ __device__ __forceinline__ float ew_unary(int op, float x) {
       // log1p(e^x) with the reference's cut-over to x above 20.  e = e^x through ex2.approx; for
       // small e the alternating series (error below e^6/6, 2e-7 relative at the switch point), else
       // log(1 + e) through lg2.approx, whose absolute error of 4e-7 is then below 5e-6 relative.
-      if (x > 20.0f) return x;
-      const float e = __expf(x);
-      if (e < 0.1f) {
-        return e * (1.0f - e * (0.5f - e * (0.33333334f - e * (0.25f - e * 0.2f))));
-      }
-      return __logf(1.0f + e);
+      // Both forms are evaluated and selected: a branch per element costs more than the five FMAs.
+      const float e = __expf(x > 20.0f ? 20.0f : x);   // a NaN passes through the select
+      const float series = e * (1.0f - e * (0.5f - e * (0.33333334f - e * (0.25f - e * 0.2f))));
+      const float lg = __logf(1.0f + e);
+      const float r = e < 0.1f ? series : lg;
+      return x > 20.0f ? x : r;
     }
     case FB200_EW_EXP: return expf(x);
     case FB200_EW_HEAVISIDE: return x >= 0.0f ? 1.0f : 0.0f;

@@ -36,6 +36,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <type_traits>
 
 #include "common.cuh"
 #include "epilogue.cuh"
@@ -113,7 +114,10 @@ struct GemmCfg {
   // 128-byte span along N is one chunk further (LBO).  One MMA covers 32 bytes of K:
   // 16 rows (two groups) for 2-byte elements, 8 rows (one group) for 4-byte elements.
   static constexpr int kBKStepBytes = (kUmmaKBytes / ELT / 8) * 1024;
-  static constexpr size_t kSmemBytes = size_t(kStages) * kStageBytes + 1024 /*align*/ + 512 /*barriers*/;
+  // after the ring: 512 bytes of barriers, then one 4 KiB transpose buffer per epilogue warp
+  static constexpr int kEpiStageBytes = 32 * 128;
+  static constexpr size_t kSmemBytes = size_t(kStages) * kStageBytes + 1024 /*align*/ + 512 /*barriers*/ +
+                                       8 * kEpiStageBytes;
 };
 
 __device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64_t tiles_n, int kGroupM,
@@ -127,7 +131,177 @@ __device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64
   *tn = in_group / group_rows;
 }
 
-template <typename T, int ELT, int BLOCK_N, int MH, int KB>
+
+// ---- epilogue ------------------------------------------------------------------------------------
+// tcgen05.ld hands lane r of a warp the 32 columns of ROW r: stores straight from that layout are
+// 32 separate 16-byte pieces per instruction, one per row.  The chunk is therefore turned through a
+// 4 KiB shared-memory buffer (16-byte pieces XOR-swizzled by the row, conflict-free both ways) into
+// a layout in which the lanes of a warp cover whole rows: 32 / W lanes per row, W = 16 / sizeof(T)
+// output elements per lane and pass.  Operand loads (a full-shape bias or residual) and the result
+// stores are then 16 bytes per lane over contiguous row segments: whole 128-byte lines for fp32,
+// 64-byte half lines for 16-bit results.
+//
+// Chains the kernel is instantiated for with the step codes as compile-time constants (the
+// per-fused-group specialisation of the GEMM epilogue); every other chain runs the same code with
+// the step list read at run time.
+enum EpiKind : int {
+  kEpiGeneric = 0,       // interpreter over epi.ops
+  kEpiNone = 1,          // plain store
+  kEpiAddFullGelu = 2,   // + full-shape bias, GELU         (Linear + GELU)
+  kEpiAddColSoftplus = 3,// + row-broadcast bias, softplus  (Mamba dt_proj)
+  kEpiGelu = 4,          // GELU                            (bias-free FFN)
+  kEpiAddFull = 5,       // + full-shape tensor             (Linear bias or residual)
+};
+
+static int classify_epilogue(const EpilogueDev& e) {
+  if (e.n_ops == 0) return kEpiNone;
+  if (e.n_ops == 1 && e.ops[0] == FB200_EW_GELU) return kEpiGelu;
+  if (e.n_ops == 1 && e.ops[0] == FB200_EW_ADD && e.modes[0] == FB200_OPERAND_FULL) return kEpiAddFull;
+  if (e.n_ops == 2 && e.ops[0] == FB200_EW_ADD && e.modes[0] == FB200_OPERAND_FULL && e.ops[1] == FB200_EW_GELU) return kEpiAddFullGelu;
+  if (e.n_ops == 2 && e.ops[0] == FB200_EW_ADD && e.modes[0] == FB200_OPERAND_COL && e.ops[1] == FB200_EW_SOFTPLUS) return kEpiAddColSoftplus;
+  return kEpiGeneric;
+}
+
+// Geometry of one 32 x 32 chunk in the row-covering layout.
+template <typename T>
+struct ChunkView {
+  static constexpr int W = 16 / sizeof(T);   // elements per lane and pass
+  static constexpr int LPR = 32 / W;         // lanes per row
+  static constexpr int RPP = W;              // rows per pass
+  static constexpr int P = 32 / W;           // passes
+  int64_t row0;      // first row of the warp's 32 rows
+  int64_t col;       // this lane's first column
+  int sub_row;       // lane / LPR
+  int64_t M, N;
+  bool vec;          // 16-byte accesses are legal for this chunk
+  __device__ __forceinline__ int64_t row(int j) const { return row0 + j * RPP + sub_row; }
+};
+
+// One step of the chain over the lane's 32 values.  `op` and `mode` are compile-time constants in the
+// specialised kernels (the switch folds away) and run-time values in the interpreter.
+// `pre` holds the lane's pieces of a FULL operand fetched ahead of the accumulator (use_pre).
+template <typename T>
+__device__ __forceinline__ void chain_step(int op, int mode, const void* operand, float (&v)[32],
+                                           const ChunkView<T>& g, const Vec16<T> (&pre)[32 / ChunkView<T>::W],
+                                           bool use_pre) {
+  constexpr int W = ChunkView<T>::W, P = ChunkView<T>::P;
+  const T* opnd = static_cast<const T*>(operand);
+  if (opnd == nullptr) {
+    ew_unary_vec<T, 32>(op, v);
+    return;
+  }
+  if (mode == FB200_OPERAND_ROW) {
+#pragma unroll
+    for (int j = 0; j < P; ++j) {
+      const int64_t r = g.row(j);
+      const float rhs = r < g.M ? to_f32(opnd[r]) : 0.0f;
+#pragma unroll
+      for (int e = 0; e < W; ++e) v[j * W + e] = round_through<T>(ew_binary(op, v[j * W + e], rhs));
+    }
+    return;
+  }
+  if (mode == FB200_OPERAND_COL) {
+    float rhs[W];
+    if (g.vec && (reinterpret_cast<uintptr_t>(opnd) & 15u) == 0) {
+      load_vec<T>(opnd + g.col, rhs);
+    } else {
+#pragma unroll
+      for (int e = 0; e < W; ++e) rhs[e] = g.col + e < g.N ? to_f32(opnd[g.col + e]) : 0.0f;
+    }
+#pragma unroll
+    for (int j = 0; j < P; ++j) {
+#pragma unroll
+      for (int e = 0; e < W; ++e) v[j * W + e] = round_through<T>(ew_binary(op, v[j * W + e], rhs[e]));
+    }
+    return;
+  }
+  const bool vec = g.vec && (reinterpret_cast<uintptr_t>(opnd) & 15u) == 0;
+#pragma unroll
+  for (int j = 0; j < P; ++j) {
+    const int64_t r = g.row(j);
+    if (r >= g.M) continue;
+    const T* src = opnd + r * g.N + g.col;
+    float rhs[W];
+    if (use_pre) {
+#pragma unroll
+      for (int e = 0; e < W; ++e) rhs[e] = to_f32(pre[j].v[e]);
+    } else if (vec) {
+      load_vec<T>(src, rhs);
+    } else {
+#pragma unroll
+      for (int e = 0; e < W; ++e) rhs[e] = g.col + e < g.N ? to_f32(src[e]) : 0.0f;
+    }
+#pragma unroll
+    for (int e = 0; e < W; ++e) v[j * W + e] = round_through<T>(ew_binary(op, v[j * W + e], rhs[e]));
+  }
+}
+
+// Step of the chain whose FULL operand is fetched ahead of the accumulator: the first such step.
+template <int EPI>
+__device__ __forceinline__ int prefetch_step(const EpilogueDev& epi) {
+  if constexpr (EPI == kEpiAddFull || EPI == kEpiAddFullGelu) {
+    return 0;
+  } else if constexpr (EPI != kEpiGeneric) {
+    return -1;
+  } else {
+    for (int s = 0; s < epi.n_ops; ++s) {
+      if (epi.operands[s] != nullptr && epi.modes[s] == FB200_OPERAND_FULL) return s;
+    }
+    return -1;
+  }
+}
+
+template <typename T, int EPI>
+__device__ __forceinline__ void apply_chain(const EpilogueDev& epi, float (&v)[32], const ChunkView<T>& g,
+                                            const Vec16<T> (&pre)[32 / ChunkView<T>::W], int pre_step) {
+  if constexpr (EPI == kEpiNone) {
+    return;
+  } else if constexpr (EPI == kEpiGelu) {
+    chain_step<T>(FB200_EW_GELU, 0, nullptr, v, g, pre, false);
+  } else if constexpr (EPI == kEpiAddFull) {
+    chain_step<T>(FB200_EW_ADD, FB200_OPERAND_FULL, epi.operands[0], v, g, pre, pre_step == 0);
+  } else if constexpr (EPI == kEpiAddFullGelu) {
+    chain_step<T>(FB200_EW_ADD, FB200_OPERAND_FULL, epi.operands[0], v, g, pre, pre_step == 0);
+    chain_step<T>(FB200_EW_GELU, 0, nullptr, v, g, pre, false);
+  } else if constexpr (EPI == kEpiAddColSoftplus) {
+    chain_step<T>(FB200_EW_ADD, FB200_OPERAND_COL, epi.operands[0], v, g, pre, false);
+    chain_step<T>(FB200_EW_SOFTPLUS, 0, nullptr, v, g, pre, false);
+  } else {
+#pragma unroll 1
+    for (int s = 0; s < epi.n_ops; ++s) chain_step<T>(epi.ops[s], epi.modes[s], epi.operands[s], v, g, pre, s == pre_step);
+  }
+}
+
+// Row r's 32 accumulator columns (held by lane r) -> the row-covering layout, through `stage`.
+template <typename T>
+__device__ __forceinline__ void transpose_chunk(const uint32_t (&r)[32], float (&v)[32], uint32_t stage, int lane) {
+  constexpr int W = ChunkView<T>::W, LPR = ChunkView<T>::LPR, P = ChunkView<T>::P;
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    const uint32_t addr = stage + static_cast<uint32_t>(lane * 128 + ((q ^ (lane & 7)) << 4));
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(r[4 * q]), "r"(r[4 * q + 1]),
+                 "r"(r[4 * q + 2]), "r"(r[4 * q + 3]) : "memory");
+  }
+  __syncwarp();
+  const int sub_row = lane / LPR, piece0 = (lane % LPR) * (W / 4);
+#pragma unroll
+  for (int j = 0; j < P; ++j) {
+    const int row = j * W + sub_row;
+#pragma unroll
+    for (int h = 0; h < W / 4; ++h) {
+      const uint32_t addr = stage + static_cast<uint32_t>(row * 128 + (((piece0 + h) ^ (row & 7)) << 4));
+      uint32_t a, b, c, d;
+      asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr) : "memory");
+      v[j * W + 4 * h + 0] = round_through<T>(__uint_as_float(a));
+      v[j * W + 4 * h + 1] = round_through<T>(__uint_as_float(b));
+      v[j * W + 4 * h + 2] = round_through<T>(__uint_as_float(c));
+      v[j * W + 4 * h + 3] = round_through<T>(__uint_as_float(d));
+    }
+  }
+  __syncwarp();   // every lane has read its pieces before the next chunk overwrites the buffer
+}
+
+template <typename T, int ELT, int BLOCK_N, int MH, int KB, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b, int b_spans_map, GemmDest dest, int64_t M,
@@ -285,80 +459,70 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     constexpr int kChunksPerWarp = MH == 2 ? BLOCK_N / 32 : BLOCK_N / 64;
     int acc = MH == 2 ? half : 0;
     uint32_t acc_phase = 0;
-    constexpr int W = 16 / sizeof(T);
+    using View = ChunkView<T>;
+    constexpr int W = View::W;
     bool vec_n = (N % W == 0) && (dest.ld % W == 0) && (dest.col0 % W == 0);
     for (int d = 0; d < dest.n; ++d) vec_n = vec_n && ((reinterpret_cast<uintptr_t>(dest.ptr[d]) & 15u) == 0);
+    const uint32_t stage_buf = bars + 512u + static_cast<uint32_t>((warp - 2) * Cfg::kEpiStageBytes);
+    const int pf_step = prefetch_step<EPI>(epi);
     bool ok = true;
     for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
       int64_t tm, tn;
       tile_coords(tile, tiles_m, tiles_n, group_m, &tm, &tn);
       if (!mbar_wait(tmem_full_bar(acc), acc_phase, status, kFaultEpilogueTmemFull)) { ok = false; break; }
       tcgen05_fence_after_sync();
-      const int64_t row = tm * Cfg::kTileM + (MH == 2 ? half * kBlockM : 0) + quarter * 32 + lane;
+      View g;
+      g.row0 = tm * Cfg::kTileM + (MH == 2 ? half * kBlockM : 0) + quarter * 32;
+      g.sub_row = lane / View::LPR;
+      g.M = M;
+      g.N = N;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(acc * BLOCK_N);
 #pragma unroll 1
       for (int c = (MH == 2 ? 0 : half * kChunksPerWarp); c < (MH == 2 ? kChunksPerWarp : (half + 1) * kChunksPerWarp); ++c) {
         const int64_t col0 = tn * BLOCK_N + c * 32;
         if (col0 >= N) break;  // warp-uniform
+        g.col = col0 + (lane % View::LPR) * W;
+        g.vec = vec_n && col0 + 32 <= N;
+        // The chain's full-shape operand (a Linear bias, a residual) does not depend on the
+        // accumulator: its loads go out first and are in flight during the TMEM read and the
+        // transposition; the next chunk's lines are pulled into L2 meanwhile.
+        Vec16<T> pre[View::P];
+        int pre_step = -1;
+        if (pf_step >= 0 && g.vec && g.row0 < M && (reinterpret_cast<uintptr_t>(epi.operands[pf_step]) & 15u) == 0) {
+          pre_step = pf_step;
+          const T* opnd = static_cast<const T*>(epi.operands[pf_step]);
+#pragma unroll
+          for (int j = 0; j < View::P; ++j) {
+            const int64_t row = g.row(j) < M ? g.row(j) : M - 1;
+            const T* src = opnd + row * N + g.col;
+            pre[j] = *reinterpret_cast<const Vec16<T>*>(src);
+            if (col0 + 64 <= N) asm volatile("prefetch.global.L2 [%0];" ::"l"(src + 32));
+          }
+        }
         uint32_t r[32];
         tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(c * 32), r);
         tmem_ld_wait();
-        if (row < M) {
-          float v[32];
+        if (g.row0 >= M) continue;  // warp-uniform: the whole 32-row band lies below the matrix
+        float v[32];
+        transpose_chunk<T>(r, v, stage_buf, lane);
+        apply_chain<T, EPI>(epi, v, g, pre, pre_step);
+        for (int d = 0; d < dest.n; ++d) {
+          T* base_dst = static_cast<T*>(dest.ptr[d]) + dest.col0 + g.col;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = round_through<T>(__uint_as_float(r[j]));
-          const bool full_chunk = vec_n && col0 + 32 <= N;
-          const int64_t idx0 = row * N + col0;
-#pragma unroll 1
-          for (int s = 0; s < epi.n_ops; ++s) {
-            {
-              const int op = epi.ops[s];
-              const T* opnd = static_cast<const T*>(epi.operands[s]);
-              if (opnd != nullptr) {
-                const int mode = epi.modes[s];
-                if (mode == FB200_OPERAND_ROW) {
-                  const float rhs = to_f32(opnd[row]);
+          for (int j = 0; j < View::P; ++j) {
+            const int64_t row = g.row(j);
+            if (row >= M) continue;
+            T* dst = base_dst + row * dest.ld;
+            if (g.vec) {
+              float o[W];
 #pragma unroll
-                  for (int j = 0; j < 32; ++j) v[j] = round_through<T>(ew_binary(op, v[j], rhs));
-                } else {
-                  const T* src = mode == FB200_OPERAND_FULL ? opnd + idx0 : opnd + col0;
-                  if (full_chunk && (reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
-#pragma unroll
-                    for (int q = 0; q < 32 / W; ++q) {
-                      float rhs[W];
-                      load_vec<T>(src + q * W, rhs);
-#pragma unroll
-                      for (int e = 0; e < W; ++e) {
-                        v[q * W + e] = round_through<T>(ew_binary(op, v[q * W + e], rhs[e]));
-                      }
-                    }
-                  } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                      if (col0 + j < N) v[j] = round_through<T>(ew_binary(op, v[j], to_f32(src[j])));
-                    }
-                  }
-                }
-              } else {
-                ew_unary_vec<T, 32>(op, v);
-              }
-            }
-          }
-          for (int d = 0; d < dest.n; ++d) {
-            T* dst = static_cast<T*>(dest.ptr[d]) + row * dest.ld + dest.col0 + col0;
-            if (full_chunk) {
-#pragma unroll
-              for (int q = 0; q < 32 / W; ++q) {
-                float o[W];
-#pragma unroll
-                for (int e = 0; e < W; ++e) o[e] = v[q * W + e];
-                store_vec<T>(dst + q * W, o);
-              }
+              for (int e = 0; e < W; ++e) o[e] = v[j * W + e];
+              store_vec<T>(dst, o);
             } else {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                if (col0 + j < N) dst[j] = from_f32<T>(v[j]);
+              for (int e = 0; e < W; ++e) {
+                if (g.col + e < N) dst[e] = from_f32<T>(v[j * W + e]);
               }
             }
           }
@@ -531,9 +695,9 @@ int device_status_word(int** dev_ptr) {
   return FB200_OK;
 }
 
-template <typename T, int ELT, int BLOCK_N, int MH = 1, int KB = 128>
-static int launch_tc(const void* a, const void* b, const GemmDest& c, int64_t m, int64_t n, int64_t k,
-                     int dtype, const EpilogueDev& epi, cudaStream_t s) {
+template <typename T, int ELT, int BLOCK_N, int MH, int KB, int EPI>
+static int launch_tc_epi(const void* a, const void* b, const GemmDest& c, int64_t m, int64_t n, int64_t k,
+                         int dtype, const EpilogueDev& epi, cudaStream_t s) {
   using Cfg = GemmCfg<ELT, BLOCK_N, MH, KB>;
   CUtensorMap ta, tb;
   if (int rc = make_tmap_rows(&ta, a, dtype, m, k, Cfg::kTileM, KB)) return rc;
@@ -549,7 +713,7 @@ static int launch_tc(const void* a, const void* b, const GemmDest& c, int64_t m,
   if (int rc = device_status_word(&status)) return rc;
   const uint32_t fmt = dtype == FB200_F32 ? kFmtTF32 : (dtype == FB200_BF16 ? kFmtBF16 : kFmtF16);
   const uint32_t idesc = make_instr_desc(fmt, /*a MN-major*/ 0, /*b MN-major*/ 1, kBlockM, BLOCK_N);
-  auto kernel = gemm_tcgen05_kernel<T, ELT, BLOCK_N, MH, KB>;
+  auto kernel = gemm_tcgen05_kernel<T, ELT, BLOCK_N, MH, KB, EPI>;
   FB200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(Cfg::kSmemBytes)));
   const int64_t tiles = ((m + Cfg::kTileM - 1) / Cfg::kTileM) * ((n + BLOCK_N - 1) / BLOCK_N);
@@ -557,6 +721,25 @@ static int launch_tc(const void* a, const void* b, const GemmDest& c, int64_t m,
   kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, b_spans_map, c, m, n, k, idesc,
                                                       epi, status);
   return after_launch("gemm_tcgen05_kernel");
+}
+
+// Picks the kernel instantiated for this epilogue chain; 16-bit float (f16) tensors and 256 x 256
+// tiles (light epilogues only) keep to the plain store and the interpreter.
+template <typename T, int ELT, int BLOCK_N, int MH = 1, int KB = 128>
+static int launch_tc(const void* a, const void* b, const GemmDest& c, int64_t m, int64_t n, int64_t k,
+                     int dtype, const EpilogueDev& epi, cudaStream_t s) {
+  const int kind = classify_epilogue(epi);
+  if (kind == kEpiNone) return launch_tc_epi<T, ELT, BLOCK_N, MH, KB, kEpiNone>(a, b, c, m, n, k, dtype, epi, s);
+  if constexpr (MH == 1 && !std::is_same<T, __half>::value) {
+    switch (kind) {
+      case kEpiAddFullGelu: return launch_tc_epi<T, ELT, BLOCK_N, MH, KB, kEpiAddFullGelu>(a, b, c, m, n, k, dtype, epi, s);
+      case kEpiAddColSoftplus: return launch_tc_epi<T, ELT, BLOCK_N, MH, KB, kEpiAddColSoftplus>(a, b, c, m, n, k, dtype, epi, s);
+      case kEpiGelu: return launch_tc_epi<T, ELT, BLOCK_N, MH, KB, kEpiGelu>(a, b, c, m, n, k, dtype, epi, s);
+      case kEpiAddFull: return launch_tc_epi<T, ELT, BLOCK_N, MH, KB, kEpiAddFull>(a, b, c, m, n, k, dtype, epi, s);
+      default: break;
+    }
+  }
+  return launch_tc_epi<T, ELT, BLOCK_N, MH, KB, kEpiGeneric>(a, b, c, m, n, k, dtype, epi, s);
 }
 
 template <typename T, int ELT>
