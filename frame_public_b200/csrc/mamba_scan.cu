@@ -162,45 +162,88 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
 template <int NS, int LANES>
 __host__ __device__ constexpr int mamba_pipe_stage_floats() { return 3 * kPipeTile * (32 / LANES) + 2 * kPipeTile * NS; }
 
-template <int NS, int LANES>
+// Which part of the time axis a launch covers.
+//   kScanWhole    the whole sequence from h = 0, results written: one pass, used when batch x
+//                 channels alone fill the machine.
+//   kScanSummary  chunk `blockIdx.z` of the sequence from h = 0, nothing written but the chunk's end
+//                 state S[n] and the sum of its deltas (the chunk's decay is exp(A[n] * sum delta),
+//                 one exponential per state instead of a product over the chunk).
+//   kScanApply    chunk `blockIdx.z` from the state the earlier chunks leave behind
+//                 (h = P_c' * h + S_c' over c' < chunk), results written.
+// Summary + apply evaluate every exponential twice, but give `chunks` times the threads: with a few
+// samples per GPU (a batch sharded over 8 GPUs leaves 2) the single pass has 2 warps per SM and
+// runs at the latency of 2048 dependent steps.
+enum MambaScanMode : int { kScanWhole = 0, kScanSummary = 1, kScanApply = 2 };
+
+struct MambaChunks {
+  int64_t chunks;      // time chunks (1 for kScanWhole)
+  int64_t chunk_len;   // steps per chunk, a multiple of kPipeTile
+  float* state;        // [batch][chunks][dm][NS]  end state of each chunk started from zero
+  float* dsum;         // [batch][chunks][dm]      sum of delta over each chunk
+};
+
+__device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
+
+// Arithmetic on pairs of states goes through the packed fp32 instructions of sm_100
+// (fma.rn.f32x2 / mul.rn.f32x2): half the issue slots per state update; the exponentials stay
+// one ex2.approx each.
+template <int NS, int LANES, int MODE>
 __global__ void __launch_bounds__(kMambaThreads)
 mamba_scan_pipe_kernel(const float* __restrict__ u, const float* __restrict__ delta,
                        const float* __restrict__ A, const float* __restrict__ B,
                        const float* __restrict__ C, const float* __restrict__ D,
-                       const float* __restrict__ z, float* __restrict__ y, int64_t len, int64_t dm) {
-  constexpr int PER = NS / LANES;
+                       const float* __restrict__ z, float* __restrict__ y, int64_t len, int64_t dm,
+                       MambaChunks ck) {
+  constexpr int PER = NS / LANES;            // states per lane
+  constexpr int PAIRS = PER / 2;
   constexpr int CW = 32 / LANES;             // channels per warp
   constexpr int TT = kPipeTile, ST = kPipeStages, U = kMambaSteps;
-  constexpr int FIN = U / LANES;
+  constexpr int FIN = TT / LANES;            // steps of a tile each lane finishes
   constexpr int kStageFloats = mamba_pipe_stage_floats<NS, LANES>();
-  static_assert(PER % 4 == 0 && U % LANES == 0 && TT % U == 0 && CW % 4 == 0, "tile geometry");
+  static_assert(PER % 4 == 0 && TT % LANES == 0 && TT % U == 0 && CW % 4 == 0, "tile geometry");
   extern __shared__ float4 mamba_smem4[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float* ws = reinterpret_cast<float*>(mamba_smem4) + warp * ST * kStageFloats;
   const int64_t ch0 = (static_cast<int64_t>(blockIdx.x) * (kMambaThreads / 32) + warp) * CW;
   if (ch0 >= dm) return;                     // whole warp; warps never wait on each other
   const int64_t bidx = blockIdx.y;
+  const int64_t chunk = MODE == kScanWhole ? 0 : blockIdx.z;
+  if (MODE == kScanSummary && chunk + 1 >= ck.chunks) return;   // nobody needs the last chunk's end state
+  const int64_t t_begin = chunk * ck.chunk_len;
+  const int64_t t_end = (MODE == kScanWhole || t_begin + ck.chunk_len > len) ? len : t_begin + ck.chunk_len;
   const int sg = lane % LANES, c = lane / LANES;
   const int64_t ch = ch0 + c;
-  float h[PER], Ar[PER];
+  float2 h[PAIRS], Ar[PAIRS];
 #pragma unroll
-  for (int n = 0; n < PER; ++n) {
-    h[n] = 0.0f;
-    Ar[n] = A[ch * NS + sg * PER + n] * 1.4426950408889634f;
+  for (int p = 0; p < PAIRS; ++p) {
+    h[p] = f2(0.0f, 0.0f);
+    Ar[p] = f2(A[ch * NS + sg * PER + 2 * p] * 1.4426950408889634f, A[ch * NS + sg * PER + 2 * p + 1] * 1.4426950408889634f);
+  }
+  if (MODE == kScanApply) {
+    // the state the chunks before this one leave behind
+    for (int64_t cp = 0; cp < chunk; ++cp) {
+      const float ds = ck.dsum[(bidx * ck.chunks + cp) * dm + ch];
+      const float* sp = ck.state + ((bidx * ck.chunks + cp) * dm + ch) * NS + sg * PER;
+#pragma unroll
+      for (int p = 0; p < PAIRS; ++p) {
+        const float2 x = __fmul2_rn(f2(ds, ds), Ar[p]);
+        h[p] = __ffma2_rn(f2(mamba_ex2(x.x), mamba_ex2(x.y)), h[p], f2(sp[2 * p], sp[2 * p + 1]));
+      }
+    }
   }
   const float Dd = D[ch];
   const float* ub = u + bidx * len * dm + ch0;
   const float* db = delta + bidx * len * dm + ch0;
-  const float* zb = z != nullptr ? z + bidx * len * dm + ch0 : nullptr;
+  const float* zb = (z != nullptr && MODE != kScanSummary) ? z + bidx * len * dm + ch0 : nullptr;
   const float* Bb = B + bidx * len * NS;
   const float* Cb = C + bidx * len * NS;
   float* yp = y + bidx * len * dm + ch;
-  const int64_t n_tiles = (len + TT - 1) / TT;
+  const int64_t n_tiles = (t_end - t_begin + TT - 1) / TT;
   // stage layout (floats): u[TT][CW] | delta[TT][CW] | z[TT][CW] | B[TT][NS] | C[TT][NS]
   auto issue = [&](int64_t tile) {
     if (tile < n_tiles) {
       float* st = ws + (tile % ST) * kStageFloats;
-      const int64_t t0 = tile * TT;
+      const int64_t t0 = t_begin + tile * TT;
       constexpr int kChunksX = TT * CW / 4, kChunksS = TT * NS / 4;
       for (int i = lane; i < kChunksX; i += 32) {
         const int r = i / (CW / 4), q = i % (CW / 4);
@@ -213,11 +256,12 @@ mamba_scan_pipe_kernel(const float* __restrict__ u, const float* __restrict__ de
         const int r = i / (NS / 4), q = i % (NS / 4);
         const int64_t t = t0 + r < len ? t0 + r : len - 1;
         cp_async16(st + 3 * TT * CW + r * NS + q * 4, Bb + t * NS + q * 4);
-        cp_async16(st + 3 * TT * CW + TT * NS + r * NS + q * 4, Cb + t * NS + q * 4);
+        if (MODE != kScanSummary) cp_async16(st + 3 * TT * CW + TT * NS + r * NS + q * 4, Cb + t * NS + q * 4);
       }
     }
     cp_async_commit();   // an empty group keeps the group count uniform
   };
+  float dsum = 0.0f;
   for (int s = 0; s < ST - 1; ++s) issue(s);
   for (int64_t tile = 0; tile < n_tiles; ++tile) {
     issue(tile + ST - 1);
@@ -229,35 +273,52 @@ mamba_scan_pipe_kernel(const float* __restrict__ u, const float* __restrict__ de
     const float* sz = st + 2 * TT * CW;
     const float* sB = st + 3 * TT * CW + sg * PER;
     const float* sC = sB + TT * NS;
+    float acc[TT], uu[TT];
 #pragma unroll
     for (int g = 0; g < TT / U; ++g) {
-      float acc[U], uu[U];
+      // everything that does not depend on the state first: U x PER exponentials and input terms
+      float2 dA[U][PAIRS], dBx[U][PAIRS];
 #pragma unroll
       for (int j = 0; j < U; ++j) {
         const int r = g * U + j;
         const float dd = sd[r * CW + c];
-        uu[j] = su[r * CW + c];
-        const float du = dd * uu[j];
-        float sum = 0.0f;
+        uu[r] = su[r * CW + c];
+        if (MODE == kScanSummary) dsum += dd;
+        const float du = dd * uu[r];
 #pragma unroll
         for (int q = 0; q < PER / 4; ++q) {
           const float4 b4 = *reinterpret_cast<const float4*>(sB + r * NS + q * 4);
-          const float4 c4 = *reinterpret_cast<const float4*>(sC + r * NS + q * 4);
-          const float bq[4] = {b4.x, b4.y, b4.z, b4.w};
-          const float cq[4] = {c4.x, c4.y, c4.z, c4.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int n = q * 4 + e;
-            h[n] = mamba_ex2(dd * Ar[n]) * h[n] + du * bq[e];
-            sum = sum + cq[e] * h[n];
-          }
+          const float2 x0 = __fmul2_rn(f2(dd, dd), Ar[2 * q]), x1 = __fmul2_rn(f2(dd, dd), Ar[2 * q + 1]);
+          dA[j][2 * q] = f2(mamba_ex2(x0.x), mamba_ex2(x0.y));
+          dA[j][2 * q + 1] = f2(mamba_ex2(x1.x), mamba_ex2(x1.y));
+          dBx[j][2 * q] = __fmul2_rn(f2(du, du), f2(b4.x, b4.y));
+          dBx[j][2 * q + 1] = __fmul2_rn(f2(du, du), f2(b4.z, b4.w));
         }
-        acc[j] = sum;
       }
+      // the recurrence itself: PAIRS independent packed FMAs per step
 #pragma unroll
       for (int j = 0; j < U; ++j) {
+        const int r = g * U + j;
+        float2 sum = f2(0.0f, 0.0f);
 #pragma unroll
-        for (int o = 1; o < LANES; o <<= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+        for (int q = 0; q < PER / 4; ++q) {
+          h[2 * q] = __ffma2_rn(dA[j][2 * q], h[2 * q], dBx[j][2 * q]);
+          h[2 * q + 1] = __ffma2_rn(dA[j][2 * q + 1], h[2 * q + 1], dBx[j][2 * q + 1]);
+          if (MODE != kScanSummary) {
+            const float4 c4 = *reinterpret_cast<const float4*>(sC + r * NS + q * 4);
+            sum = __ffma2_rn(f2(c4.x, c4.y), h[2 * q], sum);
+            sum = __ffma2_rn(f2(c4.z, c4.w), h[2 * q + 1], sum);
+          }
+        }
+        acc[r] = sum.x + sum.y;
+      }
+    }
+    if (MODE != kScanSummary) {
+      // the tile's TT sums across the lanes of a channel, then each lane finishes TT / LANES steps
+#pragma unroll
+      for (int r = 0; r < TT; ++r) {
+#pragma unroll
+        for (int o = 1; o < LANES; o <<= 1) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], o);
       }
 #pragma unroll
       for (int f = 0; f < FIN; ++f) {
@@ -266,9 +327,9 @@ mamba_scan_pipe_kernel(const float* __restrict__ u, const float* __restrict__ de
         for (int l = 1; l < LANES; ++l) {
           if (sg == l) { mine = acc[f * LANES + l]; umine = uu[f * LANES + l]; }
         }
-        const int r = g * U + f * LANES + sg;
-        const int64_t t = tile * TT + r;
-        if (t < len) {
+        const int r = f * LANES + sg;
+        const int64_t t = t_begin + tile * TT + r;
+        if (t < t_end) {
           float out = mine + Dd * umine;
           if (zb != nullptr) {
             const float zz = sz[r * CW + c];
@@ -279,6 +340,12 @@ mamba_scan_pipe_kernel(const float* __restrict__ u, const float* __restrict__ de
       }
     }
     __syncwarp();   // every lane is done with this stage before the next issue overwrites it
+  }
+  if (MODE == kScanSummary) {
+    float* sp = ck.state + ((bidx * ck.chunks + chunk) * dm + ch) * NS + sg * PER;
+#pragma unroll
+    for (int p = 0; p < PAIRS; ++p) { sp[2 * p] = h[p].x; sp[2 * p + 1] = h[p].y; }
+    if (sg == 0) ck.dsum[(bidx * ck.chunks + chunk) * dm + ch] = dsum;
   }
 }
 
@@ -320,28 +387,64 @@ extern "C" int fb200_mamba_scan(const void* u, const void* delta, const void* A,
   const bool piped = dm % cw == 0 && dm % 4 == 0 && aligned16(u) && aligned16(delta) &&
                      (z == nullptr || aligned16(z));
   if (piped) grid.x = static_cast<unsigned>((dm / cw + kMambaThreads / 32 - 1) / (kMambaThreads / 32));
+  // Time chunks: one pass when batch x channels give every SM at least 8 warps; otherwise enough
+  // chunks for about 16 warps per SM, each at least 64 steps long (a multiple of the pipeline tile).
+  MambaChunks ck{1, len, nullptr, nullptr};
+  if (piped) {
+    const int64_t warps = batch * (dm / cw);
+    if (warps < int64_t(kNumSMs) * 8) {
+      int64_t chunks = (int64_t(kNumSMs) * 16 + warps - 1) / warps;
+      if (chunks > len / 64) chunks = len / 64;
+      if (chunks > 65535) chunks = 65535;
+      if (chunks >= 2) {
+        int64_t cl = (len + chunks - 1) / chunks;
+        cl = (cl + kPipeTile - 1) / kPipeTile * kPipeTile;
+        ck.chunks = (len + cl - 1) / cl;
+        ck.chunk_len = cl;
+      }
+    }
+  }
+  float* scratch = nullptr;
+  if (ck.chunks > 1) {
+    const size_t n_state = static_cast<size_t>(batch) * ck.chunks * dm * nstate;
+    const size_t n_dsum = static_cast<size_t>(batch) * ck.chunks * dm;
+    FB200_CUDA_OK(cudaMallocAsync(reinterpret_cast<void**>(&scratch), (n_state + n_dsum) * sizeof(float), s));
+    ck.state = scratch;
+    ck.dsum = scratch + n_state;
+  }
+  int rc = FB200_OK;
+#define FB200_MAMBA_PIPE(NS, LN, MODE, GRID)                                                         \
+  do {                                                                                               \
+    const size_t smem = size_t(kMambaThreads / 32) * kPipeStages * mamba_pipe_stage_floats<NS, LN>() * 4; \
+    auto kernel = mamba_scan_pipe_kernel<NS, LN, MODE>;                                              \
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
+                                         static_cast<int>(smem));                                    \
+    if (e != cudaSuccess) { rc = cuda_error(e, "cudaFuncSetAttribute(mamba_scan)"); break; }         \
+    kernel<<<GRID, kMambaThreads, smem, s>>>(up, dp, Ap, Bp, Cp, Dp, zp, yp, len, dm, ck);           \
+    rc = after_launch("mamba_scan_pipe_kernel");                                                     \
+  } while (0)
 #define FB200_MAMBA_LAUNCH(NS, LN)                                                                   \
   do {                                                                                               \
-    if (piped) {                                                                                     \
-      const size_t smem = size_t(kMambaThreads / 32) * kPipeStages * mamba_pipe_stage_floats<NS, LN>() * 4; \
-      auto kernel = mamba_scan_pipe_kernel<NS, LN>;                                                  \
-      FB200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
-                                         static_cast<int>(smem)));                                   \
-      kernel<<<grid, kMambaThreads, smem, s>>>(up, dp, Ap, Bp, Cp, Dp, zp, yp, len, dm);             \
+    if (piped && ck.chunks > 1) {                                                                    \
+      dim3 g3(grid.x, grid.y, static_cast<unsigned>(ck.chunks));                                     \
+      FB200_MAMBA_PIPE(NS, LN, kScanSummary, g3);                                                    \
+      if (rc == FB200_OK) FB200_MAMBA_PIPE(NS, LN, kScanApply, g3);                                  \
+    } else if (piped) {                                                                              \
+      FB200_MAMBA_PIPE(NS, LN, kScanWhole, grid);                                                    \
     } else {                                                                                         \
       mamba_scan_kernel<NS, LN><<<grid, kMambaThreads, 0, s>>>(up, dp, Ap, Bp, Cp, Dp, zp, yp, len, dm); \
+      rc = after_launch("mamba_scan_kernel");                                                        \
     }                                                                                                \
   } while (0)
   if (nstate == 16) {
-    if (lanes == 4) { FB200_MAMBA_LAUNCH(16, 4); }
-    else if (lanes == 2) { FB200_MAMBA_LAUNCH(16, 2); }
-    else { FB200_MAMBA_LAUNCH(16, 1); }
+    FB200_MAMBA_LAUNCH(16, 2);
   } else if (nstate == 8) {
-    if (lanes == 2) { FB200_MAMBA_LAUNCH(8, 2); }
-    else { FB200_MAMBA_LAUNCH(8, 1); }
+    FB200_MAMBA_LAUNCH(8, 2);
   } else {
     FB200_MAMBA_LAUNCH(4, 1);
   }
 #undef FB200_MAMBA_LAUNCH
-  return after_launch("mamba_scan_kernel");
+#undef FB200_MAMBA_PIPE
+  if (scratch != nullptr) cudaFreeAsync(scratch, s);
+  return rc;
 }

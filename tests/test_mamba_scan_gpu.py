@@ -2,7 +2,8 @@
 the C ABI against the numpy oracle, which itself is pinned to the reference's selective_scan on
 materialised operands (tests/test_oracle_pins.py).  fp32; the state sum is associated differently
 on the GPU (four partial sums + two shuffles), hence the fp32 tolerance tier rather than bit
-equality."""
+equality.  Sequences of a few hundred steps with few channels run as several time chunks: the state
+a chunk starts from is rebuilt from the earlier chunks' end states and decays."""
 import numpy as np
 import pytest
 
@@ -13,7 +14,10 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("shape", [(2, 9, 5, 4), (1, 33, 40, 16), (3, 64, 70, 16), (2, 17, 32, 8),
-                                   (2, 100, 48, 16), (1, 8, 64, 16), (1, 3, 32, 4)],  # cp.async pipeline
+                                   (2, 100, 48, 16), (1, 8, 64, 16), (1, 3, 32, 4),   # cp.async pipeline
+                                   # long enough for several time chunks (summary + apply passes):
+                                   # chunk boundaries inside and at the end of the sequence
+                                   (1, 512, 64, 16), (2, 300, 32, 16), (1, 1000, 32, 8), (3, 257, 16, 16)],
                          ids=lambda s: "x".join(map(str, s)))
 @pytest.mark.parametrize("gated", [True, False], ids=["gated", "ungated"])
 def test_mamba_scan_matches_oracle(shape, gated):
