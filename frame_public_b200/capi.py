@@ -83,6 +83,8 @@ SIGNATURES = {
     "fb200_bias_add": (c_int, [_P, _P, _P, c_int64, c_int64, c_int, _P]),
     "fb200_matmul": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int, c_int,
                              POINTER(Epilogue), _P]),
+    "fb200_matmul_split": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int, c_int,
+                                   POINTER(Epilogue), _P]),
     "fb200_matmul_colsplit": (c_int, [_P, _P, _PP, c_int, c_int64, c_int64, c_int64, c_int64, c_int64,
                                       c_int, c_int, POINTER(Epilogue), _P]),
     "fb200_ipc_export": (c_int, [c_int, _P, _P]),
@@ -135,7 +137,7 @@ SIGNATURES = {
     "fb200_plan_run_host_async": (c_int, [_P, _PP, _PP, _P]),
     "fb200_plan_host_sync": (c_int, [_P]),
     "fb200_plan_bind_resident": (c_int, [_P, c_int, _P]),
-    "fb200_plan_describe": (c_int, [c_char_p, c_int, _PP]),
+    "fb200_plan_describe": (c_int, [c_char_p, c_int, c_int, _PP]),
 }
 
 _lib = None
@@ -255,6 +257,11 @@ def bias_add(x, bias, out, rows, cols, dtype, stream=None):
 def matmul(a, b, c, m, n, k, dtype, allow_tf32=False, epilogue=None, stream=None):
     ep = byref(epilogue) if epilogue is not None else None
     check(load().fb200_matmul(a, b, c, m, n, k, dtype, 1 if allow_tf32 else 0, ep, stream))
+
+
+def matmul_split(a, b, c, c_tail, tail_col, m, n, k, dtype, allow_tf32=False, epilogue=None, stream=None):
+    ep = byref(epilogue) if epilogue is not None else None
+    check(load().fb200_matmul_split(a, b, c, c_tail, tail_col, m, n, k, dtype, 1 if allow_tf32 else 0, ep, stream))
 
 
 def conv2d(x, w, bias, out, params: Conv2dParams, dtype, allow_tf32=False, epilogue=None,

@@ -79,6 +79,12 @@ struct GemmDest {
   int group_m;   // M-blocks per group of the tile walk
   int64_t ld;
   int64_t col0;
+  // columns [tail_col, N) of the result go to a dense matrix of their own (row pitch tail_ld)
+  // instead of `ptr`: a graph that only ever reads that column block as a `slice` gets it where the
+  // slice would have copied it.  tail_ptr == nullptr: no split.  tail_col is a multiple of 32.
+  void* tail_ptr;
+  int64_t tail_col;
+  int64_t tail_ld;
 };
 
 enum GemmFault : int {
@@ -463,6 +469,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     constexpr int W = View::W;
     bool vec_n = (N % W == 0) && (dest.ld % W == 0) && (dest.col0 % W == 0);
     for (int d = 0; d < dest.n; ++d) vec_n = vec_n && ((reinterpret_cast<uintptr_t>(dest.ptr[d]) & 15u) == 0);
+    if (dest.tail_ptr != nullptr) {
+      vec_n = vec_n && (dest.tail_ld % W == 0) && ((reinterpret_cast<uintptr_t>(dest.tail_ptr) & 15u) == 0);
+    }
     const uint32_t stage_buf = bars + 512u + static_cast<uint32_t>((warp - 2) * Cfg::kEpiStageBytes);
     const int pf_step = prefetch_step<EPI>(epi);
     bool ok = true;
@@ -507,13 +516,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         float v[32];
         transpose_chunk<T>(r, v, stage_buf, lane);
         apply_chain<T, EPI>(epi, v, g, pre, pre_step);
+        const bool tail = dest.tail_ptr != nullptr && col0 >= dest.tail_col;   // warp-uniform
+        const int64_t dst_ld = tail ? dest.tail_ld : dest.ld;
         for (int d = 0; d < dest.n; ++d) {
-          T* base_dst = static_cast<T*>(dest.ptr[d]) + dest.col0 + g.col;
+          T* base_dst = tail ? static_cast<T*>(dest.tail_ptr) + (g.col - dest.tail_col)
+                             : static_cast<T*>(dest.ptr[d]) + dest.col0 + g.col;
 #pragma unroll
           for (int j = 0; j < View::P; ++j) {
             const int64_t row = g.row(j);
             if (row >= M) continue;
-            T* dst = base_dst + row * dest.ld;
+            T* dst = base_dst + row * dst_ld;
             if (g.vec) {
               float o[W];
 #pragma unroll
@@ -793,20 +805,20 @@ extern "C" int fb200_matmul_uses_tensor_cores(int64_t m, int64_t n, int64_t k, i
   return tensor_core_eligible(nullptr, nullptr, nullptr, m, n, k, dtype, allow_tf32) ? 1 : 0;
 }
 
-extern "C" int fb200_matmul(const void* a, const void* b, void* c, int64_t m, int64_t n,
-                            int64_t k, int dtype, int allow_tf32, const fb200_epilogue* epilogue,
-                            fb200_stream stream) {
-  if (m < 0 || n < 0 || k < 0) return set_error(FB200_INVALID_ARGUMENT, "matmul: negative dimension");
+static int matmul_impl(const void* a, const void* b, void* c, void* c_tail, int64_t tail_col, int64_t m,
+                       int64_t n, int64_t k, int dtype, int allow_tf32, const fb200_epilogue* epilogue,
+                       fb200_stream stream, const char* who) {
+  if (m < 0 || n < 0 || k < 0) return set_error(FB200_INVALID_ARGUMENT, "%s: negative dimension", who);
   if (!is_float_dtype(dtype)) {
     return set_error(FB200_INVALID_ARGUMENT,
-                     "matmul: dtype code %d is not float32/float16/bfloat16", dtype);
+                     "%s: dtype code %d is not float32/float16/bfloat16", who, dtype);
   }
   if (m == 0 || n == 0) return FB200_OK;
   if (c == nullptr || (k > 0 && (a == nullptr || b == nullptr))) {
-    return set_error(FB200_INVALID_ARGUMENT, "matmul: null argument");
+    return set_error(FB200_INVALID_ARGUMENT, "%s: null argument", who);
   }
   EpilogueDev epi{};
-  if (int rc = make_epilogue(epilogue, &epi, "matmul")) return rc;
+  if (int rc = make_epilogue(epilogue, &epi, who)) return rc;
   cudaStream_t s = as_stream(stream);
   if (k > 0 && tensor_core_eligible(a, b, c, m, n, k, dtype, allow_tf32)) {
     GemmDest dest{};
@@ -815,13 +827,43 @@ extern "C" int fb200_matmul(const void* a, const void* b, void* c, int64_t m, in
     dest.n = 1;
     dest.ld = n;
     dest.col0 = 0;
+    dest.tail_ptr = c_tail;
+    dest.tail_col = tail_col;
+    dest.tail_ld = n - tail_col;
     switch (dtype) {
       case FB200_F32: return launch_tc_n<float, 4>(a, b, dest, m, n, k, dtype, epi, s);
       case FB200_BF16: return launch_tc_n<__nv_bfloat16, 2>(a, b, dest, m, n, k, dtype, epi, s);
       default: return launch_tc_n<__half, 2>(a, b, dest, m, n, k, dtype, epi, s);
     }
   }
+  if (c_tail != nullptr) {
+    return set_error(FB200_UNIMPLEMENTED, "%s: the split result needs a tensor-core shape "
+                     "(fb200_matmul_uses_tensor_cores)", who);
+  }
   return gemm_simt(a, b, c, m, n, k, dtype, epi, s);
+}
+
+extern "C" int fb200_matmul(const void* a, const void* b, void* c, int64_t m, int64_t n,
+                            int64_t k, int dtype, int allow_tf32, const fb200_epilogue* epilogue,
+                            fb200_stream stream) {
+  return matmul_impl(a, b, c, nullptr, 0, m, n, k, dtype, allow_tf32, epilogue, stream, "matmul");
+}
+
+// matmul whose result leaves in two pieces: columns [0, tail_col) into `c` (row pitch n, as
+// fb200_matmul writes them; the columns from tail_col on are left untouched there) and columns
+// [tail_col, n) into the dense matrix `c_tail` [m, n - tail_col].  For graphs that read a column
+// block of a projection only through a `slice` (the gate half of Mamba's in_proj): the block lands
+// where the slice would have copied it and the copy disappears.  tail_col must be a multiple of 32
+// and the shape a tensor-core one.
+extern "C" int fb200_matmul_split(const void* a, const void* b, void* c, void* c_tail, int64_t tail_col,
+                                  int64_t m, int64_t n, int64_t k, int dtype, int allow_tf32,
+                                  const fb200_epilogue* epilogue, fb200_stream stream) {
+  if (c_tail == nullptr || tail_col <= 0 || tail_col >= n || tail_col % 32 != 0) {
+    return set_error(FB200_INVALID_ARGUMENT,
+                     "matmul_split: tail_col %lld must be a multiple of 32 inside (0, n) and c_tail non-null",
+                     static_cast<long long>(tail_col));
+  }
+  return matmul_impl(a, b, c, c_tail, tail_col, m, n, k, dtype, allow_tf32, epilogue, stream, "matmul_split");
 }
 
 // Reads and clears the per-device kernel status word: 0 = no bounded wait has given up.

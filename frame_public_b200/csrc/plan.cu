@@ -44,6 +44,8 @@ struct SlotInfo {
   int output_index = -1;      // >= 0: graph output (first occurrence)
   int alias_of = -1;          // >= 0: same bytes as that slot
   void* constant = nullptr;   // materialised constant
+  bool private_buf = false;   // lives in a buffer of the plan's own, outside the planner's arena
+  void* private_ptr = nullptr;
   bool is_constant = false;   // produced by a `constant` step
   bool splat = false;         // constant whose elements are all equal ...
   float splat_value = 0.0f;   // ... to this value (as stored in the slot's dtype)
@@ -64,6 +66,8 @@ struct Step {
   std::vector<int> epi_operand_slot;         // per epilogue step: slot of the operand or -1
   std::vector<int> epi_mode;
   int write_slot = -1;                       // where the (possibly fused) result goes
+  int split_slot = -1;                       // kMatmul: slot that receives the columns from split_col on
+  int64_t split_col = 0;
   std::vector<int64_t> iv;                   // op-specific integers
   double eps = 0.0;
   // kAttentionFan: the matrices the heads' q/k/v windows lie in, where the results go, and the
@@ -515,6 +519,61 @@ static int last_use(const fb200_plan& p, int slot) {
   }
   for (int o : p.output_slots) if (root_slot(p, o) == root) last = static_cast<int>(p.steps.size());
   return last;
+}
+
+// A matmul whose result is only ever read through column slices, the last of which runs to the
+// right edge: that last block is written by the GEMM itself into a buffer of the plan's own
+// (outside the planner's arena, so no planned lifetime is disturbed) and the slice is dropped.  In
+// the Mamba block this is the gate half z of in_proj: the planner reuses the bytes of the slice's
+// output for the scan's result, so neither the slice nor the reshape behind it could become a view;
+// with a private buffer both do (201 MB less to copy, twice, at the benchmark size).
+static int split_matmul_tails(fb200_plan* p) {
+  const int n = static_cast<int>(p->steps.size());
+  for (int i = 0; i < n; ++i) {
+    Step& s = p->steps[static_cast<size_t>(i)];
+    if (s.kind != Kind::kMatmul || s.in.size() != 2 || s.out.size() != 1 || !s.chain_ops.empty()) continue;
+    const int x = s.out[0];
+    const SlotInfo& xs = p->slots[static_cast<size_t>(x)];
+    if (xs.output_index >= 0 || xs.dims.size() != 2 || xs.numel == 0) continue;
+    const int64_t rows = xs.dims[0], cols = xs.dims[1];
+    const int64_t k = p->slots[static_cast<size_t>(s.in[0])].dims.size() == 2 ? p->slots[static_cast<size_t>(s.in[0])].dims[1] : 0;
+    if (!fb200_matmul_uses_tensor_cores(rows, cols, k, xs.dtype, p->allow_tf32)) continue;
+    bool only_slices = true;
+    int tail = -1;
+    int64_t max_stop_before = 0;
+    for (int o : p->output_slots) if (o == x) only_slices = false;
+    for (int j = 0; j < n && only_slices; ++j) {
+      const Step& t = p->steps[static_cast<size_t>(j)];
+      bool reads = false;
+      for (int in : t.in) if (in == x) reads = true;
+      if (!reads) continue;
+      if (t.kind != Kind::kSlice || t.in.size() != 1 || t.iv[0] != 1 || t.iv[1] < 0) { only_slices = false; break; }
+      if (t.iv[2] == cols && tail < 0) tail = j;
+      else max_stop_before = std::max(max_stop_before, t.iv[2]);
+    }
+    if (!only_slices || tail < 0) continue;
+    const Step& ts = p->steps[static_cast<size_t>(tail)];
+    const int64_t start = ts.iv[1];
+    const int vec = 16 / itemsize_of(xs.dtype);
+    if (start <= 0 || start % 32 != 0 || (cols - start) % vec != 0 || max_stop_before > start) continue;
+    const int dst = ts.out[0];
+    SlotInfo& ds = p->slots[static_cast<size_t>(dst)];
+    if (ds.output_index >= 0 || ds.input_index >= 0 || ds.alias_of >= 0) continue;
+    if (!p->dry) {
+      void* buf = nullptr;
+      if (int rc = fb200_malloc(p->device, ds.bytes(), 256, &buf)) return rc;
+      p->owned.push_back(buf);
+      ds.private_ptr = buf;
+    }
+    ds.private_buf = true;
+    ds.arena_offset = -1;
+    s.split_slot = dst;
+    s.split_col = start;
+    p->steps[static_cast<size_t>(tail)].kind = Kind::kSkip;
+    PLAN_TRACE("matmul at step %d writes columns [%lld, %lld) straight into the output of the slice at step %d (private buffer)",
+               i, (long long)start, (long long)cols, tail);
+  }
+  return FB200_OK;
 }
 
 static void optimise(fb200_plan* p) {
@@ -1092,6 +1151,7 @@ static void* slot_ptr(fb200_plan* p, int slot, const void* const* inputs, void* 
   if (s.input_index >= 0) return const_cast<void*>(inputs[s.input_index]);
   if (s.output_index >= 0) return outputs[s.output_index];
   if (s.constant != nullptr) return s.constant;
+  if (s.private_ptr != nullptr) return s.private_ptr;
   if (s.arena_offset >= 0) return static_cast<char*>(p->arena) + s.arena_offset;
   return nullptr;
 }
@@ -1124,6 +1184,10 @@ static int run_step(fb200_plan* p, Step& s, const void* const* inputs, void* con
       }
       const int64_t m = in_slot(0).dims[0], k = in_slot(0).dims[1], n = in_slot(1).dims[1];
       if (in_slot(1).dims[0] != k) return set_error(FB200_INVALID_ARGUMENT, "op 'matmul': contraction dims differ");
+      if (s.split_slot >= 0) {
+        return fb200_matmul_split(in_ptr(0), in_ptr(1), out, slot_ptr(p, s.split_slot, inputs, outputs), s.split_col,
+                                  m, n, k, os.dtype, p->allow_tf32, epi_ptr, stream);
+      }
       return fb200_matmul(in_ptr(0), in_ptr(1), out, m, n, k, os.dtype, p->allow_tf32, epi_ptr, stream);
     }
     case Kind::kConv2d: {
@@ -1361,6 +1425,12 @@ static int plan_create_impl(const char* plan_text, int device, int allow_tf32, i
     fb200_plan_destroy(p);
     return rc;
   }
+  if (p->opt_level >= 1) {
+    if (int rc2 = split_matmul_tails(p)) {
+      fb200_plan_destroy(p);
+      return rc2;
+    }
+  }
   optimise(p);
   if (p->opt_level >= 1) {
     alias_reshape_sources(p);
@@ -1385,8 +1455,8 @@ extern "C" int fb200_plan_create(const char* plan_text, int device, int allow_tf
   return plan_create_impl(plan_text, device, allow_tf32, opt_level, false, plan);
 }
 
-extern "C" int fb200_plan_describe(const char* plan_text, int opt_level, fb200_plan** plan) {
-  return plan_create_impl(plan_text, 0, 0, opt_level, true, plan);
+extern "C" int fb200_plan_describe(const char* plan_text, int allow_tf32, int opt_level, fb200_plan** plan) {
+  return plan_create_impl(plan_text, 0, allow_tf32, opt_level, true, plan);
 }
 
 extern "C" int fb200_plan_destroy(fb200_plan* p) {

@@ -20,12 +20,12 @@ def load_plan_text(name: str) -> str:
         return f.read()
 
 
-def describe_plan(plan_text: str, opt_level: int = 1):
+def describe_plan(plan_text: str, opt_level: int = 1, allow_tf32: bool = False):
     """(step names, launches per run) of a plan after the executor's rewrites, without touching a
     GPU (fb200_plan_describe): what would run, not a runnable plan."""
     lib = capi.load()
     h = c_void_p()
-    capi.check(lib.fb200_plan_describe(plan_text.encode(), opt_level, byref(h)))
+    capi.check(lib.fb200_plan_describe(plan_text.encode(), 1 if allow_tf32 else 0, opt_level, byref(h)))
     try:
         names = []
         while True:

@@ -167,6 +167,15 @@ typedef struct fb200_epilogue {
 FB200_API int fb200_matmul(const void* a, const void* b, void* c, int64_t m, int64_t n,
                            int64_t k, int dtype, int allow_tf32, const fb200_epilogue* epilogue,
                            fb200_stream stream);
+/* The same product leaving in two pieces: columns [0, tail_col) go to `c` exactly where fb200_matmul
+ * puts them (row pitch n; the columns from tail_col on stay untouched there), columns
+ * [tail_col, n) go to the dense matrix `c_tail` [m, n - tail_col].  Replaces the reference's
+ * matmul followed by a `slice` of that column block (src/backends/cuda/kernels/shape.cpp:207, one
+ * cudaMemcpyAsync per row): the block is stored once, where the slice would have copied it.
+ * tail_col: a multiple of 32 in (0, n); tensor-core shapes only (fb200_matmul_uses_tensor_cores). */
+FB200_API int fb200_matmul_split(const void* a, const void* b, void* c, void* c_tail, int64_t tail_col,
+                                 int64_t m, int64_t n, int64_t k, int dtype, int allow_tf32,
+                                 const fb200_epilogue* epilogue, fb200_stream stream);
 /* Which kernel family fb200_matmul would pick: 1 = tcgen05/TMEM/TMA, 0 = SIMT. */
 FB200_API int fb200_matmul_uses_tensor_cores(int64_t m, int64_t n, int64_t k, int dtype,
                                              int allow_tf32);
@@ -402,8 +411,9 @@ FB200_API int fb200_plan_create(const char* plan_text, int device, int allow_tf3
 /* The same parsing and rewriting without a device: allocates nothing on the GPU (and needs none),
  * so the result only answers fb200_plan_launches_per_run / fb200_plan_step_op / io_spec /
  * arena_bytes; every run entry point refuses it.  For tooling and for tests of the rewrite rules on
- * machines without a GPU.  Free it with fb200_plan_destroy. */
-FB200_API int fb200_plan_describe(const char* plan_text, int opt_level, fb200_plan** plan);
+ * machines without a GPU.  allow_tf32 as for fb200_plan_create (some rewrites depend on which
+ * matmuls take the tensor-core kernel).  Free it with fb200_plan_destroy. */
+FB200_API int fb200_plan_describe(const char* plan_text, int allow_tf32, int opt_level, fb200_plan** plan);
 FB200_API int fb200_plan_destroy(fb200_plan* plan);
 FB200_API int fb200_plan_num_inputs(const fb200_plan* plan);
 FB200_API int fb200_plan_num_outputs(const fb200_plan* plan);

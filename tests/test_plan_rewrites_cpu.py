@@ -66,7 +66,7 @@ def test_mlp_absorbs_what_the_planner_allows():
 def test_a_described_plan_cannot_run():
     lib = capi.load()
     h = capi.c_void_p()
-    capi.check(lib.fb200_plan_describe(_golden("mlp_f32_b8").encode(), 1, capi.byref(h)))
+    capi.check(lib.fb200_plan_describe(_golden("mlp_f32_b8").encode(), 0, 1, capi.byref(h)))
     rc = lib.fb200_plan_run(h, None, None, None)
     assert rc == 1 and b"cannot run" in lib.fb200_last_error()
     lib.fb200_plan_destroy(h)
@@ -76,7 +76,7 @@ def test_unknown_op_is_unimplemented_with_its_name_without_a_gpu():
     lib = capi.load()
     text = "plan slots=2 arena=0\nin 0 0 1 4\nstep frobnicate nin=1 0 nout=1 1 0 -1 1 4 attrs=0\nout 1\n"
     h = capi.c_void_p()
-    rc = lib.fb200_plan_describe(text.encode(), 1, capi.byref(h))
+    rc = lib.fb200_plan_describe(text.encode(), 0, 1, capi.byref(h))
     assert rc == 4 and b"frobnicate" in lib.fb200_last_error()
 
 
@@ -89,7 +89,7 @@ def test_pool_and_index_ops_decode_and_opt_out_of_graph_replay_checks():
     bad = text.replace("attr alpha double 2.0", "attr alpha double -1.0")
     lib = capi.load()
     h = capi.c_void_p()
-    rc = lib.fb200_plan_describe(bad.encode(), 1, capi.byref(h))
+    rc = lib.fb200_plan_describe(bad.encode(), 0, 1, capi.byref(h))
     assert rc == 1 and b"alpha" in lib.fb200_last_error()
 
 
@@ -104,7 +104,7 @@ def test_gradient_internals_decode_as_single_steps():
     text = _golden("case_conv2d_grad_input_groups2").replace("attr stride int64_array [1, 2]", "attr stride int64_array [1]")
     lib = capi.load()
     h = capi.c_void_p()
-    rc = lib.fb200_plan_describe(text.encode(), 1, capi.byref(h))
+    rc = lib.fb200_plan_describe(text.encode(), 0, 1, capi.byref(h))
     assert rc == 1 and b"conv2d_grad_input_internal" in lib.fb200_last_error()
 
 
@@ -129,3 +129,17 @@ def test_a_fused_group_longer_than_one_launch_is_split_not_rejected():
               "attr arities int64_array [" + ", ".join(map(str, ar)) + "]", f'attr ops string "{ops}"', f"out {n_in}"]
     names, launches = runtime.describe_plan("\n".join(lines) + "\n")
     assert names == ["fused_elementwise_internal"] and launches == 2
+
+
+def test_mamba_gate_slice_is_written_by_the_projection_itself():
+    """With allow_tf32 the in_proj matmul takes the tensor-core kernel, which can store a trailing
+    column block into a buffer of its own: the `slice` of the gate half z and the `reshape` behind it
+    (a copy, because the planner reuses the slice's bytes for the scan's result) both disappear, as
+    does the slice of the last block of x_proj.  Without allow_tf32 (strict fp32 on the CUDA cores)
+    the plan keeps them."""
+    text = runtime.load_plan_text("mamba_f32_b16_s2048_d768")
+    names, launches = runtime.describe_plan(text, allow_tf32=True)
+    live = _live(names)
+    assert launches == 8 and "reshape" not in live and live.count("slice") == 2
+    strict, strict_launches = runtime.describe_plan(text, allow_tf32=False)
+    assert strict_launches == 10 and _live(strict).count("slice") == 4

@@ -164,3 +164,34 @@ def test_matmul_gradients_on_the_tensor_cores_and_strict(dt, tf32):
             assert fo.all_close(got, exp, dt, rtol=1e-3, atol=2e-3 * np.sqrt(red) / 3), fo.max_err(got, exp, dt)
     else:
         assert fo.all_close(ga, exp_a, dt, rtol=2e-2, atol=2e-2) and fo.all_close(gb, exp_b, dt, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("dt,tf32,tail_col", [(fo.DT_F32, True, 160), (fo.DT_BF16, False, 256), (fo.DT_F32, True, 64)],
+                         ids=["tf32_160", "bf16_256", "tf32_ragged_tail"])
+def test_matmul_split_stores_the_trailing_columns_separately(dt, tf32, tail_col):
+    """fb200_matmul_split: columns [0, tail_col) where fb200_matmul puts them (the rest of `c` keeps
+    its old bytes), columns [tail_col, n) in a dense matrix of their own; with an epilogue on both."""
+    m, k, n = 300, 96, 80 if tail_col == 64 else 416
+    a, b = _gen(m, k, n, dt, 17)
+    rng = np.random.default_rng(18)
+    bias = fo.from_accum(rng.normal(0, 0.5, (n,)).astype(np.float32), dt)
+    es = capi.ITEMSIZE[dt]
+    da, db, dbias = (capi.DeviceBuffer.from_numpy(t) for t in (a, b, bias))
+    fill = np.full((m, n), 0x3C3C if es == 2 else 0, capi.NP_STORAGE[dt])
+    dc = capi.DeviceBuffer.from_numpy(fill)
+    dtail = capi.DeviceBuffer(m * (n - tail_col) * es)
+    epi = capi.make_epilogue([("add", dbias.ptr, capi.OPERAND_COL), ("relu", None, 0)])
+    capi.matmul_split(da.ptr, db.ptr, dc.ptr, dtail.ptr, tail_col, m, n, k, dt, tf32, epi)
+    capi.synchronize()
+    assert capi.kernel_status(0) == 0
+    head = dc.download(capi.NP_STORAGE[dt], (m, n))
+    tail = dtail.download(capi.NP_STORAGE[dt], (m, n - tail_col))
+    exp = fo.relu(fo.bias_add(fo.matmul(a, b, dt), bias, dt), dt)
+    if tf32:
+        atol = 2e-3 * np.sqrt(k) * float(np.sqrt((a ** 2).mean()) * np.sqrt((b ** 2).mean()))
+        tol = dict(rtol=1e-3, atol=atol)
+    else:
+        tol = dict(rtol=2e-2, atol=2e-3)
+    assert fo.all_close(head[:, :tail_col], exp[:, :tail_col], dt, **tol)
+    assert fo.all_close(tail, exp[:, tail_col:], dt, **tol)
+    assert np.array_equal(head[:, tail_col:], fill[:, tail_col:])      # untouched
