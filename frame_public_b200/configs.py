@@ -418,6 +418,14 @@ def parity_tolerance(key: str, dtype: int, allow_tf32: bool, gold_f32: np.ndarra
             return dict(rtol=2e-2, atol=float(2.0 ** (np.floor(np.log2(max(top, 1e-30))) - 7)))
         return dict(rtol=2e-2, atol=2e-3)
     if not allow_tf32:
+        if key.startswith("gemm") and inputs is not None and inputs[1].shape[0] >= 1024:
+            # strict fp32 above 2^30 multiply-adds runs error-compensated on the tensor cores (three TF32
+            # products with the operands' low parts): no operand error, but the tensor core truncates
+            # its fp32 accumulator at each of the K/8 additions; measured worst element about
+            # 2^-23 * (K/8) of the output's rms, bounded here at 3 times that
+            k = inputs[1].shape[0]
+            rms = float(np.sqrt(np.mean(np.square(np.asarray(gold_f32, np.float64)))))
+            return dict(rtol=1e-5, atol=float(3 * 2.0 ** -23 * (k / 8) * max(rms, 1.0)))
         return dict(rtol=1e-5, atol=1e-6)
     if key.startswith("gemm") and inputs is not None:
         a, b = np.asarray(inputs[0][:64], np.float64), np.asarray(inputs[1][:, :64], np.float64)

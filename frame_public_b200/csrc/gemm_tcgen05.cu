@@ -85,6 +85,9 @@ struct GemmDest {
   void* tail_ptr;
   int64_t tail_col;
   int64_t tail_ld;
+  // error-compensated fp32: the low parts x - trunc_tf32(x) of A and B (same shapes), or nullptr
+  const void* a_lo;
+  const void* b_lo;
 };
 
 enum GemmFault : int {
@@ -310,7 +313,9 @@ __device__ __forceinline__ void transpose_chunk(const uint32_t (&r)[32], float (
 template <typename T, int ELT, int BLOCK_N, int MH, int KB, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                    const __grid_constant__ CUtensorMap tmap_b, int b_spans_map, GemmDest dest, int64_t M,
+                    const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_a_lo,
+                    const __grid_constant__ CUtensorMap tmap_b_lo, int parts, int b_spans_map, GemmDest dest, int64_t M,
                     int64_t N, int64_t K, uint32_t idesc, EpilogueDev epi, int* status) {
   using Cfg = GemmCfg<ELT, BLOCK_N, MH, KB>;
   static_assert(MH == 1 || (MH == 2 && BLOCK_N == 256), "two M halves fill TMEM with one 256 x 256 tile");
@@ -334,7 +339,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int64_t tiles_n = (N + BLOCK_N - 1) / BLOCK_N;
   const int64_t n_tiles = tiles_m * tiles_n;
   const int group_m = dest.group_m / MH > 0 ? dest.group_m / MH : 1;
-  const int64_t k_blocks = (K + Cfg::kBlockK - 1) / Cfg::kBlockK;
+  // parts == 3: the contraction runs three times over K into the same accumulator, with the operand
+  // pairs (A_lo, B), (A, B_lo), (A, B): fp32 operands split as x = trunc_tf32(x) + x_lo, the tensor
+  // core truncating every operand it reads to TF32 itself (error-compensated "3xTF32": all product
+  // terms but lo x lo, small terms first).
+  const int64_t k_blocks_part = (K + Cfg::kBlockK - 1) / Cfg::kBlockK;
+  const int64_t k_blocks = k_blocks_part * parts;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) {
@@ -348,6 +358,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    if (parts > 1) {
+      tma_prefetch_desc(&tmap_a_lo);
+      tma_prefetch_desc(&tmap_b_lo);
+    }
   }
   if (warp == 1) {
     __syncwarp();
@@ -379,19 +393,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (!ok) break;
         const uint32_t a_dst = base + stage * Cfg::kStageBytes;
         const uint32_t b_dst = a_dst + Cfg::kAStageBytes;
-        const int32_t k0 = static_cast<int32_t>(kb * Cfg::kBlockK);
+        const int64_t part = kb / k_blocks_part;                 // warp-uniform
+        const int32_t k0 = static_cast<int32_t>((kb - part * k_blocks_part) * Cfg::kBlockK);
         if (!loads_b) {
+          const CUtensorMap* ma = (parts > 1 && part == 0) ? &tmap_a_lo : &tmap_a;
           mbar_arrive_expect_tx_elect(full_bar(stage), Cfg::kAStageBytes);
-          tma_load_2d_elect(a_dst, &tmap_a, full_bar(stage), k0, a_row);
+          tma_load_2d_elect(a_dst, ma, full_bar(stage), k0, a_row);
         } else {
+          const CUtensorMap* mb = (parts > 1 && part == 1) ? &tmap_b_lo : &tmap_b;
           mbar_arrive_expect_tx_elect(full_bar(stage), Cfg::kBStageBytes);
           if (b_spans_map) {
             // B seen as [N / span][K][span columns]: the whole B stage is one copy
-            tma_load_3d_elect(b_dst, &tmap_b, full_bar(stage), 0, k0, b_col / Cfg::kBChunkCols);
+            tma_load_3d_elect(b_dst, mb, full_bar(stage), 0, k0, b_col / Cfg::kBChunkCols);
           } else {
 #pragma unroll
             for (int c = 0; c < Cfg::kBChunks; ++c) {
-              tma_load_2d_elect(b_dst + c * Cfg::kBChunkBytes, &tmap_b, full_bar(stage), b_col + c * Cfg::kBChunkCols, k0);
+              tma_load_2d_elect(b_dst + c * Cfg::kBChunkBytes, mb, full_bar(stage), b_col + c * Cfg::kBChunkCols, k0);
             }
           }
         }
@@ -721,6 +738,16 @@ static int launch_tc_epi(const void* a, const void* b, const GemmDest& c, int64_
   } else {
     if (int rc = make_tmap_2d(&tb, b, dtype, k, n, Cfg::kBlockK, ELT == 4)) return rc;
   }
+  CUtensorMap ta_lo = ta, tb_lo = tb;
+  const int parts = (c.a_lo != nullptr && c.b_lo != nullptr) ? 3 : 1;
+  if (parts == 3) {
+    if (int rc = make_tmap_rows(&ta_lo, c.a_lo, dtype, m, k, Cfg::kTileM, KB)) return rc;
+    if (b_spans_map) {
+      if (int rc = make_tmap_b_spans(&tb_lo, c.b_lo, dtype, k, n, Cfg::kBlockK, Cfg::kBChunks, ELT == 4)) return rc;
+    } else {
+      if (int rc = make_tmap_2d(&tb_lo, c.b_lo, dtype, k, n, Cfg::kBlockK, ELT == 4)) return rc;
+    }
+  }
   int* status = nullptr;
   if (int rc = device_status_word(&status)) return rc;
   const uint32_t fmt = dtype == FB200_F32 ? kFmtTF32 : (dtype == FB200_BF16 ? kFmtBF16 : kFmtF16);
@@ -730,7 +757,7 @@ static int launch_tc_epi(const void* a, const void* b, const GemmDest& c, int64_
                                      static_cast<int>(Cfg::kSmemBytes)));
   const int64_t tiles = ((m + Cfg::kTileM - 1) / Cfg::kTileM) * ((n + BLOCK_N - 1) / BLOCK_N);
   const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
-  kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, b_spans_map, c, m, n, k, idesc,
+  kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, ta_lo, tb_lo, parts, b_spans_map, c, m, n, k, idesc,
                                                       epi, status);
   return after_launch("gemm_tcgen05_kernel");
 }
@@ -781,6 +808,26 @@ static int launch_tc_n(const void* a, const void* b, const GemmDest& c, int64_t 
   return launch_tc<T, ELT, 64>(a, b, c, m, n, k, dtype, epi, s);
 }
 
+// x_lo = x - trunc_tf32(x): what the tensor core drops when it reads an fp32 operand as TF32 (it
+// truncates: the low 13 mantissa bits are ignored).  Exact in fp32.
+__global__ void __launch_bounds__(256)
+tf32_low_part_kernel(const float4* __restrict__ x, float4* __restrict__ lo, int64_t n_vec) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
+    const float4 v = x[i];
+    float4 r;
+    r.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
+    r.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
+    r.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
+    r.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
+    lo[i] = r;
+  }
+}
+
+// Strict fp32 products from this many multiply-adds on run on the tensor cores with error
+// compensation instead of on the CUDA cores (about 0.1 ms of the SIMT kernel).
+constexpr int64_t kCompensatedMinMacs = int64_t(1) << 30;
+
 static bool tensor_core_eligible(const void* a, const void* b, const void* c, int64_t m, int64_t n,
                                  int64_t k, int dtype, int allow_tf32) {
   (void)m;
@@ -820,7 +867,15 @@ static int matmul_impl(const void* a, const void* b, void* c, void* c_tail, int6
   EpilogueDev epi{};
   if (int rc = make_epilogue(epilogue, &epi, who)) return rc;
   cudaStream_t s = as_stream(stream);
-  if (k > 0 && tensor_core_eligible(a, b, c, m, n, k, dtype, allow_tf32)) {
+  const bool exact_order = allow_tf32 < 0;   // the CPU reference's order of additions, whatever the size
+  if (exact_order) allow_tf32 = 0;
+  // Strict fp32 (allow_tf32 == 0) of a size worth it: three TF32 products with the operands' low
+  // parts ("3xTF32") at about a third of the TF32 rate.  Operand rounding is gone; the error left is
+  // the tensor core's truncating fp32 accumulation (about 2^-23 * K/8 of the result's scale).
+  const bool compensated = dtype == FB200_F32 && allow_tf32 == 0 && !exact_order && k > 0 && m * n >= 128 * 128 &&
+                           m * n * k >= kCompensatedMinMacs && (m * k) % 4 == 0 && (k * n) % 4 == 0 &&
+                           tensor_core_eligible(a, b, c, m, n, k, dtype, 1);
+  if (k > 0 && (compensated || tensor_core_eligible(a, b, c, m, n, k, dtype, allow_tf32))) {
     GemmDest dest{};
     dest.group_m = kGemmGroupM;
     dest.ptr[0] = c;
@@ -830,6 +885,24 @@ static int matmul_impl(const void* a, const void* b, void* c, void* c_tail, int6
     dest.tail_ptr = c_tail;
     dest.tail_col = tail_col;
     dest.tail_ld = n - tail_col;
+    if (compensated) {
+      float* lo = nullptr;
+      const size_t na = static_cast<size_t>(m) * k, nb = static_cast<size_t>(k) * n;
+      FB200_CUDA_OK(cudaMallocAsync(reinterpret_cast<void**>(&lo), (na + nb) * sizeof(float), s));
+      tf32_low_part_kernel<<<grid_for(na / 4, 256, 8), 256, 0, s>>>(static_cast<const float4*>(a), reinterpret_cast<float4*>(lo), na / 4);
+      int rc = after_launch("tf32_low_part_kernel");
+      if (rc == FB200_OK) {
+        tf32_low_part_kernel<<<grid_for(nb / 4, 256, 8), 256, 0, s>>>(static_cast<const float4*>(b), reinterpret_cast<float4*>(lo + na), nb / 4);
+        rc = after_launch("tf32_low_part_kernel");
+      }
+      if (rc == FB200_OK) {
+        dest.a_lo = lo;
+        dest.b_lo = lo + na;
+        rc = launch_tc_n<float, 4>(a, b, dest, m, n, k, dtype, epi, s);
+      }
+      cudaFreeAsync(lo, s);
+      return rc;
+    }
     switch (dtype) {
       case FB200_F32: return launch_tc_n<float, 4>(a, b, dest, m, n, k, dtype, epi, s);
       case FB200_BF16: return launch_tc_n<__nv_bfloat16, 2>(a, b, dest, m, n, k, dtype, epi, s);

@@ -1188,7 +1188,10 @@ static int run_step(fb200_plan* p, Step& s, const void* const* inputs, void* con
         return fb200_matmul_split(in_ptr(0), in_ptr(1), out, slot_ptr(p, s.split_slot, inputs, outputs), s.split_col,
                                   m, n, k, os.dtype, p->allow_tf32, epi_ptr, stream);
       }
-      return fb200_matmul(in_ptr(0), in_ptr(1), out, m, n, k, os.dtype, p->allow_tf32, epi_ptr, stream);
+      // opt_level 0 is the step-by-step path in the CPU reference's own arithmetic: strict fp32
+      // products keep the CPU's order of additions at any size
+      const int precision = (p->opt_level == 0 && !p->allow_tf32) ? -1 : p->allow_tf32;
+      return fb200_matmul(in_ptr(0), in_ptr(1), out, m, n, k, os.dtype, precision, epi_ptr, stream);
     }
     case Kind::kConv2d: {
       if (s.in.size() < 2 || in_slot(0).dims.size() != 4 || in_slot(1).dims.size() != 4) {

@@ -163,7 +163,13 @@ typedef struct fb200_epilogue {
  * replaces the cublasLtMatmul call of src/backends/cuda/kernels/matmul.cpp:90-276).
  * BF16/F16: tcgen05 kind::f16.  F32: allow_tf32 != 0 selects tcgen05 kind::tf32 (the
  * CompileOptions::allow_tf32 switch, include/frame/hal/backend.h:51-63); allow_tf32 == 0 keeps
- * strict fp32 arithmetic.  `epilogue` may be NULL. */
+ * fp32 accuracy: products below 2^30 multiply-adds (and shapes TMA cannot address) run on the CUDA
+ * cores in the CPU reference's order of additions (bit-identical to it); larger ones run on the
+ * tensor cores as three TF32 products with the operands' low parts (error-compensated "3xTF32":
+ * no operand rounding left; the tensor core truncates its fp32 accumulator at each of the K/8
+ * additions, which leaves about 2^-23 * K/8 of the result's scale: 5-30 times a round-to-nearest
+ * fp32 summation, 50-100 times below TF32; about a third of the TF32 rate).  allow_tf32 < 0 forces the CPU's order at any
+ * size.  `epilogue` may be NULL. */
 FB200_API int fb200_matmul(const void* a, const void* b, void* c, int64_t m, int64_t n,
                            int64_t k, int dtype, int allow_tf32, const fb200_epilogue* epilogue,
                            fb200_stream stream);

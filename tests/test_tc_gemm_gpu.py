@@ -6,6 +6,9 @@ atol 2e-3).  fp32 with allow_tf32: operands are read as TF32 (10 explicit mantis
 error of a K-term dot product is about 2^-10 * sqrt(K) * rms(a) * rms(b); tolerance =
 rtol 1e-3 (the reference's TF32 tier, tests/cpp/common/tolerance.h:90-98) plus
 atol = 2e-3 * sqrt(K) * rms(a) * rms(b) for outputs that cancel to near zero."""
+import json
+import os
+
 import numpy as np
 import pytest
 
@@ -195,3 +198,42 @@ def test_matmul_split_stores_the_trailing_columns_separately(dt, tf32, tail_col)
     assert fo.all_close(head[:, :tail_col], exp[:, :tail_col], dt, **tol)
     assert fo.all_close(tail, exp[:, tail_col:], dt, **tol)
     assert np.array_equal(head[:, tail_col:], fill[:, tail_col:])      # untouched
+
+
+@pytest.mark.parametrize("shape", [(1024, 1024, 1024), (2048, 512, 1536), (1152, 4096, 256)], ids=lambda s: "x".join(map(str, s)))
+def test_large_strict_fp32_matmul_is_error_compensated_on_the_tensor_cores(shape):
+    """allow_tf32 = 0 from 2^30 multiply-adds on: three TF32 products with the operands' low parts.  The
+    operand error of TF32 is gone; what remains is the tensor core's own accumulation, which truncates
+    the fp32 accumulator at each of its K/8 additions: measured mean error 0.13 * 2^-23 * (K/8) * rms(out)
+    (K = 512..8192), i.e. 5-30 times a round-to-nearest fp32 summation and 50-100 times below plain
+    TF32.  Bounds: mean <= 0.3 and max <= 3 of that unit, against a float64 product."""
+    m, k, n = shape
+    a, b = _gen(m, k, n, fo.DT_F32, 19)
+    got = _run(a, b, fo.DT_F32, False)
+    exact = a.astype(np.float64) @ b.astype(np.float64)
+    err = np.abs(got.astype(np.float64) - exact)
+    unit = 2.0 ** -23 * (k / 8) * float(np.sqrt(np.mean(exact ** 2)))
+    tf32_level = 2.0 ** -11 * np.sqrt(k) * float(np.sqrt((a ** 2).mean()) * np.sqrt((b ** 2).mean()))
+    err_fp32_sum = np.abs((a @ b).astype(np.float64) - exact)
+    path = os.environ.get("FRAME_B200_ERROR_TABLE")
+    if path:
+        with open(path, "a") as f:
+            f.write(json.dumps({"case": "compensated_fp32_matmul", "shape": list(shape), "max_abs": float(err.max()),
+                                "mean_abs": float(err.mean()), "fp32_sum_mean_abs": float(err_fp32_sum.mean()),
+                                "fp32_sum_max_abs": float(err_fp32_sum.max()), "unit": unit, "tf32_level": tf32_level}) + "\n")
+    assert err.mean() <= 0.3 * unit and err.max() <= 3.0 * unit, (float(err.mean() / unit), float(err.max() / unit))
+    assert err.mean() <= tf32_level / 20, (float(err.mean()), tf32_level)
+
+
+def test_exact_order_can_be_forced_at_any_size():
+    """allow_tf32 < 0: the CPU reference's order of additions (bit-identical) even above the size from
+    which strict fp32 moves to the tensor cores."""
+    m, k, n = 1024, 1024, 1024
+    a, b = _gen(m, k, n, fo.DT_F32, 20)
+    da, db = capi.DeviceBuffer.from_numpy(a), capi.DeviceBuffer.from_numpy(b)
+    dc = capi.DeviceBuffer(m * n * 4)
+    capi.check(capi.load().fb200_matmul(da.ptr, db.ptr, dc.ptr, m, n, k, capi.F32, -1, None, None))
+    capi.synchronize()
+    got = dc.download(np.float32, (m, n))
+    rows = slice(0, 8)
+    assert np.array_equal(got[rows], fo.matmul(a[rows], b, fo.DT_F32))
