@@ -37,6 +37,12 @@ inline int after_launch(const char* kernel) {
   return FB200_OK;
 }
 
+// Stream-ordered scratch for kernels that need a temporary (cudaMallocAsync on `stream`; release it
+// with cudaFreeAsync on the same stream).  The first call on a device tells the device's default
+// memory pool to keep up to 1 GiB of freed blocks instead of returning them to the driver at every
+// synchronisation point: without that each eager call pays a driver allocation.
+cudaError_t scratch_alloc_async(void** ptr, size_t bytes, cudaStream_t stream);
+
 constexpr int kNumSMs = 148;
 
 inline int itemsize_of(int dtype) {

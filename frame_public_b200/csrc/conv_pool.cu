@@ -302,6 +302,9 @@ extern "C" int fb200_conv2d_tcgen05(const void* x, const void* w, const void* bi
                                     const fb200_epilogue* epilogue, fb200_stream stream);
 
 // Implemented in conv_halo_tcgen05.cu: the halo-tile variant, tried first.
+extern "C" int fb200_conv2d_planes_tcgen05(const void* x, const void* w, const void* bias, void* out,
+                                           const fb200_conv2d_params* p, int dtype,
+                                           const fb200_epilogue* epilogue, fb200_stream stream);
 extern "C" int fb200_conv2d_halo_tcgen05(const void* x, const void* w, const void* bias, void* out,
                                          const fb200_conv2d_params* p, int dtype,
                                          const fb200_epilogue* epilogue, fb200_stream stream);
@@ -335,6 +338,10 @@ extern "C" int fb200_conv2d(const void* x, const void* w, const void* bias, void
     return set_error(FB200_INVALID_ARGUMENT, "conv2d: null argument");
   }
   if (allow_tf32 && dtype == FB200_F32) {
+    {
+      const int rc = fb200_conv2d_planes_tcgen05(x, w, bias, out, pp, dtype, epilogue, stream);
+      if (rc != FB200_UNIMPLEMENTED) return rc;
+    }
     {
       const int rc = fb200_conv2d_halo_tcgen05(x, w, bias, out, pp, dtype, epilogue, stream);
       if (rc != FB200_UNIMPLEMENTED) return rc;

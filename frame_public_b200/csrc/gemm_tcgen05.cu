@@ -888,7 +888,7 @@ static int matmul_impl(const void* a, const void* b, void* c, void* c_tail, int6
     if (compensated) {
       float* lo = nullptr;
       const size_t na = static_cast<size_t>(m) * k, nb = static_cast<size_t>(k) * n;
-      FB200_CUDA_OK(cudaMallocAsync(reinterpret_cast<void**>(&lo), (na + nb) * sizeof(float), s));
+      FB200_CUDA_OK(scratch_alloc_async(reinterpret_cast<void**>(&lo), (na + nb) * sizeof(float), s));
       tf32_low_part_kernel<<<grid_for(na / 4, 256, 8), 256, 0, s>>>(static_cast<const float4*>(a), reinterpret_cast<float4*>(lo), na / 4);
       int rc = after_launch("tf32_low_part_kernel");
       if (rc == FB200_OK) {
@@ -1055,7 +1055,7 @@ extern "C" int fb200_matmul_grad_lhs(const void* gy, const void* b, void* ga, in
   if (n > 0 && m * k >= 128 * 128 && tensor_core_eligible(gy, b, ga, m, k, n, dtype, allow_tf32) &&
       (k * itemsize_of(dtype)) % 16 == 0) {
     void* bt = nullptr;
-    FB200_CUDA_OK(cudaMallocAsync(&bt, static_cast<size_t>(n) * k * itemsize_of(dtype), s));
+    FB200_CUDA_OK(scratch_alloc_async(&bt, static_cast<size_t>(n) * k * itemsize_of(dtype), s));
     const int64_t dims[2] = {k, n}, perm[2] = {1, 0};
     int rc = fb200_transpose(b, bt, 2, dims, perm, itemsize_of(dtype), stream);
     if (rc == FB200_OK) rc = fb200_matmul(gy, bt, ga, m, k, n, dtype, allow_tf32, nullptr, stream);
@@ -1076,7 +1076,7 @@ extern "C" int fb200_matmul_grad_rhs(const void* a, const void* gy, void* gb, in
   if (m > 0 && k * n >= 128 * 128 && tensor_core_eligible(a, gy, gb, k, n, m, dtype, allow_tf32) &&
       (k * itemsize_of(dtype)) % 16 == 0) {
     void* at = nullptr;
-    FB200_CUDA_OK(cudaMallocAsync(&at, static_cast<size_t>(m) * k * itemsize_of(dtype), s));
+    FB200_CUDA_OK(scratch_alloc_async(&at, static_cast<size_t>(m) * k * itemsize_of(dtype), s));
     const int64_t dims[2] = {m, k}, perm[2] = {1, 0};
     int rc = fb200_transpose(a, at, 2, dims, perm, itemsize_of(dtype), stream);
     if (rc == FB200_OK) rc = fb200_matmul(at, gy, gb, k, n, m, dtype, allow_tf32, nullptr, stream);

@@ -139,7 +139,7 @@ static int scatter_impl(const void* updates, const void* indices, void* out, int
   if (direct) {
     acc = static_cast<float*>(out);
   } else {
-    FB200_CUDA_OK(cudaMallocAsync(reinterpret_cast<void**>(&acc), static_cast<size_t>(n_out) * 4, s));
+    FB200_CUDA_OK(scratch_alloc_async(reinterpret_cast<void**>(&acc), static_cast<size_t>(n_out) * 4, s));
   }
   FB200_CUDA_OK(cudaMemsetAsync(acc, 0, static_cast<size_t>(n_out) * 4, s));
   int rc = FB200_OK;

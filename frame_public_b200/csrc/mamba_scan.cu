@@ -408,7 +408,7 @@ extern "C" int fb200_mamba_scan(const void* u, const void* delta, const void* A,
   if (ck.chunks > 1) {
     const size_t n_state = static_cast<size_t>(batch) * ck.chunks * dm * nstate;
     const size_t n_dsum = static_cast<size_t>(batch) * ck.chunks * dm;
-    FB200_CUDA_OK(cudaMallocAsync(reinterpret_cast<void**>(&scratch), (n_state + n_dsum) * sizeof(float), s));
+    FB200_CUDA_OK(scratch_alloc_async(reinterpret_cast<void**>(&scratch), (n_state + n_dsum) * sizeof(float), s));
     ck.state = scratch;
     ck.dsum = scratch + n_state;
   }

@@ -35,6 +35,22 @@ int cuda_error(cudaError_t err, const char* what) {
                    cudaGetErrorString(err));
 }
 
+cudaError_t scratch_alloc_async(void** ptr, size_t bytes, cudaStream_t stream) {
+  static std::atomic<uint64_t> configured{0};   // one bit per device ordinal
+  int device = 0;
+  if (cudaGetDevice(&device) == cudaSuccess && device >= 0 && device < 64 &&
+      (configured.load(std::memory_order_relaxed) & (uint64_t(1) << device)) == 0) {
+    cudaMemPool_t pool = nullptr;
+    if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess && pool != nullptr) {
+      uint64_t keep = uint64_t(1) << 30;
+      (void)cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+    }
+    (void)cudaGetLastError();
+    configured.fetch_or(uint64_t(1) << device, std::memory_order_relaxed);
+  }
+  return cudaMallocAsync(ptr, bytes, stream);
+}
+
 static int use_device(int device) {
   FB200_CUDA_OK(cudaSetDevice(device));
   return FB200_OK;

@@ -339,7 +339,7 @@ static int launch_scan(const void* x, const void* a, const void* b, const void* 
     const int64_t chunks = rows < kNumSMs * 8 ? scan_chunking(rows, steps, W, &chunk_len) : 1;
     if (chunks >= 2) {
       float2* scratch = nullptr;
-      FB200_CUDA_OK(cudaMallocAsync(reinterpret_cast<void**>(&scratch),
+      FB200_CUDA_OK(scratch_alloc_async(reinterpret_cast<void**>(&scratch),
                                     static_cast<size_t>(rows * chunks) * sizeof(float2), s));
       const int rc = scan_chunked_launch<T>(x, a, b, c, d, out, rows, steps, chunks, chunk_len, scratch, s);
       FB200_CUDA_OK(cudaFreeAsync(scratch, s));

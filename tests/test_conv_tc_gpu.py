@@ -31,6 +31,18 @@ CASES = [
     ((2, 96, 8, 8), (32, 96, 3, 3), (1, 1), (1, 1), True),
     # results through the TMA-store tile, last tile of each image only partly inside it (22 rows, 10 per tile)
     ((2, 8, 22, 12), (24, 8, 3, 3), (1, 1), (1, 1), True),
+    # column-shifted planes kernel (stride 1, channels a multiple of 8): 1x1; 3x3 without padding;
+    # 5x5 and 7x7 with "same" padding; rows of 28 (four per tile), 64 and 96 pixels; 256 -> 256 channels
+    # (eight-channel blocks, two accumulators per round); an image shorter than a tile
+    ((2, 16, 16, 16), (24, 16, 1, 1), (1, 1), (0, 0), True),
+    ((1, 8, 14, 14), (16, 8, 3, 3), (1, 1), (0, 0), False),
+    ((1, 8, 12, 12), (8, 8, 5, 5), (1, 1), (2, 2), True),
+    ((1, 8, 16, 16), (40, 8, 7, 7), (1, 1), (3, 3), True),
+    ((3, 32, 28, 28), (64, 32, 3, 3), (1, 1), (1, 1), True),
+    ((1, 16, 20, 64), (32, 16, 3, 3), (1, 1), (1, 1), True),
+    ((1, 8, 9, 96), (16, 8, 3, 3), (1, 1), (1, 1), False),
+    ((2, 256, 28, 28), (256, 256, 3, 3), (1, 1), (1, 1), True),
+    ((5, 24, 3, 8), (8, 24, 3, 3), (1, 1), (1, 1), True),
 ]
 
 
