@@ -493,6 +493,11 @@ def run_ours(args):
         pb.sync()
         cpu_baseline, parity = cpu_slab_baseline(wl, pb.output_host(0))
 
+    # ---- the same graph through the reference framework's own API with this backend plugged in ----------
+    via_frame = None
+    if rank == 0 and world == 1 and not wl.is_gemm and not args.no_cpu_baseline:
+        via_frame = via_frame_leg(wl)
+
     extras = {}
     if args.workload == DEFAULT_WORKLOAD and not args.no_extras:
         extras = default_workload_extras(args, rank, local_rank, world, device, stream, dist, wl, pb)
@@ -507,7 +512,8 @@ def run_ours(args):
             "config": bench_config(wl, world),
             "run": {"plan": pb.plan_name, "l2": pb.l2_note, "accumulate": "fp32",
                     "launches_per_step": pb.plan.launches_per_run, "arena_bytes": pb.plan.arena_bytes,
-                    "partition": f"{wl.batch // world} of {wl.batch} {'rows of A' if wl.is_gemm else 'samples'} per rank, no collective"},
+                    "partition": f"{wl.batch // world} of {wl.batch} {'rows of A' if wl.is_gemm else 'samples'} per rank, no collective",
+                    "via_frame": via_frame},
             "e2e": {"value": round(e2e_value, 3) if ok else None, "unit": wl.unit, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_ms, 3),
                     "resident": "parameters (weights, full-shape biases) stay on the device; activations and results travel"},
@@ -528,6 +534,30 @@ def bench_config(wl, world):
     """The workload description both arms print (same keys, same values)."""
     return {"workload": wl.name, "batch": wl.batch, "partition": "contiguous batch ranges, one graph per GPU",
             "n_shards": world}
+
+
+def via_frame_leg(wl):
+    """ms per Executable::run of the SAME graph compiled by the reference framework's runtime::compile
+    for backend "cuda" with this repository's plugin loaded (cache, nine-pass pipeline,
+    B200Backend::compile, then B200Executable::run on resident tensors): what a Frame user's call costs,
+    adapter validation and locking included.  Host wall clock over back-to-back runs and one stream
+    synchronise.  The framework is the reference build of oracle/_ref used as the HOST of the plugin."""
+    from oracle import ref_runtime
+    if not ref_runtime.available():
+        return None
+    try:
+        ref_runtime.load_b200_backend()
+        full = wl.full()
+        comp = ref_runtime.Compiled(full.with_backend("cuda"), "cuda", allow_tf32=wl.allow_tf32)
+        comp.run(full.inputs)
+        comp.time_run(20)
+        iters = 200 if wl.key == "mlp" else 50
+        ms = comp.time_run(iters) * 1e3
+        comp.close()
+        return {"ms_per_step": round(ms, 4), "runs": iters,
+                "path": "runtime::compile(graph, \"cuda\") -> Executable::run through the C++ adapter, resident tensors"}
+    except Exception as e:   # the leg is informational: the plan path above is what the line reports
+        return {"error": str(e)[:200]}
 
 
 # ---- the reference CPU backend on a slab of the workload ---------------------------------------------

@@ -19,6 +19,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <memory>
 #include <mutex>
 #include <sstream>
 #include <string>
@@ -44,8 +45,7 @@ struct SlotInfo {
   int output_index = -1;      // >= 0: graph output (first occurrence)
   int alias_of = -1;          // >= 0: same bytes as that slot
   void* constant = nullptr;   // materialised constant
-  bool private_buf = false;   // lives in a buffer of the plan's own, outside the planner's arena
-  void* private_ptr = nullptr;
+  int private_index = -1;     // >= 0: lives in buffer `private_index` of the run's workspace, outside the planner's arena
   bool is_constant = false;   // produced by a `constant` step
   bool splat = false;         // constant whose elements are all equal ...
   float splat_value = 0.0f;   // ... to this value (as stored in the slot's dtype)
@@ -94,15 +94,12 @@ struct fb200_plan {
   std::vector<Step> steps;
   std::vector<int> input_slots, output_slots;
   size_t arena_bytes = 0;
-  void* arena = nullptr;
-  std::vector<void*> owned;           // constants
-  std::vector<void*> stage_in, stage_out;  // device staging for run_host
-  int launches = 0;
-  std::mutex mu;
-  // CUDA-graph replay of the step list: the first run with a given set of input/output pointers
-  // is eager (it also performs every lazy initialisation), the second captures the launches into
-  // a graph, later runs with the same pointers replay it with one cudaGraphLaunch.
-  bool graph_enabled = true;
+  std::vector<void*> owned;           // constants, device tables
+  // Everything a run writes lives in a workspace: the arena at the planner's offsets plus the plan's
+  // private buffers.  Each stream that runs the plan gets a workspace of its own (up to
+  // kMaxWorkspaces), so runs on different streams from different host threads overlap on the device;
+  // callers beyond that, and callers that share a stream, take turns on a workspace's mutex.  The
+  // CUDA graphs captured for a stream belong to its workspace.
   struct GraphEntry {
     std::vector<const void*> key;   // input pointers, output pointers, stream
     int runs = 0;
@@ -110,8 +107,25 @@ struct fb200_plan {
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
   };
-  std::vector<GraphEntry> graphs;   // a few pointer sets (the pipelined host path alternates two)
-  uint64_t graph_clock = 0;
+  struct Workspace {
+    fb200_stream stream = nullptr;
+    bool claimed = false;
+    void* arena = nullptr;
+    std::vector<void*> priv;
+    std::mutex run_mu;
+    std::vector<GraphEntry> graphs;   // a few pointer sets (the pipelined host path alternates two)
+    uint64_t graph_clock = 0;
+  };
+  static constexpr size_t kMaxWorkspaces = 4;
+  std::vector<std::unique_ptr<Workspace>> workspaces;
+  std::vector<size_t> private_bytes;  // size of each private buffer
+  std::vector<void*> stage_in, stage_out;  // device staging for run_host
+  int launches = 0;
+  std::mutex mu;
+  // CUDA-graph replay of the step list: the first run with a given set of input/output pointers
+  // is eager (it also performs every lazy initialisation), the second captures the launches into
+  // a graph, later runs with the same pointers replay it with one cudaGraphLaunch.
+  std::atomic<bool> graph_enabled{true};
   // pipelined host runs: two sets of staging buffers, a copy-in and a copy-out stream, and events
   // that order H2D(k) -> run(k) -> D2H(k) and keep a staging set from being reused too early
   std::vector<void*> stage_in2, stage_out2;
@@ -559,13 +573,8 @@ static int split_matmul_tails(fb200_plan* p) {
     const int dst = ts.out[0];
     SlotInfo& ds = p->slots[static_cast<size_t>(dst)];
     if (ds.output_index >= 0 || ds.input_index >= 0 || ds.alias_of >= 0) continue;
-    if (!p->dry) {
-      void* buf = nullptr;
-      if (int rc = fb200_malloc(p->device, ds.bytes(), 256, &buf)) return rc;
-      p->owned.push_back(buf);
-      ds.private_ptr = buf;
-    }
-    ds.private_buf = true;
+    ds.private_index = static_cast<int>(p->private_bytes.size());
+    p->private_bytes.push_back(ds.bytes());
     ds.arena_offset = -1;
     s.split_slot = dst;
     s.split_col = start;
@@ -1145,14 +1154,59 @@ static void fuse_time_major_convs(fb200_plan* p) {
   }
 }
 
+// The workspace the calling thread is running on (set for the duration of a run).
+static thread_local fb200_plan::Workspace* t_ws = nullptr;
+
+static int workspace_alloc(fb200_plan* p, fb200_plan::Workspace* ws) {
+  if (p->arena_bytes > 0) { if (int rc = fb200_malloc(p->device, p->arena_bytes, 256, &ws->arena)) return rc; }
+  for (size_t bytes : p->private_bytes) {
+    void* buf = nullptr;
+    if (bytes > 0) { if (int rc = fb200_malloc(p->device, bytes, 256, &buf)) return rc; }
+    ws->priv.push_back(buf);
+  }
+  return FB200_OK;
+}
+
+static void workspace_free(fb200_plan* p, fb200_plan::Workspace* ws) {
+  for (auto& e : ws->graphs) {
+    if (e.exec) cudaGraphExecDestroy(e.exec);
+    if (e.graph) cudaGraphDestroy(e.graph);
+  }
+  if (ws->arena) fb200_free(p->device, ws->arena);
+  for (void* q : ws->priv) if (q) fb200_free(p->device, q);
+}
+
+// The workspace of `stream`: its own if it has one or one can still be made, else the first one
+// (shared; its mutex serialises the sharers).
+static int acquire_workspace(fb200_plan* p, fb200_stream stream, fb200_plan::Workspace** out) {
+  std::lock_guard<std::mutex> lock(p->mu);
+  for (auto& w : p->workspaces) {
+    if (w->claimed && w->stream == stream) { *out = w.get(); return FB200_OK; }
+  }
+  for (auto& w : p->workspaces) {
+    if (!w->claimed) { w->claimed = true; w->stream = stream; *out = w.get(); return FB200_OK; }
+  }
+  if (p->workspaces.size() < fb200_plan::kMaxWorkspaces) {
+    std::unique_ptr<fb200_plan::Workspace> w(new fb200_plan::Workspace());
+    if (int rc = workspace_alloc(p, w.get())) { workspace_free(p, w.get()); return rc; }
+    w->claimed = true;
+    w->stream = stream;
+    *out = w.get();
+    p->workspaces.push_back(std::move(w));
+    return FB200_OK;
+  }
+  *out = p->workspaces[0].get();
+  return FB200_OK;
+}
+
 static void* slot_ptr(fb200_plan* p, int slot, const void* const* inputs, void* const* outputs) {
   const int r = root_slot(*p, slot);
   const SlotInfo& s = p->slots[r];
   if (s.input_index >= 0) return const_cast<void*>(inputs[s.input_index]);
   if (s.output_index >= 0) return outputs[s.output_index];
   if (s.constant != nullptr) return s.constant;
-  if (s.private_ptr != nullptr) return s.private_ptr;
-  if (s.arena_offset >= 0) return static_cast<char*>(p->arena) + s.arena_offset;
+  if (s.private_index >= 0) return t_ws != nullptr ? t_ws->priv[static_cast<size_t>(s.private_index)] : nullptr;
+  if (s.arena_offset >= 0) return t_ws != nullptr ? static_cast<char*>(t_ws->arena) + s.arena_offset : nullptr;
   return nullptr;
 }
 
@@ -1419,7 +1473,7 @@ static int plan_create_impl(const char* plan_text, int device, int allow_tf32, i
   if (rc == FB200_OK) {
     // graph outputs are written in the caller's buffers, never in the arena
     for (int o : p->output_slots) p->slots[o].arena_offset = -1;
-    if (p->arena_bytes > 0 && !dry) rc = fb200_malloc(device, p->arena_bytes, 256, &p->arena);
+
   }
   for (size_t i = 0; rc == FB200_OK && i < p->steps.size(); ++i) {
     if (p->steps[i].kind == Kind::kConstant) rc = materialise_constant(p, p->steps[i]);
@@ -1440,7 +1494,17 @@ static int plan_create_impl(const char* plan_text, int device, int allow_tf32, i
     fuse_attention_fans(p);
     fuse_time_major_convs(p);
   }
-  if (const char* env = getenv("FRAME_B200_GRAPH")) p->graph_enabled = p->graph_enabled && atoi(env) != 0;
+  if (!dry) {
+    // the first workspace; further streams get theirs at their first run
+    std::unique_ptr<fb200_plan::Workspace> w(new fb200_plan::Workspace());
+    if (int rc2 = workspace_alloc(p, w.get())) {
+      workspace_free(p, w.get());
+      fb200_plan_destroy(p);
+      return rc2;
+    }
+    p->workspaces.push_back(std::move(w));
+  }
+  if (const char* env = getenv("FRAME_B200_GRAPH")) p->graph_enabled = p->graph_enabled.load() && atoi(env) != 0;
   p->launches = 0;
   for (const Step& s : p->steps) {
     if (s.kind != Kind::kSkip && s.kind != Kind::kAlias && s.kind != Kind::kConstant && s.kind != Kind::kCopy) ++p->launches;
@@ -1464,10 +1528,7 @@ extern "C" int fb200_plan_describe(const char* plan_text, int allow_tf32, int op
 
 extern "C" int fb200_plan_destroy(fb200_plan* p) {
   if (p == nullptr) return FB200_OK;
-  for (auto& e : p->graphs) {
-    if (e.exec) cudaGraphExecDestroy(e.exec);
-    if (e.graph) cudaGraphDestroy(e.graph);
-  }
+  for (auto& w : p->workspaces) workspace_free(p, w.get());
   for (int b = 0; b < 2; ++b) {
     if (p->ev_in[b]) cudaEventDestroy(p->ev_in[b]);
     if (p->ev_run[b]) cudaEventDestroy(p->ev_run[b]);
@@ -1477,7 +1538,6 @@ extern "C" int fb200_plan_destroy(fb200_plan* p) {
   if (p->s_d2h) cudaStreamDestroy(p->s_d2h);
   for (void* q : p->stage_in2) fb200_free(p->device, q);
   for (void* q : p->stage_out2) fb200_free(p->device, q);
-  if (p->arena) fb200_free(p->device, p->arena);
   for (void* q : p->owned) fb200_free(p->device, q);
   for (void* q : p->stage_in) fb200_free(p->device, q);
   for (void* q : p->stage_out) fb200_free(p->device, q);
@@ -1516,7 +1576,10 @@ extern "C" int fb200_plan_run(fb200_plan* p, const void* const* inputs, void* co
     if (outputs[i] == nullptr && p->slots[p->output_slots[i]].numel > 0) return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_run: output %zu is null", i);
   }
   FB200_CUDA_OK(cudaSetDevice(p->device));
-  std::lock_guard<std::mutex> lock(p->mu);  // runs share the arena
+  fb200_plan::Workspace* ws = nullptr;
+  if (int rc = acquire_workspace(p, stream, &ws)) return rc;
+  std::lock_guard<std::mutex> lock(ws->run_mu);   // callers that share a workspace take turns
+  struct Scope { Scope(fb200_plan::Workspace* w) { t_ws = w; } ~Scope() { t_ws = nullptr; } } scope(ws);
   auto run_eager = [&]() -> int {
     for (Step& s : p->steps) {
       if (int rc = run_step(p, s, inputs, outputs, stream)) {
@@ -1534,21 +1597,21 @@ extern "C" int fb200_plan_run(fb200_plan* p, const void* const* inputs, void* co
     for (size_t i = 0; i < p->output_slots.size(); ++i) key.push_back(outputs[i]);
     key.push_back(stream);
     fb200_plan::GraphEntry* ge = nullptr;
-    for (auto& e : p->graphs) if (e.key == key) ge = &e;
+    for (auto& e : ws->graphs) if (e.key == key) ge = &e;
     if (ge == nullptr) {
-      if (p->graphs.size() < 4) {
-        p->graphs.emplace_back();
-        ge = &p->graphs.back();
+      if (ws->graphs.size() < 4) {
+        ws->graphs.emplace_back();
+        ge = &ws->graphs.back();
       } else {   // replace the entry used longest ago
-        ge = &p->graphs[0];
-        for (auto& e : p->graphs) if (e.last_used < ge->last_used) ge = &e;
+        ge = &ws->graphs[0];
+        for (auto& e : ws->graphs) if (e.last_used < ge->last_used) ge = &e;
         if (ge->exec) cudaGraphExecDestroy(ge->exec);
         if (ge->graph) cudaGraphDestroy(ge->graph);
         *ge = fb200_plan::GraphEntry();
       }
       ge->key = key;
     }
-    ge->last_used = ++p->graph_clock;
+    ge->last_used = ++ws->graph_clock;
     if (ge->exec != nullptr) {
       FB200_CUDA_OK(cudaGraphLaunch(ge->exec, as_stream(stream)));
       g_launch_count.fetch_add(p->launches, std::memory_order_relaxed);
@@ -1644,7 +1707,10 @@ extern "C" int fb200_plan_profile(fb200_plan* p, const void* const* inputs, void
   *n_steps = n;
   if (cap < n) return set_error(FB200_INVALID_ARGUMENT, "fb200_plan_profile: room for %d steps, plan has %d", cap, n);
   FB200_CUDA_OK(cudaSetDevice(p->device));
-  std::lock_guard<std::mutex> lock(p->mu);
+  fb200_plan::Workspace* ws = nullptr;
+  if (int rc0 = acquire_workspace(p, stream, &ws)) return rc0;
+  std::lock_guard<std::mutex> lock(ws->run_mu);
+  struct Scope { Scope(fb200_plan::Workspace* w) { t_ws = w; } ~Scope() { t_ws = nullptr; } } scope(ws);
   std::vector<cudaEvent_t> ev(static_cast<size_t>(n) + 1);
   for (auto& e : ev) FB200_CUDA_OK(cudaEventCreate(&e));
   int rc = FB200_OK;

@@ -429,8 +429,13 @@ FB200_API int fb200_plan_io_spec(const fb200_plan* plan, int is_output, int inde
 FB200_API size_t fb200_plan_arena_bytes(const fb200_plan* plan);
 /* Number of kernel launches one run enqueues (after epilogue absorption and aliasing). */
 FB200_API int fb200_plan_launches_per_run(const fb200_plan* plan);
-/* Device pointers in, device pointers out; asynchronous on `stream`.  Runs of one plan are
- * serialised by a per-plan mutex because they share its arena. */
+/* Device pointers in, device pointers out; asynchronous on `stream`.  Every stream that runs the
+ * plan gets a workspace of its own (arena at the planner's offsets, private buffers, captured CUDA
+ * graphs), up to four: host threads that run one plan on different streams do not wait for one
+ * another and their launches overlap on the device (the reference allocates an arena inside every
+ * run for the same effect, src/backends/cuda/cuda_executable.cpp:55-61).  Callers that share a stream,
+ * and streams beyond the fourth, take turns.  The host-buffer entry points below share one set of
+ * staging buffers and are for one caller at a time. */
 FB200_API int fb200_plan_run(fb200_plan* plan, const void* const* inputs, void* const* outputs,
                              fb200_stream stream);
 /* Host buffers in and out: H2D of every input, the run, D2H of every output, one stream

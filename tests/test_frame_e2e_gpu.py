@@ -157,3 +157,28 @@ def test_twelve_elementwise_ops_fuse_into_one_group_and_run():
     (got,) = ref_runtime.Compiled(build("cuda"), "cuda").run(ins)
     assert np.array_equal(got.view(np.uint8), exp.view(np.uint8))
     assert ref_runtime.fallback_count("fused_elementwise_internal", "cuda") == 0
+
+
+@pytest.mark.parametrize("kind,args,dtype", [("transformer", (1, 512, 1024, 16, 4096, True), configs.BF16),
+                                             ("mamba", (2, 512, 256, 4, 0, True), configs.F32),
+                                             ("cnn", (8, 16, 56, 64, 10, True), configs.F32)],
+                         ids=["transformer_s512_e1024_h16", "mamba_c256_s512", "cnn_16x56x56_to_64"])
+def test_reference_nn_modules_at_a_non_miniature_size(kind, args, dtype):
+    """nn::TransformerEncoderBlock at sequence 512 / embed 1024 / 16 heads / FFN 4096 (bf16), nn::Mamba
+    with 256 channels over 512 steps and an nn::Sequential CNN on 56 x 56 images, built by the
+    reference's own builder, compiled by its runtime::compile for its CPU backend and for this plugin,
+    same seeded parameters: the two must agree within the dtype's tier (the bf16 block: the chain
+    tolerance of the full-size parity test), with nothing falling back to the eager chain."""
+    text_cpu = ref_runtime.nn_graph_text(kind, *args, dtype_code=dtype, backend="cpu")
+    text_gpu = ref_runtime.nn_graph_text(kind, *args, dtype_code=dtype, backend="cuda")
+    cpu = ref_runtime.Compiled(text_cpu, "cpu")
+    ins = configs.nn_inputs([shape for _, shape in cpu.inputs], dtype)
+    (exp,) = cpu.run(ins)
+    cpu.close()
+    gpu = ref_runtime.Compiled(text_gpu, "cuda")
+    (got,) = gpu.run(ins)
+    gpu.close()
+    tol = configs.parity_tolerance("transformer" if dtype == configs.BF16 else kind, dtype, False, fo.to_accum(exp, dtype))
+    assert fo.all_close(got, exp, dtype, **tol), (kind, fo.max_err(got, exp, dtype), tol)
+    for op in OPS:
+        assert ref_runtime.fallback_count(op, "cuda") == 0, f"op {op} fell back to the eager chain"

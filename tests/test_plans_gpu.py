@@ -187,3 +187,50 @@ def test_tensor_core_matmul_gradient_inside_a_replayed_plan():
             first = got.copy()
         assert np.array_equal(got, first)
     plan.close()
+
+
+def test_two_host_threads_on_two_streams_run_one_plan_concurrently():
+    """One compiled plan, two host threads, each with its own stream, inputs and outputs: every stream
+    gets a workspace of its own (arena + captured graphs), so the runs do not wait for one another
+    and must not disturb one another: each thread gets, run after run, exactly what a lone run
+    gives for its inputs (the reference's Executable::run is re-entrant because it allocates its
+    arena per call, src/backends/cuda/cuda_executable.cpp:55-61)."""
+    import threading
+    lib = capi.load()
+    wl = next(w for w in WORKLOADS if w.name == "transformer_bf16_b2_s128_d128")
+    plan = runtime.CompiledPlan(_plan_text(wl.name), 0)
+    rng = np.random.default_rng(17)
+    variants = []
+    for _ in range(2):
+        ins = [np.ascontiguousarray(a.copy()) for a in wl.inputs]
+        ins[0] = fo.from_accum(rng.standard_normal(ins[0].shape).astype(np.float32), fo.DT_BF16)
+        variants.append(ins)
+    expected = [plan.run_host(ins)[0].copy() for ins in variants]
+    dt, shape = plan.outputs[0]
+    errors = []
+
+    def worker(k):
+        try:
+            stream = capi.c_void_p()
+            capi.check(lib.fb200_stream_create(0, capi.byref(stream)))
+            dev_in = [capi.DeviceBuffer.from_numpy(a) for a in variants[k]]
+            dev_out = capi.DeviceBuffer(expected[k].nbytes)
+            for it in range(40):
+                capi.check(lib.fb200_memset(0, dev_out.ptr, 0, dev_out.nbytes, stream))
+                plan.run_device([b.ptr for b in dev_in], [dev_out.ptr], stream)
+                capi.synchronize(0, stream)
+                got = dev_out.download(capi.NP_STORAGE[dt], shape)
+                if not np.array_equal(got.view(np.uint8), expected[k].view(np.uint8)):
+                    errors.append((k, it))
+                    return
+        except Exception as e:   # surfaced in the main thread
+            errors.append((k, repr(e)))
+
+    threads = [threading.Thread(target=worker, args=(k,)) for k in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert capi.kernel_status(0) == 0
+    assert errors == [], errors
+    plan.close()
