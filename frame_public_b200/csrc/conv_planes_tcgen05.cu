@@ -19,8 +19,8 @@
 // element and k-block, a ring handshake per 64 k) shrinks to KW copies made with 128-bit loads and
 // stores, and one handshake per (tile, channel block).
 //
-// Roles (416 threads): warps 0-7 fetch halo tiles by 4-D TMA (zero fill = padding), build the
-// planes and keep the weights of the current channel block resident (K-major, 128-byte swizzle);
+// Roles (448 threads): warp 13 fetches halo tiles by 4-D TMA (zero fill = padding) and the packed
+// weights of each channel block by one bulk copy (K-major, 128-byte swizzle); warps 0-7 build the planes;
 // warp 8 issues tcgen05.mma kind::tf32 (M = 128, N = Cout padded to 32, K = 8 channels of one tap);
 // warps 9-12 run the epilogue (bias, chain, results through a shared-memory tile and one 4-D TMA
 // store per tile, or direct stores).  With several channel blocks the CTA sweeps all its tiles per
@@ -44,8 +44,9 @@ using namespace sm100;
 
 constexpr int kPlTileM = 128;
 constexpr int kPlProducers = 256;
-constexpr int kPlThreads = 416;   // 8 producer warps, 1 MMA warp, 4 epilogue warps
+constexpr int kPlThreads = 448;   // 8 producer warps, 1 MMA warp, 4 epilogue warps, 1 loader warp
 constexpr int kPlMmaWarp = 8;
+constexpr int kPlLoaderWarp = 13;
 constexpr int kPlMaxAcc = 8;
 constexpr int kPlMaxBufs = 4;     // halo tiles in flight
 constexpr int kPlSets = 2;        // plane sets: one being built while the other is multiplied (a third measured no faster)
@@ -224,21 +225,8 @@ conv2d_planes_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x,
   if (warp < kPlMmaWarp) {
     // ---- producers ---------------------------------------------------------------------------------
     const int tid = threadIdx.x;
-    auto issue_halo = [&](const PlWalk& it, int buf) {
-      int img, oy0;
-      tile_of(it.ti(), &img, &oy0);
-      mbar_arrive_expect_tx(halo_full(buf), static_cast<uint32_t>(g.cb * g.ih_t * g.iwp * 4));
-      tma_load_4d(base + halo_off + static_cast<uint32_t>(buf * g.halo_bytes), &tmap_x, halo_full(buf),
-                  g.x0a, oy0 - g.ph, it.cb * g.cb, img);
-    };
-    int passes = 0;
     bool ok = true;
     const int nb = g.n_halo;
-    PlWalk ahead;   // the item whose halo tile is fetched next (thread 0 only)
-    ahead.start(my_tiles, apr, g.n_cb);
-    if (tid == 0) {
-      for (int i = 0; i < nb - 1 && !ahead.done(); ++i) { issue_halo(ahead, i); ahead.next(); }
-    }
     const int G = g.ow / 4;                      // 4-pixel groups per row
     const int pairs = g.ih_t * G;                // (halo row, group) pairs of one channel
     const int units = g.cb * pairs;              // (channel, halo row, group) triples per item
@@ -260,30 +248,6 @@ conv2d_planes_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x,
     uint32_t halo_phase = 0, set_phase = 0;   // parities of the current use of `buf` / `set`
     for (; !it.done() && ok; it.next()) {
       const int idx = it.idx;
-      if (tid == 0 && !ahead.done()) {
-        // the buffer of item idx + nb - 1 was last used by item idx - 1: every producer must have left it
-        const int nbuf = buf == 0 ? nb - 1 : buf - 1;          // (idx + nb - 1) % nb
-        const uint32_t prev_phase = buf == 0 ? halo_phase ^ 1u : halo_phase;   // parity of ((idx - 1) / nb)
-        if (idx >= 1 && !mbar_wait(halo_empty(nbuf), prev_phase, status, kFaultPlReuse)) {
-          ok = false;
-        } else {
-          issue_halo(ahead, nbuf);
-          ahead.next();
-        }
-      }
-      if (tid == 0 && it.first_of_pass() && (g.n_cb > 1 || idx == 0)) {
-        // the weight block of this channel block: one bulk copy of its packed image, as soon as the
-        // MMAs of the previous pass have finished reading the block it replaces
-        if (passes >= 1 && !mbar_wait(w_free, (passes - 1) & 1, status, kFaultPlWeights)) {
-          ok = false;
-        } else {
-          mbar_arrive_expect_tx(w_full, static_cast<uint32_t>(g.w_bytes));
-          bulk_load_1d(base + w_off, w_packed + static_cast<size_t>(it.cb) * (g.w_bytes / 4), static_cast<uint32_t>(g.w_bytes), w_full);
-        }
-        ++passes;
-      }
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
       // the plane set of this item was last read by the MMAs of item idx - kPlSets
       if (idx >= kPlSets && !mbar_wait(set_empty(set), set_phase ^ 1u, status, kFaultPlSetBusy)) { ok = false; break; }
       if (!mbar_wait(halo_full(buf), halo_phase, status, kFaultPlLoad)) { ok = false; break; }
@@ -350,6 +314,40 @@ conv2d_planes_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x,
       }
       if (++buf == nb) { buf = 0; halo_phase ^= 1u; }
       if (++set == kPlSets) { set = 0; set_phase ^= 1u; }
+    }
+  } else if (warp == kPlLoaderWarp) {
+    // ---- loader: lane 0 keeps the halo buffers full, lane 1 brings each pass's weight block -----------
+    // Both run ahead of the producers by themselves: the 4-D copy of a halo tile and the wait for a
+    // free buffer used to sit in the producers' path between two handshakes.
+    if (lane == 0) {
+      PlWalk a;
+      a.start(my_tiles, apr, g.n_cb);
+      const int nb = g.n_halo;
+      int buf = 0;
+      uint32_t phase = 0;
+      for (; !a.done(); a.next()) {
+        // the n-th use of a buffer waits for its use n - 1 to be released by every producer warp
+        if (a.idx >= nb && !mbar_wait(halo_empty(buf), phase ^ 1u, status, kFaultPlReuse)) break;
+        int img, oy0;
+        tile_of(a.ti(), &img, &oy0);
+        mbar_arrive_expect_tx(halo_full(buf), static_cast<uint32_t>(g.cb * g.ih_t * g.iwp * 4));
+        tma_load_4d(base + halo_off + static_cast<uint32_t>(buf * g.halo_bytes), &tmap_x, halo_full(buf),
+                    g.x0a, oy0 - g.ph, a.cb * g.cb, img);
+        if (++buf == nb) { buf = 0; phase ^= 1u; }
+      }
+    } else if (lane == 1) {
+      PlWalk b;
+      b.start(my_tiles, apr, g.n_cb);
+      int passes = 0;
+      for (; !b.done(); b.next()) {
+        if (!(b.first_of_pass() && (g.n_cb > 1 || b.idx == 0))) continue;
+        // one bulk copy of the block's packed image, as soon as the MMAs of the previous pass have
+        // finished reading the block it replaces
+        if (passes >= 1 && !mbar_wait(w_free, static_cast<uint32_t>(passes - 1) & 1u, status, kFaultPlWeights)) break;
+        mbar_arrive_expect_tx(w_full, static_cast<uint32_t>(g.w_bytes));
+        bulk_load_1d(base + w_off, w_packed + static_cast<size_t>(b.cb) * (g.w_bytes / 4), static_cast<uint32_t>(g.w_bytes), w_full);
+        ++passes;
+      }
     }
   } else if (warp == kPlMmaWarp) {
     // The whole warp runs this loop and one elected lane issues (warp-uniform code keeps the
