@@ -91,6 +91,7 @@ SIGNATURES = {
     "fb200_ipc_import": (c_int, [c_int, _P, _PP]),
     "fb200_ipc_close": (c_int, [c_int, _P]),
     "fb200_matmul_uses_tensor_cores": (c_int, [c_int64, c_int64, c_int64, c_int, c_int]),
+    "fb200_matmul_schedule": (c_int, [c_int64, c_int64, c_int64, c_int, c_int, c_int, _I64P]),
     "fb200_conv2d": (c_int, [_P, _P, _P, _P, POINTER(Conv2dParams), c_int, c_int,
                              POINTER(Epilogue), _P]),
     "fb200_conv1d": (c_int, [_P, _P, _P, _P] + [c_int64] * 8 + [c_int, _P]),
@@ -262,6 +263,14 @@ def matmul(a, b, c, m, n, k, dtype, allow_tf32=False, epilogue=None, stream=None
 def matmul_split(a, b, c, c_tail, tail_col, m, n, k, dtype, allow_tf32=False, epilogue=None, stream=None):
     ep = byref(epilogue) if epilogue is not None else None
     check(load().fb200_matmul_split(a, b, c, c_tail, tail_col, m, n, k, dtype, 1 if allow_tf32 else 0, ep, stream))
+
+
+def matmul_schedule(m, n, k, dtype, light_epilogue=False, compensated=False):
+    """Tile shape and last-wave split fb200_matmul uses for a tensor-core product (host logic only)."""
+    out = (c_int64 * 6)()
+    check(load().fb200_matmul_schedule(m, n, k, dtype, 1 if light_epilogue else 0, 1 if compensated else 0, out))
+    keys = ("tile_n", "tile_m", "dp_tiles", "sk_units", "sk_ctas", "k_blocks")
+    return dict(zip(keys, (int(v) for v in out)))
 
 
 def conv2d(x, w, bias, out, params: Conv2dParams, dtype, allow_tf32=False, epilogue=None,

@@ -95,7 +95,100 @@ enum GemmFault : int {
   kFaultMmaFull = 102,
   kFaultMmaTmemEmpty = 103,
   kFaultEpilogueTmemFull = 104,
+  kFaultSplitPartial = 105,
 };
+
+// Work of one launch.  The first `dp_tiles` tiles of the tile order are walked whole (tile = CTA,
+// CTA + grid, ...).  The k-blocks of the remaining tiles, `sk_units` in all, are dealt out to the
+// first `sk_ctas` CTAs in contiguous ranges of equal length, so that a last wave which would occupy a
+// fraction of the SMs for a whole tile's time is spread over all of them ("stream-K").  A range cuts
+// tiles into segments [kb0, kb1).  The CTA that holds a tile's FIRST k-blocks owns it: it keeps its
+// segment in TMEM, adds the partial accumulators of the CTAs that follow (each CTA writes at most one:
+// only its first segment can start inside a tile) and runs the epilogue.  A partial tile is the raw
+// fp32 accumulator in `ws`, in the order the TMEM loads hand it out; flags[cta * 8 + epilogue warp]
+// says that the warp's share is written.  Ranges are handed out against the order in which the CTAs
+// START (a ticket taken at entry): an owner only ever waits for CTAs that started before it, each
+// working on its FIRST segment, which never waits itself.  So a waiting CTA never depends on one
+// that is not yet resident, whatever else shares the GPU, and the waits cannot form a cycle; every
+// wait is bounded all the same.  sk_units == 0: no split.
+struct GemmSplit {
+  int64_t dp_tiles;
+  int64_t sk_units;
+  int sk_ctas;
+  float* ws;     // [sk_ctas][BLOCK_N / 32][8][128] float4
+  int* flags;    // [range][8], zero before the launch; every owner clears what it has consumed
+  int* tickets;  // {CTAs started, CTAs finished}: zero before the launch, reset by the last CTA
+};
+
+struct GemmSegment {
+  int64_t tile, kb0, kb1;
+};
+
+__device__ __forceinline__ int64_t split_range_begin(const GemmSplit& sp, int cta) {
+  return sp.sk_units * cta / sp.sk_ctas;
+}
+
+// The segments of this CTA, in order; every role of the CTA walks the same list.  `rank` is the
+// CTA's place in the order in which the grid's CTAs started (blockIdx.x when nothing is split):
+// whole tiles go by rank, and rank r takes range sk_ctas - 1 - r, so that the ranges AFTER a CTA's
+// own, the ones its epilogue may wait for, belong to CTAs that started before it.
+template <bool SPLIT>
+struct SegmentWalk {
+  int64_t dp_next, dp_tiles, k_blocks, u, u1;
+  __device__ SegmentWalk(const GemmSplit& sp, int64_t k_blocks_, int rank) {
+    dp_next = rank;
+    dp_tiles = sp.dp_tiles;
+    k_blocks = k_blocks_;
+    u = u1 = 0;
+    if (SPLIT && sp.sk_units > 0 && rank < sp.sk_ctas) {
+      const int range = sp.sk_ctas - 1 - rank;
+      u = split_range_begin(sp, range);
+      u1 = split_range_begin(sp, range + 1);
+    }
+  }
+  __device__ __forceinline__ bool next(GemmSegment* sg) {
+    if (dp_next < dp_tiles) {
+      sg->tile = dp_next;
+      sg->kb0 = 0;
+      sg->kb1 = k_blocks;
+      dp_next += gridDim.x;
+      return true;
+    }
+    if (SPLIT && u < u1) {
+      const int64_t t = u / k_blocks;
+      sg->tile = dp_tiles + t;
+      sg->kb0 = u - t * k_blocks;
+      const int64_t left = u1 - u, room = k_blocks - sg->kb0;
+      const int64_t len = left < room ? left : room;
+      sg->kb1 = sg->kb0 + len;
+      u += len;
+      return true;
+    }
+    return false;
+  }
+};
+
+// Bounded wait for a flag another CTA of this launch sets (lane 0 polls, the warp gets the result).
+__device__ __forceinline__ bool split_flag_wait(const int* flag, int* status) {
+  int ok = 1;
+  if ((threadIdx.x & 31u) == 0u) {
+    const unsigned long long t0 = globaltimer_ns();
+    for (uint32_t i = 1;; ++i) {
+      int v;
+      asm volatile("ld.acquire.gpu.global.b32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+      if (v != 0) break;
+      if ((i & 255u) == 0u) {
+        if (*reinterpret_cast<volatile int*>(status) != 0) { ok = 0; break; }
+        if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+          *reinterpret_cast<volatile int*>(status) = kFaultSplitPartial;
+          ok = 0;
+          break;
+        }
+      }
+    }
+  }
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
 
 template <int ELT, int BLOCK_N, int MH = 1, int KB = 128>
 struct GemmCfg {
@@ -310,15 +403,16 @@ __device__ __forceinline__ void transpose_chunk(const uint32_t (&r)[32], float (
   __syncwarp();   // every lane has read its pieces before the next chunk overwrites the buffer
 }
 
-template <typename T, int ELT, int BLOCK_N, int MH, int KB, int EPI>
+template <typename T, int ELT, int BLOCK_N, int MH, int KB, int EPI, bool SPLIT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_a_lo,
                     const __grid_constant__ CUtensorMap tmap_b_lo, int parts, int b_spans_map, GemmDest dest, int64_t M,
-                    int64_t N, int64_t K, uint32_t idesc, EpilogueDev epi, int* status) {
+                    int64_t N, int64_t K, uint32_t idesc, EpilogueDev epi, GemmSplit split, int* status) {
   using Cfg = GemmCfg<ELT, BLOCK_N, MH, KB>;
   static_assert(MH == 1 || (MH == 2 && BLOCK_N == 256), "two M halves fill TMEM with one 256 x 256 tile");
+  static_assert(!SPLIT || MH == 1, "split ranges keep one accumulator per segment");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
@@ -337,7 +431,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int lane = threadIdx.x & 31;
   const int64_t tiles_m = (M + Cfg::kTileM - 1) / Cfg::kTileM;
   const int64_t tiles_n = (N + BLOCK_N - 1) / BLOCK_N;
-  const int64_t n_tiles = tiles_m * tiles_n;
   const int group_m = dest.group_m / MH > 0 ? dest.group_m / MH : 1;
   // parts == 3: the contraction runs three times over K into the same accumulator, with the operand
   // pairs (A_lo, B), (A, B_lo), (A, B): fp32 operands split as x = trunc_tf32(x) + x_lo, the tensor
@@ -368,10 +461,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     tmem_alloc(tmem_slot, Cfg::kTmemCols);
     tmem_relinquish();
   }
+  volatile int* rank_slot_ptr = reinterpret_cast<volatile int*>(
+      base_ptr + Cfg::kStages * Cfg::kStageBytes + 8 * (2 * Cfg::kStages + 5));
+  if (threadIdx.x == 32 * 2) {
+    *rank_slot_ptr = SPLIT ? atomicAdd(split.tickets, 1) : static_cast<int>(blockIdx.x);
+  }
   tcgen05_fence_before_sync();
   __syncthreads();
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  const int rank = SPLIT ? *rank_slot_ptr : static_cast<int>(blockIdx.x);
+  const int my_range = split.sk_ctas - 1 - rank;   // meaningful when rank < sk_ctas
 
   if (warp == 0 || warp == kGemmBProducerWarp) {
     // Producers: warp 0 loads the A tiles, warp 10 the B tiles, each with its own expect_tx arrival
@@ -383,12 +483,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+    SegmentWalk<SPLIT> walk(split, k_blocks, rank);
+    GemmSegment sg;
+    while (ok && walk.next(&sg)) {
       int64_t tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, group_m, &tm, &tn);
+      tile_coords(sg.tile, tiles_m, tiles_n, group_m, &tm, &tn);
       const int32_t a_row = static_cast<int32_t>(tm * Cfg::kTileM);
       const int32_t b_col = static_cast<int32_t>(tn * BLOCK_N);
-      for (int64_t kb = 0; kb < k_blocks; ++kb) {
+      for (int64_t kb = SPLIT ? sg.kb0 : 0; kb < (SPLIT ? sg.kb1 : k_blocks); ++kb) {
         ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(stage), phase ^ 1u, status, kFaultProducerEmpty));
         if (!ok) break;
         const uint32_t a_dst = base + stage * Cfg::kStageBytes;
@@ -429,7 +531,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint64_t a_desc0 = make_smem_desc(base, 16, 8 * KB, KB == 64 ? kLayoutSw64 : kLayoutSw128);
     const uint64_t b_desc0 = ELT == 2 ? make_smem_desc(base + Cfg::kAStageBytes, Cfg::kBChunkBytes, 1024, kLayoutSw128)
                                       : make_smem_desc(base + Cfg::kAStageBytes, Cfg::kBChunkBytes, 512, kLayoutSw128Base32);
-    for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+    SegmentWalk<SPLIT> walk(split, k_blocks, rank);
+    GemmSegment sg;
+    while (ok && walk.next(&sg)) {
       // MH = 1: the tile's accumulator alternates between the two TMEM halves; MH = 2: the tile
       // uses both (rows 0-127 and 128-255), so nothing of the next tile overlaps this epilogue.
       ok = __all_sync(0xffffffffu, mbar_wait(tmem_empty_bar(MH == 2 ? 0 : acc), acc_phase ^ 1u, status, kFaultMmaTmemEmpty));
@@ -437,7 +541,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (!ok) break;
       tcgen05_fence_after_sync();
       const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(MH == 2 ? 0 : acc * BLOCK_N);
-      for (int64_t kb = 0; kb < k_blocks; ++kb) {
+      for (int64_t kb = SPLIT ? sg.kb0 : 0; kb < (SPLIT ? sg.kb1 : k_blocks); ++kb) {
         ok = __all_sync(0xffffffffu, mbar_wait(full_bar(stage), phase, status, kFaultMmaFull));
         if (!ok) break;
         tcgen05_fence_after_sync();
@@ -450,7 +554,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
         for (int ks = 0; ks < Cfg::kStepsPerBlock; ++ks) {
           const uint64_t b_desc = b_desc0 + (stage_units + static_cast<uint32_t>(ks * Cfg::kBKStepBytes) / 16u);
-          const uint32_t accumulate = (kb > 0 || ks > 0) ? 1u : 0u;
+          const uint32_t accumulate = (kb > (SPLIT ? sg.kb0 : 0) || ks > 0) ? 1u : 0u;
 #pragma unroll
           for (int h = 0; h < MH; ++h) {
             const uint64_t a_desc = a_desc0 + (stage_units + static_cast<uint32_t>(h * kBlockM * KB + ks * Cfg::kUmmaKBytes) / 16u);
@@ -492,11 +596,32 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t stage_buf = bars + 512u + static_cast<uint32_t>((warp - 2) * Cfg::kEpiStageBytes);
     const int pf_step = prefetch_step<EPI>(epi);
     bool ok = true;
-    for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+    SegmentWalk<SPLIT> walk(split, k_blocks, rank);
+    GemmSegment sg;
+    while (ok && walk.next(&sg)) {
       int64_t tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, group_m, &tm, &tn);
+      tile_coords(sg.tile, tiles_m, tiles_n, group_m, &tm, &tn);
+      // A segment that starts inside a tile leaves as a partial accumulator; the segment with the
+      // tile's first k-blocks collects the partials of the CTAs after this one (MH = 1 only).
+      const bool partial_out = SPLIT && sg.kb0 > 0;
+      int n_peers = 0;
+      if (SPLIT && sg.kb0 == 0 && sg.kb1 < k_blocks) {
+        int64_t missing = k_blocks - sg.kb1;
+        for (int peer = my_range + 1; missing > 0 && peer < split.sk_ctas; ++peer) {
+          const int64_t len = split_range_begin(split, peer + 1) - split_range_begin(split, peer);
+          missing -= len < missing ? len : missing;
+          ++n_peers;
+        }
+      }
       if (!mbar_wait(tmem_full_bar(acc), acc_phase, status, kFaultEpilogueTmemFull)) { ok = false; break; }
       tcgen05_fence_after_sync();
+      for (int p = 1; p <= n_peers && ok; ++p) {
+        ok = split_flag_wait(split.flags + (my_range + p) * 8 + (warp - 2), status);
+      }
+      if (!ok) break;
+      // partial tiles: float4 index ((chunk * 8 + q) * 128 + row of the tile), q = 4 columns
+      float4* const my_partial = reinterpret_cast<float4*>(split.ws) +
+                                 static_cast<int64_t>(my_range > 0 ? my_range : 0) * (BLOCK_N * 32) + quarter * 32 + lane;
       View g;
       g.row0 = tm * Cfg::kTileM + (MH == 2 ? half * kBlockM : 0) + quarter * 32;
       g.sub_row = lane / View::LPR;
@@ -515,7 +640,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // transposition; the next chunk's lines are pulled into L2 meanwhile.
         Vec16<T> pre[View::P];
         int pre_step = -1;
-        if (pf_step >= 0 && g.vec && g.row0 < M && (reinterpret_cast<uintptr_t>(epi.operands[pf_step]) & 15u) == 0) {
+        if (!partial_out && pf_step >= 0 && g.vec && g.row0 < M && (reinterpret_cast<uintptr_t>(epi.operands[pf_step]) & 15u) == 0) {
           pre_step = pf_step;
           const T* opnd = static_cast<const T*>(epi.operands[pf_step]);
 #pragma unroll
@@ -530,6 +655,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(c * 32), r);
         tmem_ld_wait();
         if (g.row0 >= M) continue;  // warp-uniform: the whole 32-row band lies below the matrix
+        if constexpr (SPLIT) {
+          if (partial_out) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              __stcg(my_partial + (c * 8 + q) * 128,
+                     make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                 __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3])));
+            }
+            continue;
+          }
+          for (int p = 1; p <= n_peers; ++p) {   // fixed order: the result does not depend on timing
+            const float4* src = my_partial + static_cast<int64_t>(p) * (BLOCK_N * 32) + c * 8 * 128;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const float4 t = __ldcg(src + q * 128);
+              r[4 * q] = __float_as_uint(__uint_as_float(r[4 * q]) + t.x);
+              r[4 * q + 1] = __float_as_uint(__uint_as_float(r[4 * q + 1]) + t.y);
+              r[4 * q + 2] = __float_as_uint(__uint_as_float(r[4 * q + 2]) + t.z);
+              r[4 * q + 3] = __float_as_uint(__uint_as_float(r[4 * q + 3]) + t.w);
+            }
+          }
+        }
         float v[32];
         transpose_chunk<T>(r, v, stage_buf, lane);
         apply_chain<T, EPI>(epi, v, g, pre, pre_step);
@@ -557,6 +704,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
       }
+      if (SPLIT && n_peers > 0 && lane == 0) {
+        // consumed: the flags are zero again when the launch ends
+        for (int p = 1; p <= n_peers; ++p) split.flags[(my_range + p) * 8 + (warp - 2)] = 0;
+      }
+      if (SPLIT && partial_out) {
+        __threadfence();   // every lane's share of the partial tile is visible before the flag
+        __syncwarp();
+        if (lane == 0) {
+          int* flag = split.flags + my_range * 8 + (warp - 2);
+          asm volatile("st.release.gpu.global.b32 [%0], %1;" ::"l"(flag), "r"(1) : "memory");
+        }
+      }
       tcgen05_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
@@ -575,6 +734,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if (warp == 1) {
     __syncwarp();
     tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+  if (SPLIT && threadIdx.x == 0) {
+    // the last CTA to leave puts the tickets back to zero for the next launch on this stream
+    if (atomicAdd(split.tickets + 1, 1) == static_cast<int>(gridDim.x) - 1) {
+      split.tickets[0] = 0;
+      split.tickets[1] = 0;
+    }
   }
 }
 
@@ -724,6 +890,86 @@ int device_status_word(int** dev_ptr) {
   return FB200_OK;
 }
 
+// Scratch of a split launch: 8 flags per CTA, then one fp32 partial tile of 128 x 256 per CTA.  Kept
+// per (device, stream): launches on one stream run one after the other, so they can share it, and
+// the owners clear every flag they have consumed, so it is all zeros between launches (after a
+// launch that gave up, the status word is set and the flags are cleared here).  More than eight
+// streams at a time: stream-ordered scratch, cleared per launch.
+constexpr size_t kSplitFlagBytes = 8192;   // 148 * 8 flags, then (at kSplitTicketOffset) two tickets
+constexpr size_t kSplitTicketOffset = 6144;
+constexpr size_t kSplitBytes = kSplitFlagBytes + size_t(kNumSMs) * 256 * kBlockM * sizeof(float);
+struct SplitWorkspace { int device = -1; cudaStream_t stream = nullptr; uint8_t* ptr = nullptr; uint64_t clean_at = 0; };
+static SplitWorkspace g_split_ws[8];
+static std::mutex g_split_mu;
+static uint64_t g_fault_epoch = 0;   // counts the times a kernel was seen to have given up (under g_split_mu)
+
+static int split_workspace(cudaStream_t s, uint8_t** out, bool* pooled) {
+  int device = 0;
+  FB200_CUDA_OK(cudaGetDevice(&device));
+  *pooled = false;
+  {
+    std::lock_guard<std::mutex> lock(g_split_mu);
+    SplitWorkspace* slot = nullptr;
+    for (auto& w : g_split_ws) {
+      if (w.ptr != nullptr && w.device == device && w.stream == s) { slot = &w; break; }
+    }
+    if (slot == nullptr) {
+      for (auto& w : g_split_ws) if (w.ptr == nullptr) { slot = &w; break; }
+      if (slot != nullptr) {
+        uint8_t* p = nullptr;
+        FB200_CUDA_OK(cudaMalloc(reinterpret_cast<void**>(&p), kSplitBytes));
+        FB200_CUDA_OK(cudaMemset(p, 0, kSplitFlagBytes));
+        slot->device = device;
+        slot->stream = s;
+        slot->ptr = p;
+        slot->clean_at = g_fault_epoch;
+      }
+    }
+    if (slot != nullptr) {
+      const StatusWord& sw = g_status[device < 16 ? device : 0];
+      if (sw.host != nullptr && *reinterpret_cast<volatile int*>(sw.host) != 0) ++g_fault_epoch;
+      if (slot->clean_at != g_fault_epoch) {
+        // a kernel gave up since this workspace was last known clean: flags or tickets may be left set
+        FB200_CUDA_OK(cudaMemsetAsync(slot->ptr, 0, kSplitFlagBytes, s));
+        slot->clean_at = g_fault_epoch;
+      }
+      *out = slot->ptr;
+      return FB200_OK;
+    }
+  }
+  uint8_t* p = nullptr;
+  FB200_CUDA_OK(scratch_alloc_async(reinterpret_cast<void**>(&p), kSplitBytes, s));
+  FB200_CUDA_OK(cudaMemsetAsync(p, 0, kSplitFlagBytes, s));
+  *pooled = true;
+  *out = p;
+  return FB200_OK;
+}
+
+// Decides whether the tiles' k-blocks are split over more CTAs than there are tiles.  Measured on
+// B200 (back-to-back launches, CUDA events): with more than about a quarter of the SMs busy the
+// mainloop is bound by what the L2 can deliver to all SMs together, not by any one SM, so spreading a
+// partial last wave over the idle SMs moves the same bytes in the same time and only adds the
+// partial tiles' round trip (4096 x 1024 x 4096 bf16: 39.6 us as 128 whole tiles on 128 SMs, 47.7 us
+// split over 148; 2048 x 8192 x 8192: 212 -> 196 us, but 185 us on 256 x 256 tiles).  It pays when a
+// few tiles carry a long K (a quarter of the SMs or fewer, 64 k-blocks or more): the weight-gradient
+// shape, out[in, out] summed over all tokens.  Ranges are at least an eighth of a tile's k-blocks, so
+// an owner adds at most eight partial tiles.
+constexpr int64_t kSplitMaxTiles = kNumSMs / 4;
+constexpr int64_t kSplitMinKBlocks = 64;
+static GemmSplit plan_split(int64_t tiles, int64_t k_blocks, int mh) {
+  GemmSplit sp{};
+  sp.dp_tiles = tiles;
+  if (mh != 1 || tiles > kSplitMaxTiles || k_blocks < kSplitMinKBlocks) return sp;
+  const int64_t units = tiles * k_blocks;
+  const int64_t min_range = k_blocks / 8 > 8 ? k_blocks / 8 : 8;
+  const int64_t ctas = units / min_range < kNumSMs ? units / min_range : kNumSMs;
+  if (ctas < 2 * tiles) return sp;
+  sp.dp_tiles = 0;
+  sp.sk_units = units;
+  sp.sk_ctas = static_cast<int>(ctas);
+  return sp;
+}
+
 template <typename T, int ELT, int BLOCK_N, int MH, int KB, int EPI>
 static int launch_tc_epi(const void* a, const void* b, const GemmDest& c, int64_t m, int64_t n, int64_t k,
                          int dtype, const EpilogueDev& epi, cudaStream_t s) {
@@ -752,13 +998,40 @@ static int launch_tc_epi(const void* a, const void* b, const GemmDest& c, int64_
   if (int rc = device_status_word(&status)) return rc;
   const uint32_t fmt = dtype == FB200_F32 ? kFmtTF32 : (dtype == FB200_BF16 ? kFmtBF16 : kFmtF16);
   const uint32_t idesc = make_instr_desc(fmt, /*a MN-major*/ 0, /*b MN-major*/ 1, kBlockM, BLOCK_N);
-  auto kernel = gemm_tcgen05_kernel<T, ELT, BLOCK_N, MH, KB, EPI>;
+  const int64_t tiles = ((m + Cfg::kTileM - 1) / Cfg::kTileM) * ((n + BLOCK_N - 1) / BLOCK_N);
+  const int64_t k_blocks = ((k + Cfg::kBlockK - 1) / Cfg::kBlockK) * parts;
+  GemmSplit split{};
+  split.dp_tiles = tiles;
+  // The split form exists for 128 x 256 tiles with a plain store or the interpreted chain.
+  constexpr bool kCanSplit = MH == 1 && BLOCK_N == 256 && (EPI == kEpiNone || EPI == kEpiGeneric);
+  if constexpr (kCanSplit) {
+    const GemmSplit planned = plan_split(tiles, k_blocks, MH);
+    if (planned.sk_units > 0) {
+      // One partial-tile slot and eight flags per range, from this stream's persistent workspace (or
+      // stream-ordered scratch when the table is full); one CTA per SM.
+      split = planned;
+      auto kernel = gemm_tcgen05_kernel<T, ELT, BLOCK_N, MH, KB, EPI, true>;
+      FB200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(Cfg::kSmemBytes)));
+      uint8_t* scratch = nullptr;
+      bool pooled = false;
+      if (int rc = split_workspace(s, &scratch, &pooled)) return rc;
+      split.flags = reinterpret_cast<int*>(scratch);
+      split.ws = reinterpret_cast<float*>(scratch + kSplitFlagBytes);
+      split.tickets = reinterpret_cast<int*>(scratch + kSplitTicketOffset);
+      kernel<<<kNumSMs, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, ta_lo, tb_lo, parts, b_spans_map, c, m, n, k,
+                                                             idesc, epi, split, status);
+      const int rc = after_launch("gemm_tcgen05_kernel");
+      if (pooled) cudaFreeAsync(scratch, s);
+      return rc;
+    }
+  }
+  auto kernel = gemm_tcgen05_kernel<T, ELT, BLOCK_N, MH, KB, EPI, false>;
   FB200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(Cfg::kSmemBytes)));
-  const int64_t tiles = ((m + Cfg::kTileM - 1) / Cfg::kTileM) * ((n + BLOCK_N - 1) / BLOCK_N);
   const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
   kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, ta_lo, tb_lo, parts, b_spans_map, c, m, n, k, idesc,
-                                                      epi, status);
+                                                      epi, split, status);
   return after_launch("gemm_tcgen05_kernel");
 }
 
@@ -769,8 +1042,14 @@ static int launch_tc(const void* a, const void* b, const GemmDest& c, int64_t m,
                      int dtype, const EpilogueDev& epi, cudaStream_t s) {
   const int kind = classify_epilogue(epi);
   if (kind == kEpiNone) return launch_tc_epi<T, ELT, BLOCK_N, MH, KB, kEpiNone>(a, b, c, m, n, k, dtype, epi, s);
+  bool split_planned = false;
+  if constexpr (MH == 1 && BLOCK_N == 256) {
+    const int parts = (c.a_lo != nullptr && c.b_lo != nullptr) ? 3 : 1;
+    const int64_t tiles = ((m + kBlockM - 1) / kBlockM) * ((n + BLOCK_N - 1) / BLOCK_N);
+    split_planned = plan_split(tiles, ((k * ELT + KB - 1) / KB) * parts, MH).sk_units > 0;
+  }
   if constexpr (MH == 1 && !std::is_same<T, __half>::value) {
-    switch (kind) {
+    if (!split_planned) switch (kind) {
       case kEpiAddFullGelu: return launch_tc_epi<T, ELT, BLOCK_N, MH, KB, kEpiAddFullGelu>(a, b, c, m, n, k, dtype, epi, s);
       case kEpiAddColSoftplus: return launch_tc_epi<T, ELT, BLOCK_N, MH, KB, kEpiAddColSoftplus>(a, b, c, m, n, k, dtype, epi, s);
       case kEpiGelu: return launch_tc_epi<T, ELT, BLOCK_N, MH, KB, kEpiGelu>(a, b, c, m, n, k, dtype, epi, s);
@@ -781,9 +1060,9 @@ static int launch_tc(const void* a, const void* b, const GemmDest& c, int64_t m,
   return launch_tc_epi<T, ELT, BLOCK_N, MH, KB, kEpiGeneric>(a, b, c, m, n, k, dtype, epi, s);
 }
 
-template <typename T, int ELT>
-static int launch_tc_n(const void* a, const void* b, const GemmDest& c, int64_t m, int64_t n, int64_t k,
-                       int dtype, const EpilogueDev& epi, cudaStream_t s) {
+// Tile shape for a product: BLOCK_N in {64, 128, 256} and MH (1: 128-row tiles, 2: 256 x 256).
+struct TileChoice { int block_n, mh; };
+static TileChoice choose_tile(int64_t m, int64_t n, int64_t k, int elt, int parts, bool light) {
   const int64_t tiles_m = (m + kBlockM - 1) / kBlockM;
   auto tiles = [&](int bn) { return tiles_m * ((n + bn - 1) / bn); };
   if (n > 128 && tiles(256) >= kNumSMs) {
@@ -797,14 +1076,27 @@ static int launch_tc_n(const void* a, const void* b, const GemmDest& c, int64_t 
     const int64_t waves1 = (tiles(256) + kNumSMs - 1) / kNumSMs, waves2 = (t2 + kNumSMs - 1) / kNumSMs;
     // The exposed epilogue costs about 8-10 K cycles per tile against a gain of 6-11 % of the mainloop:
     // only worth it from 128 k-blocks per tile on (measured slower at K = 768 and 1536 TF32).
-    if (light_epilogue(epi) && m > 128 && k * ELT >= 128 * 128 && t2 >= kNumSMs &&
-        16 * waves2 <= 9 * waves1) {
-      return launch_tc<T, ELT, 256, 2>(a, b, c, m, n, k, dtype, epi, s);
-    }
-    return launch_tc<T, ELT, 256>(a, b, c, m, n, k, dtype, epi, s);
+    if (light && m > 128 && k * elt >= 128 * 128 && t2 >= kNumSMs && 16 * waves2 <= 9 * waves1) return {256, 2};
+    return {256, 1};
   }
-  if (n > 64 && tiles(128) >= kNumSMs) return launch_tc<T, ELT, 128>(a, b, c, m, n, k, dtype, epi, s);
-  if (n > 128 && tiles(64) < kNumSMs / 2) return launch_tc<T, ELT, 128>(a, b, c, m, n, k, dtype, epi, s);
+  // One wave of 128 x 256 tiles beats two waves of 128 x 128 (4096 x 1024 x 4096 bf16: 39.6 against
+  // 58.0 us; 4096 x 1024 x 1024: 16.9 against 21.0 us): wide tiles move a third less operand data per
+  // FLOP through the L2.  A few tiles with a long K are split over the SMs (plan_split).
+  const int64_t k_blocks = ((k * elt + 127) / 128) * parts;
+  if (n > 128 && (tiles(128) > kNumSMs || plan_split(tiles(256), k_blocks, 1).sk_units > 0)) return {256, 1};
+  if (n > 64 && tiles(128) >= kNumSMs) return {128, 1};
+  if (n > 128 && tiles(64) < kNumSMs / 2) return {128, 1};
+  return {64, 1};
+}
+
+template <typename T, int ELT>
+static int launch_tc_n(const void* a, const void* b, const GemmDest& c, int64_t m, int64_t n, int64_t k,
+                       int dtype, const EpilogueDev& epi, cudaStream_t s) {
+  const int parts = (c.a_lo != nullptr && c.b_lo != nullptr) ? 3 : 1;
+  const TileChoice t = choose_tile(m, n, k, ELT, parts, light_epilogue(epi));
+  if (t.mh == 2) return launch_tc<T, ELT, 256, 2>(a, b, c, m, n, k, dtype, epi, s);
+  if (t.block_n == 256) return launch_tc<T, ELT, 256>(a, b, c, m, n, k, dtype, epi, s);
+  if (t.block_n == 128) return launch_tc<T, ELT, 128>(a, b, c, m, n, k, dtype, epi, s);
   return launch_tc<T, ELT, 64>(a, b, c, m, n, k, dtype, epi, s);
 }
 
@@ -850,6 +1142,30 @@ using namespace fb200;
 extern "C" int fb200_matmul_uses_tensor_cores(int64_t m, int64_t n, int64_t k, int dtype,
                                               int allow_tf32) {
   return tensor_core_eligible(nullptr, nullptr, nullptr, m, n, k, dtype, allow_tf32) ? 1 : 0;
+}
+
+// How fb200_matmul would run a tensor-core product: out = {BLOCK_N, tile rows, tiles walked whole,
+// k-blocks dealt out in ranges, CTAs that take a range, k-blocks per tile}.  `light_epilogue`: the
+// chain is adds, multiplies and ReLU only.  `compensated`: the three-pass strict fp32 form.
+extern "C" int fb200_matmul_schedule(int64_t m, int64_t n, int64_t k, int dtype, int light_epilogue_chain,
+                                     int compensated, int64_t* out6) {
+  if (out6 == nullptr || m < 1 || n < 1 || k < 1) return set_error(FB200_INVALID_ARGUMENT, "matmul_schedule: invalid argument");
+  if (!tensor_core_eligible(nullptr, nullptr, nullptr, m, n, k, dtype, 1)) {
+    return set_error(FB200_UNIMPLEMENTED, "matmul_schedule: not a tensor-core shape");
+  }
+  const int elt = itemsize_of(dtype), parts = compensated ? 3 : 1;
+  const TileChoice t = choose_tile(m, n, k, elt, parts, light_epilogue_chain != 0);
+  const int64_t tile_m = kBlockM * t.mh;
+  const int64_t tiles = ((m + tile_m - 1) / tile_m) * ((n + t.block_n - 1) / t.block_n);
+  const int64_t k_blocks = ((k * elt + 127) / 128) * parts;
+  const GemmSplit sp = plan_split(tiles, k_blocks, t.mh);
+  out6[0] = t.block_n;
+  out6[1] = tile_m;
+  out6[2] = sp.dp_tiles;
+  out6[3] = sp.sk_units;
+  out6[4] = sp.sk_ctas;
+  out6[5] = k_blocks;
+  return FB200_OK;
 }
 
 static int matmul_impl(const void* a, const void* b, void* c, void* c_tail, int64_t tail_col, int64_t m,
@@ -947,6 +1263,10 @@ extern "C" int fb200_kernel_status(int device, int* code) {
   std::lock_guard<std::mutex> lock(g_status_mu);
   if (g_status[device].host != nullptr) {
     *code = *reinterpret_cast<volatile int*>(g_status[device].host);
+    if (*code != 0) {
+      std::lock_guard<std::mutex> lock(g_split_mu);
+      ++g_fault_epoch;   // split workspaces clear their flags before their next launch
+    }
     *g_status[device].host = 0;
   }
   return FB200_OK;

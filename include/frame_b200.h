@@ -185,6 +185,19 @@ FB200_API int fb200_matmul_split(const void* a, const void* b, void* c, void* c_
 /* Which kernel family fb200_matmul would pick: 1 = tcgen05/TMEM/TMA, 0 = SIMT. */
 FB200_API int fb200_matmul_uses_tensor_cores(int64_t m, int64_t n, int64_t k, int dtype,
                                              int allow_tf32);
+/* How fb200_matmul would schedule a tensor-core product (no reference counterpart: cuBLASLt keeps
+ * its heuristics to itself).  out6 = {tile columns, tile rows, tiles walked whole, k-blocks dealt
+ * out in ranges, CTAs taking a range, k-blocks per tile}.  When a few tiles (a quarter of the SMs or
+ * fewer) carry a long K (64 k-blocks of 128 bytes or more: the weight-gradient shape), their
+ * k-blocks are split into equal contiguous ranges over the SMs ("stream-K"): the CTA holding a
+ * tile's first k-blocks adds the partial accumulators of the ranges after it, in range order
+ * (results do not depend on timing), and runs the epilogue.  A CTA only waits for CTAs that started
+ * before it (ranges are handed out against a ticket taken at entry), so such launches need no
+ * co-residency guarantee and every wait is bounded; their
+ * partial-tile scratch (19 MB) is kept per stream.  light_epilogue_chain: the chain is adds, multiplies and ReLU only;
+ * compensated: the three-pass strict fp32 form. */
+FB200_API int fb200_matmul_schedule(int64_t m, int64_t n, int64_t k, int dtype, int light_epilogue_chain,
+                                    int compensated, int64_t* out6);
 
 /* Column-split matmul with the all-gather of C fused into the epilogue (the optional multi-GPU
  * variant of the GEMM config; the reference has no multi-GPU code at all).  This rank computes

@@ -237,3 +237,52 @@ def test_exact_order_can_be_forced_at_any_size():
     got = dc.download(np.float32, (m, n))
     rows = slice(0, 8)
     assert np.array_equal(got[rows], fo.matmul(a[rows], b, fo.DT_F32))
+
+
+SPLIT_CASES = [
+    # m, k, n, dtype, allow_tf32, chain: a few tiles with a long K, split over the SMs
+    (512, 8192, 1024, fo.DT_BF16, False, "residual"),    # 16 tiles of 128 x 256, 128 k-blocks each
+    (640, 4096, 1280, fo.DT_BF16, False, None),          # 25 tiles, 64 k-blocks: ranges of 8
+    (500, 4104, 520, fo.DT_F32, True, "col_gelu"),       # TF32, ragged in M, N and K, interpreter chain
+    (256, 8192, 512, fo.DT_BF16, False, None),           # four tiles, each shared by eight CTAs
+    (1024, 2048, 1024, fo.DT_F32, False, None),          # strict fp32: three passes over K in one range list
+]
+
+
+@pytest.mark.parametrize("m,k,n,dt,tf32,chain", SPLIT_CASES, ids=lambda v: str(v))
+def test_long_k_split_over_the_sms(m, k, n, dt, tf32, chain):
+    """Products of a few tiles with a long K: the tiles' k-blocks are dealt out in ranges to more
+    CTAs than there are tiles, partial accumulators travel through scratch memory and are added in
+    range order.  Checked
+    against the float64 product of the stored operands within the tensor-core tiers, and for
+    run-to-run identity (the order of the additions is fixed)."""
+    sched = capi.matmul_schedule(m, n, k, capi.BF16 if dt == fo.DT_BF16 else capi.F32,
+                                 light_epilogue=chain in (None, "residual"),
+                                 compensated=(dt == fo.DT_F32 and not tf32))
+    assert sched["sk_units"] > 0, sched
+    a, b = _gen(m, k, n, dt, 31)
+    rng = np.random.default_rng(32)
+    steps, ref = None, None
+    mm = (fo.to_accum(a, dt).astype(np.float64) @ fo.to_accum(b, dt).astype(np.float64)).astype(np.float32)
+    exp = fo.round_through(mm, dt)
+    if chain == "residual":
+        resid = fo.from_accum(rng.standard_normal((m, n)).astype(np.float32), dt)
+        steps = [("add", resid, capi.OPERAND_FULL)]
+        exp = fo.round_through(exp + fo.to_accum(resid, dt), dt)
+    elif chain == "col_gelu":
+        col = fo.from_accum(rng.standard_normal(n).astype(np.float32), dt)
+        steps = [("add", col, capi.OPERAND_COL), ("gelu", None, 0)]
+        exp = fo.to_accum(fo.gelu(fo.from_accum(fo.round_through(exp + fo.to_accum(col, dt)[None, :], dt), dt), dt), dt)
+    got = _run(a, b, dt, tf32, steps=steps)
+    again = _run(a, b, dt, tf32, steps=steps)
+    assert np.array_equal(got, again)
+    got32 = fo.to_accum(got, dt)
+    scale = np.sqrt(k) * float(np.sqrt((fo.to_accum(a, dt) ** 2).mean()) * np.sqrt((fo.to_accum(b, dt) ** 2).mean()))
+    if dt == fo.DT_BF16:
+        rtol, atol = 2e-2, 2e-3 * max(scale, 1.0)
+    elif tf32:
+        rtol, atol = 1e-3, 2e-3 * scale
+    else:
+        rtol, atol = 1e-5, 3 * 2.0 ** -23 * (k / 8) * max(scale, 1.0)
+    err = np.abs(got32 - exp)
+    assert np.all(err <= atol + rtol * np.abs(exp)), (float(err.max()), atol)
