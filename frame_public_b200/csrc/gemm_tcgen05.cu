@@ -951,22 +951,30 @@ static int split_workspace(cudaStream_t s, uint8_t** out, bool* pooled) {
 // partial last wave over the idle SMs moves the same bytes in the same time and only adds the
 // partial tiles' round trip (4096 x 1024 x 4096 bf16: 39.6 us as 128 whole tiles on 128 SMs, 47.7 us
 // split over 148; 2048 x 8192 x 8192: 212 -> 196 us, but 185 us on 256 x 256 tiles).  It pays when a
-// few tiles carry a long K (a quarter of the SMs or fewer, 64 k-blocks or more): the weight-gradient
-// shape, out[in, out] summed over all tokens.  Ranges are at least an eighth of a tile's k-blocks, so
-// an owner adds at most eight partial tiles.
+// few tiles carry a long K (a quarter of the SMs or fewer, 128 k-blocks or more): the weight-gradient
+// shape, out[in, out] summed over all tokens (768 x 1024 x 32768 TF32: 370 -> 165 us; 128 x 256 x
+// 65536 bf16: 365 -> 70 us; 256 x 512 x 8192: 52 -> 32 us; at 64 k-blocks it saved nothing).  Ranges
+// are at least an eighth of a tile's k-blocks, so an owner adds at most eight partial tiles.
 constexpr int64_t kSplitMaxTiles = kNumSMs / 4;
-constexpr int64_t kSplitMinKBlocks = 64;
+constexpr int64_t kSplitMinKBlocks = 128;
 static GemmSplit plan_split(int64_t tiles, int64_t k_blocks, int mh) {
   GemmSplit sp{};
   sp.dp_tiles = tiles;
-  if (mh != 1 || tiles > kSplitMaxTiles || k_blocks < kSplitMinKBlocks) return sp;
-  const int64_t units = tiles * k_blocks;
-  const int64_t min_range = k_blocks / 8 > 8 ? k_blocks / 8 : 8;
-  const int64_t ctas = units / min_range < kNumSMs ? units / min_range : kNumSMs;
-  if (ctas < 2 * tiles) return sp;
-  sp.dp_tiles = 0;
-  sp.sk_units = units;
-  sp.sk_ctas = static_cast<int>(ctas);
+  if (mh != 1 || k_blocks < kSplitMinKBlocks) return sp;
+  if (tiles <= kSplitMaxTiles) {
+    const int64_t units = tiles * k_blocks;
+    const int64_t min_range = k_blocks / 8 > 8 ? k_blocks / 8 : 8;
+    const int64_t ctas = units / min_range < kNumSMs ? units / min_range : kNumSMs;
+    if (ctas < 2 * tiles) return sp;
+    sp.dp_tiles = 0;
+    sp.sk_units = units;
+    sp.sk_ctas = static_cast<int>(ctas);
+    return sp;
+  }
+  // Whole waves followed by a light last wave (the 2048-row shard of an 8192^3 product: 3.46 waves of
+  // 148 tiles) are NOT split: dealing the last wave's k-blocks out to all SMs measured 212 -> 196 us
+  // for the plain product, which 256 x 256 tiles beat anyway (185 us), and nothing with a bias + GELU
+  // epilogue (0.2418 against 0.2403 ms per shard).
   return sp;
 }
 
@@ -1042,7 +1050,7 @@ static int launch_tc(const void* a, const void* b, const GemmDest& c, int64_t m,
                      int dtype, const EpilogueDev& epi, cudaStream_t s) {
   const int kind = classify_epilogue(epi);
   if (kind == kEpiNone) return launch_tc_epi<T, ELT, BLOCK_N, MH, KB, kEpiNone>(a, b, c, m, n, k, dtype, epi, s);
-  bool split_planned = false;
+  bool split_planned = false;   // split products take the interpreted chain
   if constexpr (MH == 1 && BLOCK_N == 256) {
     const int parts = (c.a_lo != nullptr && c.b_lo != nullptr) ? 3 : 1;
     const int64_t tiles = ((m + kBlockM - 1) / kBlockM) * ((n + BLOCK_N - 1) / BLOCK_N);

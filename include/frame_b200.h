@@ -188,7 +188,7 @@ FB200_API int fb200_matmul_uses_tensor_cores(int64_t m, int64_t n, int64_t k, in
 /* How fb200_matmul would schedule a tensor-core product (no reference counterpart: cuBLASLt keeps
  * its heuristics to itself).  out6 = {tile columns, tile rows, tiles walked whole, k-blocks dealt
  * out in ranges, CTAs taking a range, k-blocks per tile}.  When a few tiles (a quarter of the SMs or
- * fewer) carry a long K (64 k-blocks of 128 bytes or more: the weight-gradient shape), their
+ * fewer) carry a long K (128 k-blocks of 128 bytes or more: the weight-gradient shape), their
  * k-blocks are split into equal contiguous ranges over the SMs ("stream-K"): the CTA holding a
  * tile's first k-blocks adds the partial accumulators of the ranges after it, in range order
  * (results do not depend on timing), and runs the epilogue.  A CTA only waits for CTAs that started

@@ -11,7 +11,8 @@ SMS = 148
 
 
 def _segments(sched, cta):
-    """Segments (tile, kb0, kb1) of one CTA: whole tiles first, then its range of the split part."""
+    """Segments (tile, kb0, kb1) of the CTA that started `cta`-th: whole tiles first, then its range
+    of the split part."""
     kbs, segs = sched["k_blocks"], []
     grid = SMS if sched["sk_units"] else min(SMS, max(sched["dp_tiles"], 1))
     t = cta
@@ -19,8 +20,9 @@ def _segments(sched, cta):
         segs.append((t, 0, kbs))
         t += grid
     if sched["sk_units"] and cta < sched["sk_ctas"]:
-        u = sched["sk_units"] * cta // sched["sk_ctas"]
-        u1 = sched["sk_units"] * (cta + 1) // sched["sk_ctas"]
+        rng = sched["sk_ctas"] - 1 - cta     # ranges are handed out against the start order
+        u = sched["sk_units"] * rng // sched["sk_ctas"]
+        u1 = sched["sk_units"] * (rng + 1) // sched["sk_ctas"]
         while u < u1:
             tile = u // kbs
             kb0 = u - tile * kbs
@@ -30,7 +32,7 @@ def _segments(sched, cta):
     return segs
 
 
-SHAPES = [(512, 1024, 8192, capi.BF16), (640, 1280, 4096, capi.BF16), (500, 520, 4104, capi.F32),
+SHAPES = [(512, 1024, 8192, capi.BF16), (640, 1280, 8192, capi.BF16), (500, 520, 4104, capi.F32),
           (256, 512, 8192, capi.BF16), (1024, 1024, 2048, capi.F32), (128, 256, 65536, capi.BF16),
           (768, 1024, 32768, capi.F32)]
 
@@ -40,7 +42,7 @@ def test_split_ranges_cover_every_k_block_once(m, n, k, dt):
     sched = capi.matmul_schedule(m, n, k, dt, compensated=(m, n, k) == (1024, 1024, 2048))
     assert sched["sk_units"] > 0, sched
     tiles = -(-m // sched["tile_m"]) * -(-n // sched["tile_n"])
-    assert sched["dp_tiles"] == 0
+    assert sched["dp_tiles"] % SMS == 0 and sched["dp_tiles"] < tiles
     assert sched["sk_units"] == (tiles - sched["dp_tiles"]) * sched["k_blocks"]
     assert 2 <= sched["sk_ctas"] <= SMS
     seen = {}
@@ -55,20 +57,22 @@ def test_split_ranges_cover_every_k_block_once(m, n, k, dt):
                 assert (tile, kb) not in seen, (tile, kb, cta, seen[(tile, kb)])
                 seen[(tile, kb)] = cta
     assert len(seen) == tiles * sched["k_blocks"]
-    # the owner of a tile (holder of k-block 0) finds the rest with the CTAs right after it, in order
+    # the owner of a tile (holder of k-block 0) finds the rest with the CTAs that started just BEFORE
+    # it, in order: a CTA never waits for one that may not be running yet
     for tile in range(sched["dp_tiles"], tiles):
         owner = seen[(tile, 0)]
         holders = []
         for kb in range(sched["k_blocks"]):
             if not holders or holders[-1] != seen[(tile, kb)]:
                 holders.append(seen[(tile, kb)])
-        assert holders == list(range(owner, owner + len(holders))), (tile, holders)
+        assert holders == list(range(owner, owner - len(holders), -1)), (tile, holders)
 
 
 def test_full_machines_and_short_k_are_not_split():
     assert capi.matmul_schedule(8192, 8192, 8192, capi.BF16)["sk_units"] == 0      # 13.8 waves
     assert capi.matmul_schedule(32768, 1536, 48, capi.F32)["sk_units"] == 0        # two k-blocks
     assert capi.matmul_schedule(4096, 1024, 4096, capi.BF16)["sk_units"] == 0      # 128 tiles: L2-bound
+    assert capi.matmul_schedule(2048, 8192, 8192, capi.BF16)["sk_units"] == 0      # 3.46 waves: measured no gain
     assert capi.matmul_schedule(64, 256, 784, capi.F32)["sk_units"] == 0           # 25 k-blocks
     s = capi.matmul_schedule(8192, 8192, 8192, capi.BF16, light_epilogue=True)
     assert (s["tile_m"], s["tile_n"], s["sk_units"]) == (256, 256, 0)

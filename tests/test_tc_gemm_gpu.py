@@ -242,7 +242,7 @@ def test_exact_order_can_be_forced_at_any_size():
 SPLIT_CASES = [
     # m, k, n, dtype, allow_tf32, chain: a few tiles with a long K, split over the SMs
     (512, 8192, 1024, fo.DT_BF16, False, "residual"),    # 16 tiles of 128 x 256, 128 k-blocks each
-    (640, 4096, 1280, fo.DT_BF16, False, None),          # 25 tiles, 64 k-blocks: ranges of 8
+    (640, 8192, 1280, fo.DT_BF16, False, None),          # 25 tiles, 128 k-blocks: ranges of 16
     (500, 4104, 520, fo.DT_F32, True, "col_gelu"),       # TF32, ragged in M, N and K, interpreter chain
     (256, 8192, 512, fo.DT_BF16, False, None),           # four tiles, each shared by eight CTAs
     (1024, 2048, 1024, fo.DT_F32, False, None),          # strict fp32: three passes over K in one range list
