@@ -30,7 +30,7 @@ NO_FMA = {"elementwise.cu", "rowops.cu", "scan.cu", "scan_chunked.cu", "conv_poo
 
 SOURCES = ["runtime.cu", "elementwise.cu", "rowops.cu", "scan.cu", "shape_ops.cu", "conv_pool.cu",
            "gemm_simt.cu", "gemm_tcgen05.cu", "conv_tcgen05.cu", "plan.cu", "mamba_scan.cu", "scan_chunked.cu",
-           "attention_tcgen05.cu", "conv_halo_tcgen05.cu", "conv_planes_tcgen05.cu", "index_ops.cu", "grad_ops.cu", "fft_ops.cu"]
+           "attention_tcgen05.cu", "conv_halo_tcgen05.cu", "conv_planes_tcgen05.cu", "conv_rows_tcgen05.cu", "index_ops.cu", "grad_ops.cu", "fft_ops.cu"]
 
 
 def _headers_mtime() -> float:

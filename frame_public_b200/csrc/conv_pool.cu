@@ -308,6 +308,11 @@ extern "C" int fb200_conv2d_planes_tcgen05(const void* x, const void* w, const v
 extern "C" int fb200_conv2d_halo_tcgen05(const void* x, const void* w, const void* bias, void* out,
                                          const fb200_conv2d_params* p, int dtype,
                                          const fb200_epilogue* epilogue, fb200_stream stream);
+// Implemented in conv_rows_tcgen05.cu: stride 2 with few input channels (row matrices built once per
+// input row).
+extern "C" int fb200_conv2d_rows_tcgen05(const void* x, const void* w, const void* bias, void* out,
+                                         const fb200_conv2d_params* p, int dtype,
+                                         const fb200_epilogue* epilogue, fb200_stream stream);
 
 extern "C" int fb200_conv2d(const void* x, const void* w, const void* bias, void* out,
                             const fb200_conv2d_params* pp, int dtype, int allow_tf32,
@@ -340,6 +345,10 @@ extern "C" int fb200_conv2d(const void* x, const void* w, const void* bias, void
   if (allow_tf32 && dtype == FB200_F32) {
     {
       const int rc = fb200_conv2d_planes_tcgen05(x, w, bias, out, pp, dtype, epilogue, stream);
+      if (rc != FB200_UNIMPLEMENTED) return rc;
+    }
+    {
+      const int rc = fb200_conv2d_rows_tcgen05(x, w, bias, out, pp, dtype, epilogue, stream);
       if (rc != FB200_UNIMPLEMENTED) return rc;
     }
     {

@@ -43,6 +43,15 @@ CASES = [
     ((1, 8, 9, 96), (16, 8, 3, 3), (1, 1), (1, 1), False),
     ((2, 256, 28, 28), (256, 256, 3, 3), (1, 1), (1, 1), True),
     ((5, 24, 3, 8), (8, 24, 3, 3), (1, 1), (1, 1), True),
+    # row-matrix kernel (stride 2, KW * Cin <= 32, output rows a multiple of 4 pixels): runs of rows
+    # that cross images; 3x3 with four channels (K 12 -> 16); one channel, 5x5, odd height; no
+    # padding; an even 4x4 window; Cout too large for resident weights (falls back to the halo kernel)
+    ((5, 3, 90, 64), (32, 3, 7, 7), (2, 2), (3, 3), True),
+    ((2, 4, 40, 48), (40, 4, 3, 3), (2, 2), (1, 1), False),
+    ((2, 1, 33, 72), (16, 1, 5, 5), (2, 2), (2, 2), True),
+    ((1, 2, 21, 34), (8, 2, 3, 3), (2, 2), (0, 0), True),
+    ((1, 3, 16, 32), (8, 3, 4, 4), (2, 2), (1, 1), True),
+    ((1, 3, 32, 64), (200, 3, 7, 7), (2, 2), (3, 3), True),
 ]
 
 
@@ -101,6 +110,20 @@ def test_conv2d_tensor_cores_fused_relu_and_residual():
     got = _run(x, w, b, (1, 1), (1, 1), steps=[("relu", None, 0), ("add", res, capi.OPERAND_FULL)])
     exp = fo.add(fo.relu(fo.conv2d(x, w, b, (1, 1), (1, 1), 1)), res)
     ok, worst = _within_tf32_bound(got, exp, x, w, (1, 1), (1, 1))
+    assert ok, (worst, fo.max_err(got, exp))
+
+
+def test_stride2_stem_fused_relu_and_residual():
+    """The stride-2 row-matrix kernel with a chain: ReLU, then a full-shape residual; 448 output rows
+    over 148 CTAs (runs of three rows, image boundaries inside runs)."""
+    rng = np.random.default_rng(24)
+    x = rng.standard_normal((4, 3, 224, 224)).astype(np.float32)
+    w = (rng.standard_normal((64, 3, 7, 7)) * 0.1).astype(np.float32)
+    b = rng.standard_normal(64).astype(np.float32)
+    res = rng.standard_normal((4, 64, 112, 112)).astype(np.float32)
+    got = _run(x, w, b, (2, 2), (3, 3), steps=[("relu", None, 0), ("add", res, capi.OPERAND_FULL)])
+    exp = fo.add(fo.relu(fo.conv2d(x, w, b, (2, 2), (3, 3), 1)), res)
+    ok, worst = _within_tf32_bound(got, exp, x, w, (2, 2), (3, 3))
     assert ok, (worst, fo.max_err(got, exp))
 
 
