@@ -94,6 +94,8 @@ SIGNATURES = {
     "fb200_matmul_schedule": (c_int, [c_int64, c_int64, c_int64, c_int, c_int, c_int, _I64P]),
     "fb200_conv2d": (c_int, [_P, _P, _P, _P, POINTER(Conv2dParams), c_int, c_int,
                              POINTER(Epilogue), _P]),
+    "fb200_conv2d_max_pool": (c_int, [_P, _P, _P, _P, _P, POINTER(Conv2dParams)] + [c_int64] * 6 +
+                              [c_int, c_int, POINTER(Epilogue), _P]),
     "fb200_conv1d": (c_int, [_P, _P, _P, _P] + [c_int64] * 8 + [c_int, _P]),
     "fb200_max_pool2d": (c_int, [_P, _P] + [c_int64] * 10 + [c_int, _P]),
     "fb200_avg_pool2d": (c_int, [_P, _P] + [c_int64] * 10 + [c_int, _P]),
@@ -278,6 +280,14 @@ def conv2d(x, w, bias, out, params: Conv2dParams, dtype, allow_tf32=False, epilo
     ep = byref(epilogue) if epilogue is not None else None
     check(load().fb200_conv2d(x, w, bias, out, byref(params), dtype, 1 if allow_tf32 else 0, ep,
                               stream))
+
+
+def conv2d_max_pool(x, w, bias, mid, out, params: Conv2dParams, pool, dtype, allow_tf32=False, epilogue=None,
+                    stream=None):
+    """pool = (kh, kw, stride_h, stride_w, pad_h, pad_w)."""
+    ep = byref(epilogue) if epilogue is not None else None
+    check(load().fb200_conv2d_max_pool(x, w, bias, mid, out, byref(params), *pool, dtype, 1 if allow_tf32 else 0,
+                                       ep, stream))
 
 
 def conv1d(x, w, bias, out, n, cin, l, cout, k, stride, padding, groups, dtype, stream=None):

@@ -314,6 +314,10 @@ extern "C" int fb200_conv2d_rows_tcgen05(const void* x, const void* w, const voi
                                          const fb200_conv2d_params* p, int dtype,
                                          const fb200_epilogue* epilogue, fb200_stream stream);
 
+extern "C" int fb200_conv2d_rows_pooled_tcgen05(const void* x, const void* w, const void* bias, void* pooled,
+                                                const fb200_conv2d_params* p, int dtype,
+                                                const fb200_epilogue* epilogue, fb200_stream stream);
+
 extern "C" int fb200_conv2d(const void* x, const void* w, const void* bias, void* out,
                             const fb200_conv2d_params* pp, int dtype, int allow_tf32,
                             const fb200_epilogue* epilogue, fb200_stream stream) {
@@ -772,4 +776,33 @@ extern "C" int fb200_dwconv1d_time_major(const void* x, int64_t x_ld, const void
   else if (dtype == FB200_BF16) launch_dwconv<__nv_bfloat16>(grid, s, x, x_ld, w, bias, out, out_ld, len, out_len, channels, kk, shift, ops);
   else launch_dwconv<__half>(grid, s, x, x_ld, w, bias, out, out_ld, len, out_len, channels, kk, shift, ops);
   return after_launch("dwconv1d_time_major_kernel");
+}
+
+// conv2d -> [epilogue chain] -> max_pool2d as one call.  With allow_tf32, a 3 x 3 / stride 2 / pad 1
+// pool behind a stride-2 convolution of few input channels (an image stem) runs as ONE kernel that
+// never writes the convolution's result (conv_rows_tcgen05.cu); `mid` ([n, cout, oh, ow], may be
+// NULL) is then left untouched.  Every other case runs the two operators one after the other
+// through `mid`, which must then be given.
+extern "C" int fb200_conv2d_max_pool(const void* x, const void* w, const void* bias, void* mid, void* out,
+                                     const fb200_conv2d_params* pp, int64_t pool_kh, int64_t pool_kw,
+                                     int64_t pool_stride_h, int64_t pool_stride_w, int64_t pool_pad_h,
+                                     int64_t pool_pad_w, int dtype, int allow_tf32,
+                                     const fb200_epilogue* epilogue, fb200_stream stream) {
+  if (pp == nullptr) return set_error(FB200_INVALID_ARGUMENT, "conv2d_max_pool: null params");
+  if (pp->n == 0) return FB200_OK;
+  if (x == nullptr || w == nullptr || out == nullptr) return set_error(FB200_INVALID_ARGUMENT, "conv2d_max_pool: null argument");
+  if (allow_tf32 && dtype == FB200_F32 && pool_kh == 3 && pool_kw == 3 && pool_stride_h == 2 && pool_stride_w == 2 &&
+      pool_pad_h == 1 && pool_pad_w == 1 && pp->stride_h >= 1 && pp->stride_w >= 1 && pp->kh >= 1 && pp->kw >= 1) {
+    const int rc = fb200_conv2d_rows_pooled_tcgen05(x, w, bias, out, pp, dtype, epilogue, stream);
+    if (rc != FB200_UNIMPLEMENTED) return rc;
+  }
+  if (mid == nullptr) {
+    return set_error(FB200_INVALID_ARGUMENT, "conv2d_max_pool: this shape runs as two kernels and needs the "
+                     "intermediate buffer");
+  }
+  if (int rc = fb200_conv2d(x, w, bias, mid, pp, dtype, allow_tf32, epilogue, stream)) return rc;
+  const int64_t oh = (pp->h + 2 * pp->pad_h - pp->kh) / pp->stride_h + 1;
+  const int64_t ow = (pp->w + 2 * pp->pad_w - pp->kw) / pp->stride_w + 1;
+  return fb200_max_pool2d(mid, out, pp->n, pp->cout, oh, ow, pool_kh, pool_kw, pool_stride_h, pool_stride_w,
+                          pool_pad_h, pool_pad_w, dtype, stream);
 }

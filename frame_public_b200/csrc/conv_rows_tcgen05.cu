@@ -37,7 +37,7 @@
 // the launch writes 103 MB, and while the epilogue's stores queue in the SM's load/store path (about
 // 2 K cycles per output row when the memory system takes 3.9 TB/s of writes) the builders' shared
 // memory stores and global loads wait in the same queue: 42 stores take 1.8 K cycles and a load
-// takes 5 K cycles to come back, hence the cp.async prefetch three rows ahead.  The MMAs themselves
+// takes 5 K cycles to come back, hence the cp.async prefetch two rows ahead.  The MMAs themselves
 // need 1.7 K cycles per output row (82 per instruction).  Measured: 73 us against 95 us for the
 // halo kernel on this shape (floor: 103 MB of writes = 27 us).
 // FLOPs per launch = 2 * N*OH*OW * Cout * Cin*KH*KW; bytes = input + output once.
@@ -60,23 +60,26 @@ constexpr int kRowsThreads = (kRowsFirstEpiWarp + 16) * 32;
 constexpr int kRowsTasks = 3;                         // element pairs per builder thread and input row
 constexpr int kRowsMaxKh = 8;
 constexpr int kRowsMaxKw = 8;
+constexpr int kRowsPfStages = 3;                      // output rows the input-row prefetch runs ahead, plus one
 
 enum RowsFault : int {
   kFaultRowsFreed = 231,     // builders: the MMAs two output rows back never completed
   kFaultRowsBuilt = 232,     // MMA: the row matrices of this output row never arrived
   kFaultRowsTmem = 233,      // MMA: accumulator never drained
   kFaultRowsEpilogue = 234,  // epilogue: accumulator never completed
+  kFaultRowsPoolRow = 235,   // pooling epilogue: the other group's row never arrived / was never consumed
 };
 
 struct RowsGeom {
   int n, cin, h, w, cout, kh, kw, ph, pw, oh, ow;
   int kp;          // KW * Cin padded to a multiple of 8: k extent of one filter row
   int npad;        // Cout padded to a multiple of 32
-  int n_slots;     // ring slots (KH + 3); slot n_slots is the zero slot
+  int n_slots;     // ring slots (KH + 2: the KH rows an output row reads and the two being built); slot n_slots is the zero slot
   int slot_bytes;  // 4 spans x kp k-rows x 128 bytes
   int w_bytes;     // KH x npad x 128
   int tmem_cols;
   int64_t total_rows;   // n * oh
+  int poh, pow;         // fused 3 x 3 / stride 2 / pad 1 max-pool: pooled rows and columns (else 0)
 };
 
 // Byte offset of element (k, px) inside a row matrix.
@@ -87,7 +90,13 @@ __device__ __forceinline__ uint32_t rows_elem_off(int k, int px, int kp) {
 // KH and KSTEPS (= kp / 8) are compile-time so that the MMA warp's loop over an output row's filter
 // rows is straight-line code: KH descriptors, then KH * KSTEPS instructions with immediate offsets
 // (with run-time loops the issue took 167 cycles per tcgen05.mma instead of 63).
-template <int KH, int KSTEPS>
+// POOL: the epilogue max-pools the finished rows (3 x 3 windows, stride 2, padding 1) and stores only
+// the pooled tensor.  A CTA then owns a run of POOLED rows and computes the conv rows they cover
+// (2 p - 1 .. 2 p + 1; the first of them is also computed by the CTA before: one row in 25 twice).
+// Conv rows alternate between the two epilogue groups, so one group always has the odd rows and the
+// other the even ones: a thread of the odd group keeps its previous row's column maxima in
+// registers, the even row in between crosses through one of two 14 KB shared-memory buffers.
+template <int KH, int KSTEPS, bool POOL>
 __global__ void __launch_bounds__(kRowsThreads, 1)
 conv2d_rows_tcgen05_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ bias,
                            float* __restrict__ out, RowsGeom g, uint32_t idesc, EpilogueDev epi, int* status) {
@@ -106,12 +115,31 @@ conv2d_rows_tcgen05_kernel(const float* __restrict__ x, const float* __restrict_
   const uint32_t tmem_slot = bars + 64;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + bar_off + 64);
   float* bias_s = reinterpret_cast<float*>(base_ptr + bar_off + 128);   // [256]
-  const uint32_t pf_off = bar_off + 128 + 1024;   // input-row prefetch: [4 stages][2 rows][tasks][128 threads] x 8 bytes
+  const uint32_t pf_off = bar_off + 128 + 1024;   // input-row prefetch: [stages][2 rows][tasks][128 threads] x 8 bytes
+  const uint32_t edge_off = pf_off + kRowsPfStages * 2 * kRowsTasks * kRowsBuilders * 8;   // POOL: [16 warps][32] floats
+  const uint32_t even_off = edge_off + 16 * 32 * 4;                                          // POOL: two buffers of [npad][pow] floats
+  auto even_ready = [&](int b) { return bars + 8u * (9 + b); };
+  auto even_free = [&](int b) { return bars + 8u * (11 + b); };
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int64_t row_begin = g.total_rows * blockIdx.x / gridDim.x;
-  const int64_t row_end = g.total_rows * (blockIdx.x + 1) / gridDim.x;
+  int64_t row_begin, row_end;
+  if (POOL) {
+    // pooled rows [p0, p1) of the list (image, pooled row) -> the conv rows they cover
+    const int64_t p_total = static_cast<int64_t>(g.n) * g.poh;
+    const int64_t p0 = p_total * blockIdx.x / gridDim.x, p1 = p_total * (blockIdx.x + 1) / gridDim.x;
+    if (p1 > p0) {
+      const int64_t img_a = p0 / g.poh, img_b = (p1 - 1) / g.poh;
+      const int pa = static_cast<int>(p0 - img_a * g.poh), pb = static_cast<int>(p1 - 1 - img_b * g.poh);
+      row_begin = img_a * g.oh + (2 * pa - 1 > 0 ? 2 * pa - 1 : 0);
+      row_end = img_b * g.oh + (2 * pb + 1 < g.oh - 1 ? 2 * pb + 1 : g.oh - 1) + 1;
+    } else {
+      row_begin = row_end = 0;
+    }
+  } else {
+    row_begin = g.total_rows * blockIdx.x / gridDim.x;
+    row_end = g.total_rows * (blockIdx.x + 1) / gridDim.x;
+  }
   const int n_items = static_cast<int>(row_end - row_begin);
 
   if (threadIdx.x == 0) {
@@ -120,6 +148,10 @@ conv2d_rows_tcgen05_kernel(const float* __restrict__ x, const float* __restrict_
       mbar_init(freed_bar(p), 1);
       mbar_init(tmem_full(p), 1);
       mbar_init(tmem_empty(p), 8);                   // the eight warps of the accumulator's group
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(even_ready(b), 8);
+      mbar_init(even_free(b), 8);
     }
     mbar_fence_init();
   }
@@ -221,7 +253,7 @@ conv2d_rows_tcgen05_kernel(const float* __restrict__ x, const float* __restrict_
     };
     const int64_t img_elems = static_cast<int64_t>(g.cin) * g.h * g.w;
     int img = img0, oy = oy0;
-    // The two new input rows of an output row are fetched THREE output rows ahead with cp.async into
+    // The two new input rows of an output row are fetched TWO output rows ahead with cp.async into
     // a slice of shared memory that only this thread reads back (no barrier: cp.async.wait_group
     // covers it).  Register prefetching one row ahead was not enough: with the epilogue's stores
     // saturating the memory system a load takes about 5 K cycles to come back.  The copies are
@@ -245,7 +277,7 @@ conv2d_rows_tcgen05_kernel(const float* __restrict__ x, const float* __restrict_
 #pragma unroll
           for (int t = 0; t < kRowsTasks; ++t) {
             const float* src = x + img_off + r * g.w + ld_off[t];
-            asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(pf_addr(item & 3, rr, t)), "l"(src) : "memory");
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(pf_addr(item % kRowsPfStages, rr, t)), "l"(src) : "memory");
           }
         }
       }
@@ -254,21 +286,19 @@ conv2d_rows_tcgen05_kernel(const float* __restrict__ x, const float* __restrict_
     advance_cursor();   // item 0 starts the ring afresh and loads its rows itself
     fetch(1);
     advance_cursor();
-    fetch(2);
-    advance_cursor();
     bool ok = true;
     int slot_hi = 0;   // ring slot of the newest row of the output row being built
     for (int i = 0; i < n_items && ok; ++i) {
       const bool fresh = i == 0 || oy == 0;
-      fetch(i + 3);
+      fetch(i + 2);
       advance_cursor();
-      asm volatile("cp.async.wait_group 3;" ::: "memory");   // the group of item i has landed
+      asm volatile("cp.async.wait_group 2;" ::: "memory");   // the group of item i has landed
       float2 cur[2][kRowsTasks];
 #pragma unroll
       for (int rr = 0; rr < 2; ++rr) {
 #pragma unroll
         for (int t = 0; t < kRowsTasks; ++t) {
-          asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(cur[rr][t].x), "=f"(cur[rr][t].y) : "r"(pf_addr(i & 3, rr, t)) : "memory");
+          asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(cur[rr][t].x), "=f"(cur[rr][t].y) : "r"(pf_addr(i % kRowsPfStages, rr, t)) : "memory");
         }
       }
       // The slots written now were last read by the MMAs of item i - 2 (i - 1 when the ring starts
@@ -390,6 +420,126 @@ conv2d_rows_tcgen05_kernel(const float* __restrict__ x, const float* __restrict_
     bool ok = true;
     int img = img0, oy = oy0 + group;
     if (oy >= g.oh) { oy -= g.oh; ++img; }
+    if constexpr (POOL) {
+      // ---- pooling epilogue ------------------------------------------------------------------------
+      // This group's rows all have the parity of its first row (OH is even, so the alternation carries
+      // over from the last row of an image to the first row of the next).  A warp works on its 32
+      // channels in two passes of 16, to keep the previous odd row's column maxima (32 values per
+      // thread) in registers beside the pass's own values.
+      float prev_odd[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) prev_odd[j] = -INFINITY;
+      int even_rows = 0;           // even group: rows published; odd group: rows consumed
+      // edges: [pass][group, half, quarter][16]; even rows: two buffers, so that the even group can
+      // publish its next row while the odd group still reads the one before
+      float* edge_base = reinterpret_cast<float*>(base_ptr + edge_off) + ((group * 2 + half) * 4 + quarter) * 16;
+      float* even_base = reinterpret_cast<float*>(base_ptr + even_off);
+      const int even_buf_elems = g.npad * g.pow;
+      const int c0 = c_begin;      // one 32-channel chunk per warp (npad == 64)
+      const bool out_px = (px & 1) == 0 && (px >> 1) < g.pow;
+      const int q = px >> 1;
+      const int bar_id = 2 + group * 2 + half;   // the four warps (lane quarters) of this group and half
+      for (int i = group; i < n_items && ok; i += 2) {
+        const int acc = group;
+        if (!mbar_wait(tmem_full(acc), static_cast<uint32_t>(i >> 1) & 1u, status, kFaultRowsEpilogue)) { ok = false; break; }
+        tcgen05_fence_after_sync();
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc * g.npad + c0);
+        const bool even_row = (oy & 1) == 0;
+        const bool emits = !even_row && i != 0;   // a run's leading odd row only feeds the next pooled row
+        if (!even_row && oy == 1) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) prev_odd[j] = -INFINITY;   // row -1 of an image is padding
+        }
+        // the k-th even row of the run goes through buffer k & 1; its barriers complete once per use
+        const int eb = even_rows & 1;
+        if (even_row && even_rows >= 2) {
+          ok = mbar_wait_warp(even_free(eb), static_cast<uint32_t>((even_rows >> 1) - 1) & 1u, status, kFaultRowsPoolRow);
+        } else if (emits) {
+          ok = mbar_wait_warp(even_ready(eb), static_cast<uint32_t>(even_rows >> 1) & 1u, status, kFaultRowsPoolRow);
+        }
+        if (!ok) break;
+        float* even_s = even_base + eb * even_buf_elems;
+        const int p = oy >> 1;   // pooled row completed by an odd row
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t r[16];
+          tmem_ld_32x32b_x16(t_row + static_cast<uint32_t>(hh * 16), r);
+          tmem_ld_wait();
+          if (hh == 1) {
+            // the accumulator is in registers: the MMAs of the row after next may have it
+            tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tmem_empty(acc));
+          }
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]) + bias_s[c0 + hh * 16 + j];
+#pragma unroll 1
+          for (int s = 0; s < epi.n_ops; ++s) ew_unary_vec<float, 16>(epi.ops[s], v);   // unary steps only
+          // Column maxima over px - 1, px, px + 1 (needed at even px).  Neighbours are the lanes next
+          // door; lane 0 takes its left neighbour from the warp of the quarter before.
+          if (!valid) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = -INFINITY;
+          }
+          // (one edge buffer per pass: when a pass's buffer is rewritten for the next row, the other
+          // pass's barrier lies in between, so one barrier per pass is enough)
+          float* edge_s = edge_base + hh * (16 * 16);
+          if (lane == 31) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) edge_s[j] = v[j];
+          }
+          asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float l = __shfl_up_sync(0xffffffffu, v[j], 1);
+            const float r1 = __shfl_down_sync(0xffffffffu, v[j], 1);
+            if (lane == 0) l = quarter == 0 ? -INFINITY : (edge_s - 16)[j];   // pixel -1 is padding
+            v[j] = fmaxf(fmaxf(l, v[j]), r1);
+          }
+          if (even_row) {
+            if (out_px) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) even_s[(c0 + hh * 16 + j) * g.pow + q] = v[j];
+            }
+          } else {
+            if (emits && out_px) {
+              // the pooled value replaces the even row's entry (this thread is its only reader)
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                float* e = even_s + (c0 + hh * 16 + j) * g.pow + q;
+                *e = fmaxf(fmaxf(prev_odd[hh * 16 + j], *e), v[j]);
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) prev_odd[hh * 16 + j] = v[j];
+          }
+        }
+        __syncwarp();
+        if (emits) {
+          // The pooled row [Cout][POW] is complete in the buffer once the group's eight warps are
+          // here: it leaves with 16-byte stores, consecutive threads along a channel's row (32
+          // four-byte stores per thread from the lane = pixel layout took 7 K cycles per row).
+          asm volatile("bar.sync %0, 256;" ::"r"(6 + group) : "memory");
+          const int row_f4 = g.pow / 4;
+          const int total_f4 = g.cout * row_f4;
+          float* orow = out + (static_cast<int64_t>(img) * g.cout * g.poh + p) * g.pow;   // + ch * poh * pow
+          for (int idx = (ew & 7) * 32 + lane; idx < total_f4; idx += 256) {
+            const int ch = idx / row_f4, qq = idx - ch * row_f4;
+            const float4 v4 = *reinterpret_cast<const float4*>(even_s + ch * g.pow + qq * 4);
+            *reinterpret_cast<float4*>(orow + static_cast<int64_t>(ch) * g.poh * g.pow + qq * 4) = v4;
+          }
+          __syncwarp();
+        }
+        if (lane == 0) {
+          if (even_row) mbar_arrive(even_ready(eb));
+          else if (emits) mbar_arrive(even_free(eb));
+        }
+        if (even_row || emits) ++even_rows;
+        oy += 2;
+        while (oy >= g.oh) { oy -= g.oh; ++img; }
+      }
+    } else
     for (int i = group; i < n_items && ok; i += 2) {
       const int acc = group;
       if (!mbar_wait(tmem_full(acc), static_cast<uint32_t>(i >> 1) & 1u, status, kFaultRowsEpilogue)) { ok = false; break; }
@@ -401,6 +551,13 @@ conv2d_rows_tcgen05_kernel(const float* __restrict__ x, const float* __restrict_
         uint32_t r[32];
         tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(c0), r);
         tmem_ld_wait();
+        if (c0 + 32 >= c_end) {
+          // the warp's share of the accumulator is in registers: the MMAs of the row after next may
+          // have it while the arithmetic and the stores run
+          tcgen05_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tmem_empty(acc));
+        }
         if (valid) {
           float v[32];
           const int64_t obase = (static_cast<int64_t>(img) * g.cout + c0) * ohow + pix;   // + j * ohow per channel
@@ -444,9 +601,10 @@ conv2d_rows_tcgen05_kernel(const float* __restrict__ x, const float* __restrict_
           }
         }
       }
-      tcgen05_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tmem_empty(acc));
+      if (c_begin >= c_end) {   // a warp without a chunk (Cout <= 32) still owes its arrival
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tmem_empty(acc));
+      }
       oy += 2;
       while (oy >= g.oh) { oy -= g.oh; ++img; }
     }
@@ -464,11 +622,12 @@ conv2d_rows_tcgen05_kernel(const float* __restrict__ x, const float* __restrict_
 
 using namespace fb200;
 
-// Returns FB200_UNIMPLEMENTED for shapes outside this kernel's reach (the caller then tries the halo
-// kernel, the gather kernel and the direct kernel).
-extern "C" int fb200_conv2d_rows_tcgen05(const void* x, const void* w, const void* bias, void* out,
-                                         const fb200_conv2d_params* p, int dtype,
-                                         const fb200_epilogue* epilogue, fb200_stream stream) {
+// Launches the row-matrix kernel, or returns FB200_UNIMPLEMENTED for shapes outside its reach.
+// pooled != nullptr: the 3 x 3 / stride 2 / pad 1 max-pool of the result is stored there instead
+// of the result itself ([n, cout, poh, pow]).
+static int rows_launch(const void* x, const void* w, const void* bias, void* out, void* pooled,
+                       const fb200_conv2d_params* p, int dtype, const fb200_epilogue* epilogue,
+                       fb200_stream stream) {
   if (dtype != FB200_F32 || p->groups != 1 || p->cout > 256 || p->cout < 1) return FB200_UNIMPLEMENTED;
   if (p->stride_h != 2 || p->stride_w != 2) return FB200_UNIMPLEMENTED;
   if (p->kh < 1 || p->kh > kRowsMaxKh || p->kw < 1 || p->kw > kRowsMaxKw || p->kw * p->cin > 32) return FB200_UNIMPLEMENTED;
@@ -487,41 +646,77 @@ extern "C" int fb200_conv2d_rows_tcgen05(const void* x, const void* w, const voi
   g.kp = (g.kw * g.cin + 7) / 8 * 8;
   g.npad = (g.cout + 31) / 32 * 32;
   if (2 * g.npad > 512) return FB200_UNIMPLEMENTED;
+  if (pooled != nullptr) {
+    // both halves of an epilogue group must have a chunk, rows must alternate in parity across images
+    if (g.npad != 64 || g.oh % 2 != 0 || g.oh < 2 || g.ow < 2) return FB200_UNIMPLEMENTED;
+    if ((((g.ow + 2 - 3) / 2 + 1) % 4) != 0 || !aligned16(pooled)) return FB200_UNIMPLEMENTED;   // 16-byte stores of pooled rows
+    g.poh = (g.oh + 2 - 3) / 2 + 1;
+    g.pow = (g.ow + 2 - 3) / 2 + 1;
+  }
   g.tmem_cols = 32;
   while (g.tmem_cols < 2 * g.npad) g.tmem_cols *= 2;
-  g.n_slots = g.kh + 3;
+  g.n_slots = g.kh + 2;
   g.slot_bytes = 4 * g.kp * 128;
   g.w_bytes = g.kh * g.npad * 128;
   g.total_rows = static_cast<int64_t>(g.n) * g.oh;
   const size_t smem = 1024 /*align*/ + static_cast<size_t>(g.n_slots + 1) * g.slot_bytes + g.w_bytes + 128 /*barriers*/ +
-                      1024 /*bias*/ + 4 * 2 * kRowsTasks * kRowsBuilders * 8 /*prefetch*/ + 128;
+                      1024 /*bias*/ + kRowsPfStages * 2 * kRowsTasks * kRowsBuilders * 8 /*prefetch*/ +
+                      (pooled != nullptr ? 16 * 32 * 4 + 2 * g.npad * g.pow * 4 : 0) + 128;
   if (smem > 227 * 1024) return FB200_UNIMPLEMENTED;
   EpilogueDev epi{};
   if (int rc = make_epilogue(epilogue, &epi, "conv2d")) return rc;
+  if (pooled != nullptr) {
+    // chain operands are indexed in the conv result's shape, which is never materialised here:
+    // unary steps only
+    for (int i = 0; i < epi.n_ops; ++i) if (epi.operands[i] != nullptr) return FB200_UNIMPLEMENTED;
+  }
   int* status = nullptr;
   if (int rc = device_status_word(&status)) return rc;
   const uint32_t idesc = make_instr_desc(kFmtTF32, /*a MN-major*/ 1, /*b MN-major*/ 0, 128, static_cast<uint32_t>(g.npad));
-  const int grid = static_cast<int>(g.total_rows < kNumSMs ? g.total_rows : kNumSMs);
+  const int64_t units = pooled != nullptr ? static_cast<int64_t>(g.n) * g.poh : g.total_rows;
+  const int grid = static_cast<int>(units < kNumSMs ? units : kNumSMs);
   auto launch = [&](auto kernel) -> int {
     FB200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     kernel<<<grid, kRowsThreads, smem, as_stream(stream)>>>(
         static_cast<const float*>(x), static_cast<const float*>(w), static_cast<const float*>(bias),
-        static_cast<float*>(out), g, idesc, epi, status);
+        static_cast<float*>(pooled != nullptr ? pooled : out), g, idesc, epi, status);
     return FB200_OK;
   };
   int rc = FB200_UNIMPLEMENTED;
   const int ksteps = g.kp / 8;
-#define FB200_ROWS_CASE(kh_, ks_) if (g.kh == kh_ && ksteps == ks_) rc = launch(conv2d_rows_tcgen05_kernel<kh_, ks_>);
-  FB200_ROWS_CASE(7, 3)   // 7 x 7 over 3 channels (21 -> 24)
-  FB200_ROWS_CASE(7, 1)   // 7 x 7 over 1 channel
-  FB200_ROWS_CASE(5, 2)   // 5 x 5 over 3 channels (15 -> 16)
-  FB200_ROWS_CASE(5, 1)   // 5 x 5 over 1 channel
-  FB200_ROWS_CASE(3, 2)   // 3 x 3 over 3-5 channels
-  FB200_ROWS_CASE(3, 1)   // 3 x 3 over 1-2 channels
-  FB200_ROWS_CASE(3, 3)   // 3 x 3 over 6-8 channels
-  FB200_ROWS_CASE(3, 4)   // 3 x 3 over 9-10 channels
-  FB200_ROWS_CASE(4, 2)   // 4 x 4 over 3-4 channels
+  if (pooled != nullptr) {
+    if (g.kh == 7 && ksteps == 3) rc = launch(conv2d_rows_tcgen05_kernel<7, 3, true>);
+    if (g.kh == 3 && ksteps == 2) rc = launch(conv2d_rows_tcgen05_kernel<3, 2, true>);
+  } else {
+#define FB200_ROWS_CASE(kh_, ks_) if (g.kh == kh_ && ksteps == ks_) rc = launch(conv2d_rows_tcgen05_kernel<kh_, ks_, false>);
+    FB200_ROWS_CASE(7, 3)   // 7 x 7 over 3 channels (21 -> 24)
+    FB200_ROWS_CASE(7, 1)   // 7 x 7 over 1 channel
+    FB200_ROWS_CASE(5, 2)   // 5 x 5 over 3 channels (15 -> 16)
+    FB200_ROWS_CASE(5, 1)   // 5 x 5 over 1 channel
+    FB200_ROWS_CASE(3, 2)   // 3 x 3 over 3-5 channels
+    FB200_ROWS_CASE(3, 1)   // 3 x 3 over 1-2 channels
+    FB200_ROWS_CASE(3, 3)   // 3 x 3 over 6-8 channels
+    FB200_ROWS_CASE(3, 4)   // 3 x 3 over 9-10 channels
+    FB200_ROWS_CASE(4, 2)   // 4 x 4 over 3-4 channels
 #undef FB200_ROWS_CASE
+  }
   if (rc != FB200_OK) return rc;
   return after_launch("conv2d_rows_tcgen05_kernel");
+}
+
+// Returns FB200_UNIMPLEMENTED for shapes outside this kernel's reach (the caller then tries the halo
+// kernel, the gather kernel and the direct kernel).
+extern "C" int fb200_conv2d_rows_tcgen05(const void* x, const void* w, const void* bias, void* out,
+                                         const fb200_conv2d_params* p, int dtype,
+                                         const fb200_epilogue* epilogue, fb200_stream stream) {
+  return rows_launch(x, w, bias, out, nullptr, p, dtype, epilogue, stream);
+}
+
+// conv2d -> [unary chain] -> max_pool2d(3 x 3, stride 2, padding 1) in one launch when the shape
+// allows (FB200_UNIMPLEMENTED otherwise; fb200_conv2d_max_pool then runs the two kernels).
+extern "C" int fb200_conv2d_rows_pooled_tcgen05(const void* x, const void* w, const void* bias, void* pooled,
+                                                const fb200_conv2d_params* p, int dtype,
+                                                const fb200_epilogue* epilogue, fb200_stream stream) {
+  if (pooled == nullptr) return FB200_UNIMPLEMENTED;
+  return rows_launch(x, w, bias, nullptr, pooled, p, dtype, epilogue, stream);
 }

@@ -68,6 +68,8 @@ struct Step {
   int write_slot = -1;                       // where the (possibly fused) result goes
   int split_slot = -1;                       // kMatmul: slot that receives the columns from split_col on
   int64_t split_col = 0;
+  int pool_mid = -1;                         // kConv2d followed by a max_pool2d: the conv's own result slot
+  std::vector<int64_t> pool_iv;              //   and the pool's kernel, stride, padding (write_slot = pool result)
   std::vector<int64_t> iv;                   // op-specific integers
   double eps = 0.0;
   // kAttentionFan: the matrices the heads' q/k/v windows lie in, where the results go, and the
@@ -682,6 +684,43 @@ static void optimise(fb200_plan* p) {
 }
 
 
+// conv2d [+ epilogue] -> max_pool2d becomes one step (fb200_conv2d_max_pool) when the pool is the only
+// reader of the convolution's result and that result is not a graph output.  The call itself
+// decides whether the pair runs as one kernel (an image stem: the pooled rows leave the epilogue and
+// the convolution's result is never written) or as the two kernels through the planned intermediate.
+static void fuse_conv_pool(fb200_plan* p) {
+  const int n = static_cast<int>(p->steps.size());
+  auto runs = [](const Step& s) { return s.kind != Kind::kSkip && s.kind != Kind::kAlias && s.kind != Kind::kConstant; };
+  for (int i = 0; i < n; ++i) {
+    Step& s = p->steps[i];
+    if (s.kind != Kind::kConv2d || s.write_slot < 0 || !s.pool_iv.empty()) continue;
+    const int mid = s.write_slot;
+    if (p->slots[mid].output_index >= 0 || p->slots[mid].dtype != FB200_F32) continue;
+    int j = i + 1;
+    while (j < n && !runs(p->steps[j])) ++j;
+    if (j >= n) continue;
+    Step& t = p->steps[j];
+    if (t.kind != Kind::kMaxPool || t.in.size() != 1 || t.out.size() != 1 || t.in[0] != mid) continue;
+    bool single = true;
+    for (int q = 0; q < n && single; ++q) {
+      if (q == j || !runs(p->steps[q])) continue;
+      for (int in : p->steps[q].in) if (in == mid) single = false;
+      for (int in : p->steps[q].epi_operand_slot) if (in == mid) single = false;
+    }
+    if (!single) continue;
+    // the pooled result must not overlap anything the convolution reads (or its intermediate, which
+    // the two-kernel form still writes)
+    bool overlap = ranges_overlap(*p, t.out[0], mid);
+    for (int in : s.in) if (ranges_overlap(*p, t.out[0], in)) overlap = true;
+    for (int os : s.epi_operand_slot) if (os >= 0 && ranges_overlap(*p, t.out[0], os)) overlap = true;
+    if (overlap) continue;
+    s.pool_mid = mid;
+    s.pool_iv = t.iv;
+    s.write_slot = t.out[0];
+    t.kind = Kind::kSkip;
+  }
+}
+
 static bool step_runs(const Step& s) {
   return s.kind != Kind::kSkip && s.kind != Kind::kAlias && s.kind != Kind::kConstant;
 }
@@ -704,6 +743,7 @@ static bool step_touches(const fb200_plan& p, const Step& s, int slot, int own) 
   for (int x : s.in) if (hit(x)) return true;
   for (int x : s.epi_operand_slot) if (hit(x)) return true;
   if (hit(s.write_slot)) return true;
+  if (hit(s.pool_mid)) return true;
   for (int x : {s.fan_q, s.fan_k, s.fan_v, s.fan_dest, s.dw_x, s.dw_w, s.dw_bias}) if (hit(x)) return true;
   return false;
 }
@@ -1255,6 +1295,12 @@ static int run_step(fb200_plan* p, Step& s, const void* const* inputs, void* con
       q.n = in_slot(0).dims[0]; q.cin = in_slot(0).dims[1]; q.h = in_slot(0).dims[2]; q.w = in_slot(0).dims[3];
       q.cout = in_slot(1).dims[0]; q.kh = in_slot(1).dims[2]; q.kw = in_slot(1).dims[3];
       q.stride_h = s.iv[0]; q.stride_w = s.iv[1]; q.pad_h = s.iv[2]; q.pad_w = s.iv[3]; q.groups = s.iv[4];
+      if (!s.pool_iv.empty()) {
+        return fb200_conv2d_max_pool(in_ptr(0), in_ptr(1), s.in.size() > 2 ? in_ptr(2) : nullptr,
+                                     slot_ptr(p, s.pool_mid, inputs, outputs), out, &q, s.pool_iv[0], s.pool_iv[1],
+                                     s.pool_iv[2], s.pool_iv[3], s.pool_iv[4], s.pool_iv[5], os.dtype, p->allow_tf32,
+                                     epi_ptr, stream);
+      }
       return fb200_conv2d(in_ptr(0), in_ptr(1), s.in.size() > 2 ? in_ptr(2) : nullptr, out, &q,
                           os.dtype, p->allow_tf32, epi_ptr, stream);
     }
@@ -1493,6 +1539,7 @@ static int plan_create_impl(const char* plan_text, int device, int allow_tf32, i
     alias_reshape_sources(p);
     fuse_attention_fans(p);
     fuse_time_major_convs(p);
+    if (p->allow_tf32) fuse_conv_pool(p);
   }
   if (!dry) {
     // the first workspace; further streams get theirs at their first run
@@ -1824,7 +1871,8 @@ extern "C" int fb200_plan_host_sync(fb200_plan* p) {
 }
 
 // Op name of step `index`; a contraction that absorbed a following group reports
-// "matmul+epilogue" / "conv2d+epilogue", a step folded away reports "(absorbed)" or "(alias)".
+// "matmul+epilogue" / "conv2d+epilogue" (+ "+max_pool2d" when the pool behind it was folded in), a
+// step folded away reports "(absorbed)" or "(alias)".
 extern "C" const char* fb200_plan_step_op(const fb200_plan* p, int index) {
   static thread_local std::string name;
   if (p == nullptr || index < 0 || static_cast<size_t>(index) >= p->steps.size()) return "";
@@ -1833,6 +1881,7 @@ extern "C" const char* fb200_plan_step_op(const fb200_plan* p, int index) {
   else if (s.kind == Kind::kAttentionFan) name = "attention_fan";
   else if (s.kind == Kind::kDwConvTimeMajor) name = "dwconv1d_time_major";
   else if (s.kind == Kind::kAlias) name = "(alias)";
+  else if (s.kind == Kind::kConv2d && !s.pool_iv.empty()) name = s.chain_ops.empty() ? "conv2d+max_pool2d" : "conv2d+epilogue+max_pool2d";
   else if ((s.kind == Kind::kMatmul || s.kind == Kind::kConv2d) && !s.chain_ops.empty()) name = s.op + "+epilogue";
   else name = s.op;
   return name.c_str();

@@ -324,6 +324,18 @@ FB200_API int fb200_scatter_add(const void* updates, const void* indices, void* 
 /* max_pool2d: max over valid positions only, first maximum wins
  * (src/backends/cpu/kernels/pool.cpp:187-233; replaces cudnnPoolingForward,
  * src/backends/cuda/kernels/pool.cpp:231). */
+/* conv2d -> [epilogue chain] -> max_pool2d in one call (replaces the reference's three launches for
+ * an image stem: cudnnConvolutionForward + cudnnAddTensor, the activation, cudnnPoolingForward:
+ * src/backends/cuda/kernels/conv.cpp:385-520, pooling.cpp).  With allow_tf32, a 3x3 / stride 2 /
+ * pad 1 pool behind a stride-2 convolution with kw * cin <= 32, 32 < cout <= 64, an even number of
+ * output rows of at most 128 pixels and a chain of unary steps runs as ONE kernel that pools the
+ * rows in its epilogue and never writes the convolution's result; `mid` ([n, cout, oh, ow]) is then
+ * untouched and may be NULL.  Every other case runs fb200_conv2d into `mid` and fb200_max_pool2d. */
+FB200_API int fb200_conv2d_max_pool(const void* x, const void* w, const void* bias, void* mid, void* out,
+                                    const fb200_conv2d_params* params, int64_t pool_kh, int64_t pool_kw,
+                                    int64_t pool_stride_h, int64_t pool_stride_w, int64_t pool_pad_h,
+                                    int64_t pool_pad_w, int dtype, int allow_tf32,
+                                    const fb200_epilogue* epilogue, fb200_stream stream);
 FB200_API int fb200_max_pool2d(const void* x, void* out, int64_t n, int64_t c, int64_t h,
                                int64_t w, int64_t kh, int64_t kw, int64_t stride_h,
                                int64_t stride_w, int64_t pad_h, int64_t pad_w, int dtype,

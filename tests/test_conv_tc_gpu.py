@@ -127,6 +127,58 @@ def test_stride2_stem_fused_relu_and_residual():
     assert ok, (worst, fo.max_err(got, exp))
 
 
+POOL_CASES = [
+    # (x shape, w shape, padding, relu): stride-2 conv followed by max_pool2d(3, 3, stride 2, pad 1)
+    ((4, 3, 224, 224), (64, 3, 7, 7), (3, 3), True),    # 224 pooled rows over 148 CTAs: runs of 1-2 pooled rows
+    ((20, 3, 224, 224), (64, 3, 7, 7), (3, 3), True),   # runs of 7-8 pooled rows that cross image boundaries
+    ((3, 3, 64, 96), (48, 3, 7, 7), (3, 3), False),     # ragged Cout (48 of 64), negative values reach the pool
+    ((2, 4, 40, 48), (40, 4, 3, 3), (1, 1), True),      # 3x3 stem over four channels
+    ((2, 3, 36, 64), (64, 3, 5, 5), (2, 2), True),      # 5x5: not instantiated for the fused form -> two kernels
+]
+
+
+@pytest.mark.parametrize("case", POOL_CASES, ids=lambda c: "x".join(map(str, c[0])) + "_w" + "x".join(map(str, c[1])))
+def test_conv2d_max_pool_fused(case):
+    """conv2d -> [ReLU] -> max_pool2d(3x3, stride 2, pad 1) through fb200_conv2d_max_pool.  Where the
+    shape allows, one kernel pools the rows in its epilogue and the intermediate is never written
+    (checked: the buffer keeps its fill pattern).  |max a_i - max b_i| <= max |a_i - b_i|, so the
+    pooled result must lie within the max-pool of the elementwise TF32 bound."""
+    xs, ws, padding, relu = case
+    rng = np.random.default_rng(31)
+    x = rng.standard_normal(xs).astype(np.float32)
+    w = (rng.standard_normal(ws) * 0.2).astype(np.float32)
+    b = rng.standard_normal(ws[0]).astype(np.float32)
+    n, cin, h, wd = xs
+    cout, _, kh, kw = ws
+    oh = (h + 2 * padding[0] - kh) // 2 + 1
+    ow = (wd + 2 * padding[1] - kw) // 2 + 1
+    poh, pow_ = (oh + 2 - 3) // 2 + 1, (ow + 2 - 3) // 2 + 1
+    dx, dw, db = (capi.DeviceBuffer.from_numpy(t) for t in (x, w, b))
+    fill = np.full((n, cout, oh, ow), 12345.0, np.float32)
+    dmid = capi.DeviceBuffer.from_numpy(fill)
+    dout = capi.DeviceBuffer(n * cout * poh * pow_ * 4)
+    epi = capi.make_epilogue([("relu", None, 0)]) if relu else None
+    p = capi.Conv2dParams(n, cin, h, wd, cout, kh, kw, 2, 2, padding[0], padding[1], 1)
+    before = capi.load().fb200_launch_count()
+    capi.conv2d_max_pool(dx.ptr, dw.ptr, db.ptr, dmid.ptr, dout.ptr, p, (3, 3, 2, 2, 1, 1), capi.F32, True, epi)
+    launches = capi.load().fb200_launch_count() - before
+    capi.synchronize()
+    assert capi.kernel_status(0) == 0
+    got = dout.download(np.float32, (n, cout, poh, pow_))
+    fused = launches == 1
+    assert fused == (kh != 5), launches
+    if fused:
+        assert np.array_equal(dmid.download(np.float32, fill.shape), fill)
+    conv = fo.conv2d(x, w, b, (2, 2), padding, 1, fo.DT_F32)
+    if relu:
+        conv = fo.relu(conv)
+    exp = fo.max_pool2d(conv, (3, 3), (2, 2), (1, 1))
+    mag = fo.conv2d(np.abs(x), np.abs(w), None, (2, 2), padding, 1, fo.DT_F32).astype(np.float64)
+    bound = fo.max_pool2d((mag * 2.0 ** -9 + 1e-5 * np.abs(conv) + 1e-6).astype(np.float32), (3, 3), (2, 2), (1, 1))
+    err = np.abs(got.astype(np.float64) - exp.astype(np.float64))
+    assert np.all(err <= bound), float((err / bound).max())
+
+
 def test_strict_conv2d_stays_bit_identical():
     rng = np.random.default_rng(23)
     x = rng.standard_normal((2, 8, 12, 12)).astype(np.float32)

@@ -143,3 +143,22 @@ def test_mamba_gate_slice_is_written_by_the_projection_itself():
     assert launches == 8 and "reshape" not in live and live.count("slice") == 2
     strict, strict_launches = runtime.describe_plan(text, allow_tf32=False)
     assert strict_launches == 10 and _live(strict).count("slice") == 4
+
+
+def test_stem_conv_and_its_max_pool_become_one_step_when_tf32_is_allowed():
+    """conv2d + bias/ReLU epilogue followed by max_pool2d whose only reader it is: one step
+    (fb200_conv2d_max_pool; on the GPU an image stem then runs as one kernel that never writes the
+    convolution's result).  Strict fp32 keeps the operators apart."""
+    text = runtime.load_plan_text("conv_stack_f32_b32_224")
+    names, launches = runtime.describe_plan(text, allow_tf32=True)
+    running = [n for n in names if not n.startswith("(")]
+    assert running[0] == "conv2d+epilogue+max_pool2d", running
+    assert "max_pool2d" not in running
+    assert launches == 3
+    strict, strict_launches = runtime.describe_plan(text, allow_tf32=False)
+    assert [n for n in strict if not n.startswith("(")][:2] == ["conv2d+epilogue", "max_pool2d"]
+    assert strict_launches == 4
+    # the nn CNN of the reference's own layers (conv -> relu -> 2x2 pool): folded as well; the call
+    # then runs the two kernels, since only the 3x3 / stride-2 pool has a fused kernel
+    cnn, _ = runtime.describe_plan(_golden("nn_cnn_f32_b4_c16_hw32_o32"), allow_tf32=True)
+    assert any(n.startswith("conv2d") and n.endswith("+max_pool2d") for n in cnn), cnn
