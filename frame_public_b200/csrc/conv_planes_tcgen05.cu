@@ -44,7 +44,7 @@ using namespace sm100;
 
 constexpr int kPlTileM = 128;
 constexpr int kPlProducers = 256;
-constexpr int kPlThreads = 448;   // 8 producer warps, 1 MMA warp, 4 epilogue warps, 1 loader warp
+constexpr int kPlThreads = 576;   // 8 producer warps, 1 MMA warp, 4 + 4 epilogue warps (9-12, 14-17), 1 loader warp
 constexpr int kPlMmaWarp = 8;
 constexpr int kPlLoaderWarp = 13;
 constexpr int kPlMaxAcc = 8;
@@ -198,7 +198,7 @@ conv2d_planes_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x,
     mbar_init(w_full, 1);
     for (int a = 0; a < kPlMaxAcc; ++a) {
       mbar_init(tmem_full(a), 1);
-      mbar_init(tmem_empty(a), 4);
+      mbar_init(tmem_empty(a), 8);   // two epilogue warps per TMEM lane quarter, each on half of the channels
     }
     mbar_fence_init();
     tma_prefetch_desc(&tmap_x);
@@ -406,8 +406,10 @@ conv2d_planes_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x,
       if (++set == kPlSets) { set = 0; set_phase ^= 1u; }
     }
   } else {
-    // ---- epilogue warps 9..12: TMEM lane = pixel slot of the tile (row = lane / OWP) ---------------
+    // ---- epilogue warps 9..12 and 14..17: TMEM lane = pixel slot of the tile (row = lane / OWP); the two
+    // warps of a lane quarter split the 32-channel chunks -----------------------------------------------
     const int quarter = warp & 3;
+    const int ehalf = warp > kPlLoaderWarp ? 1 : 0;   // warps 9-12: first half of the 32-channel chunks; 14-17: second
     const int m = quarter * 32 + lane;
     const int pr = m / g.owp;
     const int px = m - pr * g.owp;
@@ -415,6 +417,9 @@ conv2d_planes_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x,
     const int64_t ohow = static_cast<int64_t>(g.oh) * g.ow;
     const bool use_tma_store = g.out_stage_bytes > 0;
     const int tile_px = g.rows * g.ow;
+    const int e_chunks = g.npad / 32;
+    const int ec_begin = ehalf * ((e_chunks + 1) / 2) * 32;
+    const int ec_end = ehalf == 0 ? ((e_chunks + 1) / 2) * 32 : g.npad;
     bool ok = true;
     for (int ti = 0; ti < my_tiles && ok; ++ti) {
       const int acc = ti % apr, round = ti / apr;
@@ -428,7 +433,7 @@ conv2d_planes_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x,
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
                              static_cast<uint32_t>(acc * g.npad);
 #pragma unroll 1
-      for (int c0 = 0; c0 < g.npad; c0 += 32) {
+      for (int c0 = ec_begin; c0 < ec_end; c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(t_row + static_cast<uint32_t>(c0), r);
         tmem_ld_wait();
@@ -490,13 +495,13 @@ conv2d_planes_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_x,
         // the tile is complete in shared memory: one thread hands it to the TMA, which writes the
         // cout x rows runs of ow floats (rows past the image are clipped by the tensor map)
         fence_proxy_async_smem();
-        asm volatile("bar.sync 2, 128;" ::: "memory");   // the four epilogue warps
+        asm volatile("bar.sync 2, 256;" ::: "memory");   // the eight epilogue warps
         if (warp == kPlMmaWarp + 1 && lane == 0) {
           tma_store_4d(&tmap_out, base + ostage_off, 0, oy0, 0, img);
           tma_store_commit();
           tma_store_wait_read<0>();   // the staging tile may be overwritten by the next tile
         }
-        asm volatile("bar.sync 2, 128;" ::: "memory");
+        asm volatile("bar.sync 2, 256;" ::: "memory");
       }
     }
     if (use_tma_store && warp == kPlMmaWarp + 1 && lane == 0) tma_store_wait_all();
