@@ -7,7 +7,7 @@ measured peak (the peaks file at the repository root, when present).
     python -m frame_public_b200.microbench --op gemm --m 4096 --n 4096 --k 4096 --dtype bf16
 
 Ops: fused_add_relu, gelu, silu, softmax, layer_norm, scan_rows, mamba_scan, transpose, slice,
-max_pool, conv1d_depthwise, dwconv_time_major, conv2d_tf32, attention (--batch, --cols = sequence length, --m = model
+max_pool, conv1d_depthwise, dwconv_time_major, conv2d_tf32, conv2d_stem, conv2d_stem_pool, attention (--batch, --cols = sequence length, --m = model
 width), gemm.  Inputs are seeded random data; between timed
 launches nothing is flushed, so choose sizes larger than the 126 MB L2 for HBM figures.  This is
 also the command the ncu captures summarised under profiles/ were taken with.
@@ -144,6 +144,23 @@ def main():
         fn = lambda: capi.conv2d(x.ptr, w.ptr, b.ptr, o.ptr, p, capi.F32, True)
         nbytes = (n * cin * h * h + n * cout * h * h) * 4
         flops = 2.0 * n * cout * h * h * cin * k * k
+    elif a.op in ("conv2d_stem", "conv2d_stem_pool"):
+        # the conv-stack workload's stem: 3 -> 64 channels, 7x7, stride 2, pad 3, + ReLU; _pool adds the
+        # 3x3 / stride-2 max-pool through fb200_conv2d_max_pool (one kernel)
+        n, cin, h, cout, k = a.batch, 3, 224, 64, 7
+        oh, ph = 112, 56
+        x, w, b = _rand((n, cin, h, h), capi.F32, rng), _rand((cout, cin, k, k), capi.F32, rng), _rand((cout,), capi.F32, rng)
+        p = capi.Conv2dParams(n, cin, h, h, cout, k, k, 2, 2, 3, 3, 1)
+        epi = capi.make_epilogue([("relu", None, 0)])
+        if a.op == "conv2d_stem":
+            o = capi.DeviceBuffer(n * cout * oh * oh * 4)
+            fn = lambda: capi.conv2d(x.ptr, w.ptr, b.ptr, o.ptr, p, capi.F32, True, epi)
+            nbytes = (n * cin * h * h + n * cout * oh * oh) * 4
+        else:
+            o = capi.DeviceBuffer(n * cout * ph * ph * 4)
+            fn = lambda: capi.conv2d_max_pool(x.ptr, w.ptr, b.ptr, None, o.ptr, p, (3, 3, 2, 2, 1, 1), capi.F32, True, epi)
+            nbytes = (n * cin * h * h + n * cout * ph * ph) * 4
+        flops = 2.0 * n * cout * oh * oh * cin * k * k
     elif a.op == "attention":
         # the transformer workload's layout: [batch*seq, 3*heads*64] projection, 64-wide heads
         bt, seq, heads = a.batch, a.cols, a.m // 64
