@@ -1083,8 +1083,11 @@ static TileChoice choose_tile(int64_t m, int64_t n, int64_t k, int elt, int part
     const int64_t t2 = ((m + 255) / 256) * ((n + 255) / 256);
     const int64_t waves1 = (tiles(256) + kNumSMs - 1) / kNumSMs, waves2 = (t2 + kNumSMs - 1) / kNumSMs;
     // The exposed epilogue costs about 8-10 K cycles per tile against a gain of 6-11 % of the mainloop:
-    // only worth it from 128 k-blocks per tile on (measured slower at K = 768 and 1536 TF32).
-    if (light && m > 128 && k * elt >= 128 * 128 && t2 >= kNumSMs && 16 * waves2 <= 9 * waves1) return {256, 2};
+    // for 16-bit operands only worth it from 128 k-blocks per tile on (39-68 us against 35-46 us at
+    // K = 1024 bf16); fp32 k-blocks take twice as long per byte of K, and there it pays from K = 768
+    // (32768 x 768 x 1536 TF32: 139 -> 131 us, 32768 x 3072 x 768: 269 -> 259 us).
+    const int64_t min_k_bytes = elt == 4 ? 3072 : 128 * 128;
+    if (light && m > 128 && k * elt >= min_k_bytes && t2 >= kNumSMs && 16 * waves2 <= 9 * waves1) return {256, 2};
     return {256, 1};
   }
   // One wave of 128 x 256 tiles beats two waves of 128 x 128 (4096 x 1024 x 4096 bf16: 39.6 against
