@@ -82,7 +82,7 @@ fused_chain_kernel(ChainDesc d, T* __restrict__ out, int64_t n_vec, int64_t nume
           const float rhs = to_f32(static_cast<const T*>(d.in[d.ext[s]])[i]);
           cur = round_through<T>(ew_binary_any(op, cur, rhs));
         } else {
-          cur = round_through<T>(ew_unary(op, cur));
+          cur = round_through<T>((sizeof(T) == 2 && op == FB200_EW_GELU) ? ew_gelu16(cur) : ew_unary(op, cur));
         }
       }
       out[i] = from_f32<T>(cur);

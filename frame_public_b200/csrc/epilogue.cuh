@@ -50,6 +50,11 @@ inline int make_epilogue(const fb200_epilogue* e, EpilogueDev* out, const char* 
 // One unary step over a register vector, with the op switch hoisted out of the element loop.
 template <typename T, int NV>
 __device__ __forceinline__ void ew_unary_vec(int op, float (&v)[NV]) {
+  if (sizeof(T) == 2 && op == FB200_EW_GELU) {
+#pragma unroll
+    for (int j = 0; j < NV; ++j) v[j] = round_through<T>(ew_gelu16(v[j]));
+    return;
+  }
   switch (op) {
 #define FB200_UNARY_CASE(code)                                                     \
   case code:                                                                       \
