@@ -27,6 +27,10 @@
 namespace fb200 {
 
 constexpr int kMambaThreads = 128;
+// The pipelined kernel's warps never talk to each other, so a CTA is ONE warp: 1536 CTAs of the
+// benchmark shape spread over 148 SMs as 10 or 11 each (four-warp CTAs: 2 or 3 each, i.e. a sixth of
+// the SMs' time idle at the end).
+constexpr int kPipeThreads = 32;
 constexpr int kMambaSteps = 4;  // time steps per iteration
 
 __device__ __forceinline__ float mamba_ex2(float x) {
@@ -188,7 +192,7 @@ __device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b
 // (fma.rn.f32x2 / mul.rn.f32x2): half the issue slots per state update; the exponentials stay
 // one ex2.approx each.
 template <int NS, int LANES, int MODE>
-__global__ void __launch_bounds__(kMambaThreads)
+__global__ void __launch_bounds__(kPipeThreads)
 mamba_scan_pipe_kernel(const float* __restrict__ u, const float* __restrict__ delta,
                        const float* __restrict__ A, const float* __restrict__ B,
                        const float* __restrict__ C, const float* __restrict__ D,
@@ -204,7 +208,7 @@ mamba_scan_pipe_kernel(const float* __restrict__ u, const float* __restrict__ de
   extern __shared__ float4 mamba_smem4[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float* ws = reinterpret_cast<float*>(mamba_smem4) + warp * ST * kStageFloats;
-  const int64_t ch0 = (static_cast<int64_t>(blockIdx.x) * (kMambaThreads / 32) + warp) * CW;
+  const int64_t ch0 = (static_cast<int64_t>(blockIdx.x) * (kPipeThreads / 32) + warp) * CW;
   if (ch0 >= dm) return;                     // whole warp; warps never wait on each other
   const int64_t bidx = blockIdx.y;
   const int64_t chunk = MODE == kScanWhole ? 0 : blockIdx.z;
@@ -380,13 +384,20 @@ extern "C" int fb200_mamba_scan(const void* u, const void* delta, const void* A,
   const float* zp = static_cast<const float*>(z);
   float* yp = static_cast<float*>(y);
   if (!aligned16(B) || !aligned16(C)) return set_error(FB200_INVALID_ARGUMENT, "mamba_scan: B and C must be 16-byte aligned");
-  const int lanes = mamba_lanes(nstate);
+  int lanes = mamba_lanes(nstate);
+  // 16 states: four lanes per channel (four states each) repeat the per-channel work twice as often
+  // (b16: 0.395 against 0.364 ms) but double the warps; taken when that alone fills the GPU and saves
+  // the second pass of the time chunks (b8: 0.227 against 0.279 ms).
+  if (nstate == 16 && dm % 8 == 0) {
+    const int64_t warps2 = batch * (dm / 16), warps4 = batch * (dm / 8);
+    if (warps2 < int64_t(kNumSMs) * 8 && warps4 >= int64_t(kNumSMs) * 8) lanes = 4;
+  }
   const int per_cta = kMambaThreads / lanes;
   dim3 grid(static_cast<unsigned>((dm + per_cta - 1) / per_cta), static_cast<unsigned>(batch));
   const int cw = 32 / lanes;
   const bool piped = dm % cw == 0 && dm % 4 == 0 && aligned16(u) && aligned16(delta) &&
                      (z == nullptr || aligned16(z));
-  if (piped) grid.x = static_cast<unsigned>((dm / cw + kMambaThreads / 32 - 1) / (kMambaThreads / 32));
+  if (piped) grid.x = static_cast<unsigned>((dm / cw + kPipeThreads / 32 - 1) / (kPipeThreads / 32));
   // Time chunks: one pass when batch x channels give every SM at least 8 warps; otherwise enough
   // chunks for about 16 warps per SM, each at least 64 steps long (a multiple of the pipeline tile).
   MambaChunks ck{1, len, nullptr, nullptr};
@@ -415,12 +426,12 @@ extern "C" int fb200_mamba_scan(const void* u, const void* delta, const void* A,
   int rc = FB200_OK;
 #define FB200_MAMBA_PIPE(NS, LN, MODE, GRID)                                                         \
   do {                                                                                               \
-    const size_t smem = size_t(kMambaThreads / 32) * kPipeStages * mamba_pipe_stage_floats<NS, LN>() * 4; \
+    const size_t smem = size_t(kPipeThreads / 32) * kPipeStages * mamba_pipe_stage_floats<NS, LN>() * 4; \
     auto kernel = mamba_scan_pipe_kernel<NS, LN, MODE>;                                              \
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
                                          static_cast<int>(smem));                                    \
     if (e != cudaSuccess) { rc = cuda_error(e, "cudaFuncSetAttribute(mamba_scan)"); break; }         \
-    kernel<<<GRID, kMambaThreads, smem, s>>>(up, dp, Ap, Bp, Cp, Dp, zp, yp, len, dm, ck);           \
+    kernel<<<GRID, kPipeThreads, smem, s>>>(up, dp, Ap, Bp, Cp, Dp, zp, yp, len, dm, ck);            \
     rc = after_launch("mamba_scan_pipe_kernel");                                                     \
   } while (0)
 #define FB200_MAMBA_LAUNCH(NS, LN)                                                                   \
@@ -436,7 +447,9 @@ extern "C" int fb200_mamba_scan(const void* u, const void* delta, const void* A,
       rc = after_launch("mamba_scan_kernel");                                                        \
     }                                                                                                \
   } while (0)
-  if (nstate == 16) {
+  if (nstate == 16 && lanes == 4) {
+    FB200_MAMBA_LAUNCH(16, 4);
+  } else if (nstate == 16) {
     FB200_MAMBA_LAUNCH(16, 2);
   } else if (nstate == 8) {
     FB200_MAMBA_LAUNCH(8, 2);
