@@ -286,3 +286,50 @@ def test_long_k_split_over_the_sms(m, k, n, dt, tf32, chain):
         rtol, atol = 1e-5, 3 * 2.0 ** -23 * (k / 8) * max(scale, 1.0)
     err = np.abs(got32 - exp)
     assert np.all(err <= atol + rtol * np.abs(exp)), (float(err.max()), atol)
+
+
+def test_split_products_on_two_streams_from_two_threads():
+    """Two host threads, each with its own stream, run split products (CTAs of one launch wait for
+    partial tiles of CTAs of the same launch) back to back.  The launches may be resident on the GPU
+    at the same time; ranges are handed out against the order in which CTAs start, so a waiting CTA
+    only ever depends on CTAs that are already running, and each stream has its own partial-tile
+    workspace: every run must give bit for bit what a lone run gives, and no wait may time out."""
+    import threading
+    lib = capi.load()
+    dt = fo.DT_BF16
+    shapes = [(256, 8192, 512), (512, 8192, 1024)]
+    jobs = []
+    for i, (m, k, n) in enumerate(shapes):
+        assert capi.matmul_schedule(m, n, k, capi.BF16)["sk_units"] > 0
+        a, b = _gen(m, k, n, dt, 40 + i)
+        jobs.append((a, b, _run(a, b, dt, False)))
+    errors = []
+
+    def worker(idx):
+        try:
+            a, b, expected = jobs[idx]
+            m, k = a.shape
+            n = b.shape[1]
+            stream = capi.c_void_p()
+            capi.check(lib.fb200_stream_create(0, capi.byref(stream)))
+            da, db = capi.DeviceBuffer.from_numpy(a), capi.DeviceBuffer.from_numpy(b)
+            dc = capi.DeviceBuffer(m * n * 2)
+            for it in range(50):
+                capi.matmul(da.ptr, db.ptr, dc.ptr, m, n, k, dt, False, None, stream)
+                if it % 10 == 9:
+                    capi.synchronize(0, stream)
+                    got = dc.download(capi.NP_STORAGE[dt], (m, n))
+                    if not np.array_equal(got, expected):
+                        errors.append((idx, it))
+                        return
+            capi.synchronize(0, stream)
+        except Exception as e:   # surfaced in the main thread
+            errors.append((idx, repr(e)))
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert capi.kernel_status(0) == 0
+    assert errors == [], errors
