@@ -114,6 +114,7 @@ SIGNATURES = {
     "fb200_scatter_add": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int, c_int, _P]),
     "fb200_softmax": (c_int, [_P, _P, c_int64, c_int64, c_int, _P]),
     "fb200_layer_norm": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_double, c_int, _P]),
+    "fb200_add_layer_norm": (c_int, [_P, _P, _P, _P, _P, _P, c_int64, c_int64, c_double, c_int, _P]),
     "fb200_selective_scan": (c_int, [_P] * 6 + [c_int64, c_int64, c_int, _P]),
     "fb200_selective_scan_noalloc": (c_int, [_P] * 6 + [c_int64, c_int64, c_int, _P]),
     "fb200_dwconv1d_time_major": (c_int, [_P, c_int64, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int64,
@@ -361,6 +362,10 @@ def softmax(x, out, rows, cols, dtype, stream=None):
 
 def layer_norm(x, gamma, beta, out, rows, cols, eps, dtype, stream=None):
     check(load().fb200_layer_norm(x, gamma, beta, out, rows, cols, eps, dtype, stream))
+
+
+def add_layer_norm(x, res, gamma, beta, sum_out, out, rows, cols, eps, dtype, stream=None):
+    check(load().fb200_add_layer_norm(x, res, gamma, beta, sum_out, out, rows, cols, eps, dtype, stream))
 
 
 def selective_scan(x, a, b, c, d, out, rows, steps, dtype, stream=None):

@@ -68,6 +68,7 @@ struct Step {
   int write_slot = -1;                       // where the (possibly fused) result goes
   int split_slot = -1;                       // kMatmul: slot that receives the columns from split_col on
   int64_t split_col = 0;
+  int ln_res = -1, ln_sum = -1;              // kLayerNorm of (in[0] + ln_res): the sum is also stored to ln_sum
   int pool_mid = -1;                         // kConv2d followed by a max_pool2d: the conv's own result slot
   std::vector<int64_t> pool_iv;              //   and the pool's kernel, stride, padding (write_slot = pool result)
   std::vector<int64_t> iv;                   // op-specific integers
@@ -721,6 +722,53 @@ static void fuse_conv_pool(fb200_plan* p) {
   }
 }
 
+// add(a, b) -> layer_norm becomes one step (fb200_add_layer_norm) when the layer_norm is the next
+// step that runs: a transformer block's residual add and the normalisation behind it.  The sum is
+// still stored (the block's second residual reads it); the normalisation works from registers.
+static void fuse_add_layer_norm(fb200_plan* p) {
+  const int n = static_cast<int>(p->steps.size());
+  auto runs = [](const Step& s) { return s.kind != Kind::kSkip && s.kind != Kind::kAlias && s.kind != Kind::kConstant; };
+  for (int i = 0; i < n; ++i) {
+    Step& a = p->steps[i];
+    if (a.kind != Kind::kChain || a.chain_ops.size() != 1 || a.chain_ops[0] != FB200_EW_ADD || a.chain_arity[0] != 2 ||
+        a.in.size() != 2 || a.out.size() != 1 || a.write_slot != a.out[0]) continue;
+    const int sum = a.out[0];
+    int j = i + 1;
+    while (j < n && !runs(p->steps[j])) ++j;
+    if (j >= n) continue;
+    Step& ln = p->steps[j];
+    if (ln.kind != Kind::kLayerNorm || ln.in.size() != 3 || ln.in[0] != sum || ln.ln_res >= 0) continue;
+    const SlotInfo& ss = p->slots[sum];
+    if (ss.dims.size() != 2) continue;
+    bool same = true;
+    for (int in : a.in) same = same && p->slots[in].dims == ss.dims && p->slots[in].dtype == ss.dtype;
+    if (!same) continue;
+    const int out = ln.write_slot;
+    // One kernel reads a, b, gamma, beta and writes the sum and the result.  A warp holds its whole
+    // row of a and b in registers before it writes anything, and touches no other row, so the result
+    // (or the sum) may sit EXACTLY on an addend (same bytes, same row layout: the planner likes to
+    // put the normalised rows where the dead addend was); any other overlap is refused.
+    auto exact = [&](int x, int y) {
+      const SlotInfo& sx = p->slots[root_slot(*p, x)];
+      const SlotInfo& sy = p->slots[root_slot(*p, y)];
+      return sx.arena_offset >= 0 && sx.arena_offset == sy.arena_offset && sx.bytes() == sy.bytes();
+    };
+    bool overlap = ranges_overlap(*p, out, sum);
+    for (int in : a.in) {
+      if (ranges_overlap(*p, out, in) && !exact(out, in)) overlap = true;
+      if (ranges_overlap(*p, sum, in) && !exact(sum, in)) overlap = true;
+    }
+    for (size_t q = 1; q < ln.in.size(); ++q) {
+      if (ranges_overlap(*p, out, ln.in[q]) || ranges_overlap(*p, sum, ln.in[q])) overlap = true;
+    }
+    if (overlap) continue;
+    ln.in[0] = a.in[0];
+    ln.ln_res = a.in[1];
+    ln.ln_sum = sum;
+    a.kind = Kind::kSkip;
+  }
+}
+
 static bool step_runs(const Step& s) {
   return s.kind != Kind::kSkip && s.kind != Kind::kAlias && s.kind != Kind::kConstant;
 }
@@ -744,6 +792,7 @@ static bool step_touches(const fb200_plan& p, const Step& s, int slot, int own) 
   for (int x : s.epi_operand_slot) if (hit(x)) return true;
   if (hit(s.write_slot)) return true;
   if (hit(s.pool_mid)) return true;
+  if (hit(s.ln_res) || hit(s.ln_sum)) return true;
   for (int x : {s.fan_q, s.fan_k, s.fan_v, s.fan_dest, s.dw_x, s.dw_w, s.dw_bias}) if (hit(x)) return true;
   return false;
 }
@@ -1431,6 +1480,11 @@ static int run_step(fb200_plan* p, Step& s, const void* const* inputs, void* con
       return fb200_softmax(in_ptr(0), out, os.dims[0], os.dims[1], os.dtype, stream);
     case Kind::kLayerNorm:
       if (os.dims.size() != 2 || s.in.size() != 3) return set_error(FB200_INVALID_ARGUMENT, "op 'layer_norm' requires rank-2 x, gamma, beta");
+      if (s.ln_res >= 0) {
+        return fb200_add_layer_norm(in_ptr(0), slot_ptr(p, s.ln_res, inputs, outputs), in_ptr(1), in_ptr(2),
+                                    slot_ptr(p, s.ln_sum, inputs, outputs), out, os.dims[0], os.dims[1], s.eps,
+                                    os.dtype, stream);
+      }
       return fb200_layer_norm(in_ptr(0), in_ptr(1), in_ptr(2), out, os.dims[0], os.dims[1], s.eps, os.dtype, stream);
     case Kind::kScan: {
       if (s.in.size() != 5 || os.dims.empty()) return set_error(FB200_INVALID_ARGUMENT, "op 'selective_scan' expects 5 inputs of rank >= 1");
@@ -1540,6 +1594,7 @@ static int plan_create_impl(const char* plan_text, int device, int allow_tf32, i
     fuse_attention_fans(p);
     fuse_time_major_convs(p);
     if (p->allow_tf32) fuse_conv_pool(p);
+    fuse_add_layer_norm(p);
   }
   if (!dry) {
     // the first workspace; further streams get theirs at their first run
@@ -1881,6 +1936,7 @@ extern "C" const char* fb200_plan_step_op(const fb200_plan* p, int index) {
   else if (s.kind == Kind::kAttentionFan) name = "attention_fan";
   else if (s.kind == Kind::kDwConvTimeMajor) name = "dwconv1d_time_major";
   else if (s.kind == Kind::kAlias) name = "(alias)";
+  else if (s.kind == Kind::kLayerNorm && s.ln_res >= 0) name = "add+layer_norm";
   else if (s.kind == Kind::kConv2d && !s.pool_iv.empty()) name = s.chain_ops.empty() ? "conv2d+max_pool2d" : "conv2d+epilogue+max_pool2d";
   else if ((s.kind == Kind::kMatmul || s.kind == Kind::kConv2d) && !s.chain_ops.empty()) name = s.op + "+epilogue";
   else name = s.op;

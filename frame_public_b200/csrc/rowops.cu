@@ -101,9 +101,9 @@ softmax_scalar_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t rows
 
 template <typename T, int NV>
 __global__ void __launch_bounds__(kRowThreads)
-layer_norm_vec_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
-                      const T* __restrict__ beta, T* __restrict__ out, int64_t rows, int64_t cols,
-                      float eps) {
+layer_norm_vec_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ gamma,
+                      const T* __restrict__ beta, T* __restrict__ sum_out, T* __restrict__ out, int64_t rows,
+                      int64_t cols, float eps) {
   constexpr int W = 16 / sizeof(T);
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -120,6 +120,15 @@ layer_norm_vec_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
       const int64_t vi = lane + 32 * i;
       if (vi < n_vec) {
         load_vec<T>(xr + vi * W, v[i]);
+        if (res != nullptr) {
+          // the residual add in front of the normalisation: x + res rounded to T as the separate
+          // `add` would store it, written out for the graph's other readers, normalised from registers
+          float rv[W];
+          load_vec<T>(res + row * cols + vi * W, rv);
+#pragma unroll
+          for (int e = 0; e < W; ++e) v[i][e] = round_through<T>(v[i][e] + rv[e]);
+          store_vec<T>(sum_out + row * cols + vi * W, v[i]);
+        }
 #pragma unroll
         for (int e = 0; e < W; ++e) s += v[i][e];
       }
@@ -215,21 +224,26 @@ static int launch_softmax(const void* x, void* out, int64_t rows, int64_t cols, 
 
 template <typename T>
 static int launch_layer_norm(const void* x, const void* gamma, const void* beta, void* out,
-                             int64_t rows, int64_t cols, float eps, cudaStream_t s) {
+                             int64_t rows, int64_t cols, float eps, cudaStream_t s,
+                             const void* res = nullptr, void* sum_out = nullptr) {
   constexpr int W = 16 / sizeof(T);
   const T* xp = static_cast<const T*>(x);
+  const T* rp = static_cast<const T*>(res);
+  T* sp = static_cast<T*>(sum_out);
   const T* gp = static_cast<const T*>(gamma);
   const T* bp = static_cast<const T*>(beta);
   T* op = static_cast<T*>(out);
   const int grid = grid_for(rows * 32, kRowThreads, 8);
-  const bool al = aligned16(x) && aligned16(out) && aligned16(gamma) && aligned16(beta);
+  const bool al = aligned16(x) && aligned16(out) && aligned16(gamma) && aligned16(beta) &&
+                  (res == nullptr || (aligned16(res) && aligned16(sum_out)));
   const int nv = (cols % W == 0 && al) ? pick_nv<T>(cols) : 0;
+  if (res != nullptr && nv == 0) return FB200_UNIMPLEMENTED;   // the caller runs the two operators
   switch (nv) {
-    case 1: layer_norm_vec_kernel<T, 1><<<grid, kRowThreads, 0, s>>>(xp, gp, bp, op, rows, cols, eps); break;
-    case 2: layer_norm_vec_kernel<T, 2><<<grid, kRowThreads, 0, s>>>(xp, gp, bp, op, rows, cols, eps); break;
-    case 4: layer_norm_vec_kernel<T, 4><<<grid, kRowThreads, 0, s>>>(xp, gp, bp, op, rows, cols, eps); break;
-    case 8: layer_norm_vec_kernel<T, 8><<<grid, kRowThreads, 0, s>>>(xp, gp, bp, op, rows, cols, eps); break;
-    case 16: layer_norm_vec_kernel<T, 16><<<grid, kRowThreads, 0, s>>>(xp, gp, bp, op, rows, cols, eps); break;
+    case 1: layer_norm_vec_kernel<T, 1><<<grid, kRowThreads, 0, s>>>(xp, rp, gp, bp, sp, op, rows, cols, eps); break;
+    case 2: layer_norm_vec_kernel<T, 2><<<grid, kRowThreads, 0, s>>>(xp, rp, gp, bp, sp, op, rows, cols, eps); break;
+    case 4: layer_norm_vec_kernel<T, 4><<<grid, kRowThreads, 0, s>>>(xp, rp, gp, bp, sp, op, rows, cols, eps); break;
+    case 8: layer_norm_vec_kernel<T, 8><<<grid, kRowThreads, 0, s>>>(xp, rp, gp, bp, sp, op, rows, cols, eps); break;
+    case 16: layer_norm_vec_kernel<T, 16><<<grid, kRowThreads, 0, s>>>(xp, rp, gp, bp, sp, op, rows, cols, eps); break;
     default: layer_norm_scalar_kernel<T><<<grid, kRowThreads, 0, s>>>(xp, gp, bp, op, rows, cols, eps); break;
   }
   return after_launch("layer_norm_kernel");
@@ -253,6 +267,33 @@ extern "C" int fb200_softmax(const void* x, void* out, int64_t rows, int64_t col
       return set_error(FB200_INVALID_ARGUMENT,
                        "softmax: dtype code %d is not float32/float16/bfloat16", dtype);
   }
+}
+
+// layer_norm(x + res): the residual add of a transformer block and the normalisation behind it in one
+// pass.  sum_out receives x + res (rounded to the dtype, exactly what a separate add stores), out
+// the normalised rows.  Rows that cannot take the vector path run as the two operators.
+extern "C" int fb200_add_layer_norm(const void* x, const void* res, const void* gamma, const void* beta,
+                                    void* sum_out, void* out, int64_t rows, int64_t cols, double eps,
+                                    int dtype, fb200_stream stream) {
+  if (rows < 0 || cols < 0) return set_error(FB200_INVALID_ARGUMENT, "add_layer_norm: negative shape");
+  if (rows == 0 || cols == 0) return FB200_OK;
+  if (!x || !res || !gamma || !beta || !sum_out || !out) return set_error(FB200_INVALID_ARGUMENT, "add_layer_norm: null argument");
+  cudaStream_t s = as_stream(stream);
+  const float e = static_cast<float>(eps);
+  int rc = FB200_UNIMPLEMENTED;
+  switch (dtype) {
+    case FB200_F32: rc = launch_layer_norm<float>(x, gamma, beta, out, rows, cols, e, s, res, sum_out); break;
+    case FB200_BF16: rc = launch_layer_norm<__nv_bfloat16>(x, gamma, beta, out, rows, cols, e, s, res, sum_out); break;
+    case FB200_F16: rc = launch_layer_norm<__half>(x, gamma, beta, out, rows, cols, e, s, res, sum_out); break;
+    default:
+      return set_error(FB200_INVALID_ARGUMENT, "add_layer_norm: dtype code %d is not float32/float16/bfloat16", dtype);
+  }
+  if (rc != FB200_UNIMPLEMENTED) return rc;
+  const void* ins[2] = {x, res};
+  const int ops[1] = {FB200_EW_ADD};
+  const int arity[1] = {2};
+  if (int rc2 = fb200_fused_elementwise(ins, 2, sum_out, rows * cols, dtype, ops, arity, 1, stream)) return rc2;
+  return fb200_layer_norm(sum_out, gamma, beta, out, rows, cols, eps, dtype, stream);
 }
 
 extern "C" int fb200_layer_norm(const void* x, const void* gamma, const void* beta, void* out,

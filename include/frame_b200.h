@@ -352,6 +352,13 @@ FB200_API int fb200_softmax(const void* x, void* out, int64_t rows, int64_t cols
 FB200_API int fb200_layer_norm(const void* x, const void* gamma, const void* beta, void* out,
                                int64_t rows, int64_t cols, double eps, int dtype,
                                fb200_stream stream);
+/* layer_norm(x + res): a transformer block's residual add and the normalisation behind it in one
+ * pass (the reference runs `add` and `layer_norm` as two launches, src/backends/cuda/kernels/
+ * sequence.cpp).  sum_out receives x + res rounded to the dtype, exactly what the separate add
+ * stores; out the normalised rows.  Shapes outside the vector path run as the two operators. */
+FB200_API int fb200_add_layer_norm(const void* x, const void* res, const void* gamma, const void* beta,
+                                   void* sum_out, void* out, int64_t rows, int64_t cols, double eps,
+                                   int dtype, fb200_stream stream);
 /* selective_scan: per row h_t = a_t*h_{t-1} + b_t*x_t, y_t = c_t*h_t + d_t*x_t, h_{-1} = 0,
  * time on the last axis, fp32 state (src/backends/cpu/kernels/sequence.cpp:95-106; replaces the
  * per-row CUB scans of src/backends/cuda/kernels/sequence.cu:170-217).  One launch. */

@@ -20,12 +20,14 @@ def _live(names):
     return [n for n in names if not n.startswith("(") and n != "constant"]
 
 
-def test_transformer_block_becomes_eight_launches():
+def test_transformer_block_becomes_seven_launches():
     text = runtime.load_plan_text("transformer_bf16_b8_s512_d1024")
     names, launches = runtime.describe_plan(text, opt_level=1)
     assert len(names) == 922
-    assert launches == 8
-    assert _live(names) == ["layer_norm", "matmul", "attention_fan", "matmul", "add", "layer_norm",
+    assert launches == 7
+    # the residual add in front of the second LayerNorm runs inside it (the planner puts the
+    # normalised rows exactly on the dead addend: allowed, a warp holds its row before it writes)
+    assert _live(names) == ["layer_norm", "matmul", "attention_fan", "matmul", "add+layer_norm",
                             "matmul+epilogue", "matmul+epilogue"]
     plain, plain_launches = runtime.describe_plan(text, opt_level=0)
     assert plain.count("softmax") == 128 and plain.count("attention_fan") == 0
