@@ -190,7 +190,12 @@ __device__ __forceinline__ bool split_flag_wait(const int* flag, int* status) {
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
-template <int ELT, int BLOCK_N, int MH = 1, int KB = 128>
+// EG: epilogue groups.  1: eight epilogue warps drain every tile.  2: a second group of eight warps
+// (warps 11-18), each group draining the tiles of ONE of the two TMEM accumulators, so that the
+// epilogue of tile i runs beside that of tile i + 1: for products whose K is so short that the
+// launch IS its epilogue (one 32-column chunk in flight per warp is latency-bound).  The second
+// group's transposition buffers cost a ring stage.
+template <int ELT, int BLOCK_N, int MH = 1, int KB = 128, int EG = 1>
 struct GemmCfg {
   // KB: bytes of K per A row in a ring stage (128, or 64 with the 64-byte swizzle).  What bounds the
   // mainloop is the ring's turnaround (per-role cycle counters, 8192^3 bf16: about 2400 cycles from
@@ -210,7 +215,9 @@ struct GemmCfg {
   static constexpr int kBChunkBytes = kBlockK * 128;
   static constexpr int kBStageBytes = kBChunks * kBChunkBytes;
   static constexpr int kStageBytes = kAStageBytes + kBStageBytes;
-  static constexpr int kStages = (192 * 1024) / kStageBytes > 12 ? 12 : (192 * 1024) / kStageBytes;
+  static constexpr int kRingBytes = (192 - 32 * (EG - 1)) * 1024;
+  static constexpr int kStages = kRingBytes / kStageBytes > 12 ? 12 : kRingBytes / kStageBytes;
+  static constexpr int kThreads = kGemmThreads + (EG - 1) * 256;
   static constexpr int kTmemCols = 2 * BLOCK_N;
   // B operand, MN-major, 128-byte swizzle: 8-row K groups are 1024 bytes apart (SBO); the next
   // 128-byte span along N is one chunk further (LBO).  One MMA covers 32 bytes of K:
@@ -219,7 +226,7 @@ struct GemmCfg {
   // after the ring: 512 bytes of barriers, then one 4 KiB transpose buffer per epilogue warp
   static constexpr int kEpiStageBytes = 32 * 128;
   static constexpr size_t kSmemBytes = size_t(kStages) * kStageBytes + 1024 /*align*/ + 512 /*barriers*/ +
-                                       8 * kEpiStageBytes;
+                                       8 * EG * kEpiStageBytes;
 };
 
 __device__ __forceinline__ void tile_coords(int64_t tile, int64_t tiles_m, int64_t tiles_n, int kGroupM,
@@ -403,15 +410,16 @@ __device__ __forceinline__ void transpose_chunk(const uint32_t (&r)[32], float (
   __syncwarp();   // every lane has read its pieces before the next chunk overwrites the buffer
 }
 
-template <typename T, int ELT, int BLOCK_N, int MH, int KB, int EPI, bool SPLIT>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+template <typename T, int ELT, int BLOCK_N, int MH, int KB, int EPI, bool SPLIT, int EG = 1>
+__global__ void __launch_bounds__(kGemmThreads + (EG - 1) * 256, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_a_lo,
                     const __grid_constant__ CUtensorMap tmap_b_lo, int parts, int b_spans_map, GemmDest dest, int64_t M,
                     int64_t N, int64_t K, uint32_t idesc, EpilogueDev epi, GemmSplit split, int* status) {
-  using Cfg = GemmCfg<ELT, BLOCK_N, MH, KB>;
+  using Cfg = GemmCfg<ELT, BLOCK_N, MH, KB, EG>;
   static_assert(MH == 1 || (MH == 2 && BLOCK_N == 256), "two M halves fill TMEM with one 256 x 256 tile");
+  static_assert(EG == 1 || (MH == 1 && !SPLIT), "a second epilogue group drains the second accumulator");
   static_assert(!SPLIT || MH == 1, "split ranges keep one accumulator per segment");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -576,16 +584,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       }
     }
-  } else if (warp < kGemmBProducerWarp) {
-    // Epilogue warps 2..9; a warp may only touch TMEM lanes 32*(warp%4) .. +31, so two warps share
-    // each lane quarter and split the tile's columns between them.
+  } else {
+    // Epilogue warps 2..9 (and 11..18 with a second group); a warp may only touch TMEM lanes
+    // 32*(warp%4) .. +31, so two warps of a group share each lane quarter and split the tile's columns
+    // between them.
+    const int egroup = warp > kGemmBProducerWarp ? 1 : 0;
+    const int ewarp = egroup == 0 ? warp - 2 : warp - (kGemmBProducerWarp + 1);
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int half = ewarp >> 2;
     // MH = 1: the two warps of a lane quarter split the tile's columns; MH = 2: each drains one of
     // the two accumulators (rows 0-127 / 128-255 of the tile) over all its columns.
     constexpr int kChunksPerWarp = MH == 2 ? BLOCK_N / 32 : BLOCK_N / 64;
-    int acc = MH == 2 ? half : 0;
+    int acc = MH == 2 ? half : (EG == 2 ? egroup : 0);
     uint32_t acc_phase = 0;
+    int seg_index = 0;
     using View = ChunkView<T>;
     constexpr int W = View::W;
     bool vec_n = (N % W == 0) && (dest.ld % W == 0) && (dest.col0 % W == 0);
@@ -593,12 +605,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
     if (dest.tail_ptr != nullptr) {
       vec_n = vec_n && (dest.tail_ld % W == 0) && ((reinterpret_cast<uintptr_t>(dest.tail_ptr) & 15u) == 0);
     }
-    const uint32_t stage_buf = bars + 512u + static_cast<uint32_t>((warp - 2) * Cfg::kEpiStageBytes);
+    const uint32_t stage_buf = bars + 512u + static_cast<uint32_t>((egroup * 8 + ewarp) * Cfg::kEpiStageBytes);
     const int pf_step = prefetch_step<EPI>(epi);
     bool ok = true;
     SegmentWalk<SPLIT> walk(split, k_blocks, rank);
     GemmSegment sg;
     while (ok && walk.next(&sg)) {
+      if (EG == 2 && ((seg_index++ & 1) != egroup)) continue;   // the other group's accumulator
       int64_t tm, tn;
       tile_coords(sg.tile, tiles_m, tiles_n, group_m, &tm, &tn);
       // A segment that starts inside a tile leaves as a partial accumulator; the segment with the
@@ -719,7 +732,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
       tcgen05_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty_bar(acc));
-      if (MH == 2) {
+      if (MH == 2 || EG == 2) {
         acc_phase ^= 1u;
       } else if (++acc == 2) {
         acc = 0;
@@ -978,6 +991,15 @@ static GemmSplit plan_split(int64_t tiles, int64_t k_blocks, int mh) {
   return sp;
 }
 
+// Two epilogue groups pay when the mainloop of a tile is shorter than its epilogue and every SM has
+// several tiles to alternate between.
+// (Measured: dt_proj + bias + softplus, K = 48, 0.101 -> 0.084 ms; at 16 k-blocks, the K = 1024 GEMMs
+// of the transformer block, the lost ring stage costs more than the second group gains: 0.050 ->
+// 0.054 ms.)
+static bool two_epilogue_groups(int64_t tiles, int64_t k_blocks) {
+  return k_blocks <= 4 && tiles >= 2 * kNumSMs;
+}
+
 template <typename T, int ELT, int BLOCK_N, int MH, int KB, int EPI>
 static int launch_tc_epi(const void* a, const void* b, const GemmDest& c, int64_t m, int64_t n, int64_t k,
                          int dtype, const EpilogueDev& epi, cudaStream_t s) {
@@ -1034,10 +1056,23 @@ static int launch_tc_epi(const void* a, const void* b, const GemmDest& c, int64_
       return rc;
     }
   }
+  const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
+  // Products that are all epilogue (a K of a few k-blocks under a wide result: Mamba's dt_proj, K = 48)
+  // take the form with two epilogue groups.
+  if constexpr (MH == 1 && BLOCK_N == 256 && KB == 128 && !std::is_same<T, __half>::value) {
+    if (two_epilogue_groups(tiles, k_blocks)) {
+      using Cfg2 = GemmCfg<ELT, BLOCK_N, MH, KB, 2>;
+      auto kernel2 = gemm_tcgen05_kernel<T, ELT, BLOCK_N, MH, KB, EPI, false, 2>;
+      FB200_CUDA_OK(cudaFuncSetAttribute(kernel2, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(Cfg2::kSmemBytes)));
+      kernel2<<<grid, Cfg2::kThreads, Cfg2::kSmemBytes, s>>>(ta, tb, ta_lo, tb_lo, parts, b_spans_map, c, m, n, k, idesc,
+                                                              epi, split, status);
+      return after_launch("gemm_tcgen05_kernel");
+    }
+  }
   auto kernel = gemm_tcgen05_kernel<T, ELT, BLOCK_N, MH, KB, EPI, false>;
   FB200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(Cfg::kSmemBytes)));
-  const int grid = static_cast<int>(tiles < kNumSMs ? tiles : kNumSMs);
   kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, s>>>(ta, tb, ta_lo, tb_lo, parts, b_spans_map, c, m, n, k, idesc,
                                                       epi, split, status);
   return after_launch("gemm_tcgen05_kernel");

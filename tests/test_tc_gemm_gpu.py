@@ -333,3 +333,32 @@ def test_split_products_on_two_streams_from_two_threads():
         t.join()
     assert capi.kernel_status(0) == 0
     assert errors == [], errors
+
+
+@pytest.mark.parametrize("dt,tf32,k,chain", [(fo.DT_F32, True, 48, "col_softplus"), (fo.DT_BF16, False, 64, None),
+                                               (fo.DT_BF16, False, 200, "residual")],
+                         ids=["tf32_k48_softplus", "bf16_k64", "bf16_k200_residual"])
+def test_short_k_products_with_two_epilogue_groups(dt, tf32, k, chain):
+    """A K of one to four k-blocks under 296+ tiles: the launch is all epilogue and runs with two
+    epilogue groups, one per TMEM accumulator (Mamba's dt_proj: K = 48, bias + softplus).  Ragged M and
+    N; float64 product of the stored operands as the checker."""
+    m, n = 4700, 2056
+    a, b = _gen(m, k, n, dt, 61)
+    rng = np.random.default_rng(62)
+    mm = (fo.to_accum(a, dt).astype(np.float64) @ fo.to_accum(b, dt).astype(np.float64)).astype(np.float32)
+    exp = fo.round_through(mm, dt)
+    steps = None
+    if chain == "col_softplus":
+        col = fo.from_accum(rng.standard_normal(n).astype(np.float32), dt)
+        steps = [("add", col, capi.OPERAND_COL), ("softplus", None, 0)]
+        z = (exp + fo.to_accum(col, dt)[None, :]).astype(np.float64)
+        exp = np.where(z > 20, z, np.log1p(np.exp(np.minimum(z, 20)))).astype(np.float32)
+    elif chain == "residual":
+        resid = fo.from_accum(rng.standard_normal((m, n)).astype(np.float32), dt)
+        steps = [("add", resid, capi.OPERAND_FULL)]
+        exp = fo.round_through(exp + fo.to_accum(resid, dt), dt)
+    got = fo.to_accum(_run(a, b, dt, tf32, steps=steps), dt)
+    scale = np.sqrt(k) * float(np.sqrt((fo.to_accum(a, dt) ** 2).mean()) * np.sqrt((fo.to_accum(b, dt) ** 2).mean()))
+    rtol, atol = (2e-2, 2e-3 * max(scale, 1.0)) if dt == fo.DT_BF16 else (1e-3, 2e-3 * scale)
+    err = np.abs(got - exp)
+    assert np.all(err <= atol + rtol * np.abs(exp)), (float(err.max()), atol)
