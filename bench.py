@@ -610,9 +610,17 @@ def cpu_slab_baseline(wl, gpu_output):
     dtype = wl.full().dtype
     got = slab_rows(wl, gpu_output)
     tol = configs.parity_tolerance(wl.key, dtype, wl.allow_tf32, fo.to_accum(expected, dtype), wl.full().inputs)
-    max_abs, max_rel = fo.max_err(got, expected, dtype)
+    max_abs, _ = fo.max_err(got, expected, dtype)
+    # relative error only where the expected value is above the absolute bound (at an expected value of
+    # zero a ratio says nothing); worst_over_bound is |difference| / (atol + rtol |expected|), at most 1
+    a64 = fo.to_accum(got, dtype).astype(np.float64)
+    e64 = fo.to_accum(expected, dtype).astype(np.float64)
+    diff = np.abs(a64 - e64)
+    big = np.abs(e64) > float(tol["atol"])
+    max_rel = float((diff[big] / np.abs(e64[big])).max(initial=0.0))
+    worst = float((diff / (float(tol["atol"]) + float(tol["rtol"]) * np.abs(e64))).max(initial=0.0))
     parity = {"rows": int(np.prod(expected.shape[:-1])), "elements": int(expected.size), "max_abs": max_abs,
-              "max_rel": max_rel, "rtol": tol["rtol"], "atol": tol["atol"],
+              "max_rel": max_rel, "worst_over_bound": worst, "rtol": tol["rtol"], "atol": tol["atol"],
               "ok": bool(fo.all_close(got, expected, dtype, **tol)),
               "against": "the reference CPU backend on the same seeded inputs, " + what}
     return cpu, parity
