@@ -133,6 +133,7 @@ SIGNATURES = {
     "fb200_plan_num_outputs": (c_int, [_P]),
     "fb200_plan_io_spec": (c_int, [_P, c_int, c_int, _IP, _IP, _I64P]),
     "fb200_plan_arena_bytes": (c_size_t, [_P]),
+    "fb200_plan_private_bytes": (c_size_t, [_P]),
     "fb200_plan_launches_per_run": (c_int, [_P]),
     "fb200_plan_run": (c_int, [_P, _PP, _PP, _P]),
     "fb200_plan_run_host": (c_int, [_P, _PP, _PP, _P]),

@@ -1068,6 +1068,20 @@ static void fuse_attention_fans(fb200_plan* p) {
       e.o_offset = h.dest_row * o_ld + h.dest_col;
       table.push_back(e);
     }
+    // (3) the planner laid the arena out for the unfused graph, in which the source matrices are
+    // dead (sliced into per-head copies) long before the concat's result is written, so it may have
+    // put that result over them.  The launch reads the sources while it writes the result: a result
+    // that overlaps a source moves to a private buffer.
+    const int dest_root = root_slot(*p, first.dest);
+    bool dest_private = false;
+    for (int base : {first.q.base, first.k.base, first.v.base}) {
+      if (ranges_overlap(*p, dest_root, base)) dest_private = true;
+    }
+    if (dest_private) {
+      const SlotInfo& ds = p->slots[static_cast<size_t>(dest_root)];
+      if (ds.input_index >= 0 || ds.output_index >= 0 || ds.constant != nullptr || ds.arena_offset < 0) ok = false;
+      for (int base : {first.q.base, first.k.base, first.v.base}) if (root_slot(*p, base) == dest_root) ok = false;
+    }
     void* dev_table = nullptr;
     if (ok && !p->dry) {
       const size_t bytes = table.size() * sizeof(fb200_attention_head);
@@ -1078,6 +1092,14 @@ static void fuse_attention_fans(fb200_plan* p) {
     if (!ok) { PLAN_TRACE("fan of %zu heads ending at step %d: rejected by the byte-range checks", group.size(), pos); restore(); continue; }
     PLAN_TRACE("fan of %zu heads -> one attention_fan launch at step %d (scale %g)", group.size(), pos, first.scale);
     if (dev_table != nullptr) p->owned.push_back(dev_table);
+    if (dest_private) {
+      SlotInfo& ds = p->slots[static_cast<size_t>(dest_root)];
+      ds.private_index = static_cast<int>(p->private_bytes.size());
+      p->private_bytes.push_back(ds.bytes());
+      ds.arena_offset = -1;
+      PLAN_TRACE("fan at step %d: its result overlapped a source matrix in the arena and moves to a private buffer (%zu bytes)",
+                 pos, ds.bytes());
+    }
     Step& launch = p->steps[static_cast<size_t>(pos)];
     launch.kind = Kind::kAttentionFan;
     launch.fan_q = first.q.base; launch.fan_k = first.k.base; launch.fan_v = first.v.base;
@@ -1650,6 +1672,11 @@ extern "C" int fb200_plan_destroy(fb200_plan* p) {
 extern "C" int fb200_plan_num_inputs(const fb200_plan* p) { return p ? static_cast<int>(p->input_slots.size()) : 0; }
 extern "C" int fb200_plan_num_outputs(const fb200_plan* p) { return p ? static_cast<int>(p->output_slots.size()) : 0; }
 extern "C" size_t fb200_plan_arena_bytes(const fb200_plan* p) { return p ? p->arena_bytes : 0; }
+extern "C" size_t fb200_plan_private_bytes(const fb200_plan* p) {
+  size_t total = 0;
+  if (p) for (size_t b : p->private_bytes) total += b;
+  return total;
+}
 extern "C" int fb200_plan_launches_per_run(const fb200_plan* p) { return p ? p->launches : 0; }
 
 extern "C" int fb200_plan_io_spec(const fb200_plan* p, int is_output, int index, int* dtype,

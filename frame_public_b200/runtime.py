@@ -38,6 +38,18 @@ def describe_plan(plan_text: str, opt_level: int = 1, allow_tf32: bool = False):
         lib.fb200_plan_destroy(h)
 
 
+def plan_private_bytes(plan_text: str, opt_level: int = 1, allow_tf32: bool = False) -> int:
+    """Bytes of private buffers (per stream workspace, beside the arena) the rewrites of a plan
+    ask for; no GPU needed."""
+    lib = capi.load()
+    h = c_void_p()
+    capi.check(lib.fb200_plan_describe(plan_text.encode(), 1 if allow_tf32 else 0, opt_level, byref(h)))
+    try:
+        return int(lib.fb200_plan_private_bytes(h))
+    finally:
+        lib.fb200_plan_destroy(h)
+
+
 class CompiledPlan:
     def __init__(self, plan_text: str, device: int = 0, allow_tf32: bool = False, opt_level: int = 1):
         self.lib = capi.load()
@@ -57,6 +69,10 @@ class CompiledPlan:
     @property
     def arena_bytes(self) -> int:
         return int(self.lib.fb200_plan_arena_bytes(self._h))
+
+    @property
+    def private_bytes(self) -> int:
+        return int(self.lib.fb200_plan_private_bytes(self._h))
 
     @property
     def launches_per_run(self) -> int:

@@ -459,6 +459,11 @@ FB200_API int fb200_plan_num_outputs(const fb200_plan* plan);
 FB200_API int fb200_plan_io_spec(const fb200_plan* plan, int is_output, int index, int* dtype,
                                  int* rank, int64_t* dims);
 FB200_API size_t fb200_plan_arena_bytes(const fb200_plan* plan);
+/* Bytes of the plan's private buffers, per stream workspace, beside the arena: results that a
+ * rewrite moved out of the planner's layout (a matmul's separately stored column block; the result
+ * of an attention fan that the planner, laying out the unfused graph, had put over the fan's own
+ * source matrices).  No counterpart in the reference. */
+FB200_API size_t fb200_plan_private_bytes(const fb200_plan* plan);
 /* Number of kernel launches one run enqueues (after epilogue absorption and aliasing). */
 FB200_API int fb200_plan_launches_per_run(const fb200_plan* plan);
 /* Device pointers in, device pointers out; asynchronous on `stream`.  Every stream that runs the

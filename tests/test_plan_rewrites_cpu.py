@@ -34,6 +34,16 @@ def test_transformer_block_becomes_seven_launches():
     assert plain_launches > 900
 
 
+def test_attention_fan_result_leaves_the_arena_when_the_planner_put_it_over_the_qkv_matrix():
+    """The planner lays the arena out for the unfused graph, where the fused QKV projection is dead
+    (sliced per head) long before the concat of the heads is written; in this plan it put the
+    concat's 8 MiB result 1 MiB into the 24 MiB projection.  The fused launch reads the projection
+    while it writes the result, so the result must move to a private buffer."""
+    text = runtime.load_plan_text("transformer_bf16_b8_s512_d1024")
+    assert runtime.plan_private_bytes(text, opt_level=1) == 8 * 512 * 1024 * 2
+    assert runtime.plan_private_bytes(text, opt_level=0) == 0
+
+
 def test_reference_nn_attention_with_its_scale_mul_is_recognised():
     names, _ = runtime.describe_plan(_golden("nn_transformer_bf16_b2_s128_e128_h2"))
     live = _live(names)
