@@ -7,30 +7,46 @@
 // head h of a table,
 //     S = Q_h K_h^T   (fp32 accumulate, rounded once to T: the first matmul's store; then, when a
 //                     scale other than 1 is given, multiplied by it and rounded to T again: the
-//                     `mul` by a constant of the reference's own attention)
-//     P = softmax(S)  (row max, exp(x - max), sum, e * (1 / sum) in fp32; rounded once to T)
-//     O = P V_h       (fp32 accumulate, rounded once to T)
-// i.e. the same three operators with the same rounding points (matmul:
-// src/backends/cpu/kernels/matmul.cpp:92-131, softmax: src/backends/cpu/kernels/sequence.cpp:114-174);
-// only the order of the fp32 additions differs, as in every tensor-core path.
+//                     `mul` by a constant of the reference's own attention; a power-of-two scale
+//                     of bfloat16 scores is exact and folds into the exponent's multiplier)
+//     e = exp(S - rowmax(S)), l = sum(e) in fp32
+//     O = (round_T(e) V_h) / l   (fp32 accumulate, divided in fp32, rounded once to T)
+// The reference's operators (matmul: src/backends/cpu/kernels/matmul.cpp:92-131, softmax:
+// src/backends/cpu/kernels/sequence.cpp:114-174) round P = e / l to T and then multiply by V; here
+// e is rounded to T and the division by l is applied to the fp32 result of the second product, as
+// fused attention kernels do, which saves a third sweep over the scores.  Both forms carry one
+// rounding to T per probability; they differ by a fraction of that rounding step (about 2^-9
+// relative per probability, averaged over the keys), far inside the tolerance of a chain of three
+// 16-bit operators.  The rounding of S and of O and the order of the row maximum, the exponentials
+// and their fp32 sum are the reference's; the order of the fp32 additions inside the products
+// differs, as in every tensor-core path.
 //
 // Q_h, K_h, V_h are [sq, 64] / [sk, 64] / [sk, 64] windows of row-major matrices (the fused QKV
 // projection), addressed by TMA through (row, column) coordinates, so no slice or transpose is
 // materialised; O_h is written at an element offset of an output matrix with its own row pitch,
 // so a concat can be skipped too.
 //
-// One CTA (256 threads) per (head, block of 128 query rows):
-//   thread 0   TMA loads of Q (16 KiB), K and V (sk x 128 B each, 128-byte swizzle);
-//              tcgen05.mma S[128, sk] = Q K^T into TMEM (N <= 256 per instruction);
-//   all        two threads per query row (= TMEM lane), each on half of the keys: three sweeps
-//              with tcgen05.ld (max; exp and sum, written back with tcgen05.st; normalise), P
-//              written to shared memory as the K-major, 128-byte-swizzled A operand (over K's
-//              bytes);
-//   thread 0   tcgen05.mma O[128, 64] = P V (V is the MN-major B operand straight from TMA);
-//   all        tcgen05.ld O, convert, 128-byte row stores.
-// Shared memory: 16 KiB + sk*256 + sk*128 (208 KiB at sk = 512); TMEM: sk columns (power of two).
+// One CTA per (head, run of 128-row query blocks); K and V of the head are loaded once and stay in
+// shared memory while the CTA walks its query blocks:
+//   warp 16    one elected lane of warp-uniform code: TMA loads (K, V once; Q per block, the next
+//              one as soon as QK^T has read the current one); tcgen05.mma S[128, sk] = Q K^T into
+//              TMEM (N <= 256 per instruction); then, per 64 keys of P that the softmax warps hand
+//              over, tcgen05.mma O[128, 64] += P V (V is the MN-major B operand straight from TMA);
+//   warps 0-15 four threads per query row (= TMEM lane): a sweep with tcgen05.ld over a quarter of
+//              the keys for the row maximum; then one sweep for exp, the row sum and P (16 of every
+//              64 keys per thread), P going in blocks of 64 keys into a ring of four K-major,
+//              128-byte-swizzled A-operand blocks, so that P V of a block runs while the next one is
+//              computed; tcgen05.ld of O, times 1 / l, row stores.
+// S fills TMEM (sk columns), so O accumulates over S's first 64 columns, which the first block of
+// P has consumed before the first P V instruction is issued.  The next query block's scores are
+// issued in two parts: key columns from 64 up as soon as the last block of P has been handed over
+// (all of S has been read by then), the first 64 columns once every thread has read O.
+// Shared memory: Q 16 KiB + K, V sk*128 B each + P ring 64 KiB (212 KiB at sk = 512); TMEM: sk
+// columns (power of two).
 // Algorithmic work per head: 4*sq*sk*64 FLOP; bytes (sq + 2*sk + sq) * 64 * itemsize.
 #include <cuda.h>
+
+#include <cmath>
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -43,7 +59,12 @@ int device_status_word(int** dev_ptr);
 
 using namespace sm100;
 
-constexpr int kAttnThreads = 256;
+constexpr int kAttnParts = 4;           // threads per query row, each on 1/4 of the keys
+constexpr int kAttnSoftmaxThreads = 128 * kAttnParts;
+constexpr int kAttnCtrlWarp = kAttnSoftmaxThreads / 32;
+constexpr int kAttnThreads = kAttnSoftmaxThreads + 32;
+constexpr int kAttnPRing = 4;          // 64-key blocks of P between the softmax warps and P V
+constexpr int kAttnPBlockBytes = 128 * 128;
 constexpr int kAttnBlockM = 128;
 constexpr int kAttnHeadDim = 64;
 constexpr int kAttnMaxKeys = 512;
@@ -55,19 +76,18 @@ enum AttnFault : int {
   kFaultAttnValues = 303,   // V tile never arrived
   kFaultAttnOutput = 304,   // the second tcgen05.mma batch never completed
   kFaultAttnBadHead = 305,  // a column coordinate or output offset is not a multiple of 8 elements
+  kFaultAttnProbs = 306,    // a block of P never arrived, or its ring slot was never released
+  kFaultAttnDrain = 307,    // the softmax warps never finished reading O
 };
 
-__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+__device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16]) {
   asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0],"
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16,"
-      " %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0],"
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
       :
       : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
         "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
-        "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]),
-        "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]),
-        "r"(r[29]), "r"(r[30]), "r"(r[31])
+        "r"(r[15])
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() {
@@ -90,48 +110,63 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// Value of an fp32 score after the first matmul's store to T and the softmax's load of it.  The
-// conversion instructions run on the quarter-rate XU pipe, which exp2 already saturates, so the
-// bfloat16 round-to-nearest-even is done with integer arithmetic instead (finite inputs; a NaN
-// stays a NaN).
+// Values of two fp32 scores after the first matmul's store to T and the softmax's load of them.
+// The packed conversion rounds both to nearest even in one instruction; unpacking a bfloat16 pair
+// is a shift and a mask, so a score costs 1.5 instructions here.
 template <typename T> __device__ __forceinline__ float stored_score(float v) { return round_through<T>(v); }
-template <> __device__ __forceinline__ float stored_score<__nv_bfloat16>(float v) {
-  const uint32_t b = __float_as_uint(v);
-  return __uint_as_float((b + 0x7FFFu + ((b >> 16) & 1u)) & 0xFFFF0000u);
+template <typename T> __device__ __forceinline__ void stored_pair(float& a, float& b) {
+  a = round_through<T>(a);
+  b = round_through<T>(b);
+}
+template <> __device__ __forceinline__ void stored_pair<__nv_bfloat16>(float& a, float& b) {
+  const uint32_t u = pack2<__nv_bfloat16>(a, b);
+  a = __uint_as_float(u << 16);
+  b = __uint_as_float(u & 0xFFFF0000u);
 }
 
-template <typename T>
+template <typename T, bool RESCALE>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attention_fan_kernel(const __grid_constant__ CUtensorMap tmap_q,
                      const __grid_constant__ CUtensorMap tmap_k,
                      const __grid_constant__ CUtensorMap tmap_v,
                      const fb200_attention_head* __restrict__ heads, T* __restrict__ o_base,
-                     int64_t o_ld, int sq, int sk, int q_blocks, uint32_t tmem_cols, uint32_t fmt,
-                     float scale, int* status) {
+                     int64_t o_ld, int sq, int sk, int q_blocks, int blocks_per_cta, int groups,
+                     uint32_t tmem_cols, uint32_t fmt, float scale, int* status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;  // swizzle atoms need 1024-byte alignment
   uint8_t* base_ptr = smem_raw + (base - raw_addr);
   const uint32_t q_s = base;
-  const uint32_t kp_off = kAttnBlockM * 128;                       // K, later P
-  const uint32_t v_off = kp_off + static_cast<uint32_t>(sk) * 256u;
-  const uint32_t bar_off = v_off + static_cast<uint32_t>(sk) * 128u;
-  const uint32_t kp_s = base + kp_off, v_s = base + v_off, bars = base + bar_off;
-  const uint32_t bar_qk = bars, bar_v = bars + 8, bar_s = bars + 16, bar_o = bars + 24;
-  const uint32_t tmem_slot = bars + 32;
-  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + bar_off + 32);
+  const uint32_t k_off = kAttnBlockM * 128;
+  const uint32_t v_off = k_off + static_cast<uint32_t>(sk) * 128u;
+  const uint32_t p_off = v_off + static_cast<uint32_t>(sk) * 128u;
+  const uint32_t bar_off = p_off + kAttnPRing * kAttnPBlockBytes;
+  const uint32_t k_s = base + k_off, v_s = base + v_off, p_s = base + p_off, bars = base + bar_off;
+  const uint32_t bar_q = bars, bar_k = bars + 8, bar_v = bars + 16, bar_s = bars + 24, bar_o = bars + 32;
+  const uint32_t bar_oread = bars + 40, p_full = bars + 48, p_free = bars + 48 + 8 * kAttnPRing;
+  const uint32_t tmem_slot = bars + 48 + 16 * kAttnPRing;
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(base_ptr + bar_off + 48 + 16 * kAttnPRing);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
-  const int head = blockIdx.x / q_blocks;
-  const int qb = blockIdx.x - head * q_blocks;
+  const int head = blockIdx.x / groups;
+  const int blk_begin = (blockIdx.x - head * groups) * blocks_per_cta;
+  const int nb = q_blocks - blk_begin < blocks_per_cta ? q_blocks - blk_begin : blocks_per_cta;
+  const int n_chunks = sk >> 6;   // 64-key blocks of P per query block
   const fb200_attention_head h = heads[head];
 
   if (tid == 0) {
-    mbar_init(bar_qk, 1);
+    mbar_init(bar_q, 1);
+    mbar_init(bar_k, 1);
     mbar_init(bar_v, 1);
     mbar_init(bar_s, 1);
     mbar_init(bar_o, 1);
+    mbar_init(bar_oread, kAttnSoftmaxThreads / 32);
+    for (int i = 0; i < kAttnPRing; ++i) {
+      mbar_init(p_full + 8 * i, kAttnSoftmaxThreads / 32);
+      mbar_init(p_free + 8 * i, 1);
+    }
     mbar_fence_init();
     tma_prefetch_desc(&tmap_q);
     tma_prefetch_desc(&tmap_k);
@@ -152,157 +187,230 @@ attention_fan_kernel(const __grid_constant__ CUtensorMap tmap_q,
   const bool head_ok = ((h.q_col | h.k_col | h.v_col) & 7) == 0 && (h.o_offset & 7) == 0;
   if (!head_ok && tid == 0) *reinterpret_cast<volatile int*>(status) = kFaultAttnBadHead;
 
-  if (tid == 0 && head_ok) {
-    mbar_arrive_expect_tx(bar_qk, kAttnBlockM * 128u + static_cast<uint32_t>(sk) * 128u);
-    tma_load_2d(q_s, &tmap_q, bar_qk, h.q_col, h.q_row + qb * kAttnBlockM);
-    for (int r = 0; r < sk; r += kAttnKvBoxRows) {
-      tma_load_2d(kp_s + static_cast<uint32_t>(r) * 128u, &tmap_k, bar_qk, h.k_col, h.k_row + r);
-    }
-    mbar_arrive_expect_tx(bar_v, static_cast<uint32_t>(sk) * 128u);
-    for (int r = 0; r < sk; r += kAttnKvBoxRows) {
-      tma_load_2d(v_s + static_cast<uint32_t>(r) * 128u, &tmap_v, bar_v, h.v_col, h.v_row + r);
-    }
-    if (mbar_wait(bar_qk, 0, status, kFaultAttnLoad)) {
-      tcgen05_fence_after_sync();
-      // S[128, sk] = Q[128, 64] K[sk, 64]^T: both operands K-major, four 32-byte K steps.
-      for (int n0 = 0; n0 < sk; n0 += 256) {
-        const int n = sk - n0 < 256 ? sk - n0 : 256;
-        const uint32_t idesc = make_instr_desc(fmt, 0, 0, kAttnBlockM, static_cast<uint32_t>(n));
+  if (warp == kAttnCtrlWarp) {
+    // ---- control warp: every copy and every tensor-core instruction, issued by one elected lane
+    // of warp-uniform code (descriptors then stay in uniform registers, which is what keeps the
+    // issue of the small P V instructions cheap) ------------------------------------------------------
+    if (head_ok) {
+      mbar_arrive_expect_tx_elect(bar_k, static_cast<uint32_t>(sk) * 128u);
+      for (int r = 0; r < sk; r += kAttnKvBoxRows) {
+        tma_load_2d_elect(k_s + static_cast<uint32_t>(r) * 128u, &tmap_k, bar_k, h.k_col, h.k_row + r);
+      }
+      mbar_arrive_expect_tx_elect(bar_q, kAttnBlockM * 128u);
+      tma_load_2d_elect(q_s, &tmap_q, bar_q, h.q_col, h.q_row + blk_begin * kAttnBlockM);
+      mbar_arrive_expect_tx_elect(bar_v, static_cast<uint32_t>(sk) * 128u);
+      for (int r = 0; r < sk; r += kAttnKvBoxRows) {
+        tma_load_2d_elect(v_s + static_cast<uint32_t>(r) * 128u, &tmap_v, bar_v, h.v_col, h.v_row + r);
+      }
+      // Descriptors differ only in the start address (bits 0-13, in 16-byte units), so a step is an add.
+      const uint32_t idesc_pv = make_instr_desc(fmt, 0, 1, kAttnBlockM, kAttnHeadDim);
+      const uint64_t q_desc = make_smem_desc_sw128(q_s, 16, 1024);
+      const uint64_t k_desc = make_smem_desc_sw128(k_s, 16, 1024);
+      const uint64_t p_desc = make_smem_desc_sw128(p_s, 16, 1024);
+      const uint64_t v_desc = make_smem_desc(v_s, static_cast<uint32_t>(sk) * 128u, 1024, kLayoutSw128);
+      // S[128, sk] = Q[128, 64] K[sk, 64]^T over key columns [n0, n0 + nn): both operands K-major,
+      // four 32-byte K steps.
+      auto scores = [&](int n0, int nn) {
+        if (nn <= 0) return;
+        const uint32_t idesc = make_instr_desc(fmt, 0, 0, kAttnBlockM, static_cast<uint32_t>(nn));
+        const uint64_t kb_desc = k_desc + static_cast<uint64_t>(n0 * 8);   // n0 rows of 128 bytes
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
-          const uint64_t a_desc = make_smem_desc_sw128(q_s + ks * 32, 16, 1024);
-          const uint64_t b_desc =
-              make_smem_desc_sw128(kp_s + static_cast<uint32_t>(n0) * 128u + ks * 32, 16, 1024);
-          mma_f16(tmem_base + static_cast<uint32_t>(n0), a_desc, b_desc, idesc, ks > 0 ? 1u : 0u);
+          mma_f16_elect(tmem_base + static_cast<uint32_t>(n0), q_desc + ks * 2, kb_desc + ks * 2, idesc,
+                        ks > 0 ? 1u : 0u);
+        }
+      };
+      // O lies over S's first 64 columns, so the next block's scores are issued in two parts: the
+      // columns from 64 up as soon as every softmax warp has handed over its last block of P (it
+      // has then read all of S), the first 64 once O has been read.
+      auto scores_upper = [&] {
+        scores(64, (sk < 256 ? sk : 256) - 64);
+        scores(256, sk - 256);
+      };
+      bool live = mbar_wait_warp(bar_k, 0, status, kFaultAttnLoad) &&
+                  mbar_wait_warp(bar_q, 0, status, kFaultAttnLoad);
+      if (live) {
+        tcgen05_fence_after_sync();
+        scores_upper();
+        scores(0, 64);
+        mma_commit_elect(bar_s);
+      }
+      uint32_t n = 0;   // blocks of P consumed so far: ring slot n % 4, use n / 4
+      for (int b = 0; live && b < nb; ++b) {
+        const uint32_t ph = static_cast<uint32_t>(b & 1);
+        live = mbar_wait_warp(bar_s, ph, status, kFaultAttnScores);
+        if (!live) break;
+        if (b + 1 < nb) {   // Q's bytes are free again: the next block's rows travel under the softmax
+          mbar_arrive_expect_tx_elect(bar_q, kAttnBlockM * 128u);
+          tma_load_2d_elect(q_s, &tmap_q, bar_q, h.q_col, h.q_row + (blk_begin + b + 1) * kAttnBlockM);
+        }
+        if (b == 0) live = mbar_wait_warp(bar_v, 0, status, kFaultAttnValues);
+        // O[128, 64] += P[128, 64 keys] V[64 keys, 64]: A K-major, B MN-major as loaded.
+        uint64_t vb_desc = v_desc;
+        for (int c = 0; live && c < n_chunks; ++c, ++n) {
+          const uint32_t slot = n & (kAttnPRing - 1), use = n / kAttnPRing;
+          live = mbar_wait_warp(p_full + 8 * slot, use & 1u, status, kFaultAttnProbs);
+          if (!live) break;
+          tcgen05_fence_after_sync();
+          const uint64_t pa_desc = p_desc + static_cast<uint64_t>(slot * (kAttnPBlockBytes / 16));
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            mma_f16_elect(tmem_base, pa_desc + ks * 2, vb_desc + ks * 128, idesc_pv, (c > 0 || ks > 0) ? 1u : 0u);
+          }
+          vb_desc += 4 * 128;   // 64 keys = four 2048-byte steps
+          mma_commit_elect(p_free + 8 * slot);
+        }
+        if (!live) break;
+        mma_commit_elect(bar_o);
+        if (b + 1 < nb) {
+          live = mbar_wait_warp(bar_q, static_cast<uint32_t>((b + 1) & 1), status, kFaultAttnLoad);
+          if (!live) break;
+          scores_upper();
+          // every softmax thread has read O of this block
+          live = mbar_wait_warp(bar_oread, ph, status, kFaultAttnDrain);
+          if (!live) break;
+          tcgen05_fence_after_sync();
+          scores(0, 64);
+          mma_commit_elect(bar_s);
         }
       }
-      mma_commit(bar_s);
     }
-  }
-  __syncwarp();
-  bool ok = head_ok && mbar_wait(bar_s, 0, status, kFaultAttnScores);
-  ok = __all_sync(0xffffffffu, ok);
-
-  // Two threads per query row: warp w works on TMEM lanes 32*(w & 3) .. +31 (the only lanes it may
-  // touch) and on the key columns of half w >> 2; row maximum and row sum are exchanged through
-  // shared memory.  Each sweep keeps the next 32-column tcgen05.ld in flight while the current one
-  // is processed.
-  const int quad = warp & 3, half = warp >> 2;
-  const int row_in_tile = quad * 32 + (tid & 31);
-  const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
-  const int c_begin = half * (sk / 2), c_end = c_begin + sk / 2;
-  float* red_max = reinterpret_cast<float*>(base_ptr + bar_off + 64);   // [2][128]
-  float* red_sum = red_max + 2 * kAttnBlockM;
-  auto sweep = [&](auto&& body) {
-    uint32_t ra[32], rb[32];
-    tmem_ld_32x32b_x32(lane_addr + static_cast<uint32_t>(c_begin), ra);
-    for (int c = c_begin; c < c_end; c += 64) {
-      tmem_ld_wait();
-      const bool two = c + 32 < c_end;
-      if (two) tmem_ld_32x32b_x32(lane_addr + static_cast<uint32_t>(c + 32), rb);
-      body(c, ra);
-      if (two) {
-        tmem_ld_wait();
-        if (c + 64 < c_end) tmem_ld_32x32b_x32(lane_addr + static_cast<uint32_t>(c + 64), ra);
-        body(c + 32, rb);
+    __syncwarp();
+  } else {
+    // ---- softmax warps: four threads per query row -----------------------------------------------
+    // Warp w works on TMEM lanes 32*(w & 3) .. +31 (the only lanes it may touch); in the maximum
+    // sweep on the key columns of quarter w >> 2, in the exp sweep on 16 of every 64 keys (a quarter
+    // of each block of P).  Row maximum and row sum are exchanged through shared memory.  Each sweep
+    // keeps the next 16-column tcgen05.ld in flight while the current one is processed.
+    const int quad = warp & 3, part = warp >> 2;
+    const int row_in_tile = quad * 32 + (tid & 31);
+    const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+    const int c_begin = part * (sk / kAttnParts), c_end = c_begin + sk / kAttnParts;
+    float* red_max = reinterpret_cast<float*>(base_ptr + bar_off + 128);   // [parts][128]
+    float* red_sum = red_max + kAttnParts * kAttnBlockM;
+    auto softmax_sync = [] { asm volatile("bar.sync 1, %0;" ::"n"(kAttnSoftmaxThreads) : "memory"); };
+    auto sweep = [&](auto&& body) {
+      uint32_t ra[16], rb[16];
+      tmem_ld_32x32b_x16(lane_addr + static_cast<uint32_t>(c_begin), ra);
+      for (int c = c_begin; c < c_end; c += 32) {
+        tmem_ld_wait(ra);
+        const bool two = c + 16 < c_end;
+        if (two) tmem_ld_32x32b_x16(lane_addr + static_cast<uint32_t>(c + 16), rb);
+        body(c, ra);
+        if (two) {
+          tmem_ld_wait(rb);
+          if (c + 32 < c_end) tmem_ld_32x32b_x16(lane_addr + static_cast<uint32_t>(c + 32), ra);
+          body(c + 16, rb);
+        }
       }
-    }
-  };
-  const bool scaled = scale != 1.0f;
-  float mx = -INFINITY;
-  if (ok) {
-    tcgen05_fence_after_sync();
-    sweep([&](int, uint32_t (&r)[32]) {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-    });
-    mx = stored_score<T>(mx);   // rounding is monotonic: max of the rounded = rounded max
-    // an optional `mul` by a constant between the matmul and the softmax (the reference's own
-    // attention scales there): its result is rounded to T again; a positive scale keeps the maximum
-    if (scaled) mx = stored_score<T>(mx * scale);
-  }
-  red_max[half * kAttnBlockM + row_in_tile] = mx;
-  __syncthreads();
-  mx = fmaxf(red_max[row_in_tile], red_max[kAttnBlockM + row_in_tile]);
-  float sum = 0.0f;
-  if (ok) {
-    const float mx2 = mx * 1.4426950408889634f;
-    sweep([&](int c, uint32_t (&r)[32]) {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        float sc = stored_score<T>(__uint_as_float(r[i]));
-        if (scaled) sc = stored_score<T>(sc * scale);
-        const float e = ex2_approx(fmaf(sc, 1.4426950408889634f, -mx2));
-        sum += e;
-        r[i] = __float_as_uint(e);
-      }
-      tmem_st_32x32b_x32(lane_addr + static_cast<uint32_t>(c), r);
-    });
-    tmem_st_wait();
-  }
-  red_sum[half * kAttnBlockM + row_in_tile] = sum;
-  __syncthreads();
-  sum = red_sum[row_in_tile] + red_sum[kAttnBlockM + row_in_tile];
-  if (ok) {
-    // P in the A-operand layout: blocks of 64 keys (128 bytes per row, 16 KiB per block), the
-    // 16-byte unit index XORed with (row & 7).
-    uint8_t* p_row = base_ptr + kp_off + static_cast<uint32_t>(row_in_tile) * 128u;
+    };
+    // RESCALE: the scaled scores are rounded to T again (the reference's `mul` stores them).  Without
+    // it the scale is 1 or a power of two, the product is exact, and the factor folds into the exp.
+    const float exp_mul = RESCALE ? 1.4426950408889634f : scale * 1.4426950408889634f;
+    uint8_t* p_row = base_ptr + p_off + static_cast<uint32_t>(row_in_tile) * 128u;
     const uint32_t swz = static_cast<uint32_t>(row_in_tile & 7);
-    const float inv = 1.0f / sum;
-    sweep([&](int c, uint32_t (&r)[32]) {
-      uint8_t* blk = p_row + static_cast<uint32_t>(c >> 6) * 16384u;
-      const uint32_t unit0 = static_cast<uint32_t>((c >> 3) & 7);   // 0 or 4
+    const uint32_t unit0 = static_cast<uint32_t>(part * 2);   // this thread's 16-byte units of a P row
+    bool ok = head_ok;   // warp-uniform throughout: every wait below is taken by the warp as one
+    uint32_t n = 0;      // blocks of P produced so far
+    for (int b = 0; b < nb; ++b) {
+      const uint32_t ph = static_cast<uint32_t>(b & 1);
+      ok = ok && mbar_wait_warp(bar_s, ph, status, kFaultAttnScores);
+      float mx = -INFINITY;
+      if (ok) {
+        tcgen05_fence_after_sync();
+        sweep([&](int, uint32_t (&r)[16]) {
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        uint4 v;
-        v.x = pack2<T>(__uint_as_float(r[8 * u + 0]) * inv, __uint_as_float(r[8 * u + 1]) * inv);
-        v.y = pack2<T>(__uint_as_float(r[8 * u + 2]) * inv, __uint_as_float(r[8 * u + 3]) * inv);
-        v.z = pack2<T>(__uint_as_float(r[8 * u + 4]) * inv, __uint_as_float(r[8 * u + 5]) * inv);
-        v.w = pack2<T>(__uint_as_float(r[8 * u + 6]) * inv, __uint_as_float(r[8 * u + 7]) * inv);
-        *reinterpret_cast<uint4*>(blk + (((unit0 + u) ^ swz) << 4)) = v;
+          for (int i = 0; i < 16; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        });
+        mx = stored_score<T>(mx);   // rounding is monotonic: max of the rounded = rounded max
+        // an optional `mul` by a constant between the matmul and the softmax (the reference's own
+        // attention scales there): its result is rounded to T again; a positive scale keeps the maximum
+        mx = RESCALE ? stored_score<T>(mx * scale) : mx * scale;
       }
-    });
-    fence_proxy_async_smem();   // P must be visible to the tensor core's reads
-  }
-  tcgen05_fence_before_sync();
-  __syncthreads();
-
-  if (tid == 0 && ok) {
-    if (mbar_wait(bar_v, 0, status, kFaultAttnValues)) {
-      tcgen05_fence_after_sync();
-      // O[128, 64] = P[128, sk] V[sk, 64]: A K-major (blocks of 64 keys), B MN-major as loaded.
-      const uint32_t idesc = make_instr_desc(fmt, 0, 1, kAttnBlockM, kAttnHeadDim);
-      const int k_steps = sk / 16;
-      for (int kk = 0; kk < k_steps; ++kk) {
-        const uint64_t a_desc = make_smem_desc_sw128(
-            kp_s + static_cast<uint32_t>(kk >> 2) * 16384u + static_cast<uint32_t>(kk & 3) * 32u, 16, 1024);
-        const uint64_t b_desc = make_smem_desc(v_s + static_cast<uint32_t>(kk) * 2048u,
-                                               static_cast<uint32_t>(sk) * 128u, 1024, kLayoutSw128);
-        mma_f16(tmem_base, a_desc, b_desc, idesc, kk > 0 ? 1u : 0u);
-      }
-      mma_commit(bar_o);
-    }
-  }
-  __syncwarp();
-  ok = ok && mbar_wait(bar_o, 0, status, kFaultAttnOutput);
-  ok = __all_sync(0xffffffffu, ok);
-  if (ok) {
-    tcgen05_fence_after_sync();
-    const int row = qb * kAttnBlockM + row_in_tile;
-    const int c = half * 32;   // each half of the warps stores 32 of the 64 columns
-    T* dst = o_base + h.o_offset + static_cast<int64_t>(row) * o_ld + c;
-    uint32_t r[32];
-    tmem_ld_32x32b_x32(lane_addr + static_cast<uint32_t>(c), r);
-    tmem_ld_wait();
-    if (row < sq) {
+      red_max[part * kAttnBlockM + row_in_tile] = mx;
+      softmax_sync();
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        uint4 v;
-        v.x = pack2<T>(__uint_as_float(r[8 * u + 0]), __uint_as_float(r[8 * u + 1]));
-        v.y = pack2<T>(__uint_as_float(r[8 * u + 2]), __uint_as_float(r[8 * u + 3]));
-        v.z = pack2<T>(__uint_as_float(r[8 * u + 4]), __uint_as_float(r[8 * u + 5]));
-        v.w = pack2<T>(__uint_as_float(r[8 * u + 6]), __uint_as_float(r[8 * u + 7]));
-        *reinterpret_cast<uint4*>(dst + 8 * u) = v;
+      for (int i = 0; i < kAttnParts; ++i) mx = fmaxf(mx, red_max[i * kAttnBlockM + row_in_tile]);
+      float sum = 0.0f;
+      if (ok) {
+        // exp, row sum and P in one sweep: P = e rounded to T, in the A-operand layout (a block of 64
+        // keys is 128 rows of 128 bytes, the 16-byte unit index XORed with (row & 7)); this thread
+        // converts keys 16*part .. +15 of every block.  The division by the row sum is applied to O.
+        const float mx2 = mx * 1.4426950408889634f;
+        auto emit = [&](int c, uint32_t (&r)[16]) {
+          // the ring slot's release is polled before the arithmetic, so the answer is there after it
+          const uint32_t slot = (n + c) & (kAttnPRing - 1), use = (n + c) / kAttnPRing;
+          const bool slot_free = use == 0 || mbar_try_wait(p_free + 8 * slot, (use - 1) & 1u);
+#pragma unroll
+          for (int i = 0; i < 16; i += 2) {
+            float s0 = __uint_as_float(r[i]), s1 = __uint_as_float(r[i + 1]);
+            stored_pair<T>(s0, s1);
+            if constexpr (RESCALE) {
+              s0 *= scale;
+              s1 *= scale;
+              stored_pair<T>(s0, s1);
+            }
+            const float e0 = ex2_approx(fmaf(s0, exp_mul, -mx2));
+            const float e1 = ex2_approx(fmaf(s1, exp_mul, -mx2));
+            sum += e0;
+            sum += e1;
+            r[i >> 1] = pack2<T>(e0, e1);
+          }
+          if (!__all_sync(0xffffffffu, slot_free)) ok = mbar_wait_warp(p_free + 8 * slot, (use - 1) & 1u, status, kFaultAttnProbs);
+          if (!ok) return;
+          uint8_t* blk = p_row + slot * kAttnPBlockBytes;
+          *reinterpret_cast<uint4*>(blk + (((unit0 + 0) ^ swz) << 4)) = make_uint4(r[0], r[1], r[2], r[3]);
+          *reinterpret_cast<uint4*>(blk + (((unit0 + 1) ^ swz) << 4)) = make_uint4(r[4], r[5], r[6], r[7]);
+          fence_proxy_async_smem();      // P must be visible to the tensor core's reads
+          tcgen05_fence_before_sync();   // and the loads of these columns ordered before O is written
+          __syncwarp();
+          if ((tid & 31) == 0) mbar_arrive(p_full + 8 * slot);
+        };
+        const uint32_t col0 = lane_addr + static_cast<uint32_t>(part * 16);
+        uint32_t ra[16], rb[16];
+        tmem_ld_32x32b_x16(col0, ra);
+        for (int c = 0; c < n_chunks; c += 2) {
+          tmem_ld_wait(ra);
+          const bool two = c + 1 < n_chunks;
+          if (two) tmem_ld_32x32b_x16(col0 + static_cast<uint32_t>((c + 1) * 64), rb);
+          emit(c, ra);
+          if (two) {
+            tmem_ld_wait(rb);
+            if (c + 2 < n_chunks) tmem_ld_32x32b_x16(col0 + static_cast<uint32_t>((c + 2) * 64), ra);
+            emit(c + 1, rb);
+          }
+        }
+      }
+      red_sum[part * kAttnBlockM + row_in_tile] = sum;
+      softmax_sync();
+      sum = 0.0f;   // the same order in every thread of a row
+#pragma unroll
+      for (int i = 0; i < kAttnParts; ++i) sum += red_sum[i * kAttnBlockM + row_in_tile];
+      const float inv = 1.0f / sum;
+      n += static_cast<uint32_t>(n_chunks);
+      ok = ok && mbar_wait_warp(bar_o, ph, status, kFaultAttnOutput);
+      if (ok) {
+        tcgen05_fence_after_sync();
+        const int row = (blk_begin + b) * kAttnBlockM + row_in_tile;
+        const int c = part * 16;   // each quarter of the warps stores 16 of the 64 columns
+        T* dst = o_base + h.o_offset + static_cast<int64_t>(row) * o_ld + c;
+        uint32_t r[16];
+        tmem_ld_32x32b_x16(lane_addr + static_cast<uint32_t>(c), r);
+        tmem_ld_wait(r);
+        tcgen05_fence_before_sync();
+        __syncwarp();
+        if ((tid & 31) == 0) mbar_arrive(bar_oread);   // the next block's scores may overwrite O now
+        if (row < sq) {
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            uint4 v;
+            v.x = pack2<T>(__uint_as_float(r[8 * u + 0]) * inv, __uint_as_float(r[8 * u + 1]) * inv);
+            v.y = pack2<T>(__uint_as_float(r[8 * u + 2]) * inv, __uint_as_float(r[8 * u + 3]) * inv);
+            v.z = pack2<T>(__uint_as_float(r[8 * u + 4]) * inv, __uint_as_float(r[8 * u + 5]) * inv);
+            v.w = pack2<T>(__uint_as_float(r[8 * u + 6]) * inv, __uint_as_float(r[8 * u + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + 8 * u) = v;
+          }
+        }
       }
     }
   }
@@ -348,7 +456,17 @@ extern "C" int fb200_attention_fan(const void* q_base, int64_t q_rows, int64_t q
                      "attention_fan: bases must be 16-byte aligned and row pitches multiples of 8 elements");
   }
   const int64_t q_blocks = (sq + kAttnBlockM - 1) / kAttnBlockM;
-  if (n_heads * q_blocks > 0x7fffffff) return set_error(FB200_INVALID_ARGUMENT, "attention_fan: too many tiles");
+  // Query blocks per CTA: the run length that minimises (waves of CTAs) x (loading K and V once +
+  // one softmax per block), the load counted as 0.8 of a block; longer runs win ties (less traffic).
+  int64_t per_cta = 1;
+  double best = 0.0;
+  for (int64_t g = 1; g <= q_blocks; ++g) {
+    const int64_t ctas = n_heads * ((q_blocks + g - 1) / g);
+    const double cost = static_cast<double>((ctas + kNumSMs - 1) / kNumSMs) * (0.8 + static_cast<double>(g));
+    if (g == 1 || cost <= best) { best = cost; per_cta = g; }
+  }
+  const int64_t groups = (q_blocks + per_cta - 1) / per_cta;
+  if (n_heads * groups > 0x7fffffff) return set_error(FB200_INVALID_ARGUMENT, "attention_fan: too many tiles");
   CUtensorMap tq, tk, tv;
   if (int rc = make_tmap_2d(&tq, q_base, dtype, q_rows, q_ld, kAttnBlockM, false)) return rc;
   if (int rc = make_tmap_2d(&tk, k_base, dtype, k_rows, k_ld, kAttnKvBoxRows, false)) return rc;
@@ -357,22 +475,33 @@ extern "C" int fb200_attention_fan(const void* q_base, int64_t q_rows, int64_t q
   if (int rc = device_status_word(&status)) return rc;
   uint32_t tmem_cols = 64;
   while (tmem_cols < static_cast<uint32_t>(sk)) tmem_cols *= 2;
-  const size_t smem = kAttnBlockM * 128 + static_cast<size_t>(sk) * 384 + 1024 /*align*/ + 64 /*barriers*/ +
-                      4 * kAttnBlockM * sizeof(float) /*row max and sum exchange*/;
-  const int grid = static_cast<int>(n_heads * q_blocks);
+  const size_t smem = 1024 /*align*/ + kAttnBlockM * 128 + static_cast<size_t>(sk) * 256 +
+                      kAttnPRing * kAttnPBlockBytes + 128 /*barriers*/ +
+                      2 * kAttnParts * kAttnBlockM * sizeof(float) /*row max and sum exchange*/;
+  const int grid = static_cast<int>(n_heads * groups);
   cudaStream_t s = as_stream(stream);
+  // A power-of-two scale multiplies a bfloat16 score exactly, so rounding it again changes nothing.
+  int scale_exp = 0;
+  const bool exact_scale = scale == 1.0f || (dtype == FB200_BF16 && std::frexp(scale, &scale_exp) == 0.5f &&
+                                             scale_exp >= -15 && scale_exp <= 17);
+  auto launch = [&](auto kernel, auto* out, uint32_t fmt) -> int {
+    FB200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    kernel<<<grid, kAttnThreads, smem, s>>>(tq, tk, tv, heads_dev, out, o_ld, static_cast<int>(sq),
+                                            static_cast<int>(sk), static_cast<int>(q_blocks),
+                                            static_cast<int>(per_cta), static_cast<int>(groups), tmem_cols, fmt,
+                                            scale, status);
+    return FB200_OK;
+  };
+  int rc = FB200_OK;
   if (dtype == FB200_BF16) {
-    auto kernel = attention_fan_kernel<__nv_bfloat16>;
-    FB200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    kernel<<<grid, kAttnThreads, smem, s>>>(tq, tk, tv, heads_dev, static_cast<__nv_bfloat16*>(o_base), o_ld,
-                                            static_cast<int>(sq), static_cast<int>(sk),
-                                            static_cast<int>(q_blocks), tmem_cols, kFmtBF16, scale, status);
+    auto* out = static_cast<__nv_bfloat16*>(o_base);
+    rc = exact_scale ? launch(attention_fan_kernel<__nv_bfloat16, false>, out, kFmtBF16)
+                     : launch(attention_fan_kernel<__nv_bfloat16, true>, out, kFmtBF16);
   } else {
-    auto kernel = attention_fan_kernel<__half>;
-    FB200_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-    kernel<<<grid, kAttnThreads, smem, s>>>(tq, tk, tv, heads_dev, static_cast<__half*>(o_base), o_ld,
-                                            static_cast<int>(sq), static_cast<int>(sk),
-                                            static_cast<int>(q_blocks), tmem_cols, kFmtF16, scale, status);
+    auto* out = static_cast<__half*>(o_base);
+    rc = exact_scale ? launch(attention_fan_kernel<__half, false>, out, kFmtF16)
+                     : launch(attention_fan_kernel<__half, true>, out, kFmtF16);
   }
+  if (rc != FB200_OK) return rc;
   return after_launch("attention_fan_kernel");
 }

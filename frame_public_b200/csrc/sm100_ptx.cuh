@@ -224,6 +224,16 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// The same wait with the loaded registers as in/out operands: the compiler sees every use of them
+// as depending on the wait, so no arithmetic on a register can be scheduled ahead of it.
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
+                 "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]),
+                 "+r"(r[14]), "+r"(r[15])
+               :
+               : "memory");
+}
 
 // ---- tcgen05.mma ------------------------------------------------------------------------------
 // D[tmem] (+)= A[smem desc] * B[smem desc]; issued by ONE thread.

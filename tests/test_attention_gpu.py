@@ -59,6 +59,40 @@ def test_fan_over_a_fused_qkv_projection(batch, heads, seq, dt):
         assert fo.all_close(got, exp, dt, **TOL), fo.max_err(got, exp, dt)
 
 
+def test_launches_over_the_same_buffers_are_bit_identical_at_the_transformer_size():
+    """8 sequences x 16 heads x 512 keys (128 CTAs walking four query blocks each): every hand-over
+    inside the kernel is ordered, so repeated launches agree bit for bit."""
+    batch, heads, seq, dt = 8, 16, 512, fo.DT_BF16
+    rng = np.random.default_rng(11)
+    width = heads * 64
+    qkv = _store(rng.uniform(-1, 1, (batch * seq, 3 * width)), dt)
+    table = np.zeros(batch * heads, dtype=capi.HEAD_DTYPE)
+    for b in range(batch):
+        for h in range(heads):
+            table[b * heads + h] = (b * seq, h * 64, b * seq, width + h * 64, b * seq,
+                                    2 * width + h * 64, b * seq * width + h * 64)
+    rows, ld = qkv.shape
+    d_qkv = capi.DeviceBuffer.from_numpy(qkv)
+    d_tab = capi.DeviceBuffer.from_numpy(table.view(np.uint8))
+    d_out = capi.DeviceBuffer(rows * width * 2)
+    first = None
+    for i in range(6):
+        capi.attention_fan(d_qkv.ptr, rows, ld, d_qkv.ptr, rows, ld, d_qkv.ptr, rows, ld, d_out.ptr,
+                           width, d_tab.ptr, len(table), seq, seq, 64, dt, scale=0.125)
+        capi.synchronize()
+        assert capi.kernel_status(0) == 0
+        got = d_out.download(np.uint16, (rows, width))
+        if first is None:
+            first = got
+            # one head against the oracle
+            q, k, v = qkv[:seq, :64], qkv[:seq, width:width + 64], qkv[:seq, 2 * width:2 * width + 64]
+            const = _store(np.full((seq, seq), 0.125, dtype=np.float32), dt)
+            exp = fo.matmul(fo.softmax(fo.mul(fo.matmul(q, np.ascontiguousarray(k.T), dt), const, dt), dt), v, dt)
+            assert fo.all_close(got[:seq, :64], exp, dt, **TOL), fo.max_err(got[:seq, :64], exp, dt)
+        else:
+            assert np.array_equal(first, got), (i, int((first != got).sum()))
+
+
 @pytest.mark.parametrize("scale", [0.125, 0.3])
 def test_scores_scaled_by_a_constant_before_the_softmax(scale):
     """The reference's own attention multiplies the scores by a constant tensor filled with
