@@ -382,13 +382,17 @@ FB200_API int fb200_selective_scan_noalloc(const void* x, const void* a, const v
 /* A fan of per-head attention chains in one launch.  Stands behind the per-(batch, head) node
  * groups `matmul(q, transpose(k)) -> softmax -> matmul(p, v)` that the reference builds in
  * nn::MultiHeadAttention (src/nn/layers.cpp:950-1170) and runs node by node
- * (src/backends/cuda/cuda_executable.cpp:84-118); each of the three results is rounded to the
- * storage dtype exactly where the separate operators would round it.  For head h:
+ * (src/backends/cuda/cuda_executable.cpp:84-118).  The scores and the result are rounded to the
+ * storage dtype where the separate operators round them; the probabilities are rounded before the
+ * division by their row sum, which is applied in fp32 to the second product (the separate softmax
+ * rounds the quotient): one rounding per probability either way.  O_h must not overlap any Q, K
+ * or V window that another head or query block still reads.  For head h:
  *   Q_h = sq x 64 window of q_base (row-major, q_rows x q_ld) at (q_row, q_col); K_h, V_h likewise
  *   with sk rows; O_h (sq x 64, row pitch o_ld) is written at element offset o_offset of o_base.
  * `scale` (> 0; 1 = none) stands for the elementwise `mul` by a constant that the reference's
  * attention puts between the first matmul and the softmax (src/nn/layers.cpp:1062-1071): the
- * rounded scores are multiplied by it and rounded to the storage dtype again.
+ * rounded scores are multiplied by it and rounded to the storage dtype again (a power of two
+ * multiplies bfloat16 scores exactly and is folded into the exponent instead).
  * Column coordinates must be multiples of 8 elements (a table entry that is not is refused by
  * the kernel, which records status 305).  `heads_dev` is a DEVICE array owned by the caller.
  * Supported: bfloat16 / float16, head_dim 64, 64 <= sk <= 512 in multiples of 64, any sq >= 1
