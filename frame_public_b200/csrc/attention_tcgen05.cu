@@ -144,9 +144,10 @@ attention_fan_kernel(const __grid_constant__ CUtensorMap tmap_q,
   const uint32_t k_s = base + k_off, v_s = base + v_off, p_s = base + p_off, bars = base + bar_off;
   const uint32_t bar_q = bars, bar_k = bars + 8, bar_v = bars + 16, bar_s = bars + 24, bar_o = bars + 32;
   const uint32_t bar_oread = bars + 40, p_full = bars + 48, p_free = bars + 48 + 8 * kAttnPRing;
-  const uint32_t tmem_slot = bars + 48 + 16 * kAttnPRing;
+  const uint32_t bar_su = bars + 48 + 16 * kAttnPRing;
+  const uint32_t tmem_slot = bar_su + 8;
   volatile uint32_t* tmem_slot_ptr =
-      reinterpret_cast<volatile uint32_t*>(base_ptr + bar_off + 48 + 16 * kAttnPRing);
+      reinterpret_cast<volatile uint32_t*>(base_ptr + bar_off + 56 + 16 * kAttnPRing);
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -161,6 +162,7 @@ attention_fan_kernel(const __grid_constant__ CUtensorMap tmap_q,
     mbar_init(bar_k, 1);
     mbar_init(bar_v, 1);
     mbar_init(bar_s, 1);
+    mbar_init(bar_su, 1);
     mbar_init(bar_o, 1);
     mbar_init(bar_oread, kAttnSoftmaxThreads / 32);
     for (int i = 0; i < kAttnPRing; ++i) {
@@ -226,6 +228,7 @@ attention_fan_kernel(const __grid_constant__ CUtensorMap tmap_q,
       auto scores_upper = [&] {
         scores(64, (sk < 256 ? sk : 256) - 64);
         scores(256, sk - 256);
+        mma_commit_elect(bar_su);   // the row-maximum sweep starts on these columns
       };
       bool live = mbar_wait_warp(bar_k, 0, status, kFaultAttnLoad) &&
                   mbar_wait_warp(bar_q, 0, status, kFaultAttnLoad);
@@ -278,32 +281,17 @@ attention_fan_kernel(const __grid_constant__ CUtensorMap tmap_q,
     __syncwarp();
   } else {
     // ---- softmax warps: four threads per query row -----------------------------------------------
-    // Warp w works on TMEM lanes 32*(w & 3) .. +31 (the only lanes it may touch); in the maximum
-    // sweep on the key columns of quarter w >> 2, in the exp sweep on 16 of every 64 keys (a quarter
-    // of each block of P).  Row maximum and row sum are exchanged through shared memory.  Each sweep
-    // keeps the next 16-column tcgen05.ld in flight while the current one is processed.
+    // Warp w works on TMEM lanes 32*(w & 3) .. +31 (the only lanes it may touch), on 16 of every 64
+    // keys (a quarter of each block of P).  Row maximum and row sum are exchanged through shared
+    // memory.  Each sweep keeps the next 16-column tcgen05.ld in flight while the current one is
+    // processed.
     const int quad = warp & 3, part = warp >> 2;
     const int row_in_tile = quad * 32 + (tid & 31);
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
-    const int c_begin = part * (sk / kAttnParts), c_end = c_begin + sk / kAttnParts;
     float* red_max = reinterpret_cast<float*>(base_ptr + bar_off + 128);   // [parts][128]
     float* red_sum = red_max + kAttnParts * kAttnBlockM;
     auto softmax_sync = [] { asm volatile("bar.sync 1, %0;" ::"n"(kAttnSoftmaxThreads) : "memory"); };
-    auto sweep = [&](auto&& body) {
-      uint32_t ra[16], rb[16];
-      tmem_ld_32x32b_x16(lane_addr + static_cast<uint32_t>(c_begin), ra);
-      for (int c = c_begin; c < c_end; c += 32) {
-        tmem_ld_wait(ra);
-        const bool two = c + 16 < c_end;
-        if (two) tmem_ld_32x32b_x16(lane_addr + static_cast<uint32_t>(c + 16), rb);
-        body(c, ra);
-        if (two) {
-          tmem_ld_wait(rb);
-          if (c + 32 < c_end) tmem_ld_32x32b_x16(lane_addr + static_cast<uint32_t>(c + 32), ra);
-          body(c + 16, rb);
-        }
-      }
-    };
+    const uint32_t col0 = lane_addr + static_cast<uint32_t>(part * 16);   // this thread's 16 of every 64 keys
     // RESCALE: the scaled scores are rounded to T again (the reference's `mul` stores them).  Without
     // it the scale is 1 or a power of two, the product is exact, and the factor folds into the exp.
     const float exp_mul = RESCALE ? 1.4426950408889634f : scale * 1.4426950408889634f;
@@ -314,14 +302,37 @@ attention_fan_kernel(const __grid_constant__ CUtensorMap tmap_q,
     uint32_t n = 0;      // blocks of P produced so far
     for (int b = 0; b < nb; ++b) {
       const uint32_t ph = static_cast<uint32_t>(b & 1);
-      ok = ok && mbar_wait_warp(bar_s, ph, status, kFaultAttnScores);
+      // Row maximum: the key columns from 64 up as soon as they are there, the first 64 (which wait
+      // for the previous block's O to be read) after them.
       float mx = -INFINITY;
+      auto max16 = [&](const uint32_t (&r)[16]) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+      };
+      ok = ok && mbar_wait_warp(bar_su, ph, status, kFaultAttnScores);
+      if (ok && n_chunks > 1) {
+        tcgen05_fence_after_sync();
+        uint32_t ra[16], rb[16];
+        tmem_ld_32x32b_x16(col0 + 64u, ra);
+        for (int c = 1; c < n_chunks; c += 2) {
+          tmem_ld_wait(ra);
+          const bool two = c + 1 < n_chunks;
+          if (two) tmem_ld_32x32b_x16(col0 + static_cast<uint32_t>((c + 1) * 64), rb);
+          max16(ra);
+          if (two) {
+            tmem_ld_wait(rb);
+            if (c + 2 < n_chunks) tmem_ld_32x32b_x16(col0 + static_cast<uint32_t>((c + 2) * 64), ra);
+            max16(rb);
+          }
+        }
+      }
+      ok = ok && mbar_wait_warp(bar_s, ph, status, kFaultAttnScores);
       if (ok) {
         tcgen05_fence_after_sync();
-        sweep([&](int, uint32_t (&r)[16]) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
-        });
+        uint32_t r0[16];
+        tmem_ld_32x32b_x16(col0, r0);
+        tmem_ld_wait(r0);
+        max16(r0);
         mx = stored_score<T>(mx);   // rounding is monotonic: max of the rounded = rounded max
         // an optional `mul` by a constant between the matmul and the softmax (the reference's own
         // attention scales there): its result is rounded to T again; a positive scale keeps the maximum
@@ -366,7 +377,6 @@ attention_fan_kernel(const __grid_constant__ CUtensorMap tmap_q,
           __syncwarp();
           if ((tid & 31) == 0) mbar_arrive(p_full + 8 * slot);
         };
-        const uint32_t col0 = lane_addr + static_cast<uint32_t>(part * 16);
         uint32_t ra[16], rb[16];
         tmem_ld_32x32b_x16(col0, ra);
         for (int c = 0; c < n_chunks; c += 2) {
