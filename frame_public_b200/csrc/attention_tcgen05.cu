@@ -348,6 +348,8 @@ attention_fan_kernel(const __grid_constant__ CUtensorMap tmap_q,
         // keys is 128 rows of 128 bytes, the 16-byte unit index XORed with (row & 7)); this thread
         // converts keys 16*part .. +15 of every block.  The division by the row sum is applied to O.
         const float mx2 = mx * 1.4426950408889634f;
+        const float2 mul2 = make_float2(exp_mul, exp_mul), nmx2 = make_float2(-mx2, -mx2);
+        float2 sum2 = make_float2(0.0f, 0.0f);
         auto emit = [&](int c, uint32_t (&r)[16]) {
           // the ring slot's release is polled before the arithmetic, so the answer is there after it
           const uint32_t slot = (n + c) & (kAttnPRing - 1), use = (n + c) / kAttnPRing;
@@ -361,10 +363,10 @@ attention_fan_kernel(const __grid_constant__ CUtensorMap tmap_q,
               s1 *= scale;
               stored_pair<T>(s0, s1);
             }
-            const float e0 = ex2_approx(fmaf(s0, exp_mul, -mx2));
-            const float e1 = ex2_approx(fmaf(s1, exp_mul, -mx2));
-            sum += e0;
-            sum += e1;
+            // packed fp32 pairs: one FMA-pipe instruction per two scores for the exponent and the sum
+            const float2 x = __ffma2_rn(make_float2(s0, s1), mul2, nmx2);
+            const float e0 = ex2_approx(x.x), e1 = ex2_approx(x.y);
+            sum2 = __fadd2_rn(sum2, make_float2(e0, e1));
             r[i >> 1] = pack2<T>(e0, e1);
           }
           if (!__all_sync(0xffffffffu, slot_free)) ok = mbar_wait_warp(p_free + 8 * slot, (use - 1) & 1u, status, kFaultAttnProbs);
@@ -390,6 +392,7 @@ attention_fan_kernel(const __grid_constant__ CUtensorMap tmap_q,
             emit(c + 1, rb);
           }
         }
+        sum = sum2.x + sum2.y;
       }
       red_sum[part * kAttnBlockM + row_in_tile] = sum;
       softmax_sync();
