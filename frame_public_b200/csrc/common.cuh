@@ -145,6 +145,31 @@ __device__ __forceinline__ float ew_gelu16(float x) {
   return x * r;
 }
 
+// The same form on two elements at once: packed fp32 pairs take one FMA-pipe instruction per two
+// elements (five per pair instead of ten); the operations and their rounding are those of ew_gelu16.
+__device__ __forceinline__ float2 ew_gelu16_pair(float2 x) {
+  constexpr float k1 = -2.0f * 0.7978845608028654f * 1.4426950408889634f;
+  constexpr float k2 = k1 * 0.044715f;
+  const float2 z = __fmul2_rn(x, __ffma2_rn(make_float2(k2, k2), __fmul2_rn(x, x), make_float2(k1, k1)));
+  float2 e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.x) : "f"(z.x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.y) : "f"(z.y));
+  const float2 d = __fadd2_rn(make_float2(1.0f, 1.0f), e);
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r.x) : "f"(d.x));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r.y) : "f"(d.y));
+  return __fmul2_rn(x, r);
+}
+// Two values after a store to T and a load back.  For bfloat16 the packed conversion rounds both in
+// one instruction and a shift and a mask bring them back.
+template <typename T> __device__ __forceinline__ float2 round_pair_through(float2 v) {
+  return make_float2(round_through<T>(v.x), round_through<T>(v.y));
+}
+template <> __device__ __forceinline__ float2 round_pair_through<__nv_bfloat16>(float2 v) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(v.x, v.y);
+  const uint32_t u = *reinterpret_cast<const uint32_t*>(&h);
+  return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xFFFF0000u));
+}
+
 __device__ __forceinline__ float ew_unary(int op, float x) {
   switch (op) {
     case FB200_EW_RELU: return x < 0.0f ? 0.0f : x;  // std::max(x, 0.f): NaN and -0 pass through

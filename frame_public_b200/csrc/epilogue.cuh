@@ -51,8 +51,17 @@ inline int make_epilogue(const fb200_epilogue* e, EpilogueDev* out, const char* 
 template <typename T, int NV>
 __device__ __forceinline__ void ew_unary_vec(int op, float (&v)[NV]) {
   if (sizeof(T) == 2 && op == FB200_EW_GELU) {
+    if constexpr (NV % 2 == 0) {
 #pragma unroll
-    for (int j = 0; j < NV; ++j) v[j] = round_through<T>(ew_gelu16(v[j]));
+      for (int j = 0; j < NV; j += 2) {
+        const float2 y = round_pair_through<T>(ew_gelu16_pair(make_float2(v[j], v[j + 1])));
+        v[j] = y.x;
+        v[j + 1] = y.y;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < NV; ++j) v[j] = round_through<T>(ew_gelu16(v[j]));
+    }
     return;
   }
   switch (op) {

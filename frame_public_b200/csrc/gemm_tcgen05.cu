@@ -401,10 +401,12 @@ __device__ __forceinline__ void transpose_chunk(const uint32_t (&r)[32], float (
       const uint32_t addr = stage + static_cast<uint32_t>(row * 128 + (((piece0 + h) ^ (row & 7)) << 4));
       uint32_t a, b, c, d;
       asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr) : "memory");
-      v[j * W + 4 * h + 0] = round_through<T>(__uint_as_float(a));
-      v[j * W + 4 * h + 1] = round_through<T>(__uint_as_float(b));
-      v[j * W + 4 * h + 2] = round_through<T>(__uint_as_float(c));
-      v[j * W + 4 * h + 3] = round_through<T>(__uint_as_float(d));
+      const float2 lo = round_pair_through<T>(make_float2(__uint_as_float(a), __uint_as_float(b)));
+      const float2 hi = round_pair_through<T>(make_float2(__uint_as_float(c), __uint_as_float(d)));
+      v[j * W + 4 * h + 0] = lo.x;
+      v[j * W + 4 * h + 1] = lo.y;
+      v[j * W + 4 * h + 2] = hi.x;
+      v[j * W + 4 * h + 3] = hi.y;
     }
   }
   __syncwarp();   // every lane has read its pieces before the next chunk overwrites the buffer
