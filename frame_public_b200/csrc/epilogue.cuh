@@ -47,6 +47,25 @@ inline int make_epilogue(const fb200_epilogue* e, EpilogueDev* out, const char* 
   return FB200_OK;
 }
 
+// One binary step over W values, the result rounded through T.  Sums and products of 16-bit
+// tensors go in packed fp32 pairs (one FMA-pipe instruction and one packed conversion per two
+// elements); the arithmetic and its rounding are those of the element-wise form.
+template <typename T, int W>
+__device__ __forceinline__ void ew_binary_round_vec(int op, float* v, const float (&rhs)[W]) {
+  if (sizeof(T) == 2 && W % 2 == 0 && (op == FB200_EW_ADD || op == FB200_EW_MUL)) {
+#pragma unroll
+    for (int e = 0; e < W; e += 2) {
+      const float2 a = make_float2(v[e], v[e + 1]), b = make_float2(rhs[e], rhs[e + 1]);
+      const float2 y = round_pair_through<T>(op == FB200_EW_ADD ? __fadd2_rn(a, b) : __fmul2_rn(a, b));
+      v[e] = y.x;
+      v[e + 1] = y.y;
+    }
+    return;
+  }
+#pragma unroll
+  for (int e = 0; e < W; ++e) v[e] = round_through<T>(ew_binary(op, v[e], rhs[e]));
+}
+
 // One unary step over a register vector, with the op switch hoisted out of the element loop.
 template <typename T, int NV>
 __device__ __forceinline__ void ew_unary_vec(int op, float (&v)[NV]) {

@@ -318,10 +318,7 @@ __device__ __forceinline__ void chain_step(int op, int mode, const void* operand
       for (int e = 0; e < W; ++e) rhs[e] = g.col + e < g.N ? to_f32(opnd[g.col + e]) : 0.0f;
     }
 #pragma unroll
-    for (int j = 0; j < P; ++j) {
-#pragma unroll
-      for (int e = 0; e < W; ++e) v[j * W + e] = round_through<T>(ew_binary(op, v[j * W + e], rhs[e]));
-    }
+    for (int j = 0; j < P; ++j) ew_binary_round_vec<T, W>(op, &v[j * W], rhs);
     return;
   }
   const bool vec = g.vec && (reinterpret_cast<uintptr_t>(opnd) & 15u) == 0;
@@ -340,8 +337,7 @@ __device__ __forceinline__ void chain_step(int op, int mode, const void* operand
 #pragma unroll
       for (int e = 0; e < W; ++e) rhs[e] = g.col + e < g.N ? to_f32(src[e]) : 0.0f;
     }
-#pragma unroll
-    for (int e = 0; e < W; ++e) v[j * W + e] = round_through<T>(ew_binary(op, v[j * W + e], rhs[e]));
+    ew_binary_round_vec<T, W>(op, &v[j * W], rhs);
   }
 }
 
