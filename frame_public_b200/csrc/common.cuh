@@ -159,6 +159,20 @@ __device__ __forceinline__ float2 ew_gelu16_pair(float2 x) {
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r.y) : "f"(d.y));
   return __fmul2_rn(x, r);
 }
+// sigmoid and SiLU for 16-bit results on two elements at once: 1 / (1 + 2^(-x log2 e)) through ex2
+// and rcp, about 1e-6 relative, far inside bf16 / f16 (fp32 tensors keep the two-branch form).
+// Large negative x: e = +inf, 1 / inf = 0, so sigmoid = 0 and silu = x * 0 = -0; -inf and NaN as the
+// reference's formula gives them.
+__device__ __forceinline__ float2 ew_sigmoid16_pair(float2 x) {
+  const float2 z = __fmul2_rn(x, make_float2(-1.4426950408889634f, -1.4426950408889634f));
+  float2 e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.x) : "f"(z.x));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e.y) : "f"(z.y));
+  const float2 d = __fadd2_rn(make_float2(1.0f, 1.0f), e);
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r.x) : "f"(d.x));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r.y) : "f"(d.y));
+  return r;
+}
 // Two values after a store to T and a load back.  For bfloat16 the packed conversion rounds both in
 // one instruction and a shift and a mask bring them back.
 template <typename T> __device__ __forceinline__ float2 round_pair_through(float2 v) {

@@ -34,6 +34,29 @@ __device__ __forceinline__ void pick(const float (&vals)[NIN][W], int idx, float
   }
 }
 
+// One step of a chain over a register vector, its result rounded to T (ROUND) as the unfused
+// chain's store would.
+template <typename T, int NIN, int W, bool ROUND>
+__device__ __forceinline__ void chain_vec_step(const ChainDesc& d, int s, const float (&vals)[NIN][W],
+                                               float (&cur)[W]) {
+  const int op = d.ops[s];
+  if (d.ext[s] >= 0) {
+    float rhs[W];
+    pick<NIN, W>(vals, d.ext[s], rhs);
+    if (op == FB200_EW_ADD || op == FB200_EW_MUL) {
+      ew_binary_round_vec<T, W, ROUND>(op, cur, rhs);
+    } else {
+#pragma unroll
+      for (int e = 0; e < W; ++e) {
+        const float y = ew_binary_any(op, cur[e], rhs[e]);
+        cur[e] = ROUND ? round_through<T>(y) : y;
+      }
+    }
+  } else {
+    ew_unary_vec<T, W, ROUND>(op, cur);
+  }
+}
+
 // NIN = number of external inputs held in registers (compile-time for register allocation).
 template <typename T, int NIN>
 __global__ void __launch_bounds__(256)
@@ -51,25 +74,7 @@ fused_chain_kernel(ChainDesc d, T* __restrict__ out, int64_t n_vec, int64_t nume
 #pragma unroll
     for (int e = 0; e < W; ++e) cur[e] = vals[0][e];
 #pragma unroll 1
-    for (int s = 0; s < d.n_ops; ++s) {
-      const int op = d.ops[s];
-      if (d.ext[s] >= 0) {
-        float rhs[W];
-        pick<NIN, W>(vals, d.ext[s], rhs);
-        if (op == FB200_EW_ADD) {
-#pragma unroll
-          for (int e = 0; e < W; ++e) cur[e] = round_through<T>(cur[e] + rhs[e]);
-        } else if (op == FB200_EW_MUL) {
-#pragma unroll
-          for (int e = 0; e < W; ++e) cur[e] = round_through<T>(cur[e] * rhs[e]);
-        } else {
-#pragma unroll
-          for (int e = 0; e < W; ++e) cur[e] = round_through<T>(ew_binary_any(op, cur[e], rhs[e]));
-        }
-      } else {
-        ew_unary_vec<T, W>(op, cur);
-      }
-    }
+    for (int s = 0; s < d.n_ops; ++s) chain_vec_step<T, NIN, W, true>(d, s, vals, cur);
     store_vec<T>(out + v * W, cur);
   }
   // Ragged tail (numel % W elements) and unaligned buffers: scalar path, first CTA only.

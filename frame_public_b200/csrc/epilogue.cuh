@@ -50,43 +50,60 @@ inline int make_epilogue(const fb200_epilogue* e, EpilogueDev* out, const char* 
 // One binary step over W values, the result rounded through T.  Sums and products of 16-bit
 // tensors go in packed fp32 pairs (one FMA-pipe instruction and one packed conversion per two
 // elements); the arithmetic and its rounding are those of the element-wise form.
-template <typename T, int W>
+// ROUND = false leaves the fp32 result unrounded for a caller that stores it to T next (the
+// store's conversion is then the one rounding).
+template <typename T, int W, bool ROUND = true>
 __device__ __forceinline__ void ew_binary_round_vec(int op, float* v, const float (&rhs)[W]) {
   if (sizeof(T) == 2 && W % 2 == 0 && (op == FB200_EW_ADD || op == FB200_EW_MUL)) {
 #pragma unroll
     for (int e = 0; e < W; e += 2) {
       const float2 a = make_float2(v[e], v[e + 1]), b = make_float2(rhs[e], rhs[e + 1]);
-      const float2 y = round_pair_through<T>(op == FB200_EW_ADD ? __fadd2_rn(a, b) : __fmul2_rn(a, b));
+      float2 y = op == FB200_EW_ADD ? __fadd2_rn(a, b) : __fmul2_rn(a, b);
+      if (ROUND) y = round_pair_through<T>(y);
       v[e] = y.x;
       v[e + 1] = y.y;
     }
     return;
   }
 #pragma unroll
-  for (int e = 0; e < W; ++e) v[e] = round_through<T>(ew_binary(op, v[e], rhs[e]));
+  for (int e = 0; e < W; ++e) {
+    const float y = ew_binary(op, v[e], rhs[e]);
+    v[e] = ROUND ? round_through<T>(y) : y;
+  }
 }
 
 // One unary step over a register vector, with the op switch hoisted out of the element loop.
-template <typename T, int NV>
+template <typename T, int NV, bool ROUND = true>
 __device__ __forceinline__ void ew_unary_vec(int op, float (&v)[NV]) {
-  if (sizeof(T) == 2 && op == FB200_EW_GELU) {
-    if constexpr (NV % 2 == 0) {
+  // 16-bit tensors: GELU, SiLU and sigmoid on packed fp32 pairs
+  if (sizeof(T) == 2 && NV % 2 == 0 && (op == FB200_EW_GELU || op == FB200_EW_SILU || op == FB200_EW_SIGMOID)) {
+    auto pairs = [&](auto&& f) {
 #pragma unroll
       for (int j = 0; j < NV; j += 2) {
-        const float2 y = round_pair_through<T>(ew_gelu16_pair(make_float2(v[j], v[j + 1])));
+        float2 y = f(make_float2(v[j], v[j + 1]));
+        if (ROUND) y = round_pair_through<T>(y);
         v[j] = y.x;
         v[j + 1] = y.y;
       }
+    };
+    if (op == FB200_EW_GELU) {
+      pairs([](float2 x) { return ew_gelu16_pair(x); });
+    } else if (op == FB200_EW_SILU) {
+      pairs([](float2 x) { return __fmul2_rn(x, ew_sigmoid16_pair(x)); });
     } else {
-#pragma unroll
-      for (int j = 0; j < NV; ++j) v[j] = round_through<T>(ew_gelu16(v[j]));
+      pairs([](float2 x) { return ew_sigmoid16_pair(x); });
     }
+    return;
+  }
+  if (sizeof(T) == 2 && op == FB200_EW_GELU) {
+#pragma unroll
+    for (int j = 0; j < NV; ++j) v[j] = ROUND ? round_through<T>(ew_gelu16(v[j])) : ew_gelu16(v[j]);
     return;
   }
   switch (op) {
 #define FB200_UNARY_CASE(code)                                                     \
   case code:                                                                       \
-    _Pragma("unroll") for (int j = 0; j < NV; ++j) v[j] = round_through<T>(ew_unary(code, v[j])); \
+    _Pragma("unroll") for (int j = 0; j < NV; ++j) v[j] = ROUND ? round_through<T>(ew_unary(code, v[j])) : ew_unary(code, v[j]); \
     break;
     FB200_UNARY_CASE(FB200_EW_RELU)
     FB200_UNARY_CASE(FB200_EW_SQUARE)
