@@ -159,8 +159,9 @@ __device__ __forceinline__ float2 ew_gelu16_pair(float2 x) {
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r.y) : "f"(d.y));
   return __fmul2_rn(x, r);
 }
-// sigmoid and SiLU for 16-bit results on two elements at once: 1 / (1 + 2^(-x log2 e)) through ex2
-// and rcp, about 1e-6 relative, far inside bf16 / f16 (fp32 tensors keep the two-branch form).
+// sigmoid and SiLU on two elements at once: 1 / (1 + 2^(-x log2 e)) through ex2 and rcp.  The error
+// is that of the two-branch form above (the rounding of the exponent's argument dominates both:
+// about 6e-8 |x| relative), inside the fp32 tolerance tier.
 // Large negative x: e = +inf, 1 / inf = 0, so sigmoid = 0 and silu = x * 0 = -0; -inf and NaN as the
 // reference's formula gives them.
 __device__ __forceinline__ float2 ew_sigmoid16_pair(float2 x) {

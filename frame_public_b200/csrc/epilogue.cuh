@@ -75,8 +75,8 @@ __device__ __forceinline__ void ew_binary_round_vec(int op, float* v, const floa
 // One unary step over a register vector, with the op switch hoisted out of the element loop.
 template <typename T, int NV, bool ROUND = true>
 __device__ __forceinline__ void ew_unary_vec(int op, float (&v)[NV]) {
-  // 16-bit tensors: GELU, SiLU and sigmoid on packed fp32 pairs
-  if (sizeof(T) == 2 && NV % 2 == 0 && (op == FB200_EW_GELU || op == FB200_EW_SILU || op == FB200_EW_SIGMOID)) {
+  // SiLU and sigmoid (every dtype) and GELU of 16-bit tensors on packed fp32 pairs
+  if (NV % 2 == 0 && (op == FB200_EW_SILU || op == FB200_EW_SIGMOID || (sizeof(T) == 2 && op == FB200_EW_GELU))) {
     auto pairs = [&](auto&& f) {
 #pragma unroll
       for (int j = 0; j < NV; j += 2) {
