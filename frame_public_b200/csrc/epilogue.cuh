@@ -76,7 +76,8 @@ __device__ __forceinline__ void ew_binary_round_vec(int op, float* v, const floa
 template <typename T, int NV, bool ROUND = true>
 __device__ __forceinline__ void ew_unary_vec(int op, float (&v)[NV]) {
   // SiLU and sigmoid (every dtype) and GELU of 16-bit tensors on packed fp32 pairs
-  if (NV % 2 == 0 && (op == FB200_EW_SILU || op == FB200_EW_SIGMOID || (sizeof(T) == 2 && op == FB200_EW_GELU))) {
+  if (NV % 2 == 0 && (op == FB200_EW_SILU || op == FB200_EW_SIGMOID || op == FB200_EW_SOFTPLUS ||
+                      (sizeof(T) == 2 && op == FB200_EW_GELU))) {
     auto pairs = [&](auto&& f) {
 #pragma unroll
       for (int j = 0; j < NV; j += 2) {
@@ -90,6 +91,8 @@ __device__ __forceinline__ void ew_unary_vec(int op, float (&v)[NV]) {
       pairs([](float2 x) { return ew_gelu16_pair(x); });
     } else if (op == FB200_EW_SILU) {
       pairs([](float2 x) { return __fmul2_rn(x, ew_sigmoid16_pair(x)); });
+    } else if (op == FB200_EW_SOFTPLUS) {
+      pairs([](float2 x) { return ew_softplus_pair(x); });
     } else {
       pairs([](float2 x) { return ew_sigmoid16_pair(x); });
     }
