@@ -47,14 +47,14 @@ inline int make_epilogue(const fb200_epilogue* e, EpilogueDev* out, const char* 
   return FB200_OK;
 }
 
-// One binary step over W values, the result rounded through T.  Sums and products of 16-bit
-// tensors go in packed fp32 pairs (one FMA-pipe instruction and one packed conversion per two
-// elements); the arithmetic and its rounding are those of the element-wise form.
+// One binary step over W values, the result rounded through T.  Sums and products go in packed
+// fp32 pairs (one FMA-pipe instruction per two elements and, for 16-bit tensors, one packed
+// conversion); the arithmetic and its rounding are those of the element-wise form.
 // ROUND = false leaves the fp32 result unrounded for a caller that stores it to T next (the
 // store's conversion is then the one rounding).
 template <typename T, int W, bool ROUND = true>
 __device__ __forceinline__ void ew_binary_round_vec(int op, float* v, const float (&rhs)[W]) {
-  if (sizeof(T) == 2 && W % 2 == 0 && (op == FB200_EW_ADD || op == FB200_EW_MUL)) {
+  if (W % 2 == 0 && (op == FB200_EW_ADD || op == FB200_EW_MUL)) {
 #pragma unroll
     for (int e = 0; e < W; e += 2) {
       const float2 a = make_float2(v[e], v[e + 1]), b = make_float2(rhs[e], rhs[e + 1]);
