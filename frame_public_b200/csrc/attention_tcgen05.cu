@@ -143,42 +143,32 @@ attention_fan_kernel(const __grid_constant__ CUtensorMap tmap_q,
   const int n_chunks = sk >> 6;   // 64-key blocks of P per query block
   const fb200_attention_head h = heads[head];
 
-  if (tid == 0) {
-    mbar_init(bar_q, 1);
-    mbar_init(bar_k, 1);
-    mbar_init(bar_v, 1);
-    mbar_init(bar_s, 1);
-    mbar_init(bar_su, 1);
-    mbar_init(bar_o, 1);
-    mbar_init(bar_oread, kAttnSoftmaxThreads / 32);
-    for (int i = 0; i < kAttnPRing; ++i) {
-      mbar_init(p_full + 8 * i, kAttnSoftmaxThreads / 32);
-      mbar_init(p_free + 8 * i, 1);
-    }
-    mbar_fence_init();
-    tma_prefetch_desc(&tmap_q);
-    tma_prefetch_desc(&tmap_k);
-    tma_prefetch_desc(&tmap_v);
-  }
-  if (warp == 0) {
-    __syncwarp();
-    tmem_alloc(tmem_slot, tmem_cols);
-    tmem_relinquish();
-  }
-  tcgen05_fence_before_sync();
-  __syncthreads();
-  tcgen05_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot_ptr;
-
   // A TMA copy whose innermost coordinate is not 16-byte aligned is an illegal instruction, so a
   // bad table entry is refused here, before any copy is issued.
   const bool head_ok = ((h.q_col | h.k_col | h.v_col) & 7) == 0 && (h.o_offset & 7) == 0;
   if (!head_ok && tid == 0) *reinterpret_cast<volatile int*>(status) = kFaultAttnBadHead;
 
+  // The control warp sets the barriers up and sends the first copies on their way before the CTA
+  // meets: K, Q and V travel while warp 0 allocates TMEM.
   if (warp == kAttnCtrlWarp) {
-    // ---- control warp: every copy and every tensor-core instruction, issued by one elected lane
-    // of warp-uniform code (descriptors then stay in uniform registers, which is what keeps the
-    // issue of the small P V instructions cheap) ------------------------------------------------------
+    if ((tid & 31) == 0) {
+      mbar_init(bar_q, 1);
+      mbar_init(bar_k, 1);
+      mbar_init(bar_v, 1);
+      mbar_init(bar_s, 1);
+      mbar_init(bar_su, 1);
+      mbar_init(bar_o, 1);
+      mbar_init(bar_oread, kAttnSoftmaxThreads / 32);
+      for (int i = 0; i < kAttnPRing; ++i) {
+        mbar_init(p_full + 8 * i, kAttnSoftmaxThreads / 32);
+        mbar_init(p_free + 8 * i, 1);
+      }
+      mbar_fence_init();
+      tma_prefetch_desc(&tmap_q);
+      tma_prefetch_desc(&tmap_k);
+      tma_prefetch_desc(&tmap_v);
+    }
+    __syncwarp();
     if (head_ok) {
       mbar_arrive_expect_tx_elect(bar_k, static_cast<uint32_t>(sk) * 128u);
       for (int r = 0; r < sk; r += kAttnKvBoxRows) {
@@ -190,6 +180,23 @@ attention_fan_kernel(const __grid_constant__ CUtensorMap tmap_q,
       for (int r = 0; r < sk; r += kAttnKvBoxRows) {
         tma_load_2d_elect(v_s + static_cast<uint32_t>(r) * 128u, &tmap_v, bar_v, h.v_col, h.v_row + r);
       }
+    }
+  }
+  if (warp == 0) {
+    __syncwarp();
+    tmem_alloc(tmem_slot, tmem_cols);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == kAttnCtrlWarp) {
+    // ---- control warp: every copy and every tensor-core instruction, issued by one elected lane
+    // of warp-uniform code (descriptors then stay in uniform registers, which is what keeps the
+    // issue of the small P V instructions cheap) ------------------------------------------------------
+    if (head_ok) {
       // Descriptors differ only in the start address (bits 0-13, in 16-byte units), so a step is an add.
       const uint32_t idesc_pv = make_instr_desc(fmt, 0, 1, kAttnBlockM, kAttnHeadDim);
       const uint64_t q_desc = make_smem_desc_sw128(q_s, 16, 1024);
