@@ -658,7 +658,23 @@ static void optimise(fb200_plan* p) {
       for (int in : s.in) if (ranges_overlap(*p, t.out[0], in)) overlap = true;
       for (int os : s.epi_operand_slot) if (os >= 0 && ranges_overlap(*p, t.out[0], os)) overlap = true;
       for (int e : ext) if (ranges_overlap(*p, t.out[0], e)) overlap = true;
-      if (overlap) break;
+      if (overlap) {
+        // The planner laid the arena out for the separate steps and reused bytes that the
+        // contraction still reads (typically its own A operand) for the group's result.  A private
+        // buffer for that result removes the conflict.
+        SlotInfo& os = p->slots[static_cast<size_t>(root_slot(*p, t.out[0]))];
+        if (os.input_index >= 0 || os.output_index >= 0 || os.constant != nullptr || os.arena_offset < 0) break;
+        // a single add in front of a LayerNorm is left to that rewrite (one pass over the rows
+        // instead of an epilogue that nothing overlaps)
+        if (j + 1 < n && p->steps[static_cast<size_t>(j + 1)].kind == Kind::kLayerNorm &&
+            !p->steps[static_cast<size_t>(j + 1)].in.empty() && p->steps[static_cast<size_t>(j + 1)].in[0] == t.out[0] &&
+            t.chain_ops.size() == 1 && t.chain_ops[0] == FB200_EW_ADD) break;
+        os.private_index = static_cast<int>(p->private_bytes.size());
+        p->private_bytes.push_back(os.bytes());
+        os.arena_offset = -1;
+        PLAN_TRACE("step %d: the epilogue's result overlapped an operand of the contraction at step %d and moves to a private buffer (%zu bytes)",
+                   j, i, os.bytes());
+      }
       if (t.kind == Kind::kBiasAdd) {
         if (s.kind != Kind::kMatmul || ext.size() != 1) break;
         s.chain_ops.push_back(FB200_EW_ADD);

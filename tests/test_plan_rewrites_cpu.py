@@ -66,12 +66,16 @@ def test_mamba_conv_group_and_reshape_views():
     assert small.count("dwconv1d_time_major") == 0 and small.count("conv1d") == 1
 
 
-def test_mlp_absorbs_what_the_planner_allows():
-    names, launches = runtime.describe_plan(_golden("mlp_f32_b8"))
-    assert launches == 5
-    assert _live(names) == ["matmul+epilogue", "matmul", "fused_elementwise_internal", "matmul+epilogue",
-                            "softmax"]
-    _, plain = runtime.describe_plan(_golden("mlp_f32_b8"), opt_level=0)
+def test_mlp_absorbs_every_group_the_second_through_a_private_buffer():
+    """The planner puts the second hidden layer's add;relu result on the bytes of that layer's own
+    matmul input (dead in the unfused order once the matmul has run); as the matmul's epilogue it
+    would overwrite rows other CTAs still read, so the result moves to a private buffer."""
+    text = _golden("mlp_f32_b8")
+    names, launches = runtime.describe_plan(text)
+    assert launches == 4
+    assert _live(names) == ["matmul+epilogue", "matmul+epilogue", "matmul+epilogue", "softmax"]
+    assert runtime.plan_private_bytes(text) == 8 * 32 * 4   # the miniature has 32 hidden units
+    _, plain = runtime.describe_plan(text, opt_level=0)
     assert plain == 7
 
 

@@ -54,12 +54,13 @@ def test_epilogue_absorption_reduces_launches():
     fused = runtime.CompiledPlan(_plan_text(wl.name), 0, opt_level=1)
     plain = runtime.CompiledPlan(_plan_text(wl.name), 0, opt_level=0)
     assert plain.launches_per_run == 7
-    # matmul+add;relu, matmul, add;relu, matmul+add, softmax: the second group is NOT absorbed,
-    # because the planner placed its output on the bytes of that matmul's own input.
-    assert fused.launches_per_run == 5
+    # matmul+add;relu, matmul+add;relu, matmul+add, softmax: the planner placed the second group's
+    # output on the bytes of that matmul's own input, so the fused result goes to a private buffer.
+    assert fused.launches_per_run == 4
+    assert fused.private_bytes > 0 and plain.private_bytes == 0
     before = capi.launch_count()
     fused.run_host(wl.inputs)
-    assert capi.launch_count() - before == 5
+    assert capi.launch_count() - before == 4
 
 
 def test_unknown_op_is_unimplemented_with_its_name():
